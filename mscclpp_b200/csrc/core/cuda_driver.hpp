@@ -1,0 +1,42 @@
+// CUDA driver API entry points, resolved at run time through cudaGetDriverEntryPoint so that the
+// library links against nothing but the (static) CUDA runtime and can be imported on machines
+// without a GPU or a driver.
+#pragma once
+
+#include <cuda.h>
+
+namespace mscclpp {
+
+struct CudaDriver {
+  // Returns the table, loading it on first use. Throws Error(SystemError) when the driver is absent.
+  static const CudaDriver& get();
+  // Like get() but returns nullptr instead of throwing.
+  static const CudaDriver* tryGet();
+
+  CUresult (*cuMemCreate)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long);
+  CUresult (*cuMemRelease)(CUmemGenericAllocationHandle);
+  CUresult (*cuMemAddressReserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long);
+  CUresult (*cuMemAddressFree)(CUdeviceptr, size_t);
+  CUresult (*cuMemMap)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long);
+  CUresult (*cuMemUnmap)(CUdeviceptr, size_t);
+  CUresult (*cuMemSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t);
+  CUresult (*cuMemGetAllocationGranularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags);
+  CUresult (*cuMemExportToShareableHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType,
+                                           unsigned long long);
+  CUresult (*cuMemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType);
+  CUresult (*cuMemRetainAllocationHandle)(CUmemGenericAllocationHandle*, void*);
+  CUresult (*cuMemGetAddressRange)(CUdeviceptr*, size_t*, CUdeviceptr);
+  CUresult (*cuMulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*);
+  CUresult (*cuMulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice);
+  CUresult (*cuMulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle, size_t, size_t,
+                                 unsigned long long);
+  CUresult (*cuMulticastBindAddr)(CUmemGenericAllocationHandle, size_t, CUdeviceptr, size_t, unsigned long long);
+  CUresult (*cuMulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t);
+  CUresult (*cuMulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags);
+  CUresult (*cuDeviceGet)(CUdevice*, int);
+  CUresult (*cuDeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
+  CUresult (*cuPointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr);
+  CUresult (*cuGetErrorString)(CUresult, const char**);
+};
+
+}  // namespace mscclpp

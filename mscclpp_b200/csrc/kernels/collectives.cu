@@ -1,0 +1,502 @@
+// Native sm_100a collective kernels on the symmetric heap.
+//
+//  * allreduceLLKernel   one-shot LL16: each rank stores its whole input as {data,flag} packets into
+//                        every peer's scratch (plain peer stores, or ONE multimem.st that the NVSwitch
+//                        replicates), then reduces the N packet streams locally. No barrier at all.
+//                        Role of the reference's allreduce_packet / allpair_packet / nvls_packet
+//                        (src/ext/collectives/allreduce/allreduce_packet.cu:15-151,
+//                         allreduce_allpair_packet.cu:15-69, allreduce_nvls_packet.cu:14-56).
+//  * twoShotKernel       zero-copy reduce-scatter + all-gather in one pass: a rank reduces its 1/N of
+//                        the buffer straight out of all peers' inputs (peer loads or
+//                        multimem.ld_reduce) and writes the result into all peers' outputs (peer
+//                        stores or multimem.st). Role of allreduce_rsag_zero_copy.cu:41-113 and
+//                        allreduce_nvls_zero_copy.cu:16-69. Also serves standalone reduce-scatter
+//                        and allgather (allgather_fullmesh_2.cu:11-118).
+//  Both take an optional fused epilogue that the reference does not have: add a residual stream and
+//  apply RMSNorm on the reduced rows before they are written, so the TP layer's allreduce,
+//  residual-add and norm are one kernel.
+#include "collectives.cuh"
+
+#include <mscclpp/packet_device.hpp>
+
+namespace mscclpp {
+
+namespace {
+
+template <typename T>
+struct ElemOf {
+  using type = T;
+};
+
+MSCCLPP_DEVICE_INLINE uint4 loadUnit(const char* base, uint64_t u, uint64_t bytes) {
+  const uint64_t off = u * 16;
+  if (off + 16 <= bytes) return *reinterpret_cast<const uint4*>(base + off);
+  uint32_t w[4] = {0, 0, 0, 0};
+  for (uint64_t i = off; i < bytes; i++) {
+    w[(i - off) >> 2] |= static_cast<uint32_t>(static_cast<uint8_t>(base[i])) << (8 * ((i - off) & 3));
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+MSCCLPP_DEVICE_INLINE void storeUnit(char* base, uint64_t u, uint64_t bytes, uint4 v) {
+  const uint64_t off = u * 16;
+  if (off + 16 <= bytes) {
+    *reinterpret_cast<uint4*>(base + off) = v;
+    return;
+  }
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  for (uint64_t i = off; i < bytes; i++) base[i] = static_cast<char>(w[(i - off) >> 2] >> (8 * ((i - off) & 3)));
+}
+
+// Running reduction over 16-byte words. Callers feed the contributions in rank order so that every
+// rank computes bit-identical results. Float-like types accumulate in fp32 and round once.
+template <typename T, ReduceOp Op, bool kFloat = IsFloatLike<T>::value>
+struct Accum;
+template <typename T, ReduceOp Op>
+struct Accum<T, Op, true> {
+  float acc[Vec16<T>::kElems];
+  MSCCLPP_DEVICE_INLINE void init(uint4 v) { Vec16<T>::toFloat(v, acc); }
+  MSCCLPP_DEVICE_INLINE void add(uint4 v) { accumulate16<T, Op>(acc, v); }
+  MSCCLPP_DEVICE_INLINE uint4 result() const { return Vec16<T>::fromFloat(acc); }
+};
+template <typename T, ReduceOp Op>
+struct Accum<T, Op, false> {
+  uint4 acc;
+  MSCCLPP_DEVICE_INLINE void init(uint4 v) { acc = v; }
+  MSCCLPP_DEVICE_INLINE void add(uint4 v) { acc = reduce16<T, Op>(acc, v); }
+  MSCCLPP_DEVICE_INLINE uint4 result() const { return acc; }
+};
+
+// Block-wide sum of one float per thread (blockDim.x <= 1024).
+MSCCLPP_DEVICE_INLINE float blockSum(float v) {
+  __shared__ float warpSums[32];
+  __shared__ float total;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();  // protects warpSums/total against the previous call
+  if (lane == 0) warpSums[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float s = (lane < (blockDim.x + 31) / 32) ? warpSums[lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) total = s;
+  }
+  __syncthreads();
+  return total;
+}
+
+// x = reduced + residual (rounded to T); returns sum of squares of the rounded values.
+template <typename T>
+MSCCLPP_DEVICE_INLINE float addResidual(uint4& x, uint4 residual, bool hasResidual) {
+  float f[Vec16<T>::kElems];
+  Vec16<T>::toFloat(x, f);
+  if (hasResidual) {
+    float r[Vec16<T>::kElems];
+    Vec16<T>::toFloat(residual, r);
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::kElems; i++) f[i] += r[i];
+    x = Vec16<T>::fromFloat(f);
+    Vec16<T>::toFloat(x, f);
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < Vec16<T>::kElems; i++) ss += f[i] * f[i];
+  return ss;
+}
+
+template <typename T>
+MSCCLPP_DEVICE_INLINE uint4 scaleRow(uint4 x, float rinv, const char* gamma, uint64_t unitInRow) {
+  float f[Vec16<T>::kElems];
+  Vec16<T>::toFloat(x, f);
+  if (gamma != nullptr) {
+    float g[Vec16<T>::kElems];
+    Vec16<T>::toFloat(*reinterpret_cast<const uint4*>(gamma + unitInRow * 16), g);
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::kElems; i++) f[i] = f[i] * rinv * g[i];
+  } else {
+#pragma unroll
+    for (int i = 0; i < Vec16<T>::kElems; i++) f[i] = f[i] * rinv;
+  }
+  return Vec16<T>::fromFloat(f);
+}
+
+// ============================================================================================
+// One-shot LL16 allreduce
+// ============================================================================================
+template <typename T, ReduceOp Op, bool kNvls, bool kNorm>
+__global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
+  const DeviceComm& c = a.comm;
+  const int rank = deviceRank(c);
+  const int world = c.world;
+  const uint64_t emu = static_cast<uint64_t>(blockIdx.y) * a.emuStride;
+  const char* in = reinterpret_cast<const char*>(a.in) + emu;
+  char* out = reinterpret_cast<char*>(a.out) + emu;
+  const uint32_t flag = launchEpoch(c, rank);
+  const uint64_t bufOff = c.llScratchOff + static_cast<uint64_t>(flag & 1u) * (static_cast<uint64_t>(world) * c.llSlotBytes);
+  const uint64_t bytes = a.bytes;
+  const uint64_t nunits = (bytes + 15) / 16;
+
+  // ---- unit iteration space: flat (plain allreduce) or row-per-block (fused norm)
+  const uint64_t unitsPerRow = kNorm ? (static_cast<uint64_t>(a.hidden) * sizeof(T)) / 16 : 0;
+
+  // ---- send: my whole input to every peer
+  {
+    const uint64_t start = kNorm ? 0 : static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint64_t step = kNorm ? 0 : static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    auto sendUnit = [&](uint64_t u) {
+      const uint4 d = loadUnit(in, u, bytes);
+      if constexpr (kNvls) {
+        char* mc = reinterpret_cast<char*>(c.mcBase + bufOff + static_cast<uint64_t>(rank) * c.llSlotBytes + u * 32);
+        ptx::multimem_st_v4(mc, make_uint4(d.x, flag, d.y, flag));
+        ptx::multimem_st_v4(mc + 16, make_uint4(d.z, flag, d.w, flag));
+      } else {
+        for (int i = 1; i < world; i++) {
+          const int p = (rank + i) % world;
+          LL16Packet* pk = reinterpret_cast<LL16Packet*>(c.peerBase[p] + bufOff +
+                                                         static_cast<uint64_t>(rank) * c.llSlotBytes + u * 32);
+          pk[0].write(d.x, d.y, flag);
+          pk[1].write(d.z, d.w, flag);
+        }
+      }
+    };
+    if constexpr (kNorm) {
+      for (int row = blockIdx.x; row < a.rows; row += gridDim.x)
+        for (uint64_t ru = threadIdx.x; ru < unitsPerRow; ru += blockDim.x) sendUnit(row * unitsPerRow + ru);
+    } else {
+      for (uint64_t u = start; u < nunits; u += step) sendUnit(u);
+    }
+  }
+
+  // ---- receive + reduce
+  bool healthy = true;
+  auto recvUnit = [&](uint64_t u, uint4& result) -> bool {
+    const uint4 own = loadUnit(in, u, bytes);
+    Accum<T, Op> acc;
+    for (int p = 0; p < world; p++) {
+      uint4 v = own;
+      if (p != rank) {
+        const LL16Packet* pk = reinterpret_cast<const LL16Packet*>(c.peerBase[rank] + bufOff +
+                                                                   static_cast<uint64_t>(p) * c.llSlotBytes + u * 32);
+        uint2 lo, hi;
+        if (!pk[0].read(flag, lo, c.status, c.timeoutNs, rank, p)) return false;
+        if (!pk[1].read(flag, hi, c.status, c.timeoutNs, rank, p)) return false;
+        v = make_uint4(lo.x, lo.y, hi.x, hi.y);
+      }
+      if (p == 0) acc.init(v); else acc.add(v);
+    }
+    result = acc.result();
+    return true;
+  };
+
+  if constexpr (!kNorm) {
+    const uint64_t start = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const uint64_t step = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+    for (uint64_t u = start; u < nunits && healthy; u += step) {
+      uint4 r;
+      healthy = recvUnit(u, r);
+      if (healthy) storeUnit(out, u, bytes, r);
+    }
+  } else {
+    const char* resIn = a.residualIn ? reinterpret_cast<const char*>(a.residualIn) + emu : nullptr;
+    char* resOut = a.residualOut ? reinterpret_cast<char*>(a.residualOut) + emu : nullptr;
+    const char* gamma = reinterpret_cast<const char*>(a.gamma);
+    char* stash = resOut ? resOut : out;  // where the un-normalised row lives between the passes
+    for (int row = blockIdx.x; row < a.rows; row += gridDim.x) {
+      float ss = 0.f;
+      for (uint64_t ru = threadIdx.x; ru < unitsPerRow; ru += blockDim.x) {
+        const uint64_t u = row * unitsPerRow + ru;
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (healthy) healthy = recvUnit(u, x);
+        uint4 res = resIn ? *reinterpret_cast<const uint4*>(resIn + u * 16) : make_uint4(0, 0, 0, 0);
+        ss += addResidual<T>(x, res, resIn != nullptr);
+        *reinterpret_cast<uint4*>(stash + u * 16) = x;
+      }
+      const float total = blockSum(ss);
+      const float rinv = rsqrtf(total / static_cast<float>(a.hidden) + a.eps);
+      for (uint64_t ru = threadIdx.x; ru < unitsPerRow; ru += blockDim.x) {
+        const uint64_t u = row * unitsPerRow + ru;
+        const uint4 x = *reinterpret_cast<const uint4*>(stash + u * 16);  // written by this same thread
+        *reinterpret_cast<uint4*>(out + u * 16) = scaleRow<T>(x, rinv, gamma, ru);
+      }
+    }
+  }
+  finishLaunch(c, rank, flag);
+}
+
+// ============================================================================================
+// Two-shot zero-copy (peer loads/stores or NVLS multimem)
+// ============================================================================================
+template <typename T, ReduceOp Op>
+MSCCLPP_DEVICE_INLINE uint4 multimemLoadReduce(const void* mc) {
+  if constexpr (__is_same(T, __half)) {
+    if constexpr (Op == SUM) return ptx::multimem_ld_reduce_add_f16x2_acc32(mc);
+    else return ptx::multimem_ld_reduce_min_f16x2(mc);
+  } else if constexpr (__is_same(T, __nv_bfloat16)) {
+    if constexpr (Op == SUM) return ptx::multimem_ld_reduce_add_bf16x2_acc32(mc);
+    else return ptx::multimem_ld_reduce_min_bf16x2(mc);
+  } else if constexpr (__is_same(T, float)) {
+    return ptx::multimem_ld_reduce_add_f32(mc);
+  } else if constexpr (__is_same(T, f8e4m3)) {
+    return ptx::multimem_ld_reduce_add_e4m3x4(mc);
+  } else if constexpr (__is_same(T, f8e5m2)) {
+    return ptx::multimem_ld_reduce_add_e5m2x4(mc);
+  } else if constexpr (__is_same(T, int32_t)) {
+    uint4 v;
+    const char* p = reinterpret_cast<const char*>(mc);
+    v.x = ptx::multimem_ld_reduce_add_s32(p);
+    v.y = ptx::multimem_ld_reduce_add_s32(p + 4);
+    v.z = ptx::multimem_ld_reduce_add_s32(p + 8);
+    v.w = ptx::multimem_ld_reduce_add_s32(p + 12);
+    return v;
+  } else {
+    uint4 v;
+    const char* p = reinterpret_cast<const char*>(mc);
+    v.x = ptx::multimem_ld_reduce_add_u32(p);
+    v.y = ptx::multimem_ld_reduce_add_u32(p + 4);
+    v.z = ptx::multimem_ld_reduce_add_u32(p + 8);
+    v.w = ptx::multimem_ld_reduce_add_u32(p + 12);
+    return v;
+  }
+}
+
+// Which (type, op) pairs the switch can reduce by itself.
+template <typename T, ReduceOp Op>
+constexpr bool nvlsReducible() {
+  if (__is_same(T, __half) || __is_same(T, __nv_bfloat16)) return true;
+  if (Op != SUM) return false;
+  return __is_same(T, float) || __is_same(T, int32_t) || __is_same(T, uint32_t) || __is_same(T, f8e4m3) ||
+         __is_same(T, f8e5m2);
+}
+
+// Gather the `world` contributions of 16-byte unit at byte offset `off` of the symmetric `in`.
+template <typename T, ReduceOp Op, bool kNvls>
+MSCCLPP_DEVICE_INLINE uint4 gatherReduce(const DeviceComm& c, int rank, uint64_t inOff, uint64_t off) {
+  if constexpr (kNvls) {
+    return multimemLoadReduce<T, Op>(reinterpret_cast<const void*>(c.mcBase + inOff + off));
+  } else {
+    Accum<T, Op> acc;
+    if (c.world <= 8) {
+      // issue every peer load before the first use so that all of them are in flight together
+      uint4 v[8];
+#pragma unroll
+      for (int p = 0; p < 8; p++)
+        if (p < c.world) v[p] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(c.peerBase[p] + inOff + off));
+      acc.init(v[0]);
+#pragma unroll
+      for (int p = 1; p < 8; p++)
+        if (p < c.world) acc.add(v[p]);
+    } else {
+      acc.init(ptx::ld_nc_na_v4(reinterpret_cast<const void*>(c.peerBase[0] + inOff + off)));
+      for (int p = 1; p < c.world; p++)
+        acc.add(ptx::ld_nc_na_v4(reinterpret_cast<const void*>(c.peerBase[p] + inOff + off)));
+    }
+    return acc.result();
+  }
+}
+
+template <bool kNvls>
+MSCCLPP_DEVICE_INLINE void scatterStore(const DeviceComm& c, int rank, uint64_t outOff, uint64_t off, uint4 v) {
+  if constexpr (kNvls) {
+    ptx::multimem_st_v4(reinterpret_cast<void*>(c.mcBase + outOff + off), v);
+  } else {
+    for (int i = 0; i < c.world; i++) {
+      const int p = (rank + i) % c.world;
+      ptx::st_na_v4(reinterpret_cast<void*>(c.peerBase[p] + outOff + off), v);
+    }
+  }
+}
+
+MSCCLPP_DEVICE_INLINE uint64_t splitStart(uint64_t total, int parts, int i) {
+  const uint64_t q = total / parts, r = total % parts;
+  return static_cast<uint64_t>(i) * q + (static_cast<uint64_t>(i) < r ? i : r);
+}
+
+template <typename T, ReduceOp Op, bool kNvls, bool kNorm>
+__global__ void __launch_bounds__(512, 1) twoShotKernel(CollArgs a) {
+  const DeviceComm& c = a.comm;
+  const int rank = deviceRank(c);
+  const int world = c.world;
+  // `in`/`out` are given for rank comm.rank; emulated ranks sit at the same heap offset.
+  const uint64_t inOff = reinterpret_cast<uint64_t>(a.in) - c.peerBase[c.rank];
+  const uint64_t outOff = reinterpret_cast<uint64_t>(a.out) - c.peerBase[c.rank];
+  const uint32_t epoch = launchEpoch(c, rank);
+  const int slot = blockIdx.x;
+
+  bool healthy = rankBarrier(c, rank, 0, slot, epoch);
+
+  if (healthy) {
+    if constexpr (kNorm) {
+      // rows are split over ranks; a block owns whole rows so it can take the row norm
+      const uint64_t unitsPerRow = (static_cast<uint64_t>(a.hidden) * sizeof(T)) / 16;
+      const int rowBegin = static_cast<int>(splitStart(a.rows, world, rank));
+      const int rowEnd = static_cast<int>(splitStart(a.rows, world, rank + 1));
+      const uint64_t resInOff = a.residualIn ? reinterpret_cast<uint64_t>(a.residualIn) - c.peerBase[c.rank] : 0;
+      const uint64_t resOutOff = a.residualOut ? reinterpret_cast<uint64_t>(a.residualOut) - c.peerBase[c.rank] : 0;
+      const char* gamma = reinterpret_cast<const char*>(a.gamma);
+      const uint64_t local = c.peerBase[rank];
+      // un-normalised row is stashed in the local residualOut (or local out) between the two passes
+      const uint64_t stashOff = a.residualOut ? resOutOff : outOff;
+      for (int row = rowBegin + blockIdx.x; row < rowEnd; row += gridDim.x) {
+        float ss = 0.f;
+        for (uint64_t ru = threadIdx.x; ru < unitsPerRow; ru += blockDim.x) {
+          const uint64_t off = (row * unitsPerRow + ru) * 16;
+          uint4 x = gatherReduce<T, Op, kNvls>(c, rank, inOff, off);
+          uint4 res = a.residualIn ? *reinterpret_cast<const uint4*>(local + resInOff + off) : make_uint4(0, 0, 0, 0);
+          ss += addResidual<T>(x, res, a.residualIn != nullptr);
+          if (a.residualOut && a.broadcastResidual) {
+            scatterStore<kNvls>(c, rank, resOutOff, off, x);
+            if constexpr (kNvls) *reinterpret_cast<uint4*>(local + stashOff + off) = x;  // keep a locally ordered copy
+          } else {
+            *reinterpret_cast<uint4*>(local + stashOff + off) = x;
+          }
+        }
+        const float total = blockSum(ss);
+        const float rinv = rsqrtf(total / static_cast<float>(a.hidden) + a.eps);
+        for (uint64_t ru = threadIdx.x; ru < unitsPerRow; ru += blockDim.x) {
+          const uint64_t off = (row * unitsPerRow + ru) * 16;
+          const uint4 x = *reinterpret_cast<const uint4*>(local + stashOff + off);
+          scatterStore<kNvls>(c, rank, outOff, off, scaleRow<T>(x, rinv, gamma, ru));
+        }
+      }
+    } else if (a.mode == kAllGather) {
+      // `in` = my slice (bytes/world), `out` = whole buffer on every rank
+      const uint64_t sliceUnits = a.bytes / 16 / world;
+      const uint64_t dst0 = static_cast<uint64_t>(rank) * sliceUnits * 16;
+      const uint64_t local = c.peerBase[rank];
+      for (uint64_t u = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < sliceUnits;
+           u += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+        const uint4 v = *reinterpret_cast<const uint4*>(local + inOff + u * 16);
+        scatterStore<kNvls>(c, rank, outOff, dst0 + u * 16, v);
+      }
+    } else {
+      const uint64_t nunits = a.bytes / 16;
+      const uint64_t begin = splitStart(nunits, world, rank), end = splitStart(nunits, world, rank + 1);
+      const uint64_t local = c.peerBase[rank];
+      // 4 independent 16-byte requests per thread keep enough bytes in flight over NVLink
+      constexpr int kUnroll = 4;
+      const uint64_t tid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+      const uint64_t nthreads = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+      for (uint64_t u0 = begin + tid; u0 < end; u0 += nthreads * kUnroll) {
+        uint4 r[kUnroll];
+#pragma unroll
+        for (int k = 0; k < kUnroll; k++) {
+          const uint64_t u = u0 + k * nthreads;
+          if (u < end) r[k] = gatherReduce<T, Op, kNvls>(c, rank, inOff, u * 16);
+        }
+#pragma unroll
+        for (int k = 0; k < kUnroll; k++) {
+          const uint64_t u = u0 + k * nthreads;
+          if (u < end) {
+            if (a.mode == kReduceScatter)
+              *reinterpret_cast<uint4*>(local + outOff + (u - begin) * 16) = r[k];
+            else
+              scatterStore<kNvls>(c, rank, outOff, u * 16, r[k]);
+          }
+        }
+      }
+    }
+  }
+  // all my stores are issued; tell the peers, and learn that theirs into my buffers are done
+  if (healthy) rankBarrier(c, rank, 1, slot, epoch);
+  finishLaunch(c, rank, epoch);
+}
+
+// --------------------------------------------------------------------------------------------
+template <typename KernelT>
+cudaError_t launchMaybeCooperative(KernelT kernel, const CollArgs& args, int nBlocks, int nThreads, cudaStream_t stream) {
+  dim3 grid(nBlocks, args.emuRanks > 1 ? args.emuRanks : 1, 1);
+  dim3 block(nThreads, 1, 1);
+  if (args.emuRanks > 1) {
+    // emulated ranks wait on one another inside one grid: it has to be co-resident
+    CollArgs copy = args;
+    void* params[] = {&copy};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), grid, block, params, 0, stream);
+  }
+  kernel<<<grid, block, 0, stream>>>(args);
+  return cudaGetLastError();
+}
+
+template <typename T, ReduceOp Op>
+cudaError_t launchLLTyped(const CollArgs& a, int nBlocks, int nThreads, cudaStream_t s) {
+  if (a.norm) {
+    if constexpr (IsFloatLike<T>::value && Op == SUM && sizeof(T) >= 2) {
+      return a.nvls ? launchMaybeCooperative(allreduceLLKernel<T, Op, true, true>, a, nBlocks, nThreads, s)
+                    : launchMaybeCooperative(allreduceLLKernel<T, Op, false, true>, a, nBlocks, nThreads, s);
+    } else {
+      return cudaErrorInvalidValue;
+    }
+  }
+  return a.nvls ? launchMaybeCooperative(allreduceLLKernel<T, Op, true, false>, a, nBlocks, nThreads, s)
+                : launchMaybeCooperative(allreduceLLKernel<T, Op, false, false>, a, nBlocks, nThreads, s);
+}
+
+template <typename T, ReduceOp Op>
+cudaError_t launchTwoShotTyped(const CollArgs& a, int nBlocks, int nThreads, cudaStream_t s) {
+  if (a.norm) {
+    if constexpr (IsFloatLike<T>::value && Op == SUM && sizeof(T) >= 2) {
+      if (a.nvls) return launchMaybeCooperative(twoShotKernel<T, Op, true, true>, a, nBlocks, nThreads, s);
+      return launchMaybeCooperative(twoShotKernel<T, Op, false, true>, a, nBlocks, nThreads, s);
+    } else {
+      return cudaErrorInvalidValue;
+    }
+  }
+  if (a.nvls && a.mode != kAllGather) {
+    if constexpr (nvlsReducible<T, Op>()) {
+      return launchMaybeCooperative(twoShotKernel<T, Op, true, false>, a, nBlocks, nThreads, s);
+    } else {
+      return cudaErrorInvalidValue;
+    }
+  }
+  if (a.nvls) return launchMaybeCooperative(twoShotKernel<uint32_t, SUM, true, false>, a, nBlocks, nThreads, s);
+  return launchMaybeCooperative(twoShotKernel<T, Op, false, false>, a, nBlocks, nThreads, s);
+}
+
+#define MSCCLPP_DISPATCH_TYPE_OP(FN, dtype, op, ...)                                               \
+  do {                                                                                             \
+    const bool isMin = (op) == MIN;                                                                \
+    switch (dtype) {                                                                               \
+      case DataType::FLOAT16:                                                                      \
+        return isMin ? FN<__half, MIN>(__VA_ARGS__) : FN<__half, SUM>(__VA_ARGS__);                \
+      case DataType::BFLOAT16:                                                                     \
+        return isMin ? FN<__nv_bfloat16, MIN>(__VA_ARGS__) : FN<__nv_bfloat16, SUM>(__VA_ARGS__);  \
+      case DataType::FLOAT32:                                                                      \
+        return isMin ? FN<float, MIN>(__VA_ARGS__) : FN<float, SUM>(__VA_ARGS__);                  \
+      case DataType::INT32:                                                                        \
+        return isMin ? FN<int32_t, MIN>(__VA_ARGS__) : FN<int32_t, SUM>(__VA_ARGS__);              \
+      case DataType::UINT32:                                                                       \
+        return isMin ? FN<uint32_t, MIN>(__VA_ARGS__) : FN<uint32_t, SUM>(__VA_ARGS__);            \
+      case DataType::UINT8:                                                                        \
+        return isMin ? FN<uint8_t, MIN>(__VA_ARGS__) : FN<uint8_t, SUM>(__VA_ARGS__);              \
+      case DataType::FLOAT8_E4M3:                                                                  \
+        return isMin ? FN<f8e4m3, MIN>(__VA_ARGS__) : FN<f8e4m3, SUM>(__VA_ARGS__);                \
+      case DataType::FLOAT8_E5M2:                                                                  \
+        return isMin ? FN<f8e5m2, MIN>(__VA_ARGS__) : FN<f8e5m2, SUM>(__VA_ARGS__);                \
+      case DataType::FLOAT8_E4M3B15:                                                               \
+        return isMin ? FN<f8e4m3b15, MIN>(__VA_ARGS__) : FN<f8e4m3b15, SUM>(__VA_ARGS__);          \
+      default:                                                                                     \
+        return cudaErrorInvalidValue;                                                              \
+    }                                                                                              \
+  } while (0)
+
+}  // namespace
+
+cudaError_t launchAllreduceLL(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads,
+                              cudaStream_t stream) {
+  if (args.bytes * 2 > args.comm.llSlotBytes) return cudaErrorInvalidValue;
+  if (nBlocks < 1 || nThreads < 32 || nThreads > 1024) return cudaErrorInvalidValue;
+  if (args.norm && ((static_cast<uint64_t>(args.hidden) * dataTypeSize(dtype)) % 16 != 0)) return cudaErrorInvalidValue;
+  MSCCLPP_DISPATCH_TYPE_OP(launchLLTyped, dtype, op, args, nBlocks, nThreads, stream);
+}
+
+cudaError_t launchTwoShot(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads,
+                          cudaStream_t stream) {
+  if (args.bytes % 16 != 0) return cudaErrorInvalidValue;
+  if (nBlocks < 1 || nBlocks > kBarrierSlots || nThreads < 32 || nThreads > 512) return cudaErrorInvalidValue;
+  if (nThreads < args.comm.world) return cudaErrorInvalidValue;
+  if (args.mode != kAllReduce && (args.bytes / 16) % args.comm.world != 0) return cudaErrorInvalidValue;
+  if (args.norm && ((static_cast<uint64_t>(args.hidden) * dataTypeSize(dtype)) % 16 != 0)) return cudaErrorInvalidValue;
+  MSCCLPP_DISPATCH_TYPE_OP(launchTwoShotTyped, dtype, op, args, nBlocks, nThreads, stream);
+}
+
+}  // namespace mscclpp

@@ -1,0 +1,45 @@
+// Argument block and launch entry points of the native collective kernels (allreduce, allgather,
+// reduce-scatter, with an optional fused residual-add + RMSNorm epilogue).
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include <mscclpp/device/symm.cuh>
+#include <mscclpp/gpu_data_types.hpp>
+
+namespace mscclpp {
+
+enum CollMode : int { kAllReduce = 0, kReduceScatter = 1, kAllGather = 2 };
+
+struct CollArgs {
+  DeviceComm comm;
+  const void* in;      // local buffer of rank comm.rank; emulated rank e uses in + e * emuStride
+  void* out;
+  uint64_t bytes;      // allreduce: buffer bytes; reduce-scatter: input bytes; allgather: output bytes
+  uint64_t emuStride;  // 0 unless several ranks are emulated in one launch on one GPU
+  int emuRanks;        // gridDim.y (1 = real multi-GPU mode)
+  int mode;            // CollMode
+  int nvls;            // use multimem through comm.mcBase
+  // fused epilogue: out = rmsnorm(allreduce(in) + residualIn) * gamma, residualOut = allreduce(in) + residualIn
+  int norm;
+  int rows;
+  int hidden;          // elements per row
+  float eps;
+  const void* residualIn;   // [rows, hidden] local, replicated on every rank (may be null)
+  void* residualOut;        // [rows, hidden] local (may be null)
+  const void* gamma;        // [hidden] (may be null = all ones)
+  int broadcastResidual;    // two-shot only: write residualOut on every rank, not just the owner's rows
+};
+
+// One-shot LL16 allreduce (every rank sends its whole buffer to every peer as packets).
+// Buffers may live anywhere in local memory. bytes <= comm.llSlotBytes / 2.
+cudaError_t launchAllreduceLL(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads,
+                              cudaStream_t stream);
+
+// Two-shot zero-copy allreduce / reduce-scatter / allgather over peer pointers or NVLS multimem.
+// `in` and `out` must be symmetric-heap buffers at the same offset on every rank; bytes % 16 == 0.
+cudaError_t launchTwoShot(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads,
+                          cudaStream_t stream);
+
+}  // namespace mscclpp

@@ -1,0 +1,110 @@
+// Plain bf16 GEMM on tcgen05/TMEM (see gemm_sm100.cuh for the kernel body) and tensor-map helpers.
+#include "gemm.cuh"
+
+#include <mutex>
+
+#include "gemm_sm100.cuh"
+
+namespace mscclpp {
+namespace gemm {
+
+namespace {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encodeFn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeFn>(p);
+    }
+  });
+  return fn;
+}
+
+template <int kBlockN>
+__global__ void __launch_bounds__(kNumThreads, 1)
+    gemmBf16Kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, Shape shape,
+                   __nv_bfloat16* D, int ldd, DeviceStatus* status, uint64_t budgetNs) {
+  extern __shared__ uint8_t smemRaw[];
+  NoGate gate;
+  StoreBf16 epi{D, ldd, shape.M};
+  gemmCta<kBlockN>(&tmapA, &tmapB, shape, blockIdx.x, gridDim.x, gate, epi, status, budgetNs, smemRaw);
+}
+
+template <int kBlockN>
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, Shape shape, void* D, int ldd, int numCtas,
+                   DeviceStatus* status, cudaStream_t stream) {
+  using Cfg = Config<kBlockN>;
+  static bool attrSet = false;
+  if (!attrSet) {
+    cudaError_t e = cudaFuncSetAttribute(gemmBf16Kernel<kBlockN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attrSet = true;
+  }
+  const int tiles = ((shape.M + kBlockM - 1) / kBlockM) * (shape.N / kBlockN);
+  int grid = numCtas > 0 ? numCtas : smCount();
+  if (grid > tiles) grid = tiles;
+  gemmBf16Kernel<kBlockN><<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, shape, static_cast<__nv_bfloat16*>(D),
+                                                                          ldd, status, 2000000000ull);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+int smCount() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      n = 148;
+  }
+  return n;
+}
+
+cudaError_t makeTensorMapBf16(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t rowStrideBytes,
+                              uint32_t boxRows) {
+  EncodeFn fn = encodeFn();
+  if (fn == nullptr) return cudaErrorNotSupported;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0 || (rowStrideBytes & 15) != 0) return cudaErrorInvalidValue;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {rowStrideBytes};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(kBlockK), boxRows};
+  cuuint32_t elemStrides[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elemStrides,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+cudaError_t gemmBf16(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int blockN, int numCtas,
+                     DeviceStatus* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % kBlockK != 0 || N % blockN != 0 || ldd % 8 != 0) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(D) & 15) != 0) return cudaErrorInvalidValue;
+  Shape shape{M, N, K, M < kBlockM ? M : kBlockM};
+  CUtensorMap ta, tb;
+  cudaError_t e = makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, shape.aBoxRows);
+  if (e != cudaSuccess) return e;
+  e = makeTensorMapBf16(&tb, B, N, K, static_cast<uint64_t>(K) * 2, blockN);
+  if (e != cudaSuccess) return e;
+  switch (blockN) {
+    case 64:
+      return launch<64>(ta, tb, shape, D, ldd, numCtas, status, stream);
+    case 128:
+      return launch<128>(ta, tb, shape, D, ldd, numCtas, status, stream);
+    case 256:
+      return launch<256>(ta, tb, shape, D, ldd, numCtas, status, stream);
+    default:
+      return cudaErrorInvalidValue;
+  }
+}
+
+}  // namespace gemm
+}  // namespace mscclpp

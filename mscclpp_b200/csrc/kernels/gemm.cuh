@@ -1,0 +1,26 @@
+// Host entry points of the tcgen05 bf16 GEMM and helpers shared by the fused GEMM+collective kernels.
+#pragma once
+
+#include <cstdint>
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <mscclpp/poll_device.hpp>
+
+namespace mscclpp {
+namespace gemm {
+
+// Encodes a 2-D bf16 tensor map (row-major [rows, cols], 128-byte swizzle, box = [boxRows, 64]).
+// Returns cudaErrorNotSupported when the driver entry point is unavailable.
+cudaError_t makeTensorMapBf16(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t rowStrideBytes,
+                              uint32_t boxRows);
+
+// D[M, ldd] (bf16) = A[M, K] * B[N, K]^T, fp32 accumulation on the 5th-generation tensor cores.
+// blockN in {64, 128, 256}; N % blockN == 0; K % 64 == 0; numCtas <= 0 picks one CTA per SM.
+cudaError_t gemmBf16(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int blockN, int numCtas,
+                     DeviceStatus* status, cudaStream_t stream);
+
+int smCount();
+
+}  // namespace gemm
+}  // namespace mscclpp

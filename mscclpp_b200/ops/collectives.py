@@ -1,0 +1,156 @@
+"""Collective operations on symmetric memory, dispatched to the native sm_100a kernels.
+
+Algorithm names follow the reference's default collection
+(src/ext/collectives/algorithm_collection_builder.cc:64-104):
+  "packet" / "nvls_packet"          one-shot LL16 over peer stores / one multimem.st per packet
+  "rsag_zero_copy"                  two-shot over peer loads+stores, zero copy
+  "nvls_zero_copy"                  two-shot through NVSwitch multimem.ld_reduce + multimem.st
+The selector mirrors the shape of the reference's Blackwell table
+(src/ext/nccl/algorithm_selector.cc:52-89) with thresholds measured on B200.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .._core import native
+from .._core.symm import SymmetricMemory, torch_dtype_to_native
+
+MODE_ALLREDUCE, MODE_REDUCE_SCATTER, MODE_ALLGATHER = 0, 1, 2
+
+# bytes at or below which the one-shot LL path wins (tuned on 8xB200; see profiles/)
+LL_MAX_BYTES = 512 << 10
+
+
+def _stream(stream: Optional[torch.cuda.Stream]) -> int:
+    return (stream or torch.cuda.current_stream()).cuda_stream
+
+
+def _nbytes(t: torch.Tensor) -> int:
+    return t.numel() * t.element_size()
+
+
+def _op(op: str):
+    n = native.load()
+    return {"sum": n.ReduceOp.SUM, "min": n.ReduceOp.MIN}[op]
+
+
+def select_allreduce(symm: SymmetricMemory, nbytes: int, symmetric: bool) -> str:
+    ll_cap = _ll_capacity(symm)
+    if nbytes <= min(LL_MAX_BYTES, ll_cap) or not symmetric:
+        if nbytes > ll_cap:
+            raise ValueError("buffer outside the symmetric heap is too large for the LL path; allocate it with symm.tensor()")
+        return "nvls_packet" if symm.nvls and nbytes <= (32 << 10) else "packet"
+    if nbytes % 16 != 0:
+        raise ValueError("zero-copy allreduce needs a multiple of 16 bytes")
+    return "nvls_zero_copy" if symm.nvls else "rsag_zero_copy"
+
+
+def _ll_capacity(symm: SymmetricMemory) -> int:
+    import struct
+
+    raw = symm.heap.device_comm_bytes()
+    # DeviceComm: 16 x u64 peerBase, mcBase, heapBytes, llScratchOff, llSlotBytes, ...
+    ll_slot = struct.unpack_from("<Q", raw, 8 * 19)[0]
+    return ll_slot // 2
+
+
+def _grid_for(nbytes: int, algo: str, world: int) -> tuple[int, int]:
+    if algo in ("packet", "nvls_packet"):
+        units = max(1, (nbytes + 15) // 16)
+        threads = 512
+        blocks = max(1, min(56, (units + threads - 1) // threads))
+        return blocks, threads
+    if algo == "nvls_zero_copy":
+        blocks = 16 if nbytes < (8 << 20) else (32 if nbytes < (64 << 20) else 64)
+        return blocks, 512
+    blocks = 32 if nbytes < (8 << 20) else (64 if nbytes < (64 << 20) else 128)
+    return blocks, 512
+
+
+def all_reduce(symm: SymmetricMemory, inp: torch.Tensor, out: Optional[torch.Tensor] = None, op: str = "sum",
+               algo: Optional[str] = None, stream: Optional[torch.cuda.Stream] = None, n_blocks: int = 0,
+               n_threads: int = 0) -> torch.Tensor:
+    """out = reduce over ranks of inp (out defaults to inp, i.e. in place)."""
+    n = native.load()
+    out = inp if out is None else out
+    assert inp.is_contiguous() and out.is_contiguous() and inp.dtype == out.dtype and inp.numel() == out.numel()
+    nbytes = _nbytes(inp)
+    symmetric = symm.contains(inp) and symm.contains(out)
+    algo = algo or select_allreduce(symm, nbytes, symmetric)
+    blocks, threads = _grid_for(nbytes, algo, symm.world)
+    blocks = n_blocks or blocks
+    threads = n_threads or threads
+    dt = torch_dtype_to_native(inp.dtype)
+    if algo in ("packet", "nvls_packet"):
+        if symm.emulated_mode and not symmetric:
+            raise ValueError("emulated ranks need heap tensors")
+        n.allreduce_ll(symm.heap, inp.data_ptr(), out.data_ptr(), nbytes, dt, _op(op), blocks, threads, _stream(stream),
+                       algo == "nvls_packet")
+    elif algo in ("rsag_zero_copy", "nvls_zero_copy"):
+        if not symmetric:
+            raise ValueError(f"{algo} needs tensors from symm.tensor()")
+        n.two_shot(symm.heap, inp.data_ptr(), out.data_ptr(), nbytes, dt, _op(op), MODE_ALLREDUCE, blocks, threads,
+                   _stream(stream), algo == "nvls_zero_copy")
+    else:
+        raise ValueError(f"unknown allreduce algorithm {algo}")
+    return out
+
+
+def reduce_scatter(symm: SymmetricMemory, inp: torch.Tensor, out: torch.Tensor, op: str = "sum", nvls: Optional[bool] = None,
+                   stream: Optional[torch.cuda.Stream] = None, n_blocks: int = 0) -> torch.Tensor:
+    """out (1/world of inp) = this rank's slice of the reduction. Both tensors from symm.tensor()."""
+    n = native.load()
+    nvls = symm.nvls if nvls is None else nvls
+    assert _nbytes(inp) == _nbytes(out) * symm.world
+    blocks, threads = _grid_for(_nbytes(inp), "nvls_zero_copy" if nvls else "rsag_zero_copy", symm.world)
+    n.two_shot(symm.heap, inp.data_ptr(), out.data_ptr(), _nbytes(inp), torch_dtype_to_native(inp.dtype), _op(op),
+               MODE_REDUCE_SCATTER, n_blocks or blocks, threads, _stream(stream), nvls)
+    return out
+
+
+def all_gather(symm: SymmetricMemory, inp: torch.Tensor, out: torch.Tensor, nvls: Optional[bool] = None,
+               stream: Optional[torch.cuda.Stream] = None, n_blocks: int = 0) -> torch.Tensor:
+    """out (world x inp) = concatenation of every rank's inp. Both tensors from symm.tensor()."""
+    n = native.load()
+    nvls = symm.nvls if nvls is None else nvls
+    assert _nbytes(out) == _nbytes(inp) * symm.world
+    blocks, threads = _grid_for(_nbytes(out), "nvls_zero_copy" if nvls else "rsag_zero_copy", symm.world)
+    n.two_shot(symm.heap, inp.data_ptr(), out.data_ptr(), _nbytes(out), torch_dtype_to_native(inp.dtype), _op("sum"),
+               MODE_ALLGATHER, n_blocks or blocks, threads, _stream(stream), nvls)
+    return out
+
+
+def all_reduce_rmsnorm(symm: SymmetricMemory, inp: torch.Tensor, out: torch.Tensor, residual_in: Optional[torch.Tensor],
+                       residual_out: Optional[torch.Tensor], gamma: Optional[torch.Tensor], eps: float = 1e-5,
+                       algo: Optional[str] = None, stream: Optional[torch.cuda.Stream] = None, n_blocks: int = 0) -> torch.Tensor:
+    """Fused: h = allreduce(inp) + residual_in; residual_out = h; out = rmsnorm(h) * gamma.
+
+    inp/out/residual_* are [rows, hidden]; residual_in is replicated on every rank (tensor parallel
+    residual stream). One kernel: the reduction, the residual add and the norm never round-trip
+    through HBM separately.
+    """
+    n = native.load()
+    rows, hidden = inp.shape
+    nbytes = _nbytes(inp)
+    symmetric = all(symm.contains(t) for t in (inp, out) if t is not None) and \
+        all(symm.contains(t) for t in (residual_in, residual_out) if t is not None)
+    if algo is None:
+        small = nbytes <= min(LL_MAX_BYTES, _ll_capacity(symm)) or rows < symm.world or not symmetric
+        algo = "packet" if small else ("nvls_zero_copy" if symm.nvls else "rsag_zero_copy")
+    dt = torch_dtype_to_native(inp.dtype)
+    ptr = lambda t: 0 if t is None else t.data_ptr()
+    if algo in ("packet", "nvls_packet"):
+        blocks = n_blocks or max(1, min(rows, 64))
+        threads = 1024 if hidden * inp.element_size() // 16 >= 1024 else 512
+        n.allreduce_ll_rmsnorm(symm.heap, inp.data_ptr(), out.data_ptr(), rows, hidden, dt, eps, ptr(residual_in),
+                               ptr(residual_out), ptr(gamma), blocks, threads, _stream(stream), algo == "nvls_packet")
+    else:
+        if not symmetric:
+            raise ValueError(f"{algo} needs tensors from symm.tensor()")
+        own_rows = (rows + symm.world - 1) // symm.world
+        blocks = n_blocks or max(1, min(own_rows, 128))
+        n.two_shot_rmsnorm(symm.heap, inp.data_ptr(), out.data_ptr(), rows, hidden, dt, eps, ptr(residual_in),
+                           ptr(residual_out), ptr(gamma), True, blocks, 512, _stream(stream), algo == "nvls_zero_copy")
+    return out
