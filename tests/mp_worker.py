@@ -1,0 +1,125 @@
+"""Multi-process GPU checks, one rank per GPU (launched by torch.distributed.run from test_gpu_multi.py
+or by hand). Exercises the real symmetric heap (VMM + fd passing + multicast) and every allreduce path
+against an fp32 reference. Prints one JSON line per rank-0 check; exit code 0 = all good."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from mscclpp_b200 import SymmetricMemory  # noqa: E402
+from mscclpp_b200.ops import all_gather, all_reduce, all_reduce_rmsnorm, reduce_scatter  # noqa: E402
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    nvls = os.environ.get("MSCCLPP_TEST_NVLS", "1") == "1"
+    symm = SymmetricMemory.from_env(nbytes=1 << 30, enable_nvls=nvls, timeout_ms=5000)
+    failures = []
+
+    def report(name, ok, **extra):
+        if not ok:
+            failures.append(name)
+        if rank == 0:
+            print(json.dumps({"check": name, "ok": bool(ok), **extra}), flush=True)
+
+    def gathered_reference(t):
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t)
+        return torch.stack([p.float() for p in parts]).sum(0)
+
+    algos = ["packet", "rsag_zero_copy"] + (["nvls_packet", "nvls_zero_copy"] if symm.nvls else [])
+    for dtype in (torch.bfloat16, torch.float16, torch.float32):
+        for numel in (256, 4096, 65536, 1 << 20):
+            inp = symm.tensor((numel,), dtype)
+            out = symm.tensor((numel,), dtype)
+            for algo in algos:
+                if algo in ("packet", "nvls_packet") and numel * inp.element_size() > (1 << 20):
+                    continue
+                for rep in range(2):
+                    g = torch.Generator(device=dev).manual_seed(rank * 7 + numel + rep)
+                    inp.copy_(torch.randn((numel,), generator=g, device=dev).to(dtype))
+                    expect = gathered_reference(inp).to(dtype).float()
+                    out.zero_()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    all_reduce(symm, inp, out, algo=algo)
+                    torch.cuda.synchronize()
+                    symm.check()
+                    tol = {torch.bfloat16: 6e-2, torch.float16: 8e-3, torch.float32: 1e-4}[dtype]
+                    err = (out.float() - expect).abs().max().item()
+                    report(f"allreduce/{algo}/{dtype}/{numel}/{rep}", err <= tol * max(1.0, expect.abs().max().item()), err=err)
+            symm.release(out)
+            symm.release(inp)
+
+    # reduce-scatter / all-gather
+    per = 8192
+    full = symm.tensor((world * per,), torch.bfloat16)
+    part = symm.tensor((per,), torch.bfloat16)
+    for use_nvls in ([False, True] if symm.nvls else [False]):
+        full.copy_(torch.randn((world * per,), device=dev).to(torch.bfloat16))
+        expect = gathered_reference(full)[rank * per:(rank + 1) * per].to(torch.bfloat16).float()
+        dist.barrier()
+        reduce_scatter(symm, full, part, nvls=use_nvls)
+        torch.cuda.synchronize()
+        symm.check()
+        report(f"reduce_scatter/nvls={use_nvls}", (part.float() - expect).abs().max().item() < 0.1)
+        part.copy_(torch.full((per,), float(rank + 1), device=dev).to(torch.bfloat16))
+        dist.barrier()
+        all_gather(symm, part, full, nvls=use_nvls)
+        torch.cuda.synchronize()
+        symm.check()
+        expect = torch.arange(1, world + 1, device=dev).repeat_interleave(per).float()
+        report(f"all_gather/nvls={use_nvls}", torch.equal(full.float(), expect))
+
+    # fused allreduce + residual + RMSNorm
+    for rows, hidden in ((1, 8192), (8, 8192), (128, 8192), (512, 4096)):
+        x = symm.tensor((rows, hidden), torch.bfloat16)
+        y = symm.tensor((rows, hidden), torch.bfloat16)
+        r_in = symm.tensor((rows, hidden), torch.bfloat16)
+        r_out = symm.tensor((rows, hidden), torch.bfloat16)
+        gamma = symm.tensor((hidden,), torch.bfloat16)
+        gen = torch.Generator(device=dev).manual_seed(4242)
+        r_in.copy_(torch.randn((rows, hidden), generator=gen, device=dev).to(torch.bfloat16))
+        gamma.copy_((1 + 0.1 * torch.randn((hidden,), generator=gen, device=dev)).to(torch.bfloat16))
+        x.copy_(torch.randn((rows, hidden), device=dev).to(torch.bfloat16))
+        h = (gathered_reference(x).to(torch.bfloat16).float() + r_in.float()).to(torch.bfloat16).float()
+        ref = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()).to(torch.bfloat16).float()
+        cands = ["packet"] + (["nvls_packet"] if symm.nvls else [])
+        if rows >= world:
+            cands += ["rsag_zero_copy"] + (["nvls_zero_copy"] if symm.nvls else [])
+        for algo in cands:
+            if algo in ("packet", "nvls_packet") and rows * hidden * 2 > (1 << 20):
+                continue
+            y.zero_()
+            r_out.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            all_reduce_rmsnorm(symm, x, y, r_in, r_out, gamma, eps=1e-5, algo=algo)
+            torch.cuda.synchronize()
+            symm.check()
+            e1 = (y.float() - ref).abs().max().item()
+            e2 = (r_out.float() - h).abs().max().item()
+            report(f"allreduce_rmsnorm/{algo}/{rows}x{hidden}", e1 < 0.1 and e2 < 0.1, err=e1, res_err=e2)
+        for t in (gamma, r_out, r_in, y, x):
+            symm.release(t)
+
+    dist.barrier()
+    symm.destroy()
+    dist.destroy_process_group()
+    if failures:
+        print(f"rank {rank}: {len(failures)} failures: {failures[:5]}", file=sys.stderr)
+        return 1
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -65,12 +65,35 @@ def _scripts():
     return [r for r in rel if r not in BROKEN_UPSTREAM]
 
 
+@pytest.fixture(scope="session")
+def compiled_plans():
+    """{rel: (ours, theirs)} for every example, compiled concurrently (each compile is its own process)."""
+    from concurrent.futures import ThreadPoolExecutor
+
+    rels = _scripts()
+    jobs = [(mode, rel) for rel in rels for mode in ("ours", "reference")]
+    with ThreadPoolExecutor(max(2, os.cpu_count() or 2)) as pool:
+        results = list(pool.map(lambda j: _try_run(j[0], os.path.join(EXAMPLES, j[1])), jobs))
+    out = {}
+    for (mode, rel), res in zip(jobs, results):
+        out.setdefault(rel, {})[mode] = res
+    return out
+
+
+def _try_run(mode, script):
+    try:
+        return _run(mode, script)
+    except Exception as e:  # reported by the test that looks at this entry
+        return e
+
+
 @pytest.mark.skipif(not os.path.isdir(EXAMPLES), reason="reference checkout not present")
 @pytest.mark.parametrize("rel", _scripts())
-def test_plan_equals_reference_plan(rel):
-    script = os.path.join(EXAMPLES, rel)
-    ours = _run("ours", script)
-    theirs = _run("reference", script)
+def test_plan_equals_reference_plan(rel, compiled_plans):
+    ours, theirs = compiled_plans[rel]["ours"], compiled_plans[rel]["reference"]
+    for side in (ours, theirs):
+        if isinstance(side, Exception):
+            raise side
     assert ours == theirs
     digest = hashlib.sha256(json.dumps(ours, sort_keys=True).encode()).hexdigest()
     golden = json.load(open(GOLDEN)) if os.path.exists(GOLDEN) else {}
