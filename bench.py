@@ -172,20 +172,62 @@ def main():
         symm.check()
         return max_over_ranks(start.elapsed_time(end) / steps)  # ms per step
 
+    # ------------------------------------------------------------------ pick the fused variant (untimed)
+    def fused(t, mode, nvls):
+        return lambda: layer.forward_fused(xs[t], mode=mode, nvls=nvls)
+
+    variants = [(0, False), (1, False)] + ([(0, True), (1, True)] if symm.nvls else [])
+    if world == 1:
+        variants = [(0, False)]
+    best = {}
+    for t in TOKEN_SIZES:
+        scores = {}
+        for mode, nvls in variants:
+            scores[(mode, nvls)] = time_steps(fused(t, mode, nvls), 5, 3)
+        best[t] = min(scores, key=scores.get)
+
     # ------------------------------------------------------------------ headline: fused TP layer at T = 8192
     sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
                            int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
     if rank == 0:
         sampler.start()
-    x_head = xs[HEADLINE_T]
-    ms_per_step = time_steps(lambda: layer.forward(x_head), args.steps, max(args.warmup, 3))
-    clocks = sampler.stop() if rank == 0 else {}
-    launches = args.steps * layer.launches_per_forward
+    head_mode, head_nvls = best[HEADLINE_T]
+    head_fn = fused(HEADLINE_T, head_mode, head_nvls)
+    ms_per_step = time_steps(head_fn, args.steps, max(args.warmup, 3))
+    launches = args.steps * (1 if head_mode == 0 else 2)
 
-    # ------------------------------------------------------------------ per-T table
-    tp_us = {}
+    # ------------------------------------------------------------------ per-T table: eager launches and CUDA-graph replay
+    tp_us, tp_graph_us, tp_unfused_us, tp_baseline_us = {}, {}, {}, {}
+    side = torch.cuda.Stream()
     for t in TOKEN_SIZES:
-        tp_us[str(t)] = round(time_steps(lambda t=t: layer.forward(xs[t]), max(10, args.steps), 5) * 1e3, 2)
+        fn = fused(t, *best[t])
+        tp_us[str(t)] = round(time_steps(fn, max(10, args.steps), 5) * 1e3, 2)
+        # graph replay removes the host launch cost, which dominates the small-T numbers above
+        reps = 10
+        graph = torch.cuda.CUDAGraph()
+        barrier()
+        with torch.cuda.stream(side):
+            fn()
+            torch.cuda.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(reps):
+                    layer.forward_fused(xs[t], mode=best[t][0], nvls=best[t][1], stream=side)
+        barrier()
+        tp_graph_us[str(t)] = round(time_steps(graph.replay, 5, 2) * 1e3 / reps, 2)
+        # two-kernel path of this library (GEMM, then allreduce+residual+norm)
+        tp_unfused_us[str(t)] = round(time_steps(lambda t=t: layer.forward(xs[t]), 10, 3) * 1e3, 2)
+        # library composition: cuBLAS GEMM + NCCL allreduce + PyTorch residual add and RMSNorm
+        w_t = layer.weight.t()
+        res_b = layer.residual_in[:t]
+
+        def baseline(t=t, w_t=w_t, res_b=res_b):
+            p = torch.matmul(xs[t], w_t)
+            if world > 1:
+                dist.all_reduce(p)
+            hh = p + res_b
+            return torch.nn.functional.rms_norm(hh, (HIDDEN,), layer.gamma, 1e-5)
+
+        tp_baseline_us[str(t)] = round(time_steps(baseline, 10, 3) * 1e3, 2)
 
     # ------------------------------------------------------------------ end to end through the public API
     x_host = torch.randn((HEADLINE_T, K_SHARD)).to(torch.bfloat16).pin_memory()
@@ -194,11 +236,19 @@ def main():
 
     def e2e_step():
         x_dev.copy_(x_host, non_blocking=True)
-        out, _ = layer.forward(x_dev)
+        out, _ = layer.forward_fused(x_dev, mode=head_mode, nvls=head_nvls)
         result_host.copy_(out[:, :8].float().abs().mean().reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller looks at the metric every step
 
     e2e_ms = time_steps(e2e_step, args.steps, max(args.warmup, 3))
+    # keep the GPU under the headline load until the 200 ms sampler has seen it a few times
+    t_end = time.time() + 1.5
+    while time.time() < t_end:
+        for _ in range(50):
+            head_fn()
+        torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else {}
 
     # ------------------------------------------------------------------ allreduce sweep (N > 1)
     sweep = []
@@ -256,7 +306,12 @@ def main():
                        "nvls": bool(symm.nvls)},
             "tokens_per_s": round(HEADLINE_T / (ms_per_step * 1e-3), 1),
             "aggregate_tflops": round(flops / (ms_per_step * 1e-3) / 1e12, 1),
+            "variant": {"mode": head_mode, "nvls": head_nvls, "kernel": "tpFusedKernel (tcgen05 GEMM + multimem/peer reduce + "
+                        "residual + RMSNorm in one launch)" + ("" if head_mode == 0 else " + local scale pass")},
             "tp_layer_us": tp_us,
+            "tp_layer_graph_replay_us": tp_graph_us,
+            "tp_layer_two_kernel_us": tp_unfused_us,
+            "tp_layer_cublas_nccl_torch_us": tp_baseline_us,
             "e2e": {"value": round(e2e_ms * 1e3, 2), "unit": "us", "h2d_bytes_per_step": x_host.numel() * 2,
                     "d2h_bytes_per_step": 4},
             "gpu_launches": launches,

@@ -1,6 +1,64 @@
-// Bindings of components added after the first slice (channels, executor, proxy, ...).
+// Bindings of components added after the first slice (fused layers, channels, executor, proxy, ...).
 #include "bindings.hpp"
 
-namespace py = pybind11;
+#include <pybind11/stl.h>
 
-void registerMoreBindings(py::module_& m) { (void)m; }
+#include <mscclpp/errors.hpp>
+#include <mscclpp/symmetric_heap.hpp>
+
+#include "../kernels/tp_fused.cuh"
+
+namespace py = pybind11;
+using namespace mscclpp;
+
+namespace {
+void checkCudaMore(cudaError_t e, const char* what) {
+  if (e != cudaSuccess) throw CudaError(std::string(what) + " failed", static_cast<int>(e));
+}
+}  // namespace
+
+void registerMoreBindings(py::module_& m) {
+  m.def(
+      "tp_fused",
+      [](SymmetricHeap& heap, std::vector<uintptr_t> a, std::vector<uintptr_t> b, uintptr_t partial, uintptr_t residualIn,
+         uintptr_t residualOut, uintptr_t out, uintptr_t gamma, uintptr_t rinv, int M, int N, int K, float eps, int blockN,
+         int numGemmCtas, int numReducers, int rowsPerUnit, int mode, bool nvls, uintptr_t stream) {
+        TpFusedArgs args{};
+        args.comm = heap.deviceComm();
+        args.shape.M = M;
+        args.shape.N = N;
+        args.shape.K = K;
+        args.partial = reinterpret_cast<__nv_bfloat16*>(partial);
+        args.residualIn = reinterpret_cast<const __nv_bfloat16*>(residualIn);
+        args.residualOut = reinterpret_cast<__nv_bfloat16*>(residualOut);
+        args.out = reinterpret_cast<__nv_bfloat16*>(out);
+        args.gamma = reinterpret_cast<const __nv_bfloat16*>(gamma);
+        args.rinv = reinterpret_cast<float*>(rinv);
+        args.eps = eps;
+        args.blockN = blockN;
+        args.numGemmCtas = numGemmCtas;
+        args.rowsPerUnit = rowsPerUnit;
+        args.mode = mode;
+        args.nvls = nvls ? 1 : 0;
+        args.emuRanks = heap.emulated() ? heap.world() : 1;
+        const size_t need = heap.emulated() ? heap.world() : 1;
+        if (a.size() != need || b.size() != need) throw Error("tp_fused: one A and one B pointer per (emulated) rank", ErrorCode::InvalidUsage);
+        std::vector<const void*> ap, bp;
+        for (auto v : a) ap.push_back(reinterpret_cast<const void*>(v));
+        for (auto v : b) bp.push_back(reinterpret_cast<const void*>(v));
+        checkCudaMore(launchTpFused(args, ap.data(), bp.data(), numReducers, reinterpret_cast<cudaStream_t>(stream)), "tp_fused");
+      },
+      py::arg("heap"), py::arg("a"), py::arg("b"), py::arg("partial"), py::arg("residual_in"), py::arg("residual_out"),
+      py::arg("out"), py::arg("gamma"), py::arg("rinv"), py::arg("m"), py::arg("n"), py::arg("k"), py::arg("eps"),
+      py::arg("block_n") = 256, py::arg("num_gemm_ctas") = 0, py::arg("num_reducers") = 0, py::arg("rows_per_unit") = 0,
+      py::arg("mode") = 0, py::arg("nvls") = false, py::arg("stream") = 0);
+  m.def(
+      "tp_scale_rows",
+      [](uintptr_t h, uintptr_t rinv, uintptr_t gamma, uintptr_t out, int M, int N, uintptr_t stream) {
+        checkCudaMore(launchTpScaleRows(reinterpret_cast<const void*>(h), reinterpret_cast<const float*>(rinv),
+                                        reinterpret_cast<const void*>(gamma), reinterpret_cast<void*>(out), M, N,
+                                        reinterpret_cast<cudaStream_t>(stream)),
+                      "tp_scale_rows");
+      },
+      py::arg("h"), py::arg("rinv"), py::arg("gamma"), py::arg("out"), py::arg("m"), py::arg("n"), py::arg("stream") = 0);
+}

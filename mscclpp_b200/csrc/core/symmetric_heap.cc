@@ -28,7 +28,8 @@ void SymmetricHeap::initLayout(const Options& options) {
   // [SymmControl | LL scratch: 2 buffers x world x llSlotBytes | arena]
   const size_t ctlBytes = roundUp(sizeof(SymmControl), 4096);
   const size_t llBytes = 2 * static_cast<size_t>(world_) * options.llSlotBytes;
-  arenaBegin_ = roundUp(ctlBytes + llBytes, 1u << 20);
+  const size_t auxOff = roundUp(ctlBytes + llBytes, 4096);
+  arenaBegin_ = roundUp(auxOff + kAuxFlagBytes, 1u << 20);
   if (arenaBegin_ >= bytes_) throw Error("symmetric heap too small for its control block and LL scratch", ErrorCode::InvalidUsage);
   freeBlocks_.clear();
   usedBlocks_.clear();
@@ -41,6 +42,7 @@ void SymmetricHeap::initLayout(const Options& options) {
   comm_.heapBytes = bytes_;
   comm_.llScratchOff = ctlBytes;
   comm_.llSlotBytes = options.llSlotBytes;
+  comm_.auxFlagsOff = auxOff;
   comm_.status = status_;
   int64_t ms = options.timeoutMs >= 0 ? options.timeoutMs : env()->deviceTimeoutMs;
   comm_.timeoutNs = static_cast<uint64_t>(ms) * 1000000ull;

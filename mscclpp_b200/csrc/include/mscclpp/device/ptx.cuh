@@ -109,6 +109,9 @@ MSCCLPP_DEVICE_INLINE void fence_proxy_async() { asm volatile("fence.proxy.async
 MSCCLPP_DEVICE_INLINE void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // ------------------------------------------------------------------ 16-byte vector accesses
+// Bulk data movers (ld_nc_na_v4, st_na_v4, multimem 16-byte loads/stores) carry no "memory" clobber on
+// purpose: the compiler may then keep many of them in flight; ordering against flags comes from the
+// flag accesses themselves, which do clobber memory.
 MSCCLPP_DEVICE_INLINE uint4 ld_volatile_v4(const void* p) {
   uint4 v;
   asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -134,14 +137,12 @@ MSCCLPP_DEVICE_INLINE uint4 ld_nc_na_v4(const void* p) {
   uint4 v;
   asm volatile("ld.global.relaxed.sys.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p)
-               : "memory");
+               : "l"(p));
   return v;
 }
 MSCCLPP_DEVICE_INLINE void st_na_v4(void* p, uint4 v) {
   asm volatile("st.global.relaxed.sys.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
-               "r"(v.z), "r"(v.w)
-               : "memory");
+               "r"(v.z), "r"(v.w));
 }
 
 // ------------------------------------------------------------------ NVSwitch multimem (NVLS)
@@ -151,16 +152,14 @@ MSCCLPP_DEVICE_INLINE uint4 multimem_ld_reduce_add_f16x2(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f16x2 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
+               : "l"(mc));
   return v;
 }
 MSCCLPP_DEVICE_INLINE uint4 multimem_ld_reduce_add_bf16x2(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
+               : "l"(mc));
   return v;
 }
 // bf16/f16 inputs summed with an fp32 accumulator inside the switch.
@@ -168,40 +167,35 @@ MSCCLPP_DEVICE_INLINE uint4 multimem_ld_reduce_add_f16x2_acc32(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
+               : "l"(mc));
   return v;
 }
 MSCCLPP_DEVICE_INLINE uint4 multimem_ld_reduce_add_bf16x2_acc32(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
+               : "l"(mc));
   return v;
 }
 MSCCLPP_DEVICE_INLINE uint4 multimem_ld_reduce_add_f32(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
+               : "l"(mc));
   return v;
 }
 MSCCLPP_DEVICE_INLINE uint4 multimem_ld_reduce_min_f16x2(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.min.v4.f16x2 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
+               : "l"(mc));
   return v;
 }
 MSCCLPP_DEVICE_INLINE uint4 multimem_ld_reduce_min_bf16x2(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.min.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
+               : "l"(mc));
   return v;
 }
 // fp8 reductions exist only on arch-specific Blackwell targets (sm_100a); accumulate in f16.
@@ -209,16 +203,14 @@ MSCCLPP_DEVICE_INLINE uint4 multimem_ld_reduce_add_e4m3x4(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f16.v4.e4m3x4 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
+               : "l"(mc));
   return v;
 }
 MSCCLPP_DEVICE_INLINE uint4 multimem_ld_reduce_add_e5m2x4(const void* mc) {
   uint4 v;
   asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f16.v4.e5m2x4 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(mc)
-               : "memory");
+               : "l"(mc));
   return v;
 }
 MSCCLPP_DEVICE_INLINE uint32_t multimem_ld_reduce_add_u32(const void* mc) {
@@ -233,8 +225,7 @@ MSCCLPP_DEVICE_INLINE int32_t multimem_ld_reduce_add_s32(const void* mc) {
 }
 MSCCLPP_DEVICE_INLINE void multimem_st_v4(void* mc, uint4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y),
-               "r"(v.z), "r"(v.w)
-               : "memory");
+               "r"(v.z), "r"(v.w));
 }
 MSCCLPP_DEVICE_INLINE void multimem_st_v2(void* mc, uint2 v) {
   asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};" ::"l"(mc), "r"(v.x), "r"(v.y) : "memory");

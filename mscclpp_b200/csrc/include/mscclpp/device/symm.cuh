@@ -22,6 +22,7 @@ namespace mscclpp {
 constexpr int kMaxRanks = 16;
 constexpr int kBarrierSlots = 192;   // one slot per thread block taking part in a cross-rank barrier
 constexpr int kBarrierPhases = 4;
+constexpr uint64_t kAuxFlagBytes = 2u << 20;
 
 struct SymmControl {
   uint32_t epoch;  // number of collective launches completed on this heap
@@ -40,6 +41,7 @@ struct DeviceComm {
   uint64_t heapBytes;
   uint64_t llScratchOff;    // heap offset of the LL scratch: 2 buffers x world x llSlotBytes
   uint64_t llSlotBytes;     // bytes of packets one source rank may write per buffer
+  uint64_t auxFlagsOff;     // heap offset of kAuxFlagBytes of epoch-stamped flags for fused kernels
   DeviceStatus* status;     // host-visible error block (may be null)
   uint64_t timeoutNs;       // budget of every device-side wait
   int rank;

@@ -88,7 +88,7 @@ cudaError_t gemmBf16(const void* A, const void* B, void* D, int M, int N, int K,
                      DeviceStatus* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || K % kBlockK != 0 || N % blockN != 0 || ldd % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(D) & 15) != 0) return cudaErrorInvalidValue;
-  Shape shape{M, N, K, M < kBlockM ? M : kBlockM};
+  Shape shape{M, N, K, M < kBlockM ? M : kBlockM, 0};
   CUtensorMap ta, tb;
   cudaError_t e = makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, shape.aBoxRows);
   if (e != cudaSuccess) return e;

@@ -10,6 +10,14 @@
 namespace mscclpp {
 namespace gemm {
 
+struct Shape {
+  int M, N, K;
+  int aBoxRows;  // rows of the A tensor-map box: min(kBlockM, M); rows beyond it are never stored
+  int rowMajorTiles;  // 0: consecutive tiles walk M (share a B tile); 1: walk N inside one row block, so
+                      // that row blocks complete in order (what a fused consumer of whole rows wants)
+};
+
+
 // Encodes a 2-D bf16 tensor map (row-major [rows, cols], 128-byte swizzle, box = [boxRows, 64]).
 // Returns cudaErrorNotSupported when the driver entry point is unavailable.
 cudaError_t makeTensorMapBf16(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t rowStrideBytes,

@@ -27,14 +27,17 @@
 #include <mscclpp/device/ptx.cuh>
 #include <mscclpp/poll_device.hpp>
 
+#include "gemm.cuh"
+
 namespace mscclpp {
 namespace gemm {
 
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;          // 64 bf16 = 128 bytes = one swizzle row
 constexpr int kUmmaK = 16;           // K of one tcgen05.mma for 16-bit inputs
-constexpr int kNumThreads = 192;     // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-5: epilogue
-constexpr int kNumEpilogueThreads = 128;
+constexpr int kNumEpilogueWarps = 8;  // two warps per TMEM lane quarter, each takes half of the tile's columns
+constexpr int kNumEpilogueThreads = kNumEpilogueWarps * 32;
+constexpr int kNumThreads = 64 + kNumEpilogueThreads;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
 
 template <int kBlockN>
 struct Config {
@@ -48,10 +51,15 @@ struct Config {
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024: manual alignment
 };
 
-struct Shape {
-  int M, N, K;
-  int aBoxRows;  // rows of the A tensor-map box: min(kBlockM, M); rows beyond it are never stored
-};
+MSCCLPP_DEVICE_INLINE void tileCoord(const Shape& s, int tile, int numMBlk, int numNBlk, int& mBlk, int& nBlk) {
+  if (s.rowMajorTiles) {
+    mBlk = tile / numNBlk;
+    nBlk = tile % numNBlk;
+  } else {
+    mBlk = tile % numMBlk;
+    nBlk = tile / numMBlk;
+  }
+}
 
 // 64-bit shared-memory matrix descriptor: K-major operand, 128-byte swizzle, tile base 1024B-aligned.
 // bits [0,14) start address >> 4; [16,30) leading byte offset >> 4 (unused for swizzled K-major, 1);
@@ -122,7 +130,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
     }
     for (int s = 0; s < 2; s++) {
       ptx::mbar_init(&st.tmemFull[s], 1);
-      ptx::mbar_init(&st.tmemEmpty[s], 4);  // one arrival per epilogue warp
+      ptx::mbar_init(&st.tmemEmpty[s], kNumEpilogueWarps);  // one arrival per epilogue warp
     }
     *st.abortFlag = 0;
     ptx::fence_mbar_init();
@@ -147,7 +155,8 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       uint32_t armedParity = 0;  // parity those loads complete
       bool ok = true;
       for (int tile = ctaIdx; tile < numTiles && ok; tile += numCtas) {
-        const int mBlk = tile % numMBlk, nBlk = tile / numMBlk;
+        int mBlk, nBlk;
+        tileCoord(shape, tile, numMBlk, numNBlk, mBlk, nBlk);
         ok = gate.waitRowBlock(mBlk);
         for (int kb = 0; kb < numKBlk && ok; kb++) {
           ok = mbarWait(&st.empty[stage], phase ^ 1u, status, budgetNs, 100 + stage);
@@ -220,13 +229,16 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       }
       if (!ok) *st.abortFlag = 1;
     }
-  } else {
-    // ===================================================== epilogue (4 warps, one TMEM lane quarter each)
+  } else if (warp < 2 + kNumEpilogueWarps) {
+    // ===================================================== epilogue (8 warps: lane quarter x column half)
     const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warpid%4), +32)
+    const int half = (warp - 2) >> 2;
+    constexpr int kChunksPerWarp = kBlockN / 32 / (kNumEpilogueWarps / 4);
     bool ok = true;
     int it = 0;
     for (int tile = ctaIdx; tile < numTiles && ok; tile += numCtas, it++) {
-      const int mBlk = tile % numMBlk, nBlk = tile / numMBlk;
+      int mBlk, nBlk;
+      tileCoord(shape, tile, numMBlk, numNBlk, mBlk, nBlk);
       const int acc = it & 1;
       const uint32_t accPhase = (it >> 1) & 1;
       ok = mbarWait(&st.tmemFull[acc], accPhase, status, budgetNs, 400 + acc);
@@ -236,7 +248,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       const int row = mBlk * kBlockM + quarter * 32 + lane;
       const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
 #pragma unroll 1
-      for (int c = 0; c < kBlockN / 32; c++) {
+      for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; c++) {
         uint32_t v[32];
         ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
         ptx::tmem_ld_wait();
@@ -246,7 +258,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       ptx::tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&st.tmemEmpty[acc]);
-      // all 128 epilogue threads have issued their stores -> let the fused kernel publish the tile
+      // all epilogue threads have issued their stores -> let the fused kernel publish the tile
       ptx::named_barrier(1, kNumEpilogueThreads);
       epi.tileDone(mBlk, nBlk, threadIdx.x - 64);
     }

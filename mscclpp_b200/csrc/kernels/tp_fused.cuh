@@ -1,0 +1,41 @@
+// Fused tensor-parallel layer: GEMM (tcgen05) + allreduce + residual add + RMSNorm in one launch.
+#pragma once
+
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <mscclpp/device/symm.cuh>
+
+#include "gemm.cuh"
+
+namespace mscclpp {
+
+struct TpFusedArgs {
+  DeviceComm comm;
+  gemm::Shape shape;            // M tokens, N = hidden, K = this rank's shard of the reduction dimension
+  __nv_bfloat16* partial;       // symmetric [M, N]: this rank's partial product (written by the GEMM CTAs)
+  const __nv_bfloat16* residualIn;   // symmetric-heap [M, N], replicated content (may be null)
+  __nv_bfloat16* residualOut;   // symmetric [M, N]: receives h on every rank (may be null in mode 0)
+  __nv_bfloat16* out;           // symmetric [M, N]: normalised output (mode 0: written by the owners everywhere)
+  const __nv_bfloat16* gamma;   // [N] local (may be null)
+  float* rinv;                  // symmetric [M] fp32, mode 1 only
+  float eps;
+  int blockN;                   // GEMM N tile: 64, 128 or 256
+  int numGemmCtas;              // 0 = all SMs but the reducers
+  int rowsPerUnit;              // ownership granule, power of two <= 128; 0 = pick from M and world
+  int mode;                     // 0: owners broadcast out + residualOut; 1: owners broadcast residualOut + rinv
+  int nvls;                     // multimem through comm.mcBase instead of peer loads/stores
+  int emuRanks;                 // > 1: that many emulated ranks in one cooperative launch (tests)
+};
+
+// A[e], B[e]: operands of (emulated) rank e; real multi-GPU use passes one entry each.
+// A: [M, K] bf16 row-major activations, B: [N, K] bf16 row-major weights (nn.Linear layout).
+cudaError_t launchTpFused(const TpFusedArgs& args, const void* const* A, const void* const* B, int numReducers,
+                          cudaStream_t stream);
+
+// Local pass of mode 1: out = h * rinv[row] * gamma.
+cudaError_t launchTpScaleRows(const void* h, const float* rinv, const void* gamma, void* out, int M, int N,
+                              cudaStream_t stream);
+
+}  // namespace mscclpp

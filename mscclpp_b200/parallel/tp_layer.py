@@ -40,7 +40,8 @@ class RowParallelLinearNorm:
         self.residual_out = symm.tensor((max_tokens, out_features), torch.bfloat16)
         self.gamma = symm.tensor((out_features,), torch.bfloat16)
         self.gamma.fill_(1.0)
-        self.launches_per_forward = 2
+        self.rinv = symm.tensor((max_tokens,), torch.float32)
+        self.launches_per_forward = 1  # forward_fused, mode 0
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, algo: Optional[str] = None,
                 stream: Optional[torch.cuda.Stream] = None) -> Tuple[torch.Tensor, torch.Tensor]:
@@ -56,6 +57,41 @@ class RowParallelLinearNorm:
         all_reduce_rmsnorm(self.symm, partial, out, self.residual_in[:t], res_out, self.gamma, eps=self.eps, algo=algo,
                            stream=stream)
         return out, res_out
+
+    def forward_fused(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, mode: int = 0,
+                      nvls: Optional[bool] = None, block_n: int = 0, num_reducers: int = 0, num_gemm_ctas: int = 0,
+                      rows_per_unit: int = 0, stream: Optional[torch.cuda.Stream] = None,
+                      emulated_inputs=None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Same result as forward(), in ONE kernel: GEMM tiles, cross-rank reduction, residual add and norm
+        overlap tile by tile. mode 1 halves NVLink traffic by broadcasting h and 1/rms only and finishing
+        `out` with a local pass (second, local-only launch).
+
+        emulated_inputs: for emulated heaps, [(x_r, weight_r)] for every emulated rank."""
+        from .._core import native
+
+        n = native.load()
+        t = x.shape[0]
+        assert t <= self.max_tokens and x.shape[1] == self.k_shard and x.is_contiguous()
+        if residual is not None:
+            self.residual_in[:t].copy_(residual)
+        nvls = self.symm.nvls if nvls is None else nvls
+        bn = block_n or pick_block_n(t, self.out_features)
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        if emulated_inputs is not None:
+            a_ptrs = [xi.data_ptr() for xi, _ in emulated_inputs]
+            b_ptrs = [wi.data_ptr() for _, wi in emulated_inputs]
+        else:
+            a_ptrs, b_ptrs = [x.data_ptr()], [self.weight.data_ptr()]
+        n.tp_fused(self.symm.heap, a_ptrs, b_ptrs, self.partial.data_ptr(), self.residual_in.data_ptr(),
+                   self.residual_out.data_ptr(), self.out.data_ptr(), self.gamma.data_ptr(), self.rinv.data_ptr(), t,
+                   self.out_features, self.k_shard, self.eps, bn, num_gemm_ctas, num_reducers, rows_per_unit, mode, nvls, s)
+        if mode == 1:
+            ranks = range(self.symm.world) if self.symm.emulated_mode else [self.symm.rank]
+            for r in ranks:  # one local pass per (emulated) rank
+                view = (lambda t_: self.symm.rank_view(t_, r)) if self.symm.emulated_mode else (lambda t_: t_)
+                n.tp_scale_rows(view(self.residual_out).data_ptr(), view(self.rinv).data_ptr(), self.gamma.data_ptr(),
+                                view(self.out).data_ptr(), t, self.out_features, s)
+        return self.out[:t], self.residual_out[:t]
 
     @torch.no_grad()
     def reference(self, x_shards, weights, residual: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:

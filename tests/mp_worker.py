@@ -112,6 +112,33 @@ def main():
         for t in (gamma, r_out, r_in, y, x):
             symm.release(t)
 
+    # one-kernel fused TP layer (GEMM + allreduce + residual + RMSNorm)
+    from mscclpp_b200.parallel.tp_layer import RowParallelLinearNorm
+
+    layer = RowParallelLinearNorm(symm, out_features=4096, k_shard=512, max_tokens=1024, seed=3)
+    gen = torch.Generator(device=dev).manual_seed(777)
+    layer.gamma.copy_((1 + 0.1 * torch.randn((4096,), generator=gen, device=dev)).to(torch.bfloat16))
+    for tokens in (1, 8, 100, 1024):
+        gen = torch.Generator(device=dev).manual_seed(1000 + tokens)
+        residual = torch.randn((tokens, 4096), generator=gen, device=dev).to(torch.bfloat16)
+        x = torch.randn((tokens, 512), device=dev).to(torch.bfloat16)
+        part = (x.float() @ layer.weight.float().t()).to(torch.bfloat16)
+        h = (gathered_reference(part).to(torch.bfloat16).float() + residual.float()).to(torch.bfloat16).float()
+        ref = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + layer.eps) * layer.gamma.float()).to(torch.bfloat16).float()
+        for use_nvls in ([False, True] if symm.nvls else [False]):
+            for mode in (0, 1):
+                layer.out.zero_()
+                layer.residual_out.zero_()
+                torch.cuda.synchronize()
+                dist.barrier()
+                for rep in range(2):
+                    out, res = layer.forward_fused(x, residual, mode=mode, nvls=use_nvls)
+                torch.cuda.synchronize()
+                symm.check()
+                e1 = (out.float() - ref).abs().max().item()
+                e2 = (res.float() - h).abs().max().item()
+                report(f"tp_fused/T={tokens}/nvls={use_nvls}/mode={mode}", e1 < 0.12 and e2 < 0.12, err=e1, res_err=e2)
+
     dist.barrier()
     symm.destroy()
     dist.destroy_process_group()

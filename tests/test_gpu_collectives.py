@@ -204,3 +204,39 @@ def symm_ctrl_epoch(symm):
     from mscclpp_b200 import tensor_from_pointer
 
     return tensor_from_pointer(symm.heap.local_base, (1,), torch.int32, symm.device, owner=symm)
+
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("tokens,hidden,k", [(1, 1024, 128), (8, 2048, 256), (128, 8192, 256), (300, 1024, 512), (1024, 2048, 128)])
+def test_fused_tp_layer_one_kernel(world, mode, tokens, hidden, k):
+    """GEMM + allreduce + residual + RMSNorm in one launch, all ranks emulated on one GPU."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.tp_layer import RowParallelLinearNorm
+
+    symm = SymmetricMemory.emulated(world, nbytes=256 << 20, timeout_ms=3000)
+    layer = RowParallelLinearNorm(symm, out_features=hidden, k_shard=k, max_tokens=tokens)
+    g = torch.Generator(device="cuda").manual_seed(tokens + hidden)
+    xs = [torch.randn((tokens, k), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    ws = [(torch.randn((hidden, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(world)]
+    residual = torch.randn((tokens, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    gam = (1 + 0.1 * torch.randn((hidden,), generator=g, device="cuda")).to(torch.bfloat16)
+    for r in range(world):
+        symm.rank_view(layer.residual_in, r)[:tokens].copy_(residual)
+        symm.rank_view(layer.gamma, r).copy_(gam)
+        symm.rank_view(layer.out, r).zero_()
+        symm.rank_view(layer.residual_out, r).zero_()
+    for rep in range(2):
+        layer.forward_fused(xs[0], mode=mode, nvls=False, num_reducers=4, num_gemm_ctas=max(1, 24 // world),
+                            emulated_inputs=list(zip(xs, ws)))
+        torch.cuda.synchronize()
+        symm.check()
+    acc = sum((x.float() @ w.float().t()).to(torch.bfloat16).float() for x, w in zip(xs, ws))
+    h = (acc.to(torch.bfloat16).float() + residual.float()).to(torch.bfloat16).float()
+    y = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + layer.eps) * gam.float()).to(torch.bfloat16).float()
+    for r in range(world):
+        got_h = symm.rank_view(layer.residual_out, r)[:tokens].float()
+        got_y = symm.rank_view(layer.out, r)[:tokens].float()
+        assert (got_h - h).abs().max().item() <= 0.02 * h.abs().max().item() + 0.05
+        assert (got_y - y).abs().max().item() <= 0.1
+    symm.destroy()
