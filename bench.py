@@ -173,17 +173,20 @@ def main():
         return max_over_ranks(start.elapsed_time(end) / steps)  # ms per step
 
     # ------------------------------------------------------------------ pick the fused variant (untimed)
-    def fused(t, mode, nvls):
-        return lambda: layer.forward_fused(xs[t], mode=mode, nvls=nvls)
+    def fused(t, mode, nvls, reducers):
+        if mode < 0:  # two launches: tcgen05 GEMM, then the fused allreduce + residual + RMSNorm kernel
+            return lambda: layer.forward(xs[t])
+        return lambda: layer.forward_fused(xs[t], mode=mode, nvls=nvls, num_reducers=reducers)
 
-    variants = [(0, False), (1, False)] + ([(0, True), (1, True)] if symm.nvls else [])
+    nvls_opts = [True] if symm.nvls else [False]
+    variants = [(m, nv, r) for m in (0, 1) for nv in nvls_opts for r in (24, 48)] + [(-1, symm.nvls, 0)]
     if world == 1:
-        variants = [(0, False)]
+        variants = [(0, False, 64), (1, False, 64), (-1, False, 0)]
     best = {}
     for t in TOKEN_SIZES:
         scores = {}
-        for mode, nvls in variants:
-            scores[(mode, nvls)] = time_steps(fused(t, mode, nvls), 5, 3)
+        for v in variants:
+            scores[v] = time_steps(fused(t, *v), 5, 3)
         best[t] = min(scores, key=scores.get)
 
     # ------------------------------------------------------------------ headline: fused TP layer at T = 8192
@@ -191,10 +194,10 @@ def main():
                            int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
     if rank == 0:
         sampler.start()
-    head_mode, head_nvls = best[HEADLINE_T]
-    head_fn = fused(HEADLINE_T, head_mode, head_nvls)
+    head_mode, head_nvls, head_reducers = best[HEADLINE_T]
+    head_fn = fused(HEADLINE_T, head_mode, head_nvls, head_reducers)
     ms_per_step = time_steps(head_fn, args.steps, max(args.warmup, 3))
-    launches = args.steps * (1 if head_mode == 0 else 2)
+    launches = args.steps * (1 if head_mode == 0 else 2)  # mode 1 and the two-launch path (-1) use two kernels
 
     # ------------------------------------------------------------------ per-T table: eager launches and CUDA-graph replay
     tp_us, tp_graph_us, tp_unfused_us, tp_baseline_us = {}, {}, {}, {}
@@ -211,7 +214,10 @@ def main():
             torch.cuda.synchronize()
             with torch.cuda.graph(graph, stream=side):
                 for _ in range(reps):
-                    layer.forward_fused(xs[t], mode=best[t][0], nvls=best[t][1], stream=side)
+                    if best[t][0] < 0:
+                        layer.forward(xs[t], stream=side)
+                    else:
+                        layer.forward_fused(xs[t], mode=best[t][0], nvls=best[t][1], num_reducers=best[t][2], stream=side)
         barrier()
         tp_graph_us[str(t)] = round(time_steps(graph.replay, 5, 2) * 1e3 / reps, 2)
         # two-kernel path of this library (GEMM, then allreduce+residual+norm)
@@ -236,7 +242,10 @@ def main():
 
     def e2e_step():
         x_dev.copy_(x_host, non_blocking=True)
-        out, _ = layer.forward_fused(x_dev, mode=head_mode, nvls=head_nvls)
+        if head_mode < 0:
+            out, _ = layer.forward(x_dev)
+        else:
+            out, _ = layer.forward_fused(x_dev, mode=head_mode, nvls=head_nvls, num_reducers=head_reducers)
         result_host.copy_(out[:, :8].float().abs().mean().reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller looks at the metric every step
 
@@ -306,8 +315,11 @@ def main():
                        "nvls": bool(symm.nvls)},
             "tokens_per_s": round(HEADLINE_T / (ms_per_step * 1e-3), 1),
             "aggregate_tflops": round(flops / (ms_per_step * 1e-3) / 1e12, 1),
-            "variant": {"mode": head_mode, "nvls": head_nvls, "kernel": "tpFusedKernel (tcgen05 GEMM + multimem/peer reduce + "
-                        "residual + RMSNorm in one launch)" + ("" if head_mode == 0 else " + local scale pass")},
+            "variant": {"mode": head_mode, "nvls": head_nvls, "reducer_ctas": head_reducers,
+                        "kernel": ("gemmBf16Kernel (tcgen05) then twoShot/LL allreduce+residual+RMSNorm kernel" if head_mode < 0 else
+                                   "tpFusedKernel (tcgen05 GEMM + multimem/peer reduce + residual + RMSNorm in one launch)" +
+                                   ("" if head_mode == 0 else " + local scale pass")),
+                        "per_T": {str(t): list(best[t]) for t in TOKEN_SIZES}},
             "tp_layer_us": tp_us,
             "tp_layer_graph_replay_us": tp_graph_us,
             "tp_layer_two_kernel_us": tp_unfused_us,

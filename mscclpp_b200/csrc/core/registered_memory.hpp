@@ -1,0 +1,105 @@
+// Internal layouts behind RegisteredMemory / Endpoint / Connection.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include <mscclpp/core.hpp>
+
+#include "socket.hpp"
+
+namespace mscclpp {
+
+// Everything needed to reach one GPU (or host) allocation from another process of the same host.
+// Import order: same process -> raw pointer; VMM allocation -> POSIX fd through the fd server;
+// cudaMalloc allocation -> legacy CUDA IPC handle. (Fabric handles for multi-node NVLink are not
+// produced: this library targets one NVSwitch box.)
+struct GpuIpcMemHandle {
+  enum Kind : uint32_t { kNone = 0, kRuntimeIpc = 1, kPosixFd = 2, kHost = 4 };
+  uint32_t kinds = kNone;
+  cudaIpcMemHandle_t runtimeIpc{};
+  char fdServer[96] = {0};
+  uint32_t fdId = 0;
+  uint64_t baseAddr = 0;   // base of the allocation in the owner
+  uint64_t allocSize = 0;  // size of the whole allocation
+  uint64_t offset = 0;     // offset of the registered range inside the allocation
+  int deviceId = -1;
+
+  static GpuIpcMemHandle create(void* ptr, size_t size);
+};
+
+// A mapping of somebody else's allocation into this process.
+class GpuIpcMapping {
+ public:
+  // One mapping per remote allocation and process: registrations of different ranges of the same
+  // allocation (semaphore tokens of one pool, slices of one buffer) share it.
+  static std::shared_ptr<GpuIpcMapping> acquire(const GpuIpcMemHandle& handle);
+  explicit GpuIpcMapping(const GpuIpcMemHandle& handle);
+  ~GpuIpcMapping();
+  void* base() const { return base_; }
+
+ private:
+  void* base_ = nullptr;
+  size_t size_ = 0;
+  bool vmm_ = false;
+  uint64_t vmmHandle_ = 0;
+};
+
+struct RegisteredMemory::Impl {
+  void* data = nullptr;          // usable pointer in this process
+  void* originalDataPtr = nullptr;
+  size_t size = 0;
+  uint64_t hostHash = 0;
+  uint64_t pidHash = 0;
+  TransportFlags transports;
+  bool isLocal = true;
+  bool isHostMemory = false;
+  int deviceId = -1;
+  GpuIpcMemHandle ipc;
+  std::shared_ptr<GpuIpcMapping> mapping;   // imported memory only
+  uint32_t registeredFdId = 0;              // local VMM memory only (fd parked in the fd server)
+
+  ~Impl();
+  std::vector<char> serialize() const;
+  static std::shared_ptr<Impl> deserialize(const std::vector<char>& data);
+};
+
+struct Endpoint::Impl {
+  EndpointConfig config;
+  uint64_t hostHash = 0;
+  uint64_t pidHash = 0;
+  SocketAddress ethAddress;                  // Ethernet: where this endpoint accepts its peer
+  std::shared_ptr<Socket> ethListener;       // local side only
+  std::vector<char> serialize() const;
+  static std::shared_ptr<Impl> deserialize(const std::vector<char>& data);
+};
+
+class BaseConnection {
+ public:
+  BaseConnection(std::shared_ptr<Context> context, const Endpoint& local, const Endpoint& remote)
+      : context_(context), local_(local), remote_(remote) {}
+  virtual ~BaseConnection() = default;
+  virtual void write(RegisteredMemory dst, uint64_t dstOffset, RegisteredMemory src, uint64_t srcOffset, uint64_t size) = 0;
+  virtual void updateAndSync(RegisteredMemory dst, uint64_t dstOffset, uint64_t* src, uint64_t newValue) = 0;
+  virtual void flush(int64_t timeoutUsec) = 0;
+  virtual Transport transport() const = 0;
+  virtual Transport remoteTransport() const = 0;
+  std::shared_ptr<Context> context() const { return context_; }
+  const Device& localDevice() const { return local_.device(); }
+  int maxWriteQueueSize() const { return local_.maxWriteQueueSize(); }
+  const Endpoint& localEndpoint() const { return local_; }
+  const Endpoint& remoteEndpoint() const { return remote_; }
+
+ protected:
+  std::shared_ptr<Context> context_;
+  Endpoint local_;
+  Endpoint remote_;
+};
+
+void validateTransport(const RegisteredMemory& mem, Transport transport, uint64_t offset, uint64_t size);
+
+}  // namespace mscclpp

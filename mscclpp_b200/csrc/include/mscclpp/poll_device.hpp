@@ -106,6 +106,25 @@ MSCCLPP_DEVICE_INLINE bool waitGreaterEqual(const uint32_t* p, uint32_t expected
   return true;
 }
 
+// Same contract as waitGreaterEqual, for flags that MANY threads of many blocks poll at once: relaxed
+// polls with a short sleep between them (an acquire poll per iteration from thousands of threads keeps
+// the flag's L2 slice so busy that the writer's store queues behind the readers), one acquire fence
+// after the value has been seen.
+MSCCLPP_DEVICE_INLINE bool waitGreaterEqualBackoff(const uint32_t* p, uint32_t expected, DeviceStatus* st, uint64_t budgetNs,
+                                                   uint32_t code, uint32_t rank, uint32_t where, uint32_t peer) {
+  SpinGuard g(st, budgetNs);
+  uint32_t v;
+  while (static_cast<int32_t>((v = ptx::ld_relaxed_sys(p)) - expected) < 0) {
+    __nanosleep(100);
+    if (!g.keepSpinning()) {
+      g.report(code, rank, where, peer, expected, v);
+      return false;
+    }
+  }
+  ptx::fence_acq_rel_sys();
+  return true;
+}
+
 // Bounded mbarrier wait (shared memory). false = gave up.
 MSCCLPP_DEVICE_INLINE bool mbarWait(uint64_t* bar, uint32_t parity, DeviceStatus* st, uint64_t budgetNs, uint32_t where) {
   SpinGuard g(st, budgetNs);

@@ -32,8 +32,6 @@ namespace {
 
 using bf16 = __nv_bfloat16;
 constexpr int kMaxNBlk = 128;
-constexpr int kRowsPerPass = 2;
-constexpr int kUnitsPerThread = 4;  // 16-byte words of one row held by one thread (N <= 4 * 8 * blockDim)
 
 struct TmapSet {
   CUtensorMap a[8];
@@ -84,53 +82,25 @@ struct PartialStoreSignal {
   }
 };
 
-// Sum of kRowsPerPass floats per thread over the CTA.
-template <int R>
-MSCCLPP_DEVICE_INLINE void blockSumMulti(float (&v)[R], float (&total)[R], float* smem /* [32 * R + R] */) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
-#pragma unroll
-  for (int r = 0; r < R; r++) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v[r] += __shfl_xor_sync(0xffffffffu, v[r], o);
-  }
-  __syncthreads();
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < R; r++) smem[warp * R + r] = v[r];
-  }
-  __syncthreads();
-  if (warp == 0) {
-#pragma unroll
-    for (int r = 0; r < R; r++) {
-      float s = lane < nwarps ? smem[lane * R + r] : 0.f;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if (lane == 0) smem[32 * R + r] = s;
-    }
-  }
-  __syncthreads();
-#pragma unroll
-  for (int r = 0; r < R; r++) total[r] = smem[32 * R + r];
-}
+// Reducer CTAs are split into independent groups of kGroupThreads threads; a group owns one row at a
+// time and keeps the whole row in registers (kWordsPerThread 16-byte words per thread), so that
+//  * 5 groups x 16 KB of loads are in flight per CTA (NVLink needs ~2 MB in flight per GPU), and
+//  * the code stays small: one copy of the row pipeline, loops unrolled over the words only.
+constexpr int kGroupThreads = 64;
+constexpr int kGroupsPerCta = gemm::kNumThreads / kGroupThreads;
+constexpr int kWordsPerThread = 16;  // N <= kGroupThreads * kWordsPerThread * 8 = 8192 elements
 
-template <bool kNvls>
-MSCCLPP_DEVICE_INLINE uint4 gatherRowWord(const DeviceComm& c, uint64_t heapOff) {
-  if constexpr (kNvls) {
-    return ptx::multimem_ld_reduce_add_bf16x2_acc32(reinterpret_cast<const void*>(c.mcBase + heapOff));
-  } else {
-    uint4 v[8];
-    float acc[8];
+MSCCLPP_DEVICE_INLINE void groupBarrier(int group) { ptx::named_barrier(2 + group, kGroupThreads); }
+
+// Sum over the 64 threads of a group (two warps).
+MSCCLPP_DEVICE_INLINE float groupSum(float v, float* smem2, int group) {
 #pragma unroll
-    for (int p = 0; p < 8; p++)
-      if (p < c.world) v[p] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(c.peerBase[p] + heapOff));
-    Vec16<bf16>::toFloat(v[0], acc);
-#pragma unroll
-    for (int p = 1; p < 8; p++)
-      if (p < c.world) accumulate16<bf16, SUM>(acc, v[p]);
-    for (int p = 8; p < c.world; p++)
-      accumulate16<bf16, SUM>(acc, ptx::ld_nc_na_v4(reinterpret_cast<const void*>(c.peerBase[p] + heapOff)));
-    return Vec16<bf16>::fromFloat(acc);
-  }
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int warpInGroup = (threadIdx.x >> 5) & 1;
+  groupBarrier(group);  // smem2 free again
+  if ((threadIdx.x & 31) == 0) smem2[warpInGroup] = v;
+  groupBarrier(group);
+  return smem2[0] + smem2[1];
 }
 
 template <bool kNvls>
@@ -138,6 +108,7 @@ MSCCLPP_DEVICE_INLINE void scatterWord(const DeviceComm& c, int rank, uint64_t h
   if constexpr (kNvls) {
     ptx::multimem_st_v4(reinterpret_cast<void*>(c.mcBase + heapOff), v);
   } else {
+#pragma unroll 1
     for (int i = 0; i < c.world; i++) {
       const int p = (rank + i) % c.world;
       ptx::st_na_v4(reinterpret_cast<void*>(c.peerBase[p] + heapOff), v);
@@ -164,147 +135,152 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
   const uint64_t rinvOff = a.rinv ? reinterpret_cast<uint64_t>(a.rinv) - c.peerBase[c.rank] : 0;
   const char* gamma = reinterpret_cast<const char*>(a.gamma);
 
-  __shared__ float redSmem[32 * kRowsPerPass + kRowsPerPass];
-  __shared__ int okSmem;
-  if (threadIdx.x == 0) okSmem = 1;
-  __syncthreads();
+  __shared__ float sumSmem[kGroupsPerCta][2];
+  __shared__ int okSmem[kGroupsPerCta];
+  const int group = threadIdx.x / kGroupThreads;
+  const int lane = threadIdx.x % kGroupThreads;
+  if (lane == 0) okSmem[group] = 1;
+  groupBarrier(group);
 
+  const int globalGroup = reducerIdx * kGroupsPerCta + group;
+  const int numGroups = numReducers * kGroupsPerCta;
   int readyMb = -1;
   bool healthy = true;
   // owned row j -> global row: unit = rank + (j / rpu) * world, row = unit * rpu + j % rpu
-  for (int j0 = reducerIdx * kRowsPerPass; j0 < ownedRows && healthy; j0 += numReducers * kRowsPerPass) {
-    int rows[kRowsPerPass];
-#pragma unroll
-    for (int r = 0; r < kRowsPerPass; r++) {
-      const int j = j0 + r;
-      const int row = (rank + (j / rpu) * world) * rpu + (j % rpu);
-      rows[r] = (j < ownedRows && row < M) ? row : -1;
-    }
-    // ---- wait until every rank has produced every tile of the row blocks these rows live in
-#pragma unroll
-    for (int r = 0; r < kRowsPerPass; r++) {
-      if (rows[r] < 0) continue;
-      const int mb = rows[r] / gemm::kBlockM;
-      if (mb == readyMb) continue;
-      for (int i = threadIdx.x; i < world * numNBlk; i += blockDim.x) {
+#pragma unroll 1
+  for (int j = globalGroup; j < ownedRows && healthy; j += numGroups) {
+    const int row = (rank + (j / rpu) * world) * rpu + (j % rpu);
+    if (row >= M) continue;
+    // ---- wait until every rank has produced every tile of the row block this row lives in
+    const int mb = row / gemm::kBlockM;
+    if (mb != readyMb) {
+#pragma unroll 1
+      for (int i = lane; i < world * numNBlk; i += kGroupThreads) {
         const int src = i / numNBlk, nb = i % numNBlk;
-        if (!waitGreaterEqual(readyFlag(c, rank, mb, src, nb), epoch, c.status, c.timeoutNs, kDevTimeoutFlag, rank,
-                              7000 + mb, src)) {
-          okSmem = 0;
+        if (!waitGreaterEqualBackoff(readyFlag(c, rank, mb, src, nb), epoch, c.status, c.timeoutNs, kDevTimeoutFlag, rank,
+                                     7000 + mb, src)) {
+          okSmem[group] = 0;
         }
       }
-      __syncthreads();
+      groupBarrier(group);
       readyMb = mb;
-      if (okSmem == 0) healthy = false;
-    }
-    if (!healthy) break;
-
-    // ---- pass 1: reduced partial + residual, kept in registers; row sum of squares.
-    // All loads of the pass are issued before the first use, so one CTA keeps
-    // 2 x kRowsPerPass x kUnitsPerThread x 16 B per thread in flight.
-    uint4 h[kRowsPerPass][kUnitsPerThread];
-    uint4 res[kRowsPerPass][kUnitsPerThread];
-    float ss[kRowsPerPass];
-#pragma unroll
-    for (int r = 0; r < kRowsPerPass; r++) {
-#pragma unroll
-      for (int k = 0; k < kUnitsPerThread; k++) {
-        const int ru = threadIdx.x + k * blockDim.x;
-        h[r][k] = make_uint4(0, 0, 0, 0);
-        res[r][k] = make_uint4(0, 0, 0, 0);
-        if (rows[r] >= 0 && ru < unitsPerRow) {
-          const uint64_t off = (static_cast<uint64_t>(rows[r]) * unitsPerRow + ru) * 16;
-          h[r][k] = gatherRowWord<kNvls>(c, partialOff + off);
-          if (a.residualIn) res[r][k] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(local + resInOff + off));
-        }
+      if (okSmem[group] == 0) {
+        healthy = false;
+        break;
       }
     }
+    const uint64_t rowOff = static_cast<uint64_t>(row) * unitsPerRow * 16;
+
+    // ---- gather: the row summed over all ranks, packed bf16 in registers
+    uint4 h[kWordsPerThread];
+    if constexpr (kNvls) {
 #pragma unroll
-    for (int r = 0; r < kRowsPerPass; r++) {
-      ss[r] = 0.f;
+      for (int k = 0; k < kWordsPerThread; k++) {
+        const int w = lane + k * kGroupThreads;
+        h[k] = make_uint4(0, 0, 0, 0);
+        if (w < unitsPerRow)
+          h[k] = ptx::multimem_ld_reduce_add_bf16x2_acc32(reinterpret_cast<const void*>(c.mcBase + partialOff + rowOff + w * 16));
+      }
+    } else {
+      // two halves of 8 words; per half one fp32 accumulator set, peers visited two at a time
 #pragma unroll
-      for (int k = 0; k < kUnitsPerThread; k++) {
-        const int ru = threadIdx.x + k * blockDim.x;
-        if (rows[r] >= 0 && ru < unitsPerRow) {
-          float f[8];
-          Vec16<bf16>::toFloat(h[r][k], f);
-          if (a.residualIn) {
-            float rf[8];
-            Vec16<bf16>::toFloat(res[r][k], rf);
+      for (int half = 0; half < 2; half++) {
+        float acc[8][8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) f[i] += rf[i];
-            h[r][k] = Vec16<bf16>::fromFloat(f);
-            Vec16<bf16>::toFloat(h[r][k], f);
+        for (int k = 0; k < 8; k++) {
+#pragma unroll
+          for (int i = 0; i < 8; i++) acc[k][i] = 0.f;
+        }
+#pragma unroll 1
+        for (int p = 0; p < world; p++) {
+          uint4 v[8];
+#pragma unroll
+          for (int k = 0; k < 8; k++) {
+            const int w = lane + (half * 8 + k) * kGroupThreads;
+            v[k] = make_uint4(0, 0, 0, 0);
+            if (w < unitsPerRow) v[k] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(c.peerBase[p] + partialOff + rowOff + w * 16));
           }
 #pragma unroll
-          for (int i = 0; i < 8; i++) ss[r] += f[i] * f[i];
+          for (int k = 0; k < 8; k++) accumulate16<bf16, SUM>(acc[k], v[k]);
         }
+#pragma unroll
+        for (int k = 0; k < 8; k++) h[half * 8 + k] = Vec16<bf16>::fromFloat(acc[k]);
+      }
+    }
+
+    // ---- residual add (rounded to bf16 like the unfused composition), sum of squares
+    float ss = 0.f;
+#pragma unroll
+    for (int half = 0; half < 2; half++) {
+      uint4 res[8];
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        const int w = lane + (half * 8 + k) * kGroupThreads;
+        res[k] = make_uint4(0, 0, 0, 0);
+        if (a.residualIn && w < unitsPerRow) res[k] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(local + resInOff + rowOff + w * 16));
+      }
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        float f[8], rf[8];
+        Vec16<bf16>::toFloat(h[half * 8 + k], f);
+        if (a.residualIn) {
+          Vec16<bf16>::toFloat(res[k], rf);
+#pragma unroll
+          for (int i = 0; i < 8; i++) f[i] += rf[i];
+          h[half * 8 + k] = Vec16<bf16>::fromFloat(f);
+          Vec16<bf16>::toFloat(h[half * 8 + k], f);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) ss += f[i] * f[i];
       }
     }
     if (a.residualOut) {
 #pragma unroll
-      for (int r = 0; r < kRowsPerPass; r++) {
-#pragma unroll
-        for (int k = 0; k < kUnitsPerThread; k++) {
-          const int ru = threadIdx.x + k * blockDim.x;
-          if (rows[r] >= 0 && ru < unitsPerRow) {
-            const uint64_t off = (static_cast<uint64_t>(rows[r]) * unitsPerRow + ru) * 16;
-            scatterWord<kNvls>(c, rank, resOutOff + off, h[r][k]);
-          }
-        }
+      for (int k = 0; k < kWordsPerThread; k++) {
+        const int w = lane + k * kGroupThreads;
+        if (w < unitsPerRow) scatterWord<kNvls>(c, rank, resOutOff + rowOff + w * 16, h[k]);
       }
     }
-    float total[kRowsPerPass];
-    blockSumMulti<kRowsPerPass>(ss, total, redSmem);
+    const float total = groupSum(ss, sumSmem[group], group);
+    const float rinv = rsqrtf(total / static_cast<float>(N) + a.eps);
 
-    // ---- pass 2: normalise (mode 0) or publish 1/rms (mode 1)
-    uint4 gam[kUnitsPerThread];
-    if (a.mode != 1 && gamma) {
-#pragma unroll
-      for (int k = 0; k < kUnitsPerThread; k++) {
-        const int ru = threadIdx.x + k * blockDim.x;
-        gam[k] = ru < unitsPerRow ? *reinterpret_cast<const uint4*>(gamma + static_cast<size_t>(ru) * 16) : make_uint4(0, 0, 0, 0);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < kRowsPerPass; r++) {
-      if (rows[r] < 0) continue;
-      const float rinv = rsqrtf(total[r] / static_cast<float>(N) + a.eps);
-      if (a.mode == 1) {
-        if (threadIdx.x == 0) {
-          const uint64_t off = rinvOff + static_cast<uint64_t>(rows[r]) * 4;
-          if constexpr (kNvls) {
-            ptx::multimem_st_u32(reinterpret_cast<void*>(c.mcBase + off), __float_as_uint(rinv));
-          } else {
-            for (int p = 0; p < world; p++) ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peerBase[p] + off), __float_as_uint(rinv));
-          }
+    // ---- normalise and publish (mode 0), or publish 1/rms only (mode 1)
+    if (a.mode == 1) {
+      if (lane == 0) {
+        const uint64_t off = rinvOff + static_cast<uint64_t>(row) * 4;
+        if constexpr (kNvls) {
+          ptx::multimem_st_u32(reinterpret_cast<void*>(c.mcBase + off), __float_as_uint(rinv));
+        } else {
+          for (int p = 0; p < world; p++) ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peerBase[p] + off), __float_as_uint(rinv));
         }
-      } else {
+      }
+    } else {
 #pragma unroll
-        for (int k = 0; k < kUnitsPerThread; k++) {
-          const int ru = threadIdx.x + k * blockDim.x;
-          if (ru < unitsPerRow) {
-            const uint64_t off = (static_cast<uint64_t>(rows[r]) * unitsPerRow + ru) * 16;
-            float f[8];
-            Vec16<bf16>::toFloat(h[r][k], f);
-            if (gamma) {
-              float g[8];
-              Vec16<bf16>::toFloat(gam[k], g);
+      for (int k = 0; k < kWordsPerThread; k++) {
+        const int w = lane + k * kGroupThreads;
+        if (w < unitsPerRow) {
+          float f[8];
+          Vec16<bf16>::toFloat(h[k], f);
+          if (gamma) {
+            float g[8];
+            Vec16<bf16>::toFloat(*reinterpret_cast<const uint4*>(gamma + static_cast<size_t>(w) * 16), g);
 #pragma unroll
-              for (int i = 0; i < 8; i++) f[i] = f[i] * rinv * g[i];
-            } else {
+            for (int i = 0; i < 8; i++) f[i] = f[i] * rinv * g[i];
+          } else {
 #pragma unroll
-              for (int i = 0; i < 8; i++) f[i] = f[i] * rinv;
-            }
-            scatterWord<kNvls>(c, rank, outOff + off, Vec16<bf16>::fromFloat(f));
+            for (int i = 0; i < 8; i++) f[i] = f[i] * rinv;
           }
+          scatterWord<kNvls>(c, rank, outOff + rowOff + w * 16, Vec16<bf16>::fromFloat(f));
         }
       }
     }
   }
   // every store of mine is issued: meet the peers' reducers with the same index. After it, everything
   // their reducers wrote into my buffers has landed.
-  if (healthy) rankBarrier(c, rank, 2, reducerIdx, epoch);
+  __syncthreads();
+  bool allOk = true;
+  for (int g = 0; g < kGroupsPerCta; g++) allOk = allOk && okSmem[g] != 0;
+  if (allOk) rankBarrier(c, rank, 2, reducerIdx, epoch);
 }
 
 template <int kBlockN, bool kNvls>
@@ -386,7 +362,7 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   const int world = args.comm.world;
   if (M <= 0 || N % args.blockN != 0 || K % gemm::kBlockK != 0) return cudaErrorInvalidValue;
   if (N / args.blockN > kMaxNBlk || world > 8) return cudaErrorInvalidValue;
-  if (N * 2 / 16 > kUnitsPerThread * gemm::kNumThreads) return cudaErrorInvalidValue;
+  if (N * 2 / 16 > kWordsPerThread * kGroupThreads) return cudaErrorInvalidValue;
   const int numMBlk = (M + gemm::kBlockM - 1) / gemm::kBlockM;
   if (static_cast<uint64_t>(numMBlk) * kMaxRanks * kMaxNBlk * 4 > kAuxFlagBytes) return cudaErrorInvalidValue;
   if (args.mode == 1 && args.rinv == nullptr) return cudaErrorInvalidValue;
