@@ -287,7 +287,10 @@ PYBIND11_MODULE(_native, m) {
       .def("emulated_ptr", [](SymmetricHeap& h, uintptr_t p, int r) {
         return reinterpret_cast<uintptr_t>(h.emulatedPtr(reinterpret_cast<void*>(p), r));
       })
-      .def("status", [](SymmetricHeap& h) { return h.status(); })
+      .def("status", [](SymmetricHeap& h) {
+        h.refreshStatus();
+        return h.status();
+      })
       .def("check_status", &SymmetricHeap::checkStatus)
       .def("reset_status", &SymmetricHeap::resetStatus)
       .def("set_timeout_ms", &SymmetricHeap::setTimeoutMs)

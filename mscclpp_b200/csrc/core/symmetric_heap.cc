@@ -35,7 +35,12 @@ void SymmetricHeap::initLayout(const Options& options) {
   usedBlocks_.clear();
   freeBlocks_[arenaBegin_] = bytes_ - arenaBegin_;
 
-  status_ = static_cast<DeviceStatus*>(detail::gpuCallocHost(sizeof(DeviceStatus), cudaHostAllocMapped));
+  // The error block lives in DEVICE memory: every bounded wait polls its `poisoned` word, and a word in
+  // host-mapped memory would turn each poll into a PCIe round trip in the middle of the kernels' hot
+  // spin loops. The host reads it with a copy after synchronising.
+  statusDev_ = static_cast<DeviceStatus*>(detail::gpuCalloc(sizeof(DeviceStatus)));
+  status_ = new DeviceStatus();
+  std::memset(status_, 0, sizeof(DeviceStatus));
   std::memset(&comm_, 0, sizeof(comm_));
   for (int r = 0; r < world_; r++) comm_.peerBase[r] = peerBase_[r];
   comm_.mcBase = mcBase_;
@@ -43,7 +48,7 @@ void SymmetricHeap::initLayout(const Options& options) {
   comm_.llScratchOff = ctlBytes;
   comm_.llSlotBytes = options.llSlotBytes;
   comm_.auxFlagsOff = auxOff;
-  comm_.status = status_;
+  comm_.status = statusDev_;
   int64_t ms = options.timeoutMs >= 0 ? options.timeoutMs : env()->deviceTimeoutMs;
   comm_.timeoutNs = static_cast<uint64_t>(ms) * 1000000ull;
   comm_.rank = emulated_ ? 0 : rank_;
@@ -255,7 +260,9 @@ void SymmetricHeap::destroy() {
       if (localHandle_) (void)drv->cuMemRelease(localHandle_);
     }
   }
-  if (status_) detail::gpuFreeHost(status_);
+  if (statusDev_) detail::gpuFree(statusDev_);
+  statusDev_ = nullptr;
+  delete status_;
   status_ = nullptr;
 }
 
@@ -321,7 +328,9 @@ void* SymmetricHeap::emulatedPtr(void* ptr, int r) const {
 }
 
 void SymmetricHeap::checkStatus() {
-  if (status_ == nullptr || status_->code == kDevOk) return;
+  if (statusDev_ == nullptr) return;
+  refreshStatus();
+  if (status_->code == kDevOk) return;
   DeviceStatus s = *status_;
   std::string what = "device-side wait gave up: code " + std::to_string(s.code) + " rank " + std::to_string(s.rank) +
                      " block " + std::to_string(s.block) + " site " + std::to_string(s.where) + " peer " +
@@ -330,8 +339,13 @@ void SymmetricHeap::checkStatus() {
   throw Error(what, ErrorCode::Timeout);
 }
 
+void SymmetricHeap::refreshStatus() {
+  if (statusDev_ && status_) gpuMemcpy(status_, statusDev_, sizeof(DeviceStatus), cudaMemcpyDeviceToHost);
+}
+
 void SymmetricHeap::resetStatus() {
   if (status_) std::memset(status_, 0, sizeof(DeviceStatus));
+  if (statusDev_) MSCCLPP_CUDATHROW(cudaMemset(statusDev_, 0, sizeof(DeviceStatus)));
 }
 
 void SymmetricHeap::setTimeoutMs(int64_t ms) { comm_.timeoutNs = static_cast<uint64_t>(ms) * 1000000ull; }

@@ -65,7 +65,9 @@ class SymmetricHeap {
   DeviceComm deviceComm() const { return comm_; }
 
   // Host view of the device error block. checkStatus() throws Error(Timeout) if a device wait gave up.
+  // Copy of the device error block as of the last checkStatus()/refreshStatus() (call after a synchronize).
   const DeviceStatus& status() const { return *status_; }
+  void refreshStatus();
   void checkStatus();
   void resetStatus();
   void setTimeoutMs(int64_t ms);
@@ -90,7 +92,8 @@ class SymmetricHeap {
   uint64_t peerHandles_[kMaxRanks] = {};
   uint64_t mcHandle_ = 0;
   void* emulatedAlloc_ = nullptr;
-  DeviceStatus* status_ = nullptr;
+  DeviceStatus* status_ = nullptr;     // host copy
+  DeviceStatus* statusDev_ = nullptr;  // device memory, what kernels see
   DeviceComm comm_{};
 
   // host-side first-fit allocator over [arenaBegin_, bytes_)

@@ -95,6 +95,7 @@ struct SharedState {
   uint64_t* tmemEmpty;  // [2] epilogue -> MMA
   uint32_t* tmemBase;
   volatile uint32_t* abortFlag;
+  volatile uint32_t* epiArrivals;  // epilogue warps that finished storing, summed over the tiles so far
 };
 
 // Body of a GEMM CTA. All 192 threads call it. `ctaIdx`/`numCtas` index the persistent tile loop.
@@ -117,6 +118,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
   st.tmemEmpty = bars + 2 * Cfg::kStages + 2;
   st.tmemBase = reinterpret_cast<uint32_t*>(bars + 2 * Cfg::kStages + 4);
   st.abortFlag = reinterpret_cast<volatile uint32_t*>(st.tmemBase + 1);
+  st.epiArrivals = reinterpret_cast<volatile uint32_t*>(st.tmemBase + 2);
 
   const int numMBlk = (shape.M + kBlockM - 1) / kBlockM;
   const int numNBlk = shape.N / kBlockN;
@@ -133,6 +135,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       ptx::mbar_init(&st.tmemEmpty[s], kNumEpilogueWarps);  // one arrival per epilogue warp
     }
     *st.abortFlag = 0;
+    *st.epiArrivals = 0;
     ptx::fence_mbar_init();
     ptx::tma_prefetch_desc(tmapA);
     ptx::tma_prefetch_desc(tmapB);
@@ -258,9 +261,31 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       ptx::tcgen05_fence_before_sync();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&st.tmemEmpty[acc]);
-      // all epilogue threads have issued their stores -> let the fused kernel publish the tile
-      ptx::named_barrier(1, kNumEpilogueThreads);
-      epi.tileDone(mBlk, nBlk, threadIdx.x - 64);
+      if constexpr (Epilogue::kNeedsTileBarrier) {
+        // All epilogue warps have issued their stores -> let the fused kernel publish the tile. The
+        // meeting point is a counter with a bounded wait (not bar.sync): if one warp gave up on the
+        // accumulator barrier above, the others must not wait for it forever.
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence_block();
+          atomicAdd(const_cast<uint32_t*>(st.epiArrivals), 1u);
+          const uint32_t target = static_cast<uint32_t>(it + 1) * kNumEpilogueWarps;
+          SpinGuard g(status, budgetNs);
+          while (static_cast<int32_t>(*st.epiArrivals - target) < 0) {
+            if (*st.abortFlag || !g.keepSpinning()) {
+              *st.abortFlag = 1;
+              break;
+            }
+          }
+          __threadfence_block();
+        }
+        __syncwarp();
+        if (*st.abortFlag) {
+          ok = false;
+          break;
+        }
+        if (warp == 2) epi.tileDone(mBlk, nBlk, lane);
+      }
     }
     if (!ok && lane == 0) *st.abortFlag = 1;
   }
@@ -274,6 +299,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
 
 // Plain epilogue: convert to bf16 and store row-major D[M, ldd].
 struct StoreBf16 {
+  static constexpr bool kNeedsTileBarrier = false;
   __nv_bfloat16* D;
   int ldd;
   int M;

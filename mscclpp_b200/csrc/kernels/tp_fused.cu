@@ -38,18 +38,25 @@ struct TmapSet {
   CUtensorMap b[8];
 };
 
-MSCCLPP_DEVICE_INLINE uint32_t* readyFlag(const DeviceComm& c, int owner, int mBlk, int src, int nBlk) {
-  return reinterpret_cast<uint32_t*>(c.peerBase[owner] + c.auxFlagsOff) +
-         ((static_cast<size_t>(mBlk) * kMaxRanks + src) * kMaxNBlk + nBlk);
+constexpr int kMaxMBlk = 4096;
+// Aux flag region of every heap: [kMaxMBlk][kMaxRanks] epoch-stamped "row block of rank src is complete"
+// flags written by the producers, followed by kMaxMBlk local tile counters.
+MSCCLPP_DEVICE_INLINE uint32_t* readyFlag(const DeviceComm& c, int owner, int mBlk, int src) {
+  return reinterpret_cast<uint32_t*>(c.peerBase[owner] + c.auxFlagsOff) + (static_cast<size_t>(mBlk) * kMaxRanks + src);
+}
+MSCCLPP_DEVICE_INLINE uint32_t* tileCounter(const DeviceComm& c, int rank, int mBlk) {
+  return reinterpret_cast<uint32_t*>(c.peerBase[rank] + c.auxFlagsOff) + static_cast<size_t>(kMaxMBlk) * kMaxRanks + mBlk;
 }
 
 struct PartialStoreSignal {
+  static constexpr bool kNeedsTileBarrier = true;
   const DeviceComm* comm;
   bf16* partial;  // this rank's partial product [M, N]
   int M, N;
   int rank;
   int rowsPerUnit;
   int numUnits;
+  int numNBlk;
   uint32_t epoch;
 
   MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32]) const {
@@ -67,18 +74,27 @@ struct PartialStoreSignal {
     }
   }
 
-  // Called by all epilogue threads after a CTA-wide (epilogue) barrier: thread o tells rank o.
-  MSCCLPP_DEVICE_INLINE void tileDone(int mBlk, int nBlk, int tid) const {
+  // Called by one warp after every epilogue warp has stored its part. One thread counts the tile; the CTA that
+  // completes the LAST tile of a row block publishes one flag per owner rank (the classic last-block
+  // pattern: fence, count, fence), so a row block costs `world` small NVLink stores, not world x tiles.
+  MSCCLPP_DEVICE_INLINE void tileDone(int mBlk, int /*nBlk*/, int tid) const {
+    if (tid != 0) return;
+    __threadfence();
+    uint32_t* counter = tileCounter(*comm, rank, mBlk);
+    const uint32_t done = atomicAdd(counter, 1u) + 1u;
+    if (done != static_cast<uint32_t>(numNBlk)) return;
+    *counter = 0;  // every tile of this row block has been counted: ready for the next launch
+    __threadfence();
     const int world = comm->world;
-    if (tid >= world) return;
     const int u0 = (mBlk * gemm::kBlockM) / rowsPerUnit;
     int u1 = ((mBlk + 1) * gemm::kBlockM + rowsPerUnit - 1) / rowsPerUnit;
     if (u1 > numUnits) u1 = numUnits;
-    // does rank `tid` own one of the units [u0, u1)?
-    const int first = (tid - (u0 % world) + world) % world;
-    if (first >= u1 - u0) return;
     ptx::fence_acq_rel_sys();
-    ptx::st_release_sys(readyFlag(*comm, tid, mBlk, rank, nBlk), epoch);
+    for (int o = 0; o < world; o++) {
+      // does rank o own one of the units [u0, u1)?
+      const int first = (o - (u0 % world) + world) % world;
+      if (first < u1 - u0) ptx::st_release_sys(readyFlag(*comm, o, mBlk, rank), epoch);
+    }
   }
 };
 
@@ -121,7 +137,6 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
   const DeviceComm& c = a.comm;
   const int world = c.world;
   const int M = a.shape.M, N = a.shape.N;
-  const int numNBlk = N / a.blockN;
   const int rpu = a.rowsPerUnit;
   const int numUnits = (M + rpu - 1) / rpu;
   const int ownedUnits = numUnits > rank ? (numUnits - rank + world - 1) / world : 0;
@@ -137,6 +152,14 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
 
   __shared__ float sumSmem[kGroupsPerCta][2];
   __shared__ int okSmem[kGroupsPerCta];
+  // readiness of row blocks is learned once per CTA: one group polls the (remote-written) flags, the
+  // others watch a bitmap in shared memory. Few pollers per flag line keep its L2 slice responsive.
+  __shared__ uint32_t readyBits[kMaxMBlk / 32];
+  __shared__ int pollLock;
+  __shared__ int groupState[kGroupsPerCta];
+  for (int i = threadIdx.x; i < kMaxMBlk / 32; i += blockDim.x) readyBits[i] = 0;
+  if (threadIdx.x == 0) pollLock = 0;
+  __syncthreads();
   const int group = threadIdx.x / kGroupThreads;
   const int lane = threadIdx.x % kGroupThreads;
   if (lane == 0) okSmem[group] = 1;
@@ -154,20 +177,48 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
     // ---- wait until every rank has produced every tile of the row block this row lives in
     const int mb = row / gemm::kBlockM;
     if (mb != readyMb) {
-#pragma unroll 1
-      for (int i = lane; i < world * numNBlk; i += kGroupThreads) {
-        const int src = i / numNBlk, nb = i % numNBlk;
-        if (!waitGreaterEqualBackoff(readyFlag(c, rank, mb, src, nb), epoch, c.status, c.timeoutNs, kDevTimeoutFlag, rank,
-                                     7000 + mb, src)) {
-          okSmem[group] = 0;
+      // Every decision below is taken by lane 0 and read by the group after a barrier, so all 64
+      // threads always agree on which barriers they execute.
+      for (;;) {
+        if (lane == 0) {
+          int st;
+          if ((*reinterpret_cast<volatile uint32_t*>(&readyBits[mb >> 5]) >> (mb & 31)) & 1u) st = 2;       // known ready
+          else if (c.status != nullptr && *reinterpret_cast<volatile uint32_t*>(&c.status->poisoned) != 0) st = 3;  // abort
+          else st = (atomicCAS(&pollLock, 0, 1) == 0) ? 1 : 0;                                               // poll / watch
+          groupState[group] = st;
+        }
+        groupBarrier(group);
+        const int st = groupState[group];
+        if (st == 1) {
+          if (lane < world) {
+            if (!waitGreaterEqualBackoff(readyFlag(c, rank, mb, lane), epoch, c.status, c.timeoutNs, kDevTimeoutFlag, rank,
+                                         7000 + mb, lane)) {
+              okSmem[group] = 0;
+            }
+          }
+          groupBarrier(group);
+          if (lane == 0) {
+            if (okSmem[group]) atomicOr(&readyBits[mb >> 5], 1u << (mb & 31));
+            __threadfence_block();
+            atomicExch(&pollLock, 0);
+          }
+        } else if (st == 0) {
+          __nanosleep(300);
+        }
+        groupBarrier(group);  // groupState may be rewritten from here on
+        if (st == 2) break;
+        if (st == 3 || okSmem[group] == 0) {
+          healthy = false;
+          break;
         }
       }
-      groupBarrier(group);
-      readyMb = mb;
-      if (okSmem[group] == 0) {
-        healthy = false;
+      if (!healthy) {
+        if (lane == 0) okSmem[group] = 0;
         break;
       }
+      // order my loads after the flag writes that another group of this CTA may have observed for me
+      ptx::fence_acq_rel_sys();
+      readyMb = mb;
     }
     const uint64_t rowOff = static_cast<uint64_t>(row) * unitsPerRow * 16;
 
@@ -295,7 +346,7 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
     const uint64_t partialOff = reinterpret_cast<uint64_t>(a.partial) - c.peerBase[c.rank];
     const int numUnits = (a.shape.M + a.rowsPerUnit - 1) / a.rowsPerUnit;
     PartialStoreSignal epi{&c, reinterpret_cast<bf16*>(c.peerBase[rank] + partialOff), a.shape.M, a.shape.N, rank,
-                           a.rowsPerUnit, numUnits, epoch};
+                           a.rowsPerUnit, numUnits, a.shape.N / kBlockN, epoch};
     gemm::gemmCta<kBlockN>(&maps.a[blockIdx.y], &maps.b[blockIdx.y], a.shape, blockIdx.x, a.numGemmCtas, gate, epi,
                            c.status, c.timeoutNs, smemRaw);
   } else {
@@ -364,7 +415,8 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   if (N / args.blockN > kMaxNBlk || world > 8) return cudaErrorInvalidValue;
   if (N * 2 / 16 > kWordsPerThread * kGroupThreads) return cudaErrorInvalidValue;
   const int numMBlk = (M + gemm::kBlockM - 1) / gemm::kBlockM;
-  if (static_cast<uint64_t>(numMBlk) * kMaxRanks * kMaxNBlk * 4 > kAuxFlagBytes) return cudaErrorInvalidValue;
+  if (numMBlk > kMaxMBlk) return cudaErrorInvalidValue;
+  static_assert(static_cast<uint64_t>(kMaxMBlk) * (kMaxRanks + 1) * 4 <= kAuxFlagBytes, "aux flag region too small");
   if (args.mode == 1 && args.rinv == nullptr) return cudaErrorInvalidValue;
   if (args.nvls && args.comm.mcBase == 0) return cudaErrorInvalidValue;
   const int emu = args.emuRanks > 1 ? args.emuRanks : 1;

@@ -108,7 +108,7 @@ def main():
             symm.check()
             e1 = (y.float() - ref).abs().max().item()
             e2 = (r_out.float() - h).abs().max().item()
-            report(f"allreduce_rmsnorm/{algo}/{rows}x{hidden}", e1 < 0.1 and e2 < 0.1, err=e1, res_err=e2)
+            report(f"allreduce_rmsnorm/{algo}/{rows}x{hidden}", e1 < 0.1 and e2 <= 0.02 * h.abs().max().item() + 0.05, err=e1, res_err=e2)
         for t in (gamma, r_out, r_in, y, x):
             symm.release(t)
 
@@ -137,7 +137,7 @@ def main():
                 symm.check()
                 e1 = (out.float() - ref).abs().max().item()
                 e2 = (res.float() - h).abs().max().item()
-                report(f"tp_fused/T={tokens}/nvls={use_nvls}/mode={mode}", e1 < 0.12 and e2 < 0.12, err=e1, res_err=e2)
+                report(f"tp_fused/T={tokens}/nvls={use_nvls}/mode={mode}", e1 < 0.12 and e2 <= 0.02 * h.abs().max().item() + 0.05, err=e1, res_err=e2)
 
     dist.barrier()
     symm.destroy()
