@@ -4,6 +4,7 @@
 #include <pybind11/stl.h>
 
 #include <mscclpp/errors.hpp>
+#include <mscclpp/executor.hpp>
 #include <mscclpp/symmetric_heap.hpp>
 
 #include "../kernels/tp_fused.cuh"
@@ -18,6 +19,31 @@ void checkCudaMore(cudaError_t e, const char* what) {
 }  // namespace
 
 void registerMoreBindings(py::module_& m) {
+  // ------------------------------------------------------------------ executor
+  py::enum_<PacketType>(m, "PacketType").value("LL8", PacketType::LL8).value("LL16", PacketType::LL16);
+  py::class_<ExecutionPlan>(m, "ExecutionPlan")
+      .def(py::init<const std::string&, int>(), py::arg("plan_path"), py::arg("rank"))
+      .def_static("from_string", &ExecutionPlan::fromString, py::arg("json_text"), py::arg("rank"))
+      .def_property_readonly("name", &ExecutionPlan::name)
+      .def_property_readonly("collective", &ExecutionPlan::collective)
+      .def_property_readonly("protocol", &ExecutionPlan::protocol)
+      .def_property_readonly("min_message_size", &ExecutionPlan::minMessageSize)
+      .def_property_readonly("max_message_size", &ExecutionPlan::maxMessageSize)
+      .def_property_readonly("is_in_place", &ExecutionPlan::isInPlace)
+      .def_property_readonly("n_ranks", &ExecutionPlan::nRanks);
+  py::class_<Executor>(m, "Executor")
+      .def(py::init<std::shared_ptr<SymmetricHeap>>(), py::arg("heap"))
+      .def(
+          "execute",
+          [](Executor& self, int rank, uintptr_t sendbuff, uintptr_t recvbuff, size_t sendBytes, size_t recvBytes,
+             DataType dtype, const ExecutionPlan& plan, uintptr_t stream, PacketType packetType) {
+            self.execute(rank, reinterpret_cast<void*>(sendbuff), reinterpret_cast<void*>(recvbuff), sendBytes, recvBytes, dtype,
+                         plan, reinterpret_cast<cudaStream_t>(stream), packetType);
+          },
+          py::arg("rank"), py::arg("sendbuff"), py::arg("recvbuff"), py::arg("send_bytes"), py::arg("recv_bytes"),
+          py::arg("dtype"), py::arg("plan"), py::arg("stream") = 0, py::arg("packet_type") = PacketType::LL16)
+      .def("reset", &Executor::reset);
+
   m.def(
       "tp_fused",
       [](SymmetricHeap& heap, std::vector<uintptr_t> a, std::vector<uintptr_t> b, uintptr_t partial, uintptr_t residualIn,

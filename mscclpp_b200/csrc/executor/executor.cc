@@ -1,0 +1,557 @@
+// ExecutionPlan (JSON -> per-rank op lists) and Executor (op lists -> DevPlan for a message size ->
+// interpreter kernel launch). Chunk-to-byte arithmetic follows the plan format's rules
+// (reference: src/core/executor/execution_plan.cc:191-216, 478-668; src/core/executor/executor.cc:158-563).
+#include <mscclpp/executor.hpp>
+
+#include <algorithm>
+#include <cstring>
+#include <map>
+#include <unordered_map>
+
+#include <mscclpp/gpu_utils.hpp>
+
+#include "../core/json.hpp"
+#include "../core/logger.hpp"
+#include "execution_common.hpp"
+#include "execution_kernel.hpp"
+
+namespace mscclpp {
+
+namespace {
+
+const std::unordered_map<std::string, OpType>& opNames() {
+  static const std::unordered_map<std::string, OpType> table = {
+      {"nop", OpType::NOP},
+      {"barrier", OpType::BARRIER},
+      {"signal", OpType::SIGNAL},
+      {"rlxsignal", OpType::RELAXED_SIGNAL},
+      {"wait", OpType::WAIT},
+      {"rlxwait", OpType::RELAXED_WAIT},
+      {"flush", OpType::FLUSH},
+      {"put", OpType::PUT},
+      {"pws", OpType::PUT_WITH_SIGNAL},
+      {"pwsf", OpType::PUT_WITH_SIGNAL_AND_FLUSH},
+      {"get", OpType::GET},
+      {"copy", OpType::COPY},
+      {"re", OpType::REDUCE},
+      {"res", OpType::REDUCE_SEND},
+      {"rre", OpType::READ_REDUCE},
+      {"rres", OpType::READ_REDUCE_SEND},
+      {"ppkt", OpType::PUT_PACKETS},
+      {"rppkt", OpType::READ_PUT_PACKETS},
+      {"cpkt", OpType::COPY_PACKETS},
+      {"upkt", OpType::UNPACK_PACKETS},
+      {"repkt", OpType::REDUCE_PACKETS},
+      {"respkt", OpType::REDUCE_SEND_PACKETS},
+      {"recpkt", OpType::REDUCE_COPY_PACKETS},
+      {"recspkt", OpType::REDUCE_COPY_SEND_PACKETS},
+      {"glres", OpType::GROUP_LOAD_REDUCE_STORE},
+      {"gstore", OpType::GROUP_STORE},
+      {"gstorepkt", OpType::GROUP_STORE_PACKETS},
+      {"sem_acquire", OpType::SEM_ACQUIRE},
+      {"sem_release", OpType::SEM_RELEASE},
+  };
+  return table;
+}
+
+uint64_t calcOffset(uint64_t sizeUnits, uint64_t index, uint64_t parts, uint64_t alignment) {
+  const uint64_t q = sizeUnits / parts, r = sizeUnits % parts;
+  return (index * q + std::min(index, r)) * alignment;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------ ExecutionPlan
+struct ExecutionPlan::Impl {
+  json::Value root;
+  int rank = 0;
+  std::string name, collective, protocol;
+  bool inplace = false;
+  bool reuseResources = false;
+  bool doubleScratch = false;
+  uint64_t alignment = 16;
+  uint64_t minSize = 0, maxSize = UINT64_MAX;
+  int nThreadsPerBlock = 1024;
+  int nRanks = 0;
+  // mate[type][rank][channel] = (peer, peer's channel index)
+  std::vector<std::vector<DevChannel>> mates[2];
+
+  void load(json::Value&& v, int r) {
+    root = std::move(v);
+    rank = r;
+    name = root.at("name").asString();
+    collective = root.at("collective").asString();
+    protocol = root.at("protocol").asString();
+    if (protocol != "Simple" && protocol != "LL") throw Error("plan '" + name + "': unknown protocol " + protocol, ErrorCode::ExecutorError);
+    inplace = root.boolOr("inplace", false);
+    reuseResources = root.boolOr("reuse_resources", false);
+    doubleScratch = root.boolOr("use_double_scratch_buffer", false);
+    alignment = root.uintOr("buffer_alignment", 16);
+    minSize = root.uintOr("min_message_size", 0);
+    maxSize = root.uintOr("max_message_size", UINT64_MAX);
+    nThreadsPerBlock = static_cast<int>(root.intOr("num_threads_per_block", 1024));
+    const json::Value& gpus = root.at("gpus");
+    nRanks = static_cast<int>(gpus.size());
+    if (nRanks < 1 || nRanks > kMaxRanks) throw Error("plan '" + name + "': unsupported number of ranks", ErrorCode::ExecutorError);
+    if (rank < 0 || rank >= nRanks) throw Error("plan '" + name + "' has no rank " + std::to_string(rank), ErrorCode::ExecutorError);
+    pairChannels();
+  }
+
+  static int typeIndex(const std::string& t) {
+    if (t == "memory") return 0;
+    if (t == "port") return 1;
+    return -1;
+  }
+
+  // The k-th channel from a to b pairs with the k-th channel from b to a (connections are made in per-peer order).
+  void pairChannels() {
+    const json::Value& gpus = root.at("gpus");
+    for (int t = 0; t < 2; t++) {
+      std::vector<std::vector<int>> peers(nRanks);
+      for (int r = 0; r < nRanks; r++) {
+        for (size_t c = 0; c < gpus.at(r).at("channels").size(); c++) {
+          const json::Value& ch = gpus.at(r).at("channels").at(c);
+          if (typeIndex(ch.at("channel_type").asString()) != t) continue;
+          for (size_t i = 0; i < ch.at("connected_to").size(); i++) peers[r].push_back(static_cast<int>(ch.at("connected_to").at(i).asInt()));
+        }
+        if (peers[r].size() > static_cast<size_t>(kExecMaxChannels)) throw Error("plan '" + name + "': too many channels", ErrorCode::ExecutorError);
+      }
+      mates[t].assign(nRanks, {});
+      for (int r = 0; r < nRanks; r++) {
+        std::map<int, int> seen;
+        for (size_t c = 0; c < peers[r].size(); c++) {
+          const int p = peers[r][c];
+          if (p < 0 || p >= nRanks) throw Error("plan '" + name + "': channel to invalid rank", ErrorCode::ExecutorError);
+          const int k = seen[p]++;
+          int mate = -1, count = 0;
+          for (size_t i = 0; i < peers[p].size(); i++) {
+            if (peers[p][i] == r) {
+              if (count == k) {
+                mate = static_cast<int>(i);
+                break;
+              }
+              count++;
+            }
+          }
+          mates[t][r].push_back(DevChannel{static_cast<int16_t>(p), static_cast<int16_t>(mate)});
+        }
+      }
+    }
+  }
+};
+
+ExecutionPlan::ExecutionPlan(const std::string& planPath, int rank) : impl_(std::make_shared<Impl>()) {
+  impl_->load(json::parseFile(planPath), rank);
+}
+ExecutionPlan ExecutionPlan::fromString(const std::string& jsonText, int rank) {
+  ExecutionPlan p;
+  p.impl_ = std::make_shared<Impl>();
+  p.impl_->load(json::parse(jsonText), rank);
+  return p;
+}
+ExecutionPlan::~ExecutionPlan() = default;
+ExecutionPlan::ExecutionPlan(const ExecutionPlan&) = default;
+ExecutionPlan& ExecutionPlan::operator=(const ExecutionPlan&) = default;
+std::string ExecutionPlan::name() const { return impl_->name; }
+std::string ExecutionPlan::collective() const { return impl_->collective; }
+std::string ExecutionPlan::protocol() const { return impl_->protocol; }
+size_t ExecutionPlan::minMessageSize() const { return impl_->minSize; }
+size_t ExecutionPlan::maxMessageSize() const { return impl_->maxSize; }
+bool ExecutionPlan::isInPlace() const { return impl_->inplace; }
+int ExecutionPlan::nRanks() const { return impl_->nRanks; }
+int ExecutionPlan::nThreadsPerBlock() const { return impl_->nThreadsPerBlock; }
+
+// ------------------------------------------------------------------------------------------ plan -> DevPlan
+namespace {
+
+struct Resolved {
+  std::vector<DevOp> ops;
+  DevPlan plan{};
+  uint64_t scratchBytes = 0;  // one half
+};
+
+struct Layout {
+  uint64_t S = 0, C = 0, A = 16;
+  uint64_t chunkUpper = 0;
+  uint64_t inOff = 0, outOff = 0, scratchOff = 0;  // heap offsets
+};
+
+class Resolver {
+ public:
+  Resolver(const ExecutionPlan::Impl& plan, int rank, const Layout& layout) : p_(plan), rank_(rank), l_(layout) {
+    gpu_ = &p_.root.at("gpus").at(rank);
+  }
+
+  Resolved run() {
+    Resolved out;
+    const json::Value& tbs = gpu_->at("threadblocks");
+    if (tbs.size() > static_cast<size_t>(kExecMaxThreadBlocks)) throw Error("plan '" + p_.name + "': too many thread blocks", ErrorCode::ExecutorError);
+    out.plan.nThreadBlocks = static_cast<uint32_t>(tbs.size());
+    collectGroups(out.plan);
+    for (size_t t = 0; t < tbs.size(); t++) {
+      tb_ = &tbs.at(t);
+      out.plan.tbs[t].opBegin = static_cast<uint32_t>(out.ops.size());
+      emitOps(tb_->at("ops"), out.ops, false);
+      out.plan.tbs[t].opEnd = static_cast<uint32_t>(out.ops.size());
+    }
+    out.plan.nOps = static_cast<uint32_t>(out.ops.size());
+    for (int t = 0; t < 2; t++) {
+      const auto& m = p_.mates[t][rank_];
+      for (size_t c = 0; c < m.size(); c++) out.plan.channels[t][c] = m[c];
+    }
+    const json::Value& sems = gpu_->contains("semaphores") ? gpu_->at("semaphores") : emptyArray_;
+    if (sems.size() > static_cast<size_t>(kExecMaxSemaphores)) throw Error("plan '" + p_.name + "': too many semaphores", ErrorCode::ExecutorError);
+    out.plan.nSemaphores = static_cast<uint32_t>(sems.size());
+    for (size_t i = 0; i < sems.size(); i++) out.plan.semInit[i] = static_cast<int32_t>(sems.at(i).at("init_value").asInt());
+    return out;
+  }
+
+ private:
+  void collectGroups(DevPlan& plan) {
+    const json::Value& chans = gpu_->at("channels");
+    int g = 0;
+    for (size_t c = 0; c < chans.size(); c++) {
+      const json::Value& ch = chans.at(c);
+      if (ch.at("channel_type").asString() != "switch") continue;
+      if (g >= 8) {
+        // many switch channels usually repeat the same group (instances): share entries
+      }
+      const json::Value& ranks = ch.at("rank_groups").at(0).at("ranks");
+      DevGroup grp{};
+      grp.nRanks = static_cast<int16_t>(ranks.size());
+      if (ranks.size() > static_cast<size_t>(kExecMaxRanksInGroup)) throw Error("switch group too large", ErrorCode::ExecutorError);
+      for (size_t i = 0; i < ranks.size(); i++) grp.ranks[i] = static_cast<int16_t>(ranks.at(i).asInt());
+      int found = -1;
+      for (int i = 0; i < g; i++)
+        if (std::memcmp(&plan.groups[i], &grp, sizeof(grp)) == 0) found = i;
+      if (found < 0) {
+        if (g >= 8) throw Error("plan '" + p_.name + "': more than 8 distinct switch groups", ErrorCode::ExecutorError);
+        plan.groups[g] = grp;
+        found = g++;
+      }
+      switchChannels_.push_back({ch.at("buffer_type").asString(), found});
+    }
+  }
+
+  uint64_t baseOf(const std::string& type) const {
+    if (type == "i") return l_.inOff;
+    if (type == "o") return l_.outOff;
+    if (type == "s") return l_.scratchOff;
+    throw Error("plan '" + p_.name + "': unknown buffer type '" + type + "'", ErrorCode::ExecutorError);
+  }
+
+  DevOperand operand(const json::Value& o, const json::Value& op) const {
+    const uint64_t units = l_.S / l_.A;
+    uint64_t start = calcOffset(units, o.at("index").asUInt(), l_.C, l_.A);
+    uint64_t end = calcOffset(units, o.at("index").asUInt() + o.at("size").asUInt(), l_.C, l_.A);
+    if (op.contains("tbg_info")) {
+      const uint64_t tb = op.at("tbg_info").at("tb_id").asUInt(), n = op.at("tbg_info").at("tbg_size").asUInt();
+      const uint64_t spanUnits = (end - start) / l_.A;
+      const uint64_t s2 = calcOffset(spanUnits, tb, n, l_.A), e2 = calcOffset(spanUnits, tb + 1, n, l_.A);
+      end = start + e2;
+      start = start + s2;
+    }
+    DevOperand d{};
+    d.size = end - start;
+    std::string type;
+    if (o.contains("buffer_id")) {
+      const std::string ctype = op.contains("channel_type") ? op.at("channel_type").asString() : "memory";
+      const json::Value& refs = tb_->at("remote_buffer_refs");
+      const json::Value* ids = nullptr;
+      for (size_t i = 0; i < refs.size(); i++)
+        if (refs.at(i).at("access_channel_type").asString() == ctype) ids = &refs.at(i).at("remote_buffer_ids");
+      if (ids == nullptr) throw Error("plan '" + p_.name + "': thread block has no remote buffers for " + ctype, ErrorCode::ExecutorError);
+      const json::Value& rb = gpu_->at("remote_buffers").at(ids->at(o.at("buffer_id").asUInt()).asUInt());
+      d.rank = static_cast<int16_t>(rb.at("rank").asInt());
+      type = rb.at("type").asString();
+    } else if (o.contains("switch_channel_id")) {
+      const json::Value& chans = tb_->at("channels");
+      const json::Value* ids = nullptr;
+      for (size_t i = 0; i < chans.size(); i++)
+        if (chans.at(i).at("channel_type").asString() == "switch") ids = &chans.at(i).at("channel_ids");
+      if (ids == nullptr) throw Error("plan '" + p_.name + "': thread block has no switch channels", ErrorCode::ExecutorError);
+      const size_t gpuLevel = ids->at(o.at("switch_channel_id").asUInt()).asUInt();
+      if (gpuLevel >= switchChannels_.size()) throw Error("plan '" + p_.name + "': switch channel index out of range", ErrorCode::ExecutorError);
+      d.rank = static_cast<int16_t>(rank_);
+      d.isSwitch = 1;
+      d.switchGroup = static_cast<uint16_t>(switchChannels_[gpuLevel].second);
+      type = switchChannels_[gpuLevel].first;
+    } else {
+      d.rank = static_cast<int16_t>(rank_);
+      type = o.at("type").asString();
+    }
+    d.isScratch = type == "s" ? 1 : 0;
+    d.offset = baseOf(type) + start;
+    return d;
+  }
+
+  void emitOps(const json::Value& ops, std::vector<DevOp>& out, bool inPipeline) {
+    for (size_t i = 0; i < ops.size(); i++) {
+      const json::Value& op = ops.at(i);
+      const std::string& name = op.at("name").asString();
+      if (name == "pipeline") {
+        if (inPipeline) throw Error("plan '" + p_.name + "': nested pipelines", ErrorCode::ExecutorError);
+        const uint64_t unit = op.at("iter_context").at("unit_size").asUInt();
+        const uint64_t chunks = op.at("iter_context").at("num_chunks").asUInt();
+        if (unit == 0) throw Error("plan '" + p_.name + "': pipeline with unit size 0", ErrorCode::ExecutorError);
+        DevOp begin{};
+        begin.type = static_cast<uint8_t>(OpType::PIPELINE_BEGIN);
+        begin.arg0 = static_cast<uint32_t>(std::max<uint64_t>(1, (chunks * l_.chunkUpper + unit - 1) / unit));
+        begin.arg1 = static_cast<uint32_t>(unit);
+        out.push_back(begin);
+        emitOps(op.at("ops"), out, true);
+        DevOp end{};
+        end.type = static_cast<uint8_t>(OpType::PIPELINE_END);
+        out.push_back(end);
+        continue;
+      }
+      auto it = opNames().find(name);
+      if (it == opNames().end()) throw Error("plan '" + p_.name + "': unknown op '" + name + "'", ErrorCode::ExecutorError);
+      DevOp d{};
+      d.type = static_cast<uint8_t>(it->second);
+      d.inPipeline = inPipeline ? 1 : 0;
+      const std::string ctype = op.contains("channel_type") ? op.at("channel_type").asString() : "";
+      d.channelType = ctype == "port" ? 1 : 0;
+      if (op.contains("src_buff")) {
+        const json::Value& src = op.at("src_buff");
+        if (src.size() > static_cast<size_t>(kExecMaxOperands)) throw Error("plan '" + p_.name + "': too many sources in one op", ErrorCode::ExecutorError);
+        d.nSrc = static_cast<uint8_t>(src.size());
+        for (size_t k = 0; k < src.size(); k++) d.src[k] = operand(src.at(k), op);
+      }
+      if (op.contains("dst_buff")) {
+        const json::Value& dst = op.at("dst_buff");
+        if (dst.size() > static_cast<size_t>(kExecMaxOperands)) throw Error("plan '" + p_.name + "': too many destinations in one op", ErrorCode::ExecutorError);
+        d.nDst = static_cast<uint8_t>(dst.size());
+        for (size_t k = 0; k < dst.size(); k++) d.dst[k] = operand(dst.at(k), op);
+      }
+      if (op.contains("channel_ids") && (ctype == "memory" || ctype == "port")) {
+        const json::Value& ids = op.at("channel_ids");
+        const json::Value& chans = tb_->at("channels");
+        const json::Value* table = nullptr;
+        for (size_t k = 0; k < chans.size(); k++)
+          if (chans.at(k).at("channel_type").asString() == ctype) table = &chans.at(k).at("channel_ids");
+        if (table == nullptr) throw Error("plan '" + p_.name + "': op uses " + ctype + " channels the thread block does not have", ErrorCode::ExecutorError);
+        if (ids.size() > static_cast<size_t>(kExecMaxIds)) throw Error("plan '" + p_.name + "': too many channels in one op", ErrorCode::ExecutorError);
+        d.nIds = static_cast<uint8_t>(ids.size());
+        for (size_t k = 0; k < ids.size(); k++) d.ids[k] = static_cast<uint16_t>(table->at(ids.at(k).asUInt()).asUInt());
+      }
+      if (op.contains("semaphore_ids")) {
+        const json::Value& ids = op.at("semaphore_ids");
+        d.nIds = static_cast<uint8_t>(ids.size());
+        for (size_t k = 0; k < ids.size(); k++) d.ids[k] = static_cast<uint16_t>(ids.at(k).asUInt());
+      }
+      if (it->second == OpType::BARRIER) {
+        d.arg0 = static_cast<uint32_t>(op.at("num_threadblocks").asUInt());
+        d.arg1 = static_cast<uint32_t>(op.at("barrier_id").asUInt());
+        if (d.arg1 >= static_cast<uint32_t>(kExecMaxBarriers)) throw Error("plan '" + p_.name + "': barrier id too large", ErrorCode::ExecutorError);
+      }
+      out.push_back(d);
+    }
+  }
+
+  const ExecutionPlan::Impl& p_;
+  int rank_;
+  Layout l_;
+  const json::Value* gpu_ = nullptr;
+  const json::Value* tb_ = nullptr;
+  json::Value emptyArray_ = [] {
+    json::Value v;
+    v.kind = json::Value::Kind::Array;
+    return v;
+  }();
+  std::vector<std::pair<std::string, int>> switchChannels_;
+};
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------ Executor
+struct Executor::Impl {
+  std::shared_ptr<SymmetricHeap> heap;
+  std::shared_ptr<Communicator> comm;
+
+  struct Context {
+    void* state = nullptr;      // ExecState in the heap
+    void* scratch = nullptr;    // heap
+    uint64_t scratchHalf = 0;
+    bool doubleScratch = false;
+    void* stageIn = nullptr;    // heap staging for user buffers outside the heap
+    void* stageOut = nullptr;
+    size_t stageInBytes = 0, stageOutBytes = 0;
+    uint64_t scratchBytesTotal = 0;
+    // device plans for the last message size
+    uint64_t S = 0;
+    uint64_t inOff = 0, outOff = 0;
+    std::vector<DevOp*> devOps;
+    std::vector<DevPlan*> devPlans;
+    int maxThreadBlocks = 0;
+  };
+  std::map<std::string, Context> contexts;
+
+  void freeDevPlans(Context& c) {
+    for (auto p : c.devOps) detail::gpuFree(p);
+    for (auto p : c.devPlans) detail::gpuFree(p);
+    c.devOps.clear();
+    c.devPlans.clear();
+  }
+
+  void freeContext(Context& c) {
+    freeDevPlans(c);
+    if (c.state) heap->free(c.state);
+    if (c.scratch) heap->free(c.scratch);
+    if (c.stageIn) heap->free(c.stageIn);
+    if (c.stageOut) heap->free(c.stageOut);
+    c = Context();
+  }
+};
+
+Executor::Executor(std::shared_ptr<SymmetricHeap> heap) : impl_(std::make_unique<Impl>()) { impl_->heap = std::move(heap); }
+
+Executor::Executor(std::shared_ptr<Communicator> comm, std::shared_ptr<char>) : impl_(std::make_unique<Impl>()) {
+  impl_->comm = comm;
+  SymmetricHeap::Options opt;
+  impl_->heap = SymmetricHeap::create(comm->bootstrap(), opt);
+}
+
+Executor::~Executor() {
+  try {
+    reset();
+  } catch (...) {
+  }
+}
+
+std::shared_ptr<SymmetricHeap> Executor::heap() const { return impl_->heap; }
+
+void Executor::reset() {
+  (void)cudaDeviceSynchronize();
+  for (auto& kv : impl_->contexts) impl_->freeContext(kv.second);
+  impl_->contexts.clear();
+}
+
+void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuffSize, size_t recvBuffSize, DataType dataType,
+                       const ExecutionPlan& plan, cudaStream_t stream, PacketType packetType) {
+  SymmetricHeap& heap = *impl_->heap;
+  const ExecutionPlan::Impl& p = *plan.impl_;
+  if (!heap.emulated() && rank != heap.rank()) throw Error("Executor::execute: rank does not match the heap", ErrorCode::InvalidUsage);
+  if (p.nRanks != heap.world()) throw Error("plan '" + p.name + "' is for " + std::to_string(p.nRanks) + " ranks, the heap has " + std::to_string(heap.world()), ErrorCode::ExecutorError);
+  if (packetType != PacketType::LL16) throw Error("this executor runs LL plans with LL16 packets only", ErrorCode::InvalidUsage);
+  const json::Value& g0 = p.root.at("gpus").at(0);
+  const uint64_t inChunks = g0.at("input_chunks").asUInt(), outChunks = g0.at("output_chunks").asUInt();
+  Layout layout;
+  layout.A = p.alignment;
+  if (inChunks != 0) {
+    layout.S = sendBuffSize;
+    layout.C = inChunks;
+  } else {
+    layout.S = recvBuffSize;
+    layout.C = outChunks;
+  }
+  if (layout.C == 0) throw Error("plan '" + p.name + "' has no chunks", ErrorCode::ExecutorError);
+  if (layout.S % layout.A != 0) throw Error("message size must be a multiple of the plan's buffer alignment", ErrorCode::ExecutorError);
+  if (layout.S < p.minSize || layout.S > p.maxSize) throw Error("message size outside the plan's range", ErrorCode::ExecutorError);
+  layout.chunkUpper = std::max<uint64_t>(calcOffset(layout.S / layout.A, 1, layout.C, layout.A), (layout.S + layout.C - 1) / layout.C);
+
+  Impl::Context& ctx = impl_->contexts[p.name];
+  AvoidCudaGraphCaptureGuard guard;
+  // ---- scratch sized for this message (collective: every rank takes the same decisions)
+  uint64_t maxScratchChunks = 0;
+  for (int r = 0; r < p.nRanks; r++) maxScratchChunks = std::max<uint64_t>(maxScratchChunks, p.root.at("gpus").at(r).at("scratch_chunks").asUInt());
+  uint64_t half = maxScratchChunks * layout.chunkUpper * (p.protocol == "LL" ? 2 : 1);
+  half = (half + 255) / 256 * 256;
+  const uint64_t total = half * (p.doubleScratch ? 2 : 1);
+  bool rebuild = ctx.devPlans.empty() || ctx.S != layout.S;
+  if (ctx.state == nullptr) {
+    ctx.state = heap.alloc(sizeof(ExecState), 256);
+    for (int r = 0; r < (heap.emulated() ? heap.world() : 1); r++)
+      MSCCLPP_CUDATHROW(cudaMemset(heap.emulated() ? heap.emulatedPtr(ctx.state, r) : ctx.state, 0, sizeof(ExecState)));
+    MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
+    if (heap.bootstrap()) heap.bootstrap()->barrier();  // nobody signals into a state block that is not zeroed yet
+    rebuild = true;
+  }
+  if (total > ctx.scratchBytesTotal) {
+    if (ctx.scratch) {
+      MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
+      heap.free(ctx.scratch);
+    }
+    ctx.scratch = total ? heap.alloc(total, 256) : nullptr;
+    if (ctx.scratch) {
+      for (int r = 0; r < (heap.emulated() ? heap.world() : 1); r++)
+        MSCCLPP_CUDATHROW(cudaMemset(heap.emulated() ? heap.emulatedPtr(ctx.scratch, r) : ctx.scratch, 0, total));
+      MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
+      if (heap.bootstrap()) heap.bootstrap()->barrier();
+    }
+    ctx.scratchBytesTotal = total;
+    rebuild = true;
+  }
+  if (ctx.scratchHalf != half || ctx.doubleScratch != p.doubleScratch) rebuild = true;
+  ctx.scratchHalf = half;
+  ctx.doubleScratch = p.doubleScratch;
+
+  // ---- buffers: in the heap -> in place; elsewhere -> staged
+  auto stage = [&](void* user, size_t bytes, void*& slot, size_t& slotBytes) -> void* {
+    if (user == nullptr || bytes == 0) return user;
+    if (heap.contains(user, bytes)) return user;
+    if (heap.emulated()) throw Error("emulated ranks need buffers from the heap", ErrorCode::InvalidUsage);
+    if (slotBytes < bytes) {
+      if (slot) {
+        MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
+        heap.free(slot);
+      }
+      slot = heap.alloc(bytes, 256);
+      slotBytes = bytes;
+      rebuild = true;
+    }
+    return slot;
+  };
+  void* in = stage(sendbuff, sendBuffSize, ctx.stageIn, ctx.stageInBytes);
+  void* out = p.inplace && recvbuff == sendbuff ? in : stage(recvbuff, recvBuffSize, ctx.stageOut, ctx.stageOutBytes);
+  if (in != sendbuff) MSCCLPP_CUDATHROW(cudaMemcpyAsync(in, sendbuff, sendBuffSize, cudaMemcpyDeviceToDevice, stream));
+  const uint64_t base = reinterpret_cast<uint64_t>(heap.localBase());
+  layout.inOff = in ? reinterpret_cast<uint64_t>(in) - base : 0;
+  layout.outOff = out ? reinterpret_cast<uint64_t>(out) - base : layout.inOff;
+  if (p.inplace && (in == nullptr || out == nullptr)) {
+    if (in == nullptr) layout.inOff = layout.outOff;
+    if (out == nullptr) layout.outOff = layout.inOff;
+  }
+  layout.scratchOff = ctx.scratch ? reinterpret_cast<uint64_t>(ctx.scratch) - base : 0;
+  if (ctx.inOff != layout.inOff || ctx.outOff != layout.outOff) rebuild = true;
+
+  // ---- device plans (cached per message size and buffer placement)
+  if (rebuild) {
+    MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
+    impl_->freeDevPlans(ctx);
+    const int nPlans = heap.emulated() ? heap.world() : 1;
+    ctx.maxThreadBlocks = 0;
+    for (int e = 0; e < nPlans; e++) {
+      const int r = heap.emulated() ? e : heap.rank();
+      Resolved res = Resolver(p, r, layout).run();
+      DevOp* dops = static_cast<DevOp*>(detail::gpuCalloc(std::max<size_t>(1, res.ops.size()) * sizeof(DevOp)));
+      if (!res.ops.empty()) gpuMemcpy(dops, res.ops.data(), res.ops.size() * sizeof(DevOp), cudaMemcpyHostToDevice);
+      res.plan.ops = dops;
+      DevPlan* dplan = static_cast<DevPlan*>(detail::gpuCalloc(sizeof(DevPlan)));
+      gpuMemcpy(dplan, &res.plan, sizeof(DevPlan), cudaMemcpyHostToDevice);
+      ctx.devOps.push_back(dops);
+      ctx.devPlans.push_back(dplan);
+      ctx.maxThreadBlocks = std::max<int>(ctx.maxThreadBlocks, static_cast<int>(res.plan.nThreadBlocks));
+    }
+    ctx.S = layout.S;
+    ctx.inOff = layout.inOff;
+    ctx.outOff = layout.outOff;
+  }
+
+  ExecArgs args{};
+  args.comm = heap.deviceComm();
+  for (size_t e = 0; e < ctx.devPlans.size(); e++) args.plans[e] = ctx.devPlans[e];
+  args.stateOff = reinterpret_cast<uint64_t>(ctx.state) - base;
+  args.scratchOff = layout.scratchOff;
+  args.scratchHalf = p.doubleScratch ? half : 0;
+  args.emuRanks = heap.emulated() ? heap.world() : 1;
+  if (ctx.maxThreadBlocks > 0) {
+    cudaError_t e = launchExecutionKernel(args, dataType, ctx.maxThreadBlocks, p.nThreadsPerBlock, stream);
+    if (e != cudaSuccess) throw CudaError("execution kernel launch failed for plan '" + p.name + "'", static_cast<int>(e));
+  }
+  if (out != recvbuff && recvbuff != nullptr) {
+    MSCCLPP_CUDATHROW(cudaMemcpyAsync(recvbuff, out, recvBuffSize, cudaMemcpyDeviceToDevice, stream));
+  }
+}
+
+}  // namespace mscclpp

@@ -1,0 +1,90 @@
+"""GPU plan interpreter against the numpy plan interpreter on identical plans and inputs.
+All ranks of a plan are emulated on one GPU in one cooperative launch."""
+import json
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+NP2TORCH = {np.float32: torch.float32, np.float16: torch.float16, np.int32: torch.int32}
+
+
+def _run_both(plan_json, world, in_elems, out_elems, np_dtype, inplace, launches=2):
+    from mscclpp_b200 import SymmetricMemory, native
+    from mscclpp_b200.language.interpreter import PlanInterpreter
+
+    n = native()
+    symm = SymmetricMemory.emulated(world, nbytes=128 << 20, timeout_ms=3000)
+    tdtype = NP2TORCH[np_dtype]
+    t_in = symm.tensor((in_elems,), tdtype)
+    t_out = t_in if inplace else symm.tensor((out_elems,), tdtype)
+    executor = n.Executor(symm.heap)
+    plans = [n.ExecutionPlan.from_string(plan_json, r) for r in range(world)]
+    interp = PlanInterpreter(plan_json)
+    dt = {np.float32: n.DataType.float32, np.float16: n.DataType.float16, np.int32: n.DataType.int32}[np_dtype]
+    for launch in range(launches):
+        rng = np.random.default_rng(100 + launch)
+        if np_dtype == np.int32:
+            ins = [rng.integers(-1000, 1000, size=in_elems).astype(np_dtype) for _ in range(world)]
+        else:
+            ins = [rng.uniform(-1, 1, size=in_elems).astype(np_dtype) for _ in range(world)]
+        outs = [np.zeros(out_elems, dtype=np_dtype) for _ in range(world)]
+        for r in range(world):
+            symm.rank_view(t_in, r).copy_(torch.from_numpy(ins[r]))
+            if not inplace:
+                symm.rank_view(t_out, r).zero_()
+        expect = interp.run([a.copy() for a in ins], None if inplace else outs)
+        executor.execute(0, t_in.data_ptr(), t_out.data_ptr(), in_elems * ins[0].itemsize, out_elems * ins[0].itemsize, dt,
+                         plans[0], torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        symm.check()
+        for r in range(world):
+            got = symm.rank_view(t_out, r).cpu().numpy()
+            if np_dtype == np.int32:
+                np.testing.assert_array_equal(got, expect[r])
+            else:
+                np.testing.assert_allclose(got.astype(np.float32), expect[r].astype(np.float32), rtol=2e-3, atol=2e-3)
+    executor.reset()
+    symm.destroy()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("algo", ["allreduce_allpairs", "allreduce_allpairs_packet", "allreduce_nvls"])
+@pytest.mark.parametrize("instances", [1, 2])
+def test_allreduce_plans(world, algo, instances):
+    from mscclpp_b200.default_algos import single_node
+
+    plan = single_node.build(algo, world, instances=instances).to_json()
+    elems = 4 * world * instances * 64
+    _run_both(plan, world, elems, elems, np.float32, inplace=True)
+    _run_both(plan, world, elems, elems, np.float16, inplace=True)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+def test_allgather_reducescatter_alltoall_plans(world):
+    from mscclpp_b200.default_algos import single_node
+
+    per = 256
+    _run_both(single_node.build("reducescatter_allpairs", world).to_json(), world, world * per, per, np.float32, inplace=False)
+    _run_both(single_node.build("alltoall_allpairs", world).to_json(), world, world * per, world * per, np.int32, inplace=False)
+    _run_both(single_node.build("allgather_allpairs", world, in_place=False).to_json(), world, per, world * per, np.int32, inplace=False)
+
+
+def test_malformed_plan_is_rejected():
+    from mscclpp_b200 import native
+    from mscclpp_b200.default_algos import single_node
+
+    n = native()
+    plan = json.loads(single_node.build("allreduce_allpairs", 2).to_json())
+    plan["gpus"][0]["threadblocks"][0]["ops"].append({"name": "frobnicate"})
+    from mscclpp_b200 import SymmetricMemory
+
+    symm = SymmetricMemory.emulated(2, nbytes=64 << 20, timeout_ms=1000)
+    t = symm.tensor((1024,), torch.float32, zero=True)
+    ex = n.Executor(symm.heap)
+    with pytest.raises(Exception):
+        ex.execute(0, t.data_ptr(), t.data_ptr(), 4096, 4096, n.DataType.float32, n.ExecutionPlan.from_string(json.dumps(plan), 0), 0)
+    ex.reset()
+    symm.destroy()
