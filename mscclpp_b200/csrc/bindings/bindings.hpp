@@ -4,3 +4,4 @@
 #include <pybind11/pybind11.h>
 
 void registerMoreBindings(pybind11::module_& m);
+void registerCoreBindings(pybind11::module_& m);

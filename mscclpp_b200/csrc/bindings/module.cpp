@@ -362,5 +362,6 @@ PYBIND11_MODULE(_native, m) {
       py::arg("a"), py::arg("b"), py::arg("d"), py::arg("m"), py::arg("n"), py::arg("k"), py::arg("ldd"),
       py::arg("block_n") = 256, py::arg("num_ctas") = 0, py::arg("status") = 0, py::arg("stream") = 0);
 
+  registerCoreBindings(m);
   registerMoreBindings(m);
 }
