@@ -97,7 +97,7 @@ def build(verbose: bool = True, jobs: int | None = None) -> dict[str, Path]:
     LIB.mkdir(exist_ok=True)
     BUILD.mkdir(exist_ok=True)
     hdr = _headers_digest()
-    core_srcs = _sources("core") + _sources("kernels") + _sources("executor")
+    core_srcs = _sources("core") + _sources("kernels") + _sources("executor") + _sources("ext")
     nccl_srcs = _sources("nccl")
     bind_srcs = _sources("bindings")
     py_inc = ["-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"]]

@@ -5,3 +5,4 @@
 
 void registerMoreBindings(pybind11::module_& m);
 void registerCoreBindings(pybind11::module_& m);
+void registerAlgorithmBindings(pybind11::module_& m);

@@ -363,5 +363,6 @@ PYBIND11_MODULE(_native, m) {
       py::arg("block_n") = 256, py::arg("num_ctas") = 0, py::arg("status") = 0, py::arg("stream") = 0);
 
   registerCoreBindings(m);
+  registerAlgorithmBindings(m);
   registerMoreBindings(m);
 }

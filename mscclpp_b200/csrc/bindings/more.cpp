@@ -31,7 +31,7 @@ void registerMoreBindings(py::module_& m) {
       .def_property_readonly("max_message_size", &ExecutionPlan::maxMessageSize)
       .def_property_readonly("is_in_place", &ExecutionPlan::isInPlace)
       .def_property_readonly("n_ranks", &ExecutionPlan::nRanks);
-  py::class_<Executor>(m, "Executor")
+  py::class_<Executor, std::shared_ptr<Executor>>(m, "Executor")
       .def(py::init<std::shared_ptr<SymmetricHeap>>(), py::arg("heap"))
       .def(
           "execute",

@@ -12,6 +12,7 @@
 
 #include <mscclpp/env.hpp>
 #include <mscclpp/gpu_utils.hpp>
+#include <mscclpp/npkit/npkit.hpp>
 
 #include "context.hpp"
 #include "logger.hpp"
@@ -363,13 +364,34 @@ Connection Context::connect(const Endpoint& localEndpoint, const Endpoint& remot
 
 // ------------------------------------------------------------------------------------------ Connection facade
 Connection::Connection(std::shared_ptr<BaseConnection> impl) : impl_(std::move(impl)) {}
+namespace {
+// Host-side trace events around a connection call; channel 0 collects them (one proxy thread drives them).
+struct TraceScope {
+  TraceScope(Transport t, int cudaEntry, int ethEntry, uint32_t size)
+      : on_(NpKit::Enabled()), type_(t == Transport::Ethernet ? ethEntry : cudaEntry), size_(size) {
+    if (on_) NpKit::CollectCpuEvent(static_cast<uint8_t>(type_), size_, 0, NpKit::GetCpuTimestamp(), 0);
+  }
+  ~TraceScope() {
+    if (on_) NpKit::CollectCpuEvent(static_cast<uint8_t>(type_ + 1), size_, 0, NpKit::GetCpuTimestamp(), 0);
+  }
+  bool on_;
+  int type_;
+  uint32_t size_;
+};
+}  // namespace
+
 void Connection::write(RegisteredMemory dst, uint64_t dstOffset, RegisteredMemory src, uint64_t srcOffset, uint64_t size) {
+  TraceScope trace(impl_->transport(), NPKIT_EVENT_CONN_CUDA_IPC_WRITE_ENTRY, NPKIT_EVENT_CONN_ETH_WRITE_ENTRY, static_cast<uint32_t>(size));
   impl_->write(dst, dstOffset, src, srcOffset, size);
 }
 void Connection::updateAndSync(RegisteredMemory dst, uint64_t dstOffset, uint64_t* src, uint64_t newValue) {
+  TraceScope trace(impl_->transport(), NPKIT_EVENT_CONN_CUDA_IPC_UPDATE_AND_SYNC_ENTRY, NPKIT_EVENT_CONN_ETH_UPDATE_AND_SYNC_ENTRY, 8);
   impl_->updateAndSync(dst, dstOffset, src, newValue);
 }
-void Connection::flush(int64_t timeoutUsec) { impl_->flush(timeoutUsec); }
+void Connection::flush(int64_t timeoutUsec) {
+  TraceScope trace(impl_->transport(), NPKIT_EVENT_CONN_CUDA_IPC_FLUSH_ENTRY, NPKIT_EVENT_CONN_ETH_FLUSH_ENTRY, 0);
+  impl_->flush(timeoutUsec);
+}
 Transport Connection::transport() const { return impl_->transport(); }
 Transport Connection::remoteTransport() const { return impl_->remoteTransport(); }
 std::shared_ptr<Context> Connection::context() const { return impl_->context(); }

@@ -37,6 +37,12 @@ struct CudaDriver {
   CUresult (*cuDeviceGetAttribute)(int*, CUdevice_attribute, CUdevice);
   CUresult (*cuPointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr);
   CUresult (*cuGetErrorString)(CUresult, const char**);
+  CUresult (*cuModuleLoadData)(CUmodule*, const void*);
+  CUresult (*cuModuleUnload)(CUmodule);
+  CUresult (*cuModuleGetFunction)(CUfunction*, CUmodule, const char*);
+  CUresult (*cuFuncSetAttribute)(CUfunction, CUfunction_attribute, int);
+  CUresult (*cuLaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**);
+  CUresult (*cuLaunchCooperativeKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**);
 };
 
 }  // namespace mscclpp

@@ -53,6 +53,12 @@ CudaDriver* loadDriver() {
   MSCCLPP_RESOLVE(cuDeviceGetAttribute);
   MSCCLPP_RESOLVE(cuPointerGetAttribute);
   MSCCLPP_RESOLVE(cuGetErrorString);
+  MSCCLPP_RESOLVE(cuModuleLoadData);
+  MSCCLPP_RESOLVE(cuModuleUnload);
+  MSCCLPP_RESOLVE(cuModuleGetFunction);
+  MSCCLPP_RESOLVE(cuFuncSetAttribute);
+  MSCCLPP_RESOLVE(cuLaunchKernel);
+  MSCCLPP_RESOLVE(cuLaunchCooperativeKernel);
 #undef MSCCLPP_RESOLVE
   return ok ? &table : nullptr;
 }

@@ -6,6 +6,8 @@
 
 #include <mscclpp/device/symm.cuh>
 
+#include <mscclpp/npkit/npkit_struct.hpp>
+
 namespace mscclpp {
 
 enum class OpType : uint8_t {
@@ -121,6 +123,7 @@ struct ExecArgs {
   uint64_t scratchOff;   // heap offset of the scratch buffer (first half when double buffered)
   uint64_t scratchHalf;  // bytes of one scratch half (0 = no double buffering)
   int emuRanks;
+  NpKitEventCollectContext* npkit;  // tracer buffers, nullptr = tracing off
 };
 
 }  // namespace mscclpp

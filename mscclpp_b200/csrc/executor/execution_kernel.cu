@@ -11,6 +11,7 @@
 #include "execution_kernel.hpp"
 
 #include <mscclpp/copy_device.hpp>
+#include <mscclpp/npkit/npkit.hpp>
 #include <mscclpp/packet_device.hpp>
 
 namespace mscclpp {
@@ -386,6 +387,22 @@ MSCCLPP_DEVICE_INLINE void execOp(Ctx& x, const DevOp& op) {
   }
 }
 
+// One operation with its entry/exit trace events (thread 0; the cost is one predictable branch when tracing is off).
+template <typename T>
+MSCCLPP_DEVICE_INLINE void tracedOp(Ctx& x, const DevOp& op) {
+  NpKitEventCollectContext* trace = x.a->npkit;
+  if (trace != nullptr && threadIdx.x == 0)
+    npkitCollectGpuEvent(trace, NPKIT_EVENT_EXECUTOR_OP_BASE_ENTRY + op.type, static_cast<uint32_t>(op.nSrc ? op.src[0].size : 0), x.rank);
+  execOp<T>(x, op);
+  if (trace != nullptr) {
+    // the exit stamp is taken when the whole block is done with the operation; the vote also keeps the
+    // health flag uniform, so that every thread leaves the operation loop at the same place
+    x.healthy = __syncthreads_and(x.healthy ? 1 : 0) != 0;
+    if (threadIdx.x == 0)
+      npkitCollectGpuEvent(trace, NPKIT_EVENT_EXECUTOR_OP_BASE_EXIT + op.type, static_cast<uint32_t>(op.nSrc ? op.src[0].size : 0), x.rank);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(1024, 1) executionKernel(ExecArgs a) {
   const DeviceComm& c = a.comm;
@@ -427,14 +444,14 @@ __global__ void __launch_bounds__(1024, 1) executionKernel(ExecArgs a) {
         x.pipeUnit = op.arg1;
         for (uint32_t it = 0; it < op.arg0 && x.healthy; it++) {
           x.pipeOff = static_cast<uint64_t>(it) * op.arg1;
-          for (uint32_t k = i + 1; k < end && x.healthy; k++) execOp<T>(x, ops[k]);
+          for (uint32_t k = i + 1; k < end && x.healthy; k++) tracedOp<T>(x, ops[k]);
         }
         x.pipeUnit = 0;
         x.pipeOff = 0;
         i = end + 1;
         continue;
       }
-      execOp<T>(x, op);
+      tracedOp<T>(x, op);
       i++;
     }
   }

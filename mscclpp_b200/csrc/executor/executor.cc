@@ -2,12 +2,14 @@
 // interpreter kernel launch). Chunk-to-byte arithmetic follows the plan format's rules
 // (reference: src/core/executor/execution_plan.cc:191-216, 478-668; src/core/executor/executor.cc:158-563).
 #include <mscclpp/executor.hpp>
+#include <mscclpp/npkit/npkit.hpp>
 
 #include <algorithm>
 #include <cstring>
 #include <map>
 #include <unordered_map>
 
+#include <mscclpp/env.hpp>
 #include <mscclpp/gpu_utils.hpp>
 
 #include "../core/json.hpp"
@@ -404,16 +406,32 @@ struct Executor::Impl {
   }
 };
 
-Executor::Executor(std::shared_ptr<SymmetricHeap> heap) : impl_(std::make_unique<Impl>()) { impl_->heap = std::move(heap); }
+namespace {
+// MSCCLPP_NPKIT_DUMP_DIR switches the tracer on for the life time of the executor, like in the reference
+// (src/core/executor/executor.cc: the constructor calls NpKit::Init, the destructor NpKit::Dump).
+void startTracing(SymmetricHeap& heap) {
+  if (!env()->npkitDumpDir.empty() && !NpKit::Enabled()) NpKit::Init(heap.rank());
+}
+}  // namespace
+
+Executor::Executor(std::shared_ptr<SymmetricHeap> heap) : impl_(std::make_unique<Impl>()) {
+  impl_->heap = std::move(heap);
+  startTracing(*impl_->heap);
+}
 
 Executor::Executor(std::shared_ptr<Communicator> comm, std::shared_ptr<char>) : impl_(std::make_unique<Impl>()) {
   impl_->comm = comm;
   SymmetricHeap::Options opt;
   impl_->heap = SymmetricHeap::create(comm->bootstrap(), opt);
+  startTracing(*impl_->heap);
 }
 
 Executor::~Executor() {
   try {
+    if (!env()->npkitDumpDir.empty() && NpKit::Enabled()) {
+      NpKit::Dump(env()->npkitDumpDir);
+      NpKit::Shutdown();
+    }
     reset();
   } catch (...) {
   }
@@ -545,6 +563,7 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
   args.scratchOff = layout.scratchOff;
   args.scratchHalf = p.doubleScratch ? half : 0;
   args.emuRanks = heap.emulated() ? heap.world() : 1;
+  args.npkit = NpKit::GetGpuEventCollectContexts();
   if (ctx.maxThreadBlocks > 0) {
     cudaError_t e = launchExecutionKernel(args, dataType, ctx.maxThreadBlocks, p.nThreadsPerBlock, stream);
     if (e != cudaSuccess) throw CudaError("execution kernel launch failed for plan '" + p.name + "'", static_cast<int>(e));

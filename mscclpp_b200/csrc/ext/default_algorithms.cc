@@ -1,0 +1,239 @@
+// Default native algorithms on a symmetric heap, registered under the reference's names
+// (src/ext/collectives/algorithm_collection_builder.cc:64-104), and the B200 selector.
+//
+// How the names map onto this library's kernels:
+//   default_allreduce_allpair_packet / _packet      one-shot LL16 over peer stores (any local buffers)
+//   default_allreduce_nvls_packet                   one-shot LL16, one multimem.st per packet
+//   default_allreduce_nvls_zero_copy                two-shot multimem.ld_reduce + multimem.st (heap buffers)
+//   default_allreduce_rsag_zero_copy                two-shot peer loads + stores (heap buffers)
+//   default_allreduce_nvls_warp_pipeline / _nvls_block_pipeline / _rsag / _rsag_pipeline / _fullmesh
+//                                                   the same two-shot kernels through heap staging buffers, for
+//                                                   user buffers outside the heap (copy in, reduce, copy out on the
+//                                                   caller's stream)
+//   default_allgather_fullmesh / _fullmesh2, default_reducescatter_zero_copy     two-shot kernel in AG / RS mode
+#include <mscclpp/ext/collectives/algorithm_collection_builder.hpp>
+
+#include <algorithm>
+#include <cstdlib>
+#include <dirent.h>
+#include <mutex>
+
+#include <mscclpp/env.hpp>
+#include <mscclpp/gpu_utils.hpp>
+
+#include "../core/logger.hpp"
+#include "../kernels/collectives.cuh"
+
+namespace mscclpp {
+namespace collective {
+
+namespace {
+
+struct Staging {
+  std::shared_ptr<SymmetricHeap> heap;
+  void* in = nullptr;
+  void* out = nullptr;
+  size_t inBytes = 0, outBytes = 0;
+  void* ensure(void*& slot, size_t& have, size_t bytes) {
+    if (have >= bytes) return slot;
+    AvoidCudaGraphCaptureGuard guard;
+    if (slot) {
+      (void)cudaDeviceSynchronize();
+      heap->free(slot);
+    }
+    size_t rounded = 256;
+    while (rounded < bytes) rounded <<= 1;  // every rank rounds the same way -> symmetric offsets
+    slot = heap->alloc(rounded, 256);
+    have = rounded;
+    return slot;
+  }
+};
+
+CommResult toResult(cudaError_t e) { return e == cudaSuccess ? CommResult::Success : (e == cudaErrorInvalidValue ? CommResult::InvalidArgument : CommResult::UnhandledCudaError); }
+
+CollArgs baseArgs(SymmetricHeap& heap, const void* in, void* out, size_t bytes, int mode, bool nvls) {
+  CollArgs a{};
+  a.comm = heap.deviceComm();
+  a.in = in;
+  a.out = out;
+  a.bytes = bytes;
+  a.emuRanks = 1;
+  a.mode = mode;
+  a.nvls = nvls ? 1 : 0;
+  return a;
+}
+
+void gridFor(size_t bytes, bool nvls, int& blocks, int& threads) {
+  threads = 512;
+  if (nvls) blocks = bytes < (8u << 20) ? 16 : (bytes < (64u << 20) ? 32 : 64);
+  else blocks = bytes < (8u << 20) ? 32 : (bytes < (64u << 20) ? 64 : 128);
+}
+
+std::shared_ptr<Algorithm> makeLL(const std::string& name, std::shared_ptr<SymmetricHeap> heap, bool nvls) {
+  const size_t cap = heap->deviceComm().llSlotBytes / 2;
+  return std::make_shared<NativeAlgorithm>(
+      name, "allreduce", nullptr,
+      [heap, nvls](const void* in, void* out, size_t inBytes, size_t, DataType dtype, ReduceOp op, cudaStream_t stream, int nBlocks,
+                   int nThreads, bool, const std::unordered_map<std::string, uintptr_t>&) {
+        CollArgs a = baseArgs(*heap, in, out, inBytes, kAllReduce, nvls);
+        const size_t units = (inBytes + 15) / 16;
+        if (nThreads <= 0) nThreads = 512;
+        if (nBlocks <= 0) nBlocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(56, (units + nThreads - 1) / nThreads)));
+        return toResult(launchAllreduceLL(a, dtype, op, nBlocks, nThreads, stream));
+      },
+      0, cap, CollectiveBufferMode::Any);
+}
+
+std::shared_ptr<Algorithm> makeTwoShot(const std::string& name, const std::string& collective, std::shared_ptr<SymmetricHeap> heap,
+                                       int mode, bool nvls, bool staged, std::shared_ptr<Staging> staging) {
+  return std::make_shared<NativeAlgorithm>(
+      name, collective, nullptr,
+      [heap, mode, nvls, staged, staging](const void* in, void* out, size_t inBytes, size_t outBytes, DataType dtype, ReduceOp op,
+                                          cudaStream_t stream, int nBlocks, int nThreads, bool,
+                                          const std::unordered_map<std::string, uintptr_t>&) {
+        const size_t big = std::max(inBytes, outBytes);
+        if (nBlocks <= 0 || nThreads <= 0) gridFor(big, nvls, nBlocks, nThreads);
+        const void* kin = in;
+        void* kout = out;
+        // Peers read `in` (allreduce, reducescatter) and write `out` (allreduce, allgather): only those sides
+        // must live in the heap. An allreduce whose size is not a multiple of 16 bytes is padded in staging.
+        const bool padded = mode == kAllReduce && inBytes % 16 != 0;
+        const bool needIn = mode != kAllGather && (padded || !heap->contains(in, inBytes));
+        const bool needOut = mode != kReduceScatter && (padded || !heap->contains(out, outBytes));
+        if (needIn || needOut) {
+          if (!staged) return CommResult::InvalidUsage;
+          if (needIn) {
+            kin = staging->ensure(staging->in, staging->inBytes, inBytes);
+            if (cudaMemcpyAsync(const_cast<void*>(kin), in, inBytes, cudaMemcpyDeviceToDevice, stream) != cudaSuccess) return CommResult::UnhandledCudaError;
+          }
+          if (needOut) kout = (mode == kAllReduce && needIn) ? const_cast<void*>(kin) : staging->ensure(staging->out, staging->outBytes, outBytes);
+        }
+        if (padded) inBytes = (inBytes + 15) / 16 * 16;
+        CollArgs a = baseArgs(*heap, kin, kout, mode == kAllGather ? outBytes : inBytes, mode, nvls);
+        cudaError_t e = launchTwoShot(a, dtype, op, nBlocks, nThreads, stream);
+        if (e != cudaSuccess) return toResult(e);
+        if (kout != out && cudaMemcpyAsync(out, kout, outBytes, cudaMemcpyDeviceToDevice, stream) != cudaSuccess) return CommResult::UnhandledCudaError;
+        return CommResult::Success;
+      },
+      0, UINT64_MAX, CollectiveBufferMode::Any);
+}
+
+}  // namespace
+
+std::shared_ptr<AlgorithmCollectionBuilder> AlgorithmCollectionBuilder::getInstance() {
+  static std::shared_ptr<AlgorithmCollectionBuilder> instance;
+  static std::mutex mutex;
+  std::lock_guard<std::mutex> lock(mutex);
+  if (!instance) instance = std::shared_ptr<AlgorithmCollectionBuilder>(new AlgorithmCollectionBuilder());
+  return instance;
+}
+
+void AlgorithmCollectionBuilder::reset() {
+  auto self = getInstance();
+  self->builders_.clear();
+  self->selector_ = nullptr;
+  self->fallbackSelector_ = nullptr;
+}
+
+void AlgorithmCollectionBuilder::addAlgorithmBuilder(std::shared_ptr<AlgorithmBuilder> builder) { builders_.push_back(std::move(builder)); }
+void AlgorithmCollectionBuilder::setAlgorithmSelector(AlgoSelectFunc selector) { selector_ = std::move(selector); }
+void AlgorithmCollectionBuilder::setFallbackAlgorithmSelector(AlgoSelectFunc selector) { fallbackSelector_ = std::move(selector); }
+
+AlgorithmCollection AlgorithmCollectionBuilder::build() {
+  AlgorithmCollection c;
+  for (auto& b : builders_) {
+    auto algo = b->build();
+    c.registerAlgorithm(algo->collective(), algo->name(), algo);
+  }
+  c.setSelectors(selector_, fallbackSelector_ ? fallbackSelector_ : selectDefaultAlgorithm);
+  return c;
+}
+
+AlgorithmCollection AlgorithmCollectionBuilder::buildDefaultAlgorithms(std::shared_ptr<SymmetricHeap> heap) {
+  AlgorithmCollection c = build();
+  const bool nvls = heap->nvls();
+  auto staging = std::make_shared<Staging>();
+  staging->heap = heap;
+  auto add = [&c](std::shared_ptr<Algorithm> a) { c.registerAlgorithm(a->collective(), a->name(), a); };
+  add(makeLL("default_allreduce_allpair_packet", heap, false));
+  add(makeLL("default_allreduce_packet", heap, false));
+  if (nvls) add(makeLL("default_allreduce_nvls_packet", heap, true));
+  if (nvls) add(makeTwoShot("default_allreduce_nvls_zero_copy", "allreduce", heap, kAllReduce, true, false, staging));
+  add(makeTwoShot("default_allreduce_rsag_zero_copy", "allreduce", heap, kAllReduce, false, false, staging));
+  if (nvls) {
+    add(makeTwoShot("default_allreduce_nvls_warp_pipeline", "allreduce", heap, kAllReduce, true, true, staging));
+    add(makeTwoShot("default_allreduce_nvls_block_pipeline", "allreduce", heap, kAllReduce, true, true, staging));
+  }
+  add(makeTwoShot("default_allreduce_rsag", "allreduce", heap, kAllReduce, false, true, staging));
+  add(makeTwoShot("default_allreduce_rsag_pipeline", "allreduce", heap, kAllReduce, false, true, staging));
+  add(makeTwoShot("default_allreduce_fullmesh", "allreduce", heap, kAllReduce, false, true, staging));
+  add(makeTwoShot("default_allgather_fullmesh", "allgather", heap, kAllGather, false, true, staging));
+  add(makeTwoShot("default_allgather_fullmesh2", "allgather", heap, kAllGather, nvls, true, staging));
+  add(makeTwoShot("default_reducescatter_zero_copy", "reducescatter", heap, kReduceScatter, nvls, true, staging));
+
+  // DSL plans installed under <cache>/default/*.json
+  const std::string dir = env()->cacheDir + "/default";
+  if (DIR* d = opendir(dir.c_str())) {
+    while (dirent* ent = readdir(d)) {
+      std::string file = ent->d_name;
+      if (file.size() < 6 || file.substr(file.size() - 5) != ".json") continue;
+      try {
+        ExecutionPlan plan(dir + "/" + file, heap->rank());
+        if (plan.nRanks() != heap->world()) continue;
+        auto algo = std::make_shared<DslAlgorithm>(file.substr(0, file.size() - 5), plan);
+        c.registerAlgorithm(algo->collective(), algo->name(), algo);
+      } catch (const BaseError& e) {
+        LOG_WARN(LogSubsys::ALGO, "skipping plan ", file, ": ", e.what());
+      }
+    }
+    closedir(d);
+  }
+  return c;
+}
+
+std::shared_ptr<Algorithm> selectDefaultAlgorithm(
+    const std::unordered_map<std::string, std::unordered_map<std::string, std::shared_ptr<Algorithm>>>& algoMapByCollective,
+    const CollectiveRequest& request) {
+  auto it = algoMapByCollective.find(request.collective);
+  if (it == algoMapByCollective.end()) return nullptr;
+  const auto& algos = it->second;
+  auto get = [&](const char* name) -> std::shared_ptr<Algorithm> {
+    auto a = algos.find(name);
+    return a == algos.end() ? nullptr : a->second;
+  };
+  // DSL plans that match the size and buffer mode take precedence, like in the reference
+  for (auto& kv : algos) {
+    if (kv.second->type() != AlgorithmType::DSL) continue;
+    auto range = kv.second->messageRange();
+    const bool modeOk = kv.second->bufferMode() == CollectiveBufferMode::Any || kv.second->bufferMode() == request.bufferMode();
+    if (request.messageSize >= range.first && request.messageSize <= range.second && modeOk) return kv.second;
+  }
+  const size_t n = request.messageSize;
+  if (request.collective == "allreduce") {
+    auto pkt = get("default_allreduce_packet");
+    auto nvlsPkt = get("default_allreduce_nvls_packet");
+    const size_t llCap = pkt ? pkt->messageRange().second : 0;
+    if (n <= (64u << 10) && nvlsPkt) return nvlsPkt;                 // one multimem.st per packet: flat ~latency floor
+    // user buffers outside the heap cost two extra copies on the two-shot path, so packets stay ahead for longer
+    const size_t pktMax = request.symmetricMemory ? (512u << 10) : (1u << 20);
+    if (n <= pktMax && n <= llCap && pkt) return pkt;
+    if (request.symmetricMemory && n % 16 == 0) {
+      if (auto a = get("default_allreduce_nvls_zero_copy")) return a;
+      return get("default_allreduce_rsag_zero_copy");
+    }
+    if (auto a = get(n >= (16u << 20) ? "default_allreduce_nvls_block_pipeline" : "default_allreduce_nvls_warp_pipeline")) return a;
+    return get(n >= (8u << 20) ? "default_allreduce_rsag_pipeline" : "default_allreduce_rsag");
+  }
+  if (request.collective == "allgather") {
+    if ((n * request.worldSize) % (16 * static_cast<size_t>(request.worldSize)) != 0) return nullptr;
+    return get("default_allgather_fullmesh2");
+  }
+  if (request.collective == "reducescatter") {
+    if (n % (16 * static_cast<size_t>(request.worldSize)) != 0) return nullptr;
+    return get("default_reducescatter_zero_copy");
+  }
+  return nullptr;
+}
+
+}  // namespace collective
+}  // namespace mscclpp

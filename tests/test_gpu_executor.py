@@ -1,6 +1,7 @@
 """GPU plan interpreter against the numpy plan interpreter on identical plans and inputs.
 All ranks of a plan are emulated on one GPU in one cooperative launch."""
 import json
+import os
 
 import numpy as np
 import pytest
@@ -87,4 +88,41 @@ def test_malformed_plan_is_rejected():
     with pytest.raises(Exception):
         ex.execute(0, t.data_ptr(), t.data_ptr(), 4096, 4096, n.DataType.float32, n.ExecutionPlan.from_string(json.dumps(plan), 0), 0)
     ex.reset()
+    symm.destroy()
+
+
+def test_tracer_records_executor_operations(tmp_path):
+    """With the tracer on, every thread block of a plan leaves ENTRY/EXIT pairs that convert to a Chrome trace."""
+    from mscclpp_b200 import SymmetricMemory, native
+    from mscclpp_b200.default_algos import single_node
+    from mscclpp_b200.utils.npkit_trace import convert_npkit_dump_to_trace
+
+    n = native()
+    world = 2
+    plan_json = single_node.build("allreduce_allpairs", world).to_json()
+    symm = SymmetricMemory.emulated(world, nbytes=64 << 20, timeout_ms=3000)
+    t = symm.tensor((4096,), torch.float32)
+    for r in range(world):
+        symm.rank_view(t, r).fill_(r + 1.0)
+    n.npkit.init(0)
+    try:
+        assert n.npkit.enabled()
+        executor = n.Executor(symm.heap)
+        plan = n.ExecutionPlan.from_string(plan_json, 0)
+        executor.execute(0, t.data_ptr(), t.data_ptr(), t.numel() * 4, t.numel() * 4, n.DataType.float32, plan,
+                         torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        symm.check()
+        assert bool((symm.rank_view(t, 1) == 3.0).all().item())
+        n.npkit.dump(str(tmp_path))
+    finally:
+        n.npkit.shutdown()
+    assert not n.npkit.enabled()
+    files = sorted(os.listdir(tmp_path))
+    assert any(f.startswith("gpu_events_rank_0_buf_") for f in files) and "gpu_time_sync_rank_0" in files
+    trace = json.loads(open(convert_npkit_dump_to_trace(str(tmp_path), str(tmp_path / "out"))).read())["traceEvents"]
+    slices = [e for e in trace if e["ph"] == "X"]
+    assert slices and all(e["dur"] >= 0 for e in slices)
+    assert {"EXECUTOR_OP_SIGNAL", "EXECUTOR_OP_WAIT"} & {e["name"] for e in slices} or any("EXECUTOR_OP" in e["name"] for e in slices)
+    executor.reset()
     symm.destroy()

@@ -1,0 +1,181 @@
+"""CPU-only checks of the Python surface: algorithm registry and selectors, the DSL compiler cache, the
+kernel builder, `pack`, the package exports and the host-only calls of the NCCL shim."""
+import ctypes
+import os
+import struct
+
+import numpy as np
+import pytest
+
+import mscclpp_b200 as mp
+from mscclpp_b200._core import native
+from mscclpp_b200.default_algos import allreduce_allpairs, make_spec
+from mscclpp_b200.language.collectives import AllReduce
+
+N = native.load()
+
+
+def test_reference_names_are_exported():
+    for name in ("Communicator", "TcpBootstrap", "Transport", "MemoryChannel", "PortChannel", "ProxyService", "Executor",
+                 "ExecutionPlan", "DataType", "ReduceOp", "PacketType", "RawGpuBuffer", "env", "is_nvls_supported", "Algorithm",
+                 "AlgorithmCollection", "CommGroup", "GpuBuffer", "compile", "compile_native", "get_include", "get_lib", "npkit"):
+        assert hasattr(mp, name), name
+    assert os.path.isdir(mp.get_include()) and os.path.exists(os.path.join(mp.get_include(), "mscclpp", "core.hpp"))
+    assert os.path.isdir(mp.get_lib())
+
+
+def test_python_native_algorithm_roundtrip():
+    calls = []
+
+    def kernel(inp, out, in_bytes, out_bytes, dtype, op, stream, n_blocks, n_threads, symmetric, extras):
+        calls.append((inp, out, in_bytes, out_bytes, dtype, op, n_blocks, n_threads, symmetric, dict(extras)))
+        return 0
+
+    inits = []
+    algo = mp.Algorithm.from_callable("my_allreduce", "allreduce", kernel, init=lambda comm: inits.append(comm),
+                                      min_message_size=16, max_message_size=1 << 20, tags={"fast": 1})
+    assert algo.name == "my_allreduce" and algo.collective == "allreduce"
+    assert algo.message_size_range == (16, 1 << 20)
+    assert algo.tags == {"fast": 1}
+    assert algo.is_native_algorithm() and not algo.is_dsl_algorithm()
+    rc = algo.execute(None, 0x1000, 0x2000, 64, 64, N.DataType.float16, N.ReduceOp.SUM, nblocks=3, nthreads_per_block=128,
+                      symmetric_memory=True, extras={"k": 7})
+    rc2 = algo.execute(None, 0x1000, 0x2000, 64, 64, N.DataType.float16, N.ReduceOp.SUM)
+    assert rc == 0 and rc2 == 0
+    assert len(inits) == 1, "init runs once"
+    assert calls[0][:4] == (0x1000, 0x2000, 64, 64) and calls[0][6:] == (3, 128, True, {"k": 7})
+    algo.set_message_size_range(0, 99)
+    assert algo.message_size_range == (0, 99)
+    # capsule round trip (the exchange format with separately compiled modules)
+    again = mp.Algorithm.create_from_native_capsule(algo._algorithm.to_native_capsule())
+    assert again.name == "my_allreduce"
+
+
+def test_collection_and_selectors():
+    from mscclpp_b200.ext import AlgorithmCollectionBuilder
+
+    AlgorithmCollectionBuilder.reset()
+    builder = AlgorithmCollectionBuilder()
+    small = mp.Algorithm.from_callable("small", "allreduce", lambda *a: 0, max_message_size=1024)
+    large = mp.Algorithm.from_callable("large", "allreduce", lambda *a: 0, min_message_size=1025)
+    builder.add_algorithm_builder(small)
+    builder.add_algorithm_builder(large)
+    seen = []
+
+    def selector(algo_map, request):
+        seen.append((request.collective, request.message_size))
+        for algo in algo_map.get(request.collective, {}).values():
+            lo, hi = algo.message_range
+            if lo <= request.message_size <= hi:
+                return algo
+        return None
+
+    builder.set_algorithm_selector(selector)
+    coll = builder.build()
+    assert len(coll) == 2 and {a.name for a in coll.get_by_collective("allreduce")} == {"small", "large"}
+    req = N.CollectiveRequest()
+    req.collective = "allreduce"
+    req.message_size = 512
+    assert coll.select(req).name == "small"
+    req.message_size = 4096
+    assert coll.select(req).name == "large"
+    req.collective = "allgather"
+    assert coll.select(req) is None  # the default fallback selector finds nothing either
+    assert seen[0] == ("allreduce", 512)
+    coll.register_algorithm("allgather", "ag", mp.Algorithm.from_callable("ag", "allgather", lambda *a: 0))
+    assert len(coll) == 3
+    AlgorithmCollectionBuilder.reset()
+
+
+def test_dsl_compile_caches_plan(tmp_path, monkeypatch):
+    monkeypatch.setenv("MSCCLPP_CACHE_DIR", str(tmp_path))
+    spec = make_spec("cached_allreduce", AllReduce(4, 1, True), 4, tags={"t": 1})
+    compiler = mp.DslCompiler()
+    # the native Env singleton may have latched another cache dir: go through plan_path, which reports where it wrote
+    path = compiler.plan_path(allreduce_allpairs, spec)
+    assert path.exists()
+    mtime = path.stat().st_mtime_ns
+    assert compiler.plan_path(allreduce_allpairs, spec) == path and path.stat().st_mtime_ns == mtime, "second call hits the cache"
+    other = compiler.plan_path(allreduce_allpairs, make_spec("cached_allreduce", AllReduce(4, 1, True), 4, instances=2))
+    assert other != path
+    algo = mp.compile(allreduce_allpairs, spec, rank=1)
+    assert algo.is_dsl_algorithm() and algo.collective == "allreduce" and algo.name == "cached_allreduce"
+    assert algo.tags == {"t": 1}
+
+
+def test_pack_layout():
+    from mscclpp_b200.utils import pack
+
+    a = np.zeros(4, dtype=np.float32)
+    blob = pack(a, 7, ctypes.c_size_t(1 << 40), True, 2.5, b"\x01\x02")
+    assert blob == struct.pack("P", a.ctypes.data) + struct.pack("i", 7) + struct.pack("N", 1 << 40) + struct.pack("i", 1) + \
+        struct.pack("f", 2.5) + b"\x01\x02"
+    with pytest.raises(RuntimeError):
+        pack(object())
+
+
+def test_kernel_builder_compiles_against_the_headers(tmp_path):
+    from mscclpp_b200.utils import KernelBuilder
+
+    src = tmp_path / "k.cu"
+    src.write_text(
+        '#include <mscclpp/packet_device.hpp>\n#include <mscclpp/concurrency_device.hpp>\n'
+        'extern "C" __global__ void scale(float* x, int n) {\n'
+        '  int i = blockIdx.x * blockDim.x + threadIdx.x;\n  if (i < n) x[i] *= SCALE;\n}\n')
+    kb = KernelBuilder("k.cu", "scale", file_dir=str(tmp_path), macro_dict={"SCALE": "2.0f"}, load=False)
+    assert kb.cubin[:4] == b"\x7fELF"
+    with pytest.raises(RuntimeError):
+        KernelBuilder("k.cu", "scale", file_dir=str(tmp_path), macro_dict={"SCALE": "not_defined_anywhere"}, load=False)
+
+
+def test_nccl_shim_host_calls():
+    path = os.path.join(mp.get_lib(), "libmscclpp_b200_nccl.so")
+    lib = ctypes.CDLL(path)
+    v = ctypes.c_int(0)
+    assert lib.ncclGetVersion(ctypes.byref(v)) == 0 and v.value >= 22000
+    lib.ncclGetErrorString.restype = ctypes.c_char_p
+    assert lib.ncclGetErrorString(0) == b"no error"
+    assert b"invalid argument" in lib.ncclGetErrorString(4)
+    uid = (ctypes.c_char * 128)()
+    assert lib.ncclGetUniqueId(uid) == 0 and any(uid.raw), "a unique id carries the rendezvous address"
+    assert lib.ncclGetVersion(None) == 4  # ncclInvalidArgument
+    count = ctypes.c_int()
+    assert lib.ncclCommCount(None, ctypes.byref(count)) == 4
+    for sym in ("ncclAllReduce", "ncclAllGather", "ncclReduceScatter", "ncclBroadcast", "ncclReduce", "ncclSend", "ncclRecv",
+                "ncclGroupStart", "ncclGroupEnd", "ncclCommInitRank", "ncclCommInitRankConfig", "ncclCommSplit", "ncclCommDestroy",
+                "ncclCommAbort", "ncclMemAlloc", "ncclMemFree", "ncclCommRegister", "ncclCommDeregister", "ncclAlltoAll",
+                "ncclCommGetAsyncError", "ncclGetLastError", "ncclCommUserRank", "ncclCommCuDevice", "ncclRedOpCreatePreMulSum"):
+        assert hasattr(lib, sym), sym
+
+
+def test_npkit_trace_generator(tmp_path):
+    """The converter pairs ENTRY/EXIT events of a synthetic dump and places GPU events on the host time line."""
+    from mscclpp_b200.utils.npkit_trace import convert_npkit_dump_to_trace, parse_event_header
+
+    names = parse_event_header()
+    by_name = {v: k for k, v in names.items()}
+    assert names[by_name["EXECUTOR_OP_PUT_ENTRY"] + 1] == "EXECUTOR_OP_PUT_WITH_SIGNAL_ENTRY"
+    assert not set(range(by_name["EXECUTOR_OP_NOP_ENTRY"], by_name["EXECUTOR_OP_PIPELINE_END_ENTRY"] + 1)) & \
+        set(range(by_name["EXECUTOR_OP_NOP_EXIT"], by_name["EXECUTOR_OP_PIPELINE_END_EXIT"] + 1)), "entry and exit ranges are disjoint"
+
+    def ev(type_, size, ts):
+        return struct.pack("<QQ", type_ | (size << 8), ts)
+
+    d = tmp_path / "dump"
+    d.mkdir()
+    (d / "gpu_events_rank_0_buf_0").write_bytes(
+        ev(by_name["EXECUTOR_OP_PUT_ENTRY"], 4096, 5_000) + ev(by_name["EXECUTOR_OP_PUT_EXIT"], 4096, 7_000))
+    (d / "cpu_events_rank_0_channel_0").write_bytes(
+        ev(by_name["CONN_ETH_WRITE_ENTRY"], 64, 1_000_000_500) + ev(by_name["CONN_ETH_WRITE_EXIT"], 64, 1_000_001_500))
+    (d / "gpu_clock_rate_rank_0").write_text("1000000")
+    (d / "cpu_clock_period_num_rank_0").write_text("1")
+    (d / "cpu_clock_period_den_rank_0").write_text("1000000000")
+    (d / "gpu_time_sync_rank_0").write_text("4000 1000000000")
+    import json
+
+    out = json.loads(open(convert_npkit_dump_to_trace(str(d), str(tmp_path / "out"))).read())["traceEvents"]
+    put = next(e for e in out if e["name"] == "EXECUTOR_OP_PUT")
+    assert put["ph"] == "X" and abs(put["dur"] - 2.0) < 1e-6 and abs(put["ts"] - (1e6 + 1.0)) < 1e-3
+    assert abs(put["args"]["bw (GB/s)"] - 4096 / 2.0 / 1e3) < 1e-9
+    wr = next(e for e in out if e["name"] == "CONN_ETH_WRITE")
+    assert abs(wr["dur"] - 1.0) < 1e-6 and wr["tid"] == "channel0"
