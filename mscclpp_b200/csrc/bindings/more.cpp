@@ -7,6 +7,7 @@
 #include <mscclpp/executor.hpp>
 #include <mscclpp/symmetric_heap.hpp>
 
+#include "../kernels/sp_fused.cuh"
 #include "../kernels/tp_fused.cuh"
 
 namespace py = pybind11;
@@ -78,6 +79,34 @@ void registerMoreBindings(py::module_& m) {
       py::arg("out"), py::arg("gamma"), py::arg("rinv"), py::arg("m"), py::arg("n"), py::arg("k"), py::arg("eps"),
       py::arg("block_n") = 256, py::arg("num_gemm_ctas") = 0, py::arg("num_reducers") = 0, py::arg("rows_per_unit") = 0,
       py::arg("mode") = 0, py::arg("nvls") = false, py::arg("stream") = 0);
+  m.def(
+      "all_gather_gemm",
+      [](SymmetricHeap& heap, uintptr_t aLocal, uintptr_t aFull, std::vector<uintptr_t> b, uintptr_t d, int M, int N, int K, int blockN,
+         int numGemmCtas, int numCopiers, int activation, uintptr_t stream) {
+        AgGemmArgs args{};
+        args.comm = heap.deviceComm();
+        args.shape.M = M;
+        args.shape.N = N;
+        args.shape.K = K;
+        args.aLocal = reinterpret_cast<const __nv_bfloat16*>(aLocal);
+        args.aFull = reinterpret_cast<__nv_bfloat16*>(aFull);
+        args.D = reinterpret_cast<__nv_bfloat16*>(d);
+        args.blockN = blockN;
+        args.numGemmCtas = numGemmCtas;
+        args.activation = activation;
+        args.emuRanks = heap.emulated() ? heap.world() : 1;
+        const size_t need = heap.emulated() ? heap.world() : 1;
+        if (b.size() != need) throw Error("all_gather_gemm: one B pointer per (emulated) rank", ErrorCode::InvalidUsage);
+        for (uintptr_t p : {aLocal, aFull, d}) {
+          if (!heap.contains(reinterpret_cast<const void*>(p))) throw Error("all_gather_gemm: a_local, a_full and d must be symmetric-heap memory", ErrorCode::InvalidUsage);
+        }
+        std::vector<const void*> bp;
+        for (auto v : b) bp.push_back(reinterpret_cast<const void*>(v));
+        checkCudaMore(launchAllGatherGemm(args, bp.data(), numCopiers, reinterpret_cast<cudaStream_t>(stream)), "all_gather_gemm");
+      },
+      py::arg("heap"), py::arg("a_local"), py::arg("a_full"), py::arg("b"), py::arg("d"), py::arg("m"), py::arg("n"), py::arg("k"),
+      py::arg("block_n") = 256, py::arg("num_gemm_ctas") = 0, py::arg("num_copiers") = 0, py::arg("activation") = 0,
+      py::arg("stream") = 0);
   m.def(
       "tp_scale_rows",
       [](uintptr_t h, uintptr_t rinv, uintptr_t gamma, uintptr_t out, int M, int N, uintptr_t stream) {

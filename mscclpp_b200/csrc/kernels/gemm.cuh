@@ -15,6 +15,10 @@ struct Shape {
   int aBoxRows;  // rows of the A tensor-map box: min(kBlockM, M); rows beyond it are never stored
   int rowMajorTiles;  // 0: consecutive tiles walk M (share a B tile); 1: walk N inside one row block, so
                       // that row blocks complete in order (what a fused consumer of whole rows wants)
+  int mOrder;       // order in which row blocks are visited: 0 natural; 1 interleaved over mOrderParam equal groups
+                    // (0, per, 2*per, ..., 1, per+1, ...: every group completes a block per round - reduce-scatter
+                    // owners all have work at once); 2 rotated by mOrderParam blocks (all-gather: own rows first)
+  int mOrderParam;
 };
 
 

@@ -59,6 +59,13 @@ MSCCLPP_DEVICE_INLINE void tileCoord(const Shape& s, int tile, int numMBlk, int 
     mBlk = tile % numMBlk;
     nBlk = tile / numMBlk;
   }
+  if (s.mOrder == 1) {
+    const int per = numMBlk / s.mOrderParam;
+    mBlk = (mBlk % s.mOrderParam) * per + mBlk / s.mOrderParam;
+  } else if (s.mOrder == 2) {
+    mBlk += s.mOrderParam;
+    if (mBlk >= numMBlk) mBlk -= numMBlk;
+  }
 }
 
 // 64-bit shared-memory matrix descriptor: K-major operand, 128-byte swizzle, tile base 1024B-aligned.
@@ -86,6 +93,11 @@ MSCCLPP_HOST_DEVICE_INLINE constexpr uint32_t makeInstrDesc() {
 
 struct NoGate {
   MSCCLPP_DEVICE_INLINE bool waitRowBlock(int /*mBlk*/) const { return true; }
+  // Tensor map and first row (in that map) of row block mBlk's A tiles.
+  MSCCLPP_DEVICE_INLINE const CUtensorMap* tmapA(int mBlk, const CUtensorMap* dflt, int& row) const {
+    row = mBlk * kBlockM;
+    return dflt;
+  }
 };
 
 struct SharedState {
@@ -161,6 +173,8 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
         int mBlk, nBlk;
         tileCoord(shape, tile, numMBlk, numNBlk, mBlk, nBlk);
         ok = gate.waitRowBlock(mBlk);
+        int aRow;
+        const CUtensorMap* tmapARows = gate.tmapA(mBlk, tmapA, aRow);
         for (int kb = 0; kb < numKBlk && ok; kb++) {
           ok = mbarWait(&st.empty[stage], phase ^ 1u, status, budgetNs, 100 + stage);
           if (!ok || *st.abortFlag) {
@@ -170,7 +184,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
           uint8_t* sa = tiles + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageABytes;
           ptx::mbar_expect_tx(&st.full[stage], shape.aBoxRows * kBlockK * 2 + Cfg::kStageBBytes);
-          ptx::tma_load_2d(sa, tmapA, kb * kBlockK, mBlk * kBlockM, &st.full[stage]);
+          ptx::tma_load_2d(sa, tmapARows, kb * kBlockK, aRow, &st.full[stage]);
           ptx::tma_load_2d(sb, tmapB, kb * kBlockK, nBlk * kBlockN, &st.full[stage]);
           armed |= 1u << stage;
           armedParity = (armedParity & ~(1u << stage)) | (phase << stage);

@@ -18,6 +18,8 @@
 // mode 0: the owner writes `out` and `residualOut` to every rank.
 // mode 1: the owner writes `residualOut` (= h) and one fp32 1/rms per row to every rank; `out` is then
 //         produced by a cheap local pass (tpScaleRows), which halves the bytes that cross NVLink.
+// mode 2: GEMM + reduce-scatter (sequence parallelism): rank r keeps the reduced rows [r*M/world, (r+1)*M/world)
+//         in its local `out` [M/world, N]; no residual, no norm, nothing is broadcast.
 //
 // The reference library has no counterpart: it provides the allreduce only.
 #include "tp_fused.cuh"
@@ -259,6 +261,17 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
       }
     }
 
+    if (a.mode == 2) {
+      // reduce-scatter: the reduced row stays here, in row j of this rank's [ownedRows, N] output
+      const uint64_t dstOff = outOff + static_cast<uint64_t>(j) * unitsPerRow * 16;
+#pragma unroll
+      for (int k = 0; k < kWordsPerThread; k++) {
+        const int w = lane + k * kGroupThreads;
+        if (w < unitsPerRow) ptx::st_na_v4(reinterpret_cast<void*>(local + dstOff + w * 16), h[k]);
+      }
+      continue;
+    }
+
     // ---- residual add (rounded to bf16 like the unfused composition), sum of squares
     float ss = 0.f;
 #pragma unroll
@@ -423,6 +436,14 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   if (emu > 8) return cudaErrorInvalidValue;
   args.shape.aBoxRows = M < gemm::kBlockM ? M : gemm::kBlockM;
   args.shape.rowMajorTiles = 1;
+  if (args.mode == 2) {
+    // reduce-scatter: rank r owns rows [r * M / world, (r + 1) * M / world); the GEMM visits the row blocks
+    // interleaved over the owners so that every owner's reducers have a finished block per round
+    if (M % (world * gemm::kBlockM) != 0) return cudaErrorInvalidValue;
+    args.rowsPerUnit = M / world;
+    args.shape.mOrder = 1;
+    args.shape.mOrderParam = world;
+  }
   if (args.rowsPerUnit <= 0) {
     int rpu = gemm::kBlockM;
     while (rpu > 1 && M < rpu * world) rpu >>= 1;

@@ -24,7 +24,8 @@ struct TpFusedArgs {
   int blockN;                   // GEMM N tile: 64, 128 or 256
   int numGemmCtas;              // 0 = all SMs but the reducers
   int rowsPerUnit;              // ownership granule, power of two <= 128; 0 = pick from M and world
-  int mode;                     // 0: owners broadcast out + residualOut; 1: owners broadcast residualOut + rinv
+  int mode;                     // 0: owners broadcast out + residualOut; 1: owners broadcast residualOut + rinv;
+                                // 2: reduce-scatter, out is this rank's [M / world, N] block (M % (world * 128) == 0)
   int nvls;                     // multimem through comm.mcBase instead of peer loads/stores
   int emuRanks;                 // > 1: that many emulated ranks in one cooperative launch (tests)
 };

@@ -139,6 +139,47 @@ def main():
                 e2 = (res.float() - h).abs().max().item()
                 report(f"tp_fused/T={tokens}/nvls={use_nvls}/mode={mode}", e1 < 0.12 and e2 <= 0.02 * h.abs().max().item() + 0.05, err=e1, res_err=e2)
 
+    # sequence-parallel halves: all-gather -> GEMM and GEMM -> reduce-scatter, one kernel each
+    from mscclpp_b200.parallel.sp_layer import all_gather_gemm, gemm_reduce_scatter
+
+    rows_per_rank, k, n_cols = 256, 1024, 1024
+    s_rows = rows_per_rank * world
+    a_local = symm.tensor((rows_per_rank, k), torch.bfloat16)
+    a_full = symm.tensor((s_rows, k), torch.bfloat16)
+    d = symm.tensor((s_rows, n_cols), torch.bfloat16)
+    gen = torch.Generator(device=dev).manual_seed(4242 + rank)
+    w = (torch.randn((n_cols, k), generator=gen, device=dev) * 0.05).to(torch.bfloat16)
+    for rep in range(3):
+        a_local.copy_(torch.randn((rows_per_rank, k), generator=gen, device=dev).to(torch.bfloat16))
+        parts = [torch.empty_like(a_local) for _ in range(world)]
+        dist.all_gather(parts, a_local)
+        ref = torch.nn.functional.gelu(torch.cat(parts).float() @ w.float().t(), approximate="tanh")
+        a_full.fill_(float("nan"))
+        d.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        all_gather_gemm(symm, a_local, a_full, w, d, activation="gelu")
+        torch.cuda.synchronize()
+        symm.check()
+        err = (d.float() - ref).abs().max().item()
+        report(f"all_gather_gemm/{rep}", err <= 0.02 * ref.abs().max().item() + 0.02, err=err)
+    partial = symm.tensor((s_rows, n_cols), torch.bfloat16)
+    out_rs = symm.tensor((rows_per_rank, n_cols), torch.bfloat16)
+    for use_nvls in ([False, True] if symm.nvls else [False]):
+        for rep in range(2):
+            x = torch.randn((s_rows, k), generator=gen, device=dev).to(torch.bfloat16)
+            mine = (x.float() @ w.float().t()).to(torch.bfloat16)
+            total = gathered_reference(mine)
+            out_rs.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            gemm_reduce_scatter(symm, x, w, partial, out_rs, nvls=use_nvls)
+            torch.cuda.synchronize()
+            symm.check()
+            ref = total[rank * rows_per_rank:(rank + 1) * rows_per_rank]
+            err = (out_rs.float() - ref).abs().max().item()
+            report(f"gemm_reduce_scatter/nvls={use_nvls}/{rep}", err <= 0.02 * ref.abs().max().item() + 0.05, err=err)
+
     dist.barrier()
     symm.destroy()
     dist.destroy_process_group()

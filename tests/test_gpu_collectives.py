@@ -240,3 +240,66 @@ def test_fused_tp_layer_one_kernel(world, mode, tokens, hidden, k):
         assert (got_h - h).abs().max().item() <= 0.02 * h.abs().max().item() + 0.05
         assert (got_y - y).abs().max().item() <= 0.1
     symm.destroy()
+
+
+@pytest.mark.parametrize("world,rows_per_rank,k,n_cols,act", [(2, 256, 256, 256, "none"), (4, 128, 512, 512, "gelu"), (8, 128, 256, 256, "silu")])
+def test_all_gather_gemm_one_kernel(world, rows_per_rank, k, n_cols, act):
+    """All-gather -> GEMM in one launch (copier CTAs + gated tcgen05 GEMM), all ranks emulated on one GPU."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.sp_layer import all_gather_gemm
+
+    symm = SymmetricMemory.emulated(world, nbytes=128 << 20, timeout_ms=3000)
+    s_rows = world * rows_per_rank
+    a_local = symm.tensor((rows_per_rank, k), torch.bfloat16)
+    a_full = symm.tensor((s_rows, k), torch.bfloat16)
+    out = symm.tensor((s_rows, n_cols), torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(world * 100 + k)
+    ws = [(torch.randn((n_cols, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(world)]
+    for rep in range(2):
+        shards = [torch.randn((rows_per_rank, k), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+        for r in range(world):
+            symm.rank_view(a_local, r).copy_(shards[r])
+            symm.rank_view(a_full, r).fill_(float("nan"))  # own rows are never copied there: must not be read
+            symm.rank_view(out, r).zero_()
+        all_gather_gemm(symm, a_local, a_full, ws, out, activation=act, block_n=256 if n_cols % 256 == 0 else 128, num_copiers=2,
+                        num_gemm_ctas=max(1, 16 // world))
+        torch.cuda.synchronize()
+        symm.check()
+        full = torch.cat(shards).float()
+        for r in range(world):
+            ref = full @ ws[r].float().t()
+            if act == "gelu":
+                ref = torch.nn.functional.gelu(ref, approximate="tanh")
+            elif act == "silu":
+                ref = torch.nn.functional.silu(ref)
+            got = symm.rank_view(out, r).float()
+            assert (got - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 0.02, (r, rep)
+    symm.destroy()
+
+
+@pytest.mark.parametrize("world,rows_per_rank,k,n_cols", [(2, 256, 128, 512), (4, 128, 256, 1024), (8, 128, 64, 256)])
+def test_gemm_reduce_scatter_one_kernel(world, rows_per_rank, k, n_cols):
+    """GEMM -> reduce-scatter in one launch: rank r ends with its row block of the summed product."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.sp_layer import gemm_reduce_scatter
+
+    symm = SymmetricMemory.emulated(world, nbytes=128 << 20, timeout_ms=3000)
+    s_rows = world * rows_per_rank
+    partial = symm.tensor((s_rows, n_cols), torch.bfloat16)
+    out = symm.tensor((rows_per_rank, n_cols), torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(world * 10 + k)
+    for rep in range(2):
+        xs = [torch.randn((s_rows, k), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+        ws = [(torch.randn((n_cols, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(world)]
+        for r in range(world):
+            symm.rank_view(out, r).zero_()
+        gemm_reduce_scatter(symm, xs, ws, partial, out, nvls=False, block_n=256 if n_cols % 256 == 0 else 128, num_reducers=3,
+                            num_gemm_ctas=max(1, 16 // world))
+        torch.cuda.synchronize()
+        symm.check()
+        total = sum((x.float() @ w.float().t()).to(torch.bfloat16).float() for x, w in zip(xs, ws))
+        for r in range(world):
+            ref = total[r * rows_per_rank:(r + 1) * rows_per_rank]
+            got = symm.rank_view(out, r).float()
+            assert (got - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 0.05, (r, rep)
+    symm.destroy()
