@@ -7,6 +7,7 @@
 #include <mscclpp/executor.hpp>
 #include <mscclpp/symmetric_heap.hpp>
 
+#include "../kernels/moe.cuh"
 #include "../kernels/sp_fused.cuh"
 #include "../kernels/tp_fused.cuh"
 
@@ -107,6 +108,58 @@ void registerMoreBindings(py::module_& m) {
       py::arg("heap"), py::arg("a_local"), py::arg("a_full"), py::arg("b"), py::arg("d"), py::arg("m"), py::arg("n"), py::arg("k"),
       py::arg("block_n") = 256, py::arg("num_gemm_ctas") = 0, py::arg("num_copiers") = 0, py::arg("activation") = 0,
       py::arg("stream") = 0);
+  m.def("moe_workspace_bytes", [] { return moeWorkspaceBytes(); });
+  m.def(
+      "moe_dispatch",
+      [](SymmetricHeap& heap, uintptr_t x, uintptr_t topkIdx, uintptr_t slotMap, uintptr_t recvX, uintptr_t recvScales, uintptr_t recvSrc,
+         uintptr_t recvCounts, uintptr_t workspace, int tokens, int hidden, int topk, int numExperts, int capacity, bool fp8, int nBlocks,
+         uintptr_t stream) {
+        MoeDispatchArgs a{};
+        a.comm = heap.deviceComm();
+        a.tokens = tokens;
+        a.hidden = hidden;
+        a.topk = topk;
+        a.numExperts = numExperts;
+        a.capacity = capacity;
+        a.fp8 = fp8 ? 1 : 0;
+        a.x = reinterpret_cast<const __nv_bfloat16*>(x);
+        a.topkIdx = reinterpret_cast<const int32_t*>(topkIdx);
+        a.slotMap = reinterpret_cast<int32_t*>(slotMap);
+        a.recvX = reinterpret_cast<void*>(recvX);
+        a.recvScales = reinterpret_cast<float*>(recvScales);
+        a.recvSrc = reinterpret_cast<int32_t*>(recvSrc);
+        a.recvCounts = reinterpret_cast<int32_t*>(recvCounts);
+        a.workspace = reinterpret_cast<uint32_t*>(workspace);
+        a.emuRanks = heap.emulated() ? heap.world() : 1;
+        for (uintptr_t p : {recvX, recvSrc, workspace}) {
+          if (!heap.contains(reinterpret_cast<const void*>(p))) throw Error("moe_dispatch: receive buffers and workspace must be symmetric-heap memory", ErrorCode::InvalidUsage);
+        }
+        checkCudaMore(launchMoeDispatch(a, nBlocks, reinterpret_cast<cudaStream_t>(stream)), "moe_dispatch");
+      },
+      py::arg("heap"), py::arg("x"), py::arg("topk_idx"), py::arg("slot_map"), py::arg("recv_x"), py::arg("recv_scales"), py::arg("recv_src"),
+      py::arg("recv_counts"), py::arg("workspace"), py::arg("tokens"), py::arg("hidden"), py::arg("topk"), py::arg("num_experts"),
+      py::arg("capacity"), py::arg("fp8") = false, py::arg("n_blocks") = 0, py::arg("stream") = 0);
+  m.def(
+      "moe_combine",
+      [](SymmetricHeap& heap, uintptr_t topkIdx, uintptr_t topkWeights, uintptr_t slotMap, uintptr_t expertOut, uintptr_t y, int tokens,
+         int hidden, int topk, int numExperts, int nBlocks, uintptr_t stream) {
+        MoeCombineArgs a{};
+        a.comm = heap.deviceComm();
+        a.tokens = tokens;
+        a.hidden = hidden;
+        a.topk = topk;
+        a.numExperts = numExperts;
+        a.topkIdx = reinterpret_cast<const int32_t*>(topkIdx);
+        a.topkWeights = reinterpret_cast<const float*>(topkWeights);
+        a.slotMap = reinterpret_cast<const int32_t*>(slotMap);
+        a.expertOut = reinterpret_cast<const __nv_bfloat16*>(expertOut);
+        a.y = reinterpret_cast<__nv_bfloat16*>(y);
+        a.emuRanks = heap.emulated() ? heap.world() : 1;
+        if (!heap.contains(reinterpret_cast<const void*>(expertOut))) throw Error("moe_combine: expert_out must be symmetric-heap memory", ErrorCode::InvalidUsage);
+        checkCudaMore(launchMoeCombine(a, nBlocks, reinterpret_cast<cudaStream_t>(stream)), "moe_combine");
+      },
+      py::arg("heap"), py::arg("topk_idx"), py::arg("topk_weights"), py::arg("slot_map"), py::arg("expert_out"), py::arg("y"), py::arg("tokens"),
+      py::arg("hidden"), py::arg("topk"), py::arg("num_experts"), py::arg("n_blocks") = 0, py::arg("stream") = 0);
   m.def(
       "tp_scale_rows",
       [](uintptr_t h, uintptr_t rinv, uintptr_t gamma, uintptr_t out, int M, int N, uintptr_t stream) {

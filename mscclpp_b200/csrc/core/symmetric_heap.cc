@@ -332,6 +332,11 @@ void SymmetricHeap::checkStatus() {
   refreshStatus();
   if (status_->code == kDevOk) return;
   DeviceStatus s = *status_;
+  if (s.code == kDevErrorCapacity) {
+    throw Error("receive buffer too small on rank " + std::to_string(s.rank) + ": capacity " + std::to_string(s.expected) +
+                    " rows (nothing was sent; call resetStatus() and retry with a larger buffer)",
+                ErrorCode::InvalidUsage);
+  }
   std::string what = "device-side wait gave up: code " + std::to_string(s.code) + " rank " + std::to_string(s.rank) +
                      " block " + std::to_string(s.block) + " site " + std::to_string(s.where) + " peer " +
                      std::to_string(s.peer) + " expected " + std::to_string(s.expected) + " observed " +

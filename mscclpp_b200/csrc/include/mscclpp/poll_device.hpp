@@ -25,6 +25,7 @@ enum DeviceErrorCode : uint32_t {
   kDevTimeoutMbarrier = 5,
   kDevTimeoutFlag = 6,
   kDevBadArgument = 7,
+  kDevErrorCapacity = 8,  // a receive buffer is too small for the rows routed to it (MoE dispatch)
 };
 
 // Lives in host-pinned (mapped) memory or in device memory; 64 bytes.

@@ -180,6 +180,52 @@ def main():
             err = (out_rs.float() - ref).abs().max().item()
             report(f"gemm_reduce_scatter/nvls={use_nvls}/{rep}", err <= 0.02 * ref.abs().max().item() + 0.05, err=err)
 
+    # MoE expert-parallel dispatch / combine on real peers
+    from mscclpp_b200.parallel.moe import ExpertParallelDispatcher, dequantize_rows
+
+    experts, hid, toks, topk = 8 * world, 2048, 512, 2
+    el = experts // world
+    for fp8 in (False, True):
+        disp = ExpertParallelDispatcher(symm, num_experts=experts, hidden=hid, max_tokens=toks, topk=topk, fp8=fp8)
+        gen = torch.Generator(device=dev).manual_seed(31 + rank)
+        for rep in range(2):
+            xm = torch.randn((toks, hid), generator=gen, device=dev).to(torch.bfloat16)
+            idx = torch.stack([torch.randperm(experts, generator=gen, device=dev)[:topk] for _ in range(toks)]).to(torch.int32)
+            wt = torch.rand((toks, topk), generator=gen, device=dev)
+            torch.cuda.synchronize()
+            dist.barrier()
+            recv_x, counts, slot_map = disp.dispatch(xm, idx)
+            torch.cuda.synchronize()
+            symm.check()
+            cnt = counts.cpu().tolist()
+            # what should have arrived: gather everybody's tokens and routing
+            all_x = [torch.empty_like(xm) for _ in range(world)]
+            all_idx = [torch.empty_like(idx) for _ in range(world)]
+            dist.all_gather(all_x, xm)
+            dist.all_gather(all_idx, idx)
+            expect_cnt = [sum(int((all_idx[s] == rank * el + j).sum()) for s in range(world)) for j in range(el)]
+            src = disp.recv_src[:cnt[el]].cpu().tolist()
+            rows = recv_x[:cnt[el]]
+            got = dequantize_rows(rows, disp.recv_scales[:cnt[el]]) if fp8 else rows.float()
+            want = torch.stack([all_x[v >> 24][v & 0xFFFFFF].float() for v in src]) if src else got
+            err = (got - want).abs().max().item() if src else 0.0
+            report(f"moe_dispatch/fp8={fp8}/{rep}", cnt[:el] == expect_cnt and err <= (0.07 * want.abs().max().item() if fp8 else 0.0), err=err)
+            start = 0
+            for j in range(el):
+                disp.expert_out[start:start + cnt[j]] = (got[start:start + cnt[j]] * (0.5 * (rank * el + j + 1))).to(torch.bfloat16)
+                start += cnt[j]
+            torch.cuda.synchronize()
+            dist.barrier()
+            y = disp.combine(idx, wt, slot_map)
+            torch.cuda.synchronize()
+            symm.check()
+            ref = torch.zeros((toks, hid), device=dev)
+            for k in range(topk):
+                e = idx[:, k].long()
+                ref += wt[:, k:k + 1] * (xm.float() * (0.5 * (e + 1)).unsqueeze(1)).to(torch.bfloat16).float()
+            err = (y.float() - ref).abs().max().item()
+            report(f"moe_combine/fp8={fp8}/{rep}", err <= (0.08 if fp8 else 0.02) * ref.abs().max().item() + 0.02, err=err)
+
     dist.barrier()
     symm.destroy()
     dist.destroy_process_group()

@@ -303,3 +303,103 @@ def test_gemm_reduce_scatter_one_kernel(world, rows_per_rank, k, n_cols):
             got = symm.rank_view(out, r).float()
             assert (got - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 0.05, (r, rep)
     symm.destroy()
+
+
+def _moe_reference(xs, idxs, wts, world, experts, f):
+    """fp32 PyTorch model of dispatch -> expert function f(e, rows) -> combine, for all ranks."""
+    ys = []
+    for r in range(world):
+        y = torch.zeros_like(xs[r], dtype=torch.float32)
+        for k in range(idxs[r].shape[1]):
+            e = idxs[r][:, k]
+            valid = e >= 0
+            contrib = torch.zeros_like(y)
+            for ex in range(experts):
+                m = valid & (e == ex)
+                if m.any():
+                    contrib[m] = f(ex, xs[r][m].float())
+            y += wts[r][:, k:k + 1] * contrib
+        ys.append(y)
+    return ys
+
+
+@pytest.mark.parametrize("world,experts,tokens,hidden,topk,fp8", [(2, 8, 200, 512, 2, False), (4, 16, 96, 1024, 2, True), (8, 64, 64, 4096, 2, False),
+                                                                  (8, 64, 33, 1024, 4, True)])
+def test_moe_dispatch_combine(world, experts, tokens, hidden, topk, fp8):
+    """Dispatch pushes every (token, expert) pair into the hosting rank's expert-grouped buffer; combine pulls the expert
+    outputs back. All ranks emulated on one GPU; checked against a plain PyTorch model of the same exchange."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.moe import ExpertParallelDispatcher, dequantize_rows
+
+    symm = SymmetricMemory.emulated(world, nbytes=256 << 20, timeout_ms=3000)
+    disp = ExpertParallelDispatcher(symm, num_experts=experts, hidden=hidden, max_tokens=tokens, topk=topk, fp8=fp8)
+    el = experts // world
+    g = torch.Generator(device="cuda").manual_seed(world * 1000 + tokens)
+    for rep in range(2):
+        xs = [torch.randn((tokens, hidden), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+        idxs = [torch.stack([torch.randperm(experts, generator=g, device="cuda")[:topk] for _ in range(tokens)]).to(torch.int32) for _ in range(world)]
+        idxs[0][0, 0] = -1  # an unused slot
+        wts = [torch.rand((tokens, topk), generator=g, device="cuda") for _ in range(world)]
+        for r in range(world):
+            x_s, idx_s, w_s = disp.stage(r, xs[r], idxs[r], wts[r])
+        recv_x, counts, slot_map = disp.dispatch(x_s, idx_s, n_blocks=4)
+        torch.cuda.synchronize()
+        symm.check()
+        # every destination holds exactly the rows routed to it, grouped by expert, tagged with their source
+        for d in range(world):
+            cnt = symm.rank_view(counts, d).cpu().tolist()
+            expect_cnt = [sum(int((idxs[s] == d * el + j).sum()) for s in range(world)) for j in range(el)]
+            assert cnt[:el] == expect_cnt and cnt[el] == sum(expect_cnt)
+            rows = symm.rank_view(recv_x, d)[:cnt[el]]
+            src = symm.rank_view(disp.recv_src, d)[:cnt[el]].cpu()
+            got = dequantize_rows(rows, symm.rank_view(disp.recv_scales, d)[:cnt[el]]) if fp8 else rows.float()
+            want = torch.stack([xs[int(v) >> 24][int(v) & 0xFFFFFF].float() for v in src.tolist()]) if cnt[el] else got
+            tol = 0.07 * want.abs().max().item() if fp8 else 0.0
+            assert (got - want).abs().max().item() <= tol
+            # the expert of a row follows from its position
+            bounds = [0]
+            for c_ in expect_cnt:
+                bounds.append(bounds[-1] + c_)
+            for j in range(el):
+                for v in src[bounds[j]:bounds[j + 1]].tolist():
+                    s_, t_ = int(v) >> 24, int(v) & 0xFFFFFF
+                    assert (idxs[s_][t_] == d * el + j).any()
+        # experts: out = (e + 1) * 0.5 * row  (cheap, expert dependent)
+        for d in range(world):
+            cnt = symm.rank_view(counts, d).cpu().tolist()
+            rows = symm.rank_view(recv_x, d)
+            val = dequantize_rows(rows[:cnt[el]], symm.rank_view(disp.recv_scales, d)[:cnt[el]]) if fp8 else rows[:cnt[el]].float()
+            out = symm.rank_view(disp.expert_out, d)
+            start = 0
+            for j in range(el):
+                out[start:start + cnt[j]] = (val[start:start + cnt[j]] * (0.5 * (d * el + j + 1))).to(torch.bfloat16)
+                start += cnt[j]
+        y = disp.combine(idx_s, w_s, slot_map, n_blocks=4)
+        torch.cuda.synchronize()
+        symm.check()
+        ref = _moe_reference(xs, idxs, wts, world, experts, lambda e, rows: (rows * (0.5 * (e + 1))).to(torch.bfloat16).float())
+        for r in range(world):
+            got = symm.rank_view(y, r).float()
+            scale = ref[r].abs().max().item()
+            assert (got - ref[r]).abs().max().item() <= (0.08 if fp8 else 0.02) * scale + 0.02, (r, rep)
+    symm.destroy()
+
+
+def test_moe_dispatch_reports_small_receive_buffer():
+    """A receive buffer that cannot hold the routed rows is reported as an error; nothing is written out of bounds."""
+    from mscclpp_b200 import SymmetricMemory, native
+    from mscclpp_b200.parallel.moe import ExpertParallelDispatcher
+
+    symm = SymmetricMemory.emulated(2, nbytes=64 << 20, timeout_ms=1000)
+    disp = ExpertParallelDispatcher(symm, num_experts=4, hidden=256, max_tokens=64, topk=2, capacity=16)
+    x = torch.ones((64, 256), dtype=torch.bfloat16, device="cuda")
+    idx = torch.tensor([[0, 1]] * 64, dtype=torch.int32, device="cuda")  # everything goes to rank 0
+    for r in range(2):
+        x_s, idx_s, _ = disp.stage(r, x, idx)
+    disp.dispatch(x_s, idx_s, n_blocks=2)
+    torch.cuda.synchronize()
+    with pytest.raises(native().Error):
+        symm.check()
+    assert int(symm.rank_view(disp.slot_map, 0).max()) == -1
+    symm.heap.reset_status()
+    symm.destroy()
