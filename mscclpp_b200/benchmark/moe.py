@@ -1,0 +1,124 @@
+"""MoE expert-parallel dispatch / combine benchmark against NCCL all-to-all (torch.distributed.all_to_all_single
+plus the permutes it needs) on the same routing.
+
+    python -m torch.distributed.run --nproc-per-node 8 -m mscclpp_b200.benchmark.moe --experts 64 --topk 2 --hidden 4096 --tokens 4096
+
+Reports microseconds (device-timed, max over ranks) and the payload bandwidth per GPU: bytes of token rows that
+leave (dispatch) or enter (combine) a GPU over NVLink divided by the time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+
+import torch
+import torch.distributed as dist
+
+from .common import Dist, time_eager
+
+LINK_GBS = 770.0
+
+
+def run(args) -> dict:
+    import mscclpp_b200 as mp
+    from mscclpp_b200.parallel.moe import ExpertParallelDispatcher
+
+    d = Dist()
+    ep = d.world
+    T, H, K, E = args.tokens, args.hidden, args.topk, args.experts
+    el = E // ep
+    cap = 2 * T * K
+    heap = cap * H * 2 * 2 + cap * H + T * H * 2 * 3 + (512 << 20)
+    symm = mp.SymmetricMemory.from_env(nbytes=2 * heap)
+    g = torch.Generator(device=d.device).manual_seed(77 + d.rank)
+    x = torch.randn((T, H), generator=g, device=d.device).to(torch.bfloat16)
+    scores = torch.rand((T, E), generator=g, device=d.device)
+    wts, idx = torch.topk(scores, K, dim=1)
+    idx = idx.to(torch.int32).contiguous()
+    wts = (wts / wts.sum(1, keepdim=True)).float().contiguous()
+    remote_pairs = int((idx // el != d.rank).sum().item())
+    out = {"config": {"experts": E, "topk": K, "hidden": H, "tokens_per_rank": T, "ep": ep, "routing": "uniform random top-k",
+                      "l2": "64 MB of rows per direction per step plus receive buffers exceed the L2"}}
+    for fp8 in (False, True):
+        disp = ExpertParallelDispatcher(symm, num_experts=E, hidden=H, max_tokens=T, topk=K, capacity=cap, fp8=fp8)
+        best = None
+        for nb in args.blocks:
+            us = time_eager(d, lambda: disp.dispatch(x, idx, n_blocks=nb), args.iters, args.warmup, check=symm.check) * 1e3
+            if best is None or us < best[0]:
+                best = (us, nb)
+        row_bytes = H * (1 if fp8 else 2) + (H // 128 * 4 if fp8 else 0)
+        out["dispatch_fp8" if fp8 else "dispatch_bf16"] = {
+            "us": round(best[0], 2), "blocks": best[1], "nvlink_gbs_per_gpu": round(remote_pairs * row_bytes / best[0] / 1e3, 1),
+            "frac_of_link": round(remote_pairs * row_bytes / best[0] / 1e3 / LINK_GBS, 3)}
+        if not fp8:
+            _, _, slot_map = disp.dispatch(x, idx, n_blocks=best[1])
+            disp.expert_out.copy_(disp.recv_x)  # identity experts
+            torch.cuda.synchronize()
+            d.barrier()
+            bestc = None
+            for nb in args.blocks:
+                us = time_eager(d, lambda: disp.combine(idx, wts, slot_map, n_blocks=nb), args.iters, args.warmup, check=symm.check) * 1e3
+                if bestc is None or us < bestc[0]:
+                    bestc = (us, nb)
+            y = disp.combine(idx, wts, slot_map, n_blocks=bestc[1])
+            torch.cuda.synchronize()
+            ref = x.float() * wts.sum(1, keepdim=True)  # identity experts: y = sum_k w_k x
+            err = (y.float() - ref).abs().max().item() / ref.abs().max().item()
+            out["combine_bf16"] = {"us": round(bestc[0], 2), "blocks": bestc[1], "rel_err": err,
+                                   "nvlink_gbs_per_gpu": round(remote_pairs * H * 2 / bestc[0] / 1e3, 1),
+                                   "frac_of_link": round(remote_pairs * H * 2 / bestc[0] / 1e3 / LINK_GBS, 3)}
+        del disp
+
+    # ---- NCCL baseline: sort pairs by destination rank, exchange sizes, all_to_all_single both ways
+    if ep > 1:
+        flat_e = idx.flatten().long()
+        order = torch.argsort(flat_e // el, stable=True)
+        send_counts = torch.bincount(flat_e // el, minlength=ep)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts)
+        s_list, r_list = send_counts.tolist(), recv_counts.tolist()
+        tok_of_pair = (order // K)
+        recv_buf = torch.empty((sum(r_list), H), dtype=torch.bfloat16, device=d.device)
+        back_buf = torch.empty((sum(s_list), H), dtype=torch.bfloat16, device=d.device)
+
+        def nccl_dispatch():
+            send = x[tok_of_pair]  # the permute a library user has to do
+            dist.all_to_all_single(recv_buf, send, r_list, s_list)
+
+        def nccl_combine():
+            dist.all_to_all_single(back_buf, recv_buf, s_list, r_list)
+            y2 = torch.zeros((T, H), dtype=torch.float32, device=d.device)
+            y2.index_add_(0, tok_of_pair, back_buf.float() * wts.flatten()[order].unsqueeze(1))
+            return y2.to(torch.bfloat16)
+
+        out["nccl_dispatch_bf16_us"] = round(time_eager(d, nccl_dispatch, args.iters, args.warmup) * 1e3, 2)
+        out["nccl_combine_bf16_us"] = round(time_eager(d, nccl_combine, args.iters, args.warmup) * 1e3, 2)
+        out["dispatch_speedup_vs_nccl"] = round(out["nccl_dispatch_bf16_us"] / out["dispatch_bf16"]["us"], 3)
+        out["combine_speedup_vs_nccl"] = round(out["nccl_combine_bf16_us"] / out["combine_bf16"]["us"], 3)
+    d.barrier()
+    symm.destroy()
+    if args.standalone:
+        d.close()
+    return out if d.rank == 0 else {}
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser()
+    p.add_argument("--experts", type=int, default=64)
+    p.add_argument("--topk", type=int, default=2)
+    p.add_argument("--hidden", type=int, default=4096)
+    p.add_argument("--tokens", type=int, default=4096)
+    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--blocks", type=int, nargs="*", default=[32, 64, 128])
+    args = p.parse_args(argv)
+    args.standalone = True
+    res = run(args)
+    if res:
+        print(json.dumps({"moe": res}), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

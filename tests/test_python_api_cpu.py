@@ -179,3 +179,25 @@ def test_npkit_trace_generator(tmp_path):
     assert abs(put["args"]["bw (GB/s)"] - 4096 / 2.0 / 1e3) < 1e-9
     wr = next(e for e in out if e["name"] == "CONN_ETH_WRITE")
     assert abs(wr["dur"] - 1.0) < 1e-6 and wr["tid"] == "channel0"
+
+
+def test_tuning_config_store(tmp_path):
+    from mscclpp_b200.benchmark.tuning_config import TuningConfig
+
+    path = str(tmp_path / "tuned.json")
+    store = TuningConfig()
+    store.record("B200-x8-nvls", "allreduce", "bfloat16", 1 << 20, "default_allreduce_packet", 32, 512, 11.5)
+    store.record("B200-x8-nvls", "allreduce", "bfloat16", 1 << 10, "default_allreduce_nvls_packet", 8, 256, 6.0)
+    store.record("B200-x8-nvls", "allreduce", "bfloat16", 1 << 20, "default_allreduce_nvls_zero_copy", 16, 512, 10.0)  # replaces
+    store.save(path)
+    again = TuningConfig(path)
+    assert again.lookup("B200-x8-nvls", "allreduce", "bfloat16", 512)["algorithm"] == "default_allreduce_nvls_packet"
+    assert again.lookup("B200-x8-nvls", "allreduce", "bfloat16", 4096)["algorithm"] == "default_allreduce_nvls_zero_copy"
+    assert again.lookup("B200-x8-nvls", "allreduce", "bfloat16", 1 << 30)["n_blocks"] == 16  # beyond the table: last row
+    assert again.lookup("other", "allreduce", "bfloat16", 4096) is None
+    # the store doubles as an algorithm selector
+    sel = again.make_selector("B200-x8-nvls")
+    req = N.CollectiveRequest()
+    req.collective, req.message_size, req.dtype = "allreduce", 100, N.DataType.bfloat16
+    algo = mp.Algorithm.from_callable("default_allreduce_nvls_packet", "allreduce", lambda *a: 0)
+    assert sel({"allreduce": {"default_allreduce_nvls_packet": algo._algorithm}}, req).name == "default_allreduce_nvls_packet"
