@@ -167,6 +167,13 @@ class SymmetricMemory:
     def contains(self, t: torch.Tensor) -> bool:
         return self.heap.contains(t.data_ptr(), max(t.numel() * t.element_size(), 1))
 
+    def barrier(self) -> None:
+        """Host-side barrier over the ranks of the heap, after this rank's GPU work has finished. Needed after
+        initialising symmetric memory that peers write into (a late zero-fill would wipe what an early peer wrote)."""
+        torch.cuda.synchronize(self.device)
+        if not self.emulated_mode and self.bootstrap is not None and self.world > 1:
+            self.bootstrap.barrier()
+
     # ------------------------------------------------------------------ health
     def check(self) -> None:
         """Raise if a device-side wait of an earlier launch gave up (call after a synchronize)."""

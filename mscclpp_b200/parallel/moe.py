@@ -43,7 +43,7 @@ class ExpertParallelDispatcher:
         ranks = range(symm.world) if symm.emulated_mode else [symm.rank]
         for r in ranks:
             (symm.rank_view(self.workspace, r) if symm.emulated_mode else self.workspace).zero_()
-        torch.cuda.synchronize()
+        symm.barrier()  # peers write their counts into this workspace: nobody may start before everybody has zeroed it
 
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, n_blocks: int = 0,
                  stream: Optional[torch.cuda.Stream] = None) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
