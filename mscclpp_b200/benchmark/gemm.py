@@ -20,6 +20,7 @@ def main(argv=None) -> int:
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--no-cublas", action="store_true")
+    p.add_argument("--two-sm", type=int, default=-1, help="1: 256x256 tiles on SM pairs, 0: one-SM tiles, -1: automatic")
     args = p.parse_args(argv)
     from mscclpp_b200.ops.gemm import gemm_bf16, pick_block_n
 
@@ -42,9 +43,10 @@ def main(argv=None) -> int:
         torch.cuda.synchronize()
         return s.elapsed_time(e) / args.iters * 1e3
 
-    us = timed(lambda: gemm_bf16(a, b, d, block_n=bn))
+    two_sm = None if args.two_sm < 0 else bool(args.two_sm)
+    us = timed(lambda: gemm_bf16(a, b, d, block_n=args.block_n, two_sm=two_sm))
     flops = 2.0 * args.m * args.n * args.k
-    out = {"shape": [args.m, args.n, args.k], "block_n": bn, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1)}
+    out = {"shape": [args.m, args.n, args.k], "block_n": bn, "two_sm": args.two_sm, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1)}
     ref = a.float() @ b.float().t() if args.m * args.n <= (1 << 26) else None
     if ref is not None:
         out["rel_err"] = ((d.float() - ref).abs().max() / ref.abs().max()).item()

@@ -362,6 +362,16 @@ PYBIND11_MODULE(_native, m) {
       py::arg("a"), py::arg("b"), py::arg("d"), py::arg("m"), py::arg("n"), py::arg("k"), py::arg("ldd"),
       py::arg("block_n") = 256, py::arg("num_ctas") = 0, py::arg("status") = 0, py::arg("stream") = 0);
 
+  m.def(
+      "gemm_bf16_two_sm",
+      [](uintptr_t A, uintptr_t B, uintptr_t D, int M, int N, int K, int ldd, int numCtas, uintptr_t status, uintptr_t stream) {
+        checkCuda(gemm::gemmBf16TwoSm(reinterpret_cast<const void*>(A), reinterpret_cast<const void*>(B), reinterpret_cast<void*>(D), M, N,
+                                      K, ldd, numCtas, reinterpret_cast<DeviceStatus*>(status), reinterpret_cast<cudaStream_t>(stream)),
+                  "gemm_bf16_two_sm");
+      },
+      py::arg("a"), py::arg("b"), py::arg("d"), py::arg("m"), py::arg("n"), py::arg("k"), py::arg("ldd"), py::arg("num_ctas") = 0,
+      py::arg("status") = 0, py::arg("stream") = 0);
+
   registerCoreBindings(m);
   registerAlgorithmBindings(m);
   registerMoreBindings(m);

@@ -404,6 +404,63 @@ MSCCLPP_DEVICE_INLINE void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32])
 }
 MSCCLPP_DEVICE_INLINE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- two-SM (cta_group::2) forms: a pair of CTAs of one cluster works on one MMA tile. The leader (cluster rank 0)
+// issues the MMAs; both CTAs hold half of the operands and half of the accumulator rows.
+MSCCLPP_DEVICE_INLINE uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the variable at `smemAddr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+MSCCLPP_DEVICE_INLINE uint32_t mapa_shared(uint32_t smemAddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smemAddr), "r"(rank));
+  return r;
+}
+MSCCLPP_DEVICE_INLINE void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive (count 1) on an mbarrier of any CTA of the cluster, given its shared::cluster address.
+MSCCLPP_DEVICE_INLINE void mbar_arrive_cluster(uint32_t clusterAddr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterAddr) : "memory");
+}
+// Tiled load into THIS CTA's shared memory whose completion bytes are counted on an mbarrier given by its
+// shared::cluster address (the pair leader's). No multicast: each CTA fetches its own half of the operands.
+MSCCLPP_DEVICE_INLINE void tma_load_2d_pair(void* smem_dst, const void* tmap, int x, int y, uint32_t barClusterAddr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], "
+      "[%4];" ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(x), "r"(y), "r"(barClusterAddr)
+      : "memory");
+}
+MSCCLPP_DEVICE_INLINE void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols)
+               : "memory");
+}
+MSCCLPP_DEVICE_INLINE void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+MSCCLPP_DEVICE_INLINE void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+MSCCLPP_DEVICE_INLINE void tcgen05_mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the mbarrier at this offset in every CTA of `ctaMask` once the MMAs issued so far have retired.
+MSCCLPP_DEVICE_INLINE void tcgen05_commit_pair(uint64_t* bar, uint16_t ctaMask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+                   smem_u32(bar)),
+               "h"(ctaMask)
+               : "memory");
+}
+
 // Named barrier among `nthreads` threads of the CTA (ids 1..15; 0 is __syncthreads()).
 MSCCLPP_DEVICE_INLINE void named_barrier(uint32_t id, uint32_t nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");

@@ -3,6 +3,7 @@
 
 #include <mutex>
 
+#include "gemm2_sm100.cuh"
 #include "gemm_sm100.cuh"
 
 namespace mscclpp {
@@ -57,7 +58,63 @@ cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, Shape shape, vo
   return cudaGetLastError();
 }
 
+__global__ void __launch_bounds__(kNumThreads, 1)
+    gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, Shape shape,
+                       __nv_bfloat16* D, int ldd, DeviceStatus* status, uint64_t budgetNs) {
+  extern __shared__ uint8_t smemRaw[];
+  NoGate gate;
+  StoreBf16 epi{D, ldd, shape.M};
+  gemmCtaPair(&tmapA, &tmapB, shape, blockIdx.x / 2, gridDim.x / 2, gate, epi, status, budgetNs, smemRaw);
+}
+
 }  // namespace
+
+cudaError_t launchClusterPair(const void* kernel, dim3 grid, dim3 block, size_t smemBytes, void** params, bool cooperative,
+                              cudaStream_t stream) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  attrs[0].id = cudaLaunchAttributeClusterDimension;
+  attrs[0].val.clusterDim.x = 2;
+  attrs[0].val.clusterDim.y = 1;
+  attrs[0].val.clusterDim.z = 1;
+  attrs[1].id = cudaLaunchAttributeCooperative;
+  attrs[1].val.cooperative = 1;
+  cfg.attrs = attrs;
+  cfg.numAttrs = cooperative ? 2 : 1;
+  return cudaLaunchKernelExC(&cfg, kernel, params);
+}
+
+cudaError_t gemmBf16TwoSm(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int numCtas, DeviceStatus* status,
+                          cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % kBlockK != 0 || N % Config2::kBlockN != 0 || ldd % 8 != 0) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(D) & 15) != 0) return cudaErrorInvalidValue;
+  Shape shape{M, N, K, kBlockM, 0, 0, 0};
+  CUtensorMap ta, tb;
+  cudaError_t e = makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, kBlockM);
+  if (e != cudaSuccess) return e;
+  e = makeTensorMapBf16(&tb, B, N, K, static_cast<uint64_t>(K) * 2, Config2::kBlockN / 2);
+  if (e != cudaSuccess) return e;
+  static bool attrSet = false;
+  if (!attrSet) {
+    e = cudaFuncSetAttribute(gemmBf16PairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config2::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attrSet = true;
+  }
+  const int tiles = ((M + Config2::kPairM - 1) / Config2::kPairM) * (N / Config2::kBlockN);
+  int grid = numCtas > 0 ? numCtas : smCount();
+  grid &= ~1;
+  if (grid > 2 * tiles) grid = 2 * tiles;
+  if (grid < 2) grid = 2;
+  __nv_bfloat16* d = static_cast<__nv_bfloat16*>(D);
+  uint64_t budget = 2000000000ull;
+  void* params[] = {&ta, &tb, &shape, &d, &ldd, &status, &budget};
+  return launchClusterPair(reinterpret_cast<const void*>(gemmBf16PairKernel), dim3(grid), dim3(kNumThreads), Config2::kSmemBytes, params,
+                           false, stream);
+}
 
 int smCount() {
   static int n = 0;

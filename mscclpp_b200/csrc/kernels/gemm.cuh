@@ -32,6 +32,15 @@ cudaError_t makeTensorMapBf16(CUtensorMap* map, const void* ptr, uint64_t rows, 
 cudaError_t gemmBf16(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int blockN, int numCtas,
                      DeviceStatus* status, cudaStream_t stream);
 
+// Same product on 256 x 256 tiles shared by pairs of SMs (tcgen05 cta_group::2, clusters of two CTAs).
+// N % 256 == 0; K % 64 == 0; numCtas <= 0 picks one CTA per SM (rounded down to an even number).
+cudaError_t gemmBf16TwoSm(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int numCtas, DeviceStatus* status,
+                          cudaStream_t stream);
+
+// Launch helper for kernels built on the two-SM core: clusters of two CTAs along x, optionally cooperative.
+cudaError_t launchClusterPair(const void* kernel, dim3 grid, dim3 block, size_t smemBytes, void** params, bool cooperative,
+                              cudaStream_t stream);
+
 int smCount();
 
 }  // namespace gemm

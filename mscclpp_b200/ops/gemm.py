@@ -21,8 +21,11 @@ def pick_block_n(m: int, n: int) -> int:
 
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, block_n: int = 0, num_ctas: int = 0,
-              stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
-    """out[M, N] = a[M, K] @ w[N, K]^T  (w in nn.Linear layout: out_features x in_features)."""
+              stream: Optional[torch.cuda.Stream] = None, two_sm: Optional[bool] = None) -> torch.Tensor:
+    """out[M, N] = a[M, K] @ w[N, K]^T  (w in nn.Linear layout: out_features x in_features).
+
+    two_sm: run 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2); None picks it when the problem has enough
+    such tiles to fill the GPU and no N tile was asked for."""
     n = native.load()
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
     m, k = a.shape
@@ -31,7 +34,12 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     if out is None:
         out = torch.empty((m, nn), dtype=torch.bfloat16, device=a.device)
     assert out.is_contiguous() and out.shape == (m, nn)
-    bn = block_n or pick_block_n(m, nn)
     s = (stream or torch.cuda.current_stream()).cuda_stream
+    if two_sm is None:
+        two_sm = block_n == 0 and nn % 256 == 0 and ((m + 255) // 256) * (nn // 256) >= 74
+    if two_sm:
+        n.gemm_bf16_two_sm(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, nn, k, nn, num_ctas, 0, s)
+        return out
+    bn = block_n or pick_block_n(m, nn)
     n.gemm_bf16(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, nn, k, nn, bn, num_ctas, 0, s)
     return out
