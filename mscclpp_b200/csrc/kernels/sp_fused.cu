@@ -15,6 +15,7 @@
 
 #include <mscclpp/gpu_data_types.hpp>
 
+#include "gemm2_sm100.cuh"
 #include "gemm_sm100.cuh"
 
 namespace mscclpp {
@@ -198,19 +199,35 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
     StoreAct<kAct> epi{reinterpret_cast<bf16*>(c.peerBase[rank] + dOff), a.shape.N, a.shape.M};
     gemm::Shape shape = a.shape;
     shape.mOrder = 2;
-    shape.mOrderParam = rank * per;
-    gemm::gemmCta<kBlockN>(&maps.aFull[blockIdx.y], &maps.b[blockIdx.y], shape, blockIdx.x, a.numGemmCtas, gate, epi, c.status,
-                           c.timeoutNs, smemRaw);
+    if constexpr (kBlockN == 0) {
+      shape.mOrderParam = rank * per / 2;  // the pair core orders 256-row blocks
+      gemm::gemmCtaPair(&maps.aFull[blockIdx.y], &maps.b[blockIdx.y], shape, blockIdx.x / 2, a.numGemmCtas / 2, gate, epi, c.status,
+                        c.timeoutNs, smemRaw);
+    } else {
+      shape.mOrderParam = rank * per;
+      gemm::gemmCta<kBlockN>(&maps.aFull[blockIdx.y], &maps.b[blockIdx.y], shape, blockIdx.x, a.numGemmCtas, gate, epi, c.status,
+                             c.timeoutNs, smemRaw);
+    }
   } else {
     copierCta(a, rank, epoch, blockIdx.x - a.numGemmCtas, gridDim.x - a.numGemmCtas, smemRaw);
   }
   finishLaunch(c, rank, epoch);
 }
 
+template <int kBlockN>
+struct SmemOf {
+  static constexpr int kSmemBytes = gemm::Config<kBlockN>::kSmemBytes;
+};
+template <>
+struct SmemOf<0> {
+  static constexpr int kSmemBytes = gemm::Config2::kSmemBytes;
+};
+
+// kBlockN == 0 selects the two-SM GEMM core (256 x 256 tiles on CTA pairs, clusters of two CTAs).
 template <int kBlockN, int kAct>
 cudaError_t launchTyped(const AgTmaps& maps, const AgGemmArgs& args, int grid, cudaStream_t stream) {
-  using Cfg = gemm::Config<kBlockN>;
-  static_assert(Cfg::kSmemBytes >= kRingStages * static_cast<int>(kPieceBytes) + 128 || kBlockN != 256, "ring must fit");
+  using Cfg = SmemOf<kBlockN>;
+  static_assert(Cfg::kSmemBytes >= kRingStages * static_cast<int>(kPieceBytes) + 128, "ring must fit");
   auto kernel = agGemmKernel<kBlockN, kAct>;
   static bool attrSet = false;
   if (!attrSet) {
@@ -224,6 +241,9 @@ cudaError_t launchTyped(const AgTmaps& maps, const AgGemmArgs& args, int grid, c
   AgTmaps m = maps;
   AgGemmArgs a = args;
   void* params[] = {&m, &a};
+  if constexpr (kBlockN == 0) {
+    return gemm::launchClusterPair(reinterpret_cast<const void*>(kernel), g, b, Cfg::kSmemBytes, params, true, stream);
+  }
   return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), g, b, params, Cfg::kSmemBytes, stream);
 }
 
@@ -248,12 +268,15 @@ cudaError_t launchAllGatherGemm(const AgGemmArgs& argsIn, const void* const* B, 
   const int M = args.shape.M, N = args.shape.N, K = args.shape.K;
   const int world = args.comm.world;
   if (M <= 0 || world < 1 || world > 8 || M % (world * gemm::kBlockM) != 0) return cudaErrorInvalidValue;
-  if (N % args.blockN != 0 || K % 128 != 0) return cudaErrorInvalidValue;
+  const bool twoSm = args.blockN == 0;  // block_n 0 = 256 x 256 tiles on SM pairs
+  const int tileN = twoSm ? gemm::Config2::kBlockN : args.blockN;
+  if (N % tileN != 0 || K % 128 != 0) return cudaErrorInvalidValue;
+  if (twoSm && M % (world * gemm::Config2::kPairM) != 0) return cudaErrorInvalidValue;
   if ((static_cast<uint64_t>(gemm::kBlockM) * K * 2) % kPieceBytes != 0) return cudaErrorInvalidValue;
   const int numMBlk = M / gemm::kBlockM;
   if (numMBlk > kAgMaxMBlk) return cudaErrorInvalidValue;
   // the copy ring lives in the GEMM's dynamic shared memory: only the two larger tile configurations have room
-  if (args.blockN != 256 && args.blockN != 128) return cudaErrorInvalidValue;
+  if (args.blockN != 256 && args.blockN != 128 && !twoSm) return cudaErrorInvalidValue;
   const int emu = args.emuRanks > 1 ? args.emuRanks : 1;
   if (emu > 8 || (emu > 1 && emu != world)) return cudaErrorInvalidValue;
   args.shape.aBoxRows = gemm::kBlockM;
@@ -270,18 +293,24 @@ cudaError_t launchAllGatherGemm(const AgGemmArgs& argsIn, const void* const* B, 
     err = gemm::makeTensorMapBf16(&maps.aFull[e], reinterpret_cast<const void*>(heap + aFullOff), M, K, static_cast<uint64_t>(K) * 2,
                                   gemm::kBlockM);
     if (err != cudaSuccess) return err;
-    err = gemm::makeTensorMapBf16(&maps.b[e], B[e], N, K, static_cast<uint64_t>(K) * 2, args.blockN);
+    err = gemm::makeTensorMapBf16(&maps.b[e], B[e], N, K, static_cast<uint64_t>(K) * 2, twoSm ? tileN / 2 : tileN);
     if (err != cudaSuccess) return err;
   }
-  const int tiles = numMBlk * (N / args.blockN);
+  const int tiles = numMBlk * (N / tileN);
   const int sms = gemm::smCount() / emu;
   if (numCopiers <= 0) numCopiers = world == 1 ? 1 : (sms >= 64 ? 12 : 2);
   if (numCopiers > kBarrierSlots) numCopiers = kBarrierSlots;
   int gemmCtas = args.numGemmCtas > 0 ? args.numGemmCtas : sms - numCopiers;
   if (gemmCtas > tiles) gemmCtas = tiles;
   if (gemmCtas < 1) gemmCtas = 1;
+  if (twoSm) {
+    gemmCtas &= ~1;
+    if (gemmCtas < 2) gemmCtas = 2;
+    numCopiers = (numCopiers + 1) & ~1;
+  }
   args.numGemmCtas = gemmCtas;
   const int grid = gemmCtas + numCopiers;
+  if (twoSm) return launchAct<0>(maps, args, grid, stream);
   if (args.blockN == 256) return launchAct<256>(maps, args, grid, stream);
   return launchAct<128>(maps, args, grid, stream);
 }

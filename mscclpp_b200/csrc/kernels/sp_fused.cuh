@@ -17,7 +17,7 @@ struct AgGemmArgs {
   const __nv_bfloat16* aLocal;  // symmetric [M / world, K]: this rank's rows (global rows rank * M / world ...)
   __nv_bfloat16* aFull;       // symmetric [M, K] workspace; peers' rows land here (own rows are read from aLocal)
   __nv_bfloat16* D;           // symmetric [M, N] output
-  int blockN;                 // 64, 128 or 256
+  int blockN;                 // 128 or 256; 0 = 256 x 256 tiles on pairs of SMs (M % (world * 256) == 0)
   int numGemmCtas;            // 0 = all SMs but the copiers
   int activation;             // 0 none, 1 GELU (tanh form), 2 SiLU - applied to the fp32 accumulator
   int emuRanks;               // > 1: emulated ranks in one cooperative launch (tests)

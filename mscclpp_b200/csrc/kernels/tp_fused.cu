@@ -26,6 +26,7 @@
 
 #include <mscclpp/gpu_data_types.hpp>
 
+#include "gemm2_sm100.cuh"
 #include "gemm_sm100.cuh"
 
 namespace mscclpp {
@@ -347,6 +348,7 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
   if (allOk) rankBarrier(c, rank, 2, reducerIdx, epoch);
 }
 
+// kBlockN == 0 selects the two-SM GEMM core (256 x 256 tiles on CTA pairs; the launch uses clusters of two).
 template <int kBlockN, bool kNvls>
 __global__ void __launch_bounds__(gemm::kNumThreads, 1)
     tpFusedKernel(const __grid_constant__ TmapSet maps, const __grid_constant__ TpFusedArgs a) {
@@ -358,10 +360,16 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
     gemm::NoGate gate;
     const uint64_t partialOff = reinterpret_cast<uint64_t>(a.partial) - c.peerBase[c.rank];
     const int numUnits = (a.shape.M + a.rowsPerUnit - 1) / a.rowsPerUnit;
+    constexpr int kTileN = kBlockN == 0 ? gemm::Config2::kBlockN : kBlockN;
     PartialStoreSignal epi{&c, reinterpret_cast<bf16*>(c.peerBase[rank] + partialOff), a.shape.M, a.shape.N, rank,
-                           a.rowsPerUnit, numUnits, a.shape.N / kBlockN, epoch};
-    gemm::gemmCta<kBlockN>(&maps.a[blockIdx.y], &maps.b[blockIdx.y], a.shape, blockIdx.x, a.numGemmCtas, gate, epi,
-                           c.status, c.timeoutNs, smemRaw);
+                           a.rowsPerUnit, numUnits, a.shape.N / kTileN, epoch};
+    if constexpr (kBlockN == 0) {
+      gemm::gemmCtaPair(&maps.a[blockIdx.y], &maps.b[blockIdx.y], a.shape, blockIdx.x / 2, a.numGemmCtas / 2, gate, epi, c.status,
+                        c.timeoutNs, smemRaw);
+    } else {
+      gemm::gemmCta<kBlockN>(&maps.a[blockIdx.y], &maps.b[blockIdx.y], a.shape, blockIdx.x, a.numGemmCtas, gate, epi,
+                             c.status, c.timeoutNs, smemRaw);
+    }
   } else {
     reducerCta<kNvls>(a, rank, epoch, blockIdx.x - a.numGemmCtas, gridDim.x - a.numGemmCtas);
   }
@@ -393,8 +401,17 @@ __global__ void __launch_bounds__(512) tpScaleRowsKernel(const bf16* h, const fl
 }
 
 template <int kBlockN>
+struct SmemOf {
+  static constexpr int kSmemBytes = gemm::Config<kBlockN>::kSmemBytes;
+};
+template <>
+struct SmemOf<0> {
+  static constexpr int kSmemBytes = gemm::Config2::kSmemBytes;
+};
+
+template <int kBlockN>
 cudaError_t launchTyped(const TmapSet& maps, const TpFusedArgs& args, int grid, cudaStream_t stream) {
-  using Cfg = gemm::Config<kBlockN>;
+  using Cfg = SmemOf<kBlockN>;
   auto kernelNvls = tpFusedKernel<kBlockN, true>;
   auto kernelP2p = tpFusedKernel<kBlockN, false>;
   static bool attrSet = false;
@@ -407,6 +424,12 @@ cudaError_t launchTyped(const TmapSet& maps, const TpFusedArgs& args, int grid, 
   dim3 g(grid, args.emuRanks > 1 ? args.emuRanks : 1, 1);
   dim3 b(gemm::kNumThreads, 1, 1);
   auto kernel = args.nvls ? kernelNvls : kernelP2p;
+  if constexpr (kBlockN == 0) {
+    TmapSet m = maps;
+    TpFusedArgs a = args;
+    void* params[] = {&m, &a};
+    return gemm::launchClusterPair(reinterpret_cast<const void*>(kernel), g, b, Cfg::kSmemBytes, params, args.emuRanks > 1, stream);
+  }
   if (args.emuRanks > 1) {
     TmapSet m = maps;
     TpFusedArgs a = args;
@@ -424,8 +447,11 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   TpFusedArgs args = argsIn;
   const int M = args.shape.M, N = args.shape.N, K = args.shape.K;
   const int world = args.comm.world;
-  if (M <= 0 || N % args.blockN != 0 || K % gemm::kBlockK != 0) return cudaErrorInvalidValue;
-  if (N / args.blockN > kMaxNBlk || world > 8) return cudaErrorInvalidValue;
+  const bool twoSm = args.blockN == 0;  // block_n 0 = 256 x 256 tiles on SM pairs
+  const int tileN = twoSm ? gemm::Config2::kBlockN : args.blockN;
+  if (M <= 0 || N % tileN != 0 || K % gemm::kBlockK != 0) return cudaErrorInvalidValue;
+  if (twoSm && M < gemm::Config2::kPairM) return cudaErrorInvalidValue;
+  if (N / tileN > kMaxNBlk || world > 8) return cudaErrorInvalidValue;
   if (N * 2 / 16 > kWordsPerThread * kGroupThreads) return cudaErrorInvalidValue;
   const int numMBlk = (M + gemm::kBlockM - 1) / gemm::kBlockM;
   if (numMBlk > kMaxMBlk) return cudaErrorInvalidValue;
@@ -439,7 +465,7 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   if (args.mode == 2) {
     // reduce-scatter: rank r owns rows [r * M / world, (r + 1) * M / world); the GEMM visits the row blocks
     // interleaved over the owners so that every owner's reducers have a finished block per round
-    if (M % (world * gemm::kBlockM) != 0) return cudaErrorInvalidValue;
+    if (M % (world * (twoSm ? gemm::Config2::kPairM : gemm::kBlockM)) != 0) return cudaErrorInvalidValue;
     args.rowsPerUnit = M / world;
     args.shape.mOrder = 1;
     args.shape.mOrderParam = world;
@@ -453,19 +479,27 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   for (int e = 0; e < emu; e++) {
     cudaError_t err = gemm::makeTensorMapBf16(&maps.a[e], A[e], M, K, static_cast<uint64_t>(K) * 2, args.shape.aBoxRows);
     if (err != cudaSuccess) return err;
-    err = gemm::makeTensorMapBf16(&maps.b[e], B[e], N, K, static_cast<uint64_t>(K) * 2, args.blockN);
+    err = gemm::makeTensorMapBf16(&maps.b[e], B[e], N, K, static_cast<uint64_t>(K) * 2, twoSm ? tileN / 2 : tileN);
     if (err != cudaSuccess) return err;
   }
-  const int tiles = numMBlk * (N / args.blockN);
+  const int tiles = twoSm ? 2 * ((M + gemm::Config2::kPairM - 1) / gemm::Config2::kPairM) * (N / tileN) : numMBlk * (N / tileN);
   int sms = gemm::smCount() / emu;
   if (numReducers <= 0) numReducers = sms >= 64 ? 24 : 2;
   if (numReducers > kBarrierSlots) numReducers = kBarrierSlots;
   int gemmCtas = args.numGemmCtas > 0 ? args.numGemmCtas : sms - numReducers;
   if (gemmCtas > tiles) gemmCtas = tiles;
   if (gemmCtas < 1) gemmCtas = 1;
+  if (twoSm) {
+    // CTA pairs: an even number of GEMM CTAs and of reducers, so that clusters never straddle the two roles
+    gemmCtas &= ~1;
+    if (gemmCtas < 2) gemmCtas = 2;
+    numReducers = (numReducers + 1) & ~1;
+  }
   args.numGemmCtas = gemmCtas;
   const int grid = gemmCtas + numReducers;
   switch (args.blockN) {
+    case 0:
+      return launchTyped<0>(maps, args, grid, stream);
     case 64:
       return launchTyped<64>(maps, args, grid, stream);
     case 128:

@@ -21,7 +21,7 @@ struct TpFusedArgs {
   const __nv_bfloat16* gamma;   // [N] local (may be null)
   float* rinv;                  // symmetric [M] fp32, mode 1 only
   float eps;
-  int blockN;                   // GEMM N tile: 64, 128 or 256
+  int blockN;                   // GEMM N tile: 64, 128 or 256; 0 = 256 x 256 tiles on pairs of SMs (M >= 256, N % 256 == 0)
   int numGemmCtas;              // 0 = all SMs but the reducers
   int rowsPerUnit;              // ownership granule, power of two <= 128; 0 = pick from M and world
   int mode;                     // 0: owners broadcast out + residualOut; 1: owners broadcast residualOut + rinv;

@@ -21,7 +21,7 @@ ACTIVATIONS = {"none": 0, "gelu": 1, "silu": 2}
 
 
 def all_gather_gemm(symm: SymmetricMemory, a_local: torch.Tensor, a_full: torch.Tensor, weight, out: torch.Tensor,
-                    activation: str = "none", block_n: int = 256, num_copiers: int = 0, num_gemm_ctas: int = 0,
+                    activation: str = "none", block_n: int = -1, num_copiers: int = 0, num_gemm_ctas: int = 0,
                     stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """out[S, N] = act(concat_r(a_local_r) @ weight^T). `a_local` [S/tp, K], `a_full` [S, K] workspace and `out` are
     symmetric-heap tensors; `weight` [N, K] is local (a list with one weight per rank for emulated heaps)."""
@@ -30,6 +30,8 @@ def all_gather_gemm(symm: SymmetricMemory, a_local: torch.Tensor, a_full: torch.
     weights = weight if isinstance(weight, (list, tuple)) else [weight]
     n_cols = weights[0].shape[0]
     assert a_local.shape == (s_rows // symm.world, k) and out.shape == (s_rows, n_cols)
+    if block_n < 0:  # 0 = two-SM tiles (256 x 256 on SM pairs) when the shape allows, else one-SM 256- or 128-wide tiles
+        block_n = 0 if (s_rows % (symm.world * 256) == 0 and n_cols % 256 == 0) else (256 if n_cols % 256 == 0 else 128)
     assert all(w.shape == (n_cols, k) and w.is_contiguous() and w.dtype == torch.bfloat16 for w in weights)
     st = (stream or torch.cuda.current_stream()).cuda_stream
     n.all_gather_gemm(symm.heap, a_local.data_ptr(), a_full.data_ptr(), [w.data_ptr() for w in weights], out.data_ptr(), s_rows, n_cols, k,
@@ -38,7 +40,7 @@ def all_gather_gemm(symm: SymmetricMemory, a_local: torch.Tensor, a_full: torch.
 
 
 def gemm_reduce_scatter(symm: SymmetricMemory, a, weight, partial: torch.Tensor, out: torch.Tensor, nvls: Optional[bool] = None,
-                        block_n: int = 256, num_reducers: int = 0, num_gemm_ctas: int = 0,
+                        block_n: int = -1, num_reducers: int = 0, num_gemm_ctas: int = 0,
                         stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """out_r[S/tp, N] = rows of sum_r(a_r @ weight_r^T) that rank r owns. `partial` [S, N] and `out` [S/tp, N] are
     symmetric-heap tensors; `a` [S, K] and `weight` [N, K] are local (lists with one entry per rank for emulated heaps)."""
@@ -48,6 +50,8 @@ def gemm_reduce_scatter(symm: SymmetricMemory, a, weight, partial: torch.Tensor,
     s_rows, k = a_list[0].shape
     n_cols = w_list[0].shape[0]
     assert partial.shape == (s_rows, n_cols) and out.shape == (s_rows // symm.world, n_cols)
+    if block_n < 0:
+        block_n = 0 if (s_rows % (symm.world * 256) == 0 and n_cols % 256 == 0) else (256 if n_cols % 256 == 0 else 128)
     nvls = symm.nvls if nvls is None else nvls
     st = (stream or torch.cuda.current_stream()).cuda_stream
     n.tp_fused(symm.heap, [x.data_ptr() for x in a_list], [w.data_ptr() for w in w_list], partial.data_ptr(), 0, 0, out.data_ptr(), 0, 0,

@@ -64,7 +64,8 @@ class RowParallelLinearNorm:
                       emulated_inputs=None) -> Tuple[torch.Tensor, torch.Tensor]:
         """Same result as forward(), in ONE kernel: GEMM tiles, cross-rank reduction, residual add and norm
         overlap tile by tile. mode 1 halves NVLink traffic by broadcasting h and 1/rms only and finishing
-        `out` with a local pass (second, local-only launch).
+        `out` with a local pass (second, local-only launch). block_n: N tile of the one-SM GEMM core (64/128/256), -1
+        forces the two-SM core (256 x 256 tiles on SM pairs), 0 picks (two-SM from 1024 tokens on).
 
         emulated_inputs: for emulated heaps, [(x_r, weight_r)] for every emulated rank."""
         from .._core import native
@@ -75,7 +76,10 @@ class RowParallelLinearNorm:
         if residual is not None:
             self.residual_in[:t].copy_(residual)
         nvls = self.symm.nvls if nvls is None else nvls
-        bn = block_n or pick_block_n(t, self.out_features)
+        if block_n < 0 or (block_n == 0 and t >= 1024 and self.out_features % 256 == 0):
+            bn = 0  # 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2)
+        else:
+            bn = block_n or pick_block_n(t, self.out_features)
         s = (stream or torch.cuda.current_stream()).cuda_stream
         if emulated_inputs is not None:
             a_ptrs = [xi.data_ptr() for xi, _ in emulated_inputs]

@@ -403,3 +403,79 @@ def test_moe_dispatch_reports_small_receive_buffer():
     assert int(symm.rank_view(disp.slot_map, 0).max()) == -1
     symm.heap.reset_status()
     symm.destroy()
+
+
+@pytest.mark.parametrize("world,rows_per_rank", [(2, 256), (4, 512)])
+def test_two_sm_core_in_fused_kernels(world, rows_per_rank):
+    """The fused kernels on the two-SM GEMM core (256 x 256 tiles on CTA pairs, clusters of two): all-gather -> GEMM,
+    GEMM -> reduce-scatter and the fused TP layer, all ranks emulated on one GPU."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.sp_layer import all_gather_gemm, gemm_reduce_scatter
+    from mscclpp_b200.parallel.tp_layer import RowParallelLinearNorm
+
+    symm = SymmetricMemory.emulated(world, nbytes=256 << 20, timeout_ms=3000)
+    s_rows, k, n_cols = world * rows_per_rank, 256, 512
+    g = torch.Generator(device="cuda").manual_seed(world + rows_per_rank)
+    ctas = max(2, (24 // world) & ~1)
+    # all-gather -> GEMM
+    a_local = symm.tensor((rows_per_rank, k), torch.bfloat16)
+    a_full = symm.tensor((s_rows, k), torch.bfloat16)
+    out = symm.tensor((s_rows, n_cols), torch.bfloat16)
+    ws = [(torch.randn((n_cols, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(world)]
+    shards = [torch.randn((rows_per_rank, k), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    for rep in range(2):
+        for r in range(world):
+            symm.rank_view(a_local, r).copy_(shards[r])
+            symm.rank_view(out, r).zero_()
+        all_gather_gemm(symm, a_local, a_full, ws, out, block_n=0, num_copiers=2, num_gemm_ctas=ctas)
+        torch.cuda.synchronize()
+        symm.check()
+    full = torch.cat(shards).float()
+    for r in range(world):
+        ref = full @ ws[r].float().t()
+        assert (symm.rank_view(out, r).float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 0.02
+    # GEMM -> reduce-scatter
+    partial = symm.tensor((s_rows, n_cols), torch.bfloat16)
+    out_rs = symm.tensor((rows_per_rank, n_cols), torch.bfloat16)
+    xs = [torch.randn((s_rows, k), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    for rep in range(2):
+        gemm_reduce_scatter(symm, xs, ws, partial, out_rs, nvls=False, block_n=0, num_reducers=2, num_gemm_ctas=ctas)
+        torch.cuda.synchronize()
+        symm.check()
+    total = sum((x.float() @ w.float().t()).to(torch.bfloat16).float() for x, w in zip(xs, ws))
+    for r in range(world):
+        ref = total[r * rows_per_rank:(r + 1) * rows_per_rank]
+        assert (symm.rank_view(out_rs, r).float() - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 0.05
+    # fused TP layer (GEMM + allreduce + residual + RMSNorm)
+    tokens = 512
+    layer = RowParallelLinearNorm(symm, out_features=n_cols, k_shard=k, max_tokens=tokens)
+    xt = [torch.randn((tokens, k), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    residual = torch.randn((tokens, n_cols), generator=g, device="cuda").to(torch.bfloat16)
+    for r in range(world):
+        symm.rank_view(layer.residual_in, r)[:tokens].copy_(residual)
+        symm.rank_view(layer.gamma, r).fill_(1.0)
+    for mode in (0, 1):
+        for rep in range(2):
+            layer.forward_fused(xt[0], mode=mode, nvls=False, block_n=-1, num_reducers=2, num_gemm_ctas=ctas, emulated_inputs=list(zip(xt, ws)))
+            torch.cuda.synchronize()
+            symm.check()
+        acc = sum((x.float() @ w.float().t()).to(torch.bfloat16).float() for x, w in zip(xt, ws))
+        h = (acc.to(torch.bfloat16).float() + residual.float()).to(torch.bfloat16).float()
+        y = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + layer.eps)).to(torch.bfloat16).float()
+        for r in range(world):
+            assert (symm.rank_view(layer.residual_out, r)[:tokens].float() - h).abs().max().item() <= 0.02 * h.abs().max().item() + 0.05
+            assert (symm.rank_view(layer.out, r)[:tokens].float() - y).abs().max().item() <= 0.1
+    symm.destroy()
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (777, 512, 256), (2048, 1024, 512)])
+def test_two_sm_gemm(m, n, k):
+    from mscclpp_b200.ops.gemm import gemm_bf16
+
+    g = torch.Generator(device="cuda").manual_seed(m + n + k)
+    a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn((n, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16)
+    d = gemm_bf16(a, w, two_sm=True)
+    torch.cuda.synchronize()
+    ref = a.float() @ w.float().t()
+    assert (d.float() - ref).abs().max().item() <= 0.01 * ref.abs().max().item() + 0.01
