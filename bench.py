@@ -120,6 +120,7 @@ def main():
 
     from mscclpp_b200 import SymmetricMemory
     from mscclpp_b200.ops import all_reduce
+    from mscclpp_b200.ops.gemm import pick_block_n
     from mscclpp_b200.parallel.tp_layer import RowParallelLinearNorm
 
     rank = int(os.environ.get("RANK", "0"))
@@ -173,19 +174,23 @@ def main():
         return max_over_ranks(start.elapsed_time(end) / steps)  # ms per step
 
     # ------------------------------------------------------------------ pick the fused variant (untimed)
-    def fused(t, mode, nvls, reducers):
+    # variant = (mode, nvls, reducer CTAs, GEMM core): core 1 = one-SM tiles, 2 = 256 x 256 tiles on SM pairs (cta_group::2)
+    def fused(t, mode, nvls, reducers, core=1):
         if mode < 0:  # two launches: tcgen05 GEMM, then the fused allreduce + residual + RMSNorm kernel
             return lambda: layer.forward(xs[t])
-        return lambda: layer.forward_fused(xs[t], mode=mode, nvls=nvls, num_reducers=reducers)
+        bn = -1 if core == 2 else pick_block_n(t, HIDDEN)
+        return lambda: layer.forward_fused(xs[t], mode=mode, nvls=nvls, num_reducers=reducers, block_n=bn)
 
     nvls_opts = [True] if symm.nvls else [False]
-    variants = [(m, nv, r) for m in (0, 1) for nv in nvls_opts for r in (24, 48)] + [(-1, symm.nvls, 0)]
+    variants = [(m, nv, r, c) for m in (0, 1) for nv in nvls_opts for r in (24, 48) for c in (1, 2)] + [(-1, symm.nvls, 0, 1)]
     if world == 1:
-        variants = [(0, False, 64), (1, False, 64), (-1, False, 0)]
+        variants = [(0, False, 64, 1), (1, False, 64, 1), (0, False, 64, 2), (1, False, 64, 2), (-1, False, 0, 1)]
     best = {}
     for t in TOKEN_SIZES:
         scores = {}
         for v in variants:
+            if v[3] == 2 and t < 256:
+                continue
             scores[v] = time_steps(fused(t, *v), 5, 3)
         best[t] = min(scores, key=scores.get)
 
@@ -194,8 +199,8 @@ def main():
                            int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
     if rank == 0:
         sampler.start()
-    head_mode, head_nvls, head_reducers = best[HEADLINE_T]
-    head_fn = fused(HEADLINE_T, head_mode, head_nvls, head_reducers)
+    head_mode, head_nvls, head_reducers, head_core = best[HEADLINE_T]
+    head_fn = fused(HEADLINE_T, head_mode, head_nvls, head_reducers, head_core)
     ms_per_step = time_steps(head_fn, args.steps, max(args.warmup, 3))
     launches = args.steps * (1 if head_mode == 0 else 2)  # mode 1 and the two-launch path (-1) use two kernels
 
@@ -217,7 +222,8 @@ def main():
                     if best[t][0] < 0:
                         layer.forward(xs[t], stream=side)
                     else:
-                        layer.forward_fused(xs[t], mode=best[t][0], nvls=best[t][1], num_reducers=best[t][2], stream=side)
+                        layer.forward_fused(xs[t], mode=best[t][0], nvls=best[t][1], num_reducers=best[t][2], stream=side,
+                                            block_n=-1 if best[t][3] == 2 else pick_block_n(t, HIDDEN))
         barrier()
         tp_graph_us[str(t)] = round(time_steps(graph.replay, 5, 2) * 1e3 / reps, 2)
         # two-kernel path of this library (GEMM, then allreduce+residual+norm)
@@ -245,7 +251,8 @@ def main():
         if head_mode < 0:
             out, _ = layer.forward(x_dev)
         else:
-            out, _ = layer.forward_fused(x_dev, mode=head_mode, nvls=head_nvls, num_reducers=head_reducers)
+            out, _ = layer.forward_fused(x_dev, mode=head_mode, nvls=head_nvls, num_reducers=head_reducers,
+                                         block_n=-1 if head_core == 2 else pick_block_n(HEADLINE_T, HIDDEN))
         result_host.copy_(out[:, :8].float().abs().mean().reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller looks at the metric every step
 
@@ -316,6 +323,7 @@ def main():
             "tokens_per_s": round(HEADLINE_T / (ms_per_step * 1e-3), 1),
             "aggregate_tflops": round(flops / (ms_per_step * 1e-3) / 1e12, 1),
             "variant": {"mode": head_mode, "nvls": head_nvls, "reducer_ctas": head_reducers,
+                        "gemm_core": "two-SM 256x256 (cta_group::2)" if head_core == 2 else "one-SM 128x256",
                         "kernel": ("gemmBf16Kernel (tcgen05) then twoShot/LL allreduce+residual+RMSNorm kernel" if head_mode < 0 else
                                    "tpFusedKernel (tcgen05 GEMM + multimem/peer reduce + residual + RMSNorm in one launch)" +
                                    ("" if head_mode == 0 else " + local scale pass")),

@@ -52,7 +52,7 @@ class RowParallelLinearNorm:
         partial = self.partial[:t]
         if residual is not None:
             self.residual_in[:t].copy_(residual)
-        gemm_bf16(x, self.weight, partial, block_n=pick_block_n(t, self.out_features), stream=stream)
+        gemm_bf16(x, self.weight, partial, stream=stream)  # two-SM tiles when the problem fills the GPU, else one-SM
         out, res_out = self.out[:t], self.residual_out[:t]
         all_reduce_rmsnorm(self.symm, partial, out, self.residual_in[:t], res_out, self.gamma, eps=self.eps, algo=algo,
                            stream=stream)
