@@ -191,7 +191,7 @@ def main():
         for v in variants:
             if v[3] == 2 and t < 256:
                 continue
-            scores[v] = time_steps(fused(t, *v), 5, 3)
+            scores[v] = time_steps(fused(t, *v), 5 if t >= 8192 else 20, 3)
         best[t] = min(scores, key=scores.get)
 
     # ------------------------------------------------------------------ headline: fused TP layer at T = 8192

@@ -77,13 +77,17 @@ def _link(objs: list[Path], out: Path, extra: list[str], verbose: bool) -> None:
     newest = max(o.stat().st_mtime for o in objs)
     if out.exists() and out.stat().st_mtime >= newest:
         return
-    cmd = [_nvcc(), "-shared", "-o", str(out)] + [str(o) for o in objs] + ARCH_FLAGS + [
+    # link into a temporary name and rename: a reader (an importing process, a snapshot) never sees a partial library
+    tmp = out.with_name(out.name + f".tmp.{os.getpid()}")
+    cmd = [_nvcc(), "-shared", "-o", str(tmp)] + [str(o) for o in objs] + ARCH_FLAGS + [
         "-cudart", "static", "-Xlinker", "-rpath,$ORIGIN", "-lpthread", "-ldl", "-lrt"] + extra
     if verbose:
         print(f"[link] {out.relative_to(ROOT)}", flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
+        tmp.unlink(missing_ok=True)
         raise RuntimeError(f"link failed: {' '.join(cmd)}\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, out)
 
 
 def native_module_path() -> Path:

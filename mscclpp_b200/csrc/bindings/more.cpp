@@ -108,6 +108,30 @@ void registerMoreBindings(py::module_& m) {
       py::arg("heap"), py::arg("a_local"), py::arg("a_full"), py::arg("b"), py::arg("d"), py::arg("m"), py::arg("n"), py::arg("k"),
       py::arg("block_n") = 256, py::arg("num_gemm_ctas") = 0, py::arg("num_copiers") = 0, py::arg("activation") = 0,
       py::arg("stream") = 0);
+  m.def(
+      "tp_reduce_norm",
+      [](SymmetricHeap& heap, uintptr_t partial, uintptr_t residualIn, uintptr_t residualOut, uintptr_t out, uintptr_t gamma, uintptr_t rinv,
+         int M, int N, float eps, int numCtas, int rowsPerUnit, int mode, bool nvls, uintptr_t stream) {
+        TpFusedArgs args{};
+        args.comm = heap.deviceComm();
+        args.shape.M = M;
+        args.shape.N = N;
+        args.partial = reinterpret_cast<__nv_bfloat16*>(partial);
+        args.residualIn = reinterpret_cast<const __nv_bfloat16*>(residualIn);
+        args.residualOut = reinterpret_cast<__nv_bfloat16*>(residualOut);
+        args.out = reinterpret_cast<__nv_bfloat16*>(out);
+        args.gamma = reinterpret_cast<const __nv_bfloat16*>(gamma);
+        args.rinv = reinterpret_cast<float*>(rinv);
+        args.eps = eps;
+        args.rowsPerUnit = rowsPerUnit;
+        args.mode = mode;
+        args.nvls = nvls ? 1 : 0;
+        args.emuRanks = heap.emulated() ? heap.world() : 1;
+        checkCudaMore(launchTpReduceNorm(args, numCtas, reinterpret_cast<cudaStream_t>(stream)), "tp_reduce_norm");
+      },
+      py::arg("heap"), py::arg("partial"), py::arg("residual_in"), py::arg("residual_out"), py::arg("out"), py::arg("gamma"), py::arg("rinv"),
+      py::arg("m"), py::arg("n"), py::arg("eps"), py::arg("num_ctas") = 0, py::arg("rows_per_unit") = 0, py::arg("mode") = 0,
+      py::arg("nvls") = false, py::arg("stream") = 0);
   m.def("moe_workspace_bytes", [] { return moeWorkspaceBytes(); });
   m.def(
       "moe_dispatch",

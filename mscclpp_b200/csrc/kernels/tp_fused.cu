@@ -179,7 +179,7 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
     if (row >= M) continue;
     // ---- wait until every rank has produced every tile of the row block this row lives in
     const int mb = row / gemm::kBlockM;
-    if (mb != readyMb) {
+    if (mb != readyMb && !a.noFlags) {
       // Every decision below is taken by lane 0 and read by the group after a barrier, so all 64
       // threads always agree on which barriers they execute.
       for (;;) {
@@ -376,6 +376,16 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
   finishLaunch(c, rank, epoch);
 }
 
+template <bool kNvls>
+__global__ void __launch_bounds__(gemm::kNumThreads, 1) tpReduceNormKernel(const __grid_constant__ TpFusedArgs a) {
+  const DeviceComm& c = a.comm;
+  const int rank = deviceRank(c);
+  const uint32_t epoch = launchEpoch(c, rank);
+  // every rank's partial product is final once its kernel runs
+  if (rankBarrier(c, rank, 0, blockIdx.x, epoch)) reducerCta<kNvls>(a, rank, epoch, blockIdx.x, gridDim.x);
+  finishLaunch(c, rank, epoch);
+}
+
 // out[row] = h[row] * rinv[row] * gamma (local pass of mode 1)
 __global__ void __launch_bounds__(512) tpScaleRowsKernel(const bf16* h, const float* rinv, const bf16* gamma, bf16* out,
                                                          int M, int N) {
@@ -509,6 +519,36 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
     default:
       return cudaErrorInvalidValue;
   }
+}
+
+cudaError_t launchTpReduceNorm(const TpFusedArgs& argsIn, int numCtas, cudaStream_t stream) {
+  TpFusedArgs args = argsIn;
+  const int M = args.shape.M, N = args.shape.N;
+  const int world = args.comm.world;
+  if (M <= 0 || N % 8 != 0 || N * 2 / 16 > kWordsPerThread * kGroupThreads || world > 8) return cudaErrorInvalidValue;
+  if (args.mode != 0 && args.mode != 1) return cudaErrorInvalidValue;
+  if (args.mode == 1 && args.rinv == nullptr) return cudaErrorInvalidValue;
+  if (args.nvls && args.comm.mcBase == 0) return cudaErrorInvalidValue;
+  const int emu = args.emuRanks > 1 ? args.emuRanks : 1;
+  if (emu > 8) return cudaErrorInvalidValue;
+  if (args.rowsPerUnit <= 0) {
+    int rpu = 64;  // smaller units than the fused kernel's: nothing ties ownership to GEMM row blocks here
+    while (rpu > 1 && M < rpu * world) rpu >>= 1;
+    args.rowsPerUnit = rpu;
+  }
+  args.noFlags = 1;
+  args.numGemmCtas = 0;
+  const int sms = gemm::smCount() / emu;
+  if (numCtas <= 0) numCtas = sms < 128 ? sms : 128;
+  if (numCtas > kBarrierSlots) numCtas = kBarrierSlots;
+  dim3 g(numCtas, emu, 1), b(gemm::kNumThreads, 1, 1);
+  auto kernel = args.nvls ? tpReduceNormKernel<true> : tpReduceNormKernel<false>;
+  if (emu > 1) {
+    void* params[] = {&args};
+    return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), g, b, params, 0, stream);
+  }
+  kernel<<<g, b, 0, stream>>>(args);
+  return cudaGetLastError();
 }
 
 cudaError_t launchTpScaleRows(const void* h, const float* rinv, const void* gamma, void* out, int M, int N,

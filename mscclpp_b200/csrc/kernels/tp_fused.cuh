@@ -28,12 +28,17 @@ struct TpFusedArgs {
                                 // 2: reduce-scatter, out is this rank's [M / world, N] block (M % (world * 128) == 0)
   int nvls;                     // multimem through comm.mcBase instead of peer loads/stores
   int emuRanks;                 // > 1: that many emulated ranks in one cooperative launch (tests)
+  int noFlags;                  // set by launchTpReduceNorm: rows are complete at kernel start, no per-block flags
 };
 
 // A[e], B[e]: operands of (emulated) rank e; real multi-GPU use passes one entry each.
 // A: [M, K] bf16 row-major activations, B: [N, K] bf16 row-major weights (nn.Linear layout).
 cudaError_t launchTpFused(const TpFusedArgs& args, const void* const* A, const void* const* B, int numReducers,
                           cudaStream_t stream);
+
+// The reducer half alone: allreduce + residual + RMSNorm of an existing [M, N] bf16 `partial` (modes 0 and 1 as above).
+// Starts with a cross-rank barrier (every rank's partial is final), then every CTA is a reducer.
+cudaError_t launchTpReduceNorm(const TpFusedArgs& args, int numCtas, cudaStream_t stream);
 
 // Local pass of mode 1: out = h * rinv[row] * gamma.
 cudaError_t launchTpScaleRows(const void* h, const float* rinv, const void* gamma, void* out, int M, int N,

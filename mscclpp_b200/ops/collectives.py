@@ -122,6 +122,17 @@ def all_gather(symm: SymmetricMemory, inp: torch.Tensor, out: torch.Tensor, nvls
     return out
 
 
+def _rinv_buffer(symm: SymmetricMemory, rows: int) -> torch.Tensor:
+    """Symmetric fp32 [rows] scratch for the per-row 1/rms, allocated once per heap (every rank asks in the same order)."""
+    cache = symm.__dict__.setdefault("_rinv_cache", {})
+    cap = 1
+    while cap < rows:
+        cap <<= 1
+    if cap not in cache:
+        cache[cap] = symm.tensor((cap,), torch.float32)
+    return cache[cap]
+
+
 def all_reduce_rmsnorm(symm: SymmetricMemory, inp: torch.Tensor, out: torch.Tensor, residual_in: Optional[torch.Tensor],
                        residual_out: Optional[torch.Tensor], gamma: Optional[torch.Tensor], eps: float = 1e-5,
                        algo: Optional[str] = None, stream: Optional[torch.cuda.Stream] = None, n_blocks: int = 0) -> torch.Tensor:
@@ -138,9 +149,23 @@ def all_reduce_rmsnorm(symm: SymmetricMemory, inp: torch.Tensor, out: torch.Tens
         all(symm.contains(t) for t in (residual_in, residual_out) if t is not None)
     if algo is None:
         small = nbytes <= min(LL_MAX_BYTES, _ll_capacity(symm)) or rows < symm.world or not symmetric
-        algo = "packet" if small else ("nvls_zero_copy" if symm.nvls else "rsag_zero_copy")
+        rows_ok = inp.dtype == torch.bfloat16 and hidden % 8 == 0 and hidden <= 8192 and not symm.emulated_mode
+        algo = "packet" if small else ("rows" if rows_ok else ("nvls_zero_copy" if symm.nvls else "rsag_zero_copy"))
     dt = torch_dtype_to_native(inp.dtype)
     ptr = lambda t: 0 if t is None else t.data_ptr()
+    if algo in ("rows", "rows_p2p"):
+        # row-owner kernel: 64-thread groups keep a whole row in registers; with a residual stream the owners broadcast
+        # h and one 1/rms per row only and every rank finishes `out` locally (half the NVLink bytes)
+        if not symmetric or inp.dtype != torch.bfloat16:
+            raise ValueError("the row-owner kernel needs bf16 tensors from symm.tensor()")
+        mode = 1 if residual_out is not None else 0
+        rinv = _rinv_buffer(symm, rows) if mode == 1 else None
+        nvls = symm.nvls and algo == "rows"
+        n.tp_reduce_norm(symm.heap, inp.data_ptr(), ptr(residual_in), ptr(residual_out), out.data_ptr(), ptr(gamma), ptr(rinv), rows, hidden,
+                         eps, n_blocks, 0, mode, nvls, _stream(stream))
+        if mode == 1:
+            n.tp_scale_rows(residual_out.data_ptr(), rinv.data_ptr(), ptr(gamma), out.data_ptr(), rows, hidden, _stream(stream))
+        return out
     if algo in ("packet", "nvls_packet"):
         blocks = n_blocks or max(1, min(rows, 64))
         threads = 1024 if hidden * inp.element_size() // 16 >= 1024 else 512

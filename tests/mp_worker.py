@@ -81,7 +81,7 @@ def main():
         report(f"all_gather/nvls={use_nvls}", torch.equal(full.float(), expect))
 
     # fused allreduce + residual + RMSNorm
-    for rows, hidden in ((1, 8192), (8, 8192), (128, 8192), (512, 4096)):
+    for rows, hidden in ((1, 8192), (8, 8192), (128, 8192), (512, 4096), (1000, 8192)):
         x = symm.tensor((rows, hidden), torch.bfloat16)
         y = symm.tensor((rows, hidden), torch.bfloat16)
         r_in = symm.tensor((rows, hidden), torch.bfloat16)
@@ -95,7 +95,7 @@ def main():
         ref = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()).to(torch.bfloat16).float()
         cands = ["packet"] + (["nvls_packet"] if symm.nvls else [])
         if rows >= world:
-            cands += ["rsag_zero_copy"] + (["nvls_zero_copy"] if symm.nvls else [])
+            cands += ["rsag_zero_copy", "rows_p2p"] + (["nvls_zero_copy", "rows"] if symm.nvls else [])
         for algo in cands:
             if algo in ("packet", "nvls_packet") and rows * hidden * 2 > (1 << 20):
                 continue

@@ -479,3 +479,47 @@ def test_two_sm_gemm(m, n, k):
     torch.cuda.synchronize()
     ref = a.float() @ w.float().t()
     assert (d.float() - ref).abs().max().item() <= 0.01 * ref.abs().max().item() + 0.01
+
+
+@pytest.mark.parametrize("world,rows,hidden,with_residual", [(2, 100, 1024, True), (4, 64, 8192, True), (8, 333, 4096, False)])
+def test_row_owner_allreduce_rmsnorm(world, rows, hidden, with_residual):
+    """Standalone allreduce + residual + RMSNorm on the fused kernel's reducer (row owners, whole rows in registers)."""
+    from mscclpp_b200 import SymmetricMemory, native
+
+    n = native()
+    symm = SymmetricMemory.emulated(world, nbytes=128 << 20, timeout_ms=3000)
+    partial = symm.tensor((rows, hidden), torch.bfloat16)
+    res_in = symm.tensor((rows, hidden), torch.bfloat16)
+    res_out = symm.tensor((rows, hidden), torch.bfloat16)
+    out = symm.tensor((rows, hidden), torch.bfloat16)
+    gamma = symm.tensor((hidden,), torch.bfloat16)
+    rinv = symm.tensor((rows,), torch.float32)
+    g = torch.Generator(device="cuda").manual_seed(rows)
+    parts = [torch.randn((rows, hidden), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    residual = torch.randn((rows, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    gam = (1 + 0.1 * torch.randn((hidden,), generator=g, device="cuda")).to(torch.bfloat16)
+    for r in range(world):
+        symm.rank_view(partial, r).copy_(parts[r])
+        symm.rank_view(res_in, r).copy_(residual)
+        symm.rank_view(gamma, r).copy_(gam)
+    mode = 1 if with_residual else 0
+    for rep in range(2):
+        for r in range(world):
+            symm.rank_view(out, r).zero_()
+        n.tp_reduce_norm(symm.heap, partial.data_ptr(), res_in.data_ptr() if with_residual else 0, res_out.data_ptr() if with_residual else 0,
+                         out.data_ptr(), gamma.data_ptr(), rinv.data_ptr(), rows, hidden, 1e-5, 4, 0, mode, False,
+                         torch.cuda.current_stream().cuda_stream)
+        if mode == 1:
+            for r in range(world):
+                n.tp_scale_rows(symm.rank_view(res_out, r).data_ptr(), symm.rank_view(rinv, r).data_ptr(), gamma.data_ptr(),
+                                symm.rank_view(out, r).data_ptr(), rows, hidden, torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        symm.check()
+    acc = sum(p.float() for p in parts).to(torch.bfloat16).float()
+    h = (acc + residual.float()).to(torch.bfloat16).float() if with_residual else acc
+    y = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5) * gam.float()).to(torch.bfloat16).float()
+    for r in range(world):
+        assert (symm.rank_view(out, r).float() - y).abs().max().item() <= 0.1
+        if with_residual:
+            assert (symm.rank_view(res_out, r).float() - h).abs().max().item() <= 0.02 * h.abs().max().item() + 0.05
+    symm.destroy()
