@@ -219,8 +219,10 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
         if (lane == 0) okSmem[group] = 0;
         break;
       }
-      // order my loads after the flag writes that another group of this CTA may have observed for me
-      ptx::fence_acq_rel_sys();
+      // The poller took a system-scope acquire on the flags before it set the bit in shared memory; a CTA-scope
+      // fence after reading the bit completes the chain for this thread. (A system-scope fence here would also wait
+      // for this thread's outstanding peer stores of the previous row - microseconds per row.)
+      __threadfence_block();
       readyMb = mb;
     }
     const uint64_t rowOff = static_cast<uint64_t>(row) * unitsPerRow * 16;

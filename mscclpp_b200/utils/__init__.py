@@ -48,7 +48,12 @@ class Kernel:
         every parameter inside it."""
         cuda_stream = 0
         if stream is not None:
-            cuda_stream = getattr(stream, "cuda_stream", None) or getattr(stream, "ptr", None) or int(stream)
+            if hasattr(stream, "cuda_stream"):  # torch.cuda.Stream (0 = the default stream)
+                cuda_stream = int(stream.cuda_stream)
+            elif hasattr(stream, "ptr"):  # cupy stream
+                cuda_stream = int(stream.ptr)
+            else:
+                cuda_stream = int(stream)
         _loader.load().launch_packed(self._function, bytes(params), nblocks, grid_y, nthreads, shared, cuda_stream, cooperative,
                                      list(offsets))
 
