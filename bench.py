@@ -182,10 +182,11 @@ def main():
         return lambda: layer.forward_fused(xs[t], mode=mode, nvls=nvls, num_reducers=reducers, block_n=bn)
 
     nvls_opts = [True] if symm.nvls else [False]
-    variants = [(m, nv, r, c) for m in (0, 1) for nv in nvls_opts for r in (24, 48) for c in (1, 2)] + [(-1, symm.nvls, 0, 1)]
+    variants = [(m, nv, r, c) for m in (0, 1) for nv in nvls_opts for r in (24, 32, 48) for c in (1, 2)] + [(-1, symm.nvls, 0, 1)]
     if world == 1:
         variants = [(0, False, 64, 1), (1, False, 64, 1), (0, False, 64, 2), (1, False, 64, 2), (-1, False, 0, 1)]
     best = {}
+    tune_scores = {}
     for t in TOKEN_SIZES:
         scores = {}
         for v in variants:
@@ -193,6 +194,7 @@ def main():
                 continue
             scores[v] = time_steps(fused(t, *v), 5 if t >= 8192 else 20, 3)
         best[t] = min(scores, key=scores.get)
+        tune_scores[str(t)] = {"/".join(str(int(x)) for x in v): round(ms * 1e3, 1) for v, ms in scores.items()}
 
     # ------------------------------------------------------------------ headline: fused TP layer at T = 8192
     sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
@@ -327,7 +329,8 @@ def main():
                         "kernel": ("gemmBf16Kernel (tcgen05) then twoShot/LL allreduce+residual+RMSNorm kernel" if head_mode < 0 else
                                    "tpFusedKernel (tcgen05 GEMM + multimem/peer reduce + residual + RMSNorm in one launch)" +
                                    ("" if head_mode == 0 else " + local scale pass")),
-                        "per_T": {str(t): list(best[t]) for t in TOKEN_SIZES}},
+                        "per_T": {str(t): list(best[t]) for t in TOKEN_SIZES},
+                        "autotune_us (mode/nvls/reducer_ctas/gemm_core)": tune_scores[str(HEADLINE_T)]},
             "tp_layer_us": tp_us,
             "tp_layer_graph_replay_us": tp_graph_us,
             "tp_layer_two_kernel_us": tp_unfused_us,

@@ -136,7 +136,10 @@ MSCCLPP_DEVICE_INLINE void scatterWord(const DeviceComm& c, int rank, uint64_t h
 }
 
 template <bool kNvls>
-MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t epoch, int reducerIdx, int numReducers) {
+// `slot` names this CTA in the closing cross-rank barrier (the same grid runs on every rank). Rows are handed out
+// dynamically, in ascending order, from a per-rank counter: CTAs that were GEMM CTAs join in when their tiles are done,
+// so after the matmul the whole GPU works on the reduction.
+MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t epoch, int slot) {
   const DeviceComm& c = a.comm;
   const int world = c.world;
   const int M = a.shape.M, N = a.shape.N;
@@ -168,15 +171,34 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
   if (lane == 0) okSmem[group] = 1;
   groupBarrier(group);
 
-  const int globalGroup = reducerIdx * kGroupsPerCta + group;
-  const int numGroups = numReducers * kGroupsPerCta;
+  __shared__ int nextRow[kGroupsPerCta];
+  uint32_t* rowCounter = &control(c, rank)->gridSync[7];  // zero at launch start (finishLaunch re-arms it)
   int readyMb = -1;
   bool healthy = true;
   // owned row j -> global row: unit = rank + (j / rpu) * world, row = unit * rpu + j % rpu
 #pragma unroll 1
-  for (int j = globalGroup; j < ownedRows && healthy; j += numGroups) {
+  for (;;) {
+    if (lane == 0) nextRow[group] = healthy ? static_cast<int>(atomicAdd(rowCounter, 1u)) : ownedRows;
+    groupBarrier(group);
+    const int j = nextRow[group];
+    groupBarrier(group);  // nextRow may be rewritten from here on
+    if (j >= ownedRows) break;
     const int row = (rank + (j / rpu) * world) * rpu + (j % rpu);
     if (row >= M) continue;
+    // The residual does not depend on anybody's GEMM: with the switch doing the reduction there are registers to
+    // spare, so its loads are put in flight before the readiness wait and the gather.
+    [[maybe_unused]] uint4 resEarly[kWordsPerThread];
+    if constexpr (kNvls) {
+      if (a.residualIn && a.mode != 2) {
+        const uint64_t resRow = local + resInOff + static_cast<uint64_t>(row) * unitsPerRow * 16;
+#pragma unroll
+        for (int k = 0; k < kWordsPerThread; k++) {
+          const int w = lane + k * kGroupThreads;
+          resEarly[k] = make_uint4(0, 0, 0, 0);
+          if (w < unitsPerRow) resEarly[k] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(resRow + w * 16));
+        }
+      }
+    }
     // ---- wait until every rank has produced every tile of the row block this row lives in
     const int mb = row / gemm::kBlockM;
     if (mb != readyMb && !a.noFlags) {
@@ -283,8 +305,12 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
 #pragma unroll
       for (int k = 0; k < 8; k++) {
         const int w = lane + (half * 8 + k) * kGroupThreads;
-        res[k] = make_uint4(0, 0, 0, 0);
-        if (a.residualIn && w < unitsPerRow) res[k] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(local + resInOff + rowOff + w * 16));
+        if constexpr (kNvls) {
+          res[k] = resEarly[half * 8 + k];
+        } else {
+          res[k] = make_uint4(0, 0, 0, 0);
+          if (a.residualIn && w < unitsPerRow) res[k] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(local + resInOff + rowOff + w * 16));
+        }
       }
 #pragma unroll
       for (int k = 0; k < 8; k++) {
@@ -347,7 +373,7 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
   __syncthreads();
   bool allOk = true;
   for (int g = 0; g < kGroupsPerCta; g++) allOk = allOk && okSmem[g] != 0;
-  if (allOk) rankBarrier(c, rank, 2, reducerIdx, epoch);
+  if (allOk) rankBarrier(c, rank, 2, slot, epoch);
 }
 
 // kBlockN == 0 selects the two-SM GEMM core (256 x 256 tiles on CTA pairs; the launch uses clusters of two).
@@ -372,9 +398,9 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
       gemm::gemmCta<kBlockN>(&maps.a[blockIdx.y], &maps.b[blockIdx.y], a.shape, blockIdx.x, a.numGemmCtas, gate, epi,
                              c.status, c.timeoutNs, smemRaw);
     }
-  } else {
-    reducerCta<kNvls>(a, rank, epoch, blockIdx.x - a.numGemmCtas, gridDim.x - a.numGemmCtas);
   }
+  // dedicated reducer CTAs start here at once; GEMM CTAs arrive when their last tile is stored
+  reducerCta<kNvls>(a, rank, epoch, blockIdx.x);
   finishLaunch(c, rank, epoch);
 }
 
@@ -384,7 +410,7 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1) tpReduceNormKernel(const
   const int rank = deviceRank(c);
   const uint32_t epoch = launchEpoch(c, rank);
   // every rank's partial product is final once its kernel runs
-  if (rankBarrier(c, rank, 0, blockIdx.x, epoch)) reducerCta<kNvls>(a, rank, epoch, blockIdx.x, gridDim.x);
+  if (rankBarrier(c, rank, 0, blockIdx.x, epoch)) reducerCta<kNvls>(a, rank, epoch, blockIdx.x);
   finishLaunch(c, rank, epoch);
 }
 
