@@ -61,7 +61,8 @@ class Kernel:
 class KernelBuilder:
     """Compile one kernel of a .cu file to a cubin for sm_100a with this library's headers on the include path."""
 
-    kernel_map: dict = {}
+    kernel_map: dict = {}   # (source, macros, kernel name) -> Kernel
+    cubin_map: dict = {}    # (source, macros) -> cubin bytes: several kernels of one file share one compilation
 
     @staticmethod
     def get_key(file, kernel_name, macro_dict):
@@ -71,17 +72,16 @@ class KernelBuilder:
         macro_dict = macro_dict or {}
         self._dir = file_dir if file_dir else os.getcwd()
         self._source = os.path.join(self._dir, file)
-        key = self.get_key(self._source, kernel_name, macro_dict)
+        cubin_key = self.get_key(self._source, "", macro_dict)
+        if cubin_key not in self.cubin_map:
+            self.cubin_map[cubin_key] = self._compile_cuda(self._source, [f"-D{k}={v}" for k, v in macro_dict.items()])
+        self.cubin = self.cubin_map[cubin_key]
         self._kernel = None
-        if key in self.kernel_map:
-            self.cubin, self._kernel = self.kernel_map[key]
-            if self._kernel is not None or not load:
-                return
-        else:
-            self.cubin = self._compile_cuda(self._source, [f"-D{k}={v}" for k, v in macro_dict.items()])
         if load:
-            self._kernel = Kernel(self.cubin, kernel_name)
-        self.kernel_map[key] = (self.cubin, self._kernel)
+            key = self.get_key(self._source, kernel_name, macro_dict)
+            if key not in self.kernel_map:
+                self.kernel_map[key] = Kernel(self.cubin, kernel_name)
+            self._kernel = self.kernel_map[key]
 
     @staticmethod
     def _compile_cuda(source_file: str, macros, std_version: str = "c++17") -> bytes:
