@@ -1,6 +1,8 @@
 // Context internals: copy streams for CudaIpc connections and the token pool semaphores draw from.
 #pragma once
 
+#include <map>
+
 #include <cuda_runtime.h>
 #include <memory>
 #include <mutex>
@@ -45,9 +47,9 @@ class TokenPool {
 struct Context::Impl {
   std::mutex mutex;
   std::vector<std::shared_ptr<IpcStream>> streams;
-  std::shared_ptr<TokenPool> tokenPool;
+  std::map<int, std::shared_ptr<TokenPool>> tokenPools;  // one pool per GPU of this process
   std::shared_ptr<IpcStream> ipcStream();
-  std::shared_ptr<TokenPool> tokens();
+  std::shared_ptr<TokenPool> tokens();  // the pool of the current device
 };
 
 }  // namespace mscclpp

@@ -235,6 +235,21 @@ void gpuFreeHost(void* ptr) {
   (void)cudaFreeHost(ptr);
 }
 
+bool gpuGrantAccessPhysical(const void* ptr, int dev) {
+  std::lock_guard<std::mutex> lock(physMutex);
+  auto it = physAllocs.upper_bound(const_cast<void*>(ptr));
+  if (it == physAllocs.begin()) return false;
+  --it;
+  const char* base = static_cast<const char*>(it->first);
+  if (static_cast<const char*>(ptr) >= base + it->second.bytes) return false;
+  CUmemAccessDesc access{};
+  access.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  access.location.id = dev;
+  access.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  MSCCLPP_CUTHROW(CudaDriver::get().cuMemSetAccess(reinterpret_cast<CUdeviceptr>(base), it->second.bytes, &access, 1));
+  return true;
+}
+
 void gpuFreePhysical(void* ptr) {
   if (ptr == nullptr) return;
   AvoidCudaGraphCaptureGuard guard;

@@ -28,6 +28,7 @@ GpuIpcMemHandle GpuIpcMemHandle::create(void* ptr, size_t size) {
     return h;
   }
   h.deviceId = attr.device;
+  CudaDeviceGuard onOwner(attr.device);  // the driver queries below want the owning device's context current
   const CudaDriver& drv = CudaDriver::get();
   CUdeviceptr base = 0;
   size_t allocSize = 0;
@@ -162,6 +163,8 @@ std::shared_ptr<RegisteredMemory::Impl> RegisteredMemory::Impl::deserialize(cons
     if (!impl->isHostMemory && impl->deviceId >= 0) {
       int dev = 0;
       if (cudaGetDevice(&dev) == cudaSuccess && dev != impl->deviceId) {
+        // VMM allocations of this process need an explicit access grant; everything else goes through peer access
+        (void)detail::gpuGrantAccessPhysical(impl->originalDataPtr, dev);
         cudaError_t e = cudaDeviceEnablePeerAccess(impl->deviceId, 0);
         if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
           (void)cudaGetLastError();

@@ -40,8 +40,11 @@ std::shared_ptr<uint64_t> TokenPool::getToken() {
 }
 std::shared_ptr<TokenPool> Context::Impl::tokens() {
   std::lock_guard<std::mutex> lock(mutex);
-  if (!tokenPool) tokenPool = std::make_shared<TokenPool>(32768);
-  return tokenPool;
+  int dev = 0;
+  MSCCLPP_CUDATHROW(cudaGetDevice(&dev));
+  auto& pool = tokenPools[dev];
+  if (!pool) pool = std::make_shared<TokenPool>(32768);
+  return pool;
 }
 
 // ------------------------------------------------------------------------------------------ SemaphoreStub / Semaphore

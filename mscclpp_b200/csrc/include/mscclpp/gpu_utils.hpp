@@ -65,6 +65,9 @@ void* gpuCallocPhysical(size_t bytes, size_t granularity = 0);
 void gpuFree(void* ptr);
 void gpuFreeHost(void* ptr);
 void gpuFreePhysical(void* ptr);
+// If `ptr` lies inside an allocation of gpuCallocPhysical made by this process, give device `dev` read/write access
+// to it (VMM allocations are not covered by cudaDeviceEnablePeerAccess). Returns false for other memory.
+bool gpuGrantAccessPhysical(const void* ptr, int dev);
 size_t physicalGranularity(bool forMulticast);
 }  // namespace detail
 

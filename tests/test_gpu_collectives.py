@@ -523,3 +523,36 @@ def test_row_owner_allreduce_rmsnorm(world, rows, hidden, with_residual):
         if with_residual:
             assert (symm.rank_view(res_out, r).float() - h).abs().max().item() <= 0.02 * h.abs().max().item() + 0.05
     symm.destroy()
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("dtype", [torch.float8_e4m3fn, torch.float8_e5m2])
+@pytest.mark.parametrize("algo", ["packet", "rsag_zero_copy"])
+def test_fp8_allreduce_accumulates_in_fp32(world, dtype, algo):
+    """FP8 inputs are summed in fp32 and rounded once: the result equals round(fp32 sum) and its error is never
+    larger than that of summing in fp8 step by step (the property the reference checks in test_fp8_accum.py)."""
+    from mscclpp_b200.ops import all_reduce
+
+    symm = _symm(world)
+    numel = 16384
+    inp = symm.tensor((numel,), dtype)
+    out = symm.tensor((numel,), dtype)
+    vals = []
+    for r in range(world):
+        g = torch.Generator(device="cuda").manual_seed(900 + r)
+        x = (torch.randn(numel, generator=g, device="cuda") * 0.5).to(dtype)
+        symm.rank_view(inp, r).copy_(x)
+        vals.append(x.float())
+    all_reduce(symm, inp, out, algo=algo, n_blocks=4)
+    torch.cuda.synchronize()
+    symm.check()
+    exact = torch.stack(vals).sum(0)
+    oracle = exact.to(dtype).float()          # one rounding of the fp32 sum
+    stepwise = vals[0].clone()
+    for v in vals[1:]:
+        stepwise = (stepwise + v).to(dtype).float()   # what accumulating in fp8 would give
+    for r in range(world):
+        got = symm.rank_view(out, r).float()
+        assert torch.equal(got, oracle), (r, (got - oracle).abs().max().item())
+    assert (oracle - exact).abs().mean().item() <= (stepwise - exact).abs().mean().item() + 1e-9
+    symm.destroy()
