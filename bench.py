@@ -176,6 +176,8 @@ def main():
     # ------------------------------------------------------------------ pick the fused variant (untimed)
     # variant = (mode, nvls, reducer CTAs, GEMM core): core 1 = one-SM tiles, 2 = 256 x 256 tiles on SM pairs (cta_group::2)
     def fused(t, mode, nvls, reducers, core=1):
+        if mode == -2:  # one GPU: GEMM whose epilogue adds the residual and sums the squares, then the scale pass
+            return lambda: layer.forward_local(xs[t], two_sm=(core == 2))
         if mode < 0:  # two launches: tcgen05 GEMM, then the fused allreduce + residual + RMSNorm kernel
             return lambda: layer.forward(xs[t])
         bn = -1 if core == 2 else pick_block_n(t, HIDDEN)
@@ -185,7 +187,8 @@ def main():
     nvls_opts = ([True, False] if world <= 4 else [True]) if symm.nvls else [False]
     variants = [(m, nv, r, c) for m in (0, 1) for nv in nvls_opts for r in (24, 32, 48) for c in (1, 2)] + [(-1, symm.nvls, 0, 1)]
     if world == 1:
-        variants = [(0, False, 64, 1), (1, False, 64, 1), (0, False, 64, 2), (1, False, 64, 2), (-1, False, 0, 1)]
+        variants = [(0, False, 64, 1), (1, False, 64, 1), (0, False, 64, 2), (1, False, 64, 2), (-1, False, 0, 1), (-2, False, 0, 1),
+                    (-2, False, 0, 2)]
     best = {}
     tune_scores = {}
     for t in TOKEN_SIZES:
@@ -222,7 +225,9 @@ def main():
             torch.cuda.synchronize()
             with torch.cuda.graph(graph, stream=side):
                 for _ in range(reps):
-                    if best[t][0] < 0:
+                    if best[t][0] == -2:
+                        layer.forward_local(xs[t], two_sm=(best[t][3] == 2), stream=side)
+                    elif best[t][0] < 0:
                         layer.forward(xs[t], stream=side)
                     else:
                         layer.forward_fused(xs[t], mode=best[t][0], nvls=best[t][1], num_reducers=best[t][2], stream=side,
@@ -251,7 +256,9 @@ def main():
 
     def e2e_step():
         x_dev.copy_(x_host, non_blocking=True)
-        if head_mode < 0:
+        if head_mode == -2:
+            out, _ = layer.forward_local(x_dev, two_sm=(head_core == 2))
+        elif head_mode < 0:
             out, _ = layer.forward(x_dev)
         else:
             out, _ = layer.forward_fused(x_dev, mode=head_mode, nvls=head_nvls, num_reducers=head_reducers,
@@ -327,7 +334,9 @@ def main():
             "aggregate_tflops": round(flops / (ms_per_step * 1e-3) / 1e12, 1),
             "variant": {"mode": head_mode, "nvls": head_nvls, "reducer_ctas": head_reducers,
                         "gemm_core": "two-SM 256x256 (cta_group::2)" if head_core == 2 else "one-SM 128x256",
-                        "kernel": ("gemmBf16Kernel (tcgen05) then twoShot/LL allreduce+residual+RMSNorm kernel" if head_mode < 0 else
+                        "kernel": ("gemmResidualSumsqKernel (tcgen05 GEMM, epilogue adds residual + row sums of squares) then scale pass"
+                                   if head_mode == -2 else
+                                   "gemmBf16Kernel (tcgen05) then twoShot/LL allreduce+residual+RMSNorm kernel" if head_mode < 0 else
                                    "tpFusedKernel (tcgen05 GEMM + multimem/peer reduce + residual + RMSNorm in one launch)" +
                                    ("" if head_mode == 0 else " + local scale pass")),
                         "per_T": {str(t): list(best[t]) for t in TOKEN_SIZES},

@@ -132,6 +132,27 @@ void registerMoreBindings(py::module_& m) {
       py::arg("heap"), py::arg("partial"), py::arg("residual_in"), py::arg("residual_out"), py::arg("out"), py::arg("gamma"), py::arg("rinv"),
       py::arg("m"), py::arg("n"), py::arg("eps"), py::arg("num_ctas") = 0, py::arg("rows_per_unit") = 0, py::arg("mode") = 0,
       py::arg("nvls") = false, py::arg("stream") = 0);
+  m.def(
+      "gemm_residual_sumsq",
+      [](uintptr_t a, uintptr_t b, uintptr_t residual, uintptr_t h, uintptr_t sumsq, int M, int N, int K, int blockN, bool twoSm,
+         uintptr_t stream) {
+        checkCudaMore(launchGemmResidualSumsq(reinterpret_cast<const void*>(a), reinterpret_cast<const void*>(b),
+                                              reinterpret_cast<const void*>(residual), reinterpret_cast<void*>(h),
+                                              reinterpret_cast<float*>(sumsq), M, N, K, blockN, twoSm, nullptr,
+                                              reinterpret_cast<cudaStream_t>(stream)),
+                      "gemm_residual_sumsq");
+      },
+      py::arg("a"), py::arg("b"), py::arg("residual"), py::arg("h"), py::arg("sumsq"), py::arg("m"), py::arg("n"), py::arg("k"),
+      py::arg("block_n") = 256, py::arg("two_sm") = false, py::arg("stream") = 0);
+  m.def(
+      "tp_scale_rows_from_sumsq",
+      [](uintptr_t h, uintptr_t sumsq, uintptr_t gamma, uintptr_t out, int M, int N, float eps, uintptr_t stream) {
+        checkCudaMore(launchTpScaleRowsFromSumsq(reinterpret_cast<const void*>(h), reinterpret_cast<const float*>(sumsq),
+                                                 reinterpret_cast<const void*>(gamma), reinterpret_cast<void*>(out), M, N, eps,
+                                                 reinterpret_cast<cudaStream_t>(stream)),
+                      "tp_scale_rows_from_sumsq");
+      },
+      py::arg("h"), py::arg("sumsq"), py::arg("gamma"), py::arg("out"), py::arg("m"), py::arg("n"), py::arg("eps"), py::arg("stream") = 0);
   m.def("moe_workspace_bytes", [] { return moeWorkspaceBytes(); });
   m.def(
       "moe_dispatch",

@@ -140,8 +140,12 @@ struct PhysicalAlloc {
 std::mutex physMutex;
 std::map<void*, PhysicalAlloc> physAllocs;
 
+// One set-up stream per (thread, device): a stream belongs to the device that was current when it was made.
 cudaStream_t setupStream() {
-  static thread_local cudaStream_t s = nullptr;
+  static thread_local std::map<int, cudaStream_t> streams;
+  int dev = 0;
+  MSCCLPP_CUDATHROW(cudaGetDevice(&dev));
+  cudaStream_t& s = streams[dev];
   if (s == nullptr) MSCCLPP_CUDATHROW(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
   return s;
 }

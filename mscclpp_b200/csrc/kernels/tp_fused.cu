@@ -414,6 +414,76 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1) tpReduceNormKernel(const
   finishLaunch(c, rank, epoch);
 }
 
+// Epilogue of the single-GPU layer: h = bf16(acc) + residual (rounded to bf16 like the unfused composition), stored;
+// the row's sum of squares of the rounded values is added to sumsq[row] (one fp32 reduction per thread and chunk).
+struct ResidualSumsqStore {
+  static constexpr bool kNeedsTileBarrier = false;
+  const bf16* residual;  // [M, N] or null
+  bf16* h;               // [M, N]
+  float* sumsq;          // [M]
+  int M, N;
+  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32]) const {
+    if (row >= M) return;
+    const size_t off = static_cast<size_t>(row) * N + col;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      float f[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) f[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[8 * i + j])));
+      if (residual != nullptr) {
+        float r[8];
+        Vec16<bf16>::toFloat(ptx::ld_nc_na_v4(residual + off + 8 * i), r);
+#pragma unroll
+        for (int j = 0; j < 8; j++) f[j] += r[j];
+      }
+      const uint4 packed = Vec16<bf16>::fromFloat(f);
+      Vec16<bf16>::toFloat(packed, f);
+#pragma unroll
+      for (int j = 0; j < 8; j++) ss += f[j] * f[j];
+      *reinterpret_cast<uint4*>(h + off + 8 * i) = packed;
+    }
+    atomicAdd(sumsq + row, ss);
+  }
+  MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
+};
+
+template <int kBlockN>
+__global__ void __launch_bounds__(gemm::kNumThreads, 1)
+    gemmResidualSumsqKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, gemm::Shape shape,
+                            ResidualSumsqStore epi, DeviceStatus* status, uint64_t budgetNs) {
+  extern __shared__ uint8_t smemRaw[];
+  gemm::NoGate gate;
+  if constexpr (kBlockN == 0) {
+    gemm::gemmCtaPair(&tmapA, &tmapB, shape, blockIdx.x / 2, gridDim.x / 2, gate, epi, status, budgetNs, smemRaw);
+  } else {
+    gemm::gemmCta<kBlockN>(&tmapA, &tmapB, shape, blockIdx.x, gridDim.x, gate, epi, status, budgetNs, smemRaw);
+  }
+}
+
+__global__ void __launch_bounds__(512) tpScaleRowsSumsqKernel(const bf16* h, const float* sumsq, const bf16* gamma, bf16* out, int M, int N,
+                                                              float eps) {
+  const int unitsPerRow = N / 8;
+  const size_t total = static_cast<size_t>(M) * unitsPerRow;
+  const float invN = 1.f / static_cast<float>(N);
+  for (size_t u = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < total; u += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(u / unitsPerRow), ru = static_cast<int>(u % unitsPerRow);
+    float f[8];
+    Vec16<bf16>::toFloat(*reinterpret_cast<const uint4*>(h + u * 8), f);
+    const float s = rsqrtf(sumsq[row] * invN + eps);
+    if (gamma) {
+      float g[8];
+      Vec16<bf16>::toFloat(*reinterpret_cast<const uint4*>(gamma + static_cast<size_t>(ru) * 8), g);
+#pragma unroll
+      for (int i = 0; i < 8; i++) f[i] = f[i] * s * g[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; i++) f[i] = f[i] * s;
+    }
+    *reinterpret_cast<uint4*>(out + u * 8) = Vec16<bf16>::fromFloat(f);
+  }
+}
+
 // out[row] = h[row] * rinv[row] * gamma (local pass of mode 1)
 __global__ void __launch_bounds__(512) tpScaleRowsKernel(const bf16* h, const float* rinv, const bf16* gamma, bf16* out,
                                                          int M, int N) {
@@ -576,6 +646,74 @@ cudaError_t launchTpReduceNorm(const TpFusedArgs& argsIn, int numCtas, cudaStrea
     return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), g, b, params, 0, stream);
   }
   kernel<<<g, b, 0, stream>>>(args);
+  return cudaGetLastError();
+}
+
+template <int kBlockN>
+cudaError_t launchLocalTyped(const CUtensorMap& ta, const CUtensorMap& tb, gemm::Shape shape, ResidualSumsqStore epi, DeviceStatus* status,
+                             cudaStream_t stream) {
+  using Cfg = SmemOf<kBlockN>;
+  auto kernel = gemmResidualSumsqKernel<kBlockN>;
+  static bool attrSet = false;
+  if (!attrSet) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (e != cudaSuccess) return e;
+    attrSet = true;
+  }
+  uint64_t budget = 2000000000ull;
+  if constexpr (kBlockN == 0) {
+    const int tiles = ((shape.M + gemm::Config2::kPairM - 1) / gemm::Config2::kPairM) * (shape.N / gemm::Config2::kBlockN);
+    int grid = gemm::smCount() & ~1;
+    if (grid > 2 * tiles) grid = 2 * tiles;
+    void* params[] = {const_cast<CUtensorMap*>(&ta), const_cast<CUtensorMap*>(&tb), &shape, &epi, &status, &budget};
+    return gemm::launchClusterPair(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(gemm::kNumThreads), Cfg::kSmemBytes, params, false,
+                                   stream);
+  } else {
+    const int tiles = ((shape.M + gemm::kBlockM - 1) / gemm::kBlockM) * (shape.N / kBlockN);
+    int grid = gemm::smCount();
+    if (grid > tiles) grid = tiles;
+    kernel<<<grid, gemm::kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, shape, epi, status, budget);
+    return cudaGetLastError();
+  }
+}
+
+cudaError_t launchGemmResidualSumsq(const void* A, const void* B, const void* residual, void* h, float* sumsq, int M, int N, int K,
+                                    int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % gemm::kBlockK != 0 || N % 8 != 0) return cudaErrorInvalidValue;
+  if (twoSm && (M < gemm::Config2::kPairM || N % gemm::Config2::kBlockN != 0)) return cudaErrorInvalidValue;
+  if (!twoSm && (blockN != 64 && blockN != 128 && blockN != 256)) return cudaErrorInvalidValue;
+  if (!twoSm && N % blockN != 0) return cudaErrorInvalidValue;
+  cudaError_t e = cudaMemsetAsync(sumsq, 0, static_cast<size_t>(M) * sizeof(float), stream);
+  if (e != cudaSuccess) return e;
+  gemm::Shape shape{M, N, K, M < gemm::kBlockM ? M : gemm::kBlockM, 0, 0, 0};
+  if (twoSm) shape.aBoxRows = gemm::kBlockM;
+  CUtensorMap ta, tb;
+  e = gemm::makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, shape.aBoxRows);
+  if (e != cudaSuccess) return e;
+  e = gemm::makeTensorMapBf16(&tb, B, N, K, static_cast<uint64_t>(K) * 2, twoSm ? gemm::Config2::kBlockN / 2 : blockN);
+  if (e != cudaSuccess) return e;
+  ResidualSumsqStore epi{static_cast<const bf16*>(residual), static_cast<bf16*>(h), sumsq, M, N};
+  if (twoSm) return launchLocalTyped<0>(ta, tb, shape, epi, status, stream);
+  switch (blockN) {
+    case 64:
+      return launchLocalTyped<64>(ta, tb, shape, epi, status, stream);
+    case 128:
+      return launchLocalTyped<128>(ta, tb, shape, epi, status, stream);
+    default:
+      return launchLocalTyped<256>(ta, tb, shape, epi, status, stream);
+  }
+}
+
+cudaError_t launchTpScaleRowsFromSumsq(const void* h, const float* sumsq, const void* gamma, void* out, int M, int N, float eps,
+                                       cudaStream_t stream) {
+  if (N % 8 != 0) return cudaErrorInvalidValue;
+  const size_t total = static_cast<size_t>(M) * (N / 8);
+  int blocks = static_cast<int>((total + 511) / 512);
+  const int cap = gemm::smCount() * 4;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  tpScaleRowsSumsqKernel<<<blocks, 512, 0, stream>>>(static_cast<const bf16*>(h), sumsq, static_cast<const bf16*>(gamma), static_cast<bf16*>(out),
+                                                      M, N, eps);
   return cudaGetLastError();
 }
 

@@ -40,6 +40,15 @@ cudaError_t launchTpFused(const TpFusedArgs& args, const void* const* A, const v
 // Starts with a cross-rank barrier (every rank's partial is final), then every CTA is a reducer.
 cudaError_t launchTpReduceNorm(const TpFusedArgs& args, int numCtas, cudaStream_t stream);
 
+// One GPU, no collective: h = bf16(A * B^T) + residual written by the GEMM epilogue, which also adds every row's
+// sum of squares into sumsq[M] (fp32, zeroed here first); launchTpScaleRowsFromSumsq then produces the RMSNorm.
+// twoSm selects the 256 x 256 pair tiles (M >= 256, N % 256 == 0), else one-SM tiles of blockN columns.
+cudaError_t launchGemmResidualSumsq(const void* A, const void* B, const void* residual, void* h, float* sumsq, int M, int N, int K,
+                                    int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream);
+// out = h * rsqrt(sumsq[row] / N + eps) * gamma
+cudaError_t launchTpScaleRowsFromSumsq(const void* h, const float* sumsq, const void* gamma, void* out, int M, int N, float eps,
+                                       cudaStream_t stream);
+
 // Local pass of mode 1: out = h * rinv[row] * gamma.
 cudaError_t launchTpScaleRows(const void* h, const float* rinv, const void* gamma, void* out, int M, int N,
                               cudaStream_t stream);

@@ -97,6 +97,27 @@ class RowParallelLinearNorm:
                                 view(self.out).data_ptr(), t, self.out_features, s)
         return self.out[:t], self.residual_out[:t]
 
+    def forward_local(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, two_sm: Optional[bool] = None,
+                      stream: Optional[torch.cuda.Stream] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """World size 1 (no collective): the GEMM's epilogue adds the residual, stores h and accumulates every row's
+        sum of squares; a second, memory-bound launch applies 1/rms and gamma. Two launches, no intermediate passes."""
+        from .._core import native
+
+        assert self.symm.world == 1, "forward_local is the single-GPU path"
+        n = native.load()
+        t = x.shape[0]
+        assert t <= self.max_tokens and x.shape[1] == self.k_shard and x.is_contiguous()
+        if residual is not None:
+            self.residual_in[:t].copy_(residual)
+        if two_sm is None:
+            two_sm = t >= 1024 and self.out_features % 256 == 0
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        n.gemm_residual_sumsq(x.data_ptr(), self.weight.data_ptr(), self.residual_in.data_ptr(), self.residual_out.data_ptr(),
+                              self.rinv.data_ptr(), t, self.out_features, self.k_shard, pick_block_n(t, self.out_features), two_sm, s)
+        n.tp_scale_rows_from_sumsq(self.residual_out.data_ptr(), self.rinv.data_ptr(), self.gamma.data_ptr(), self.out.data_ptr(), t,
+                                   self.out_features, self.eps, s)
+        return self.out[:t], self.residual_out[:t]
+
     @torch.no_grad()
     def reference(self, x_shards, weights, residual: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
         """Plain PyTorch fp32 composition of the same layer (all shards given)."""

@@ -40,3 +40,27 @@ def test_gemm_auto_tile_and_repeat():
         out = gemm_bf16(a, w)
         torch.cuda.synchronize()
         assert (out.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+
+
+@pytest.mark.parametrize("tokens,hidden,k,two_sm", [(200, 1024, 256, False), (1024, 2048, 512, True), (777, 512, 128, False)])
+def test_single_gpu_layer_gemm_epilogue_residual_sumsq(tokens, hidden, k, two_sm):
+    """One GPU: GEMM whose epilogue adds the residual and accumulates the rows' sums of squares, then the scale pass."""
+    import os
+
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.tp_layer import RowParallelLinearNorm
+
+    symm = SymmetricMemory.emulated(1, nbytes=128 << 20, timeout_ms=3000)
+    layer = RowParallelLinearNorm(symm, out_features=hidden, k_shard=k, max_tokens=tokens)
+    g = torch.Generator(device="cuda").manual_seed(tokens)
+    x = torch.randn((tokens, k), generator=g, device="cuda").to(torch.bfloat16)
+    residual = torch.randn((tokens, hidden), generator=g, device="cuda").to(torch.bfloat16)
+    layer.gamma.copy_((1 + 0.1 * torch.randn((hidden,), generator=g, device="cuda")).to(torch.bfloat16))
+    for rep in range(2):
+        out, res = layer.forward_local(x, residual, two_sm=two_sm)
+        torch.cuda.synchronize()
+    h = ((x.float() @ layer.weight.float().t()).to(torch.bfloat16).float() + residual.float()).to(torch.bfloat16).float()
+    y = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + layer.eps) * layer.gamma.float()).to(torch.bfloat16).float()
+    assert (res.float() - h).abs().max().item() <= 0.02 * h.abs().max().item() + 0.05
+    assert (out.float() - y).abs().max().item() <= 0.1
+    symm.destroy()
