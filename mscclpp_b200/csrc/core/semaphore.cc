@@ -86,7 +86,20 @@ struct Semaphore::Impl {
   Impl(const SemaphoreStub& l, const SemaphoreStub& r) : local(l), remote(r) {}
 };
 Semaphore::Semaphore(const SemaphoreStub& localStub, const SemaphoreStub& remoteStub)
-    : pimpl_(std::make_shared<Impl>(localStub, remoteStub)) {}
+    : pimpl_(std::make_shared<Impl>(localStub, remoteStub)) {
+  // Both stubs made in this process for different GPUs (no serialisation in between, so nothing has mapped the remote
+  // token for the local GPU yet): give the local GPU access to the remote token. Tokens are VMM allocations, which
+  // peer access does not cover; other memory goes through cudaDeviceEnablePeerAccess.
+  const auto& l = *localStub.pimpl_;
+  const auto& r = *remoteStub.pimpl_;
+  if (r.token && l.device.type == DeviceType::GPU && r.device.type == DeviceType::GPU && l.device.id != r.device.id && l.device.id >= 0) {
+    CudaDeviceGuard guard(l.device.id);
+    if (!detail::gpuGrantAccessPhysical(r.token.get(), l.device.id)) {
+      cudaError_t e = cudaDeviceEnablePeerAccess(r.device.id, 0);
+      if (e != cudaSuccess) (void)cudaGetLastError();
+    }
+  }
+}
 Connection& Semaphore::connection() { return pimpl_->local.pimpl_->connection; }
 const RegisteredMemory& Semaphore::localMemory() const { return pimpl_->local.memory(); }
 const RegisteredMemory& Semaphore::remoteMemory() const { return pimpl_->remote.memory(); }

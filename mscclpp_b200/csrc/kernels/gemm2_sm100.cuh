@@ -182,18 +182,21 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
       const int mBlk = 2 * mBlk2 + static_cast<int>(ctaRank);
       const int acc = it & 1;
       const uint32_t accPhase = (it >> 1) & 1;
+      const int row = mBlk * kBlockM + quarter * 32 + lane;
+      // lets the epilogue put loads it will need (a residual, a bias) in flight while the MMAs of this tile still run
+      epi.tileBegin(row, nBlk * Cfg::kBlockN + half * kChunksPerWarp * 32);
       ok = mbarWait(&st.tmemFull[acc], accPhase, status, budgetNs, 400 + acc);
       ok = __all_sync(0xffffffffu, ok) && (*st.abortFlag == 0);
       if (!ok) break;
       ptx::tcgen05_fence_after_sync();
-      const int row = mBlk * kBlockM + quarter * 32 + lane;
       const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::kBlockN;
-#pragma unroll 1
-      for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; c++) {
+#pragma unroll
+      for (int i = 0; i < kChunksPerWarp; i++) {
+        const int c = half * kChunksPerWarp + i;
         uint32_t v[32];
         ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
         ptx::tmem_ld_wait();
-        epi.store(row, nBlk * Cfg::kBlockN + c * 32, v);
+        epi.store(row, nBlk * Cfg::kBlockN + c * 32, v, i);  // i: index of the slice within this warp's part of the tile
       }
       ptx::tcgen05_fence_before_sync();
       __syncwarp();

@@ -258,18 +258,21 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       tileCoord(shape, tile, numMBlk, numNBlk, mBlk, nBlk);
       const int acc = it & 1;
       const uint32_t accPhase = (it >> 1) & 1;
+      const int row = mBlk * kBlockM + quarter * 32 + lane;
+      // lets the epilogue put loads it will need (a residual, a bias) in flight while the MMAs of this tile still run
+      epi.tileBegin(row, nBlk * kBlockN + half * kChunksPerWarp * 32);
       ok = mbarWait(&st.tmemFull[acc], accPhase, status, budgetNs, 400 + acc);
       ok = __all_sync(0xffffffffu, ok) && (*st.abortFlag == 0);
       if (!ok) break;
       ptx::tcgen05_fence_after_sync();
-      const int row = mBlk * kBlockM + quarter * 32 + lane;
       const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
-#pragma unroll 1
-      for (int c = half * kChunksPerWarp; c < (half + 1) * kChunksPerWarp; c++) {
+#pragma unroll
+      for (int i = 0; i < kChunksPerWarp; i++) {
+        const int c = half * kChunksPerWarp + i;
         uint32_t v[32];
         ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
         ptx::tmem_ld_wait();
-        epi.store(row, nBlk * kBlockN + c * 32, v);
+        epi.store(row, nBlk * kBlockN + c * 32, v, i);  // i: index of the slice within this warp's part of the tile
       }
       // accumulator buffer can be overwritten by the MMA warp from here on
       ptx::tcgen05_fence_before_sync();
@@ -317,7 +320,8 @@ struct StoreBf16 {
   __nv_bfloat16* D;
   int ldd;
   int M;
-  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32]) const {
+  MSCCLPP_DEVICE_INLINE void tileBegin(int, int) const {}
+  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32], int /*slice*/ = 0) const {
     if (row >= M) return;
     uint4* dst = reinterpret_cast<uint4*>(D + static_cast<size_t>(row) * ldd + col);
 #pragma unroll

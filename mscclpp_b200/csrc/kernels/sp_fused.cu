@@ -82,7 +82,8 @@ struct StoreAct {
       return x;
     }
   }
-  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32]) const {
+  MSCCLPP_DEVICE_INLINE void tileBegin(int, int) const {}
+  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32], int /*slice*/ = 0) const {
     if (row >= M) return;
     uint4* dst = reinterpret_cast<uint4*>(D + static_cast<size_t>(row) * ldd + col);
 #pragma unroll

@@ -62,7 +62,8 @@ struct PartialStoreSignal {
   int numNBlk;
   uint32_t epoch;
 
-  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32]) const {
+  MSCCLPP_DEVICE_INLINE void tileBegin(int, int) const {}
+  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32], int /*slice*/ = 0) const {
     if (row >= M) return;
     uint4* dst = reinterpret_cast<uint4*>(partial + static_cast<size_t>(row) * N + col);
 #pragma unroll
@@ -422,10 +423,25 @@ struct ResidualSumsqStore {
   bf16* h;               // [M, N]
   float* sumsq;          // [M]
   int M, N;
-  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32]) const {
+  // Residual of this thread's row for the warp's whole part of the tile (up to 4 slices of 32 columns = 256 bytes),
+  // requested at tileBegin - before the accumulator is ready - so the loads overlap the tile's MMAs.
+  uint4 pre[16];
+  int slices;  // 32-column slices per warp and tile: kBlockN / 64
+  MSCCLPP_DEVICE_INLINE void tileBegin(int row, int col0) {
+    if (residual == nullptr || row >= M) return;
+    const bf16* src = residual + static_cast<size_t>(row) * N + col0;
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      if (i < 4 * slices) pre[i] = ptx::ld_nc_na_v4(src + 8 * i);
+    }
+  }
+  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32], int slice) {
     if (row >= M) return;
     const size_t off = static_cast<size_t>(row) * N + col;
     float ss = 0.f;
+    uint4 res[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) res[i] = pre[4 * slice + i];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
       float f[8];
@@ -433,7 +449,7 @@ struct ResidualSumsqStore {
       for (int j = 0; j < 8; j++) f[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[8 * i + j])));
       if (residual != nullptr) {
         float r[8];
-        Vec16<bf16>::toFloat(ptx::ld_nc_na_v4(residual + off + 8 * i), r);
+        Vec16<bf16>::toFloat(res[i], r);
 #pragma unroll
         for (int j = 0; j < 8; j++) f[j] += r[j];
       }
@@ -692,7 +708,13 @@ cudaError_t launchGemmResidualSumsq(const void* A, const void* B, const void* re
   if (e != cudaSuccess) return e;
   e = gemm::makeTensorMapBf16(&tb, B, N, K, static_cast<uint64_t>(K) * 2, twoSm ? gemm::Config2::kBlockN / 2 : blockN);
   if (e != cudaSuccess) return e;
-  ResidualSumsqStore epi{static_cast<const bf16*>(residual), static_cast<bf16*>(h), sumsq, M, N};
+  ResidualSumsqStore epi{};
+  epi.residual = static_cast<const bf16*>(residual);
+  epi.h = static_cast<bf16*>(h);
+  epi.sumsq = sumsq;
+  epi.M = M;
+  epi.N = N;
+  epi.slices = (twoSm ? gemm::Config2::kBlockN : blockN) / 64;
   if (twoSm) return launchLocalTyped<0>(ta, tb, shape, epi, status, stream);
   switch (blockN) {
     case 64:
