@@ -121,6 +121,20 @@ def build(verbose: bool = True, jobs: int | None = None) -> dict[str, Path]:
         nccl_lib = LIB / "libmscclpp_b200_nccl.so"
         _link(nccl_o, nccl_lib, ["-L", str(LIB), "-lmscclpp_b200"], verbose)
         out["nccl"] = nccl_lib
+    audit_src = CSRC / "nccl_audit" / "audit_nccl.cc"
+    if audit_src.exists():
+        # tiny stand-alone library (no CUDA, no dependency on the core): plain g++
+        audit_lib = LIB / "libmscclpp_b200_audit_nccl.so"
+        if not audit_lib.exists() or audit_lib.stat().st_mtime < audit_src.stat().st_mtime:
+            tmp = audit_lib.with_name(audit_lib.name + f".tmp.{os.getpid()}")
+            res = subprocess.run(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", str(audit_src), "-o", str(tmp), "-ldl"],
+                                 capture_output=True, text=True)
+            if res.returncode != 0:
+                raise RuntimeError(f"audit shim build failed:\n{res.stderr}")
+            os.replace(tmp, audit_lib)
+            if verbose:
+                print(f"[link] {audit_lib.relative_to(ROOT)}", flush=True)
+        out["audit"] = audit_lib
     if bind_o:
         mod = native_module_path()
         _link(bind_o, mod, ["-L", str(LIB), "-lmscclpp_b200"], verbose)

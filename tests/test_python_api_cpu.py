@@ -201,3 +201,23 @@ def test_tuning_config_store(tmp_path):
     req.collective, req.message_size, req.dtype = "allreduce", 100, N.DataType.bfloat16
     algo = mp.Algorithm.from_callable("default_allreduce_nvls_packet", "allreduce", lambda *a: 0)
     assert sel({"allreduce": {"default_allreduce_nvls_packet": algo._algorithm}}, req).name == "default_allreduce_nvls_packet"
+
+
+def test_audit_library_redirects_nccl_loads(tmp_path):
+    """LD_AUDIT with the audit library answers a dlopen of libnccl.so.2 with the shim (host-only: the shim's
+    version query needs no GPU)."""
+    import subprocess
+    import sys
+
+    lib = mp.get_lib()
+    audit = os.path.join(lib, "libmscclpp_b200_audit_nccl.so")
+    shim = os.path.join(lib, "libmscclpp_b200_nccl.so")
+    assert os.path.exists(audit)
+    code = ("import ctypes\n"
+            "l = ctypes.CDLL('libnccl.so.2')\n"
+            "l.ncclGetErrorString.restype = ctypes.c_char_p\n"
+            "print(any('libmscclpp_b200_nccl' in x for x in open('/proc/self/maps')), l.ncclGetErrorString(5))\n")
+    env = dict(os.environ, LD_AUDIT=audit, MSCCLPP_B200_NCCL_SHIM=shim)
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert r.stdout.strip().startswith("True") and "invalid usage" in r.stdout
