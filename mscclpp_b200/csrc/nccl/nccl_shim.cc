@@ -162,6 +162,12 @@ struct ncclComm {
   int rank = 0, nranks = 1, cudaDev = 0;
   ncclComm_t real = nullptr;
   bool destroyed = false;
+  // asynchronous error reporting: the device status block is copied to pinned host memory on a stream of its own
+  DeviceStatus* hostStatus = nullptr;
+  cudaStream_t statusStream = nullptr;
+  cudaEvent_t statusEvent = nullptr;
+  bool statusPending = false;
+  ncclResult_t asyncError = ncclSuccess;
 };
 
 namespace {
@@ -184,6 +190,10 @@ ncclResult_t initComm(ncclComm_t* out, int nranks, const UniqueId& id, int rank)
       std::lock_guard<std::mutex> lock(g_heapMutex);
       g_lastHeap = c->heap;
     }
+    MSCCLPP_CUDATHROW(cudaHostAlloc(reinterpret_cast<void**>(&c->hostStatus), sizeof(DeviceStatus), cudaHostAllocDefault));
+    std::memset(c->hostStatus, 0, sizeof(DeviceStatus));
+    MSCCLPP_CUDATHROW(cudaStreamCreateWithFlags(&c->statusStream, cudaStreamNonBlocking));
+    MSCCLPP_CUDATHROW(cudaEventCreateWithFlags(&c->statusEvent, cudaEventDisableTiming));
     RealNccl& real = realNccl();
     if (real.ok) {
       ncclUniqueId realId{};
@@ -300,6 +310,9 @@ ncclResult_t ncclCommDestroy(ncclComm_t comm) {
   try {
     (void)cudaDeviceSynchronize();
     if (comm->real && realNccl().CommDestroy) realNccl().CommDestroy(comm->real);
+    if (comm->statusStream) (void)cudaStreamDestroy(comm->statusStream);
+    if (comm->statusEvent) (void)cudaEventDestroy(comm->statusEvent);
+    if (comm->hostStatus) (void)cudaFreeHost(comm->hostStatus);
     comm->executor.reset();
     comm->algos = AlgorithmCollection();
     if (comm->heap) comm->heap->destroy();
@@ -377,9 +390,29 @@ const char* ncclGetLastError(ncclComm_t) { return lastError.c_str(); }
 
 ncclResult_t ncclCommGetAsyncError(ncclComm_t comm, ncclResult_t* asyncError) {
   if (comm == nullptr || asyncError == nullptr) return ncclInvalidArgument;
-  *asyncError = ncclSuccess;
-  // a device-side wait that ran out is the asynchronous error of this library (cheap host-side peek only
-  // after work has completed; never synchronises here)
+  // A device-side wait that ran out is this library's asynchronous error. The status block lives in device memory;
+  // it is copied to pinned host memory on a non-blocking stream of its own, so this call never waits for the
+  // application's kernels: it reports what the previous copy found and starts the next one.
+  DeviceStatus* dev = comm->heap ? comm->heap->deviceComm().status : nullptr;
+  if (dev != nullptr && comm->hostStatus != nullptr && !comm->destroyed) {
+    if (comm->statusPending && cudaEventQuery(comm->statusEvent) == cudaSuccess) {
+      comm->statusPending = false;
+      if (comm->hostStatus->code != kDevOk && comm->asyncError == ncclSuccess) {
+        comm->asyncError = comm->hostStatus->code == kDevErrorCapacity ? ncclInvalidUsage : ncclRemoteError;
+        lastError = "device-side wait gave up (code " + std::to_string(comm->hostStatus->code) + ", site " +
+                    std::to_string(comm->hostStatus->where) + ", peer " + std::to_string(comm->hostStatus->peer) + ")";
+      }
+    }
+    if (!comm->statusPending) {
+      if (cudaMemcpyAsync(comm->hostStatus, dev, sizeof(DeviceStatus), cudaMemcpyDeviceToHost, comm->statusStream) == cudaSuccess &&
+          cudaEventRecord(comm->statusEvent, comm->statusStream) == cudaSuccess) {
+        comm->statusPending = true;
+      } else {
+        (void)cudaGetLastError();
+      }
+    }
+  }
+  *asyncError = comm->asyncError;
   return ncclSuccess;
 }
 

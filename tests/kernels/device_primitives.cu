@@ -90,3 +90,18 @@ extern "C" __global__ void packetWaitRunsOut(const LL16Packet* packets, DeviceSt
   uint2 v;
   if (threadIdx.x == 0 && !packets[0].read(12345u, v, status, budgetNs)) *gaveUp = 1;
 }
+
+#include <mscclpp/fifo_device.hpp>
+
+// One thread pushes `n` triggers (fst = i + 1). With nobody consuming, pushes beyond the ring size give up after
+// `budgetNs` and return UINT64_MAX: `accepted` counts the ones that went in.
+extern "C" __global__ void fifoPush(FifoDeviceHandle fifo, int n, unsigned long long budgetNs, int* accepted) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  for (int i = 0; i < n; i++) {
+    ProxyTrigger t;
+    t.fst = static_cast<uint64_t>(i + 1);
+    t.snd = 0;
+    if (fifo.push(t, nullptr, budgetNs) == UINT64_MAX) return;
+    atomicAdd(accepted, 1);
+  }
+}

@@ -121,3 +121,30 @@ def test_packet_wait_runs_out_and_reports():
     assert st[0] == 2 and st[1] == 1, st[:4]  # code = packet time-out, poisoned
     # the context is still usable
     assert int((torch.ones(4, device="cuda") * 2).sum().item()) == 8
+
+
+def test_fifo_push_with_and_without_a_consumer():
+    """GPU -> host FIFO: triggers pushed by a kernel arrive in order on the host; with a stalled consumer the ring
+    fills up and further pushes give up after their budget instead of spinning forever."""
+    from mscclpp_b200 import native
+
+    n = native()
+    k = _kernel("fifoPush")
+    fifo = n.Fifo(8)
+    accepted = torch.zeros(1, dtype=torch.int32, device="cuda")
+    raw = bytes(fifo.device_handle().raw)
+    # stalled proxy: nobody pops; 8 slots accept 8 triggers, the 9th waits 30 ms and gives up
+    params = raw + struct.pack("iQP", 12, 30_000_000, accepted.data_ptr())
+    pad = (-len(raw)) % 8
+    params = raw + b"\x00" * pad + struct.pack("iQP", 12, 30_000_000, accepted.data_ptr())
+    k.launch_kernel(params, 1, 32, stream=torch.cuda.current_stream())
+    torch.cuda.synchronize()
+    assert int(accepted.item()) == 8
+    got = []
+    while True:
+        t = fifo.poll()
+        if t.fst == 0:
+            break
+        got.append(t.fst)
+        fifo.pop()
+    assert got == list(range(1, 9))
