@@ -178,8 +178,15 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
   bool healthy = true;
   // owned row j -> global row: unit = rank + (j / rpu) * world, row = unit * rpu + j % rpu
 #pragma unroll 1
+  // Lane 0 draws the row after the current one while the current one is in flight, so the atomic's round trip to L2
+  // is off the per-row critical path. (A drawn row is always processed or lies beyond the last one.)
+  int drawn = 0;
+  if (lane == 0) drawn = static_cast<int>(atomicAdd(rowCounter, 1u));
   for (;;) {
-    if (lane == 0) nextRow[group] = healthy ? static_cast<int>(atomicAdd(rowCounter, 1u)) : ownedRows;
+    if (lane == 0) {
+      nextRow[group] = healthy ? drawn : ownedRows;
+      if (healthy && drawn < ownedRows) drawn = static_cast<int>(atomicAdd(rowCounter, 1u));
+    }
     groupBarrier(group);
     const int j = nextRow[group];
     groupBarrier(group);  // nextRow may be rewritten from here on

@@ -221,3 +221,56 @@ def test_audit_library_redirects_nccl_loads(tmp_path):
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stderr[-2000:]
     assert r.stdout.strip().startswith("True") and "invalid usage" in r.stdout
+
+
+def test_comm_group_over_ethernet_on_cpu():
+    """CommGroup (bootstrap + communicator + helpers) with two CPU ranks as threads: connections over the Ethernet
+    transport, memory registration and exchange, semaphores, a write that lands in the peer's numpy buffer."""
+    import socket
+    import threading
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    results = {}
+
+    def rank_main(rank):
+        try:
+            group = mp.CommGroup(interfaceIpPortTrio=f"127.0.0.1:{port}", rank=rank, size=2)
+            assert (group.my_rank, group.nranks) == (rank, 2)
+            peer = 1 - rank
+            cfg = N.EndpointConfig(N.Transport.Ethernet, N.Device(N.DeviceType.CPU))
+            conns = group.make_connection([peer], cfg)
+            buf = np.full(256, rank + 1, dtype=np.int64)
+            mems = group.register_tensor_with_connections(buf, conns)
+            assert set(mems) == {0, 1}
+            sems = group.make_semaphores(conns)
+            h2h = N.Host2HostSemaphore(sems[peer])
+            if rank == 0:
+                conns[peer].write(mems[peer], 0, mems[rank], 0, buf.nbytes)
+                conns[peer].flush()
+                h2h.signal()
+            else:
+                h2h.wait()
+                results["received"] = buf.copy()
+            group.barrier()
+            # bootstrap point-to-point helpers
+            msg = np.arange(4, dtype=np.int32) + rank
+            if rank == 0:
+                group.send(msg, 1, 5)
+            else:
+                got = np.zeros(4, dtype=np.int32)
+                group.recv(got, 0, 5)
+                results["msg"] = got
+            group.barrier()
+        except Exception as e:  # noqa: BLE001
+            results[f"error{rank}"] = repr(e)
+
+    threads = [threading.Thread(target=rank_main, args=(r,)) for r in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(120)
+    assert not any(k.startswith("error") for k in results), results
+    assert (results["received"] == 1).all()
+    assert results["msg"].tolist() == [0, 1, 2, 3]
