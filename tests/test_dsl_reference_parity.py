@@ -13,7 +13,7 @@ import sys
 
 import pytest
 
-REF_PY = os.environ.get("MSCCLPP_REFERENCE_PYTHON", "/root/reference/python")
+REF_PY = os.environ.get("MSCCLPP_REFERENCE_PYTHON", os.path.join(os.path.expanduser("~"), "reference", "python"))
 EXAMPLES = os.path.join(REF_PY, "mscclpp", "language", "tests")
 RUNNER = os.path.join(os.path.dirname(__file__), "_dsl_runner.py")
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "dsl_plan_digests.json")
