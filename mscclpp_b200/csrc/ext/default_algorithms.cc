@@ -118,6 +118,39 @@ std::shared_ptr<Algorithm> makeTwoShot(const std::string& name, const std::strin
       0, UINT64_MAX, CollectiveBufferMode::Any);
 }
 
+// Broadcast: the root's `in` goes to every rank's `out` (staged through the heap when `out` is an ordinary buffer).
+// The root travels in extras["root"].
+std::shared_ptr<Algorithm> makeBroadcast(std::shared_ptr<SymmetricHeap> heap, bool nvls, std::shared_ptr<Staging> staging) {
+  return std::make_shared<NativeAlgorithm>(
+      "default_broadcast", "broadcast", nullptr,
+      [heap, nvls, staging](const void* in, void* out, size_t inBytes, size_t outBytes, DataType, ReduceOp, cudaStream_t stream, int nBlocks,
+                            int nThreads, bool, const std::unordered_map<std::string, uintptr_t>& extras) {
+        auto it = extras.find("root");
+        if (it == extras.end() || inBytes != outBytes) return CommResult::InvalidArgument;
+        const int root = static_cast<int>(it->second);
+        const size_t padded = (inBytes + 15) / 16 * 16;
+        if (nBlocks <= 0 || nThreads <= 0) gridFor(padded, nvls, nBlocks, nThreads);
+        // every rank writes into / receives in a heap buffer at the same offset; the root's source may be anywhere
+        const bool direct = padded == inBytes && heap->contains(out, outBytes);
+        void* kout = direct ? out : staging->ensure(staging->out, staging->outBytes, padded);
+        const void* kin = in;
+        if (heap->rank() == root && padded != inBytes) {
+          // pad the source through the staging buffer so that the kernel moves whole 16-byte words
+          kin = staging->ensure(staging->in, staging->inBytes, padded);
+          if (cudaMemcpyAsync(const_cast<void*>(kin), in, inBytes, cudaMemcpyDeviceToDevice, stream) != cudaSuccess) return CommResult::UnhandledCudaError;
+        } else if (padded != inBytes) {
+          (void)staging->ensure(staging->in, staging->inBytes, padded);  // keep the allocation sequence equal on all ranks
+        }
+        CollArgs a = baseArgs(*heap, kin, kout, padded, kBroadcast, nvls);
+        a.root = root;
+        cudaError_t e = launchTwoShot(a, DataType::UINT32, SUM, nBlocks, nThreads, stream);
+        if (e != cudaSuccess) return toResult(e);
+        if (kout != out && cudaMemcpyAsync(out, kout, outBytes, cudaMemcpyDeviceToDevice, stream) != cudaSuccess) return CommResult::UnhandledCudaError;
+        return CommResult::Success;
+      },
+      0, UINT64_MAX, CollectiveBufferMode::Any);
+}
+
 }  // namespace
 
 std::shared_ptr<AlgorithmCollectionBuilder> AlgorithmCollectionBuilder::getInstance() {
@@ -170,6 +203,7 @@ AlgorithmCollection AlgorithmCollectionBuilder::buildDefaultAlgorithms(std::shar
   add(makeTwoShot("default_allgather_fullmesh", "allgather", heap, kAllGather, false, true, staging));
   add(makeTwoShot("default_allgather_fullmesh2", "allgather", heap, kAllGather, nvls, true, staging));
   add(makeTwoShot("default_reducescatter_zero_copy", "reducescatter", heap, kReduceScatter, nvls, true, staging));
+  add(makeBroadcast(heap, nvls, staging));
 
   // DSL plans installed under <cache>/default/*.json
   const std::string dir = env()->cacheDir + "/default";
@@ -228,6 +262,7 @@ std::shared_ptr<Algorithm> selectDefaultAlgorithm(
     if ((n * request.worldSize) % (16 * static_cast<size_t>(request.worldSize)) != 0) return nullptr;
     return get("default_allgather_fullmesh2");
   }
+  if (request.collective == "broadcast") return get("default_broadcast");
   if (request.collective == "reducescatter") {
     if (n % (16 * static_cast<size_t>(request.worldSize)) != 0) return nullptr;
     return get("default_reducescatter_zero_copy");

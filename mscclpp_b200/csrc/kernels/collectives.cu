@@ -359,6 +359,17 @@ __global__ void __launch_bounds__(512, 1) twoShotKernel(CollArgs a) {
           scatterStore<kNvls>(c, rank, outOff, off, scaleRow<T>(x, rinv, gamma, ru));
         }
       }
+    } else if (a.mode == kBroadcast) {
+      // the root streams its buffer into every rank's `out` (one multimem.st or one peer store per rank and word)
+      if (rank == a.root) {
+        const uint64_t nunits = a.bytes / 16;
+        const uint64_t local = c.peerBase[rank];
+        for (uint64_t u = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < nunits;
+             u += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+          const uint4 v = *reinterpret_cast<const uint4*>(local + inOff + u * 16);
+          scatterStore<kNvls>(c, rank, outOff, u * 16, v);
+        }
+      }
     } else if (a.mode == kAllGather) {
       // `in` = my slice (bytes/world), `out` = whole buffer on every rank
       const uint64_t sliceUnits = a.bytes / 16 / world;
@@ -441,7 +452,7 @@ cudaError_t launchTwoShotTyped(const CollArgs& a, int nBlocks, int nThreads, cud
       return cudaErrorInvalidValue;
     }
   }
-  if (a.nvls && a.mode != kAllGather) {
+  if (a.nvls && a.mode != kAllGather && a.mode != kBroadcast) {
     if constexpr (nvlsReducible<T, Op>()) {
       return launchMaybeCooperative(twoShotKernel<T, Op, true, false>, a, nBlocks, nThreads, s);
     } else {
@@ -494,7 +505,8 @@ cudaError_t launchTwoShot(const CollArgs& args, DataType dtype, ReduceOp op, int
   if (args.bytes % 16 != 0) return cudaErrorInvalidValue;
   if (nBlocks < 1 || nBlocks > kBarrierSlots || nThreads < 32 || nThreads > 512) return cudaErrorInvalidValue;
   if (nThreads < args.comm.world) return cudaErrorInvalidValue;
-  if (args.mode != kAllReduce && (args.bytes / 16) % args.comm.world != 0) return cudaErrorInvalidValue;
+  if ((args.mode == kReduceScatter || args.mode == kAllGather) && (args.bytes / 16) % args.comm.world != 0) return cudaErrorInvalidValue;
+  if (args.mode == kBroadcast && (args.root < 0 || args.root >= args.comm.world)) return cudaErrorInvalidValue;
   if (args.norm && ((static_cast<uint64_t>(args.hidden) * dataTypeSize(dtype)) % 16 != 0)) return cudaErrorInvalidValue;
   MSCCLPP_DISPATCH_TYPE_OP(launchTwoShotTyped, dtype, op, args, nBlocks, nThreads, stream);
 }

@@ -10,13 +10,13 @@
 
 namespace mscclpp {
 
-enum CollMode : int { kAllReduce = 0, kReduceScatter = 1, kAllGather = 2 };
+enum CollMode : int { kAllReduce = 0, kReduceScatter = 1, kAllGather = 2, kBroadcast = 3 };
 
 struct CollArgs {
   DeviceComm comm;
   const void* in;      // local buffer of rank comm.rank; emulated rank e uses in + e * emuStride
   void* out;
-  uint64_t bytes;      // allreduce: buffer bytes; reduce-scatter: input bytes; allgather: output bytes
+  uint64_t bytes;      // allreduce / broadcast: buffer bytes; reduce-scatter: input bytes; allgather: output bytes
   uint64_t emuStride;  // 0 unless several ranks are emulated in one launch on one GPU
   int emuRanks;        // gridDim.y (1 = real multi-GPU mode)
   int mode;            // CollMode
@@ -30,6 +30,7 @@ struct CollArgs {
   void* residualOut;        // [rows, hidden] local (may be null)
   const void* gamma;        // [hidden] (may be null = all ones)
   int broadcastResidual;    // two-shot only: write residualOut on every rank, not just the owner's rows
+  int root;                 // kBroadcast: the rank whose `in` is copied into everybody's `out`
 };
 
 // One-shot LL16 allreduce (every rank sends its whole buffer to every peer as packets).

@@ -524,8 +524,30 @@ ncclResult_t ncclBroadcast(const void* sendbuff, void* recvbuff, size_t count, n
     if (sendbuff != recvbuff && cudaMemcpyAsync(recvbuff, sendbuff, bytes, cudaMemcpyDeviceToDevice, stream) != cudaSuccess) return ncclUnhandledCudaError;
     return ncclSuccess;
   }
+  if (root < 0 || root >= comm->nranks) return fail(ncclInvalidArgument, "broadcast: bad root");
+  if (!forcedFallback("broadcast") && bytes > 0) {
+    CollectiveRequest req;
+    req.worldSize = comm->nranks;
+    req.nRanksPerNode = comm->bootstrap->getNranksPerNode();
+    req.rank = comm->rank;
+    req.inputBuffer = sendbuff;
+    req.outputBuffer = recvbuff;
+    req.messageSize = bytes;
+    req.stream = stream;
+    req.collective = "broadcast";
+    req.dtype = DataType::UINT8;
+    auto algo = comm->algos.selectAlgorithm(req);
+    if (algo) {
+      // the root may pass a null / unrelated recvbuff semantics-wise equal to sendbuff: NCCL requires recvbuff everywhere
+      CommResult r = algo->execute(comm->comm, sendbuff != nullptr ? sendbuff : recvbuff, recvbuff, bytes, bytes, DataType::UINT8, NOP, stream,
+                                   comm->executor, 0, 0, false, {{"root", static_cast<uintptr_t>(root)}}, DataType::AUTO);
+      if (r == CommResult::Success) return ncclSuccess;
+      if (r != CommResult::InvalidUsage && r != CommResult::InvalidArgument) return fail(toNccl(r), "broadcast: default_broadcast failed");
+    }
+  }
+  if (bytes == 0) return ncclSuccess;
   if (comm->real != nullptr) return realNccl().Broadcast(sendbuff, recvbuff, count, datatype, root, comm->real, stream);
-  return fail(ncclInvalidUsage, "broadcast: no algorithm registered and no fallback NCCL is loaded (set MSCCLPP_NCCL_LIB_PATH)");
+  return fail(ncclInvalidUsage, "broadcast: no algorithm handles this call and no fallback NCCL is loaded (set MSCCLPP_NCCL_LIB_PATH)");
 }
 
 ncclResult_t ncclBcast(void* buff, size_t count, ncclDataType_t datatype, int root, ncclComm_t comm, cudaStream_t stream) {

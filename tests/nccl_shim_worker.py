@@ -48,11 +48,11 @@ def main():
         tot = sum(r + 1 for r in range(world))
         want = (torch.arange(world * n, dtype=torch.float32) % 17)[rank * n:(rank + 1) * n] * tot
         ok &= bool(torch.equal(rs.cpu(), want))
-    # broadcast: served by the fallback library when one is configured
-    if os.environ.get("MSCCLPP_NCCL_LIB_PATH"):
-        b = torch.full((100,), float(rank), device=dev)
-        dist.broadcast(b, src=world - 1)
-        ok &= bool((b == world - 1).all().item())
+    # broadcast: native (root streams into every rank's buffer), any size, any root
+    for n, root in ((100, world - 1), (1 << 20, 0), ((1 << 18) + 3, world // 2)):
+        b = torch.full((n,), float(rank), device=dev, dtype=torch.float16)
+        dist.broadcast(b, src=root)
+        ok &= bool((b == root).all().item())
     # CUDA-graph capture of an allreduce
     y = torch.ones(1 << 16, device=dev, dtype=torch.bfloat16)
     s = torch.cuda.Stream()
