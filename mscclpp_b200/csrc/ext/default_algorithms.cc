@@ -98,7 +98,8 @@ std::shared_ptr<Algorithm> makeTwoShot(const std::string& name, const std::strin
         // Peers read `in` (allreduce, reducescatter) and write `out` (allreduce, allgather): only those sides
         // must live in the heap. An allreduce whose size is not a multiple of 16 bytes is padded in staging.
         const bool padded = mode == kAllReduce && inBytes % 16 != 0;
-        const bool needIn = mode != kAllGather && (padded || !heap->contains(in, inBytes));
+        // all-to-all reads `in` locally only, like all-gather
+        const bool needIn = mode != kAllGather && mode != kAllToAll && (padded || !heap->contains(in, inBytes));
         const bool needOut = mode != kReduceScatter && (padded || !heap->contains(out, outBytes));
         if (needIn || needOut) {
           if (!staged) return CommResult::InvalidUsage;
@@ -204,6 +205,7 @@ AlgorithmCollection AlgorithmCollectionBuilder::buildDefaultAlgorithms(std::shar
   add(makeTwoShot("default_allgather_fullmesh2", "allgather", heap, kAllGather, nvls, true, staging));
   add(makeTwoShot("default_reducescatter_zero_copy", "reducescatter", heap, kReduceScatter, nvls, true, staging));
   add(makeBroadcast(heap, nvls, staging));
+  add(makeTwoShot("default_alltoall", "alltoall", heap, kAllToAll, false, true, staging));
 
   // DSL plans installed under <cache>/default/*.json
   const std::string dir = env()->cacheDir + "/default";
@@ -263,6 +265,10 @@ std::shared_ptr<Algorithm> selectDefaultAlgorithm(
     return get("default_allgather_fullmesh2");
   }
   if (request.collective == "broadcast") return get("default_broadcast");
+  if (request.collective == "alltoall") {
+    if (n % (16 * static_cast<size_t>(request.worldSize)) != 0) return nullptr;
+    return get("default_alltoall");
+  }
   if (request.collective == "reducescatter") {
     if (n % (16 * static_cast<size_t>(request.worldSize)) != 0) return nullptr;
     return get("default_reducescatter_zero_copy");

@@ -359,6 +359,19 @@ __global__ void __launch_bounds__(512, 1) twoShotKernel(CollArgs a) {
           scatterStore<kNvls>(c, rank, outOff, off, scaleRow<T>(x, rinv, gamma, ru));
         }
       }
+    } else if (a.mode == kAllToAll) {
+      // chunk p of my `in` becomes chunk `rank` of rank p's `out`: plain peer stores, own chunk first
+      const uint64_t chunkUnits = a.bytes / 16 / world;
+      const uint64_t local = c.peerBase[rank];
+      for (int i = 0; i < world; i++) {
+        const int p = (rank + i) % world;
+        const uint64_t dst = c.peerBase[p] + outOff + static_cast<uint64_t>(rank) * chunkUnits * 16;
+        const uint64_t src = local + inOff + static_cast<uint64_t>(p) * chunkUnits * 16;
+        for (uint64_t u = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < chunkUnits;
+             u += static_cast<uint64_t>(gridDim.x) * blockDim.x) {
+          ptx::st_na_v4(reinterpret_cast<void*>(dst + u * 16), *reinterpret_cast<const uint4*>(src + u * 16));
+        }
+      }
     } else if (a.mode == kBroadcast) {
       // the root streams its buffer into every rank's `out` (one multimem.st or one peer store per rank and word)
       if (rank == a.root) {
@@ -452,7 +465,7 @@ cudaError_t launchTwoShotTyped(const CollArgs& a, int nBlocks, int nThreads, cud
       return cudaErrorInvalidValue;
     }
   }
-  if (a.nvls && a.mode != kAllGather && a.mode != kBroadcast) {
+  if (a.nvls && a.mode != kAllGather && a.mode != kBroadcast && a.mode != kAllToAll) {
     if constexpr (nvlsReducible<T, Op>()) {
       return launchMaybeCooperative(twoShotKernel<T, Op, true, false>, a, nBlocks, nThreads, s);
     } else {
@@ -505,7 +518,7 @@ cudaError_t launchTwoShot(const CollArgs& args, DataType dtype, ReduceOp op, int
   if (args.bytes % 16 != 0) return cudaErrorInvalidValue;
   if (nBlocks < 1 || nBlocks > kBarrierSlots || nThreads < 32 || nThreads > 512) return cudaErrorInvalidValue;
   if (nThreads < args.comm.world) return cudaErrorInvalidValue;
-  if ((args.mode == kReduceScatter || args.mode == kAllGather) && (args.bytes / 16) % args.comm.world != 0) return cudaErrorInvalidValue;
+  if ((args.mode == kReduceScatter || args.mode == kAllGather || args.mode == kAllToAll) && (args.bytes / 16) % args.comm.world != 0) return cudaErrorInvalidValue;
   if (args.mode == kBroadcast && (args.root < 0 || args.root >= args.comm.world)) return cudaErrorInvalidValue;
   if (args.norm && ((static_cast<uint64_t>(args.hidden) * dataTypeSize(dtype)) % 16 != 0)) return cudaErrorInvalidValue;
   MSCCLPP_DISPATCH_TYPE_OP(launchTwoShotTyped, dtype, op, args, nBlocks, nThreads, stream);

@@ -10,13 +10,13 @@
 
 namespace mscclpp {
 
-enum CollMode : int { kAllReduce = 0, kReduceScatter = 1, kAllGather = 2, kBroadcast = 3 };
+enum CollMode : int { kAllReduce = 0, kReduceScatter = 1, kAllGather = 2, kBroadcast = 3, kAllToAll = 4 };
 
 struct CollArgs {
   DeviceComm comm;
   const void* in;      // local buffer of rank comm.rank; emulated rank e uses in + e * emuStride
   void* out;
-  uint64_t bytes;      // allreduce / broadcast: buffer bytes; reduce-scatter: input bytes; allgather: output bytes
+  uint64_t bytes;      // allreduce / broadcast / all-to-all: buffer bytes; reduce-scatter: input bytes; allgather: output bytes
   uint64_t emuStride;  // 0 unless several ranks are emulated in one launch on one GPU
   int emuRanks;        // gridDim.y (1 = real multi-GPU mode)
   int mode;            // CollMode

@@ -563,9 +563,18 @@ ncclResult_t ncclReduce(const void* sendbuff, void* recvbuff, size_t count, nccl
 
 ncclResult_t ncclAlltoAll(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm,
                           cudaStream_t stream) {
+  // `count` elements go to (and come from) every rank
   if (comm == nullptr) return ncclInvalidArgument;
-  if (comm->real != nullptr && realNccl().AlltoAll) return realNccl().AlltoAll(sendbuff, recvbuff, count, datatype, comm->real, stream);
-  return fail(ncclInvalidUsage, "alltoall: handled by the fallback NCCL only (set MSCCLPP_NCCL_LIB_PATH)");
+  const size_t total = count * typeSize(datatype) * static_cast<size_t>(comm->nranks);
+  if (comm->nranks == 1) {
+    if (sendbuff != recvbuff && cudaMemcpyAsync(recvbuff, sendbuff, total, cudaMemcpyDeviceToDevice, stream) != cudaSuccess) return ncclUnhandledCudaError;
+    return ncclSuccess;
+  }
+  if (sendbuff == recvbuff) return fail(ncclInvalidUsage, "alltoall: in-place operation is not supported");
+  return runCollective(comm, "alltoall", "alltoall", sendbuff, recvbuff, total, total, total, ncclUint8, ncclSum, stream, [&] {
+    if (realNccl().AlltoAll) return realNccl().AlltoAll(sendbuff, recvbuff, count, datatype, comm->real, stream);
+    return fail(ncclInvalidUsage, "alltoall: the fallback NCCL has no ncclAlltoAll");
+  });
 }
 
 ncclResult_t ncclSend(const void* sendbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream) {

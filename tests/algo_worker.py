@@ -104,6 +104,24 @@ def main():
     torch.cuda.synchronize()
     report("reducescatter/user", rc == 0 and bool((out == world * (world + 1) / 2).all().item()))
 
+    # all-to-all: chunk p of my input becomes chunk `rank` of rank p's output
+    a2a = coll.get_by_name("default_alltoall")
+    send = (torch.arange(world * per, device=dev, dtype=torch.float32) + 1000000 * rank)
+    recv = torch.zeros(world * per, device=dev, dtype=torch.float32)
+    rc = a2a.execute(None, send.data_ptr(), recv.data_ptr(), world * per * 4, world * per * 4, n.DataType.uint8, n.ReduceOp.NOP, stream, executor)
+    torch.cuda.synchronize()
+    want = torch.cat([torch.arange(rank * per, (rank + 1) * per, device=dev, dtype=torch.float32) + 1000000 * p for p in range(world)])
+    report("alltoall/user", rc == 0 and bool(torch.equal(recv, want)))
+
+    # broadcast from the last rank, odd size (padded through staging)
+    bc = coll.get_by_name("default_broadcast")
+    nb = 100003
+    buf = torch.full((nb,), float(rank), device=dev, dtype=torch.float16)
+    rc = bc.execute(None, buf.data_ptr(), buf.data_ptr(), nb * 2, nb * 2, n.DataType.uint8, n.ReduceOp.NOP, stream, executor,
+                    extras={"root": world - 1})
+    torch.cuda.synchronize()
+    report("broadcast/user_odd_size", rc == 0 and bool((buf == world - 1).all().item()))
+
     # a DSL algorithm compiled at run time runs through the same interface
     from mscclpp_b200.default_algos import allreduce_allpairs, make_spec
     from mscclpp_b200.language.collectives import AllReduce
