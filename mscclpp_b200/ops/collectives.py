@@ -17,7 +17,7 @@ import torch
 from .._core import native
 from .._core.symm import SymmetricMemory, torch_dtype_to_native
 
-MODE_ALLREDUCE, MODE_REDUCE_SCATTER, MODE_ALLGATHER = 0, 1, 2
+MODE_ALLREDUCE, MODE_REDUCE_SCATTER, MODE_ALLGATHER, MODE_BROADCAST, MODE_ALLTOALL = 0, 1, 2, 3, 4
 
 # bytes at or below which the one-shot LL path wins (tuned on 8xB200; see profiles/)
 LL_MAX_BYTES = 512 << 10
@@ -119,6 +119,30 @@ def all_gather(symm: SymmetricMemory, inp: torch.Tensor, out: torch.Tensor, nvls
     blocks, threads = _grid_for(_nbytes(out), "nvls_zero_copy" if nvls else "rsag_zero_copy", symm.world)
     n.two_shot(symm.heap, inp.data_ptr(), out.data_ptr(), _nbytes(out), torch_dtype_to_native(inp.dtype), _op("sum"),
                MODE_ALLGATHER, n_blocks or blocks, threads, _stream(stream), nvls)
+    return out
+
+
+def broadcast(symm: SymmetricMemory, inp: torch.Tensor, out: torch.Tensor, root: int, nvls: Optional[bool] = None,
+              stream: Optional[torch.cuda.Stream] = None, n_blocks: int = 0) -> torch.Tensor:
+    """Every rank's `out` = the root's `inp` (the root streams its buffer: one multimem.st, or one store per peer, per
+    16 bytes). `out` from symm.tensor(); sizes multiples of 16 bytes."""
+    n = native.load()
+    nvls = symm.nvls if nvls is None else nvls
+    assert _nbytes(inp) == _nbytes(out) and 0 <= root < symm.world
+    blocks, threads = _grid_for(_nbytes(out), "nvls_zero_copy" if nvls else "rsag_zero_copy", symm.world)
+    n.two_shot(symm.heap, inp.data_ptr(), out.data_ptr(), _nbytes(out), n.DataType.uint32, _op("sum"), MODE_BROADCAST, n_blocks or blocks,
+               threads, _stream(stream), nvls, root)
+    return out
+
+
+def all_to_all(symm: SymmetricMemory, inp: torch.Tensor, out: torch.Tensor, stream: Optional[torch.cuda.Stream] = None,
+               n_blocks: int = 0) -> torch.Tensor:
+    """Chunk p of `inp` becomes chunk `rank` of rank p's `out` (equal chunks, peer stores). `out` from symm.tensor()."""
+    n = native.load()
+    assert _nbytes(inp) == _nbytes(out) and _nbytes(inp) % (16 * symm.world) == 0 and inp.data_ptr() != out.data_ptr()
+    blocks, threads = _grid_for(_nbytes(out), "rsag_zero_copy", symm.world)
+    n.two_shot(symm.heap, inp.data_ptr(), out.data_ptr(), _nbytes(out), n.DataType.uint32, _op("sum"), MODE_ALLTOALL, n_blocks or blocks,
+               threads, _stream(stream), False, 0)
     return out
 
 

@@ -556,3 +556,34 @@ def test_fp8_allreduce_accumulates_in_fp32(world, dtype, algo):
         assert torch.equal(got, oracle), (r, (got - oracle).abs().max().item())
     assert (oracle - exact).abs().mean().item() <= (stepwise - exact).abs().mean().item() + 1e-9
     symm.destroy()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_broadcast_and_all_to_all(world):
+    """Native broadcast (root streams into every rank) and all-to-all (peer stores), all ranks emulated on one GPU."""
+    from mscclpp_b200.ops import all_to_all, broadcast
+
+    symm = _symm(world)
+    per = 4096
+    src = symm.tensor((world * per,), torch.float32)
+    dst = symm.tensor((world * per,), torch.float32)
+    for r in range(world):
+        symm.rank_view(src, r).copy_(torch.arange(world * per, device="cuda", dtype=torch.float32) + 100000 * r)
+    for root in (0, world - 1):
+        for r in range(world):
+            symm.rank_view(dst, r).zero_()
+        broadcast(symm, src, dst, root=root, nvls=False, n_blocks=4)
+        torch.cuda.synchronize()
+        symm.check()
+        want = symm.rank_view(src, root)
+        for r in range(world):
+            assert torch.equal(symm.rank_view(dst, r), want)
+    for r in range(world):
+        symm.rank_view(dst, r).zero_()
+    all_to_all(symm, src, dst, n_blocks=4)
+    torch.cuda.synchronize()
+    symm.check()
+    for r in range(world):
+        want = torch.cat([symm.rank_view(src, p)[r * per:(r + 1) * per] for p in range(world)])
+        assert torch.equal(symm.rank_view(dst, r), want)
+    symm.destroy()
