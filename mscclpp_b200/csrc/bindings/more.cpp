@@ -50,12 +50,13 @@ void registerMoreBindings(py::module_& m) {
       "tp_fused",
       [](SymmetricHeap& heap, std::vector<uintptr_t> a, std::vector<uintptr_t> b, uintptr_t partial, uintptr_t residualIn,
          uintptr_t residualOut, uintptr_t out, uintptr_t gamma, uintptr_t rinv, int M, int N, int K, float eps, int blockN,
-         int numGemmCtas, int numReducers, int rowsPerUnit, int mode, bool nvls, uintptr_t stream) {
+         int numGemmCtas, int numReducers, int rowsPerUnit, int mode, bool nvls, uintptr_t stream, uintptr_t timeline) {
         TpFusedArgs args{};
         args.comm = heap.deviceComm();
         args.shape.M = M;
         args.shape.N = N;
         args.shape.K = K;
+        args.timeline = reinterpret_cast<unsigned long long*>(timeline);
         args.partial = reinterpret_cast<__nv_bfloat16*>(partial);
         args.residualIn = reinterpret_cast<const __nv_bfloat16*>(residualIn);
         args.residualOut = reinterpret_cast<__nv_bfloat16*>(residualOut);
@@ -79,7 +80,7 @@ void registerMoreBindings(py::module_& m) {
       py::arg("heap"), py::arg("a"), py::arg("b"), py::arg("partial"), py::arg("residual_in"), py::arg("residual_out"),
       py::arg("out"), py::arg("gamma"), py::arg("rinv"), py::arg("m"), py::arg("n"), py::arg("k"), py::arg("eps"),
       py::arg("block_n") = 256, py::arg("num_gemm_ctas") = 0, py::arg("num_reducers") = 0, py::arg("rows_per_unit") = 0,
-      py::arg("mode") = 0, py::arg("nvls") = false, py::arg("stream") = 0);
+      py::arg("mode") = 0, py::arg("nvls") = false, py::arg("stream") = 0, py::arg("timeline") = 0);
   m.def(
       "all_gather_gemm",
       [](SymmetricHeap& heap, uintptr_t aLocal, uintptr_t aFull, std::vector<uintptr_t> b, uintptr_t d, int M, int N, int K, int blockN,

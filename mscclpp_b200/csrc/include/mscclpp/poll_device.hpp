@@ -122,7 +122,8 @@ MSCCLPP_DEVICE_INLINE bool waitGreaterEqualBackoff(const uint32_t* p, uint32_t e
       return false;
     }
   }
-  ptx::fence_acq_rel_sys();
+  // Acquire through a load, not a fence: a system-scope fence would also wait for this thread's earlier peer stores.
+  (void)ptx::ld_acquire_sys(p);
   return true;
 }
 

@@ -152,8 +152,8 @@ MSCCLPP_DEVICE_INLINE void copierCta(const AgGemmArgs& a, int rank, uint32_t epo
       int mBlk;
       locate(p, src, dst, mBlk);
       ptx::fence_proxy_async();
-      __threadfence();
-      ptx::st_release_sys(blockFlag(c, rank, mBlk), epoch);
+      __threadfence();  // GPU scope is enough: the flag and the rows are in this GPU's memory and read by its own GEMM CTAs
+      ptx::st_relaxed_sys(blockFlag(c, rank, mBlk), epoch);
     };
     int issued = 0;
     for (; issued < kRingStages - 1 && issued < P; issued++) issueLoad(issued);

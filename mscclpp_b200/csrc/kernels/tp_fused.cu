@@ -61,6 +61,7 @@ struct PartialStoreSignal {
   int numUnits;
   int numNBlk;
   uint32_t epoch;
+  unsigned long long* tl;  // this CTA's time-line words or null
 
   MSCCLPP_DEVICE_INLINE void tileBegin(int, int) const {}
   MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32], int /*slice*/ = 0) const {
@@ -83,9 +84,23 @@ struct PartialStoreSignal {
   // pattern: fence, count, fence), so a row block costs `world` small NVLink stores, not world x tiles.
   MSCCLPP_DEVICE_INLINE void tileDone(int mBlk, int /*nBlk*/, int tid) const {
     if (tid != 0) return;
+    unsigned long long tIn = 0;
+    if (tl) {
+      tIn = ptx::globaltimer();
+      if (tl[14] != 0 && tIn - tl[14] > tl[15]) {
+        tl[15] = tIn - tl[14];  // longest time between two finished tiles of this CTA ...
+        tl[7] = tIn;            // ... and when it ended
+      }
+      tl[14] = tIn;
+    }
     __threadfence();
     uint32_t* counter = tileCounter(*comm, rank, mBlk);
     const uint32_t done = atomicAdd(counter, 1u) + 1u;
+    if (tl) {
+      const unsigned long long dt = ptx::globaltimer() - tIn;
+      tl[11] += dt;
+      if (dt > tl[12]) tl[12] = dt;
+    }
     if (done != static_cast<uint32_t>(numNBlk)) return;
     *counter = 0;  // every tile of this row block has been counted: ready for the next launch
     __threadfence();
@@ -93,12 +108,16 @@ struct PartialStoreSignal {
     const int u0 = (mBlk * gemm::kBlockM) / rowsPerUnit;
     int u1 = ((mBlk + 1) * gemm::kBlockM + rowsPerUnit - 1) / rowsPerUnit;
     if (u1 > numUnits) u1 = numUnits;
-    ptx::fence_acq_rel_sys();
+    // The fence above has GPU scope on purpose. The tiles live in THIS GPU's memory, whose L2 every peer's load (plain
+    // or multimem) goes through, so "performed at this GPU's L2" is all a reader needs; the flag goes out after it.
+    // A system-scope fence here also waits for this SM's share of the NVLink queues to drain: once the reducers
+    // saturate the links that took tens of microseconds per row block and stalled the GEMM CTA that published it.
     for (int o = 0; o < world; o++) {
       // does rank o own one of the units [u0, u1)?
       const int first = (o - (u0 % world) + world) % world;
-      if (first < u1 - u0) ptx::st_release_sys(readyFlag(*comm, o, mBlk, rank), epoch);
+      if (first < u1 - u0) ptx::st_relaxed_sys(readyFlag(*comm, o, mBlk, rank), epoch);
     }
+    if (tl) tl[13] += ptx::globaltimer() - tIn;
   }
 };
 
@@ -176,6 +195,9 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
   uint32_t* rowCounter = &control(c, rank)->gridSync[7];  // zero at launch start (finishLaunch re-arms it)
   int readyMb = -1;
   bool healthy = true;
+  // optional stamps (group 0, lane 0 of every CTA)
+  unsigned long long* tl = (a.timeline != nullptr && blockIdx.y == 0 && threadIdx.x == 0) ? a.timeline + static_cast<size_t>(blockIdx.x) * kTimelineWords : nullptr;
+  unsigned long long tlRows = 0, tlWait = 0, tlWork = 0, tlMark = 0, tlGather = 0, tlMath = 0, tlScatter = 0, tlPhase = 0;
   // owned row j -> global row: unit = rank + (j / rpu) * world, row = unit * rpu + j % rpu
 #pragma unroll 1
   // Lane 0 draws the row after the current one while the current one is in flight, so the atomic's round trip to L2
@@ -209,6 +231,7 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
     }
     // ---- wait until every rank has produced every tile of the row block this row lives in
     const int mb = row / gemm::kBlockM;
+    if (tl) tlMark = ptx::globaltimer();
     if (mb != readyMb && !a.noFlags) {
       // Every decision below is taken by lane 0 and read by the group after a barrier, so all 64
       // threads always agree on which barriers they execute.
@@ -256,6 +279,11 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
       readyMb = mb;
     }
     const uint64_t rowOff = static_cast<uint64_t>(row) * unitsPerRow * 16;
+    if (tl) {
+      const unsigned long long now = ptx::globaltimer();
+      tlWait += now - tlMark;
+      tlMark = now;
+    }
 
     // ---- gather: the row summed over all ranks, packed bf16 in registers
     uint4 h[kWordsPerThread];
@@ -268,7 +296,23 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
           h[k] = ptx::multimem_ld_reduce_add_bf16x2_acc32(reinterpret_cast<const void*>(c.mcBase + partialOff + rowOff + w * 16));
       }
     } else {
-      // two halves of 8 words; per half one fp32 accumulator set, peers visited two at a time
+      // Two halves of 8 words, one fp32 accumulator set per half. The loads of the next peer (and, at the end of the
+      // first half, of the second half's first peer) are put in flight before the current peer's words are added, so
+      // a row costs about one NVLink round trip plus the issue time instead of 2 x world round trips in series.
+      // Peers are visited starting with this rank (local memory answers first) - every rank a different order.
+      const uint64_t rowBase = partialOff + rowOff;
+      auto issue = [&](uint4 (&buf)[8], int half, int step) {
+        const int p = (rank + step) % world;
+        const uint64_t base = c.peerBase[p] + rowBase;
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+          const int w = lane + (half * 8 + k) * kGroupThreads;
+          buf[k] = make_uint4(0, 0, 0, 0);
+          if (w < unitsPerRow) buf[k] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(base + w * 16));
+        }
+      };
+      uint4 va[8], vb[8];
+      issue(va, 0, 0);
 #pragma unroll
       for (int half = 0; half < 2; half++) {
         float acc[8][8];
@@ -278,22 +322,30 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
           for (int i = 0; i < 8; i++) acc[k][i] = 0.f;
         }
 #pragma unroll 1
-        for (int p = 0; p < world; p++) {
-          uint4 v[8];
+        for (int step = 0; step < world; step += 2) {
+          if (step + 1 < world) issue(vb, half, step + 1);
 #pragma unroll
-          for (int k = 0; k < 8; k++) {
-            const int w = lane + (half * 8 + k) * kGroupThreads;
-            v[k] = make_uint4(0, 0, 0, 0);
-            if (w < unitsPerRow) v[k] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(c.peerBase[p] + partialOff + rowOff + w * 16));
+          for (int k = 0; k < 8; k++) accumulate16<bf16, SUM>(acc[k], va[k]);
+          if (step + 2 < world) {
+            issue(va, half, step + 2);
+          } else if (half == 0) {
+            issue(va, 1, 0);
           }
+          if (step + 1 < world) {
 #pragma unroll
-          for (int k = 0; k < 8; k++) accumulate16<bf16, SUM>(acc[k], v[k]);
+            for (int k = 0; k < 8; k++) accumulate16<bf16, SUM>(acc[k], vb[k]);
+          }
         }
 #pragma unroll
         for (int k = 0; k < 8; k++) h[half * 8 + k] = Vec16<bf16>::fromFloat(acc[k]);
       }
     }
-
+    if (tl) {
+      // (the first use of h below waits for the loads, so this stamp is taken after a dependent read)
+      const unsigned long long now = ptx::globaltimer() + (h[0].x == 0x7fc07fc1u ? 1 : 0);
+      tlGather += now - tlMark;
+      tlPhase = now;
+    }
     if (a.mode == 2) {
       // reduce-scatter: the reduced row stays here, in row j of this rank's [ownedRows, N] output
       const uint64_t dstOff = outOff + static_cast<uint64_t>(j) * unitsPerRow * 16;
@@ -335,12 +387,21 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
         for (int i = 0; i < 8; i++) ss += f[i] * f[i];
       }
     }
+    if (tl) {
+      const unsigned long long now = ptx::globaltimer() + (ss == -1.f ? 1 : 0);
+      tlMath += now - tlPhase;
+      tlPhase = now;
+    }
     if (a.residualOut) {
 #pragma unroll
       for (int k = 0; k < kWordsPerThread; k++) {
         const int w = lane + k * kGroupThreads;
         if (w < unitsPerRow) scatterWord<kNvls>(c, rank, resOutOff + rowOff + w * 16, h[k]);
       }
+    }
+    if (tl) {
+      const unsigned long long now = ptx::globaltimer();
+      tlScatter += now - tlPhase;
     }
     const float total = groupSum(ss, sumSmem[group], group);
     const float rinv = rsqrtf(total / static_cast<float>(N) + a.eps);
@@ -375,6 +436,20 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
         }
       }
     }
+    if (tl) {
+      const unsigned long long now = ptx::globaltimer();
+      tlWork += now - tlMark;
+      if (tlRows == 0) tl[6] = now;
+      tlRows++;
+    }
+  }
+  if (tl) {
+    tl[3] = tlRows;
+    tl[4] = tlWait;
+    tl[5] = tlWork;
+    tl[8] = tlGather;
+    tl[9] = tlMath;
+    tl[10] = tlScatter;
   }
   // every store of mine is issued: meet the peers' reducers with the same index. After it, everything
   // their reducers wrote into my buffers has landed.
@@ -382,6 +457,7 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
   bool allOk = true;
   for (int g = 0; g < kGroupsPerCta; g++) allOk = allOk && okSmem[g] != 0;
   if (allOk) rankBarrier(c, rank, 2, slot, epoch);
+  if (tl) tl[2] = ptx::globaltimer();
 }
 
 // kBlockN == 0 selects the two-SM GEMM core (256 x 256 tiles on CTA pairs; the launch uses clusters of two).
@@ -392,13 +468,16 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
   const DeviceComm& c = a.comm;
   const int rank = deviceRank(c);
   const uint32_t epoch = launchEpoch(c, rank);
+  const bool stamp = a.timeline != nullptr && blockIdx.y == 0 && threadIdx.x == 0;
+  if (stamp) a.timeline[static_cast<size_t>(blockIdx.x) * kTimelineWords] = ptx::globaltimer();
   if (static_cast<int>(blockIdx.x) < a.numGemmCtas) {
     gemm::NoGate gate;
     const uint64_t partialOff = reinterpret_cast<uint64_t>(a.partial) - c.peerBase[c.rank];
     const int numUnits = (a.shape.M + a.rowsPerUnit - 1) / a.rowsPerUnit;
     constexpr int kTileN = kBlockN == 0 ? gemm::Config2::kBlockN : kBlockN;
     PartialStoreSignal epi{&c, reinterpret_cast<bf16*>(c.peerBase[rank] + partialOff), a.shape.M, a.shape.N, rank,
-                           a.rowsPerUnit, numUnits, a.shape.N / kTileN, epoch};
+                           a.rowsPerUnit, numUnits, a.shape.N / kTileN, epoch,
+                           (a.timeline != nullptr && blockIdx.y == 0) ? a.timeline + static_cast<size_t>(blockIdx.x) * kTimelineWords : nullptr};
     if constexpr (kBlockN == 0) {
       gemm::gemmCtaPair(&maps.a[blockIdx.y], &maps.b[blockIdx.y], a.shape, blockIdx.x / 2, a.numGemmCtas / 2, gate, epi, c.status,
                         c.timeoutNs, smemRaw);
@@ -407,6 +486,7 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
                              c.status, c.timeoutNs, smemRaw);
     }
   }
+  if (stamp) a.timeline[static_cast<size_t>(blockIdx.x) * kTimelineWords + 1] = ptx::globaltimer();
   // dedicated reducer CTAs start here at once; GEMM CTAs arrive when their last tile is stored
   reducerCta<kNvls>(a, rank, epoch, blockIdx.x);
   finishLaunch(c, rank, epoch);

@@ -29,7 +29,18 @@ struct TpFusedArgs {
   int nvls;                     // multimem through comm.mcBase instead of peer loads/stores
   int emuRanks;                 // > 1: that many emulated ranks in one cooperative launch (tests)
   int noFlags;                  // set by launchTpReduceNorm: rows are complete at kernel start, no per-block flags
+  unsigned long long* timeline; // optional device buffer, kTimelineWords words per CTA (of emulated rank 0's grid layout):
+                                // [0] CTA start, [1] GEMM part done, [2] reducer part done (all globaltimer ns),
+                                // [3] rows reduced by group 0, [4] ns group 0 waited for readiness, [5] ns it spent on rows,
+                                // [6] time group 0 finished its first row, [8] ns of [5] in the gather (loads of all ranks'
+                                // partial rows), [9] ns in residual add + sum of squares, [10] ns issuing the broadcast
+                                // stores of h; GEMM CTAs: [11] ns spent counting finished tiles (fence + atomic), [12] the
+                                // longest such call, [13] ns spent in calls that published row-block flags, [14] time of
+                                // the last finished tile, [15] longest time between two finished tiles, [7] when that ended.
+                                // The caller zeroes the buffer. Null = no stamps.
 };
+
+constexpr int kTimelineWords = 16;
 
 // A[e], B[e]: operands of (emulated) rank e; real multi-GPU use passes one entry each.
 // A: [M, K] bf16 row-major activations, B: [N, K] bf16 row-major weights (nn.Linear layout).

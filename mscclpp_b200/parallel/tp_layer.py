@@ -61,13 +61,16 @@ class RowParallelLinearNorm:
     def forward_fused(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, mode: int = 0,
                       nvls: Optional[bool] = None, block_n: int = 0, num_reducers: int = 0, num_gemm_ctas: int = 0,
                       rows_per_unit: int = 0, stream: Optional[torch.cuda.Stream] = None,
-                      emulated_inputs=None) -> Tuple[torch.Tensor, torch.Tensor]:
+                      emulated_inputs=None, timeline: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """Same result as forward(), in ONE kernel: GEMM tiles, cross-rank reduction, residual add and norm
         overlap tile by tile. mode 1 halves NVLink traffic by broadcasting h and 1/rms only and finishing
         `out` with a local pass (second, local-only launch). block_n: N tile of the one-SM GEMM core (64/128/256), -1
         forces the two-SM core (256 x 256 tiles on SM pairs), 0 picks (two-SM from 1024 tokens on).
 
-        emulated_inputs: for emulated heaps, [(x_r, weight_r)] for every emulated rank."""
+        emulated_inputs: for emulated heaps, [(x_r, weight_r)] for every emulated rank.
+        timeline: optional int64 CUDA tensor [grid CTAs, 16] that receives per-CTA time stamps (ns): start, GEMM part
+        done, reducer part done, rows reduced / ns waited / ns worked by the CTA's first reducer group, first row done,
+        and (words 8-10) the ns of the work spent in the gather, the residual math and the broadcast stores."""
         from .._core import native
 
         n = native.load()
@@ -88,7 +91,8 @@ class RowParallelLinearNorm:
             a_ptrs, b_ptrs = [x.data_ptr()], [self.weight.data_ptr()]
         n.tp_fused(self.symm.heap, a_ptrs, b_ptrs, self.partial.data_ptr(), self.residual_in.data_ptr(),
                    self.residual_out.data_ptr(), self.out.data_ptr(), self.gamma.data_ptr(), self.rinv.data_ptr(), t,
-                   self.out_features, self.k_shard, self.eps, bn, num_gemm_ctas, num_reducers, rows_per_unit, mode, nvls, s)
+                   self.out_features, self.k_shard, self.eps, bn, num_gemm_ctas, num_reducers, rows_per_unit, mode, nvls, s,
+                   0 if timeline is None else timeline.data_ptr())
         if mode == 1:
             ranks = range(self.symm.world) if self.symm.emulated_mode else [self.symm.rank]
             for r in ranks:  # one local pass per (emulated) rank

@@ -242,6 +242,31 @@ def test_fused_tp_layer_one_kernel(world, mode, tokens, hidden, k):
     symm.destroy()
 
 
+def test_fused_tp_layer_timeline_stamps():
+    """The optional per-CTA time stamps of the fused kernel: ordered, and the reducer groups account for rows."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.tp_layer import RowParallelLinearNorm
+
+    world, tokens, hidden, k = 2, 512, 2048, 128
+    symm = SymmetricMemory.emulated(world, nbytes=128 << 20, timeout_ms=3000)
+    layer = RowParallelLinearNorm(symm, out_features=hidden, k_shard=k, max_tokens=tokens)
+    xs = [torch.randn((tokens, k), device="cuda").to(torch.bfloat16) for _ in range(world)]
+    ws = [(torch.randn((hidden, k), device="cuda") * 0.05).to(torch.bfloat16) for _ in range(world)]
+    gemm_ctas, reducers = 8, 4
+    tl = torch.zeros((gemm_ctas + reducers, 16), dtype=torch.int64, device="cuda")
+    layer.forward_fused(xs[0], mode=1, nvls=False, block_n=256, num_reducers=reducers, num_gemm_ctas=gemm_ctas,
+                        emulated_inputs=list(zip(xs, ws)), timeline=tl)
+    torch.cuda.synchronize()
+    symm.check()
+    t = tl.cpu()
+    assert (t[:, 0] > 0).all()
+    assert (t[:, 1] >= t[:, 0]).all() and (t[:, 2] >= t[:, 1]).all()
+    assert int(t[:, 3].sum()) > 0  # first groups of the CTAs reduced rows
+    assert (t[:, 8] + t[:, 9] + t[:, 10] <= t[:, 5]).all()  # the phases are parts of the time spent on rows
+    assert (t[:gemm_ctas, 1] > t[:gemm_ctas, 0]).all()  # GEMM CTAs spent time in the matmul
+    symm.destroy()
+
+
 @pytest.mark.parametrize("world,rows_per_rank,k,n_cols,act", [(2, 256, 256, 256, "none"), (4, 128, 512, 512, "gelu"), (8, 128, 256, 256, "silu")])
 def test_all_gather_gemm_one_kernel(world, rows_per_rank, k, n_cols, act):
     """All-gather -> GEMM in one launch (copier CTAs + gated tcgen05 GEMM), all ranks emulated on one GPU."""
