@@ -186,6 +186,8 @@ def main():
     # the switch reduction wins from 8 ranks on; with 2 or 4 peers plain peer loads/stores are as fast or faster
     nvls_opts = ([True, False] if world <= 4 else [True]) if symm.nvls else [False]
     variants = [(m, nv, r, c) for m in (0, 1) for nv in nvls_opts for r in (8, 16, 32, 48, 64) for c in (1, 2)] + [(-1, symm.nvls, 0, 1)]
+    if world > 4 and symm.nvls:  # plain peer loads/stores for comparison
+        variants += [(1, False, r, 2) for r in (32, 64)]
     if world == 1:
         variants = [(0, False, 64, 1), (1, False, 64, 1), (0, False, 64, 2), (1, False, 64, 2), (-1, False, 0, 1), (-2, False, 0, 1),
                     (-2, False, 0, 2)]
