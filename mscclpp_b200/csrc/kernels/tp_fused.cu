@@ -695,9 +695,10 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   }
   const int tiles = twoSm ? 2 * ((M + gemm::Config2::kPairM - 1) / gemm::Config2::kPairM) * (N / tileN) : numMBlk * (N / tileN);
   int sms = gemm::smCount() / emu;
-  // Measured on 2 and 8 B200s: from about a thousand tokens on the reduction is the longer half and wants ~48 CTAs from the
-  // first finished row block; below that the GEMM is short and few dedicated reducers keep more SMs on it.
-  if (numReducers <= 0) numReducers = sms >= 64 ? (M >= 1024 ? 48 : 8) : 2;
+  // Measured on 2 and 8 B200s with K = 1024 per rank: from about a thousand tokens on the reduction is the longer half and
+  // wants ~48 CTAs from the first finished row block; below that the GEMM is short and few dedicated reducers keep more
+  // SMs on it. With a long reduction dimension the matmul is the longer half again and gets the SMs back.
+  if (numReducers <= 0) numReducers = sms >= 64 ? (M < 1024 ? 8 : (K <= 2048 ? 48 : 24)) : 2;
   if (numReducers > kBarrierSlots) numReducers = kBarrierSlots;
   int gemmCtas = args.numGemmCtas > 0 ? args.numGemmCtas : sms - numReducers;
   if (gemmCtas > tiles) gemmCtas = tiles;
