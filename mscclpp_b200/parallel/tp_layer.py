@@ -58,13 +58,14 @@ class RowParallelLinearNorm:
                            stream=stream)
         return out, res_out
 
-    def forward_fused(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, mode: int = 0,
+    def forward_fused(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, mode: Optional[int] = None,
                       nvls: Optional[bool] = None, block_n: int = 0, num_reducers: int = 0, num_gemm_ctas: int = 0,
                       rows_per_unit: int = 0, stream: Optional[torch.cuda.Stream] = None,
                       emulated_inputs=None, timeline: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """Same result as forward(), in ONE kernel: GEMM tiles, cross-rank reduction, residual add and norm
         overlap tile by tile. mode 1 halves NVLink traffic by broadcasting h and 1/rms only and finishing
-        `out` with a local pass (second, local-only launch). block_n: N tile of the one-SM GEMM core (64/128/256), -1
+        `out` with a local pass (second, local-only launch); mode 0 is one launch. Default: mode 1 from 1024 tokens on
+        (measured on 2 and 8 GPUs: the saved bytes outweigh the second launch there), else mode 0. block_n: N tile of the one-SM GEMM core (64/128/256), -1
         forces the two-SM core (256 x 256 tiles on SM pairs), 0 picks (two-SM from 1024 tokens on).
 
         emulated_inputs: for emulated heaps, [(x_r, weight_r)] for every emulated rank.
@@ -76,6 +77,8 @@ class RowParallelLinearNorm:
         n = native.load()
         t = x.shape[0]
         assert t <= self.max_tokens and x.shape[1] == self.k_shard and x.is_contiguous()
+        if mode is None:
+            mode = 1 if t >= 1024 else 0
         if residual is not None:
             self.residual_in[:t].copy_(residual)
         nvls = self.symm.nvls if nvls is None else nvls
