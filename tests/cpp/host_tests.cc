@@ -1,0 +1,265 @@
+// Host-only unit tests of the pieces below the Communicator: sockets (addresses, loopback transfer, deadlines),
+// descriptor passing over AF_UNIX, the JSON reader, the algorithm registry and its selectors, the environment singleton
+// and the execution-plan loader on a plan produced by the DSL (path in MSCCLPP_TEST_PLAN). No GPU needed.
+#include <unistd.h>
+
+#include <atomic>
+#include <chrono>
+#include <cstdlib>
+#include <cstring>
+#include <thread>
+
+#include <mscclpp/algorithm.hpp>
+#include <mscclpp/core.hpp>
+#include <mscclpp/env.hpp>
+#include <mscclpp/errors.hpp>
+#include <mscclpp/executor.hpp>
+
+#include "core/json.hpp"
+#include "core/socket.hpp"
+#include "core/unix_socket.hpp"
+#include "framework.hpp"
+
+using namespace mscclpp;
+
+TEST(SocketAddress, ParseAndPrint) {
+  SocketAddress a = SocketAddress::parse("127.0.0.1:4321");
+  EXPECT_EQ(a.family(), AF_INET);
+  EXPECT_EQ(a.port(), uint16_t(4321));
+  EXPECT_EQ(a.toString(), std::string("127.0.0.1:4321"));
+  EXPECT_EQ(a.toString(false), std::string("127.0.0.1"));
+  SocketAddress b = SocketAddress::parse("[::1]:80");
+  EXPECT_EQ(b.family(), AF_INET6);
+  EXPECT_EQ(b.port(), uint16_t(80));
+  SocketAddress c = SocketAddress::parse("127.0.0.1", 99);
+  EXPECT_EQ(c.port(), uint16_t(99));
+  c.setPort(100);
+  EXPECT_EQ(c.port(), uint16_t(100));
+  EXPECT_TRUE(a.sameHost(c));
+  EXPECT_TRUE(!a.sameHost(b));
+}
+
+TEST(Socket, LoopbackTransferOfOneMegabyte) {
+  Socket listener;
+  SocketAddress bound = listener.listen(SocketAddress::parse("127.0.0.1:0"));
+  EXPECT_TRUE(bound.port() != 0);
+  const size_t n = 1 << 20;
+  std::vector<uint8_t> sent(n), got(n, 0);
+  for (size_t i = 0; i < n; i++) sent[i] = static_cast<uint8_t>(i * 131 + 7);
+  testing::Timer timer;
+  std::thread client([&] {
+    Socket s;
+    s.connect(bound, 5000);
+    s.sendAll(sent.data(), n, 5000);
+    uint32_t ack = 0;
+    s.recvAll(&ack, sizeof(ack), 5000);
+    if (ack != 0xabcd) sent[0] ^= 0xff;  // makes the comparison below fail
+  });
+  Socket peer = listener.accept(5000);
+  EXPECT_TRUE(peer.valid());
+  peer.recvAll(got.data(), n, 5000);
+  uint32_t ack = 0xabcd;
+  peer.sendAll(&ack, sizeof(ack), 5000);
+  client.join();
+  EXPECT_TRUE(std::memcmp(sent.data(), got.data(), n) == 0);
+  testing::reportPerf("socket_loopback_1MB", timer.elapsedUs(), "us");
+}
+
+TEST(Socket, DeadlinesAndAbortFlag) {
+  Socket listener;
+  SocketAddress bound = listener.listen(SocketAddress::parse("127.0.0.1:0"));
+  // nobody connects: accept gives up at its deadline
+  auto t0 = std::chrono::steady_clock::now();
+  EXPECT_THROW(listener.accept(200), BaseError);
+  auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+  EXPECT_TRUE(ms >= 150 && ms < 3000);
+  // an abort flag raised by another thread ends a long wait early
+  std::atomic<uint32_t> abortFlag{0};
+  std::thread raiser([&] {
+    std::this_thread::sleep_for(std::chrono::milliseconds(100));
+    abortFlag.store(1);
+  });
+  t0 = std::chrono::steady_clock::now();
+  EXPECT_THROW(listener.accept(20000, &abortFlag), BaseError);
+  ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+  raiser.join();
+  EXPECT_TRUE(ms < 5000);
+  // a peer that connects but sends nothing: recvAll gives up, readable() says no
+  std::thread client([&] {
+    Socket s;
+    s.connect(bound, 5000);
+    std::this_thread::sleep_for(std::chrono::milliseconds(600));
+  });
+  Socket peer = listener.accept(5000);
+  EXPECT_TRUE(!peer.readable(50));
+  char byte;
+  EXPECT_THROW(peer.recvAll(&byte, 1, 200), BaseError);
+  client.join();
+}
+
+TEST(Socket, InterfaceDiscovery) {
+  auto all = findInterfaces("^nonexistent", AF_UNSPEC);
+  EXPECT_TRUE(!all.empty());  // at least loopback
+  auto lo = findInterfaces("=lo", AF_INET);
+  for (const auto& itf : lo) EXPECT_EQ(itf.name, std::string("lo"));
+  EXPECT_TRUE(getHostHash() == getHostHash());
+  EXPECT_TRUE(getPidHash() == getPidHash());
+}
+
+TEST(UnixFd, DescriptorTravelsThroughTheServer) {
+  int fds[2];
+  ASSERT_TRUE(::pipe(fds) == 0);
+  UnixFdServer& server = UnixFdServer::instance();
+  const uint32_t id = server.registerFd(fds[1]);
+  int received = -1;
+  std::thread peer([&] { received = requestFdFromPeer(server.name(), id, 5000); });
+  peer.join();
+  ASSERT_TRUE(received >= 0);
+  EXPECT_TRUE(received != fds[1]);  // a new descriptor for the same pipe
+  const char msg[] = "through the duplicate";
+  ASSERT_TRUE(::write(received, msg, sizeof(msg)) == static_cast<ssize_t>(sizeof(msg)));
+  char back[64] = {0};
+  ASSERT_TRUE(::read(fds[0], back, sizeof(back)) == static_cast<ssize_t>(sizeof(msg)));
+  EXPECT_EQ(std::string(back), std::string(msg));
+  EXPECT_THROW(requestFdFromPeer(server.name(), id + 1000, 1000), BaseError);  // unknown id
+  server.unregisterFd(id);
+  EXPECT_THROW(requestFdFromPeer(server.name(), id, 1000), BaseError);
+  ::close(received);
+  ::close(fds[0]);
+  ::close(fds[1]);
+}
+
+TEST(Json, ValuesNestingAndErrors) {
+  json::Value v = json::parse(R"({"name": "plan \"a\"\n", "n": 42, "neg": -7, "x": 1.5e2, "ok": true, "none": null,
+                                  "list": [1, [2, 3], {"k": "v"}], "big": 18446744073709551615})");
+  EXPECT_EQ(v.at("name").asString(), std::string("plan \"a\"\n"));
+  EXPECT_EQ(v.at("n").asInt(), int64_t(42));
+  EXPECT_EQ(v.at("neg").asInt(), int64_t(-7));
+  EXPECT_EQ(v.at("x").asInt(), int64_t(150));
+  EXPECT_TRUE(v.at("ok").asBool());
+  EXPECT_TRUE(v.contains("none") && !v.contains("missing"));
+  EXPECT_EQ(v.at("list").size(), size_t(3));
+  EXPECT_EQ(v.at("list").at(1).at(1).asInt(), int64_t(3));
+  EXPECT_EQ(v.at("list").at(2).at("k").asString(), std::string("v"));
+  EXPECT_EQ(v.at("big").asUInt(), UINT64_MAX);
+  EXPECT_EQ(v.intOr("missing", 5), int64_t(5));
+  EXPECT_THROW(v.at("missing"), BaseError);
+  EXPECT_THROW(v.at("n").asString(), BaseError);
+  EXPECT_THROW(v.at("neg").asUInt(), BaseError);
+  EXPECT_THROW(json::parse("{\"a\": [1, 2"), BaseError);
+  EXPECT_THROW(json::parse("{\"a\" 1}"), BaseError);
+  EXPECT_THROW(json::parse(""), BaseError);
+}
+
+static std::shared_ptr<Algorithm> dummyAlgo(const std::string& name, const std::string& collective, size_t lo, size_t hi, int* calls) {
+  return std::make_shared<NativeAlgorithm>(
+      name, collective, [](std::shared_ptr<Communicator>) {},
+      [calls](const void*, void*, size_t, size_t, DataType, ReduceOp, cudaStream_t, int, int, bool,
+              const std::unordered_map<std::string, uintptr_t>&) {
+        (*calls)++;
+        return CommResult::Success;
+      },
+      lo, hi);
+}
+
+TEST(AlgorithmCollection, RegistrySelectorsAndExtend) {
+  int smallCalls = 0, largeCalls = 0, otherCalls = 0;
+  AlgorithmCollection coll;
+  coll.registerAlgorithm("allreduce", "small", dummyAlgo("small", "allreduce", 0, 4096, &smallCalls));
+  coll.registerAlgorithm("allreduce", "large", dummyAlgo("large", "allreduce", 4097, UINT64_MAX, &largeCalls));
+  EXPECT_EQ(coll.getAlgorithmsByCollective("allreduce").size(), size_t(2));
+  EXPECT_EQ(coll.getAlgorithmsByCollective("allgather").size(), size_t(0));
+  EXPECT_EQ(coll.getAllAlgorithms().size(), size_t(2));
+
+  CollectiveRequest req;
+  req.collective = "allreduce";
+  req.messageSize = 1024;
+  EXPECT_TRUE(coll.selectAlgorithm(req) == nullptr);  // no selector installed yet
+
+  // fallback: first algorithm whose message range holds the request; user selector: only answers for >= 1 MB
+  auto byRange = [](const auto& map, const CollectiveRequest& r) -> std::shared_ptr<Algorithm> {
+    auto it = map.find(r.collective);
+    if (it == map.end()) return nullptr;
+    for (const auto& kv : it->second) {
+      auto range = kv.second->messageRange();
+      if (r.messageSize >= range.first && r.messageSize <= range.second) return kv.second;
+    }
+    return nullptr;
+  };
+  auto userSel = [](const auto& map, const CollectiveRequest& r) -> std::shared_ptr<Algorithm> {
+    if (r.messageSize < (1u << 20)) return nullptr;
+    return map.at(r.collective).at("small");  // deliberately odd, to see that the user selector wins
+  };
+  coll.setSelectors(userSel, byRange);
+  EXPECT_EQ(coll.selectAlgorithm(req)->name(), std::string("small"));
+  req.messageSize = 65536;
+  EXPECT_EQ(coll.selectAlgorithm(req)->name(), std::string("large"));
+  req.messageSize = 4u << 20;
+  EXPECT_EQ(coll.selectAlgorithm(req)->name(), std::string("small"));
+  req.collective = "broadcast";
+  req.messageSize = 8;
+  EXPECT_TRUE(coll.selectAlgorithm(req) == nullptr);
+
+  // ranges can be retuned after registration
+  auto large = coll.getAlgorithmsByCollective("allreduce").at("large");
+  large->setMessageSizeRange(100, 200);
+  EXPECT_EQ(large->messageRange().first, size_t(100));
+  EXPECT_EQ(large->messageRange().second, size_t(200));
+  EXPECT_TRUE(large->type() == AlgorithmType::Native);
+  EXPECT_TRUE(large->bufferMode() == CollectiveBufferMode::Any);
+
+  AlgorithmCollection other;
+  other.registerAlgorithm("allgather", "other", dummyAlgo("other", "allgather", 0, UINT64_MAX, &otherCalls));
+  coll.extend(other);
+  EXPECT_EQ(coll.getAllAlgorithms().size(), size_t(3));
+  EXPECT_EQ(coll.getAlgorithmsByCollective("allgather").count("other"), size_t(1));
+
+  // execute reaches the closure (no communicator or executor needed by a native algorithm that ignores them)
+  auto algo = coll.getAlgorithmsByCollective("allgather").at("other");
+  CommResult res = algo->execute(nullptr, nullptr, nullptr, 0, 0, DataType::FLOAT32, SUM, nullptr, nullptr, 0, 0, false, {}, DataType::AUTO);
+  EXPECT_TRUE(res == CommResult::Success);
+  EXPECT_EQ(otherCalls, 1);
+  EXPECT_EQ(smallCalls + largeCalls, 0);
+}
+
+TEST(CollectiveRequest, BufferMode) {
+  CollectiveRequest req;
+  int a = 0, b = 0;
+  req.inputBuffer = &a;
+  req.outputBuffer = &a;
+  EXPECT_TRUE(req.bufferMode() == CollectiveBufferMode::InPlace);
+  req.outputBuffer = &b;
+  EXPECT_TRUE(req.bufferMode() == CollectiveBufferMode::OutOfPlace);
+}
+
+TEST(Env, SingletonAndDefaults) {
+  auto e1 = env();
+  auto e2 = env();
+  EXPECT_TRUE(e1.get() == e2.get());
+  const char* timeout = std::getenv("MSCCLPP_DEVICE_TIMEOUT_MS");
+  if (timeout == nullptr) EXPECT_EQ(e1->deviceTimeoutMs, 10000L);
+  else EXPECT_EQ(e1->deviceTimeoutMs, std::atol(timeout));
+  if (std::getenv("MSCCLPP_HEAP_BYTES") == nullptr) EXPECT_EQ(e1->heapBytes, 2L << 30);
+  if (std::getenv("MSCCLPP_IB_GID_INDEX") == nullptr) EXPECT_EQ(e1->ibGidIndex, -1);
+  EXPECT_TRUE(!e1->cacheDir.empty());
+}
+
+TEST(ExecutionPlan, LoadsAPlanWrittenByTheDsl) {
+  const char* path = std::getenv("MSCCLPP_TEST_PLAN");
+  if (path == nullptr) {
+    std::printf("[  SKIPPED ] MSCCLPP_TEST_PLAN is not set\n");
+    return;
+  }
+  ExecutionPlan plan(path, 0);
+  EXPECT_EQ(plan.collective(), std::string("allreduce"));
+  EXPECT_TRUE(!plan.name().empty());
+  EXPECT_EQ(plan.nRanks(), 8);
+  EXPECT_TRUE(plan.nThreadsPerBlock() > 0);
+  EXPECT_TRUE(plan.minMessageSize() <= plan.maxMessageSize());
+  ExecutionPlan lastRank(path, 7);
+  EXPECT_EQ(lastRank.name(), plan.name());
+  EXPECT_THROW(ExecutionPlan(path, 8), BaseError);  // rank outside the plan
+  EXPECT_THROW(ExecutionPlan("/nonexistent/plan.json", 0), BaseError);
+}
+
+int main(int argc, char** argv) { return testing::runAll(argc, argv); }
