@@ -1,6 +1,6 @@
 # Locates libnuma. Sets NUMA_FOUND, NUMA_INCLUDE_DIRS, NUMA_LIBRARIES and the target NUMA::numa.
-# Hints: NUMA_ROOT (variable or environment). The library here pins its proxy threads with sched_setaffinity and reads
-# the GPU's NUMA node from sysfs, so libnuma is optional.
+# Hints: NUMA_ROOT (variable or environment). The library binds its proxy threads with sched_setaffinity and reads the
+# GPU's NUMA node from sysfs (csrc/core/numa.cc), so libnuma is optional.
 find_path(NUMA_INCLUDE_DIR NAMES numa.h HINTS ${NUMA_ROOT} ENV NUMA_ROOT PATH_SUFFIXES include PATHS /usr /usr/local)
 find_library(NUMA_LIBRARY NAMES numa
              HINTS ${NUMA_ROOT} ENV NUMA_ROOT PATH_SUFFIXES lib lib64 lib/x86_64-linux-gnu lib/aarch64-linux-gnu

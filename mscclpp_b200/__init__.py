@@ -25,19 +25,27 @@ _NATIVE_NAMES = (
     "Executor", "ExecutionPlan", "PacketType", "RawGpuBuffer", "ReduceOp", "env", "is_bulk_supported", "is_nvls_supported",
     "SwitchChannel", "NvlsConnection", "BaseMemoryChannel", "BasePortChannel", "Context", "Endpoint", "Bootstrap", "SymmetricHeap",
     "CollectiveRequest", "CollectiveBufferMode", "AlgorithmType", "CommResult", "Error", "BaseError", "CudaError", "CuError",
-    "SysError", "IbError", "npkit",
+    "SysError", "IbError", "npkit", "numa", "GpuBufferGranularity",
 )
 
 __all__ = [
     "SymmetricMemory", "Algorithm", "AlgorithmBuilder", "AlgorithmCollection", "CommGroup", "GpuBuffer", "DslCompiler",
     "NativeCodeCompiler", "compile", "compile_native", "get_flag_buffer", "get_include", "get_lib", "version", "__version__",
-    *_NATIVE_NAMES,
+    "alloc_shared_physical_cuda", *_NATIVE_NAMES,
 ]
 
 
 def native():
     """The compiled runtime module (raises if it has not been built)."""
     return _native_loader.load()
+
+
+def alloc_shared_physical_cuda(nbytes: int, granularity=None):
+    """Zeroed physical (VMM) device memory of at least `nbytes`, shareable with peers and bindable to NVLink multicast.
+    Returns the owning `RawGpuBuffer` (`.data()` is the device pointer, `.bytes()` the rounded size); the memory is
+    freed when the object is dropped. (The name is exported by the reference's package as well: python/mscclpp/__init__.py:93.)"""
+    n = _native_loader.load()
+    return n.RawGpuBuffer(int(nbytes)) if granularity is None else n.RawGpuBuffer(int(nbytes), granularity)
 
 
 def __getattr__(name):

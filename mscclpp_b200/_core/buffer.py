@@ -13,8 +13,9 @@ from .symm import tensor_from_pointer
 __all__ = ["GpuBuffer"]
 
 
-def GpuBuffer(shape: Union[int, Sequence[int]], dtype: torch.dtype = torch.float32, device=None) -> torch.Tensor:
+def GpuBuffer(shape: Union[int, Sequence[int]], dtype: torch.dtype = torch.float32, device=None, granularity=None) -> torch.Tensor:
     """Allocate `shape` elements of `dtype` with the multicast granularity and return them as a tensor.
+    `granularity`: a `GpuBufferGranularity` (default: the driver's recommended multicast granularity).
 
     The tensor keeps the allocation alive; `tensor.data_ptr()` is what `Communicator.register_memory` and
     `NvlsConnection.bind_allocated_memory` take."""
@@ -24,6 +25,7 @@ def GpuBuffer(shape: Union[int, Sequence[int]], dtype: torch.dtype = torch.float
     if any(s <= 0 for s in shape):
         raise ValueError("Shape must be positive.")
     nbytes = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
-    raw = _loader.load().RawGpuBuffer(nbytes)
+    n = _loader.load()
+    raw = n.RawGpuBuffer(nbytes) if granularity is None else n.RawGpuBuffer(nbytes, granularity)
     dev = torch.device(device) if device is not None else torch.device("cuda", raw.device_id())
     return tensor_from_pointer(raw.data(), shape, dtype, dev, owner=raw)

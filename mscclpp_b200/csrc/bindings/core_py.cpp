@@ -9,6 +9,7 @@
 #include <cstring>
 
 #include <mscclpp/core.hpp>
+#include <mscclpp/numa.hpp>
 #include <mscclpp/fifo.hpp>
 #include <mscclpp/gpu_utils.hpp>
 #include <mscclpp/memory_channel.hpp>
@@ -42,7 +43,8 @@ std::vector<char> toVec(const py::bytes& b) {
 
 // A device allocation owned by Python: VMM-backed (multicast-bindable) when NVLS is available.
 struct RawGpuBuffer {
-  explicit RawGpuBuffer(size_t bytes) : buffer(bytes) {}
+  explicit RawGpuBuffer(size_t bytes, GpuBufferGranularity granularity = GpuBufferGranularity::MultiCastRecommended)
+      : buffer(bytes, granularity) {}
   GpuBuffer<char> buffer;
 };
 
@@ -275,8 +277,19 @@ void registerCoreBindings(py::module_& m) {
   });
 
   // ------------------------------------------------------------------ buffers
+  py::enum_<GpuBufferGranularity>(m, "GpuBufferGranularity")
+      .value("MultiCastMinimum", GpuBufferGranularity::MultiCastMinimum)
+      .value("MultiCastRecommended", GpuBufferGranularity::MultiCastRecommended);
+  {
+    py::module_ numa = m.def_submodule("numa", "NUMA placement helpers");
+    numa.def("get_device_numa_node", &getDeviceNumaNode, py::arg("device_id"));
+    numa.def("get_numa_node_cpus", &getNumaNodeCpus, py::arg("node"));
+    numa.def("numa_bind", &numaBind, py::arg("node"));
+    numa.def("parse_cpu_list", &parseCpuList, py::arg("text"));
+  }
   py::class_<RawGpuBuffer, std::shared_ptr<RawGpuBuffer>>(m, "RawGpuBuffer")
-      .def(py::init<size_t>())
+      .def(py::init<size_t, GpuBufferGranularity>(), py::arg("nbytes"),
+           py::arg("granularity") = GpuBufferGranularity::MultiCastRecommended)
       .def("data", [](RawGpuBuffer& b) { return reinterpret_cast<uintptr_t>(b.buffer.data()); })
       .def("bytes", [](RawGpuBuffer& b) { return b.buffer.bytes(); })
       .def("device_id", [](RawGpuBuffer& b) { return b.buffer.deviceId(); });

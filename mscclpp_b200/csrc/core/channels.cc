@@ -1,5 +1,6 @@
 // Host objects of MemoryChannel and PortChannel, and the ProxyService.
 #include <mscclpp/memory_channel.hpp>
+#include <mscclpp/numa.hpp>
 #include <mscclpp/port_channel.hpp>
 
 #include <mscclpp/gpu_utils.hpp>
@@ -69,7 +70,13 @@ ProxyService::ProxyService(int fifoSize) {
   const int dev = deviceId_;
   proxy_ = std::make_shared<Proxy>([this](ProxyTrigger t) { return handleTrigger(t); },
                                    [dev] {
-                                     if (dev >= 0) (void)cudaSetDevice(dev);
+                                     if (dev < 0) return;
+                                     (void)cudaSetDevice(dev);
+                                     // run next to the GPU: CPUs and memory of its NUMA node (best effort)
+                                     try {
+                                       numaBind(getDeviceNumaNode(dev));
+                                     } catch (const std::exception&) {
+                                     }
                                    },
                                    fifoSize);
 }

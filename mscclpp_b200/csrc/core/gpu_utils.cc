@@ -199,6 +199,25 @@ size_t physicalGranularity(bool forMulticast) {
   return gran;
 }
 
+size_t multicastGranularity(bool recommended) {
+  if (recommended) return physicalGranularity(true);
+  const CudaDriver& drv = CudaDriver::get();
+  int dev = 0;
+  MSCCLPP_CUDATHROW(cudaGetDevice(&dev));
+  CUmemAllocationProp prop = physicalProp(dev);
+  size_t gran = 0;
+  MSCCLPP_CUTHROW(drv.cuMemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_MINIMUM));
+  if (isNvlsSupported()) {
+    CUmulticastObjectProp mp{};
+    mp.numDevices = 2;
+    mp.size = gran;
+    mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    size_t mg = 0;
+    if (drv.cuMulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_MINIMUM) == CUDA_SUCCESS && mg > gran) gran = mg;
+  }
+  return gran;
+}
+
 void* gpuCallocPhysical(size_t bytes, size_t granularity) {
   AvoidCudaGraphCaptureGuard guard;
   const CudaDriver& drv = CudaDriver::get();

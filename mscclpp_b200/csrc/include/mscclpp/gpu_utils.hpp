@@ -69,7 +69,16 @@ void gpuFreePhysical(void* ptr);
 // to it (VMM allocations are not covered by cudaDeviceEnablePeerAccess). Returns false for other memory.
 bool gpuGrantAccessPhysical(const void* ptr, int dev);
 size_t physicalGranularity(bool forMulticast);
+// Allocation granularity that is also valid for binding to a multicast object: the larger of the device's allocation
+// granularity and the multicast granularity, both taken as the driver's minimum or recommended value.
+size_t multicastGranularity(bool recommended);
 }  // namespace detail
+
+// How a GpuBuffer is rounded so that it can be bound to NVLink multicast (NVLS) later.
+enum class GpuBufferGranularity {
+  MultiCastMinimum,      // smallest granularity the multicast API accepts: least memory
+  MultiCastRecommended,  // the driver's recommended granularity (may be larger)
+};
 
 template <class T>
 struct GpuDeleter {
@@ -116,11 +125,15 @@ bool isFp8MultimemSupported();   // multimem fp8 reductions: sm_100a build runni
 template <class T = char>
 class GpuBuffer {
  public:
-  explicit GpuBuffer(size_t nelems) : nelems_(nelems), bytes_(nelems * sizeof(T)) {
+  // The default is the recommended granularity (what the NVLS paths of this library are measured with); pass
+  // MultiCastMinimum to save memory on many small buffers.
+  explicit GpuBuffer(size_t nelems, GpuBufferGranularity granularity = GpuBufferGranularity::MultiCastRecommended)
+      : nelems_(nelems), bytes_(nelems * sizeof(T)) {
     if (nelems == 0) return;
     MSCCLPP_CUDATHROW(cudaGetDevice(&deviceId_));
     if (isNvlsSupported()) {
-      size_t gran = detail::physicalGranularity(true);
+      size_t gran = granularity == GpuBufferGranularity::MultiCastRecommended ? detail::physicalGranularity(true)
+                                                                              : detail::multicastGranularity(false);
       bytes_ = (bytes_ + gran - 1) / gran * gran;
       memory_ = gpuCallocPhysicalShared<T>(bytes_ / sizeof(T) + (bytes_ % sizeof(T) ? 1 : 0), gran);
     } else {

@@ -3,6 +3,9 @@
 // and the execution-plan loader on a plan produced by the DSL (path in MSCCLPP_TEST_PLAN). No GPU needed.
 #include <unistd.h>
 
+#include <sched.h>
+
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <cstdlib>
@@ -14,6 +17,7 @@
 #include <mscclpp/env.hpp>
 #include <mscclpp/errors.hpp>
 #include <mscclpp/executor.hpp>
+#include <mscclpp/numa.hpp>
 
 #include "core/json.hpp"
 #include "core/socket.hpp"
@@ -242,6 +246,31 @@ TEST(Env, SingletonAndDefaults) {
   if (std::getenv("MSCCLPP_HEAP_BYTES") == nullptr) EXPECT_EQ(e1->heapBytes, 2L << 30);
   if (std::getenv("MSCCLPP_IB_GID_INDEX") == nullptr) EXPECT_EQ(e1->ibGidIndex, -1);
   EXPECT_TRUE(!e1->cacheDir.empty());
+}
+
+TEST(Numa, CpuListsAndBinding) {
+  std::vector<int> cpus = parseCpuList("0-2,5, 7-8\n");
+  EXPECT_EQ(cpus.size(), size_t(6));
+  EXPECT_EQ(cpus.back(), 8);
+  EXPECT_THROW(parseCpuList("4-2"), BaseError);
+  EXPECT_THROW(parseCpuList("x"), BaseError);
+  EXPECT_THROW(getNumaNodeCpus(4096), BaseError);
+  numaBind(-1);  // unknown node: no-op
+  std::thread worker([] {  // bind a thread of its own, the test runner keeps its affinity
+    try {
+      std::vector<int> node0 = getNumaNodeCpus(0);
+      numaBind(0);
+      cpu_set_t now;
+      CPU_ZERO(&now);
+      sched_getaffinity(0, sizeof(now), &now);
+      for (int c = 0; c < CPU_SETSIZE; c++) {
+        if (CPU_ISSET(c, &now)) EXPECT_TRUE(std::find(node0.begin(), node0.end(), c) != node0.end());
+      }
+    } catch (const BaseError&) {
+      // machines without NUMA information in sysfs, or a cpuset that excludes node 0
+    }
+  });
+  worker.join();
 }
 
 TEST(ExecutionPlan, LoadsAPlanWrittenByTheDsl) {

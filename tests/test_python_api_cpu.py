@@ -274,3 +274,40 @@ def test_comm_group_over_ethernet_on_cpu():
     assert not any(k.startswith("error") for k in results), results
     assert (results["received"] == 1).all()
     assert results["msg"].tolist() == [0, 1, 2, 3]
+
+
+def test_numa_helpers_and_reference_export_names():
+    """NUMA helpers work from sysfs without libnuma; every name the reference's package exports exists here."""
+    import os
+
+    import mscclpp_b200 as mp
+
+    assert mp.numa.parse_cpu_list("0-3, 8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    for bad in ("3-1", "a", "1-"):
+        with pytest.raises(Exception):
+            mp.numa.parse_cpu_list(bad)
+    with pytest.raises(Exception):
+        mp.numa.get_numa_node_cpus(4096)
+    mp.numa.numa_bind(-1)  # "unknown node": nothing happens
+    if os.path.exists("/sys/devices/system/node/node0/cpulist"):
+        cpus = set(mp.numa.get_numa_node_cpus(0))
+        before = os.sched_getaffinity(0)
+        try:
+            if cpus & before:
+                mp.numa.numa_bind(0)
+                assert os.sched_getaffinity(0) == cpus & before
+        finally:
+            os.sched_setaffinity(0, before)
+    assert {m.name for m in mp.GpuBufferGranularity.__members__.values()} == {"MultiCastMinimum", "MultiCastRecommended"}
+    assert callable(mp.alloc_shared_physical_cuda)
+    # the public names of the reference's Python package (its __all__)
+    reference_names = [
+        'Algorithm', 'AlgorithmCollection', 'CommGroup', 'Communicator', 'Connection', 'DataType', 'Device',
+        'DeviceType', 'EndpointConfig', 'EndpointConfigIb', 'ErrorCode', 'ExecutionPlan', 'Executor', 'Fifo',
+        'GpuBuffer', 'GpuBufferGranularity', 'Host2DeviceSemaphore', 'Host2HostSemaphore', 'IbMode',
+        'MemoryChannel', 'MemoryDevice2DeviceSemaphore', 'PacketType', 'PortChannel', 'ProxyService',
+        'RawGpuBuffer', 'ReduceOp', 'RegisteredMemory', 'Semaphore', 'TcpBootstrap', 'Transport', 'TransportFlags',
+        '__version__', 'alloc_shared_physical_cuda', 'connect_nvls_collective', 'env', 'get_include', 'get_lib',
+        'is_bulk_supported', 'is_nvls_supported', 'npkit', 'numa', 'version',
+    ]
+    assert not [n for n in reference_names if not hasattr(mp, n)]
