@@ -151,6 +151,7 @@ class TcpBootstrap::Impl {
   Socket rootListen;  // rank 0 only
   std::thread rootThread;
   std::string rootError;
+  ErrorCode rootErrorCode = ErrorCode::InternalError;
 
   Socket peerListen;
   std::vector<RankInfo> table;
@@ -204,6 +205,10 @@ class TcpBootstrap::Impl {
         conns[info.rank] = std::move(s);
       }
       for (int r = 0; r < nRanks; r++) conns[r].sendAll(infos.data(), sizeof(RankInfo) * nRanks, timeoutMs, &abortFlag);
+    } catch (const Error& e) {
+      rootError = e.what();
+      rootErrorCode = e.getErrorCode();
+      LOG_WARN(LogSubsys::NET, "bootstrap root failed: ", rootError);
     } catch (const std::exception& e) {
       rootError = e.what();
       LOG_WARN(LogSubsys::NET, "bootstrap root failed: ", rootError);
@@ -234,7 +239,17 @@ class TcpBootstrap::Impl {
     toRoot.connect(rootAddr, timeoutMs, &abortFlag);
     toRoot.sendAll(&mine, sizeof(mine), timeoutMs, &abortFlag);
     table.resize(nRanks);
-    toRoot.recvAll(table.data(), sizeof(RankInfo) * nRanks, timeoutMs, &abortFlag);
+    try {
+      toRoot.recvAll(table.data(), sizeof(RankInfo) * nRanks, timeoutMs, &abortFlag);
+    } catch (const BaseError&) {
+      // Rank 0 talks to its own root thread. When that thread gave up (a rank never joined) it dropped every
+      // connection, which this side sees as "peer closed": report the root's reason (Timeout) instead.
+      if (rank == 0 && rootThread.joinable()) {
+        rootThread.join();
+        if (!rootError.empty()) throw Error(rootError, rootErrorCode);
+      }
+      throw;
+    }
     if (rank == 0 && rootThread.joinable()) rootThread.join();
     nRanksPerNode = 0;
     for (int r = 0; r < nRanks; r++)
