@@ -31,13 +31,30 @@ _NATIVE_NAMES = (
 __all__ = [
     "SymmetricMemory", "Algorithm", "AlgorithmBuilder", "AlgorithmCollection", "CommGroup", "GpuBuffer", "DslCompiler",
     "NativeCodeCompiler", "compile", "compile_native", "get_flag_buffer", "get_include", "get_lib", "version", "__version__",
-    "alloc_shared_physical_cuda", *_NATIVE_NAMES,
+    "alloc_shared_physical_cuda", "deprecated", *_NATIVE_NAMES,
 ]
 
 
 def native():
     """The compiled runtime module (raises if it has not been built)."""
     return _native_loader.load()
+
+
+def deprecated(new_cls):
+    """Decorator for a kept-for-compatibility name: calling the decorated class or function warns and builds `new_cls`
+    instead (same helper as the reference's package: python/mscclpp/__init__.py:119-131)."""
+    import functools
+    import warnings
+
+    def decorator(old_cls):
+        @functools.wraps(old_cls)
+        def wrapper(*args, **kwargs):
+            warnings.warn(f"{old_cls.__name__} is deprecated, use {new_cls.__name__} instead.", DeprecationWarning, stacklevel=2)
+            return new_cls(*args, **kwargs)
+
+        return wrapper
+
+    return decorator
 
 
 def alloc_shared_physical_cuda(nbytes: int, granularity=None):

@@ -10,7 +10,13 @@ import torch
 from . import native as _loader
 from .symm import tensor_from_pointer
 
-__all__ = ["GpuBuffer"]
+__all__ = ["GpuBuffer", "GpuBufferGranularity"]
+
+
+def __getattr__(name):
+    if name == "GpuBufferGranularity":  # the native enum, resolved on first use (the library may not be built yet)
+        return _loader.load().GpuBufferGranularity
+    raise AttributeError(name)
 
 
 def GpuBuffer(shape: Union[int, Sequence[int]], dtype: torch.dtype = torch.float32, device=None, granularity=None) -> torch.Tensor:

@@ -1,0 +1,5 @@
+"""`allgather_multi_nodes` under the module name the reference uses (python/mscclpp/default_algos/allgather_multi_nodes.py);
+the program itself lives in `multi_node.py` with the other hierarchical algorithms."""
+from .multi_node import allgather_multi_nodes
+
+__all__ = ["allgather_multi_nodes"]

@@ -1,0 +1,5 @@
+"""`allreduce_multi_nodes` under the module name the reference uses (python/mscclpp/default_algos/allreduce_multi_nodes.py);
+the program itself lives in `multi_node.py` with the other hierarchical algorithms."""
+from .multi_node import allreduce_multi_nodes
+
+__all__ = ["allreduce_multi_nodes"]

@@ -311,3 +311,33 @@ def test_numa_helpers_and_reference_export_names():
         'is_bulk_supported', 'is_nvls_supported', 'npkit', 'numa', 'version',
     ]
     assert not [n for n in reference_names if not hasattr(mp, n)]
+
+
+def test_compat_names_of_the_reference_layout():
+    import warnings
+
+    import mscclpp_b200 as mp
+    from mscclpp_b200._core import buffer
+    from mscclpp_b200.default_algos import multi_node
+    from mscclpp_b200.default_algos.allgather_multi_nodes import allgather_multi_nodes
+    from mscclpp_b200.default_algos.allreduce_multi_nodes import allreduce_multi_nodes
+    from mscclpp_b200.default_algos.reducescatter_multi_nodes import reducescatter_multi_nodes
+
+    assert allgather_multi_nodes is multi_node.allgather_multi_nodes
+    assert allreduce_multi_nodes is multi_node.allreduce_multi_nodes
+    assert reducescatter_multi_nodes is multi_node.reducescatter_multi_nodes
+    assert buffer.GpuBufferGranularity is mp.GpuBufferGranularity
+
+    class New:
+        def __init__(self, x):
+            self.x = x
+
+    @mp.deprecated(New)
+    class Old:
+        pass
+
+    with warnings.catch_warnings(record=True) as caught:
+        warnings.simplefilter("always")
+        obj = Old(3)
+    assert isinstance(obj, New) and obj.x == 3
+    assert any(issubclass(w.category, DeprecationWarning) and "Old is deprecated, use New" in str(w.message) for w in caught)
