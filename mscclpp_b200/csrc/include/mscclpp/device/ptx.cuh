@@ -7,8 +7,12 @@
 #include <cstdint>
 #include <cuda_runtime.h>
 
+#ifndef MSCCLPP_DEVICE_INLINE
 #define MSCCLPP_DEVICE_INLINE __forceinline__ __device__
+#endif
+#ifndef MSCCLPP_HOST_DEVICE_INLINE
 #define MSCCLPP_HOST_DEVICE_INLINE __forceinline__ __host__ __device__
+#endif
 
 #if defined(__CUDACC__)
 

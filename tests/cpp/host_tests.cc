@@ -18,6 +18,9 @@
 #include <mscclpp/errors.hpp>
 #include <mscclpp/executor.hpp>
 #include <mscclpp/numa.hpp>
+#include <mscclpp/utils.hpp>
+#include <mscclpp/version.hpp>
+#include <mscclpp/device.hpp>
 
 #include "core/json.hpp"
 #include "core/socket.hpp"
@@ -246,6 +249,32 @@ TEST(Env, SingletonAndDefaults) {
   if (std::getenv("MSCCLPP_HEAP_BYTES") == nullptr) EXPECT_EQ(e1->heapBytes, 2L << 30);
   if (std::getenv("MSCCLPP_IB_GID_INDEX") == nullptr) EXPECT_EQ(e1->ibGidIndex, -1);
   EXPECT_TRUE(!e1->cacheDir.empty());
+}
+
+TEST(Utils, HostNameIbDevicesVersion) {
+  const std::string full = getHostName(1024, '\0');
+  EXPECT_TRUE(!full.empty());
+  EXPECT_TRUE(getHostName(3, '\0').size() <= 3);
+  EXPECT_TRUE(getHostName(1024, full[0]).empty());  // cut at the first occurrence of the delimiter
+  const int n = getIBDeviceCount();
+  EXPECT_TRUE(n >= 0);
+  if (n == 0) {
+    EXPECT_THROW(getIBDeviceName(Transport::IB0), BaseError);
+  } else {
+    EXPECT_TRUE(getIBTransportByDeviceName(getIBDeviceName(Transport::IB0)) == Transport::IB0);
+  }
+  EXPECT_THROW(getIBDeviceName(Transport::CudaIpc), BaseError);
+  EXPECT_THROW(getIBTransportByDeviceName("no_such_device"), BaseError);
+  EXPECT_EQ(MSCCLPP_VERSION, MSCCLPP_MAJOR * 10000 + MSCCLPP_MINOR * 100 + MSCCLPP_PATCH);
+  EXPECT_TRUE(version().rfind(std::to_string(MSCCLPP_MAJOR) + "." + std::to_string(MSCCLPP_MINOR) + "." + std::to_string(MSCCLPP_PATCH), 0) == 0);
+  std::size_t seed = 0;
+  detail::hashCombine(seed, std::string("a"));
+  const std::size_t one = seed;
+  detail::hashCombine(seed, 7);
+  EXPECT_TRUE(one != 0 && seed != one);
+#ifndef MSCCLPP_HOST_COMPILE
+  EXPECT_TRUE(false);  // a plain host compiler must see MSCCLPP_HOST_COMPILE
+#endif
 }
 
 TEST(Numa, CpuListsAndBinding) {

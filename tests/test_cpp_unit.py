@@ -34,3 +34,17 @@ def test_cpp_host_unit_tests(tmp_path):
     r = subprocess.run([exe], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
     assert "0 failures" in r.stdout and "SKIPPED" not in r.stdout and "PERF socket_loopback_1MB" in r.stdout
+
+
+def test_device_side_public_headers_compile(tmp_path):
+    """assert_device / atomic_device / device / gpu / version headers in one sm_100a translation unit (compile only)."""
+    nvcc = "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        import pytest
+
+        pytest.skip("needs nvcc")
+    for flags in ([], ["-DDEBUG_BUILD"]):
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-I", os.path.join(PKG, "csrc", "include"), "-c",
+               os.path.join(ROOT, "tests", "kernels", "public_headers.cu"), "-o", str(tmp_path / "public_headers.o")] + flags
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-3000:]
