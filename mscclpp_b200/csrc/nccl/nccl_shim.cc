@@ -83,6 +83,11 @@ RealNccl& realNccl() {
 
 thread_local std::string lastError;
 
+// execution plans loaded through mscclLoadAlgo, by handle
+std::mutex loadedAlgoMutex;
+std::map<int, std::shared_ptr<DslAlgorithm>> loadedAlgos;
+int nextAlgoHandle = 1;
+
 ncclResult_t fail(ncclResult_t code, const std::string& msg) {
   lastError = msg;
   LOG_WARN(LogSubsys::NCCL, msg);
@@ -103,15 +108,7 @@ bool toDataType(ncclDataType_t t, DataType& out) {
   }
 }
 
-size_t typeSize(ncclDataType_t t) {
-  switch (t) {
-    case ncclInt8: case ncclUint8: case ncclFloat8e4m3: case ncclFloat8e5m2: return 1;
-    case ncclFloat16: case ncclBfloat16: return 2;
-    case ncclInt32: case ncclUint32: case ncclFloat32: return 4;
-    case ncclInt64: case ncclUint64: case ncclFloat64: return 8;
-    default: return 0;
-  }
-}
+size_t typeSize(ncclDataType_t t) { return ncclTypeSize(t); }
 
 bool forcedFallback(const char* op) {
   static std::vector<std::string> list = [] {
@@ -575,6 +572,84 @@ ncclResult_t ncclAlltoAll(const void* sendbuff, void* recvbuff, size_t count, nc
     if (realNccl().AlltoAll) return realNccl().AlltoAll(sendbuff, recvbuff, count, datatype, comm->real, stream);
     return fail(ncclInvalidUsage, "alltoall: the fallback NCCL has no ncclAlltoAll");
   });
+}
+
+ncclResult_t ncclAllToAll(const void* sendbuff, void* recvbuff, size_t count, ncclDataType_t datatype, ncclComm_t comm,
+                          cudaStream_t stream) {
+  return ncclAlltoAll(sendbuff, recvbuff, count, datatype, comm, stream);  // the spelling of the MSCCL++ header
+}
+
+ncclResult_t ncclAllToAllv(const void* sendbuff, const size_t sendcounts[], const size_t sdispls[], void* recvbuff,
+                           const size_t recvcounts[], const size_t rdispls[], ncclDataType_t datatype, ncclComm_t comm,
+                           cudaStream_t stream) {
+  if (comm == nullptr || comm->destroyed) return fail(ncclInvalidArgument, "alltoallv: invalid communicator");
+  if (sendcounts == nullptr || sdispls == nullptr || recvcounts == nullptr || rdispls == nullptr) return ncclInvalidArgument;
+  const int n = comm->nranks;
+  // Equal counts laid out back to back are a plain all-to-all: the native kernel takes it.
+  bool uniform = true;
+  for (int r = 0; r < n && uniform; r++) {
+    uniform = sendcounts[r] == sendcounts[0] && recvcounts[r] == sendcounts[0] && sdispls[r] == static_cast<size_t>(r) * sendcounts[0] &&
+              rdispls[r] == static_cast<size_t>(r) * sendcounts[0];
+  }
+  if (uniform) return ncclAlltoAll(sendbuff, recvbuff, sendcounts[0], datatype, comm, stream);
+  // Ragged sizes: grouped point-to-point on the fallback NCCL (the native ragged exchange lives in the MoE kernels).
+  if (comm->real == nullptr) {
+    return fail(ncclInvalidUsage, "alltoallv with ragged counts needs the fallback NCCL (set MSCCLPP_NCCL_LIB_PATH)");
+  }
+  RealNccl& r = realNccl();
+  const size_t ts = typeSize(datatype);
+  ncclResult_t rc = r.GroupStart();
+  for (int peer = 0; peer < n && rc == ncclSuccess; peer++) {
+    if (sendcounts[peer] > 0) rc = r.Send(static_cast<const char*>(sendbuff) + sdispls[peer] * ts, sendcounts[peer], datatype, peer, comm->real, stream);
+    if (rc == ncclSuccess && recvcounts[peer] > 0) rc = r.Recv(static_cast<char*>(recvbuff) + rdispls[peer] * ts, recvcounts[peer], datatype, peer, comm->real, stream);
+  }
+  const ncclResult_t end = r.GroupEnd();
+  return rc != ncclSuccess ? rc : end;
+}
+
+ncclResult_t mscclLoadAlgo(const char* mscclAlgoFilePath, mscclAlgoHandle_t* mscclAlgoHandle, int rank) {
+  if (mscclAlgoFilePath == nullptr || mscclAlgoHandle == nullptr) return ncclInvalidArgument;
+  try {
+    ExecutionPlan plan(mscclAlgoFilePath, rank);
+    auto algo = std::make_shared<DslAlgorithm>(mscclAlgoFilePath, plan);
+    std::lock_guard<std::mutex> lock(loadedAlgoMutex);
+    *mscclAlgoHandle = nextAlgoHandle++;
+    loadedAlgos[*mscclAlgoHandle] = algo;
+    return ncclSuccess;
+  } catch (const std::exception& e) {
+    return fail(ncclInvalidUsage, std::string("mscclLoadAlgo: ") + e.what());
+  }
+}
+
+ncclResult_t mscclRunAlgo(const void* sendBuff, const size_t[] /*sendCounts*/, const size_t[] /*sDisPls*/, void* recvBuff,
+                          const size_t[] /*recvCounts*/, const size_t[] /*rDisPls*/, size_t count, ncclDataType_t dataType, int /*root*/,
+                          int /*peer*/, ncclRedOp_t op, mscclAlgoHandle_t mscclAlgoHandle, ncclComm_t comm, cudaStream_t stream) {
+  if (comm == nullptr || comm->destroyed) return fail(ncclInvalidArgument, "mscclRunAlgo: invalid communicator");
+  std::shared_ptr<DslAlgorithm> algo;
+  {
+    std::lock_guard<std::mutex> lock(loadedAlgoMutex);
+    auto it = loadedAlgos.find(mscclAlgoHandle);
+    if (it == loadedAlgos.end()) return fail(ncclInvalidArgument, "mscclRunAlgo: unknown algorithm handle");
+    algo = it->second;
+  }
+  DataType dtype;
+  if (!toDataType(dataType, dtype)) return fail(ncclInvalidArgument, "mscclRunAlgo: unsupported data type");
+  if (op != ncclSum && op != ncclMin) return fail(ncclInvalidArgument, "mscclRunAlgo: sum and min are supported");
+  // `count` follows the NCCL convention of the plan's collective
+  const size_t unit = count * typeSize(dataType), all = unit * static_cast<size_t>(comm->nranks);
+  const std::string& coll = algo->collective();
+  const size_t inBytes = (coll == "reducescatter" || coll == "alltoall") ? all : unit;
+  const size_t outBytes = (coll == "allgather" || coll == "alltoall") ? all : unit;
+  if (sendBuff == nullptr || recvBuff == nullptr) return ncclInvalidArgument;
+  if (count == 0) return ncclSuccess;
+  const CommResult r = algo->execute(comm->comm, sendBuff, recvBuff, inBytes, outBytes, dtype, op == ncclMin ? MIN : SUM, stream,
+                                     comm->executor, 0, 0, false, {}, DataType::AUTO);
+  return r == CommResult::Success ? ncclSuccess : fail(toNccl(r), "mscclRunAlgo: " + algo->name() + " failed");
+}
+
+ncclResult_t mscclUnloadAlgo(mscclAlgoHandle_t mscclAlgoHandle) {
+  std::lock_guard<std::mutex> lock(loadedAlgoMutex);
+  return loadedAlgos.erase(mscclAlgoHandle) == 1 ? ncclSuccess : ncclInvalidArgument;
 }
 
 ncclResult_t ncclSend(const void* sendbuff, size_t count, ncclDataType_t datatype, int peer, ncclComm_t comm, cudaStream_t stream) {

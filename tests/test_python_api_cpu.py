@@ -341,3 +341,30 @@ def test_compat_names_of_the_reference_layout():
         obj = Old(3)
     assert isinstance(obj, New) and obj.x == 3
     assert any(issubclass(w.category, DeprecationWarning) and "Old is deprecated, use New" in str(w.message) for w in caught)
+
+
+def test_nccl_shim_plan_handles_and_alltoall_names(tmp_path):
+    """mscclLoadAlgo / mscclUnloadAlgo keep plans by handle; the entry points of the MSCCL++ header all exist."""
+    import mscclpp_b200 as mp
+    from mscclpp_b200.default_algos import single_node
+
+    lib = ctypes.CDLL(os.path.join(mp.get_lib(), "libmscclpp_b200_nccl.so"))
+    for name in ("ncclAllToAll", "ncclAlltoAll", "ncclAllToAllv", "mscclLoadAlgo", "mscclRunAlgo", "mscclUnloadAlgo"):
+        assert hasattr(lib, name), name
+    plan = tmp_path / "ar.json"
+    plan.write_text(single_node.build("allreduce_allpairs", 4).to_json())
+    h1, h2 = ctypes.c_int(0), ctypes.c_int(0)
+    assert lib.mscclLoadAlgo(str(plan).encode(), ctypes.byref(h1), 0) == 0
+    assert lib.mscclLoadAlgo(str(plan).encode(), ctypes.byref(h2), 3) == 0
+    assert h1.value > 0 and h2.value != h1.value
+    assert lib.mscclLoadAlgo(str(plan).encode(), ctypes.byref(h2), 4) != 0          # rank outside the plan
+    assert lib.mscclLoadAlgo(b"/nonexistent/plan.json", ctypes.byref(h2), 0) != 0
+    assert lib.mscclLoadAlgo(None, ctypes.byref(h2), 0) != 0
+    assert lib.mscclUnloadAlgo(h1.value) == 0
+    assert lib.mscclUnloadAlgo(h1.value) != 0                                         # already gone
+    # running needs a communicator: a null one is refused, as is an unknown handle
+    lib.mscclRunAlgo.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_size_t, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                        ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    assert lib.mscclRunAlgo(None, None, None, None, None, None, 16, 7, 0, 0, 0, 12345, None, None) != 0
+    lib.ncclAllToAllv.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
+    assert lib.ncclAllToAllv(None, None, None, None, None, None, 7, None, None) != 0
