@@ -10,6 +10,7 @@
 
 #include <mscclpp/core.hpp>
 #include <mscclpp/numa.hpp>
+#include <mscclpp/utils.hpp>
 #include <mscclpp/fifo.hpp>
 #include <mscclpp/gpu_utils.hpp>
 #include <mscclpp/memory_channel.hpp>
@@ -71,6 +72,9 @@ void registerCoreBindings(py::module_& m) {
       .def("none", &TransportFlags::none)
       .def("any", &TransportFlags::any)
       .def("count", &TransportFlags::count)
+      .def("all", &TransportFlags::all)
+      .def("__ior__", [](TransportFlags& a, const TransportFlags& b) { a |= b; return a; })
+      .def("__iand__", [](TransportFlags& a, const TransportFlags& b) { a &= b; return a; })
       .def("__or__", [](const TransportFlags& a, const TransportFlags& b) { return a | b; })
       .def("__or__", [](const TransportFlags& a, Transport b) { return a | b; })
       .def("__and__", [](const TransportFlags& a, const TransportFlags& b) { return a & b; })
@@ -114,6 +118,7 @@ void registerCoreBindings(py::module_& m) {
       .def("host_hash", &Endpoint::hostHash)
       .def("pid_hash", &Endpoint::pidHash)
       .def("max_write_queue_size", &Endpoint::maxWriteQueueSize)
+      .def("config", &Endpoint::config)
       .def("serialize", [](const Endpoint& e) {
         auto v = e.serialize();
         return py::bytes(v.data(), v.size());
@@ -148,7 +153,8 @@ void registerCoreBindings(py::module_& m) {
       .def("transport", &Connection::transport)
       .def("remote_transport", &Connection::remoteTransport)
       .def("local_device", &Connection::localDevice)
-      .def("get_max_write_queue_size", &Connection::getMaxWriteQueueSize);
+      .def("get_max_write_queue_size", &Connection::getMaxWriteQueueSize)
+      .def("context", &Connection::context);
 
   py::class_<Context, std::shared_ptr<Context>>(m, "Context")
       .def_static("create", &Context::create)
@@ -174,7 +180,8 @@ void registerCoreBindings(py::module_& m) {
   py::class_<Semaphore>(m, "Semaphore")
       .def(py::init<>())
       .def("local_memory", &Semaphore::localMemory)
-      .def("remote_memory", &Semaphore::remoteMemory);
+      .def("remote_memory", &Semaphore::remoteMemory)
+      .def("connection", &Semaphore::connection, py::return_value_policy::reference_internal);
 
   py::class_<Communicator, std::shared_ptr<Communicator>>(m, "Communicator")
       .def(py::init<std::shared_ptr<Bootstrap>, std::shared_ptr<Context>>(), py::arg("bootstrap"), py::arg("context") = nullptr)
@@ -190,6 +197,12 @@ void registerCoreBindings(py::module_& m) {
       .def("connect", [](Communicator& c, const Endpoint& e, int remoteRank, int tag) { return c.connect(e, remoteRank, tag); },
            py::arg("local_endpoint"), py::arg("remote_rank"), py::arg("tag") = 0)
       .def("build_semaphore", &Communicator::buildSemaphore, py::arg("connection"), py::arg("remote_rank"), py::arg("tag") = 0)
+      // names of the earlier two-phase API, kept as synonyms: everything is set up when the call returns
+      .def("connect_on_setup", [](Communicator& c, int remoteRank, int tag, const EndpointConfig& cfg) { return c.connect(cfg, remoteRank, tag); },
+           py::arg("remote_rank"), py::arg("tag"), py::arg("local_config"), py::call_guard<py::gil_scoped_release>())
+      .def("send_memory_on_setup", &Communicator::sendMemory, py::arg("memory"), py::arg("remote_rank"), py::arg("tag"))
+      .def("recv_memory_on_setup", &Communicator::recvMemory, py::arg("remote_rank"), py::arg("tag"))
+      .def("setup", [](Communicator&) {})
       .def("remote_rank_of", &Communicator::remoteRankOf)
       .def("tag_of", &Communicator::tagOf);
 
@@ -200,11 +213,13 @@ void registerCoreBindings(py::module_& m) {
       .def(py::init<const Semaphore&>())
       .def(py::init<Communicator&, const Connection&>(), py::call_guard<py::gil_scoped_release>())
       .def("signal", &Host2DeviceSemaphore::signal)
+      .def("connection", &Host2DeviceSemaphore::connection, py::return_value_policy::reference_internal)
       .def("device_handle", &Host2DeviceSemaphore::deviceHandle);
   py::class_<Host2HostSemaphore, std::shared_ptr<Host2HostSemaphore>>(m, "Host2HostSemaphore")
       .def(py::init<const Semaphore&>())
       .def(py::init<Communicator&, const Connection&>(), py::call_guard<py::gil_scoped_release>())
       .def("signal", &Host2HostSemaphore::signal)
+      .def("connection", &Host2HostSemaphore::connection, py::return_value_policy::reference_internal)
       .def("poll", &Host2HostSemaphore::poll)
       .def("wait", [](Host2HostSemaphore& s, int64_t maxSpin) {
         py::gil_scoped_release rel;
@@ -213,6 +228,7 @@ void registerCoreBindings(py::module_& m) {
   py::class_<MemoryDevice2DeviceSemaphore, std::shared_ptr<MemoryDevice2DeviceSemaphore>>(m, "MemoryDevice2DeviceSemaphore")
       .def(py::init<const Semaphore&>())
       .def(py::init<Communicator&, const Connection&>(), py::call_guard<py::gil_scoped_release>())
+      .def("connection", &MemoryDevice2DeviceSemaphore::connection, py::return_value_policy::reference_internal)
       .def("device_handle", &MemoryDevice2DeviceSemaphore::deviceHandle);
 
   // ------------------------------------------------------------------ channels
@@ -277,6 +293,7 @@ void registerCoreBindings(py::module_& m) {
   });
 
   // ------------------------------------------------------------------ buffers
+  m.def("get_host_name", &getHostName, py::arg("maxlen"), py::arg("delim"));
   py::enum_<GpuBufferGranularity>(m, "GpuBufferGranularity")
       .value("MultiCastMinimum", GpuBufferGranularity::MultiCastMinimum)
       .value("MultiCastRecommended", GpuBufferGranularity::MultiCastRecommended);
@@ -292,5 +309,6 @@ void registerCoreBindings(py::module_& m) {
            py::arg("granularity") = GpuBufferGranularity::MultiCastRecommended)
       .def("data", [](RawGpuBuffer& b) { return reinterpret_cast<uintptr_t>(b.buffer.data()); })
       .def("bytes", [](RawGpuBuffer& b) { return b.buffer.bytes(); })
+      .def("nelems", [](RawGpuBuffer& b) { return b.buffer.nelems(); })
       .def("device_id", [](RawGpuBuffer& b) { return b.buffer.deviceId(); });
 }

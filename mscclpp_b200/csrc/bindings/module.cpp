@@ -224,6 +224,7 @@ PYBIND11_MODULE(_native, m) {
       .value("float32", DataType::FLOAT32)
       .value("bfloat16", DataType::BFLOAT16)
       .value("float8_e4m3", DataType::FLOAT8_E4M3)
+      .value("float8_e4m3fn", DataType::FLOAT8_E4M3)  // the name torch and the reference use for the same format
       .value("float8_e5m2", DataType::FLOAT8_E5M2)
       .value("uint8", DataType::UINT8)
       .value("float8_e4m3b15", DataType::FLOAT8_E4M3B15)

@@ -368,3 +368,21 @@ def test_nccl_shim_plan_handles_and_alltoall_names(tmp_path):
     assert lib.mscclRunAlgo(None, None, None, None, None, None, 16, 7, 0, 0, 0, 12345, None, None) != 0
     lib.ncclAllToAllv.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p]
     assert lib.ncclAllToAllv(None, None, None, None, None, None, 7, None, None) != 0
+
+
+def test_binding_synonyms_of_the_reference(native):
+    import mscclpp_b200 as mp
+
+    assert native.get_host_name(64, ".") and "." not in native.get_host_name(64, ".")
+    assert mp.DataType.float8_e4m3fn == mp.DataType.float8_e4m3
+    flags = mp.TransportFlags(mp.Transport.CudaIpc)
+    flags |= mp.TransportFlags(mp.Transport.Ethernet)
+    assert flags.count() == 2 and not flags.all()
+    flags &= mp.TransportFlags(mp.Transport.Ethernet)
+    assert flags.count() == 1 and flags.has(mp.Transport.Ethernet)
+    for name in ("connect_on_setup", "send_memory_on_setup", "recv_memory_on_setup", "setup"):
+        assert hasattr(mp.Communicator, name)
+    for cls, name in ((mp.Connection, "context"), (mp.Semaphore, "connection"), (mp.Host2HostSemaphore, "connection"),
+                      (mp.Host2DeviceSemaphore, "connection"), (mp.MemoryDevice2DeviceSemaphore, "connection"),
+                      (native.RawGpuBuffer, "nelems"), (native.Endpoint, "config")):
+        assert hasattr(cls, name), (cls, name)
