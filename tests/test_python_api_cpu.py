@@ -386,3 +386,16 @@ def test_binding_synonyms_of_the_reference(native):
                       (mp.Host2DeviceSemaphore, "connection"), (mp.MemoryDevice2DeviceSemaphore, "connection"),
                       (native.RawGpuBuffer, "nelems"), (native.Endpoint, "config")):
         assert hasattr(cls, name), (cls, name)
+
+
+def test_raw_buffer_dlpack_helper_parses_types(native):
+    import torch
+
+    from mscclpp_b200._core.native import parse_torch_dtype
+
+    assert parse_torch_dtype("torch.float16") is torch.float16
+    assert parse_torch_dtype("bfloat16") is torch.bfloat16
+    assert parse_torch_dtype(torch.int32) is torch.int32
+    with pytest.raises(ValueError):
+        parse_torch_dtype("torch.nope")
+    assert callable(native.RawGpuBuffer.to_dlpack)
