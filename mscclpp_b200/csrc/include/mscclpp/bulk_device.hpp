@@ -33,7 +33,21 @@ struct BulkBarrier {
     return mbarWait(&word, phase, status, timeoutNs, 30);
   }
   MSCCLPP_DEVICE_INLINE void invalidate() { ptx::mbar_inval(&word); }
+
+  // The same operations under the names of the reference's BulkBarrier (include/mscclpp/bulk_device.hpp:68-136).
+  MSCCLPP_DEVICE_INLINE uint32_t addr() const { return static_cast<uint32_t>(__cvta_generic_to_shared(&word)); }
+  // init without the fence that publishes it to the async proxy (the caller fences, e.g. after several barriers)
+  MSCCLPP_DEVICE_INLINE void relaxedInit(uint32_t arrivals = 1) { ptx::mbar_init(&word, arrivals); }
+  // raise the expected byte count without arriving
+  MSCCLPP_DEVICE_INLINE void expect(uint32_t bytes) {
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(addr()), "r"(bytes) : "memory");
+  }
+  MSCCLPP_DEVICE_INLINE void arriveAndExpect(uint32_t bytes) { arriveExpectTx(bytes); }
+  MSCCLPP_DEVICE_INLINE bool poll(uint32_t phase) { return tryWait(phase); }
 };
+
+// cp.async.bulk wants both addresses on 16-byte boundaries (and sizes in multiples of 16 bytes).
+MSCCLPP_DEVICE_INLINE bool bulkAligned(const void* ptr) { return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0; }
 
 // global -> shared::cta, completion counted on `bar`.
 MSCCLPP_DEVICE_INLINE void bulkLoad(void* smemDst, const void* gmemSrc, uint32_t bytes, BulkBarrier& bar) {
@@ -74,6 +88,18 @@ MSCCLPP_DEVICE_INLINE void bulkWaitRead() {
 }
 // Make generic-proxy writes to shared memory visible to the async proxy before a bulkStore reads them.
 MSCCLPP_DEVICE_INLINE void bulkFenceSmem() { ptx::fence_proxy_async_smem(); }
+
+// Names of the reference for the four calls above (include/mscclpp/bulk_device.hpp:242-272).
+MSCCLPP_DEVICE_INLINE void bulkFence() { bulkFenceSmem(); }
+MSCCLPP_DEVICE_INLINE void bulkStoreCommit() { bulkCommit(); }
+template <uint32_t PendingGroups = 0>
+MSCCLPP_DEVICE_INLINE void bulkStoreWait() {
+  ptx::bulk_wait<static_cast<int>(PendingGroups)>();
+}
+template <uint32_t PendingGroups = 0>
+MSCCLPP_DEVICE_INLINE void bulkStoreWaitSource() {
+  ptx::bulk_wait_read<static_cast<int>(PendingGroups)>();
+}
 
 #endif  // __CUDACC__
 

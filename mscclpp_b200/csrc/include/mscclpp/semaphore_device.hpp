@@ -30,6 +30,14 @@ struct Host2DeviceSemaphoreDeviceHandle {
     const uint64_t next = ++(*expectedInboundToken);
     return waitGreaterEqual(inboundToken, next, status, timeoutNs, kDevTimeoutSemaphore, 0, 1, 0);
   }
+  // Building blocks under the names of the reference (include/mscclpp/semaphore_device.hpp:33-49), for kernels that
+  // compose their own waits.
+  MSCCLPP_DEVICE_INLINE uint64_t loadExpectedInbound() { return *reinterpret_cast<volatile uint64_t*>(expectedInboundToken); }
+  MSCCLPP_DEVICE_INLINE uint64_t incExpectedInbound() {
+    return atomicAdd(reinterpret_cast<unsigned long long*>(expectedInboundToken), 1ull) + 1;
+  }
+  MSCCLPP_DEVICE_INLINE uint64_t loadInbound() { return ptx::ld_acquire_sys(inboundToken); }
+  MSCCLPP_DEVICE_INLINE uint64_t loadInboundRelaxed() { return ptx::ld_relaxed_sys(inboundToken); }
 #endif
 };
 
@@ -75,6 +83,14 @@ struct MemoryDevice2DeviceSemaphoreDeviceHandle {
     ++(*outboundToken);
     ptx::red_relaxed_sys_add(remoteInboundToken, 1);
   }
+  // Building blocks under the names of the reference (include/mscclpp/semaphore_device.hpp:33-49), for kernels that
+  // compose their own waits.
+  MSCCLPP_DEVICE_INLINE uint64_t loadExpectedInbound() { return *reinterpret_cast<volatile uint64_t*>(expectedInboundToken); }
+  MSCCLPP_DEVICE_INLINE uint64_t incExpectedInbound() {
+    return atomicAdd(reinterpret_cast<unsigned long long*>(expectedInboundToken), 1ull) + 1;
+  }
+  MSCCLPP_DEVICE_INLINE uint64_t loadInbound() { return ptx::ld_acquire_sys(inboundToken); }
+  MSCCLPP_DEVICE_INLINE uint64_t loadInboundRelaxed() { return ptx::ld_relaxed_sys(inboundToken); }
 #endif
 };
 
