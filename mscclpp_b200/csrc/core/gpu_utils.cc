@@ -297,6 +297,13 @@ void gpuMemcpyAsync(void* dst, const void* src, size_t bytes, cudaStream_t strea
   MSCCLPP_CUDATHROW(cudaMemcpyAsync(dst, src, bytes, kind, stream));
 }
 
+void gpuMemset(void* ptr, int value, size_t bytes) {
+  AvoidCudaGraphCaptureGuard guard;
+  cudaStream_t s = setupStream();
+  MSCCLPP_CUDATHROW(cudaMemsetAsync(ptr, value, bytes, s));
+  MSCCLPP_CUDATHROW(cudaStreamSynchronize(s));
+}
+
 void gpuMemcpy(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind) {
   AvoidCudaGraphCaptureGuard guard;
   cudaStream_t s = setupStream();

@@ -111,9 +111,37 @@ std::shared_ptr<T> gpuCallocPhysicalShared(size_t count = 1, size_t granularity 
                             GpuPhysicalDeleter<T>());
 }
 
+// The remaining members of the allocation family (unique_ptr flavours; "uncached" is ordinary device memory on NVIDIA
+// GPUs, where fine-grained coherence needs no special allocation - the name exists for source compatibility with
+// include/mscclpp/gpu_utils.hpp:205-300 of the reference).
+template <class T>
+using UniqueGpuPtr = std::unique_ptr<T, GpuDeleter<T>>;
+template <class T>
+using UniqueGpuHostPtr = std::unique_ptr<T, GpuHostDeleter<T>>;
+template <class T>
+using UniqueGpuPhysicalPtr = std::unique_ptr<T, GpuPhysicalDeleter<T>>;
+template <class T>
+UniqueGpuHostPtr<T> gpuCallocHostUnique(size_t count = 1, unsigned flags = cudaHostAllocMapped) {
+  return UniqueGpuHostPtr<T>(static_cast<T*>(detail::gpuCallocHost(count * sizeof(T), flags)));
+}
+template <class T>
+UniqueGpuPhysicalPtr<T> gpuCallocPhysicalUnique(size_t count = 1, size_t granularity = 0) {
+  return UniqueGpuPhysicalPtr<T>(static_cast<T*>(detail::gpuCallocPhysical(count * sizeof(T), granularity)));
+}
+template <class T>
+std::shared_ptr<T> gpuCallocUncachedShared(size_t count = 1) {
+  return gpuCallocShared<T>(count);
+}
+template <class T>
+UniqueGpuPtr<T> gpuCallocUncachedUnique(size_t count = 1) {
+  return gpuCallocUnique<T>(count);
+}
+
 // Synchronous copy helpers (cudaMemcpy on a private stream, safe during graph capture elsewhere).
 void gpuMemcpy(void* dst, const void* src, size_t bytes, cudaMemcpyKind kind = cudaMemcpyDefault);
 void gpuMemcpyAsync(void* dst, const void* src, size_t bytes, cudaStream_t stream, cudaMemcpyKind kind = cudaMemcpyDefault);
+// Synchronous byte fill on the same private stream.
+void gpuMemset(void* ptr, int value, size_t bytes);
 
 bool isNvlsSupported();          // multicast objects available and not disabled by MSCCLPP_FORCE_DISABLE_NVLS
 bool isBulkSupported();          // cp.async.bulk available (compute capability >= 9)

@@ -17,6 +17,7 @@
 #include <mscclpp/env.hpp>
 #include <mscclpp/errors.hpp>
 #include <mscclpp/executor.hpp>
+#include <mscclpp/gpu_utils.hpp>
 #include <mscclpp/numa.hpp>
 #include <mscclpp/utils.hpp>
 #include <mscclpp/version.hpp>
@@ -275,6 +276,17 @@ TEST(Utils, HostNameIbDevicesVersion) {
 #ifndef MSCCLPP_HOST_COMPILE
   EXPECT_TRUE(false);  // a plain host compiler must see MSCCLPP_HOST_COMPILE
 #endif
+}
+
+TEST(GpuUtils, AllocationFamilyInstantiates) {
+  // no GPU here: only check that every member of the family exists with the expected types
+  std::shared_ptr<int> (*a)(size_t) = &gpuCallocUncachedShared<int>;
+  UniqueGpuPtr<int> (*b)(size_t) = &gpuCallocUncachedUnique<int>;
+  UniqueGpuHostPtr<int> (*c)(size_t, unsigned) = &gpuCallocHostUnique<int>;
+  UniqueGpuPhysicalPtr<int> (*d)(size_t, size_t) = &gpuCallocPhysicalUnique<int>;
+  void (*e)(void*, int, size_t) = &gpuMemset;
+  EXPECT_TRUE(a != nullptr && b != nullptr && c != nullptr && d != nullptr && e != nullptr);
+  EXPECT_TRUE(static_cast<int>(GpuBufferGranularity::MultiCastMinimum) != static_cast<int>(GpuBufferGranularity::MultiCastRecommended));
 }
 
 TEST(Numa, CpuListsAndBinding) {
