@@ -38,6 +38,17 @@ MSCCLPP_DEVICE_INLINE void copyBytes(void* dst, const void* src, uint64_t bytes,
   }
 }
 
+// The two `copy` overloads of the reference (include/mscclpp/copy_device.hpp:34-127). The byte form ignores its
+// template parameters: copyBytes already picks the widest access the two addresses allow and always copies the tail.
+template <typename T>
+MSCCLPP_DEVICE_INLINE void copy(T* dst, T* src, uint64_t numElems, uint32_t threadId, uint32_t numThreads) {
+  for (uint64_t i = threadId; i < numElems; i += numThreads) dst[i] = src[i];
+}
+template <int Alignment = 16, bool CopyRemainder = true>
+MSCCLPP_DEVICE_INLINE void copy(void* dst, void* src, uint64_t bytes, uint32_t threadId, uint32_t numThreads) {
+  copyBytes(dst, src, bytes, threadId, numThreads);
+}
+
 // Plain data -> packets. originBytes must be a multiple of the packet payload (8 for LL16, 4 for LL8).
 template <typename PacketType>
 MSCCLPP_DEVICE_INLINE void copyToPackets(void* packets, const void* origin, uint64_t originBytes, uint32_t threadId,

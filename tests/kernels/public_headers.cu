@@ -6,6 +6,7 @@
 #include <mscclpp/gpu.hpp>
 #include <mscclpp/version.hpp>
 #include <mscclpp/bulk_device.hpp>
+#include <mscclpp/copy_device.hpp>
 #include <mscclpp/semaphore_device.hpp>
 
 #if !defined(MSCCLPP_DEVICE_CUDA) || !defined(CUDA_NVLS_API_AVAILABLE)
@@ -43,4 +44,10 @@ __global__ void names(mscclpp::MemoryDevice2DeviceSemaphoreDeviceHandle sem, msc
     out[0] = sem.loadInbound() + sem.loadInboundRelaxed() + sem.loadExpectedInbound() + sem.incExpectedInbound();
     out[1] = h2d.loadInbound() + h2d.loadExpectedInbound();
   }
+}
+
+__global__ void copies(float* a, float* b, void* c, void* d, unsigned long long bytes) {
+  mscclpp::copy(a, b, bytes / 4, threadIdx.x, blockDim.x);
+  mscclpp::copy(c, d, bytes, threadIdx.x, blockDim.x);
+  mscclpp::copy<4, false>(c, d, bytes, threadIdx.x, blockDim.x);
 }
