@@ -43,6 +43,8 @@ union alignas(16) LL16Packet {
     out = make_uint2(r.x, r.z);
     return r.y == flag && r.w == flag;
   }
+  // Name and sense of the reference (include/mscclpp/packet_device.hpp:66): true while the packet has NOT arrived.
+  MSCCLPP_DEVICE_INLINE bool readOnce(uint32_t flag, uint2& data) const { return !tryRead(flag, data); }
   // Bounded blocking read. Returns false (payload undefined) when the budget ran out.
   MSCCLPP_DEVICE_INLINE bool read(uint32_t flag, uint2& out, DeviceStatus* st, uint64_t budgetNs, uint32_t rank = 0,
                                   uint32_t peer = 0) const {
@@ -76,6 +78,7 @@ union alignas(8) LL8Packet {
     out = r.x;
     return r.y == f;
   }
+  MSCCLPP_DEVICE_INLINE bool readOnce(uint32_t f, uint32_t& data) const { return !tryRead(f, data); }
   MSCCLPP_DEVICE_INLINE bool read(uint32_t f, uint32_t& out, DeviceStatus* st, uint64_t budgetNs, uint32_t rank = 0,
                                   uint32_t peer = 0) const {
     SpinGuard g(st, budgetNs);

@@ -7,6 +7,7 @@
 #include <mscclpp/version.hpp>
 #include <mscclpp/bulk_device.hpp>
 #include <mscclpp/copy_device.hpp>
+#include <mscclpp/packet_device.hpp>
 #include <mscclpp/semaphore_device.hpp>
 
 #if !defined(MSCCLPP_DEVICE_CUDA) || !defined(CUDA_NVLS_API_AVAILABLE)
@@ -50,4 +51,11 @@ __global__ void copies(float* a, float* b, void* c, void* d, unsigned long long 
   mscclpp::copy(a, b, bytes / 4, threadIdx.x, blockDim.x);
   mscclpp::copy(c, d, bytes, threadIdx.x, blockDim.x);
   mscclpp::copy<4, false>(c, d, bytes, threadIdx.x, blockDim.x);
+}
+
+__global__ void packets(mscclpp::LL16Packet* p16, mscclpp::LL8Packet* p8, unsigned* out) {
+  uint2 a;
+  unsigned b;
+  out[0] = p16->readOnce(1u, a) ? 0u : a.x;
+  out[1] = p8->readOnce(1u, b) ? 0u : b;
 }
