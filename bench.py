@@ -94,20 +94,44 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    """The reference arm must run the unmodified reference installed under baseline/_ref. Its offline
-    install does not complete in this image (the build backend needs setuptools_scm, which is absent,
-    and its CMake project fetches nlohmann_json / nanobind / dlpack from the network), so there is
-    nothing to run."""
-    ref_dir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "baseline", "_ref")
-    usable = os.path.isdir(os.path.join(ref_dir, "mscclpp")) and any(
-        f.startswith("_mscclpp") for f in os.listdir(os.path.join(ref_dir, "mscclpp")))
-    if not usable:
-        print(json.dumps({"impl": "reference", "unavailable": "offline install of the reference failed: build backend needs "
-                          "setuptools_scm (absent) and CMake FetchContent needs network (nlohmann_json, nanobind, dlpack)"}))
+    """Runs the unmodified reference (built with CMake into baseline/_ref) on its stock PyTorch path: this
+    interpreter is replaced by one that has the reference's NCCL-API library preloaded (LD_PRELOAD, the way its
+    quickstart documents; MSCCLPP_NCCL_LIB_PATH names the real NCCL for what the reference does not implement) and
+    runs baseline/reference_arm.py: cuBLAS GEMM + dist.all_reduce through the reference + PyTorch residual add and
+    RMSNorm, same shapes, steps, warm-up and copies as the other arm. Nothing of this repository's package is on
+    that path."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    ref_lib = os.path.join(here, "baseline", "_ref", "lib")
+    shim = os.path.join(ref_lib, "libmscclpp_nccl.so")
+    script = os.path.join(here, "baseline", "reference_arm.py")
+    if not os.path.exists(shim):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/lib/libmscclpp_nccl.so is missing: build the "
+                          "reference with baseline/build_reference.sh (CMake, no network needed)"}))
         return 0
-    print(json.dumps({"impl": "reference", "unavailable": "reference present but it has no fused TP-layer entry point "
-                      "(it is a collective library only)"}))
-    return 0
+    try:
+        import ctypes
+        ctypes.CDLL("libcuda.so.1")
+    except OSError:
+        print(json.dumps({"impl": "reference", "unavailable": "no CUDA driver (libcuda.so.1) on this machine: the preloaded "
+                          "reference library cannot be loaded here"}))
+        return 0
+    try:
+        import nvidia.cuda_runtime
+        import nvidia.nccl
+        nccl_lib = os.path.join(list(nvidia.nccl.__path__)[0], "lib", "libnccl.so.2")
+        cudart_dir = os.path.join(list(nvidia.cuda_runtime.__path__)[0], "lib")
+    except ImportError:
+        nccl_lib, cudart_dir = "", "/usr/local/cuda/lib64"
+    env = dict(os.environ)
+    env["LD_PRELOAD"] = shim + (":" + env["LD_PRELOAD"] if env.get("LD_PRELOAD") else "")
+    env["LD_LIBRARY_PATH"] = ":".join(x for x in (ref_lib, cudart_dir, env.get("LD_LIBRARY_PATH", "")) if x)
+    if nccl_lib and os.path.exists(nccl_lib):
+        env.setdefault("MSCCLPP_NCCL_LIB_PATH", nccl_lib)
+    env.setdefault("MSCCLPP_SOCKET_IFNAME", "lo")  # one node: the reference's bootstrap stays on the loopback interface
+    argv = [sys.executable, script, "--gpus", str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup),
+            "--sweep-max-bytes", str(args.sweep_max_bytes)] + (["--no-sweep"] if args.no_sweep else [])
+    sys.stdout.flush()
+    os.execve(sys.executable, argv, env)
 
 
 def main():
