@@ -232,6 +232,7 @@ def main() -> int:
     if world > 1 and not args.no_sweep:
         buf = torch.empty((args.sweep_max_bytes // 2,), dtype=torch.bfloat16, device=dev).normal_()
         size = 1024
+        graphs_ok = True  # small messages capture fine even where a large layer did not
         while size <= args.sweep_max_bytes:
             n = size // 2
             iters = 50 if size <= (1 << 20) else (20 if size <= (64 << 20) else 8)

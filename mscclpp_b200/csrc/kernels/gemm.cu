@@ -2,6 +2,8 @@
 #include "gemm.cuh"
 
 #include <mutex>
+#include <set>
+#include <utility>
 
 #include "gemm2_sm100.cuh"
 #include "gemm_sm100.cuh"
@@ -31,43 +33,53 @@ EncodeFn encodeFn() {
 
 template <int kBlockN>
 __global__ void __launch_bounds__(kNumThreads, 1)
-    gemmBf16Kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, Shape shape,
-                   __nv_bfloat16* D, int ldd, DeviceStatus* status, uint64_t budgetNs) {
+    gemmBf16Kernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                   const __grid_constant__ CUtensorMap tmapD, Shape shape, DeviceStatus* status, uint64_t budgetNs) {
   extern __shared__ uint8_t smemRaw[];
   NoGate gate;
-  StoreBf16 epi{D, ldd, shape.M};
+  StoreBf16 epi{&tmapD, shape.M};
+  if (threadIdx.x == 0) ptx::tma_prefetch_desc(&tmapD);
   gemmCta<kBlockN>(&tmapA, &tmapB, shape, blockIdx.x, gridDim.x, gate, epi, status, budgetNs, smemRaw);
 }
 
 template <int kBlockN>
-cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, Shape shape, void* D, int ldd, int numCtas,
+cudaError_t launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& td, Shape shape, int numCtas,
                    DeviceStatus* status, cudaStream_t stream) {
   using Cfg = Config<kBlockN>;
-  static bool attrSet = false;
-  if (!attrSet) {
-    cudaError_t e = cudaFuncSetAttribute(gemmBf16Kernel<kBlockN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         Cfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attrSet = true;
-  }
+  cudaError_t e = ensureDynamicSmem(reinterpret_cast<const void*>(gemmBf16Kernel<kBlockN>), Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
   const int tiles = ((shape.M + kBlockM - 1) / kBlockM) * (shape.N / kBlockN);
   int grid = numCtas > 0 ? numCtas : smCount();
   if (grid > tiles) grid = tiles;
-  gemmBf16Kernel<kBlockN><<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, shape, static_cast<__nv_bfloat16*>(D),
-                                                                          ldd, status, 2000000000ull);
+  gemmBf16Kernel<kBlockN><<<grid, kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, td, shape, status, 2000000000ull);
   return cudaGetLastError();
 }
 
 __global__ void __launch_bounds__(kNumThreads, 1)
-    gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, Shape shape,
-                       __nv_bfloat16* D, int ldd, DeviceStatus* status, uint64_t budgetNs) {
+    gemmBf16PairKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB,
+                       const __grid_constant__ CUtensorMap tmapD, Shape shape, DeviceStatus* status, uint64_t budgetNs) {
   extern __shared__ uint8_t smemRaw[];
   NoGate gate;
-  StoreBf16 epi{D, ldd, shape.M};
+  StoreBf16 epi{&tmapD, shape.M};
+  if (threadIdx.x == 0) ptx::tma_prefetch_desc(&tmapD);
   gemmCtaPair(&tmapA, &tmapB, shape, blockIdx.x / 2, gridDim.x / 2, gate, epi, status, budgetNs, smemRaw);
 }
 
 }  // namespace
+
+cudaError_t ensureDynamicSmem(const void* kernel, int bytes) {
+  // the attribute belongs to the (kernel, device) pair: a process that drives several GPUs sets it on each of them
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.count({kernel, dev})) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.insert({kernel, dev});
+  return e;
+}
 
 cudaError_t launchClusterPair(const void* kernel, dim3 grid, dim3 block, size_t smemBytes, void** params, bool cooperative,
                               cudaStream_t stream) {
@@ -89,41 +101,40 @@ cudaError_t launchClusterPair(const void* kernel, dim3 grid, dim3 block, size_t 
 }
 
 cudaError_t gemmBf16TwoSm(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int numCtas, DeviceStatus* status,
-                          cudaStream_t stream) {
+                          cudaStream_t stream, int probe) {
   if (M <= 0 || N <= 0 || K <= 0 || K % kBlockK != 0 || N % Config2::kBlockN != 0 || ldd % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(D) & 15) != 0) return cudaErrorInvalidValue;
-  Shape shape{M, N, K, kBlockM, 0, 0, 0};
-  CUtensorMap ta, tb;
+  Shape shape{M, N, K, kBlockM, 0, 0, 0, probe};
+  CUtensorMap ta, tb, td;
   cudaError_t e = makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, kBlockM);
   if (e != cudaSuccess) return e;
   e = makeTensorMapBf16(&tb, B, N, K, static_cast<uint64_t>(K) * 2, Config2::kBlockN / 2);
   if (e != cudaSuccess) return e;
-  static bool attrSet = false;
-  if (!attrSet) {
-    e = cudaFuncSetAttribute(gemmBf16PairKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Config2::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attrSet = true;
-  }
+  e = makeTensorMapBf16(&td, D, M, N, static_cast<uint64_t>(ldd) * 2, 32);
+  if (e != cudaSuccess) return e;
+  e = ensureDynamicSmem(reinterpret_cast<const void*>(gemmBf16PairKernel), Config2::kSmemBytes);
+  if (e != cudaSuccess) return e;
   const int tiles = ((M + Config2::kPairM - 1) / Config2::kPairM) * (N / Config2::kBlockN);
   int grid = numCtas > 0 ? numCtas : smCount();
   grid &= ~1;
   if (grid > 2 * tiles) grid = 2 * tiles;
   if (grid < 2) grid = 2;
-  __nv_bfloat16* d = static_cast<__nv_bfloat16*>(D);
   uint64_t budget = 2000000000ull;
-  void* params[] = {&ta, &tb, &shape, &d, &ldd, &status, &budget};
+  void* params[] = {&ta, &tb, &td, &shape, &status, &budget};
   return launchClusterPair(reinterpret_cast<const void*>(gemmBf16PairKernel), dim3(grid), dim3(kNumThreads), Config2::kSmemBytes, params,
                            false, stream);
 }
 
 int smCount() {
-  static int n = 0;
-  if (n == 0) {
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-      n = 148;
+  static int cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
   }
-  return n;
+  return cached[dev];
 }
 
 cudaError_t makeTensorMapBf16(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t rowStrideBytes,
@@ -142,22 +153,24 @@ cudaError_t makeTensorMapBf16(CUtensorMap* map, const void* ptr, uint64_t rows, 
 }
 
 cudaError_t gemmBf16(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int blockN, int numCtas,
-                     DeviceStatus* status, cudaStream_t stream) {
+                     DeviceStatus* status, cudaStream_t stream, int probe) {
   if (M <= 0 || N <= 0 || K <= 0 || K % kBlockK != 0 || N % blockN != 0 || ldd % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(D) & 15) != 0) return cudaErrorInvalidValue;
-  Shape shape{M, N, K, M < kBlockM ? M : kBlockM, 0};
-  CUtensorMap ta, tb;
+  Shape shape{M, N, K, M < kBlockM ? M : kBlockM, 0, 0, 0, probe};
+  CUtensorMap ta, tb, td;
   cudaError_t e = makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, shape.aBoxRows);
   if (e != cudaSuccess) return e;
   e = makeTensorMapBf16(&tb, B, N, K, static_cast<uint64_t>(K) * 2, blockN);
   if (e != cudaSuccess) return e;
+  e = makeTensorMapBf16(&td, D, M, N, static_cast<uint64_t>(ldd) * 2, 32);  // 64-column x 32-row boxes of the output
+  if (e != cudaSuccess) return e;
   switch (blockN) {
     case 64:
-      return launch<64>(ta, tb, shape, D, ldd, numCtas, status, stream);
+      return launch<64>(ta, tb, td, shape, numCtas, status, stream);
     case 128:
-      return launch<128>(ta, tb, shape, D, ldd, numCtas, status, stream);
+      return launch<128>(ta, tb, td, shape, numCtas, status, stream);
     case 256:
-      return launch<256>(ta, tb, shape, D, ldd, numCtas, status, stream);
+      return launch<256>(ta, tb, td, shape, numCtas, status, stream);
     default:
       return cudaErrorInvalidValue;
   }

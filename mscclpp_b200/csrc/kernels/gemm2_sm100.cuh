@@ -25,7 +25,9 @@ struct Config2 {
   static constexpr int kStages = 6;
   static constexpr int kTmemCols = 2 * kBlockN;  // two accumulator buffers of 256 columns
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+  static constexpr int kEpiWarps = kNumEpilogueWarps;
+  static constexpr int kColsPerWarp = kBlockN / 2;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueStagingBytes + kBarrierBytes + 1024;
 };
 
 MSCCLPP_HOST_DEVICE_INLINE constexpr uint32_t makeInstrDescPair() {
@@ -46,7 +48,8 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
 
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint8_t* staging = smem + Cfg::kStages * Cfg::kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpilogueStagingBytes);
   SharedState st;
   st.full = bars;
   st.empty = bars + Cfg::kStages;
@@ -111,9 +114,13 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
           uint8_t* sa = tiles + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageABytes;
           const uint32_t leaderFull = ptx::mapa_shared(ptx::smem_u32(&st.full[stage]), 0);
-          if (leader) ptx::mbar_expect_tx(&st.full[stage], 2 * Cfg::kStageBytes);
-          ptx::tma_load_2d_pair(sa, tmapARows, kb * kBlockK, aRow, leaderFull);
-          ptx::tma_load_2d_pair(sb, tmapB, kb * kBlockK, nBlk * Cfg::kBlockN + static_cast<int>(ctaRank) * (Cfg::kBlockN / 2), leaderFull);
+          if (shape.probe & 1) {
+            if (leader) ptx::mbar_arrive(&st.full[stage]);
+          } else {
+            if (leader) ptx::mbar_expect_tx(&st.full[stage], 2 * Cfg::kStageBytes);
+            ptx::tma_load_2d_pair(sa, tmapARows, kb * kBlockK, aRow, leaderFull);
+            ptx::tma_load_2d_pair(sb, tmapB, kb * kBlockK, nBlk * Cfg::kBlockN + static_cast<int>(ctaRank) * (Cfg::kBlockN / 2), leaderFull);
+          }
           issuedUses++;
           if (++stage == Cfg::kStages) {
             stage = 0;
@@ -155,9 +162,11 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
           const uint32_t sb = sa + Cfg::kStageABytes;
           const uint64_t descA = makeSmemDesc(sa);
           const uint64_t descB = makeSmemDesc(sb);
+          if (!(shape.probe & 2)) {
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; k++) {
-            ptx::tcgen05_mma_f16_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kBlockK / kUmmaK; k++) {
+              ptx::tcgen05_mma_f16_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           ptx::tcgen05_commit_pair(&st.empty[stage], 3);  // both CTAs may refill this stage once the MMAs retire
           if (++stage == Cfg::kStages) {
@@ -172,8 +181,8 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
   } else if (warp < 2 + kNumEpilogueWarps) {
     // ===================================================== epilogue (8 warps per CTA, on this CTA's accumulator rows)
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
-    constexpr int kChunksPerWarp = Cfg::kBlockN / 32 / (kNumEpilogueWarps / 4);
+    const int part = (warp - 2) >> 2;
+    uint8_t* stage = staging + (warp - 2) * kStagingBytesPerWarp;
     bool ok = true;
     int it = 0;
     for (int tile = pairIdx; tile < numTiles && ok; tile += numPairs, it++) {
@@ -182,25 +191,17 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
       const int mBlk = 2 * mBlk2 + static_cast<int>(ctaRank);
       const int acc = it & 1;
       const uint32_t accPhase = (it >> 1) & 1;
-      const int row = mBlk * kBlockM + quarter * 32 + lane;
+      const int row0 = mBlk * kBlockM + quarter * 32;
+      const int col0 = nBlk * Cfg::kBlockN + part * Cfg::kColsPerWarp;
       // lets the epilogue put loads it will need (a residual, a bias) in flight while the MMAs of this tile still run
-      epi.tileBegin(row, nBlk * Cfg::kBlockN + half * kChunksPerWarp * 32);
+      epi.tileBegin(row0, col0, lane);
       ok = mbarWait(&st.tmemFull[acc], accPhase, status, budgetNs, 400 + acc);
       ok = __all_sync(0xffffffffu, ok) && (*st.abortFlag == 0);
       if (!ok) break;
       ptx::tcgen05_fence_after_sync();
-      const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::kBlockN;
-#pragma unroll
-      for (int i = 0; i < kChunksPerWarp; i++) {
-        const int c = half * kChunksPerWarp + i;
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
-        ptx::tmem_ld_wait();
-        epi.store(row, nBlk * Cfg::kBlockN + c * 32, v, i);  // i: index of the slice within this warp's part of the tile
-      }
-      ptx::tcgen05_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(&st.tmemEmpty[acc]), 0));
+      const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::kBlockN + part * Cfg::kColsPerWarp;
+      const uint32_t leaderEmpty = ptx::mapa_shared(ptx::smem_u32(&st.tmemEmpty[acc]), 0);
+      stagedEpilogueTile<Cfg::kColsPerWarp>(epi, taddr, stage, row0, col0, lane, [&] { ptx::mbar_arrive_cluster(leaderEmpty); }, (shape.probe & 4) != 0);
       if constexpr (Epilogue::kNeedsTileBarrier) {
         __syncwarp();
         if (lane == 0) {
@@ -225,6 +226,9 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
       }
     }
     if (!ok && lane == 0) *st.abortFlag = 1;
+    if constexpr (Epilogue::kBulkStore) {
+      if (lane == 0) ptx::bulk_wait<0>();
+    }
   }
 
   // ---- teardown: both CTAs meet (the peer may still read my shared memory or signal my barriers until then)

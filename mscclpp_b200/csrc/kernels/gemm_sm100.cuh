@@ -10,9 +10,13 @@
 // Hooks for that fusion:
 //   * AGate     - called by the TMA producer before it loads the A tiles of a row block, so an
 //                 all-gather that is still in flight can be waited for block by block;
-//   * Epilogue  - receives each 32-column slice of the accumulator (one row per thread) and a
-//                 tileDone() call after all 128 epilogue threads have stored their part, where a
-//                 fused kernel signals consumers (reduce-scatter / allreduce owners);
+//   * Epilogue  - each epilogue warp converts a 32-row x 64-column block of the accumulator to bf16 and
+//                 writes it into its own 4 KB of shared memory in the 128-byte-swizzled layout of a TMA
+//                 box; Epilogue::block() then moves it out with ONE cp.async.bulk.tensor store, or re-reads
+//                 it with a row-contiguous lane mapping (stagedRead) so that every global load and store
+//                 of a fused epilogue (residual add, partial products for a collective) covers whole
+//                 128-byte lines. tileDone() follows once all epilogue warps have stored their part; there
+//                 a fused kernel signals consumers (reduce-scatter / allreduce owners);
 //   * aux CTAs  - blocks with blockIdx.x >= number of GEMM CTAs run a caller-supplied role
 //                 (reducer, copier) inside the same launch.
 // Every wait is bounded; on expiry the kernel records a DeviceStatus, drains its own TMA copies,
@@ -38,6 +42,8 @@ constexpr int kUmmaK = 16;           // K of one tcgen05.mma for 16-bit inputs
 constexpr int kNumEpilogueWarps = 8;  // two warps per TMEM lane quarter, each takes half of the tile's columns
 constexpr int kNumEpilogueThreads = kNumEpilogueWarps * 32;
 constexpr int kNumThreads = 64 + kNumEpilogueThreads;  // warp 0: TMA, warp 1: MMA + TMEM owner, warps 2-9: epilogue
+constexpr int kStagingBytesPerWarp = 32 * 128;  // 32 rows x 64 bf16 columns
+constexpr int kEpilogueStagingBytes = kNumEpilogueWarps * kStagingBytesPerWarp;
 
 template <int kBlockN>
 struct Config {
@@ -48,7 +54,10 @@ struct Config {
   static constexpr int kStages = kBlockN == 256 ? 4 : (kBlockN == 128 ? 6 : 8);
   static constexpr int kTmemCols = 2 * kBlockN;  // two accumulator buffers (power of two >= 32)
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;  // +1024: manual alignment
+  // epilogue warps that take part: every warp owns 32 rows (its TMEM lane quarter) x a multiple of 64 columns
+  static constexpr int kEpiWarps = kBlockN >= 128 ? kNumEpilogueWarps : 4;
+  static constexpr int kColsPerWarp = kBlockN / (kEpiWarps / 4);
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpilogueStagingBytes + kBarrierBytes + 1024;  // +1024: manual alignment
 };
 
 MSCCLPP_DEVICE_INLINE void tileCoord(const Shape& s, int tile, int numMBlk, int numNBlk, int& mBlk, int& nBlk) {
@@ -100,6 +109,17 @@ struct NoGate {
   }
 };
 
+// ---- epilogue staging: a warp's 32 x 64 bf16 block in shared memory, laid out like a SWIZZLE_128B TMA box
+// (row r at byte r * 128, its 16-byte chunk c at position c ^ (r & 7)); the buffer is 1024-byte aligned.
+MSCCLPP_DEVICE_INLINE uint32_t stagedOffset(int r, int c) { return static_cast<uint32_t>(r * 128 + ((c ^ (r & 7)) << 4)); }
+// Row-contiguous view for fused epilogues: in step i (0..7) lane l holds chunk (l & 7) of row 4 * i + (l >> 3), so a
+// warp-wide global access built on it touches four complete 128-byte lines.
+MSCCLPP_DEVICE_INLINE int stagedRow(int i, int lane) { return 4 * i + (lane >> 3); }
+MSCCLPP_DEVICE_INLINE int stagedCol(int lane) { return (lane & 7) * 8; }
+MSCCLPP_DEVICE_INLINE uint4 stagedRead(const uint8_t* stage, int i, int lane) {
+  return *reinterpret_cast<const uint4*>(stage + stagedOffset(stagedRow(i, lane), lane & 7));
+}
+
 struct SharedState {
   uint64_t* full;       // [stages] TMA -> MMA
   uint64_t* empty;      // [stages] MMA -> TMA
@@ -109,6 +129,54 @@ struct SharedState {
   volatile uint32_t* abortFlag;
   volatile uint32_t* epiArrivals;  // epilogue warps that finished storing, summed over the tiles so far
 };
+
+// Columns [8k, 8k+8) of a thread's 32 accumulator values as packed bf16.
+template <typename Epilogue>
+MSCCLPP_DEVICE_INLINE uint4 packChunk(const uint32_t (&v)[32], int k) {
+  uint32_t w[4];
+#pragma unroll
+  for (int j = 0; j < 4; j++) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(Epilogue::convert(__uint_as_float(v[8 * k + 2 * j])),
+                                             Epilogue::convert(__uint_as_float(v[8 * k + 2 * j + 1])));
+    w[j] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// One epilogue warp, one tile: `taddr` is the TMEM address of the warp's lane quarter at its first column,
+// (row0, col0) the global coordinates of that corner. Calls arriveEmpty() as soon as the warp's last accumulator
+// read has completed, i.e. before the last block is written out.
+template <int kColsPerWarp, typename Epilogue, typename ArriveEmpty>
+MSCCLPP_DEVICE_INLINE void stagedEpilogueTile(Epilogue& epi, uint32_t taddr, uint8_t* stage, int row0, int col0, int lane,
+                                              ArriveEmpty&& arriveEmpty, bool drop = false) {
+  static_assert(kColsPerWarp % 64 == 0, "an epilogue warp works in blocks of 64 columns");
+  constexpr int kBlocks = kColsPerWarp / 64;
+#pragma unroll
+  for (int b = 0; b < kBlocks; b++) {
+    uint32_t v0[32], v1[32];
+    ptx::tmem_ld_32x32b_x32(taddr + b * 64, v0);
+    ptx::tmem_ld_32x32b_x32(taddr + b * 64 + 32, v1);
+    ptx::tmem_ld_wait();
+    if (b == kBlocks - 1) {
+      ptx::tcgen05_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) arriveEmpty();
+    }
+    // the buffer is free once the bulk store of the previous block has read it (or block() has ended)
+    if constexpr (Epilogue::kBulkStore) {
+      if (lane == 0) ptx::bulk_wait_read<0>();
+    }
+    __syncwarp();
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      *reinterpret_cast<uint4*>(stage + stagedOffset(lane, c)) = packChunk<Epilogue>(v0, c);
+      *reinterpret_cast<uint4*>(stage + stagedOffset(lane, c + 4)) = packChunk<Epilogue>(v1, c);
+    }
+    if constexpr (Epilogue::kBulkStore) ptx::fence_proxy_async_smem();
+    __syncwarp();
+    if (!drop) epi.block(stage, row0, col0 + b * 64, lane, b);
+  }
+}
 
 // Body of a GEMM CTA. All 192 threads call it. `ctaIdx`/`numCtas` index the persistent tile loop.
 template <int kBlockN, typename AGate, typename Epilogue>
@@ -122,7 +190,8 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
   // ---- carve shared memory (tiles need 1024-byte alignment for the 128B swizzle)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kStages * Cfg::kStageBytes);
+  uint8_t* staging = smem + Cfg::kStages * Cfg::kStageBytes;  // 1024-byte aligned: every stage is a multiple of 1024 bytes
+  uint64_t* bars = reinterpret_cast<uint64_t*>(staging + kEpilogueStagingBytes);
   SharedState st;
   st.full = bars;
   st.empty = bars + Cfg::kStages;
@@ -144,7 +213,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
     }
     for (int s = 0; s < 2; s++) {
       ptx::mbar_init(&st.tmemFull[s], 1);
-      ptx::mbar_init(&st.tmemEmpty[s], kNumEpilogueWarps);  // one arrival per epilogue warp
+      ptx::mbar_init(&st.tmemEmpty[s], Cfg::kEpiWarps);  // one arrival per epilogue warp that takes part
     }
     *st.abortFlag = 0;
     *st.epiArrivals = 0;
@@ -183,9 +252,13 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
           }
           uint8_t* sa = tiles + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageABytes;
-          ptx::mbar_expect_tx(&st.full[stage], shape.aBoxRows * kBlockK * 2 + Cfg::kStageBBytes);
-          ptx::tma_load_2d(sa, tmapARows, kb * kBlockK, aRow, &st.full[stage]);
-          ptx::tma_load_2d(sb, tmapB, kb * kBlockK, nBlk * kBlockN, &st.full[stage]);
+          if (shape.probe & 1) {
+            ptx::mbar_arrive(&st.full[stage]);
+          } else {
+            ptx::mbar_expect_tx(&st.full[stage], shape.aBoxRows * kBlockK * 2 + Cfg::kStageBBytes);
+            ptx::tma_load_2d(sa, tmapARows, kb * kBlockK, aRow, &st.full[stage]);
+            ptx::tma_load_2d(sb, tmapB, kb * kBlockK, nBlk * kBlockN, &st.full[stage]);
+          }
           armed |= 1u << stage;
           armedParity = (armedParity & ~(1u << stage)) | (phase << stage);
           if (++stage == Cfg::kStages) {
@@ -231,10 +304,12 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
           const uint32_t sb = sa + Cfg::kStageABytes;
           const uint64_t descA = makeSmemDesc(sa);
           const uint64_t descB = makeSmemDesc(sb);
+          if (!(shape.probe & 2)) {
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; k++) {
-            // advancing K by 16 elements = 32 bytes inside the 128-byte swizzle row: +2 in the (>>4) address field
-            ptx::tcgen05_mma_f16(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < kBlockK / kUmmaK; k++) {
+              // advancing K by 16 elements = 32 bytes inside the 128-byte swizzle row: +2 in the (>>4) address field
+              ptx::tcgen05_mma_f16(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           ptx::tcgen05_commit(&st.empty[stage]);  // frees the smem stage once these MMAs retire
           if (++stage == Cfg::kStages) {
@@ -246,11 +321,11 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       }
       if (!ok) *st.abortFlag = 1;
     }
-  } else if (warp < 2 + kNumEpilogueWarps) {
-    // ===================================================== epilogue (8 warps: lane quarter x column half)
+  } else if (warp < 2 + Cfg::kEpiWarps) {
+    // ===================================================== epilogue (lane quarter x column part per warp)
     const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32*(warpid%4), +32)
-    const int half = (warp - 2) >> 2;
-    constexpr int kChunksPerWarp = kBlockN / 32 / (kNumEpilogueWarps / 4);
+    const int part = (warp - 2) >> 2;
+    uint8_t* stage = staging + (warp - 2) * kStagingBytesPerWarp;
     bool ok = true;
     int it = 0;
     for (int tile = ctaIdx; tile < numTiles && ok; tile += numCtas, it++) {
@@ -258,26 +333,17 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       tileCoord(shape, tile, numMBlk, numNBlk, mBlk, nBlk);
       const int acc = it & 1;
       const uint32_t accPhase = (it >> 1) & 1;
-      const int row = mBlk * kBlockM + quarter * 32 + lane;
+      const int row0 = mBlk * kBlockM + quarter * 32;
+      const int col0 = nBlk * kBlockN + part * Cfg::kColsPerWarp;
       // lets the epilogue put loads it will need (a residual, a bias) in flight while the MMAs of this tile still run
-      epi.tileBegin(row, nBlk * kBlockN + half * kChunksPerWarp * 32);
+      epi.tileBegin(row0, col0, lane);
       ok = mbarWait(&st.tmemFull[acc], accPhase, status, budgetNs, 400 + acc);
       ok = __all_sync(0xffffffffu, ok) && (*st.abortFlag == 0);
       if (!ok) break;
       ptx::tcgen05_fence_after_sync();
-      const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN;
-#pragma unroll
-      for (int i = 0; i < kChunksPerWarp; i++) {
-        const int c = half * kChunksPerWarp + i;
-        uint32_t v[32];
-        ptx::tmem_ld_32x32b_x32(taddr + c * 32, v);
-        ptx::tmem_ld_wait();
-        epi.store(row, nBlk * kBlockN + c * 32, v, i);  // i: index of the slice within this warp's part of the tile
-      }
-      // accumulator buffer can be overwritten by the MMA warp from here on
-      ptx::tcgen05_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&st.tmemEmpty[acc]);
+      const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN + part * Cfg::kColsPerWarp;
+      // the accumulator buffer can be overwritten by the MMA warp as soon as every warp has read its part
+      stagedEpilogueTile<Cfg::kColsPerWarp>(epi, taddr, stage, row0, col0, lane, [&] { ptx::mbar_arrive(&st.tmemEmpty[acc]); }, (shape.probe & 4) != 0);
       if constexpr (Epilogue::kNeedsTileBarrier) {
         // All epilogue warps have issued their stores -> let the fused kernel publish the tile. The
         // meeting point is a counter with a bounded wait (not bar.sync): if one warp gave up on the
@@ -286,7 +352,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
         if (lane == 0) {
           __threadfence_block();
           atomicAdd(const_cast<uint32_t*>(st.epiArrivals), 1u);
-          const uint32_t target = static_cast<uint32_t>(it + 1) * kNumEpilogueWarps;
+          const uint32_t target = static_cast<uint32_t>(it + 1) * Cfg::kEpiWarps;
           SpinGuard g(status, budgetNs);
           while (static_cast<int32_t>(*st.epiArrivals - target) < 0) {
             if (*st.abortFlag || !g.keepSpinning()) {
@@ -305,6 +371,10 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       }
     }
     if (!ok && lane == 0) *st.abortFlag = 1;
+    // bulk stores of this warp still read its staging buffer: the CTA must not end before they have
+    if constexpr (Epilogue::kBulkStore) {
+      if (lane == 0) ptx::bulk_wait<0>();
+    }
   }
 
   // ---- teardown: everybody meets, then the allocating warp frees TMEM
@@ -314,25 +384,19 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
   if (warp == 1) ptx::tmem_dealloc(tmemBase, Cfg::kTmemCols);
 }
 
-// Plain epilogue: convert to bf16 and store row-major D[M, ldd].
+// Plain epilogue: every staged 32 x 64 block leaves with one tiled bulk store (rows beyond M are clipped by the
+// tensor map, whose box is 64 columns x 32 rows with the 128-byte swizzle of the staging layout).
 struct StoreBf16 {
   static constexpr bool kNeedsTileBarrier = false;
-  __nv_bfloat16* D;
-  int ldd;
+  static constexpr bool kBulkStore = true;
+  const CUtensorMap* tmapD;
   int M;
-  MSCCLPP_DEVICE_INLINE void tileBegin(int, int) const {}
-  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32], int /*slice*/ = 0) const {
-    if (row >= M) return;
-    uint4* dst = reinterpret_cast<uint4*>(D + static_cast<size_t>(row) * ldd + col);
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      uint32_t w[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
-        w[j] = *reinterpret_cast<uint32_t*>(&h);
-      }
-      dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  MSCCLPP_DEVICE_INLINE static float convert(float x) { return x; }
+  MSCCLPP_DEVICE_INLINE void tileBegin(int, int, int) const {}
+  MSCCLPP_DEVICE_INLINE void block(const uint8_t* stage, int row0, int col0, int lane, int /*b*/) const {
+    if (lane == 0 && row0 < M) {
+      ptx::tma_store_2d(tmapD, stage, col0, row0);
+      ptx::bulk_commit();
     }
   }
   MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
