@@ -283,6 +283,12 @@ PYBIND11_MODULE(_native, m) {
            py::arg("bytes"), py::arg("alignment") = 256)
       .def("free", [](SymmetricHeap& h, uintptr_t p) { h.free(reinterpret_cast<void*>(p)); })
       .def("bytes_free", &SymmetricHeap::bytesFree)
+      .def("symmetric_on_all_ranks",
+           [](SymmetricHeap& h, uintptr_t p, size_t bytes) {
+             py::gil_scoped_release release;  // may exchange offsets over the bootstrap
+             return h.symmetricOnAllRanks(reinterpret_cast<void*>(p), bytes);
+           },
+           py::arg("ptr"), py::arg("bytes"))
       .def("contains", [](SymmetricHeap& h, uintptr_t p, size_t bytes) { return h.contains(reinterpret_cast<void*>(p), bytes); },
            py::arg("ptr"), py::arg("bytes") = 1)
       .def("emulated_ptr", [](SymmetricHeap& h, uintptr_t p, int r) {
@@ -336,6 +342,31 @@ PYBIND11_MODULE(_native, m) {
       py::arg("mode") = 0, py::arg("n_blocks") = 32, py::arg("n_threads") = 512, py::arg("stream") = 0,
       py::arg("nvls") = false, py::arg("root") = 0);
   m.def(
+      "pipeline_allreduce",
+      [](SymmetricHeap& heap, uintptr_t in, uintptr_t out, uint64_t bytes, DataType dtype, ReduceOp op, uintptr_t scratch, uint64_t sliceBytes,
+         int nBlocks, int nThreads, uintptr_t stream, bool nvls, uint64_t emuStride) {
+        if (nvls && !heap.nvls()) throw Error("NVLS requested but the heap has no multicast mapping", ErrorCode::InvalidUsage);
+        if (!heap.contains(reinterpret_cast<const void*>(scratch), pipelineScratchBytes(nBlocks, sliceBytes)))
+          throw Error("pipeline_allreduce: the scratch must be symmetric-heap memory of pipeline_scratch_bytes(n_blocks, slice_bytes)",
+                      ErrorCode::InvalidUsage);
+        PipeArgs a{};
+        a.comm = heap.deviceComm();
+        a.in = reinterpret_cast<const void*>(in);
+        a.out = reinterpret_cast<void*>(out);
+        a.bytes = bytes;
+        a.scratch = reinterpret_cast<void*>(scratch);
+        a.sliceBytes = sliceBytes;
+        a.emuRanks = heap.emulated() ? heap.world() : 1;
+        a.emuStride = heap.emulated() ? emuStride : 0;
+        a.nvls = nvls ? 1 : 0;
+        checkCuda(launchPipelineAllreduce(a, dtype, op, nBlocks, nThreads, reinterpret_cast<cudaStream_t>(stream)), "pipeline_allreduce");
+      },
+      py::arg("heap"), py::arg("input"), py::arg("output"), py::arg("bytes"), py::arg("dtype"), py::arg("op") = SUM, py::arg("scratch"),
+      py::arg("slice_bytes"), py::arg("n_blocks") = 64, py::arg("n_threads") = 512, py::arg("stream") = 0, py::arg("nvls") = false,
+      py::arg("emu_stride") = 0);
+  m.def("pipeline_scratch_bytes", [](int nBlocks, uint64_t sliceBytes) { return pipelineScratchBytes(nBlocks, sliceBytes); },
+        py::arg("n_blocks"), py::arg("slice_bytes"));
+  m.def(
       "two_shot_rmsnorm",
       [](SymmetricHeap& heap, uintptr_t in, uintptr_t out, int rows, int hidden, DataType dtype, float eps,
          uintptr_t residualIn, uintptr_t residualOut, uintptr_t gamma, bool broadcastResidual, int nBlocks, int nThreads,
@@ -355,24 +386,25 @@ PYBIND11_MODULE(_native, m) {
   m.def(
       "gemm_bf16",
       [](uintptr_t A, uintptr_t B, uintptr_t D, int M, int N, int K, int ldd, int blockN, int numCtas, uintptr_t status,
-         uintptr_t stream) {
+         uintptr_t stream, int probe, int band) {
         checkCuda(gemm::gemmBf16(reinterpret_cast<const void*>(A), reinterpret_cast<const void*>(B),
                                  reinterpret_cast<void*>(D), M, N, K, ldd, blockN, numCtas,
-                                 reinterpret_cast<DeviceStatus*>(status), reinterpret_cast<cudaStream_t>(stream)),
+                                 reinterpret_cast<DeviceStatus*>(status), reinterpret_cast<cudaStream_t>(stream), probe, band),
                   "gemm_bf16");
       },
       py::arg("a"), py::arg("b"), py::arg("d"), py::arg("m"), py::arg("n"), py::arg("k"), py::arg("ldd"),
-      py::arg("block_n") = 256, py::arg("num_ctas") = 0, py::arg("status") = 0, py::arg("stream") = 0);
+      py::arg("block_n") = 256, py::arg("num_ctas") = 0, py::arg("status") = 0, py::arg("stream") = 0, py::arg("probe") = 0,
+      py::arg("band") = 0);
 
   m.def(
       "gemm_bf16_two_sm",
-      [](uintptr_t A, uintptr_t B, uintptr_t D, int M, int N, int K, int ldd, int numCtas, uintptr_t status, uintptr_t stream) {
+      [](uintptr_t A, uintptr_t B, uintptr_t D, int M, int N, int K, int ldd, int numCtas, uintptr_t status, uintptr_t stream, int probe, int band) {
         checkCuda(gemm::gemmBf16TwoSm(reinterpret_cast<const void*>(A), reinterpret_cast<const void*>(B), reinterpret_cast<void*>(D), M, N,
-                                      K, ldd, numCtas, reinterpret_cast<DeviceStatus*>(status), reinterpret_cast<cudaStream_t>(stream)),
+                                      K, ldd, numCtas, reinterpret_cast<DeviceStatus*>(status), reinterpret_cast<cudaStream_t>(stream), probe, band),
                   "gemm_bf16_two_sm");
       },
       py::arg("a"), py::arg("b"), py::arg("d"), py::arg("m"), py::arg("n"), py::arg("k"), py::arg("ldd"), py::arg("num_ctas") = 0,
-      py::arg("status") = 0, py::arg("stream") = 0);
+      py::arg("status") = 0, py::arg("stream") = 0, py::arg("probe") = 0, py::arg("band") = 0);
 
   registerCoreBindings(m);
   registerAlgorithmBindings(m);

@@ -1,6 +1,7 @@
 #include <mscclpp/symmetric_heap.hpp>
 
 #include <cstring>
+#include <vector>
 #include <unistd.h>
 
 #include <mscclpp/env.hpp>
@@ -294,6 +295,11 @@ void SymmetricHeap::free(void* ptr) {
   if (it == usedBlocks_.end()) throw Error("SymmetricHeap::free of an unknown pointer", ErrorCode::InvalidUsage);
   size_t begin = off, size = it->second;
   usedBlocks_.erase(it);
+  // agreements about buffers inside the freed block are void: the range may be handed out differently next time
+  {
+    const uint64_t lo = peerBase_[rank_] + off, hi = lo + size;
+    for (auto c = symmetricCache_.lower_bound({lo, 0}); c != symmetricCache_.end() && c->first.first < hi;) c = symmetricCache_.erase(c);
+  }
   // coalesce with neighbours
   auto next = freeBlocks_.lower_bound(begin);
   if (next != freeBlocks_.end() && next->first == begin + size) {
@@ -321,6 +327,32 @@ size_t SymmetricHeap::bytesFree() const {
 bool SymmetricHeap::contains(const void* ptr, size_t bytes) const {
   const uint64_t p = reinterpret_cast<uint64_t>(ptr);
   return p >= peerBase_[rank_] && p + bytes <= peerBase_[rank_] + bytes_;
+}
+
+bool SymmetricHeap::symmetricOnAllRanks(const void* ptr, size_t bytes) {
+  const bool mine = contains(ptr, bytes);
+  if (emulated_ || world_ == 1 || !bootstrap_) return mine;
+  // A buffer outside the local heap settles the answer without talking to anybody: addresses of ordinary allocations
+  // repeat in a rank-dependent way (caching allocators), so "first time seen" would not line up across ranks for them.
+  // Heap buffers come from the symmetric allocator, whose call order is the same everywhere by contract. Should a peer
+  // pass an ordinary buffer where this rank passes a heap one, the exchange below runs into the bootstrap's timeout and
+  // the peer's kernel into its device-side one: a loud failure, never a kernel that addresses peers at a wrong offset.
+  if (!mine) return false;
+  const std::pair<uint64_t, size_t> key{reinterpret_cast<uint64_t>(ptr), bytes};
+  {
+    std::lock_guard<std::mutex> lock(allocMutex_);
+    auto it = symmetricCache_.find(key);
+    if (it != symmetricCache_.end()) return it->second;
+  }
+  // one word per rank: the buffer's heap offset
+  std::vector<uint64_t> all(world_, 0);
+  all[rank_] = reinterpret_cast<uint64_t>(ptr) - peerBase_[rank_];
+  bootstrap_->allGather(all.data(), sizeof(uint64_t));
+  bool same = mine;
+  for (int r = 0; r < world_ && same; r++) same = all[r] == all[rank_];
+  std::lock_guard<std::mutex> lock(allocMutex_);
+  symmetricCache_[key] = same;
+  return same;
 }
 
 void* SymmetricHeap::emulatedPtr(void* ptr, int r) const {

@@ -507,7 +507,8 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
   // ---- buffers: in the heap -> in place; elsewhere -> staged
   auto stage = [&](void* user, size_t bytes, void*& slot, size_t& slotBytes) -> void* {
     if (user == nullptr || bytes == 0) return user;
-    if (heap.contains(user, bytes)) return user;
+    // in place only when every rank's buffer sits in the heap at the same offset (the plan addresses peers by offset)
+    if (heap.symmetricOnAllRanks(user, bytes)) return user;
     if (heap.emulated()) throw Error("emulated ranks need buffers from the heap", ErrorCode::InvalidUsage);
     if (slotBytes < bytes) {
       if (slot) {

@@ -2,14 +2,17 @@
 // (src/ext/collectives/algorithm_collection_builder.cc:64-104), and the B200 selector.
 //
 // How the names map onto this library's kernels:
-//   default_allreduce_allpair_packet / _packet      one-shot LL16 over peer stores (any local buffers)
+//   default_allreduce_packet                        one-shot LL16 over peer stores (any local buffers)
+//   default_allreduce_allpair_packet                one-shot LL8 over peer stores (8-byte packets: lowest latency, tiny messages)
 //   default_allreduce_nvls_packet                   one-shot LL16, one multimem.st per packet
 //   default_allreduce_nvls_zero_copy                two-shot multimem.ld_reduce + multimem.st (heap buffers)
 //   default_allreduce_rsag_zero_copy                two-shot peer loads + stores (heap buffers)
-//   default_allreduce_nvls_warp_pipeline / _nvls_block_pipeline / _rsag / _rsag_pipeline / _fullmesh
-//                                                   the same two-shot kernels through heap staging buffers, for
-//                                                   user buffers outside the heap (copy in, reduce, copy out on the
-//                                                   caller's stream)
+//   for user buffers outside the heap, ONE kernel that copies in, reduces through heap scratch and copies out, slice by
+//   slice (collectives_pipeline.cu):
+//   default_allreduce_nvls_block_pipeline           switch reduction, 64 KB slices
+//   default_allreduce_nvls_warp_pipeline            switch reduction, 16 KB slices (finer grain for mid sizes)
+//   default_allreduce_rsag_pipeline                 peer loads/stores, 64 KB slices
+//   default_allreduce_rsag / _fullmesh              peer loads/stores, the whole message in one round (<= scratch / 4)
 //   default_allgather_fullmesh / _fullmesh2, default_reducescatter_zero_copy     two-shot kernel in AG / RS mode
 #include <mscclpp/ext/collectives/algorithm_collection_builder.hpp>
 
@@ -98,9 +101,11 @@ std::shared_ptr<Algorithm> makeTwoShot(const std::string& name, const std::strin
         // Peers read `in` (allreduce, reducescatter) and write `out` (allreduce, allgather): only those sides
         // must live in the heap. An allreduce whose size is not a multiple of 16 bytes is padded in staging.
         const bool padded = mode == kAllReduce && inBytes % 16 != 0;
-        // all-to-all reads `in` locally only, like all-gather
-        const bool needIn = mode != kAllGather && mode != kAllToAll && (padded || !heap->contains(in, inBytes));
-        const bool needOut = mode != kReduceScatter && (padded || !heap->contains(out, outBytes));
+        // The choice between the caller's buffers and staging is the same on every rank: it rests on sizes, on the mode
+        // and on symmetricOnAllRanks(), never on where THIS rank's buffer happens to be. (all-to-all reads `in` locally
+        // only, like all-gather.)
+        const bool needIn = mode != kAllGather && mode != kAllToAll && (padded || !heap->symmetricOnAllRanks(in, inBytes));
+        const bool needOut = mode != kReduceScatter && (padded || !heap->symmetricOnAllRanks(out, outBytes));
         if (needIn || needOut) {
           if (!staged) return CommResult::InvalidUsage;
           if (needIn) {
@@ -117,6 +122,61 @@ std::shared_ptr<Algorithm> makeTwoShot(const std::string& name, const std::strin
         return CommResult::Success;
       },
       0, UINT64_MAX, CollectiveBufferMode::Any);
+}
+
+// Pipeline scratch of one heap: carved out when the default algorithms are built (a collective moment, so the offset is the
+// same on every rank) and shared by the pipeline algorithms, which run one at a time on a heap anyway.
+struct PipeScratch {
+  std::shared_ptr<SymmetricHeap> heap;
+  void* base = nullptr;
+  size_t bytes = 0;
+  ~PipeScratch() {
+    try {
+      if (base) heap->free(base);
+    } catch (...) {
+    }
+  }
+};
+
+// Allreduce of buffers outside the heap in one kernel. sliceBytes == 0: one round covers the whole message.
+std::shared_ptr<Algorithm> makePipeline(const std::string& name, std::shared_ptr<SymmetricHeap> heap, bool nvls, size_t sliceBytes,
+                                        std::shared_ptr<PipeScratch> scratch) {
+  const int world = heap->world();
+  const size_t maxBytes = sliceBytes == 0 ? scratch->bytes / 4 : UINT64_MAX;
+  return std::make_shared<NativeAlgorithm>(
+      name, "allreduce", nullptr,
+      [heap, nvls, sliceBytes, scratch, world](const void* in, void* out, size_t inBytes, size_t, DataType dtype, ReduceOp op, cudaStream_t stream,
+                                                int nBlocks, int nThreads, bool, const std::unordered_map<std::string, uintptr_t>&) {
+        const size_t unit = 16 * static_cast<size_t>(world);
+        size_t slice = sliceBytes;
+        int maxBlocks = 128;
+        if (slice == 0) {
+          // one round: as many blocks as give each at least 16 KB, each block's slice a multiple of 16 * world bytes
+          int blocks = static_cast<int>(std::min<size_t>(maxBlocks, std::max<size_t>(1, inBytes / (16u << 10))));
+          if (nBlocks > 0) blocks = std::min(nBlocks, kBarrierSlots);
+          slice = ((inBytes + blocks - 1) / blocks + unit - 1) / unit * unit;
+          if (pipelineScratchBytes(blocks, slice) > scratch->bytes) return CommResult::InvalidUsage;
+          nBlocks = blocks;
+        } else {
+          slice = (slice + unit - 1) / unit * unit;
+          maxBlocks = static_cast<int>(std::min<size_t>(kBarrierSlots, scratch->bytes / (4 * slice)));
+          if (maxBlocks < 1) return CommResult::InvalidUsage;
+          const int want = static_cast<int>(std::min<size_t>(maxBlocks, (inBytes + slice - 1) / slice));
+          nBlocks = nBlocks > 0 ? std::min(nBlocks, maxBlocks) : std::min(want, 128);
+        }
+        if (nThreads <= 0) nThreads = 512;
+        PipeArgs a{};
+        a.comm = heap->deviceComm();
+        a.in = in;
+        a.out = out;
+        a.bytes = inBytes;
+        a.scratch = scratch->base;
+        a.sliceBytes = slice;
+        a.emuRanks = 1;
+        a.nvls = nvls ? 1 : 0;
+        return toResult(launchPipelineAllreduce(a, dtype, op, nBlocks, nThreads, stream));
+      },
+      0, maxBytes, CollectiveBufferMode::Any);
 }
 
 // Broadcast: the root's `in` goes to every rank's `out` (staged through the heap when `out` is an ordinary buffer).
@@ -189,18 +249,40 @@ AlgorithmCollection AlgorithmCollectionBuilder::buildDefaultAlgorithms(std::shar
   auto staging = std::make_shared<Staging>();
   staging->heap = heap;
   auto add = [&c](std::shared_ptr<Algorithm> a) { c.registerAlgorithm(a->collective(), a->name(), a); };
-  add(makeLL("default_allreduce_allpair_packet", heap, false));
   add(makeLL("default_allreduce_packet", heap, false));
   if (nvls) add(makeLL("default_allreduce_nvls_packet", heap, true));
   if (nvls) add(makeTwoShot("default_allreduce_nvls_zero_copy", "allreduce", heap, kAllReduce, true, false, staging));
   add(makeTwoShot("default_allreduce_rsag_zero_copy", "allreduce", heap, kAllReduce, false, false, staging));
-  if (nvls) {
-    add(makeTwoShot("default_allreduce_nvls_warp_pipeline", "allreduce", heap, kAllReduce, true, true, staging));
-    add(makeTwoShot("default_allreduce_nvls_block_pipeline", "allreduce", heap, kAllReduce, true, true, staging));
+  // Buffers outside the heap: one pipelined kernel through heap scratch. The scratch is carved out here, where every
+  // rank is (building the collection is collective), never on a code path that only some ranks may take.
+  auto pipeScratch = std::make_shared<PipeScratch>();
+  pipeScratch->heap = heap;
+  {
+    size_t want = 32u << 20;  // 128 blocks x 64 KB slices, double buffered, in + out
+    if (const char* e = std::getenv("MSCCLPP_PIPELINE_SCRATCH_MB")) want = static_cast<size_t>(std::max(1, std::atoi(e))) << 20;
+    if (heap->bytesFree() >= want + (64u << 20)) {
+      try {
+        pipeScratch->base = heap->alloc(want, 256);
+        pipeScratch->bytes = want;
+      } catch (const BaseError&) {
+        pipeScratch->base = nullptr;
+      }
+    }
   }
-  add(makeTwoShot("default_allreduce_rsag", "allreduce", heap, kAllReduce, false, true, staging));
-  add(makeTwoShot("default_allreduce_rsag_pipeline", "allreduce", heap, kAllReduce, false, true, staging));
-  add(makeTwoShot("default_allreduce_fullmesh", "allreduce", heap, kAllReduce, false, true, staging));
+  if (pipeScratch->base != nullptr) {
+    if (nvls) {
+      add(makePipeline("default_allreduce_nvls_warp_pipeline", heap, true, 16u << 10, pipeScratch));
+      add(makePipeline("default_allreduce_nvls_block_pipeline", heap, true, 64u << 10, pipeScratch));
+    }
+    add(makePipeline("default_allreduce_rsag", heap, false, 0, pipeScratch));
+    add(makePipeline("default_allreduce_rsag_pipeline", heap, false, 64u << 10, pipeScratch));
+    add(makePipeline("default_allreduce_fullmesh", heap, false, 0, pipeScratch));
+  } else {
+    // a heap too small for the scratch: copy in, two-shot kernel, copy out (three operations on the caller's stream)
+    LOG_WARN(LogSubsys::ALGO, "symmetric heap too small for the pipeline scratch: buffers outside the heap take staged copies");
+    if (nvls) add(makeTwoShot("default_allreduce_nvls_block_pipeline", "allreduce", heap, kAllReduce, true, true, staging));
+    add(makeTwoShot("default_allreduce_rsag_pipeline", "allreduce", heap, kAllReduce, false, true, staging));
+  }
   add(makeTwoShot("default_allgather_fullmesh", "allgather", heap, kAllGather, false, true, staging));
   add(makeTwoShot("default_allgather_fullmesh2", "allgather", heap, kAllGather, nvls, true, staging));
   add(makeTwoShot("default_reducescatter_zero_copy", "reducescatter", heap, kReduceScatter, nvls, true, staging));
@@ -245,20 +327,32 @@ std::shared_ptr<Algorithm> selectDefaultAlgorithm(
     if (request.messageSize >= range.first && request.messageSize <= range.second && modeOk) return kv.second;
   }
   const size_t n = request.messageSize;
+  const int world = request.worldSize;
   if (request.collective == "allreduce") {
+    // Thresholds measured on 2, 4 and 8 B200s (eager launches, bf16). Every rank sends its whole buffer to every peer in
+    // the one-shot packet algorithms, so their range shrinks as the world grows.
     auto pkt = get("default_allreduce_packet");
     auto nvlsPkt = get("default_allreduce_nvls_packet");
     const size_t llCap = pkt ? pkt->messageRange().second : 0;
-    if (n <= (64u << 10) && nvlsPkt) return nvlsPkt;                 // one multimem.st per packet: flat ~latency floor
-    // user buffers outside the heap cost two extra copies on the two-shot path, so packets stay ahead for longer
-    const size_t pktMax = request.symmetricMemory ? (512u << 10) : (1u << 20);
+    if (n <= (64u << 10) && nvlsPkt) return nvlsPkt;  // one multimem.st per packet: flat latency floor
+    size_t pktMax = world <= 2 ? (1u << 20) : (world <= 4 ? (256u << 10) : (128u << 10));
+    // buffers outside the heap pay the scratch detour on the large-message path, so packets stay ahead a little longer
+    if (!request.symmetricMemory) pktMax *= 2;
     if (n <= pktMax && n <= llCap && pkt) return pkt;
     if (request.symmetricMemory && n % 16 == 0) {
-      if (auto a = get("default_allreduce_nvls_zero_copy")) return a;
+      // with two ranks the switch has nothing to combine: plain peer loads win from 16 MB on
+      const bool preferSwitch = world > 2 || n < (16u << 20);
+      if (preferSwitch) {
+        if (auto a = get("default_allreduce_nvls_zero_copy")) return a;
+      }
       return get("default_allreduce_rsag_zero_copy");
     }
-    if (auto a = get(n >= (16u << 20) ? "default_allreduce_nvls_block_pipeline" : "default_allreduce_nvls_warp_pipeline")) return a;
-    return get(n >= (8u << 20) ? "default_allreduce_rsag_pipeline" : "default_allreduce_rsag");
+    if (world > 2 || n < (16u << 20)) {
+      if (auto a = get(n >= (4u << 20) ? "default_allreduce_nvls_block_pipeline" : "default_allreduce_nvls_warp_pipeline")) return a;
+    }
+    auto rsag = get("default_allreduce_rsag");
+    if (rsag && n < (4u << 20) && n <= rsag->messageRange().second) return rsag;
+    return get("default_allreduce_rsag_pipeline");
   }
   if (request.collective == "allgather") {
     if ((n * request.worldSize) % (16 * static_cast<size_t>(request.worldSize)) != 0) return nullptr;

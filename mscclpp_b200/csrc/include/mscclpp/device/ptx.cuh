@@ -388,6 +388,15 @@ MSCCLPP_DEVICE_INLINE void tcgen05_mma_f16(uint32_t tmem_d, uint64_t desc_a, uin
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same, always accumulating (the predicate folds to "true": no register, no compare on the issue path).
+MSCCLPP_DEVICE_INLINE void tcgen05_mma_f16_acc(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc)
+      : "memory");
+}
 // Arrive (count 1) on a CTA-local mbarrier once all previously issued MMAs of this thread retire.
 MSCCLPP_DEVICE_INLINE void tcgen05_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -455,6 +464,14 @@ MSCCLPP_DEVICE_INLINE void tcgen05_mma_f16_pair(uint32_t tmem_d, uint64_t desc_a
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+MSCCLPP_DEVICE_INLINE void tcgen05_mma_f16_pair_acc(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc)
       : "memory");
 }
 // Arrive on the mbarrier at this offset in every CTA of `ctaMask` once the MMAs issued so far have retired.

@@ -127,6 +127,23 @@ MSCCLPP_DEVICE_INLINE bool waitGreaterEqualBackoff(const uint32_t* p, uint32_t e
   return true;
 }
 
+// Bounded mbarrier wait for the hot loops of a pipeline: the common case (the phase has completed, or completes within
+// the hardware's own try_wait window) costs one instruction and touches nothing else. `abortFlag` (shared memory, may
+// be null) is looked at only while actually waiting. false = gave up or aborted.
+MSCCLPP_DEVICE_INLINE bool mbarWaitFast(uint64_t* bar, uint32_t parity, DeviceStatus* st, uint64_t budgetNs, uint32_t where,
+                                        const volatile uint32_t* abortFlag) {
+  if (ptx::mbar_try_wait(bar, parity)) return true;
+  SpinGuard g(st, budgetNs);
+  while (!ptx::mbar_try_wait(bar, parity)) {
+    if (abortFlag != nullptr && *abortFlag != 0) return false;
+    if (!g.keepSpinning()) {
+      g.report(kDevTimeoutMbarrier, 0, where, 0, parity, 0);
+      return false;
+    }
+  }
+  return true;
+}
+
 // Bounded mbarrier wait (shared memory). false = gave up.
 MSCCLPP_DEVICE_INLINE bool mbarWait(uint64_t* bar, uint32_t parity, DeviceStatus* st, uint64_t budgetNs, uint32_t where) {
   SpinGuard g(st, budgetNs);

@@ -18,6 +18,7 @@
 #include <map>
 #include <memory>
 #include <mutex>
+#include <utility>
 
 #include "core.hpp"
 #include "device/symm.cuh"
@@ -58,6 +59,14 @@ class SymmetricHeap {
   void free(void* ptr);
   size_t bytesFree() const;
   bool contains(const void* ptr, size_t bytes = 1) const;
+  // True when, on every rank, the buffer lies inside the heap at the same offset - the condition under which kernels may
+  // address the peers' copies by offset. contains() is a rank-local fact; code that chooses between a zero-copy kernel
+  // and a staged one must choose from this answer, or the ranks can end up in different kernels. For a buffer inside
+  // the local heap the first call per (ptr, bytes) is COLLECTIVE (offsets are compared over the bootstrap; ranks must
+  // present their heap buffers in the same order, as with any registration) and later calls are cache lookups; a
+  // buffer outside the local heap answers false at once. Entries are dropped when the heap block that holds them is
+  // freed. Emulated heaps answer from contains().
+  bool symmetricOnAllRanks(const void* ptr, size_t bytes);
   // Emulated heaps: address of `ptr` (a rank-0 heap address) in emulated rank r's heap.
   void* emulatedPtr(void* ptr, int r) const;
 
@@ -101,6 +110,7 @@ class SymmetricHeap {
   size_t arenaBegin_ = 0;
   std::map<size_t, size_t> freeBlocks_;   // offset -> size
   std::map<size_t, size_t> usedBlocks_;   // offset -> size
+  std::map<std::pair<uint64_t, size_t>, bool> symmetricCache_;  // (address, bytes) -> agreed answer
 };
 
 }  // namespace mscclpp

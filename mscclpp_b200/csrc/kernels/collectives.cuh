@@ -43,4 +43,21 @@ cudaError_t launchAllreduceLL(const CollArgs& args, DataType dtype, ReduceOp op,
 cudaError_t launchTwoShot(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads,
                           cudaStream_t stream);
 
+// Allreduce of buffers outside the symmetric heap through heap scratch, pipelined inside one kernel (see
+// collectives_pipeline.cu). `scratch`: pipelineScratchBytes(nBlocks, sliceBytes) bytes of symmetric-heap memory at the
+// same offset on every rank. sliceBytes: a multiple of 16 * world; one round moves nBlocks * sliceBytes of the message.
+struct PipeArgs {
+  DeviceComm comm;
+  const void* in;      // local buffer, anywhere in device memory, 16-byte aligned; emulated rank e uses in + e * emuStride
+  void* out;
+  uint64_t bytes;      // any size (a tail shorter than 16 bytes is zero-padded inside the scratch)
+  void* scratch;
+  uint64_t sliceBytes;
+  uint64_t emuStride;
+  int emuRanks;
+  int nvls;
+};
+size_t pipelineScratchBytes(int nBlocks, uint64_t sliceBytes);
+cudaError_t launchPipelineAllreduce(const PipeArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads, cudaStream_t stream);
+
 }  // namespace mscclpp

@@ -65,6 +65,15 @@ __global__ void __launch_bounds__(kNumThreads, 1)
   gemmCtaPair(&tmapA, &tmapB, shape, blockIdx.x / 2, gridDim.x / 2, gate, epi, status, budgetNs, smemRaw);
 }
 
+// Tile order of a plain GEMM: bands of `band` row blocks (0 = the default for the tile shape, < 0 = plain column-major walk).
+void setBandOrder(Shape& shape, int numMBlk, int band, int dflt) {
+  if (band == 0) band = dflt;
+  if (band > 0 && numMBlk > band) {
+    shape.mOrder = 3;
+    shape.mOrderParam = band;
+  }
+}
+
 }  // namespace
 
 cudaError_t ensureDynamicSmem(const void* kernel, int bytes) {
@@ -101,10 +110,11 @@ cudaError_t launchClusterPair(const void* kernel, dim3 grid, dim3 block, size_t 
 }
 
 cudaError_t gemmBf16TwoSm(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int numCtas, DeviceStatus* status,
-                          cudaStream_t stream, int probe) {
+                          cudaStream_t stream, int probe, int band) {
   if (M <= 0 || N <= 0 || K <= 0 || K % kBlockK != 0 || N % Config2::kBlockN != 0 || ldd % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(D) & 15) != 0) return cudaErrorInvalidValue;
   Shape shape{M, N, K, kBlockM, 0, 0, 0, probe};
+  setBandOrder(shape, (M + Config2::kPairM - 1) / Config2::kPairM, band, 8);
   CUtensorMap ta, tb, td;
   cudaError_t e = makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, kBlockM);
   if (e != cudaSuccess) return e;
@@ -153,10 +163,11 @@ cudaError_t makeTensorMapBf16(CUtensorMap* map, const void* ptr, uint64_t rows, 
 }
 
 cudaError_t gemmBf16(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int blockN, int numCtas,
-                     DeviceStatus* status, cudaStream_t stream, int probe) {
+                     DeviceStatus* status, cudaStream_t stream, int probe, int band) {
   if (M <= 0 || N <= 0 || K <= 0 || K % kBlockK != 0 || N % blockN != 0 || ldd % 8 != 0) return cudaErrorInvalidValue;
   if ((reinterpret_cast<uintptr_t>(D) & 15) != 0) return cudaErrorInvalidValue;
   Shape shape{M, N, K, M < kBlockM ? M : kBlockM, 0, 0, 0, probe};
+  setBandOrder(shape, (M + kBlockM - 1) / kBlockM, band, 16);
   CUtensorMap ta, tb, td;
   cudaError_t e = makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, shape.aBoxRows);
   if (e != cudaSuccess) return e;

@@ -17,10 +17,11 @@ struct Shape {
                       // that row blocks complete in order (what a fused consumer of whole rows wants)
   int mOrder;       // order in which row blocks are visited: 0 natural; 1 interleaved over mOrderParam equal groups
                     // (0, per, 2*per, ..., 1, per+1, ...: every group completes a block per round - reduce-scatter
-                    // owners all have work at once); 2 rotated by mOrderParam blocks (all-gather: own rows first)
+                    // owners all have work at once); 2 rotated by mOrderParam blocks (all-gather: own rows first);
+                    // 3 bands of mOrderParam row blocks walked row-block-first (L2-friendly order of a plain GEMM)
   int mOrderParam;
   int probe;  // diagnostics, 0 in production: bit 0 = the producer issues no loads (stages are handed over empty), bit 1 = no
-              // MMAs are issued (barriers only), bit 2 = the epilogue drops its blocks instead of storing them. Timing the
+              // MMAs are issued (barriers only), bit 2 = the epilogue drops its blocks instead of storing them, bit 3 = it does not even read the accumulator. Timing the
               // kernel with each bit shows which of the three pipelines bounds a shape; results are then meaningless.
 };
 
@@ -32,13 +33,14 @@ cudaError_t makeTensorMapBf16(CUtensorMap* map, const void* ptr, uint64_t rows, 
 
 // D[M, ldd] (bf16) = A[M, K] * B[N, K]^T, fp32 accumulation on the 5th-generation tensor cores.
 // blockN in {64, 128, 256}; N % blockN == 0; K % 64 == 0; numCtas <= 0 picks one CTA per SM.
+// band: row blocks per band of the tile order (0 = default, < 0 = none); probe: see Shape::probe.
 cudaError_t gemmBf16(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int blockN, int numCtas,
-                     DeviceStatus* status, cudaStream_t stream, int probe = 0);
+                     DeviceStatus* status, cudaStream_t stream, int probe = 0, int band = 0);
 
 // Same product on 256 x 256 tiles shared by pairs of SMs (tcgen05 cta_group::2, clusters of two CTAs).
 // N % 256 == 0; K % 64 == 0; numCtas <= 0 picks one CTA per SM (rounded down to an even number).
 cudaError_t gemmBf16TwoSm(const void* A, const void* B, void* D, int M, int N, int K, int ldd, int numCtas, DeviceStatus* status,
-                          cudaStream_t stream, int probe = 0);
+                          cudaStream_t stream, int probe = 0, int band = 0);
 
 // Raises the kernel's dynamic shared-memory limit once per (kernel, device); call before every launch that needs > 48 KB.
 cudaError_t ensureDynamicSmem(const void* kernel, int bytes);

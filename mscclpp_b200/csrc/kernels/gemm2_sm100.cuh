@@ -106,11 +106,8 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
         int aRow;
         const CUtensorMap* tmapARows = gate.tmapA(mBlk, tmapA, aRow);
         for (int kb = 0; kb < numKBlk && ok; kb++) {
-          ok = mbarWait(&st.empty[stage], phase ^ 1u, status, budgetNs, 100 + stage);
-          if (!ok || *st.abortFlag) {
-            ok = false;
-            break;
-          }
+          ok = mbarWaitFast(&st.empty[stage], phase ^ 1u, status, budgetNs, 100 + stage, st.abortFlag);
+          if (!ok) break;
           uint8_t* sa = tiles + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageABytes;
           const uint32_t leaderFull = ptx::mapa_shared(ptx::smem_u32(&st.full[stage]), 0);
@@ -137,6 +134,12 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
     // ===================================================== MMA issuer (one thread of the leader CTA)
     if (lane == 0 && leader) {
       constexpr uint32_t idesc = makeInstrDescPair();
+      // one thread feeds the tensor cores of both SMs: descriptors are stepped by adds, waits cost one instruction when
+      // the data is already there
+      const uint64_t descA0 = makeSmemDesc(ptx::smem_u32(tiles));
+      const uint64_t descB0 = makeSmemDesc(ptx::smem_u32(tiles) + Cfg::kStageABytes);
+      constexpr uint64_t kStageStep = Cfg::kStageBytes >> 4;
+      const bool issue = (shape.probe & 2) == 0;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -144,29 +147,20 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
       for (int tile = pairIdx; tile < numTiles && ok; tile += numPairs, it++) {
         const int acc = it & 1;
         const uint32_t accPhase = (it >> 1) & 1;
-        ok = mbarWait(&st.tmemEmpty[acc], accPhase ^ 1u, status, budgetNs, 200 + acc);
-        if (!ok || *st.abortFlag) {
-          ok = false;
-          break;
-        }
+        ok = mbarWaitFast(&st.tmemEmpty[acc], accPhase ^ 1u, status, budgetNs, 200 + acc, st.abortFlag);
+        if (!ok) break;
         ptx::tcgen05_fence_after_sync();
         const uint32_t tmemD = tmemBase + acc * Cfg::kBlockN;
         for (int kb = 0; kb < numKBlk; kb++) {
-          ok = mbarWait(&st.full[stage], phase, status, budgetNs, 300 + stage);
-          if (!ok || *st.abortFlag) {
-            ok = false;
-            break;
-          }
+          ok = mbarWaitFast(&st.full[stage], phase, status, budgetNs, 300 + stage, st.abortFlag);
+          if (!ok) break;
           ptx::tcgen05_fence_after_sync();
-          const uint32_t sa = ptx::smem_u32(tiles + stage * Cfg::kStageBytes);
-          const uint32_t sb = sa + Cfg::kStageABytes;
-          const uint64_t descA = makeSmemDesc(sa);
-          const uint64_t descB = makeSmemDesc(sb);
-          if (!(shape.probe & 2)) {
+          const uint64_t descA = descA0 + stage * kStageStep;
+          const uint64_t descB = descB0 + stage * kStageStep;
+          if (issue) {
+            ptx::tcgen05_mma_f16_pair(tmemD, descA, descB, idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; k++) {
-              ptx::tcgen05_mma_f16_pair(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-            }
+            for (int k = 1; k < kBlockK / kUmmaK; k++) ptx::tcgen05_mma_f16_pair_acc(tmemD, descA + 2 * k, descB + 2 * k, idesc);
           }
           ptx::tcgen05_commit_pair(&st.empty[stage], 3);  // both CTAs may refill this stage once the MMAs retire
           if (++stage == Cfg::kStages) {
@@ -201,7 +195,7 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
       ptx::tcgen05_fence_after_sync();
       const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * Cfg::kBlockN + part * Cfg::kColsPerWarp;
       const uint32_t leaderEmpty = ptx::mapa_shared(ptx::smem_u32(&st.tmemEmpty[acc]), 0);
-      stagedEpilogueTile<Cfg::kColsPerWarp>(epi, taddr, stage, row0, col0, lane, [&] { ptx::mbar_arrive_cluster(leaderEmpty); }, (shape.probe & 4) != 0);
+      stagedEpilogueTile<Cfg::kColsPerWarp>(epi, taddr, stage, row0, col0, lane, [&] { ptx::mbar_arrive_cluster(leaderEmpty); }, shape.probe);
       if constexpr (Epilogue::kNeedsTileBarrier) {
         __syncwarp();
         if (lane == 0) {
@@ -224,7 +218,10 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
         }
         if (warp == 2) epi.tileDone(mBlk, nBlk, lane);
       }
+      // per-warp hook: this warp's part of the tile is stored (fused epilogues count it and may take on follow-up work)
+      epi.warpTileDone(mBlk, lane);
     }
+    if (ok) epi.warpDrain(lane);  // follow-up work that is left once the warp has no tile of its own any more
     if (!ok && lane == 0) *st.abortFlag = 1;
     if constexpr (Epilogue::kBulkStore) {
       if (lane == 0) ptx::bulk_wait<0>();

@@ -74,6 +74,17 @@ MSCCLPP_DEVICE_INLINE void tileCoord(const Shape& s, int tile, int numMBlk, int 
   } else if (s.mOrder == 2) {
     mBlk += s.mOrderParam;
     if (mBlk >= numMBlk) mBlk -= numMBlk;
+  } else if (s.mOrder == 3) {
+    // bands of mOrderParam row blocks, walked row-block-first inside a band: the tiles that run at the same time cover
+    // a near-square region, so each wave re-reads a band of A and a few column panels of B from L2 instead of all of A
+    const int g = s.mOrderParam;
+    const int perBand = g * numNBlk;
+    const int band = tile / perBand;
+    const int first = band * g;
+    const int rows = numMBlk - first < g ? numMBlk - first : g;  // the last band may be shorter
+    const int t = tile - band * perBand;
+    mBlk = first + t % rows;
+    nBlk = t / rows;
   }
 }
 
@@ -148,9 +159,16 @@ MSCCLPP_DEVICE_INLINE uint4 packChunk(const uint32_t (&v)[32], int k) {
 // read has completed, i.e. before the last block is written out.
 template <int kColsPerWarp, typename Epilogue, typename ArriveEmpty>
 MSCCLPP_DEVICE_INLINE void stagedEpilogueTile(Epilogue& epi, uint32_t taddr, uint8_t* stage, int row0, int col0, int lane,
-                                              ArriveEmpty&& arriveEmpty, bool drop = false) {
+                                              ArriveEmpty&& arriveEmpty, int probe = 0) {
   static_assert(kColsPerWarp % 64 == 0, "an epilogue warp works in blocks of 64 columns");
   constexpr int kBlocks = kColsPerWarp / 64;
+  const bool drop = (probe & 4) != 0;
+  if (probe & 8) {  // diagnostics: hand the accumulator back unread
+    ptx::tcgen05_fence_before_sync();
+    __syncwarp();
+    if (lane == 0) arriveEmpty();
+    return;
+  }
 #pragma unroll
   for (int b = 0; b < kBlocks; b++) {
     uint32_t v0[32], v1[32];
@@ -245,11 +263,8 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
         int aRow;
         const CUtensorMap* tmapARows = gate.tmapA(mBlk, tmapA, aRow);
         for (int kb = 0; kb < numKBlk && ok; kb++) {
-          ok = mbarWait(&st.empty[stage], phase ^ 1u, status, budgetNs, 100 + stage);
-          if (!ok || *st.abortFlag) {
-            ok = false;
-            break;
-          }
+          ok = mbarWaitFast(&st.empty[stage], phase ^ 1u, status, budgetNs, 100 + stage, st.abortFlag);
+          if (!ok) break;
           uint8_t* sa = tiles + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageABytes;
           if (shape.probe & 1) {
@@ -279,6 +294,12 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
     // ===================================================== MMA issuer (one thread)
     if (lane == 0) {
       constexpr uint32_t idesc = makeInstrDesc<kBlockN>();
+      // The issue loop is ONE thread feeding the tensor core: every instruction in it is on the critical path of the
+      // whole SM. Descriptors are formed once and stepped by adds; the common case of each wait is one instruction.
+      const uint64_t descA0 = makeSmemDesc(ptx::smem_u32(tiles));
+      const uint64_t descB0 = makeSmemDesc(ptx::smem_u32(tiles) + Cfg::kStageABytes);
+      constexpr uint64_t kStageStep = Cfg::kStageBytes >> 4;  // a stage, in the descriptor's 16-byte address units
+      const bool issue = (shape.probe & 2) == 0;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -286,30 +307,21 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       for (int tile = ctaIdx; tile < numTiles && ok; tile += numCtas, it++) {
         const int acc = it & 1;
         const uint32_t accPhase = (it >> 1) & 1;
-        ok = mbarWait(&st.tmemEmpty[acc], accPhase ^ 1u, status, budgetNs, 200 + acc);
-        if (!ok || *st.abortFlag) {
-          ok = false;
-          break;
-        }
+        ok = mbarWaitFast(&st.tmemEmpty[acc], accPhase ^ 1u, status, budgetNs, 200 + acc, st.abortFlag);
+        if (!ok) break;
         ptx::tcgen05_fence_after_sync();
         const uint32_t tmemD = tmemBase + acc * kBlockN;
         for (int kb = 0; kb < numKBlk; kb++) {
-          ok = mbarWait(&st.full[stage], phase, status, budgetNs, 300 + stage);
-          if (!ok || *st.abortFlag) {
-            ok = false;
-            break;
-          }
+          ok = mbarWaitFast(&st.full[stage], phase, status, budgetNs, 300 + stage, st.abortFlag);
+          if (!ok) break;
           ptx::tcgen05_fence_after_sync();
-          const uint32_t sa = ptx::smem_u32(tiles + stage * Cfg::kStageBytes);
-          const uint32_t sb = sa + Cfg::kStageABytes;
-          const uint64_t descA = makeSmemDesc(sa);
-          const uint64_t descB = makeSmemDesc(sb);
-          if (!(shape.probe & 2)) {
+          const uint64_t descA = descA0 + stage * kStageStep;
+          const uint64_t descB = descB0 + stage * kStageStep;
+          if (issue) {
+            // advancing K by 16 elements = 32 bytes inside the 128-byte swizzle row: +2 in the (>>4) address field
+            ptx::tcgen05_mma_f16(tmemD, descA, descB, idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; k++) {
-              // advancing K by 16 elements = 32 bytes inside the 128-byte swizzle row: +2 in the (>>4) address field
-              ptx::tcgen05_mma_f16(tmemD, descA + 2 * k, descB + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-            }
+            for (int k = 1; k < kBlockK / kUmmaK; k++) ptx::tcgen05_mma_f16_acc(tmemD, descA + 2 * k, descB + 2 * k, idesc);
           }
           ptx::tcgen05_commit(&st.empty[stage]);  // frees the smem stage once these MMAs retire
           if (++stage == Cfg::kStages) {
@@ -343,7 +355,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       ptx::tcgen05_fence_after_sync();
       const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN + part * Cfg::kColsPerWarp;
       // the accumulator buffer can be overwritten by the MMA warp as soon as every warp has read its part
-      stagedEpilogueTile<Cfg::kColsPerWarp>(epi, taddr, stage, row0, col0, lane, [&] { ptx::mbar_arrive(&st.tmemEmpty[acc]); }, (shape.probe & 4) != 0);
+      stagedEpilogueTile<Cfg::kColsPerWarp>(epi, taddr, stage, row0, col0, lane, [&] { ptx::mbar_arrive(&st.tmemEmpty[acc]); }, shape.probe);
       if constexpr (Epilogue::kNeedsTileBarrier) {
         // All epilogue warps have issued their stores -> let the fused kernel publish the tile. The
         // meeting point is a counter with a bounded wait (not bar.sync): if one warp gave up on the
@@ -369,7 +381,10 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
         }
         if (warp == 2) epi.tileDone(mBlk, nBlk, lane);
       }
+      // per-warp hook: this warp's part of the tile is stored (fused epilogues count it and may take on follow-up work)
+      epi.warpTileDone(mBlk, lane);
     }
+    if (ok) epi.warpDrain(lane);  // follow-up work that is left once the warp has no tile of its own any more
     if (!ok && lane == 0) *st.abortFlag = 1;
     // bulk stores of this warp still read its staging buffer: the CTA must not end before they have
     if constexpr (Epilogue::kBulkStore) {
@@ -400,6 +415,8 @@ struct StoreBf16 {
     }
   }
   MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
+  MSCCLPP_DEVICE_INLINE void warpTileDone(int, int) const {}
+  MSCCLPP_DEVICE_INLINE void warpDrain(int) const {}
 };
 
 }  // namespace gemm

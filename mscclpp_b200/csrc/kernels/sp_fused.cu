@@ -38,6 +38,7 @@ struct AgTmaps {
   CUtensorMap aLocal[8];
   CUtensorMap aFull[8];
   CUtensorMap b[8];
+  CUtensorMap d[8];  // output, 64-column x 32-row boxes (epilogue bulk stores)
 };
 
 // Gate of the GEMM's TMA producer: own row blocks come from aLocal at once, the others from aFull when landed.
@@ -66,13 +67,14 @@ struct GatherGate {
   }
 };
 
+// Activation in fp32 on the accumulator, then one tiled bulk store per staged 32 x 64 block.
 template <int kAct>
 struct StoreAct {
   static constexpr bool kNeedsTileBarrier = false;
-  bf16* D;
-  int ldd;
+  static constexpr bool kBulkStore = true;
+  const CUtensorMap* tmapD;
   int M;
-  MSCCLPP_DEVICE_INLINE static float act(float x) {
+  MSCCLPP_DEVICE_INLINE static float convert(float x) {
     if constexpr (kAct == 1) {
       const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
       return 0.5f * x * (1.f + tanhf(u));
@@ -82,22 +84,16 @@ struct StoreAct {
       return x;
     }
   }
-  MSCCLPP_DEVICE_INLINE void tileBegin(int, int) const {}
-  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32], int /*slice*/ = 0) const {
-    if (row >= M) return;
-    uint4* dst = reinterpret_cast<uint4*>(D + static_cast<size_t>(row) * ldd + col);
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-      uint32_t w[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(act(__uint_as_float(v[8 * i + 2 * j])), act(__uint_as_float(v[8 * i + 2 * j + 1])));
-        w[j] = *reinterpret_cast<uint32_t*>(&h);
-      }
-      dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
+  MSCCLPP_DEVICE_INLINE void tileBegin(int, int, int) const {}
+  MSCCLPP_DEVICE_INLINE void block(const uint8_t* stage, int row0, int col0, int lane, int /*b*/) const {
+    if (lane == 0 && row0 < M) {
+      ptx::tma_store_2d(tmapD, stage, col0, row0);
+      ptx::bulk_commit();
     }
   }
   MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
+  MSCCLPP_DEVICE_INLINE void warpTileDone(int, int) const {}
+  MSCCLPP_DEVICE_INLINE void warpDrain(int) const {}
 };
 
 constexpr uint32_t kPieceBytes = 32768;
@@ -196,8 +192,7 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
   if (static_cast<int>(blockIdx.x) < a.numGemmCtas) {
     const int per = a.shape.M / gemm::kBlockM / c.world;
     GatherGate gate{&c, &maps.aLocal[blockIdx.y], rank, rank * per, per, epoch};
-    const uint64_t dOff = reinterpret_cast<uint64_t>(a.D) - c.peerBase[c.rank];
-    StoreAct<kAct> epi{reinterpret_cast<bf16*>(c.peerBase[rank] + dOff), a.shape.N, a.shape.M};
+    StoreAct<kAct> epi{&maps.d[blockIdx.y], a.shape.M};
     gemm::Shape shape = a.shape;
     shape.mOrder = 2;
     if constexpr (kBlockN == 0) {
@@ -230,12 +225,8 @@ cudaError_t launchTyped(const AgTmaps& maps, const AgGemmArgs& args, int grid, c
   using Cfg = SmemOf<kBlockN>;
   static_assert(Cfg::kSmemBytes >= kRingStages * static_cast<int>(kPieceBytes) + 128, "ring must fit");
   auto kernel = agGemmKernel<kBlockN, kAct>;
-  static bool attrSet = false;
-  if (!attrSet) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attrSet = true;
-  }
+  cudaError_t e = gemm::ensureDynamicSmem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
   dim3 g(grid, args.emuRanks > 1 ? args.emuRanks : 1, 1);
   dim3 b(gemm::kNumThreads, 1, 1);
   // GEMM CTAs wait for copier CTAs of the same launch: co-residency is required, so the launch is cooperative
@@ -285,6 +276,7 @@ cudaError_t launchAllGatherGemm(const AgGemmArgs& argsIn, const void* const* B, 
   const uint64_t base = args.comm.peerBase[args.comm.rank];
   const uint64_t aLocalOff = reinterpret_cast<uint64_t>(args.aLocal) - base;
   const uint64_t aFullOff = reinterpret_cast<uint64_t>(args.aFull) - base;
+  const uint64_t dOff = reinterpret_cast<uint64_t>(args.D) - base;
   AgTmaps maps;
   for (int e = 0; e < emu; e++) {
     const uint64_t heap = emu > 1 ? args.comm.peerBase[e] : base;
@@ -295,6 +287,8 @@ cudaError_t launchAllGatherGemm(const AgGemmArgs& argsIn, const void* const* B, 
                                   gemm::kBlockM);
     if (err != cudaSuccess) return err;
     err = gemm::makeTensorMapBf16(&maps.b[e], B[e], N, K, static_cast<uint64_t>(K) * 2, twoSm ? tileN / 2 : tileN);
+    if (err != cudaSuccess) return err;
+    err = gemm::makeTensorMapBf16(&maps.d[e], reinterpret_cast<const void*>(heap + dOff), M, N, static_cast<uint64_t>(N) * 2, 32);
     if (err != cudaSuccess) return err;
   }
   const int tiles = numMBlk * (N / tileN);

@@ -63,20 +63,20 @@ struct PartialStoreSignal {
   uint32_t epoch;
   unsigned long long* tl;  // this CTA's time-line words or null
 
-  MSCCLPP_DEVICE_INLINE void tileBegin(int, int) const {}
-  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32], int /*slice*/ = 0) const {
-    if (row >= M) return;
-    uint4* dst = reinterpret_cast<uint4*>(partial + static_cast<size_t>(row) * N + col);
+  static constexpr bool kBulkStore = false;
+  MSCCLPP_DEVICE_INLINE static float convert(float x) { return x; }
+  MSCCLPP_DEVICE_INLINE void tileBegin(int, int, int) const {}
+  // Plain (generic-proxy) stores, four complete 128-byte lines per warp instruction: the flag that tileDone() publishes
+  // afterwards orders them for the peers' reducers with ordinary fences.
+  MSCCLPP_DEVICE_INLINE void block(const uint8_t* stage, int row0, int col0, int lane, int /*b*/) const {
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-      uint32_t w[4];
-#pragma unroll
-      for (int j = 0; j < 4; j++) {
-        __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[8 * i + 2 * j]), __uint_as_float(v[8 * i + 2 * j + 1]));
-        w[j] = *reinterpret_cast<uint32_t*>(&h);
+    for (int i = 0; i < 8; i++) {
+      const int row = row0 + gemm::stagedRow(i, lane);
+      if (row < M) {
+        *reinterpret_cast<uint4*>(partial + static_cast<size_t>(row) * N + col0 + gemm::stagedCol(lane)) = gemm::stagedRead(stage, i, lane);
       }
-      dst[i] = make_uint4(w[0], w[1], w[2], w[3]);
     }
+    __syncwarp();  // the staging buffer may be overwritten from here on
   }
 
   // Called by one warp after every epilogue warp has stored its part. One thread counts the tile; the CTA that
@@ -119,6 +119,8 @@ struct PartialStoreSignal {
     }
     if (tl) tl[13] += ptx::globaltimer() - tIn;
   }
+  MSCCLPP_DEVICE_INLINE void warpTileDone(int, int) const {}
+  MSCCLPP_DEVICE_INLINE void warpDrain(int) const {}
 };
 
 // Reducer CTAs are split into independent groups of kGroupThreads threads; a group owns one row at a
@@ -503,37 +505,39 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1) tpReduceNormKernel(const
 }
 
 // Epilogue of the single-GPU layer: h = bf16(acc) + residual (rounded to bf16 like the unfused composition), stored;
-// the row's sum of squares of the rounded values is added to sumsq[row] (one fp32 reduction per thread and chunk).
+// the row's sum of squares of the rounded values is added to sumsq[row] (one fp32 reduction per row and 64-column block).
+// The residual of a block is requested one block ahead (the first at tileBegin, before the accumulator is ready), with the
+// row-contiguous lane mapping of the staging buffer: every load and store covers complete 128-byte lines.
 struct ResidualSumsqStore {
   static constexpr bool kNeedsTileBarrier = false;
+  static constexpr bool kBulkStore = false;
   const bf16* residual;  // [M, N] or null
   bf16* h;               // [M, N]
   float* sumsq;          // [M]
   int M, N;
-  // Residual of this thread's row for the warp's whole part of the tile (up to 4 slices of 32 columns = 256 bytes),
-  // requested at tileBegin - before the accumulator is ready - so the loads overlap the tile's MMAs.
-  uint4 pre[16];
-  int slices;  // 32-column slices per warp and tile: kBlockN / 64
-  MSCCLPP_DEVICE_INLINE void tileBegin(int row, int col0) {
-    if (residual == nullptr || row >= M) return;
-    const bf16* src = residual + static_cast<size_t>(row) * N + col0;
+  int blocksPerWarp;  // 64-column blocks per warp and tile
+  uint4 pre[8];       // residual words of the block that comes next
+  MSCCLPP_DEVICE_INLINE static float convert(float x) { return x; }
+  MSCCLPP_DEVICE_INLINE void prefetch(int row0, int col0, int lane) {
+    if (residual == nullptr) return;
 #pragma unroll
-    for (int i = 0; i < 16; i++) {
-      if (i < 4 * slices) pre[i] = ptx::ld_nc_na_v4(src + 8 * i);
+    for (int i = 0; i < 8; i++) {
+      const int row = row0 + gemm::stagedRow(i, lane);
+      pre[i] = make_uint4(0, 0, 0, 0);
+      if (row < M) pre[i] = ptx::ld_nc_na_v4(residual + static_cast<size_t>(row) * N + col0 + gemm::stagedCol(lane));
     }
   }
-  MSCCLPP_DEVICE_INLINE void store(int row, int col, const uint32_t (&v)[32], int slice) {
-    if (row >= M) return;
-    const size_t off = static_cast<size_t>(row) * N + col;
-    float ss = 0.f;
-    uint4 res[4];
+  MSCCLPP_DEVICE_INLINE void tileBegin(int row0, int col0, int lane) { prefetch(row0, col0, lane); }
+  MSCCLPP_DEVICE_INLINE void block(const uint8_t* stage, int row0, int col0, int lane, int b) {
+    uint4 res[8];
 #pragma unroll
-    for (int i = 0; i < 4; i++) res[i] = pre[4 * slice + i];
+    for (int i = 0; i < 8; i++) res[i] = pre[i];
+    if (b + 1 < blocksPerWarp) prefetch(row0, col0 + 64, lane);
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < 8; i++) {
+      const int row = row0 + gemm::stagedRow(i, lane);
       float f[8];
-#pragma unroll
-      for (int j = 0; j < 8; j++) f[j] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[8 * i + j])));
+      Vec16<bf16>::toFloat(gemm::stagedRead(stage, i, lane), f);
       if (residual != nullptr) {
         float r[8];
         Vec16<bf16>::toFloat(res[i], r);
@@ -542,14 +546,169 @@ struct ResidualSumsqStore {
       }
       const uint4 packed = Vec16<bf16>::fromFloat(f);
       Vec16<bf16>::toFloat(packed, f);
+      float ss = 0.f;
 #pragma unroll
       for (int j = 0; j < 8; j++) ss += f[j] * f[j];
-      *reinterpret_cast<uint4*>(h + off + 8 * i) = packed;
+      // the eight lanes that share a row
+      ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+      ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      if (row < M) {
+        *reinterpret_cast<uint4*>(h + static_cast<size_t>(row) * N + col0 + gemm::stagedCol(lane)) = packed;
+        if ((lane & 7) == 0) atomicAdd(sumsq + row, ss);
+      }
     }
-    atomicAdd(sumsq + row, ss);
+    __syncwarp();
   }
   MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
+  MSCCLPP_DEVICE_INLINE void warpTileDone(int, int) const {}
+  MSCCLPP_DEVICE_INLINE void warpDrain(int) const {}
 };
+
+// The whole single-GPU layer in ONE kernel: the epilogue of ResidualSumsqStore, plus the normalisation. Every epilogue
+// warp counts its finished part of a tile on the tile's 128-row block; once a block has all its arrivals its rows are
+// final (h stored, sums of squares added) and become units of follow-up work, two rows each, handed out in ascending
+// order from one counter. A warp takes at most one unit after each tile part (without ever waiting: a unit is only
+// taken when its block is already complete), so the normalisation of block i runs in the shadow of the MMAs of the
+// blocks after it and h is re-read from L2; after its last tile a warp drains what is left, now with bounded waits.
+struct ResidualNormStore {
+  static constexpr bool kNeedsTileBarrier = false;
+  static constexpr bool kBulkStore = false;
+  static constexpr int kRowsPerUnit = 2;
+  ResidualSumsqStore base;
+  bf16* out;            // [M, N]
+  const bf16* gamma;    // [N] or null
+  uint32_t* blockCount;  // [ceil(M / 128)] arrivals per row block, zero at launch
+  uint32_t* nextUnit;    // zero at launch
+  uint32_t fullCount;    // arrivals that complete a row block: N tiles x epilogue warps per tile
+  float eps;
+  DeviceStatus* status;
+  uint64_t budgetNs;
+  uint32_t pendingUnit;  // per thread (lane 0 of each epilogue warp): a claimed unit whose block was not complete yet
+  MSCCLPP_DEVICE_INLINE static float convert(float x) { return x; }
+  MSCCLPP_DEVICE_INLINE void tileBegin(int row0, int col0, int lane) { base.tileBegin(row0, col0, lane); }
+  MSCCLPP_DEVICE_INLINE void block(const uint8_t* stage, int row0, int col0, int lane, int b) { base.block(stage, row0, col0, lane, b); }
+  MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
+
+  MSCCLPP_DEVICE_INLINE void normaliseRow(int row, int lane) const {
+    const int N = base.N;
+    const float rinv = rsqrtf(__ldcg(base.sumsq + row) / static_cast<float>(N) + eps);
+    const int words = N / 8;
+    const uint4* src = reinterpret_cast<const uint4*>(base.h + static_cast<size_t>(row) * N);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * N);
+    const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
+    for (int w0 = lane; w0 < words; w0 += 32 * 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        const int w = w0 + 32 * k;
+        if (w < words) v[k] = ptx::ld_nc_na_v4(src + w);  // written by other SMs during this launch: never through L1
+      }
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        const int w = w0 + 32 * k;
+        if (w < words) {
+          float f[8];
+          Vec16<bf16>::toFloat(v[k], f);
+          if (gamma != nullptr) {
+            float g[8];
+            Vec16<bf16>::toFloat(__ldg(g4 + w), g);
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = f[i] * rinv * g[i];
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = f[i] * rinv;
+          }
+          dst[w] = Vec16<bf16>::fromFloat(f);
+        }
+      }
+    }
+  }
+
+  MSCCLPP_DEVICE_INLINE void normaliseUnit(uint32_t u, int lane) const {
+    const int r0 = static_cast<int>(u) * kRowsPerUnit;
+#pragma unroll 1
+    for (int r = r0; r < r0 + kRowsPerUnit && r < base.M; r++) normaliseRow(r, lane);
+  }
+  MSCCLPP_DEVICE_INLINE bool blockComplete(uint32_t unit) const {
+    return ptx::ld_acquire_gpu(blockCount + unit * kRowsPerUnit / gemm::kBlockM) >= fullCount;
+  }
+
+  // Between tiles (never waits). A warp holds at most one claimed unit. It claims the next one - an atomic add, which
+  // cannot fail, so hundreds of warps do not pile up on one word - when the unit at the head of the queue belongs to a
+  // complete block; the unit it gets may lie a little further on, in a block that is not complete yet, and then stays
+  // with the warp until a later call (or the drain) finds its block complete.
+  MSCCLPP_DEVICE_INLINE void warpTileDone(int mBlk, int lane) {
+    constexpr uint32_t kNone = 0xffffffffu;
+    const uint32_t totalUnits = static_cast<uint32_t>((base.M + kRowsPerUnit - 1) / kRowsPerUnit);
+    __syncwarp();
+    uint32_t go = kNone;
+    if (lane == 0) {
+      __threadfence();  // this warp's h stores and sum-of-squares updates, before the arrival that may complete the block
+      atomicAdd(blockCount + mBlk, 1u);
+      if (pendingUnit == kNone) {
+        const uint32_t head = ptx::ld_volatile(nextUnit);
+        if (head < totalUnits && blockComplete(head)) {
+          const uint32_t mine = atomicAdd(nextUnit, 1u);
+          if (mine < totalUnits) pendingUnit = mine;
+        }
+      }
+      if (pendingUnit != kNone && blockComplete(pendingUnit)) {
+        go = pendingUnit;
+        pendingUnit = kNone;
+      }
+    }
+    go = __shfl_sync(0xffffffffu, go, 0);
+    if (go != kNone) normaliseUnit(go, lane);
+  }
+
+  // The warp has no tile left: finish the unit it holds, then claim and finish units until none is left. Waiting is
+  // safe here (bounded all the same): what a block still lacks is produced by warps that do not depend on this one.
+  MSCCLPP_DEVICE_INLINE void warpDrain(int lane) {
+    constexpr uint32_t kNone = 0xffffffffu;
+    const uint32_t totalUnits = static_cast<uint32_t>((base.M + kRowsPerUnit - 1) / kRowsPerUnit);
+    for (;;) {
+      uint32_t go = kNone;
+      if (lane == 0) {
+        uint32_t mine = pendingUnit;
+        pendingUnit = kNone;
+        if (mine == kNone && ptx::ld_volatile(nextUnit) < totalUnits) {
+          mine = atomicAdd(nextUnit, 1u);
+          if (mine >= totalUnits) mine = kNone;
+        }
+        if (mine != kNone) {
+          SpinGuard g(status, budgetNs);
+          bool ready = true;
+          while (!blockComplete(mine)) {
+            __nanosleep(200);
+            if (!g.keepSpinning()) {
+              g.report(kDevTimeoutFlag, 0, 7500, 0, fullCount, mine);
+              ready = false;
+              break;
+            }
+          }
+          if (ready) go = mine;
+        }
+      }
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (go == kNone) return;
+      normaliseUnit(go, lane);
+    }
+  }
+};
+
+template <int kBlockN>
+__global__ void __launch_bounds__(gemm::kNumThreads, 1)
+    tpLocalFusedKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, gemm::Shape shape,
+                       ResidualNormStore epi) {
+  extern __shared__ uint8_t smemRaw[];
+  gemm::NoGate gate;
+  if constexpr (kBlockN == 0) {
+    gemm::gemmCtaPair(&tmapA, &tmapB, shape, blockIdx.x / 2, gridDim.x / 2, gate, epi, epi.status, epi.budgetNs, smemRaw);
+  } else {
+    gemm::gemmCta<kBlockN>(&tmapA, &tmapB, shape, blockIdx.x, gridDim.x, gate, epi, epi.status, epi.budgetNs, smemRaw);
+  }
+}
 
 template <int kBlockN>
 __global__ void __launch_bounds__(gemm::kNumThreads, 1)
@@ -625,13 +784,9 @@ cudaError_t launchTyped(const TmapSet& maps, const TpFusedArgs& args, int grid, 
   using Cfg = SmemOf<kBlockN>;
   auto kernelNvls = tpFusedKernel<kBlockN, true>;
   auto kernelP2p = tpFusedKernel<kBlockN, false>;
-  static bool attrSet = false;
-  if (!attrSet) {
-    cudaError_t e = cudaFuncSetAttribute(kernelNvls, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(kernelP2p, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attrSet = true;
-  }
+  cudaError_t e = gemm::ensureDynamicSmem(reinterpret_cast<const void*>(kernelNvls), Cfg::kSmemBytes);
+  if (e == cudaSuccess) e = gemm::ensureDynamicSmem(reinterpret_cast<const void*>(kernelP2p), Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
   dim3 g(grid, args.emuRanks > 1 ? args.emuRanks : 1, 1);
   dim3 b(gemm::kNumThreads, 1, 1);
   auto kernel = args.nvls ? kernelNvls : kernelP2p;
@@ -760,12 +915,8 @@ cudaError_t launchLocalTyped(const CUtensorMap& ta, const CUtensorMap& tb, gemm:
                              cudaStream_t stream) {
   using Cfg = SmemOf<kBlockN>;
   auto kernel = gemmResidualSumsqKernel<kBlockN>;
-  static bool attrSet = false;
-  if (!attrSet) {
-    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
-    if (e != cudaSuccess) return e;
-    attrSet = true;
-  }
+  cudaError_t e = gemm::ensureDynamicSmem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
   uint64_t budget = 2000000000ull;
   if constexpr (kBlockN == 0) {
     const int tiles = ((shape.M + gemm::Config2::kPairM - 1) / gemm::Config2::kPairM) * (shape.N / gemm::Config2::kBlockN);
@@ -804,7 +955,7 @@ cudaError_t launchGemmResidualSumsq(const void* A, const void* B, const void* re
   epi.sumsq = sumsq;
   epi.M = M;
   epi.N = N;
-  epi.slices = (twoSm ? gemm::Config2::kBlockN : blockN) / 64;
+  epi.blocksPerWarp = twoSm ? gemm::Config2::kColsPerWarp / 64 : (blockN >= 128 ? blockN / 128 : 1);
   if (twoSm) return launchLocalTyped<0>(ta, tb, shape, epi, status, stream);
   switch (blockN) {
     case 64:
@@ -813,6 +964,82 @@ cudaError_t launchGemmResidualSumsq(const void* A, const void* B, const void* re
       return launchLocalTyped<128>(ta, tb, shape, epi, status, stream);
     default:
       return launchLocalTyped<256>(ta, tb, shape, epi, status, stream);
+  }
+}
+
+template <int kBlockN>
+cudaError_t launchLocalFusedTyped(const CUtensorMap& ta, const CUtensorMap& tb, gemm::Shape shape, ResidualNormStore epi, cudaStream_t stream) {
+  using Cfg = SmemOf<kBlockN>;
+  auto kernel = tpLocalFusedKernel<kBlockN>;
+  cudaError_t e = gemm::ensureDynamicSmem(reinterpret_cast<const void*>(kernel), Cfg::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  if constexpr (kBlockN == 0) {
+    const int tiles = ((shape.M + gemm::Config2::kPairM - 1) / gemm::Config2::kPairM) * (shape.N / gemm::Config2::kBlockN);
+    int grid = gemm::smCount() & ~1;
+    if (grid > 2 * tiles) grid = 2 * tiles;
+    void* params[] = {const_cast<CUtensorMap*>(&ta), const_cast<CUtensorMap*>(&tb), &shape, &epi};
+    return gemm::launchClusterPair(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(gemm::kNumThreads), Cfg::kSmemBytes, params, false,
+                                   stream);
+  } else {
+    const int tiles = ((shape.M + gemm::kBlockM - 1) / gemm::kBlockM) * (shape.N / kBlockN);
+    int grid = gemm::smCount();
+    if (grid > tiles) grid = tiles;
+    kernel<<<grid, gemm::kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, shape, epi);
+    return cudaGetLastError();
+  }
+}
+
+size_t tpLocalFusedWorkspaceBytes(int M) {
+  // [M] sums of squares, [row blocks, rounded up to the pair core's 256-row tiles] arrival counters, one unit counter
+  const size_t blocks = 2 * static_cast<size_t>((M + gemm::Config2::kPairM - 1) / gemm::Config2::kPairM);
+  return (static_cast<size_t>(M) + blocks + 1) * 4;
+}
+
+cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residual, void* h, void* out, const void* gamma, void* workspace,
+                               int M, int N, int K, float eps, int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % gemm::kBlockK != 0 || N % 8 != 0) return cudaErrorInvalidValue;
+  if (twoSm && (M < gemm::Config2::kPairM || N % gemm::Config2::kBlockN != 0)) return cudaErrorInvalidValue;
+  if (!twoSm && (blockN != 64 && blockN != 128 && blockN != 256)) return cudaErrorInvalidValue;
+  if (!twoSm && N % blockN != 0) return cudaErrorInvalidValue;
+  if ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual) |
+       reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(workspace)) & 15)
+    return cudaErrorInvalidValue;
+  cudaError_t e = cudaMemsetAsync(workspace, 0, tpLocalFusedWorkspaceBytes(M), stream);
+  if (e != cudaSuccess) return e;
+  // row blocks are walked one after the other (all their N tiles first), so that they complete in order and early
+  gemm::Shape shape{M, N, K, M < gemm::kBlockM ? M : gemm::kBlockM, 1, 0, 0, 0};
+  if (twoSm) shape.aBoxRows = gemm::kBlockM;
+  CUtensorMap ta, tb;
+  e = gemm::makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, shape.aBoxRows);
+  if (e != cudaSuccess) return e;
+  const int tileN = twoSm ? gemm::Config2::kBlockN : blockN;
+  e = gemm::makeTensorMapBf16(&tb, B, N, K, static_cast<uint64_t>(K) * 2, twoSm ? tileN / 2 : tileN);
+  if (e != cudaSuccess) return e;
+  const int epiWarps = tileN >= 128 ? gemm::kNumEpilogueWarps : 4;
+  ResidualNormStore epi{};
+  epi.base.residual = static_cast<const bf16*>(residual);
+  epi.base.h = static_cast<bf16*>(h);
+  epi.base.sumsq = static_cast<float*>(workspace);
+  epi.base.M = M;
+  epi.base.N = N;
+  epi.base.blocksPerWarp = tileN / (epiWarps / 4) / 64;
+  epi.out = static_cast<bf16*>(out);
+  epi.gamma = static_cast<const bf16*>(gamma);
+  epi.blockCount = reinterpret_cast<uint32_t*>(static_cast<float*>(workspace) + M);
+  epi.nextUnit = epi.blockCount + 2 * ((M + gemm::Config2::kPairM - 1) / gemm::Config2::kPairM);
+  epi.fullCount = static_cast<uint32_t>((N / tileN) * epiWarps);
+  epi.eps = eps;
+  epi.status = status;
+  epi.budgetNs = 2000000000ull;
+  epi.pendingUnit = 0xffffffffu;
+  if (twoSm) return launchLocalFusedTyped<0>(ta, tb, shape, epi, stream);
+  switch (blockN) {
+    case 64:
+      return launchLocalFusedTyped<64>(ta, tb, shape, epi, stream);
+    case 128:
+      return launchLocalFusedTyped<128>(ta, tb, shape, epi, stream);
+    default:
+      return launchLocalFusedTyped<256>(ta, tb, shape, epi, stream);
   }
 }
 

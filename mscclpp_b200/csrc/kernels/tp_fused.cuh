@@ -60,6 +60,13 @@ cudaError_t launchGemmResidualSumsq(const void* A, const void* B, const void* re
 cudaError_t launchTpScaleRowsFromSumsq(const void* h, const float* sumsq, const void* gamma, void* out, int M, int N, float eps,
                                        cudaStream_t stream);
 
+// The same single-GPU layer in ONE launch: h = bf16(A * B^T) + residual and out = h * rsqrt(mean(h^2) + eps) * gamma.
+// Rows are normalised by the epilogue warps as soon as their 128-row block is complete, while the MMAs of later blocks
+// run. `workspace`: tpLocalFusedWorkspaceBytes(M) bytes of device memory, 16-byte aligned (cleared here on `stream`).
+size_t tpLocalFusedWorkspaceBytes(int M);
+cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residual, void* h, void* out, const void* gamma, void* workspace,
+                               int M, int N, int K, float eps, int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream);
+
 // Local pass of mode 1: out = h * rinv[row] * gamma.
 cudaError_t launchTpScaleRows(const void* h, const float* rinv, const void* gamma, void* out, int M, int N,
                               cudaStream_t stream);

@@ -230,7 +230,8 @@ ncclResult_t runCollective(ncclComm_t comm, const char* opName, const char* coll
     req.collective = collective;
     req.dtype = dtype;
     req.op = op == ncclMin ? MIN : SUM;
-    req.symmetricMemory = comm->heap->contains(sendbuff, inBytes) && comm->heap->contains(recvbuff, outBytes);
+    // agreed among all ranks (a rank-local test could send the ranks into different kernels)
+    req.symmetricMemory = comm->heap->symmetricOnAllRanks(sendbuff, inBytes) && comm->heap->symmetricOnAllRanks(recvbuff, outBytes);
     cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
     if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess) req.inCapture = cap != cudaStreamCaptureStatusNone;
     else (void)cudaGetLastError();
@@ -585,15 +586,18 @@ ncclResult_t ncclAllToAllv(const void* sendbuff, const size_t sendcounts[], cons
   if (comm == nullptr || comm->destroyed) return fail(ncclInvalidArgument, "alltoallv: invalid communicator");
   if (sendcounts == nullptr || sdispls == nullptr || recvcounts == nullptr || rdispls == nullptr) return ncclInvalidArgument;
   const int n = comm->nranks;
-  // Equal counts laid out back to back are a plain all-to-all: the native kernel takes it.
-  bool uniform = true;
-  for (int r = 0; r < n && uniform; r++) {
-    uniform = sendcounts[r] == sendcounts[0] && recvcounts[r] == sendcounts[0] && sdispls[r] == static_cast<size_t>(r) * sendcounts[0] &&
-              rdispls[r] == static_cast<size_t>(r) * sendcounts[0];
-  }
-  if (uniform) return ncclAlltoAll(sendbuff, recvbuff, sendcounts[0], datatype, comm, stream);
-  // Ragged sizes: grouped point-to-point on the fallback NCCL (the native ragged exchange lives in the MoE kernels).
+  // Whether the layout is uniform is a property of THIS rank's arguments; a peer's row may be ragged. Choosing the native
+  // all-to-all kernel from it could put some ranks into that kernel and others into send/recv, so with a fallback NCCL
+  // loaded every alltoallv takes the grouped point-to-point path, whatever the counts look like here.
   if (comm->real == nullptr) {
+    // No fallback library: only the uniform case can run at all (the native kernel), and only if it is uniform on every
+    // rank - which the caller has to guarantee; a ragged call is refused.
+    bool uniform = true;
+    for (int r = 0; r < n && uniform; r++) {
+      uniform = sendcounts[r] == sendcounts[0] && recvcounts[r] == sendcounts[0] && sdispls[r] == static_cast<size_t>(r) * sendcounts[0] &&
+                rdispls[r] == static_cast<size_t>(r) * sendcounts[0];
+    }
+    if (uniform) return ncclAlltoAll(sendbuff, recvbuff, sendcounts[0], datatype, comm, stream);
     return fail(ncclInvalidUsage, "alltoallv with ragged counts needs the fallback NCCL (set MSCCLPP_NCCL_LIB_PATH)");
   }
   RealNccl& r = realNccl();

@@ -18,7 +18,7 @@ def _tb_targets(tb: Optional[int], tb_group: Optional[ThreadBlockGroup]):
         return [(tb, None)]
     if tb_group is not None:
         return [(t, TbgInfo(tb_group.get_internal_id(t), tb_group.numtb())) for t in tb_group.tb_list]
-    raise RuntimeError("Either 'tb' (thread block ID) or 'tb_group' (ThreadBlockGroup) must be provided, but both are None.")
+    raise RuntimeError("no thread block given: pass tb=<id> or tb_group=<ThreadBlockGroup>")
 
 
 def _local(chunk: Chunk) -> Operand:
@@ -29,7 +29,7 @@ class Rank:
     def __init__(self, rank: int):
         self.rank = rank
         if rank >= get_program().num_ranks:
-            raise RuntimeError(f"Rank {rank} is out of bounds. Number of ranks: {get_program().num_ranks}")
+            raise RuntimeError(f"rank {rank} does not exist in a program of {get_program().num_ranks} ranks")
 
     def get_input_buffer(self) -> BaseBuffer:
         return get_program().buffers[self.rank][BufferType.input]
@@ -37,15 +37,20 @@ class Rank:
     def get_output_buffer(self) -> BaseBuffer:
         return get_program().buffers[self.rank][BufferType.output]
 
-    def _copy(self, dst_chunk: Chunk, src_chunk: Chunk, tb, tb_group, from_packet=False, to_packet=False):
-        if dst_chunk.rank != self.rank or src_chunk.rank != self.rank:
-            raise RuntimeError(f"Inconsistent ranks: dst {dst_chunk.rank}, src {src_chunk.rank}, self {self.rank}. They must match.")
+    def _check_local_pair(self, dst_chunk: Chunk, src_chunk: Chunk):
+        """Both chunks live on this rank and cover the same number of chunks."""
+        for name, chunk in (("destination", dst_chunk), ("source", src_chunk)):
+            if chunk.rank != self.rank:
+                raise RuntimeError(f"{name} chunk belongs to rank {chunk.rank}, the operation runs on rank {self.rank}")
         if dst_chunk.size != src_chunk.size:
-            raise RuntimeError(f"Inconsistent chunk sizes: dst {dst_chunk.size}, src {src_chunk.size}. They must match.")
+            raise RuntimeError(f"destination covers {dst_chunk.size} chunks, source {src_chunk.size}: sizes must be equal")
+
+    def _copy(self, dst_chunk: Chunk, src_chunk: Chunk, tb, tb_group, from_packet=False, to_packet=False):
+        self._check_local_pair(dst_chunk, src_chunk)
         if from_packet and src_chunk.buffer != BufferType.scratch:
-            raise RuntimeError("Source chunk must be of type scratch.")
+            raise RuntimeError("packets are unpacked from the scratch buffer: the source chunk is elsewhere")
         if to_packet and dst_chunk.buffer != BufferType.scratch:
-            raise RuntimeError("Destination chunk must be of type scratch.")
+            raise RuntimeError("packets are written into the scratch buffer: the destination chunk is elsewhere")
         for tb_id, tbg in _tb_targets(tb, tb_group):
             op = ir.make_copy(_local(src_chunk), _local(dst_chunk), tbg, from_packet, to_packet)
             get_program().add_operation(self.rank, tb_id, op)
@@ -63,19 +68,16 @@ class Rank:
                dst_chunk: Chunk = None, reduce_op: ReduceOperationType = ReduceOperationType.sum, packet: bool = False):
         if dst_chunk is None:
             dst_chunk = src_chunk
-        if dst_chunk.rank != self.rank or src_chunk.rank != self.rank:
-            raise RuntimeError(f"Inconsistent ranks: dst {dst_chunk.rank}, src {src_chunk.rank}, self {self.rank}. They must match.")
-        if dst_chunk.size != src_chunk.size:
-            raise RuntimeError(f"Inconsistent chunk sizes: dst {dst_chunk.size}, src {src_chunk.size}. They must match.")
-        if len(other_chunks) == 0:
-            raise RuntimeError("Other chunk empty.")
+        self._check_local_pair(dst_chunk, src_chunk)
+        if not other_chunks:
+            raise RuntimeError("reduce needs at least one chunk besides the source")
         for chunk in other_chunks:
             if chunk.rank != self.rank:
-                raise RuntimeError(f"Other chunk rank {chunk.rank} does not match current rank {self.rank}.")
+                raise RuntimeError(f"reduce on rank {self.rank} was given a chunk of rank {chunk.rank}")
             if chunk.size != src_chunk.size:
-                raise RuntimeError(f"Inconsistent chunk sizes: other {chunk.size}, src {src_chunk.size}. They must match.")
+                raise RuntimeError(f"reduce operands differ in size: {chunk.size} vs {src_chunk.size} chunks")
             if packet and chunk.buffer != BufferType.scratch:
-                raise RuntimeError("Other chunk must be of type scratch.")
+                raise RuntimeError("a packet reduce reads its other operands from the scratch buffer")
         for tb_id, tbg in _tb_targets(tb, tb_group):
             op = ir.make_reduce([_local(src_chunk)] + [_local(c) for c in other_chunks], [_local(dst_chunk)],
                                 reduce_op=reduce_op, tbg=tbg, packet=packet)
@@ -83,7 +85,7 @@ class Rank:
 
     def barrier(self, tb_list: List[int]):
         if len(tb_list) == 0:
-            raise RuntimeError("Barrier requires at least thread block.")
+            raise RuntimeError("a barrier needs at least one thread block")
         prog = get_program()
         if len(tb_list) == 1:
             prog.add_operation(self.rank, tb_list[0], ir.make_sync())
@@ -99,7 +101,7 @@ class Semaphore:
     def __init__(self, rank: int, initial_value: int):
         prog = get_program()
         if rank >= prog.num_ranks:
-            raise RuntimeError(f"Source rank {rank} is out of bounds. Number of ranks: {prog.num_ranks}")
+            raise RuntimeError(f"semaphore on rank {rank}: the program has {prog.num_ranks} ranks")
         self.id = prog.next_semaphore_id(rank)
         self.rank = rank
         self.initial_value = initial_value

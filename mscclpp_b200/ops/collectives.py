@@ -5,6 +5,8 @@ Algorithm names follow the reference's default collection
   "packet" / "nvls_packet"          one-shot LL16 over peer stores / one multimem.st per packet
   "rsag_zero_copy"                  two-shot over peer loads+stores, zero copy
   "nvls_zero_copy"                  two-shot through NVSwitch multimem.ld_reduce + multimem.st
+  "nvls_block_pipeline" / "rsag_pipeline"   tensors OUTSIDE the heap: one kernel copies in, reduces through heap scratch
+                                    (switch reduction / peer loads) and copies out, slice by slice
 The selector mirrors the shape of the reference's Blackwell table
 (src/ext/nccl/algorithm_selector.cc:52-89) with thresholds measured on B200.
 """
@@ -36,15 +38,44 @@ def _op(op: str):
     return {"sum": n.ReduceOp.SUM, "min": n.ReduceOp.MIN}[op]
 
 
+def ll_max_bytes(world: int) -> int:
+    """Largest message for which the one-shot packet algorithm wins (every rank sends its whole buffer to every peer, so
+    the range shrinks as the world grows; measured on 2, 4 and 8 B200s)."""
+    return (1 << 20) if world <= 2 else ((256 << 10) if world <= 4 else (128 << 10))
+
+
 def select_allreduce(symm: SymmetricMemory, nbytes: int, symmetric: bool) -> str:
     ll_cap = _ll_capacity(symm)
-    if nbytes <= min(LL_MAX_BYTES, ll_cap) or not symmetric:
-        if nbytes > ll_cap:
-            raise ValueError("buffer outside the symmetric heap is too large for the LL path; allocate it with symm.tensor()")
-        return "nvls_packet" if symm.nvls and nbytes <= (32 << 10) else "packet"
+    ll_max = ll_max_bytes(symm.world) * (1 if symmetric else 2)
+    if nbytes <= min(ll_max, ll_cap):
+        return "nvls_packet" if symm.nvls and nbytes <= (64 << 10) else "packet"
+    # with two ranks the switch has nothing to combine: plain peer loads win from 16 MB on
+    use_switch = symm.nvls and (symm.world > 2 or nbytes < (16 << 20))
+    if not symmetric:
+        return "nvls_block_pipeline" if use_switch else "rsag_pipeline"
     if nbytes % 16 != 0:
         raise ValueError("zero-copy allreduce needs a multiple of 16 bytes")
-    return "nvls_zero_copy" if symm.nvls else "rsag_zero_copy"
+    return "nvls_zero_copy" if use_switch else "rsag_zero_copy"
+
+
+PIPELINE_SLICE_BYTES = 64 << 10
+PIPELINE_MAX_BLOCKS = 128
+
+
+def _pipeline_scratch(symm: SymmetricMemory) -> torch.Tensor:
+    """Heap scratch of the pipelined allreduce, made on first use (every rank gets here on the same call)."""
+    cache = symm.__dict__.setdefault("_pipeline_scratch", None)
+    if cache is None:
+        n = native.load()
+        nbytes = n.pipeline_scratch_bytes(PIPELINE_MAX_BLOCKS, _pipeline_slice(symm))
+        cache = symm.tensor((nbytes,), torch.uint8)
+        symm.__dict__["_pipeline_scratch"] = cache
+    return cache
+
+
+def _pipeline_slice(symm: SymmetricMemory) -> int:
+    unit = 16 * symm.world
+    return (PIPELINE_SLICE_BYTES + unit - 1) // unit * unit
 
 
 def _ll_capacity(symm: SymmetricMemory) -> int:
@@ -77,8 +108,24 @@ def all_reduce(symm: SymmetricMemory, inp: torch.Tensor, out: Optional[torch.Ten
     out = inp if out is None else out
     assert inp.is_contiguous() and out.is_contiguous() and inp.dtype == out.dtype and inp.numel() == out.numel()
     nbytes = _nbytes(inp)
-    symmetric = symm.contains(inp) and symm.contains(out)
+    if symm.emulated_mode or symm.world == 1:
+        symmetric = symm.contains(inp) and symm.contains(out)
+    else:  # agreed among the ranks: a rank-local test could send them into different kernels
+        symmetric = symm.heap.symmetric_on_all_ranks(inp.data_ptr(), nbytes) and symm.heap.symmetric_on_all_ranks(out.data_ptr(), nbytes)
     algo = algo or select_allreduce(symm, nbytes, symmetric)
+    if algo in ("nvls_block_pipeline", "rsag_pipeline"):
+        scratch = _pipeline_scratch(symm)
+        slice_bytes = _pipeline_slice(symm)
+        blocks = n_blocks or max(1, min(PIPELINE_MAX_BLOCKS, (nbytes + slice_bytes - 1) // slice_bytes))
+        emu_stride = 0
+        if symm.emulated_mode:  # emulated ranks: row r of a [world, ...] tensor is rank r's buffer
+            assert inp.shape[0] == symm.world and out.shape[0] == symm.world
+            nbytes //= symm.world
+            emu_stride = nbytes
+            blocks = min(blocks, 16)
+        n.pipeline_allreduce(symm.heap, inp.data_ptr(), out.data_ptr(), nbytes, torch_dtype_to_native(inp.dtype), _op(op), scratch.data_ptr(),
+                             slice_bytes, blocks, n_threads or 512, _stream(stream), algo == "nvls_block_pipeline", emu_stride)
+        return out
     blocks, threads = _grid_for(nbytes, algo, symm.world)
     blocks = n_blocks or blocks
     threads = n_threads or threads

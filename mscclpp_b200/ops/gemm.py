@@ -21,11 +21,14 @@ def pick_block_n(m: int, n: int) -> int:
 
 
 def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, block_n: int = 0, num_ctas: int = 0,
-              stream: Optional[torch.cuda.Stream] = None, two_sm: Optional[bool] = None) -> torch.Tensor:
+              stream: Optional[torch.cuda.Stream] = None, two_sm: Optional[bool] = None, probe: int = 0, band: int = 0) -> torch.Tensor:
     """out[M, N] = a[M, K] @ w[N, K]^T  (w in nn.Linear layout: out_features x in_features).
 
     two_sm: run 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2); None picks it when the problem has enough
-    such tiles to fill the GPU and no N tile was asked for."""
+    such tiles to fill the GPU and no N tile was asked for.
+    band: row blocks per band of the tile order (0 = default for the tile shape, -1 = plain column-major walk).
+    probe: diagnostics only (the result is then garbage): bit 0 drops the operand loads, bit 1 the MMAs, bit 2 the
+    epilogue's stores; timing each shows which of the kernel's three pipelines bounds a shape."""
     n = native.load()
     assert a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.is_contiguous() and w.is_contiguous()
     m, k = a.shape
@@ -38,8 +41,8 @@ def gemm_bf16(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = No
     if two_sm is None:
         two_sm = block_n == 0 and nn % 256 == 0 and ((m + 255) // 256) * (nn // 256) >= 74
     if two_sm:
-        n.gemm_bf16_two_sm(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, nn, k, nn, num_ctas, 0, s)
+        n.gemm_bf16_two_sm(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, nn, k, nn, num_ctas, 0, s, probe, band)
         return out
     bn = block_n or pick_block_n(m, nn)
-    n.gemm_bf16(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, nn, k, nn, bn, num_ctas, 0, s)
+    n.gemm_bf16(a.data_ptr(), w.data_ptr(), out.data_ptr(), m, nn, k, nn, bn, num_ctas, 0, s, probe, band)
     return out

@@ -41,6 +41,7 @@ class RowParallelLinearNorm:
         self.gamma = symm.tensor((out_features,), torch.bfloat16)
         self.gamma.fill_(1.0)
         self.rinv = symm.tensor((max_tokens,), torch.float32)
+        self._local_ws = None  # workspace of the one-kernel single-GPU path, made on first use
         self.launches_per_forward = 1  # forward_fused, mode 0
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, algo: Optional[str] = None,
@@ -105,9 +106,11 @@ class RowParallelLinearNorm:
         return self.out[:t], self.residual_out[:t]
 
     def forward_local(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, two_sm: Optional[bool] = None,
-                      stream: Optional[torch.cuda.Stream] = None) -> Tuple[torch.Tensor, torch.Tensor]:
-        """World size 1 (no collective): the GEMM's epilogue adds the residual, stores h and accumulates every row's
-        sum of squares; a second, memory-bound launch applies 1/rms and gamma. Two launches, no intermediate passes."""
+                      stream: Optional[torch.cuda.Stream] = None, one_kernel: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+        """World size 1 (no collective). one_kernel (default): ONE launch - the GEMM's epilogue adds the residual, stores h
+        and accumulates every row's sum of squares, and the epilogue warps normalise each 128-row block as soon as it is
+        complete, in the shadow of the MMAs of the later blocks. one_kernel=False: the same epilogue, then a second,
+        memory-bound launch that applies 1/rms and gamma."""
         from .._core import native
 
         assert self.symm.world == 1, "forward_local is the single-GPU path"
@@ -119,6 +122,14 @@ class RowParallelLinearNorm:
         if two_sm is None:
             two_sm = t >= 1024 and self.out_features % 256 == 0
         s = (stream or torch.cuda.current_stream()).cuda_stream
+        if one_kernel:
+            if self._local_ws is None:
+                self._local_ws = torch.empty((n.tp_local_fused_workspace_bytes(self.max_tokens) + 15) // 16 * 4, dtype=torch.float32,
+                                             device=self.symm.device)
+            n.tp_local_fused(x.data_ptr(), self.weight.data_ptr(), self.residual_in.data_ptr(), self.residual_out.data_ptr(),
+                             self.out.data_ptr(), self.gamma.data_ptr(), self._local_ws.data_ptr(), t, self.out_features, self.k_shard,
+                             self.eps, pick_block_n(t, self.out_features), two_sm, 0, s)
+            return self.out[:t], self.residual_out[:t]
         n.gemm_residual_sumsq(x.data_ptr(), self.weight.data_ptr(), self.residual_in.data_ptr(), self.residual_out.data_ptr(),
                               self.rinv.data_ptr(), t, self.out_features, self.k_shard, pick_block_n(t, self.out_features), two_sm, s)
         n.tp_scale_rows_from_sumsq(self.residual_out.data_ptr(), self.rinv.data_ptr(), self.gamma.data_ptr(), self.out.data_ptr(), t,

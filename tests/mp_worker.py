@@ -60,6 +60,32 @@ def main():
             symm.release(out)
             symm.release(inp)
 
+    # ordinary tensors (outside the heap): the pipelined kernel, sizes with a tail and of many rounds
+    for dtype in (torch.bfloat16, torch.float32):
+        for numel in (70001, 1 << 20, (5 << 20) + 24):
+            for algo in ["rsag_pipeline"] + (["nvls_block_pipeline"] if symm.nvls else []):
+                for rep in range(2):
+                    g = torch.Generator(device=dev).manual_seed(rank * 11 + numel + rep)
+                    x = torch.randn((numel,), generator=g, device=dev).to(dtype)
+                    y = torch.full_like(x, float("nan"))
+                    expect = gathered_reference(x).to(dtype).float()
+                    torch.cuda.synchronize()
+                    dist.barrier()
+                    all_reduce(symm, x, y, algo=algo)
+                    torch.cuda.synchronize()
+                    symm.check()
+                    tol = {torch.bfloat16: 6e-2, torch.float32: 1e-4}[dtype]
+                    err = (y.float() - expect).abs().max().item()
+                    report(f"allreduce_outside_heap/{algo}/{dtype}/{numel}/{rep}", err <= tol * max(1.0, expect.abs().max().item()), err=err)
+    # default choice for an ordinary tensor, in place
+    x = torch.randn((3 << 20,), device=dev).to(torch.bfloat16)
+    expect = gathered_reference(x).to(torch.bfloat16).float()
+    dist.barrier()
+    all_reduce(symm, x)
+    torch.cuda.synchronize()
+    symm.check()
+    report("allreduce_outside_heap/default/in_place", (x.float() - expect).abs().max().item() <= 6e-2 * max(1.0, expect.abs().max().item()))
+
     # reduce-scatter / all-gather
     per = 8192
     full = symm.tensor((world * per,), torch.bfloat16)

@@ -56,6 +56,29 @@ def test_allreduce_ll(world, dtype, numel):
     symm.destroy()
 
 
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("numel", [4096, 262144 + 8, 3 << 20])
+def test_allreduce_pipeline_buffers_outside_the_heap(world, dtype, numel):
+    """Ordinary CUDA tensors (not heap memory): one kernel copies in, reduces through heap scratch and copies out.
+    Row r of the [world, numel] tensors is emulated rank r's buffer; with 4 blocks the larger sizes take many rounds."""
+    from mscclpp_b200.ops import all_reduce
+
+    symm = _symm(world)
+    for launch in range(2):
+        g = torch.Generator(device="cuda").manual_seed(numel + launch)
+        x = torch.randn((world, numel), generator=g, device="cuda").to(dtype)
+        out = torch.full_like(x, float("nan"))
+        assert not symm.contains(x)
+        all_reduce(symm, x, out, algo="rsag_pipeline", n_blocks=4)
+        torch.cuda.synchronize()
+        symm.check()
+        expect = x.float().sum(0).to(dtype).float()
+        for r in range(world):
+            torch.testing.assert_close(out[r].float(), expect, atol=_tol(dtype) * 4, rtol=_tol(dtype))
+    symm.destroy()
+
+
 @pytest.mark.parametrize("world", [2, 8])
 def test_allreduce_ll_int_and_min(world):
     from mscclpp_b200.ops import all_reduce
