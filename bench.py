@@ -197,15 +197,50 @@ def main():
         symm.check()
         return max_over_ranks(start.elapsed_time(end) / steps)  # ms per step
 
+    # ------------------------------------------------------------------ values first: the layer against an fp32 PyTorch reference
+    def verify(t_check, fn, label):
+        """fn() runs the layer on xs_check; every rank compares the result with the fp32 composition of ALL ranks' shards."""
+        out, res = fn()
+        torch.cuda.synchronize()
+        symm.check()
+        if world > 1:
+            x_all = [torch.empty_like(x_check) for _ in range(world)]
+            w_all = [torch.empty_like(layer.weight) for _ in range(world)]
+            dist.all_gather(x_all, x_check)
+            dist.all_gather(w_all, layer.weight)
+        else:
+            x_all, w_all = [x_check], [layer.weight]
+        ref_out, ref_res = layer.reference(x_all, w_all, layer.residual_in[:t_check])
+        err_out = (out.float() - ref_out.float()).abs().max().item()
+        err_res = (res.float() - ref_res.float()).abs().max().item()
+        tol_res = 0.02 * ref_res.float().abs().max().item() + 0.05
+        ok = err_out <= 0.1 and err_res <= tol_res
+        worst = max_over_ranks(0.0 if ok else 1.0)
+        if worst > 0:
+            raise RuntimeError(f"bench.py: {label} disagrees with the fp32 reference (out {err_out:.4f}, residual {err_res:.4f})")
+        return {"max_abs_err_out": round(err_out, 4), "max_abs_err_residual": round(err_res, 4)}
+
+    T_CHECK = 256
+    x_check = xs[2048][:T_CHECK].contiguous()
+    value_check = {}
+
     # ------------------------------------------------------------------ pick the fused variant (untimed)
     # variant = (mode, nvls, reducer CTAs, GEMM core): core 1 = one-SM tiles, 2 = 256 x 256 tiles on SM pairs (cta_group::2)
     def fused(t, mode, nvls, reducers, core=1):
-        if mode == -2:  # one GPU: GEMM whose epilogue adds the residual and sums the squares, then the scale pass
-            return lambda: layer.forward_local(xs[t], two_sm=(core == 2))
+        if mode in (-2, -3):  # one GPU: GEMM whose epilogue adds the residual and sums the squares; the normalisation as a
+            # second, local launch (-2) or inside the same launch (-3)
+            return lambda: layer.forward_local(xs[t], two_sm=(core == 2), one_kernel=(mode == -3))
         if mode < 0:  # two launches: tcgen05 GEMM, then the fused allreduce + residual + RMSNorm kernel
             return lambda: layer.forward(xs[t])
         bn = -1 if core == 2 else pick_block_n(t, HIDDEN)
         return lambda: layer.forward_fused(xs[t], mode=mode, nvls=nvls, num_reducers=reducers, block_n=bn)
+
+    def fused_kwargs(v, t):
+        """forward_fused arguments of a variant (for forward_from_host, which launches one piece of the rows at a time)."""
+        mode, nvls, reducers, core = v
+        if mode < 0:
+            return {}
+        return {"mode": mode, "nvls": nvls, "num_reducers": reducers, "block_n": -1 if core == 2 else pick_block_n(t, HIDDEN)}
 
     # the switch reduction wins from 8 ranks on; with 2 or 4 peers plain peer loads/stores are as fast or faster
     nvls_opts = ([True, False] if world <= 4 else [True]) if symm.nvls else [False]
@@ -213,8 +248,7 @@ def main():
     if world > 4 and symm.nvls:  # plain peer loads/stores for comparison
         variants += [(1, False, r, 2) for r in (32, 64)]
     if world == 1:
-        variants = [(0, False, 64, 1), (1, False, 64, 1), (0, False, 64, 2), (1, False, 64, 2), (-1, False, 0, 1), (-2, False, 0, 1),
-                    (-2, False, 0, 2)]
+        variants = [(1, False, 64, 1), (-1, False, 0, 1), (-2, False, 0, 1), (-2, False, 0, 2), (-3, False, 0, 1), (-3, False, 0, 2)]
     best = {}
     tune_scores = {}
     for t in TOKEN_SIZES:
@@ -226,6 +260,21 @@ def main():
         best[t] = min(scores, key=scores.get)
         tune_scores[str(t)] = {"/".join(str(int(x)) for x in v): round(ms * 1e3, 1) for v, ms in scores.items()}
 
+    # the variant that will be timed, on 256 tokens, against the fp32 reference of all ranks' shards
+    def run_variant(x, v):
+        mode, nvls, reducers, core = v
+        if mode in (-2, -3):
+            return layer.forward_local(x, two_sm=(core == 2 and x.shape[0] >= 256), one_kernel=(mode == -3))
+        if mode < 0:
+            return layer.forward(x)
+        return layer.forward_fused(x, mode=mode, nvls=nvls, num_reducers=reducers,
+                                   block_n=-1 if (core == 2 and x.shape[0] >= 256) else pick_block_n(x.shape[0], HIDDEN))
+
+    value_check["headline_variant_T256"] = verify(T_CHECK, lambda: run_variant(x_check, best[HEADLINE_T]), "the headline variant")
+    value_check["end_to_end_path_T256"] = verify(
+        T_CHECK, lambda: layer.forward_from_host(x_check.cpu().pin_memory(), chunks=1, **fused_kwargs(best[HEADLINE_T], T_CHECK)),
+        "the end-to-end path")
+
     # ------------------------------------------------------------------ headline: fused TP layer at T = 8192
     sampler = ClockSampler(local_rank if "CUDA_VISIBLE_DEVICES" not in os.environ else
                            int(os.environ["CUDA_VISIBLE_DEVICES"].split(",")[local_rank]))
@@ -234,7 +283,9 @@ def main():
     head_mode, head_nvls, head_reducers, head_core = best[HEADLINE_T]
     head_fn = fused(HEADLINE_T, head_mode, head_nvls, head_reducers, head_core)
     ms_per_step = time_steps(head_fn, args.steps, max(args.warmup, 3))
-    launches = args.steps * (1 if head_mode == 0 else 2)  # mode 1 and the two-launch path (-1) use two kernels
+    # kernels of this library per step: the one-kernel paths (fused mode 0, the single-GPU layer) launch 1, fused mode 1 adds
+    # its local scale pass, the unfused path is GEMM + allreduce/norm kernel
+    launches = args.steps * (1 if head_mode in (0, -3) else 2)
 
     # ------------------------------------------------------------------ per-T table: eager launches and CUDA-graph replay
     tp_us, tp_graph_us, tp_unfused_us, tp_baseline_us = {}, {}, {}, {}
@@ -251,8 +302,8 @@ def main():
             torch.cuda.synchronize()
             with torch.cuda.graph(graph, stream=side):
                 for _ in range(reps):
-                    if best[t][0] == -2:
-                        layer.forward_local(xs[t], two_sm=(best[t][3] == 2), stream=side)
+                    if best[t][0] in (-2, -3):
+                        layer.forward_local(xs[t], two_sm=(best[t][3] == 2), one_kernel=(best[t][0] == -3), stream=side)
                     elif best[t][0] < 0:
                         layer.forward(xs[t], stream=side)
                     else:
@@ -277,18 +328,16 @@ def main():
 
     # ------------------------------------------------------------------ end to end through the public API
     x_host = torch.randn((HEADLINE_T, K_SHARD)).to(torch.bfloat16).pin_memory()
-    x_dev = torch.empty_like(x_host, device=dev)
     result_host = torch.empty((1,), dtype=torch.float32).pin_memory()
 
+    E2E_CHUNKS = 4
+    e2e_kwargs = fused_kwargs(best[HEADLINE_T], HEADLINE_T // E2E_CHUNKS)
+    if head_mode == -1:  # the two-launch variant has no row-offset form: the one-launch kernel takes the pieces
+        e2e_kwargs = {"mode": 1, "nvls": head_nvls}
+
     def e2e_step():
-        x_dev.copy_(x_host, non_blocking=True)
-        if head_mode == -2:
-            out, _ = layer.forward_local(x_dev, two_sm=(head_core == 2))
-        elif head_mode < 0:
-            out, _ = layer.forward(x_dev)
-        else:
-            out, _ = layer.forward_fused(x_dev, mode=head_mode, nvls=head_nvls, num_reducers=head_reducers,
-                                         block_n=-1 if head_core == 2 else pick_block_n(HEADLINE_T, HIDDEN))
+        # public API on host input: piece i+1 of the rows crosses PCIe while piece i is computed
+        out, _ = layer.forward_from_host(x_host, chunks=E2E_CHUNKS, **e2e_kwargs)
         result_host.copy_(out[:, :8].float().abs().mean().reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()  # the caller looks at the metric every step
 
@@ -309,6 +358,22 @@ def main():
         buf_out = symm.tensor((sweep_bytes // 2,), torch.bfloat16)
         buf_in.normal_()
         nccl_buf = torch.empty((sweep_bytes // 2,), dtype=torch.bfloat16, device=dev).normal_()
+        side2 = torch.cuda.Stream()
+
+        def graph_us(fn, reps=20):
+            """Per-call device time when `reps` calls are replayed from one CUDA graph (the reference's own timing method,
+            test/mscclpp-test/common.cc:204-225: no host launch cost between the calls)."""
+            graph = torch.cuda.CUDAGraph()
+            barrier()
+            with torch.cuda.stream(side2):
+                with torch.cuda.graph(graph, stream=side2):
+                    for _ in range(reps):
+                        fn(side2)
+            barrier()
+            us = time_steps(graph.replay, 5, 2) * 1e3 / reps
+            del graph
+            return round(us, 2)
+
         size = 1024
         while size <= sweep_bytes:
             n = size // 2
@@ -327,14 +392,20 @@ def main():
                     row[algo + "_us"] = round(ms * 1e3, 2)
                 except Exception as e:  # noqa: BLE001
                     row[algo + "_err"] = str(e)[:80]
+            # what a caller gets without naming an algorithm (the selector), eager and replayed from a graph
+            row["auto_us"] = round(time_steps(lambda: all_reduce(symm, buf_in[:n], buf_out[:n]), iters, 5) * 1e3, 2)
+            if size <= (16 << 20):
+                row["auto_graph_us"] = graph_us(lambda st: all_reduce(symm, buf_in[:n], buf_out[:n], stream=st))
+            # an ordinary tensor (outside the symmetric heap), in place: packets, or the pipelined copy-in/reduce/copy-out kernel
+            row["outside_heap_us"] = round(time_steps(lambda: all_reduce(symm, nccl_buf[:n]), iters, 5) * 1e3, 2)
             ms = time_steps(lambda: dist.all_reduce(nccl_buf[:n]), iters, 5)
             row["nccl_us"] = round(ms * 1e3, 2)
-            ours = min(v for k, v in row.items() if k.endswith("_us") and k != "nccl_us")
+            ours = min(v for k, v in row.items() if k.endswith("_us") and k not in ("nccl_us", "auto_graph_us", "outside_heap_us"))
             row["best_us"] = ours
             row["busbw_gbs"] = round(size * 2 * (world - 1) / world / (ours * 1e-6) / 1e9, 2)
             row["nccl_busbw_gbs"] = round(size * 2 * (world - 1) / world / (row["nccl_us"] * 1e-6) / 1e9, 2)
             sweep.append(row)
-            size *= 4
+            size *= 2
 
     if rank == 0:
         us = ms_per_step * 1e3
@@ -362,6 +433,7 @@ def main():
                         "gemm_core": "two-SM 256x256 (cta_group::2)" if head_core == 2 else "one-SM 128x256",
                         "kernel": ("gemmResidualSumsqKernel (tcgen05 GEMM, epilogue adds residual + row sums of squares) then scale pass"
                                    if head_mode == -2 else
+                                   "tpLocalFusedKernel (tcgen05 GEMM + residual + RMSNorm in one launch)" if head_mode == -3 else
                                    "gemmBf16Kernel (tcgen05) then twoShot/LL allreduce+residual+RMSNorm kernel" if head_mode < 0 else
                                    "tpFusedKernel (tcgen05 GEMM + multimem/peer reduce + residual + RMSNorm in one launch)" +
                                    ("" if head_mode == 0 else " + local scale pass")),
@@ -372,10 +444,12 @@ def main():
             "tp_layer_two_kernel_us": tp_unfused_us,
             "tp_layer_cublas_nccl_torch_us": tp_baseline_us,
             "e2e": {"value": round(e2e_ms * 1e3, 2), "unit": "us", "h2d_bytes_per_step": x_host.numel() * 2,
-                    "d2h_bytes_per_step": 4},
+                    "d2h_bytes_per_step": 4, "how": f"layer.forward_from_host: {E2E_CHUNKS} pieces of the rows, the copy of piece i+1 overlaps "
+                                                    "the launch of piece i"},
             "gpu_launches": launches,
             "clocks": clocks,
             "allreduce_sweep": sweep,
+            "value_check": value_check,
         }
         print(json.dumps(line), flush=True)
     barrier()

@@ -3,6 +3,7 @@ cooperative launch (gridDim.y = world) on one GPU, so the kernels can be capture
 multi-process job. Device-timed; numbers are NOT comparable to real multi-GPU runs (all "peers" share one HBM).
 
     python -m mscclpp_b200.benchmark.single_gpu tp-layer   --tokens 2048 --world 1
+    python -m mscclpp_b200.benchmark.single_gpu tp-local   --tokens 2048 [--probe 128] [--two-sm 1] [--one-kernel 0]
     python -m mscclpp_b200.benchmark.single_gpu allreduce  --world 8 --mbytes 16
     python -m mscclpp_b200.benchmark.single_gpu moe        --world 8 --tokens 1024
 """
@@ -51,6 +52,25 @@ def tp_layer(args):
     symm.destroy()
 
 
+def tp_local(args):
+    """The single-GPU layer (GEMM + residual + RMSNorm, world size 1) through its own kernel(s)."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.tp_layer import RowParallelLinearNorm
+
+    symm = SymmetricMemory.emulated(1, nbytes=(5 * args.tokens * args.hidden * 2) + (64 << 20), timeout_ms=5000)
+    layer = RowParallelLinearNorm(symm, args.hidden, args.k, max_tokens=args.tokens)
+    x = torch.randn((args.tokens, args.k), device="cuda").to(torch.bfloat16)
+    layer.residual_in.normal_()
+    fn = lambda: layer.forward_local(x, two_sm=bool(args.two_sm), one_kernel=bool(args.one_kernel), probe=args.probe)  # noqa: E731
+    us = _timed(fn, args.iters, args.warmup)
+    moved = args.tokens * args.hidden * 2 * 3 + (args.tokens + args.hidden) * args.k * 2
+    print(json.dumps({"tp_local": {"tokens": args.tokens, "hidden": args.hidden, "k": args.k, "two_sm": bool(args.two_sm),
+                                   "one_kernel": bool(args.one_kernel), "probe": args.probe, "us": round(us, 2),
+                                   "tflops": round(2.0 * args.tokens * args.k * args.hidden / us / 1e6, 1),
+                                   "algorithmic_gbs": round(moved / us / 1e3, 1)}}), flush=True)
+    symm.destroy()
+
+
 def allreduce(args):
     from mscclpp_b200 import SymmetricMemory
     from mscclpp_b200.ops import all_reduce
@@ -96,25 +116,28 @@ def moe(args):
 def main(argv=None) -> int:
     p = argparse.ArgumentParser()
     sub = p.add_subparsers(dest="cmd", required=True)
-    for name in ("tp-layer", "allreduce", "moe"):
+    for name in ("tp-layer", "tp-local", "allreduce", "moe"):
         s = sub.add_parser(name)
-        s.add_argument("--world", type=int, default=1 if name == "tp-layer" else 8)
+        s.add_argument("--world", type=int, default=1 if name.startswith("tp-") else 8)
         s.add_argument("--iters", type=int, default=10)
         s.add_argument("--warmup", type=int, default=3)
-        s.add_argument("--tokens", type=int, default=2048 if name == "tp-layer" else 1024)
-        s.add_argument("--hidden", type=int, default=8192 if name == "tp-layer" else 4096)
-        if name == "tp-layer":
+        s.add_argument("--tokens", type=int, default=2048 if name.startswith("tp-") else 1024)
+        s.add_argument("--hidden", type=int, default=8192 if name.startswith("tp-") else 4096)
+        if name.startswith("tp-"):
             s.add_argument("--k", type=int, default=1024)
             s.add_argument("--mode", type=int, default=1)
             s.add_argument("--reducers", type=int, default=0)
             s.add_argument("--two-sm", type=int, default=0)
+        if name == "tp-local":
+            s.add_argument("--one-kernel", type=int, default=1)
+            s.add_argument("--probe", type=int, default=0, help="diagnostic bits of the kernel (0 in production)")
         if name == "allreduce":
             s.add_argument("--mbytes", type=int, default=16)
             s.add_argument("--algo", default="rsag_zero_copy")
         if name == "moe":
             s.add_argument("--fp8", type=int, default=0)
     args = p.parse_args(argv)
-    {"tp-layer": tp_layer, "allreduce": allreduce, "moe": moe}[args.cmd](args)
+    {"tp-layer": tp_layer, "tp-local": tp_local, "allreduce": allreduce, "moe": moe}[args.cmd](args)
     return 0
 
 

@@ -310,12 +310,13 @@ PYBIND11_MODULE(_native, m) {
   m.def(
       "allreduce_ll",
       [](SymmetricHeap& heap, uintptr_t in, uintptr_t out, uint64_t bytes, DataType dtype, ReduceOp op, int nBlocks,
-         int nThreads, uintptr_t stream, bool nvls) {
+         int nThreads, uintptr_t stream, bool nvls, bool ll8) {
         CollArgs a = makeCollArgs(heap, in, out, bytes, kAllReduce, nvls);
+        a.ll8 = ll8 ? 1 : 0;
         checkCuda(launchAllreduceLL(a, dtype, op, nBlocks, nThreads, reinterpret_cast<cudaStream_t>(stream)), "allreduce_ll");
       },
       py::arg("heap"), py::arg("input"), py::arg("output"), py::arg("bytes"), py::arg("dtype"), py::arg("op") = SUM,
-      py::arg("n_blocks") = 8, py::arg("n_threads") = 512, py::arg("stream") = 0, py::arg("nvls") = false);
+      py::arg("n_blocks") = 8, py::arg("n_threads") = 512, py::arg("stream") = 0, py::arg("nvls") = false, py::arg("ll8") = false);
   m.def(
       "allreduce_ll_rmsnorm",
       [](SymmetricHeap& heap, uintptr_t in, uintptr_t out, int rows, int hidden, DataType dtype, float eps,

@@ -149,16 +149,17 @@ void registerMoreBindings(py::module_& m) {
   m.def(
       "tp_local_fused",
       [](uintptr_t a, uintptr_t b, uintptr_t residual, uintptr_t h, uintptr_t out, uintptr_t gamma, uintptr_t workspace, int M, int N, int K,
-         float eps, int blockN, bool twoSm, uintptr_t status, uintptr_t stream) {
+         float eps, int blockN, bool twoSm, uintptr_t status, uintptr_t stream, int probe, uintptr_t stamps) {
         checkCudaMore(launchTpLocalFused(reinterpret_cast<const void*>(a), reinterpret_cast<const void*>(b), reinterpret_cast<const void*>(residual),
                                          reinterpret_cast<void*>(h), reinterpret_cast<void*>(out), reinterpret_cast<const void*>(gamma),
                                          reinterpret_cast<void*>(workspace), M, N, K, eps, blockN, twoSm,
-                                         reinterpret_cast<DeviceStatus*>(status), reinterpret_cast<cudaStream_t>(stream)),
+                                         reinterpret_cast<DeviceStatus*>(status), reinterpret_cast<cudaStream_t>(stream), probe,
+                                         reinterpret_cast<unsigned long long*>(stamps)),
                       "tp_local_fused");
       },
       py::arg("a"), py::arg("b"), py::arg("residual"), py::arg("h"), py::arg("out"), py::arg("gamma"), py::arg("workspace"), py::arg("m"),
       py::arg("n"), py::arg("k"), py::arg("eps") = 1e-5f, py::arg("block_n") = 256, py::arg("two_sm") = false, py::arg("status") = 0,
-      py::arg("stream") = 0);
+      py::arg("stream") = 0, py::arg("probe") = 0, py::arg("stamps") = 0);
   m.def(
       "tp_scale_rows_from_sumsq",
       [](uintptr_t h, uintptr_t sumsq, uintptr_t gamma, uintptr_t out, int M, int N, float eps, uintptr_t stream) {

@@ -5,6 +5,7 @@
 #include <cstdint>
 
 #include <mscclpp/device/symm.cuh>
+#include <mscclpp/fifo_device.hpp>
 
 #include <mscclpp/npkit/npkit_struct.hpp>
 
@@ -53,7 +54,7 @@ constexpr int kExecMaxBarriers = 32;
 constexpr int kExecMaxRanksInGroup = 16;
 
 // One buffer range. `offset` is a HEAP offset (payload space); packet-space operands are expanded by the
-// kernel (scratch base + 2 x payload offset for LL16).
+// kernel (scratch base + 2 x payload offset, for LL16 and LL8 alike).
 struct DevOperand {
   uint64_t offset;      // heap offset of the first byte (payload space)
   uint64_t size;        // bytes (payload space)
@@ -116,6 +117,35 @@ struct DevPlan {
   const DevOp* ops;       // device array
 };
 
+// Request of a port-channel operation to the executor's host proxy (one 16-byte FIFO trigger):
+//   fst: source heap offset [0,40) | size low 20 bits [40,60) | issuing rank [60,64)
+//   snd: destination heap offset [0,40) | size high 8 bits [40,48) | channel id [48,56) | kind [56,59) | context [59,63)
+// (bit 63 of snd belongs to the FIFO). Sizes are bytes, at most kPortMaxBytes per request.
+constexpr uint64_t kPortMaxBytes = (1ull << 28) - 16;
+constexpr uint32_t kPortData = 1, kPortSignal = 2, kPortSync = 4;
+struct PortRequest {
+  uint64_t srcOff, dstOff, size;
+  uint32_t rank, channel, kind, context;
+};
+MSCCLPP_HOST_DEVICE_INLINE ProxyTrigger encodePortRequest(const PortRequest& r) {
+  ProxyTrigger t;
+  t.fst = (r.srcOff & ((1ull << 40) - 1)) | ((r.size & 0xfffffull) << 40) | (static_cast<uint64_t>(r.rank & 15u) << 60);
+  t.snd = (r.dstOff & ((1ull << 40) - 1)) | (((r.size >> 20) & 0xffull) << 40) | (static_cast<uint64_t>(r.channel & 255u) << 48) |
+          (static_cast<uint64_t>(r.kind & 7u) << 56) | (static_cast<uint64_t>(r.context & 15u) << 59);
+  return t;
+}
+MSCCLPP_HOST_DEVICE_INLINE PortRequest decodePortRequest(const ProxyTrigger& t) {
+  PortRequest r;
+  r.srcOff = t.fst & ((1ull << 40) - 1);
+  r.size = ((t.fst >> 40) & 0xfffffull) | (((t.snd >> 40) & 0xffull) << 20);
+  r.rank = static_cast<uint32_t>(t.fst >> 60) & 15u;
+  r.dstOff = t.snd & ((1ull << 40) - 1);
+  r.channel = static_cast<uint32_t>(t.snd >> 48) & 255u;
+  r.kind = static_cast<uint32_t>(t.snd >> 56) & 7u;
+  r.context = static_cast<uint32_t>(t.snd >> 59) & 15u;
+  return r;
+}
+
 struct ExecArgs {
   DeviceComm comm;
   const DevPlan* plans[kMaxRanks];  // [emulated rank]; real mode uses entry 0
@@ -123,6 +153,9 @@ struct ExecArgs {
   uint64_t scratchOff;   // heap offset of the scratch buffer (first half when double buffered)
   uint64_t scratchHalf;  // bytes of one scratch half (0 = no double buffering)
   int emuRanks;
+  int packetLL8;         // packet ops use 8-byte LL8 packets instead of 16-byte LL16 ones
+  int portContext;       // index of this plan context in the host proxy's table
+  FifoDeviceHandle portFifo;  // request queue of the executor's host proxy (triggers == nullptr: the plan has no port ops)
   NpKitEventCollectContext* npkit;  // tracer buffers, nullptr = tracing off
 };
 

@@ -3,7 +3,11 @@
 // src/core/include/execution_kernel.hpp:75-685), re-implemented on the symmetric heap:
 //   * operands are (rank, heap offset) pairs resolved by the host; peer memory is peerBase[rank] + offset;
 //   * channel signals are counters in the peer's ExecState; waits are bounded;
-//   * LL16 packets carry the launch epoch as flag, so scratch is never cleared;
+//   * port-channel put / signal / flush are REQUESTS to the executor's host proxy (a trigger in its FIFO, like the
+//     reference's port channels, src/core/include/execution_kernel.hpp:120-187): the proxy thread copies the bytes with
+//     the copy engines, writes the peer's signal word behind them and answers a flush when its stream has drained;
+//   * LL packets (16-byte LL16 or 8-byte LL8, chosen per launch like the reference's PacketType) carry the launch epoch as
+//     flag, so scratch is never cleared;
 //   * switch ops use multimem when the heap has a multicast mapping and fall back to a loop over the
 //     group's ranks otherwise (which is also how emulated ranks on one GPU run them);
 //   * float-like types reduce with an fp32 accumulator and round once per op; fp8 plans work (the
@@ -62,10 +66,41 @@ MSCCLPP_DEVICE_INLINE uint64_t sliced(const Ctx& x, const DevOp& op, const DevOp
 MSCCLPP_DEVICE_INLINE char* plainAddr(const Ctx& x, const DevOperand& o, uint64_t skip) {
   return reinterpret_cast<char*>(x.c->peerBase[o.rank] + o.offset + (o.isScratch ? x.half : 0) + skip);
 }
-// Packet space: scratch base + 2 x payload offset (an LL16 packet is 16 bytes for 8 bytes of payload).
-MSCCLPP_DEVICE_INLINE LL16Packet* pktAddr(const Ctx& x, const DevOperand& o, uint64_t skip, int rank) {
+// Packet space: scratch base + 2 x payload offset (both packet formats spend twice the payload: 16 bytes for 8, 8 for 4).
+template <typename Pkt>
+MSCCLPP_DEVICE_INLINE Pkt* pktAddr(const Ctx& x, const DevOperand& o, uint64_t skip, int rank) {
+  static_assert(sizeof(Pkt) == 2 * sizeof(typename Pkt::Payload), "packet space is twice the payload space");
   const uint64_t payloadOff = o.offset - x.a->scratchOff + skip;
-  return reinterpret_cast<LL16Packet*>(x.c->peerBase[rank] + x.a->scratchOff + x.half + 2 * payloadOff);
+  return reinterpret_cast<Pkt*>(x.c->peerBase[rank] + x.a->scratchOff + x.half + 2 * payloadOff);
+}
+
+// `count` payload words (4 bytes each) starting at packet `pk`, into / out of a zero-padded 16-byte vector.
+template <typename Pkt>
+MSCCLPP_DEVICE_INLINE bool readWords(const Pkt* pk, int words, uint32_t epoch, uint4& out, const Ctx& x, int src) {
+  uint32_t w[4] = {0, 0, 0, 0};
+  if constexpr (sizeof(typename Pkt::Payload) == 8) {
+    for (int i = 0; i < words / 2; i++) {
+      uint2 v;
+      if (!pk[i].read(epoch, v, x.c->status, x.c->timeoutNs, x.rank, src)) return false;
+      w[2 * i] = v.x;
+      w[2 * i + 1] = v.y;
+    }
+  } else {
+    for (int i = 0; i < words; i++) {
+      if (!pk[i].read(epoch, w[i], x.c->status, x.c->timeoutNs, x.rank, src)) return false;
+    }
+  }
+  out = make_uint4(w[0], w[1], w[2], w[3]);
+  return true;
+}
+template <typename Pkt>
+MSCCLPP_DEVICE_INLINE void writeWords(Pkt* pk, int words, uint4 v, uint32_t epoch) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  if constexpr (sizeof(typename Pkt::Payload) == 8) {
+    for (int i = 0; i < words / 2; i++) pk[i].write(w[2 * i], w[2 * i + 1], epoch);
+  } else {
+    for (int i = 0; i < words; i++) pk[i].write(w[i], epoch);
+  }
 }
 
 MSCCLPP_DEVICE_INLINE void signalChannels(const Ctx& x, const DevOp& op, bool relaxed) {
@@ -98,6 +133,58 @@ MSCCLPP_DEVICE_INLINE void waitChannels(Ctx& x, const DevOp& op, bool relaxed) {
   }
   __syncthreads();
   if (!waitOk) x.healthy = false;
+}
+
+// Port-channel operations: thread 0 queues one request per destination for the host proxy. kind: data and/or signal
+// and/or sync; with sync the thread also waits (bounded) until the proxy has consumed the request, which it does only
+// after its copy stream has drained.
+// packetSpace: both ends are packet-format scratch ranges (the bytes moved are the packets themselves, twice the payload).
+MSCCLPP_DEVICE_INLINE void portRequests(Ctx& x, const DevOp& op, uint32_t kind, bool packetSpace = false) {
+  __shared__ int portOk;
+  __syncthreads();  // data this block produced for the put is complete
+  if (threadIdx.x == 0) {
+    portOk = 1;
+    __threadfence_system();  // ... and visible to the copy engines
+    FifoDeviceHandle fifo = x.a->portFifo;
+    uint64_t last = UINT64_MAX;
+    const int n = (kind & kPortData) ? op.nDst : op.nIds;
+    for (int i = 0; i < n && portOk; i++) {
+      PortRequest r{};
+      r.rank = static_cast<uint32_t>(x.rank);
+      r.channel = op.ids[i < op.nIds ? i : 0];
+      r.context = static_cast<uint32_t>(x.a->portContext);
+      uint64_t left = 0, skip = 0;
+      if (kind & kPortData) {
+        const DevOperand& so = i < op.nSrc ? op.src[i] : op.src[0];
+        left = sliced(x, op, so, skip);
+        if (packetSpace) {
+          r.srcOff = x.a->scratchOff + x.half + 2 * (so.offset - x.a->scratchOff + skip);
+          r.dstOff = x.a->scratchOff + x.half + 2 * (op.dst[i].offset - x.a->scratchOff + skip);
+          left *= 2;
+        } else {
+          r.srcOff = so.offset + (so.isScratch ? x.half : 0) + skip;
+          r.dstOff = op.dst[i].offset + (op.dst[i].isScratch ? x.half : 0) + skip;
+        }
+      }
+      do {  // large puts go out in pieces; signal and sync ride on the last one
+        r.size = left > kPortMaxBytes ? kPortMaxBytes : left;
+        left -= r.size;
+        r.kind = left == 0 ? kind : kPortData;
+        if (r.size == 0) r.kind &= ~kPortData;
+        if (r.kind != 0) {
+          last = fifo.push(encodePortRequest(r), x.c->status, x.c->timeoutNs);
+          if (last == UINT64_MAX) portOk = 0;
+        }
+        r.srcOff += r.size;
+        r.dstOff += r.size;
+      } while (left != 0 && portOk);
+    }
+    if ((kind & kPortSync) && portOk && last != UINT64_MAX) {
+      if (!fifo.sync(last, x.c->status, x.c->timeoutNs)) portOk = 0;
+    }
+  }
+  __syncthreads();
+  if (!portOk) x.healthy = false;
 }
 
 // dst[k] (all of them) = sum over src[*]. Sizes are multiples of 16 bytes (plans align chunks to 16).
@@ -136,38 +223,51 @@ MSCCLPP_DEVICE_INLINE void reduceOp(const Ctx& x, const DevOp& op) {
 
 // Packet flavours of reduce: plain src[0] (+) packets src[1..] -> plain dst[0]; optionally the result as a
 // packet into local dst[1] (copy variants) and as packets into the remaining (remote) destinations.
-template <typename T>
+template <typename T, typename Pkt>
 MSCCLPP_DEVICE_INLINE void reducePacketsOp(Ctx& x, const DevOp& op, bool copyPacket) {
   uint64_t skip;
   const uint64_t bytes = sliced(x, op, op.src[0], skip);
-  const uint64_t npkt = bytes / 8;
-  const uint64_t npair = npkt / 2;  // work in 16-byte units = two packets, so the reduction runs on full vectors
+  constexpr int kPktPer16 = 16 / static_cast<int>(sizeof(typename Pkt::Payload));
+  const uint64_t nvec = bytes / 16;  // full 16-byte units: the reduction runs on whole vectors
+  // what is left after them is a whole number of payloads (a trailing 8-byte packet with LL16, up to three 4-byte ones
+  // with LL8): thread 0 takes it through a zero-padded vector
+  const int tailWords = static_cast<int>((bytes - nvec * 16) / 4);
   bool ok = true;
-  for (uint64_t i = threadIdx.x; i < npair && ok; i += blockDim.x) {
+  auto unit = [&](uint64_t i, int words) {
     ExecAccum<T> acc;
-    acc.init(*reinterpret_cast<const uint4*>(plainAddr(x, op.src[0], skip) + i * 16));
-    for (int s = 1; s < op.nSrc && ok; s++) {
-      const LL16Packet* pk = pktAddr(x, op.src[s], skip, x.rank) + 2 * i;
-      uint2 lo, hi;
-      ok = pk[0].read(x.epoch, lo, x.c->status, x.c->timeoutNs, x.rank, s) && pk[1].read(x.epoch, hi, x.c->status, x.c->timeoutNs, x.rank, s);
-      if (ok) acc.add(make_uint4(lo.x, lo.y, hi.x, hi.y));
+    const char* srcp = plainAddr(x, op.src[0], skip) + i * 16;
+    uint4 own;
+    if (words == 4) {
+      own = *reinterpret_cast<const uint4*>(srcp);
+    } else {
+      uint32_t w[4] = {0, 0, 0, 0};
+      for (int k = 0; k < words; k++) w[k] = reinterpret_cast<const uint32_t*>(srcp)[k];
+      own = make_uint4(w[0], w[1], w[2], w[3]);
     }
-    if (!ok) break;
+    acc.init(own);
+    for (int s = 1; s < op.nSrc && ok; s++) {
+      uint4 v;
+      ok = readWords<Pkt>(pktAddr<Pkt>(x, op.src[s], skip, x.rank) + kPktPer16 * i, words, x.epoch, v, x, s);
+      if (ok) acc.add(v);
+    }
+    if (!ok) return;
     const uint4 r = acc.result();
-    *reinterpret_cast<uint4*>(plainAddr(x, op.dst[0], skip) + i * 16) = r;
+    char* dstp = plainAddr(x, op.dst[0], skip) + i * 16;
+    if (words == 4) {
+      *reinterpret_cast<uint4*>(dstp) = r;
+    } else {
+      const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+      for (int k = 0; k < words; k++) reinterpret_cast<uint32_t*>(dstp)[k] = w[k];
+    }
     int d = 1;
     if (copyPacket && op.nDst > 1) {
-      LL16Packet* pk = pktAddr(x, op.dst[1], skip, x.rank) + 2 * i;
-      pk[0].write(r.x, r.y, x.epoch);
-      pk[1].write(r.z, r.w, x.epoch);
+      writeWords<Pkt>(pktAddr<Pkt>(x, op.dst[1], skip, x.rank) + kPktPer16 * i, words, r, x.epoch);
       d = 2;
     }
-    for (; d < op.nDst; d++) {
-      LL16Packet* pk = pktAddr(x, op.dst[d], skip, op.dst[d].rank) + 2 * i;
-      pk[0].write(r.x, r.y, x.epoch);
-      pk[1].write(r.z, r.w, x.epoch);
-    }
-  }
+    for (; d < op.nDst; d++) writeWords<Pkt>(pktAddr<Pkt>(x, op.dst[d], skip, op.dst[d].rank) + kPktPer16 * i, words, r, x.epoch);
+  };
+  for (uint64_t i = threadIdx.x; i < nvec && ok; i += blockDim.x) unit(i, 4);
+  if (ok && tailWords != 0 && threadIdx.x == 0) unit(nvec, tailWords);
   if (!ok) x.healthy = false;
 }
 
@@ -202,8 +302,9 @@ MSCCLPP_DEVICE_INLINE void switchStore(const Ctx& x, const DevOperand& o, uint64
     ptx::st_na_v4(reinterpret_cast<void*>(x.c->peerBase[g.ranks[i]] + o.offset + (o.isScratch ? x.half : 0) + byteOff), v);
 }
 
-template <typename T>
+template <typename T, typename Pkt>
 MSCCLPP_DEVICE_INLINE void execOp(Ctx& x, const DevOp& op) {
+  using Payload = typename Pkt::Payload;
   const OpType type = static_cast<OpType>(op.type);
   uint64_t skip = 0;
   switch (type) {
@@ -234,10 +335,12 @@ MSCCLPP_DEVICE_INLINE void execOp(Ctx& x, const DevOp& op) {
       break;
     }
     case OpType::SIGNAL:
-      signalChannels(x, op, false);
+      if (op.channelType == 1 && x.a->portFifo.triggers != nullptr) portRequests(x, op, kPortSignal);
+      else signalChannels(x, op, false);
       break;
     case OpType::RELAXED_SIGNAL:
-      signalChannels(x, op, true);
+      if (op.channelType == 1 && x.a->portFifo.triggers != nullptr) portRequests(x, op, kPortSignal);
+      else signalChannels(x, op, true);
       break;
     case OpType::WAIT:
       waitChannels(x, op, false);
@@ -246,10 +349,16 @@ MSCCLPP_DEVICE_INLINE void execOp(Ctx& x, const DevOp& op) {
       waitChannels(x, op, true);
       break;
     case OpType::FLUSH:
-      break;  // port-channel data is moved by this kernel's own stores: nothing is pending on a proxy
+      // everything this rank asked of the proxy so far has been carried out when this returns
+      if (x.a->portFifo.triggers != nullptr) portRequests(x, op, kPortSync);
+      break;
     case OpType::PUT:
     case OpType::PUT_WITH_SIGNAL:
     case OpType::PUT_WITH_SIGNAL_AND_FLUSH:
+      if (op.channelType == 1 && x.a->portFifo.triggers != nullptr) {
+        portRequests(x, op, kPortData | (type != OpType::PUT ? kPortSignal : 0u) | (type == OpType::PUT_WITH_SIGNAL_AND_FLUSH ? kPortSync : 0u));
+        break;
+      }
       for (int i = 0; i < op.nDst; i++) {
         const uint64_t n = sliced(x, op, op.src[i], skip);
         copyBytes(plainAddr(x, op.dst[i], skip), plainAddr(x, op.src[i], skip), n, threadIdx.x, blockDim.x);
@@ -273,33 +382,52 @@ MSCCLPP_DEVICE_INLINE void execOp(Ctx& x, const DevOp& op) {
       reduceOp<T>(x, op);
       break;
     case OpType::PUT_PACKETS:
+      // over a port channel the source is packet-format scratch that this block completed earlier: the proxy moves the
+      // packets as they are (the reference makes the same assumption, src/core/include/execution_kernel.hpp:275-289)
+      if (op.channelType == 1 && x.a->portFifo.triggers != nullptr && op.src[0].isScratch) {
+        portRequests(x, op, kPortData, true);
+        break;
+      }
       for (int i = 0; i < op.nDst; i++) {
         const DevOperand& s = i < op.nSrc ? op.src[i] : op.src[0];
         const uint64_t n = sliced(x, op, s, skip);
-        copyToPackets<LL16Packet>(pktAddr(x, op.dst[i], skip, op.dst[i].rank), plainAddr(x, s, skip), n, threadIdx.x, blockDim.x, x.epoch);
+        copyToPackets<Pkt>(pktAddr<Pkt>(x, op.dst[i], skip, op.dst[i].rank), plainAddr(x, s, skip), n, threadIdx.x, blockDim.x, x.epoch);
       }
       break;
     case OpType::READ_PUT_PACKETS: {
-      const uint64_t n = sliced(x, op, op.src[0], skip) / 8;
-      const LL16Packet* in = pktAddr(x, op.src[0], skip, x.rank);
+      const uint64_t n = sliced(x, op, op.src[0], skip) / sizeof(Payload);
+      const Pkt* in = pktAddr<Pkt>(x, op.src[0], skip, x.rank);
       bool ok = true;
+      if (op.channelType == 1 && x.a->portFifo.triggers != nullptr) {
+        // wait until every local packet of the range has arrived, then let the proxy forward the packets unchanged
+        for (uint64_t i = threadIdx.x; i < n && ok; i += blockDim.x) {
+          Payload v;
+          ok = in[i].read(x.epoch, v, x.c->status, x.c->timeoutNs, x.rank, 0);
+        }
+        if (!__syncthreads_and(ok ? 1 : 0)) {
+          x.healthy = false;
+          break;
+        }
+        portRequests(x, op, kPortData, true);
+        break;
+      }
       for (uint64_t i = threadIdx.x; i < n && ok; i += blockDim.x) {
-        uint2 v;
+        Payload v;
         ok = in[i].read(x.epoch, v, x.c->status, x.c->timeoutNs, x.rank, 0);
         if (!ok) break;
-        for (int d = 0; d < op.nDst; d++) pktAddr(x, op.dst[d], skip, op.dst[d].rank)[i].write(v, x.epoch);
+        for (int d = 0; d < op.nDst; d++) pktAddr<Pkt>(x, op.dst[d], skip, op.dst[d].rank)[i].write(v, x.epoch);
       }
       if (!ok) x.healthy = false;
       break;
     }
     case OpType::COPY_PACKETS: {
       const uint64_t n = sliced(x, op, op.src[0], skip);
-      copyToPackets<LL16Packet>(pktAddr(x, op.dst[0], skip, x.rank), plainAddr(x, op.src[0], skip), n, threadIdx.x, blockDim.x, x.epoch);
+      copyToPackets<Pkt>(pktAddr<Pkt>(x, op.dst[0], skip, x.rank), plainAddr(x, op.src[0], skip), n, threadIdx.x, blockDim.x, x.epoch);
       break;
     }
     case OpType::UNPACK_PACKETS: {
       const uint64_t n = sliced(x, op, op.src[0], skip);
-      if (!copyFromPackets<LL16Packet>(plainAddr(x, op.dst[0], skip), pktAddr(x, op.src[0], skip, x.rank), n, threadIdx.x, blockDim.x,
+      if (!copyFromPackets<Pkt>(plainAddr(x, op.dst[0], skip), pktAddr<Pkt>(x, op.src[0], skip, x.rank), n, threadIdx.x, blockDim.x,
                                        x.epoch, x.c->status, x.c->timeoutNs)) {
         x.healthy = false;
       }
@@ -307,11 +435,11 @@ MSCCLPP_DEVICE_INLINE void execOp(Ctx& x, const DevOp& op) {
     }
     case OpType::REDUCE_PACKETS:
     case OpType::REDUCE_SEND_PACKETS:
-      reducePacketsOp<T>(x, op, false);
+      reducePacketsOp<T, Pkt>(x, op, false);
       break;
     case OpType::REDUCE_COPY_PACKETS:
     case OpType::REDUCE_COPY_SEND_PACKETS:
-      reducePacketsOp<T>(x, op, true);
+      reducePacketsOp<T, Pkt>(x, op, true);
       break;
     case OpType::GROUP_LOAD_REDUCE_STORE: {
       const uint64_t n = sliced(x, op, op.src[0], skip) / 16;
@@ -328,20 +456,24 @@ MSCCLPP_DEVICE_INLINE void execOp(Ctx& x, const DevOp& op) {
       break;
     }
     case OpType::GROUP_STORE_PACKETS: {
-      const uint64_t n = sliced(x, op, op.src[0], skip) / 8;
-      const LL16Packet* in = pktAddr(x, op.src[0], skip, x.rank);
+      const uint64_t n = sliced(x, op, op.src[0], skip) / sizeof(Payload);
+      const Pkt* in = pktAddr<Pkt>(x, op.src[0], skip, x.rank);
       const DevGroup& g = x.plan->groups[op.dst[0].switchGroup];
       bool ok = true;
       for (uint64_t i = threadIdx.x; i < n && ok; i += blockDim.x) {
-        uint2 v;
+        Payload v;
         ok = in[i].read(x.epoch, v, x.c->status, x.c->timeoutNs, x.rank, 0);
         if (!ok) break;
         if (x.c->mcBase != 0) {
           const uint64_t payloadOff = op.dst[0].offset - x.a->scratchOff + skip;
-          ptx::multimem_st_v4(reinterpret_cast<void*>(x.c->mcBase + x.a->scratchOff + x.half + 2 * payloadOff + i * 16),
-                              make_uint4(v.x, x.epoch, v.y, x.epoch));
+          void* mc = reinterpret_cast<void*>(x.c->mcBase + x.a->scratchOff + x.half + 2 * payloadOff + i * sizeof(Pkt));
+          if constexpr (sizeof(Payload) == 8) {
+            ptx::multimem_st_v4(mc, make_uint4(v.x, x.epoch, v.y, x.epoch));
+          } else {
+            ptx::multimem_st_v2(mc, make_uint2(v, x.epoch));
+          }
         } else {
-          for (int r = 0; r < g.nRanks; r++) pktAddr(x, op.dst[0], skip, g.ranks[r])[i].write(v, x.epoch);
+          for (int r = 0; r < g.nRanks; r++) pktAddr<Pkt>(x, op.dst[0], skip, g.ranks[r])[i].write(v, x.epoch);
         }
       }
       if (!ok) x.healthy = false;
@@ -388,12 +520,12 @@ MSCCLPP_DEVICE_INLINE void execOp(Ctx& x, const DevOp& op) {
 }
 
 // One operation with its entry/exit trace events (thread 0; the cost is one predictable branch when tracing is off).
-template <typename T>
+template <typename T, typename Pkt>
 MSCCLPP_DEVICE_INLINE void tracedOp(Ctx& x, const DevOp& op) {
   NpKitEventCollectContext* trace = x.a->npkit;
   if (trace != nullptr && threadIdx.x == 0)
     npkitCollectGpuEvent(trace, NPKIT_EVENT_EXECUTOR_OP_BASE_ENTRY + op.type, static_cast<uint32_t>(op.nSrc ? op.src[0].size : 0), x.rank);
-  execOp<T>(x, op);
+  execOp<T, Pkt>(x, op);
   if (trace != nullptr) {
     // the exit stamp is taken when the whole block is done with the operation; the vote also keeps the
     // health flag uniform, so that every thread leaves the operation loop at the same place
@@ -403,7 +535,7 @@ MSCCLPP_DEVICE_INLINE void tracedOp(Ctx& x, const DevOp& op) {
   }
 }
 
-template <typename T>
+template <typename T, typename Pkt>
 __global__ void __launch_bounds__(1024, 1) executionKernel(ExecArgs a) {
   const DeviceComm& c = a.comm;
   const int rank = deviceRank(c);
@@ -444,14 +576,14 @@ __global__ void __launch_bounds__(1024, 1) executionKernel(ExecArgs a) {
         x.pipeUnit = op.arg1;
         for (uint32_t it = 0; it < op.arg0 && x.healthy; it++) {
           x.pipeOff = static_cast<uint64_t>(it) * op.arg1;
-          for (uint32_t k = i + 1; k < end && x.healthy; k++) tracedOp<T>(x, ops[k]);
+          for (uint32_t k = i + 1; k < end && x.healthy; k++) tracedOp<T, Pkt>(x, ops[k]);
         }
         x.pipeUnit = 0;
         x.pipeOff = 0;
         i = end + 1;
         continue;
       }
-      tracedOp<T>(x, op);
+      tracedOp<T, Pkt>(x, op);
       i++;
     }
   }
@@ -478,7 +610,15 @@ cudaError_t launchTyped(const ExecArgs& args, int nBlocks, int nThreads, cudaStr
   // thread blocks of a plan wait on one another (barriers, semaphores) and on peers: co-residency is required
   ExecArgs copy = args;
   void* params[] = {&copy};
-  return cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(executionKernel<T>), grid, block, params, 0, stream);
+  const void* kernel = args.packetLL8 ? reinterpret_cast<const void*>(executionKernel<T, LL8Packet>)
+                                      : reinterpret_cast<const void*>(executionKernel<T, LL16Packet>);
+  // every block of the launch has to be resident at once: say so here, with numbers, instead of leaving it to the launch
+  int perSm = 0, sms = 0, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess &&
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, kernel, nThreads, 0) == cudaSuccess) {
+    if (static_cast<long long>(perSm) * sms < static_cast<long long>(grid.x) * grid.y) return cudaErrorCooperativeLaunchTooLarge;
+  }
+  return cudaLaunchCooperativeKernel(kernel, grid, block, params, 0, stream);
 }
 
 }  // namespace

@@ -5,12 +5,16 @@
 #include <mscclpp/npkit/npkit.hpp>
 
 #include <algorithm>
+#include <atomic>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <unordered_map>
 
 #include <mscclpp/env.hpp>
 #include <mscclpp/gpu_utils.hpp>
+#include <mscclpp/numa.hpp>
+#include <mscclpp/proxy.hpp>
 
 #include "../core/json.hpp"
 #include "../core/logger.hpp"
@@ -170,6 +174,7 @@ struct Resolved {
   std::vector<DevOp> ops;
   DevPlan plan{};
   uint64_t scratchBytes = 0;  // one half
+  bool usesPort = false;      // the plan has port-channel operations: its launches need the executor's host proxy
 };
 
 struct Layout {
@@ -197,6 +202,7 @@ class Resolver {
       out.plan.tbs[t].opEnd = static_cast<uint32_t>(out.ops.size());
     }
     out.plan.nOps = static_cast<uint32_t>(out.ops.size());
+    out.usesPort = usesPort_;
     for (int t = 0; t < 2; t++) {
       const auto& m = p_.mates[t][rank_];
       for (size_t c = 0; c < m.size(); c++) out.plan.channels[t][c] = m[c];
@@ -314,6 +320,7 @@ class Resolver {
       d.inPipeline = inPipeline ? 1 : 0;
       const std::string ctype = op.contains("channel_type") ? op.at("channel_type").asString() : "";
       d.channelType = ctype == "port" ? 1 : 0;
+      if (d.channelType == 1) usesPort_ = true;
       if (op.contains("src_buff")) {
         const json::Value& src = op.at("src_buff");
         if (src.size() > static_cast<size_t>(kExecMaxOperands)) throw Error("plan '" + p_.name + "': too many sources in one op", ErrorCode::ExecutorError);
@@ -353,6 +360,7 @@ class Resolver {
 
   const ExecutionPlan::Impl& p_;
   int rank_;
+  bool usesPort_ = false;
   Layout l_;
   const json::Value* gpu_ = nullptr;
   const json::Value* tb_ = nullptr;
@@ -386,8 +394,111 @@ struct Executor::Impl {
     std::vector<DevOp*> devOps;
     std::vector<DevPlan*> devPlans;
     int maxThreadBlocks = 0;
+    // port channels: what the host proxy needs to carry out a request of this context
+    bool usesPort = false;
+    int portIndex = -1;                                    // slot in Impl::portTable
+    std::vector<std::vector<DevChannel>> portChannels;     // [local (emulated) rank][channel] -> peer, mate
+    std::vector<std::vector<uint64_t>> portSignalsSent;    // [local rank][channel]: value last written to the peer's word
   };
   std::map<std::string, Context> contexts;
+
+  // ---- host proxy for port-channel operations (the reference's executor owns a ProxyService the same way,
+  // src/core/executor/executor.cc:145-155): one thread drains the FIFO the interpreter kernel pushes requests into.
+  static constexpr int kPortContexts = 16;
+  static constexpr int kSignalRing = 1024;
+  std::unique_ptr<Proxy> proxy;
+  cudaStream_t proxyStream = nullptr;
+  uint64_t* signalRing = nullptr;  // pinned host words, one per signal in flight
+  uint64_t signalsIssued = 0;
+  Context* portTable[kPortContexts] = {};
+  std::mutex portMutex;            // portTable is written by execute() and read by the proxy thread
+  std::atomic<bool> proxyFailed{false};
+  std::string proxyError;
+
+  void failProxy(const std::string& what) {
+    // Remember the failure for the next execute() and poison the device status, so that kernels waiting for a signal or a
+    // flush that will never be honoured give up at once instead of running out their budget.
+    {
+      std::lock_guard<std::mutex> lock(portMutex);
+      if (proxyError.empty()) proxyError = what;
+    }
+    proxyFailed.store(true);
+    LOG_ERROR(LogSubsys::EXEC, "executor proxy: ", what);
+    DeviceStatus* st = heap->deviceComm().status;
+    if (st != nullptr) {
+      static const uint32_t one = 1;
+      (void)cudaMemcpy(&st->poisoned, &one, sizeof(one), cudaMemcpyHostToDevice);
+    }
+  }
+
+  ProxyHandlerResult handlePortRequest(ProxyTrigger trigger) {
+    const PortRequest r = decodePortRequest(trigger);
+    Context* ctx = nullptr;
+    {
+      std::lock_guard<std::mutex> lock(portMutex);
+      ctx = portTable[r.context % kPortContexts];
+    }
+    const int localRank = heap->emulated() ? static_cast<int>(r.rank) : 0;
+    if (ctx == nullptr || localRank >= static_cast<int>(ctx->portChannels.size()) ||
+        r.channel >= ctx->portChannels[localRank].size()) {
+      failProxy("request names an unknown context or channel");
+      return ProxyHandlerResult::Continue;
+    }
+    const DevChannel ch = ctx->portChannels[localRank][r.channel];
+    const int srcRank = heap->emulated() ? static_cast<int>(r.rank) : heap->rank();
+    char* srcBase = static_cast<char*>(heap->peerBase(srcRank));
+    char* dstBase = static_cast<char*>(heap->peerBase(ch.peer));
+    cudaError_t e = cudaSuccess;
+    if ((r.kind & kPortData) && r.size != 0) {
+      if (r.srcOff + r.size > heap->bytes() || r.dstOff + r.size > heap->bytes()) {
+        failProxy("request reaches beyond the heap");
+        return ProxyHandlerResult::Continue;
+      }
+      e = cudaMemcpyAsync(dstBase + r.dstOff, srcBase + r.srcOff, r.size, cudaMemcpyDeviceToDevice, proxyStream);
+    }
+    if (e == cudaSuccess && (r.kind & kPortSignal)) {
+      // the peer's signal word receives the running count, stream-ordered behind the data
+      if (signalsIssued != 0 && signalsIssued % kSignalRing == 0) e = cudaStreamSynchronize(proxyStream);  // ring slots are free again
+      if (e == cudaSuccess) {
+        uint64_t* slot = signalRing + signalsIssued % kSignalRing;
+        signalsIssued++;
+        *slot = ++ctx->portSignalsSent[localRank][r.channel];
+        ExecState* peerState = reinterpret_cast<ExecState*>(dstBase + (reinterpret_cast<char*>(ctx->state) - static_cast<char*>(heap->localBase())));
+        e = cudaMemcpyAsync(&peerState->inbound[1][ch.mate], slot, sizeof(uint64_t), cudaMemcpyHostToDevice, proxyStream);
+      }
+    }
+    if (e == cudaSuccess && (r.kind & kPortSync)) e = cudaStreamSynchronize(proxyStream);
+    if (e != cudaSuccess) failProxy(std::string("CUDA call failed: ") + cudaGetErrorString(e));
+    return ProxyHandlerResult::Continue;
+  }
+
+  void ensureProxy() {
+    if (proxy) return;
+    AvoidCudaGraphCaptureGuard guard;
+    int dev = 0;
+    MSCCLPP_CUDATHROW(cudaGetDevice(&dev));
+    MSCCLPP_CUDATHROW(cudaStreamCreateWithFlags(&proxyStream, cudaStreamNonBlocking));
+    MSCCLPP_CUDATHROW(cudaHostAlloc(reinterpret_cast<void**>(&signalRing), kSignalRing * sizeof(uint64_t), cudaHostAllocDefault));
+    proxy = std::make_unique<Proxy>([this](ProxyTrigger t) { return handlePortRequest(t); },
+                                    [dev] {
+                                      (void)cudaSetDevice(dev);
+                                      try {
+                                        numaBind(getDeviceNumaNode(dev));
+                                      } catch (const BaseError&) {
+                                        // best effort: the proxy works from any node
+                                      }
+                                    });
+    proxy->start();
+  }
+
+  void stopProxy() {
+    if (proxy) proxy->stop();
+    proxy.reset();
+    if (proxyStream) (void)cudaStreamDestroy(proxyStream);
+    if (signalRing) (void)cudaFreeHost(signalRing);
+    proxyStream = nullptr;
+    signalRing = nullptr;
+  }
 
   void freeDevPlans(Context& c) {
     for (auto p : c.devOps) detail::gpuFree(p);
@@ -397,6 +508,11 @@ struct Executor::Impl {
   }
 
   void freeContext(Context& c) {
+    {
+      std::lock_guard<std::mutex> lock(portMutex);
+      for (auto& slot : portTable)
+        if (slot == &c) slot = nullptr;
+    }
     freeDevPlans(c);
     if (c.state) heap->free(c.state);
     if (c.scratch) heap->free(c.scratch);
@@ -433,6 +549,7 @@ Executor::~Executor() {
       NpKit::Shutdown();
     }
     reset();
+    impl_->stopProxy();
   } catch (...) {
   }
 }
@@ -449,9 +566,12 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
                        const ExecutionPlan& plan, cudaStream_t stream, PacketType packetType) {
   SymmetricHeap& heap = *impl_->heap;
   const ExecutionPlan::Impl& p = *plan.impl_;
+  if (impl_->proxyFailed.load()) {
+    std::lock_guard<std::mutex> lock(impl_->portMutex);
+    throw Error("the executor's host proxy failed earlier: " + impl_->proxyError, ErrorCode::ExecutorError);
+  }
   if (!heap.emulated() && rank != heap.rank()) throw Error("Executor::execute: rank does not match the heap", ErrorCode::InvalidUsage);
   if (p.nRanks != heap.world()) throw Error("plan '" + p.name + "' is for " + std::to_string(p.nRanks) + " ranks, the heap has " + std::to_string(heap.world()), ErrorCode::ExecutorError);
-  if (packetType != PacketType::LL16) throw Error("this executor runs LL plans with LL16 packets only", ErrorCode::InvalidUsage);
   const json::Value& g0 = p.root.at("gpus").at(0);
   const uint64_t inChunks = g0.at("input_chunks").asUInt(), outChunks = g0.at("output_chunks").asUInt();
   Layout layout;
@@ -540,9 +660,14 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
     impl_->freeDevPlans(ctx);
     const int nPlans = heap.emulated() ? heap.world() : 1;
     ctx.maxThreadBlocks = 0;
+    ctx.usesPort = false;
+    ctx.portChannels.assign(nPlans, {});
+    if (ctx.portSignalsSent.size() != static_cast<size_t>(nPlans)) ctx.portSignalsSent.assign(nPlans, std::vector<uint64_t>(kExecMaxChannels, 0));
     for (int e = 0; e < nPlans; e++) {
       const int r = heap.emulated() ? e : heap.rank();
       Resolved res = Resolver(p, r, layout).run();
+      ctx.usesPort = ctx.usesPort || res.usesPort;
+      ctx.portChannels[e].assign(res.plan.channels[1], res.plan.channels[1] + kExecMaxChannels);
       DevOp* dops = static_cast<DevOp*>(detail::gpuCalloc(std::max<size_t>(1, res.ops.size()) * sizeof(DevOp)));
       if (!res.ops.empty()) gpuMemcpy(dops, res.ops.data(), res.ops.size() * sizeof(DevOp), cudaMemcpyHostToDevice);
       res.plan.ops = dops;
@@ -564,9 +689,33 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
   args.scratchOff = layout.scratchOff;
   args.scratchHalf = p.doubleScratch ? half : 0;
   args.emuRanks = heap.emulated() ? heap.world() : 1;
+  args.packetLL8 = packetType == PacketType::LL8 ? 1 : 0;
+  if (ctx.usesPort) {
+    impl_->ensureProxy();
+    std::lock_guard<std::mutex> lock(impl_->portMutex);
+    if (ctx.portIndex < 0) {
+      // a free slot, else the one of the least recently created context (sixteen plans with port channels at a time)
+      int slot = -1;
+      for (int i = 0; i < Impl::kPortContexts && slot < 0; i++)
+        if (impl_->portTable[i] == nullptr) slot = i;
+      if (slot < 0) throw Error("more than 16 plans with port channels are live on this executor: call reset()", ErrorCode::ExecutorError);
+      ctx.portIndex = slot;
+    }
+    impl_->portTable[ctx.portIndex] = &ctx;
+    args.portContext = ctx.portIndex;
+    args.portFifo = impl_->proxy->fifo()->deviceHandle();
+  }
   args.npkit = NpKit::GetGpuEventCollectContexts();
   if (ctx.maxThreadBlocks > 0) {
     cudaError_t e = launchExecutionKernel(args, dataType, ctx.maxThreadBlocks, p.nThreadsPerBlock, stream);
+    if (e == cudaErrorCooperativeLaunchTooLarge) {
+      (void)cudaGetLastError();
+      throw Error("plan '" + p.name + "' needs " + std::to_string(ctx.maxThreadBlocks) + " thread blocks of " + std::to_string(p.nThreadsPerBlock) +
+                      " threads" + (args.emuRanks > 1 ? " for each of " + std::to_string(args.emuRanks) + " emulated ranks" : std::string()) +
+                      " resident at the same time (its blocks wait on one another); this GPU cannot hold that many - use fewer thread "
+                      "blocks or fewer threads per block",
+                  ErrorCode::ExecutorError);
+    }
     if (e != cudaSuccess) throw CudaError("execution kernel launch failed for plan '" + p.name + "'", static_cast<int>(e));
   }
   if (out != recvbuff && recvbuff != nullptr) {

@@ -72,13 +72,14 @@ void gridFor(size_t bytes, bool nvls, int& blocks, int& threads) {
   else blocks = bytes < (8u << 20) ? 32 : (bytes < (64u << 20) ? 64 : 128);
 }
 
-std::shared_ptr<Algorithm> makeLL(const std::string& name, std::shared_ptr<SymmetricHeap> heap, bool nvls) {
+std::shared_ptr<Algorithm> makeLL(const std::string& name, std::shared_ptr<SymmetricHeap> heap, bool nvls, bool ll8 = false) {
   const size_t cap = heap->deviceComm().llSlotBytes / 2;
   return std::make_shared<NativeAlgorithm>(
       name, "allreduce", nullptr,
-      [heap, nvls](const void* in, void* out, size_t inBytes, size_t, DataType dtype, ReduceOp op, cudaStream_t stream, int nBlocks,
-                   int nThreads, bool, const std::unordered_map<std::string, uintptr_t>&) {
+      [heap, nvls, ll8](const void* in, void* out, size_t inBytes, size_t, DataType dtype, ReduceOp op, cudaStream_t stream, int nBlocks,
+                        int nThreads, bool, const std::unordered_map<std::string, uintptr_t>&) {
         CollArgs a = baseArgs(*heap, in, out, inBytes, kAllReduce, nvls);
+        a.ll8 = ll8 ? 1 : 0;
         const size_t units = (inBytes + 15) / 16;
         if (nThreads <= 0) nThreads = 512;
         if (nBlocks <= 0) nBlocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(56, (units + nThreads - 1) / nThreads)));
@@ -250,6 +251,7 @@ AlgorithmCollection AlgorithmCollectionBuilder::buildDefaultAlgorithms(std::shar
   staging->heap = heap;
   auto add = [&c](std::shared_ptr<Algorithm> a) { c.registerAlgorithm(a->collective(), a->name(), a); };
   add(makeLL("default_allreduce_packet", heap, false));
+  add(makeLL("default_allreduce_allpair_packet", heap, false, true));
   if (nvls) add(makeLL("default_allreduce_nvls_packet", heap, true));
   if (nvls) add(makeTwoShot("default_allreduce_nvls_zero_copy", "allreduce", heap, kAllReduce, true, false, staging));
   add(makeTwoShot("default_allreduce_rsag_zero_copy", "allreduce", heap, kAllReduce, false, false, staging));

@@ -144,6 +144,20 @@ MSCCLPP_DEVICE_INLINE uint4 ld_nc_na_v4(const void* p) {
                : "l"(p));
   return v;
 }
+// Weak 16-byte loads for LOCAL memory. ld_cg_v4 reads through L2 only: for data that other SMs wrote during this launch
+// and that was ordered by an acquire on a flag or counter. ld_input_v4 takes the non-coherent path without keeping the
+// line: for kernel inputs that nothing writes during the launch. Both pipeline freely (the system-scope relaxed load
+// above is a strong operation; a long run of them per thread was measured several times slower on local memory).
+MSCCLPP_DEVICE_INLINE uint4 ld_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+MSCCLPP_DEVICE_INLINE uint4 ld_input_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
 MSCCLPP_DEVICE_INLINE void st_na_v4(void* p, uint4 v) {
   asm volatile("st.global.relaxed.sys.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
                "r"(v.z), "r"(v.w));

@@ -30,7 +30,13 @@
  * different host threads) use the same intermediates and race: serialise them.
  *
  * The first call on each device looks up the device address of the array (cudaGetSymbolAddress) and
- * sets a function attribute. Make that first call outside of any stream capture.
+ * raises the kernel's shared-memory limit on that device (both are remembered per device, so a process
+ * that drives several GPUs pays this once on each). Make that first call outside of any stream capture.
+ *
+ * A device-side wait that runs out of time (every wait in the kernel is bounded) leaves out /
+ * residual_out partly unwritten although the launch itself succeeded. The kernel records that in an
+ * error block inside the array; mscclpp_b200_tp_layer_noalloc_status() copies the block out. The next
+ * call of the entry point clears it, so ask before calling again when a result looks wrong.
  *
  * Returns 0 on success, otherwise a cudaError_t value; when `err` is not NULL a description of the
  * failure is written there (at most err_len bytes, always terminated).
@@ -49,6 +55,12 @@ extern "C" {
 int mscclpp_b200_tp_layer_noalloc(const void* x, const void* w, const void* residual, const void* gamma, void* out,
                                   void* residual_out, int m, int n, int k, float eps, void* cuda_stream, char* err,
                                   size_t err_len);
+
+/* Copies the 64-byte error block of the current device's array into status_words[16] (waits for `cuda_stream`, i.e. for
+ * the calls queued on it so far). status_words[0] is 0 when no wait gave up; otherwise it is the kind of wait, words 2-5
+ * say where (rank, thread block, site, peer). Allocates nothing. Returns 0 when the block could be read. No counterpart
+ * in the reference. */
+int mscclpp_b200_tp_layer_noalloc_status(void* cuda_stream, unsigned int* status_words, char* err, size_t err_len);
 
 #ifdef __cplusplus
 }

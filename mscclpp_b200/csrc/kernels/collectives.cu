@@ -6,6 +6,9 @@
 //                        Role of the reference's allreduce_packet / allpair_packet / nvls_packet
 //                        (src/ext/collectives/allreduce/allreduce_packet.cu:15-151,
 //                         allreduce_allpair_packet.cu:15-69, allreduce_nvls_packet.cu:14-56).
+//                        With kLL8 the same exchange uses 8-byte {data, flag} packets (one 8-byte store each, the
+//                        format of the reference's all-pairs kernel, allreduce_allpair_packet.cu:15-69): twice the
+//                        stores per byte of payload, but each packet is a single naturally atomic access.
 //  * twoShotKernel       zero-copy reduce-scatter + all-gather in one pass: a rank reduces its 1/N of
 //                        the buffer straight out of all peers' inputs (peer loads or
 //                        multimem.ld_reduce) and writes the result into all peers' outputs (peer
@@ -124,8 +127,9 @@ MSCCLPP_DEVICE_INLINE uint4 scaleRow(uint4 x, float rinv, const char* gamma, uin
 // ============================================================================================
 // One-shot LL16 allreduce
 // ============================================================================================
-template <typename T, ReduceOp Op, bool kNvls, bool kNorm>
+template <typename T, ReduceOp Op, bool kNvls, bool kNorm, bool kLL8 = false>
 __global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
+  static_assert(!(kLL8 && (kNvls || kNorm)), "the 8-byte packet form is the plain peer-store exchange only");
   const DeviceComm& c = a.comm;
   const int rank = deviceRank(c);
   const int world = c.world;
@@ -150,6 +154,15 @@ __global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
         char* mc = reinterpret_cast<char*>(c.mcBase + bufOff + static_cast<uint64_t>(rank) * c.llSlotBytes + u * 32);
         ptx::multimem_st_v4(mc, make_uint4(d.x, flag, d.y, flag));
         ptx::multimem_st_v4(mc + 16, make_uint4(d.z, flag, d.w, flag));
+      } else if constexpr (kLL8) {
+        for (int i = 1; i < world; i++) {
+          const int p = (rank + i) % world;
+          LL8Packet* pk = reinterpret_cast<LL8Packet*>(c.peerBase[p] + bufOff + static_cast<uint64_t>(rank) * c.llSlotBytes + u * 32);
+          pk[0].write(d.x, flag);
+          pk[1].write(d.y, flag);
+          pk[2].write(d.z, flag);
+          pk[3].write(d.w, flag);
+        }
       } else {
         for (int i = 1; i < world; i++) {
           const int p = (rank + i) % world;
@@ -176,12 +189,20 @@ __global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
     for (int p = 0; p < world; p++) {
       uint4 v = own;
       if (p != rank) {
-        const LL16Packet* pk = reinterpret_cast<const LL16Packet*>(c.peerBase[rank] + bufOff +
-                                                                   static_cast<uint64_t>(p) * c.llSlotBytes + u * 32);
-        uint2 lo, hi;
-        if (!pk[0].read(flag, lo, c.status, c.timeoutNs, rank, p)) return false;
-        if (!pk[1].read(flag, hi, c.status, c.timeoutNs, rank, p)) return false;
-        v = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        if constexpr (kLL8) {
+          const LL8Packet* pk = reinterpret_cast<const LL8Packet*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * c.llSlotBytes + u * 32);
+          if (!pk[0].read(flag, v.x, c.status, c.timeoutNs, rank, p)) return false;
+          if (!pk[1].read(flag, v.y, c.status, c.timeoutNs, rank, p)) return false;
+          if (!pk[2].read(flag, v.z, c.status, c.timeoutNs, rank, p)) return false;
+          if (!pk[3].read(flag, v.w, c.status, c.timeoutNs, rank, p)) return false;
+        } else {
+          const LL16Packet* pk = reinterpret_cast<const LL16Packet*>(c.peerBase[rank] + bufOff +
+                                                                     static_cast<uint64_t>(p) * c.llSlotBytes + u * 32);
+          uint2 lo, hi;
+          if (!pk[0].read(flag, lo, c.status, c.timeoutNs, rank, p)) return false;
+          if (!pk[1].read(flag, hi, c.status, c.timeoutNs, rank, p)) return false;
+          v = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        }
       }
       if (p == 0) acc.init(v); else acc.add(v);
     }
@@ -444,12 +465,17 @@ cudaError_t launchMaybeCooperative(KernelT kernel, const CollArgs& args, int nBl
 template <typename T, ReduceOp Op>
 cudaError_t launchLLTyped(const CollArgs& a, int nBlocks, int nThreads, cudaStream_t s) {
   if (a.norm) {
+    if (a.ll8) return cudaErrorInvalidValue;
     if constexpr (IsFloatLike<T>::value && Op == SUM && sizeof(T) >= 2) {
       return a.nvls ? launchMaybeCooperative(allreduceLLKernel<T, Op, true, true>, a, nBlocks, nThreads, s)
                     : launchMaybeCooperative(allreduceLLKernel<T, Op, false, true>, a, nBlocks, nThreads, s);
     } else {
       return cudaErrorInvalidValue;
     }
+  }
+  if (a.ll8) {
+    if (a.nvls) return cudaErrorInvalidValue;
+    return launchMaybeCooperative(allreduceLLKernel<T, Op, false, false, true>, a, nBlocks, nThreads, s);
   }
   return a.nvls ? launchMaybeCooperative(allreduceLLKernel<T, Op, true, false>, a, nBlocks, nThreads, s)
                 : launchMaybeCooperative(allreduceLLKernel<T, Op, false, false>, a, nBlocks, nThreads, s);

@@ -31,6 +31,7 @@ struct CollArgs {
   const void* gamma;        // [hidden] (may be null = all ones)
   int broadcastResidual;    // two-shot only: write residualOut on every rank, not just the owner's rows
   int root;                 // kBroadcast: the rank whose `in` is copied into everybody's `out`
+  int ll8;                  // one-shot allreduce only: 8-byte {data, flag} packets instead of 16-byte ones (peer stores, no norm)
 };
 
 // One-shot LL16 allreduce (every rank sends its whole buffer to every peer as packets).

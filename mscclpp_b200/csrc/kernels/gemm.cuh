@@ -23,7 +23,13 @@ struct Shape {
   int probe;  // diagnostics, 0 in production: bit 0 = the producer issues no loads (stages are handed over empty), bit 1 = no
               // MMAs are issued (barriers only), bit 2 = the epilogue drops its blocks instead of storing them, bit 3 = it does not even read the accumulator. Timing the
               // kernel with each bit shows which of the three pipelines bounds a shape; results are then meaningless.
+  unsigned long long* stamps;  // optional time line, kStampWords words per CTA (null = off), all in globaltimer ns:
+                               // [0] CTA start, [1] last MMA issued, [2] ns the MMA thread waited for a free accumulator,
+                               // [3] ns it waited for operands, [4] epilogue warp 2: last tile part stored, [5] ns it
+                               // waited for a full accumulator, [6] ns it spent in Epilogue::block, [7] its drain done,
+                               // [8] ns the producer waited for a free stage; [9..15] belong to the epilogue
 };
+constexpr int kStampWords = 16;
 
 
 // Encodes a 2-D bf16 tensor map (row-major [rows, cols], 128-byte swizzle, box = [boxRows, 64]).

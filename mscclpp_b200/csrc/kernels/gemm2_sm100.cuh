@@ -226,6 +226,10 @@ MSCCLPP_DEVICE_INLINE void gemmCtaPair(const CUtensorMap* tmapA, const CUtensorM
     if constexpr (Epilogue::kBulkStore) {
       if (lane == 0) ptx::bulk_wait<0>();
     }
+  } else if (warp >= 2 + kNumEpilogueWarps) {
+    // warps beyond the ten of the GEMM roles (a kernel may launch more threads): follow-up work of a fused epilogue that
+    // must stay off the epilogue warps' critical path
+    epi.auxWarp(warp - (2 + kNumEpilogueWarps), lane);
   }
 
   // ---- teardown: both CTAs meet (the peer may still read my shared memory or signal my barriers until then)

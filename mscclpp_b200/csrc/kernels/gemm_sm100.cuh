@@ -223,6 +223,8 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
   const int numNBlk = shape.N / kBlockN;
   const int numTiles = numMBlk * numNBlk;
   const int numKBlk = shape.K / kBlockK;
+  unsigned long long* tl = shape.stamps != nullptr ? shape.stamps + static_cast<size_t>(blockIdx.x) * kStampWords : nullptr;
+  if (tl != nullptr && threadIdx.x == 0) tl[0] = ptx::globaltimer();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::kStages; s++) {
@@ -263,7 +265,13 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
         int aRow;
         const CUtensorMap* tmapARows = gate.tmapA(mBlk, tmapA, aRow);
         for (int kb = 0; kb < numKBlk && ok; kb++) {
-          ok = mbarWaitFast(&st.empty[stage], phase ^ 1u, status, budgetNs, 100 + stage, st.abortFlag);
+          if (tl != nullptr) {
+            const unsigned long long t0 = ptx::globaltimer();
+            ok = mbarWaitFast(&st.empty[stage], phase ^ 1u, status, budgetNs, 100 + stage, st.abortFlag);
+            tl[8] += ptx::globaltimer() - t0;
+          } else {
+            ok = mbarWaitFast(&st.empty[stage], phase ^ 1u, status, budgetNs, 100 + stage, st.abortFlag);
+          }
           if (!ok) break;
           uint8_t* sa = tiles + stage * Cfg::kStageBytes;
           uint8_t* sb = sa + Cfg::kStageABytes;
@@ -307,12 +315,24 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       for (int tile = ctaIdx; tile < numTiles && ok; tile += numCtas, it++) {
         const int acc = it & 1;
         const uint32_t accPhase = (it >> 1) & 1;
-        ok = mbarWaitFast(&st.tmemEmpty[acc], accPhase ^ 1u, status, budgetNs, 200 + acc, st.abortFlag);
+        if (tl != nullptr) {
+          const unsigned long long t0 = ptx::globaltimer();
+          ok = mbarWaitFast(&st.tmemEmpty[acc], accPhase ^ 1u, status, budgetNs, 200 + acc, st.abortFlag);
+          tl[2] += ptx::globaltimer() - t0;
+        } else {
+          ok = mbarWaitFast(&st.tmemEmpty[acc], accPhase ^ 1u, status, budgetNs, 200 + acc, st.abortFlag);
+        }
         if (!ok) break;
         ptx::tcgen05_fence_after_sync();
         const uint32_t tmemD = tmemBase + acc * kBlockN;
         for (int kb = 0; kb < numKBlk; kb++) {
-          ok = mbarWaitFast(&st.full[stage], phase, status, budgetNs, 300 + stage, st.abortFlag);
+          if (tl != nullptr) {
+            const unsigned long long t0 = ptx::globaltimer();
+            ok = mbarWaitFast(&st.full[stage], phase, status, budgetNs, 300 + stage, st.abortFlag);
+            tl[3] += ptx::globaltimer() - t0;
+          } else {
+            ok = mbarWaitFast(&st.full[stage], phase, status, budgetNs, 300 + stage, st.abortFlag);
+          }
           if (!ok) break;
           ptx::tcgen05_fence_after_sync();
           const uint64_t descA = descA0 + stage * kStageStep;
@@ -331,6 +351,7 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
         }
         if (ok) ptx::tcgen05_commit(&st.tmemFull[acc]);
       }
+      if (tl != nullptr) tl[1] = ptx::globaltimer();
       if (!ok) *st.abortFlag = 1;
     }
   } else if (warp < 2 + Cfg::kEpiWarps) {
@@ -349,13 +370,26 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       const int col0 = nBlk * kBlockN + part * Cfg::kColsPerWarp;
       // lets the epilogue put loads it will need (a residual, a bias) in flight while the MMAs of this tile still run
       epi.tileBegin(row0, col0, lane);
+      const bool stampIt = tl != nullptr && warp == 2 && lane == 0;
+      unsigned long long tw0 = 0;
+      if (stampIt) tw0 = ptx::globaltimer();
       ok = mbarWait(&st.tmemFull[acc], accPhase, status, budgetNs, 400 + acc);
       ok = __all_sync(0xffffffffu, ok) && (*st.abortFlag == 0);
       if (!ok) break;
+      if (stampIt) {
+        const unsigned long long now = ptx::globaltimer();
+        tl[5] += now - tw0;
+        tw0 = now;
+      }
       ptx::tcgen05_fence_after_sync();
       const uint32_t taddr = tmemBase + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kBlockN + part * Cfg::kColsPerWarp;
       // the accumulator buffer can be overwritten by the MMA warp as soon as every warp has read its part
       stagedEpilogueTile<Cfg::kColsPerWarp>(epi, taddr, stage, row0, col0, lane, [&] { ptx::mbar_arrive(&st.tmemEmpty[acc]); }, shape.probe);
+      if (stampIt) {
+        const unsigned long long now = ptx::globaltimer();
+        tl[6] += now - tw0;
+        tl[4] = now;
+      }
       if constexpr (Epilogue::kNeedsTileBarrier) {
         // All epilogue warps have issued their stores -> let the fused kernel publish the tile. The
         // meeting point is a counter with a bounded wait (not bar.sync): if one warp gave up on the
@@ -385,11 +419,16 @@ MSCCLPP_DEVICE_INLINE void gemmCta(const CUtensorMap* tmapA, const CUtensorMap* 
       epi.warpTileDone(mBlk, lane);
     }
     if (ok) epi.warpDrain(lane);  // follow-up work that is left once the warp has no tile of its own any more
+    if (tl != nullptr && warp == 2 && lane == 0) tl[7] = ptx::globaltimer();
     if (!ok && lane == 0) *st.abortFlag = 1;
     // bulk stores of this warp still read its staging buffer: the CTA must not end before they have
     if constexpr (Epilogue::kBulkStore) {
       if (lane == 0) ptx::bulk_wait<0>();
     }
+  } else if (warp >= 2 + kNumEpilogueWarps) {
+    // warps beyond the ten of the GEMM roles (a kernel may launch more threads): follow-up work of a fused epilogue that
+    // must stay off the epilogue warps' critical path
+    epi.auxWarp(warp - (2 + kNumEpilogueWarps), lane);
   }
 
   // ---- teardown: everybody meets, then the allocating warp frees TMEM
@@ -417,6 +456,7 @@ struct StoreBf16 {
   MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
   MSCCLPP_DEVICE_INLINE void warpTileDone(int, int) const {}
   MSCCLPP_DEVICE_INLINE void warpDrain(int) const {}
+  MSCCLPP_DEVICE_INLINE void auxWarp(int, int) const {}
 };
 
 }  // namespace gemm

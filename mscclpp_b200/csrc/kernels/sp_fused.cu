@@ -94,6 +94,7 @@ struct StoreAct {
   MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
   MSCCLPP_DEVICE_INLINE void warpTileDone(int, int) const {}
   MSCCLPP_DEVICE_INLINE void warpDrain(int) const {}
+  MSCCLPP_DEVICE_INLINE void auxWarp(int, int) const {}
 };
 
 constexpr uint32_t kPieceBytes = 32768;

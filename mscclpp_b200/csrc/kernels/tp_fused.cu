@@ -36,19 +36,48 @@ namespace {
 using bf16 = __nv_bfloat16;
 constexpr int kMaxNBlk = 128;
 
+// Packed bf16 arithmetic for the element-wise parts of the single-GPU layer. With a dozen warps per SM these loops are
+// bound by instruction latency, not by memory: one HADD2 / HMUL2 / HFMA2 per two elements instead of a convert - operate -
+// convert chain per element is what makes them fit in the shadow of the MMAs.
+MSCCLPP_DEVICE_INLINE __nv_bfloat162 asBf162(uint32_t w) { return *reinterpret_cast<__nv_bfloat162*>(&w); }
+MSCCLPP_DEVICE_INLINE uint32_t asWord(__nv_bfloat162 v) { return *reinterpret_cast<uint32_t*>(&v); }
+// a + b per element, each sum rounded once to bf16 (the adder works in fp32 internally: same result as an fp32 add + round)
+MSCCLPP_DEVICE_INLINE uint4 addBf16x8(uint4 a, uint4 b) {
+  return make_uint4(asWord(__hadd2(asBf162(a.x), asBf162(b.x))), asWord(__hadd2(asBf162(a.y), asBf162(b.y))),
+                    asWord(__hadd2(asBf162(a.z), asBf162(b.z))), asWord(__hadd2(asBf162(a.w), asBf162(b.w))));
+}
+MSCCLPP_DEVICE_INLINE float sumSquaresBf16x8(uint4 v) {
+  const float2 a = __bfloat1622float2(asBf162(v.x)), b = __bfloat1622float2(asBf162(v.y));
+  const float2 c = __bfloat1622float2(asBf162(v.z)), d = __bfloat1622float2(asBf162(v.w));
+  float s0 = a.x * a.x, s1 = b.x * b.x;
+  s0 = fmaf(a.y, a.y, s0);
+  s1 = fmaf(b.y, b.y, s1);
+  s0 = fmaf(c.x, c.x, s0);
+  s1 = fmaf(d.x, d.x, s1);
+  s0 = fmaf(c.y, c.y, s0);
+  s1 = fmaf(d.y, d.y, s1);
+  return s0 + s1;
+}
+// v * g * s with the fp32 scale s split into a bf16 head and a bf16 tail (s = hi + lo up to 2^-17 relative), so that the
+// result carries the two product roundings of bf16 arithmetic but not a third from rounding s itself.
+MSCCLPP_DEVICE_INLINE uint32_t scaleBf16x2(uint32_t v, uint32_t g, __nv_bfloat162 hi, __nv_bfloat162 lo, bool hasGamma) {
+  const __nv_bfloat162 p = hasGamma ? __hmul2(asBf162(v), asBf162(g)) : asBf162(v);
+  return asWord(__hfma2(p, lo, __hmul2(p, hi)));
+}
+
 struct TmapSet {
   CUtensorMap a[8];
   CUtensorMap b[8];
 };
 
-constexpr int kMaxMBlk = 4096;
+constexpr int kMaxMBlk = kTpMaxMBlk;
 // Aux flag region of every heap: [kMaxMBlk][kMaxRanks] epoch-stamped "row block of rank src is complete"
 // flags written by the producers, followed by kMaxMBlk local tile counters.
 MSCCLPP_DEVICE_INLINE uint32_t* readyFlag(const DeviceComm& c, int owner, int mBlk, int src) {
   return reinterpret_cast<uint32_t*>(c.peerBase[owner] + c.auxFlagsOff) + (static_cast<size_t>(mBlk) * kMaxRanks + src);
 }
 MSCCLPP_DEVICE_INLINE uint32_t* tileCounter(const DeviceComm& c, int rank, int mBlk) {
-  return reinterpret_cast<uint32_t*>(c.peerBase[rank] + c.auxFlagsOff) + static_cast<size_t>(kMaxMBlk) * kMaxRanks + mBlk;
+  return reinterpret_cast<uint32_t*>(c.peerBase[rank] + c.auxFlagsOff + kTpTileCounterOffset) + mBlk;
 }
 
 struct PartialStoreSignal {
@@ -121,6 +150,7 @@ struct PartialStoreSignal {
   }
   MSCCLPP_DEVICE_INLINE void warpTileDone(int, int) const {}
   MSCCLPP_DEVICE_INLINE void warpDrain(int) const {}
+  MSCCLPP_DEVICE_INLINE void auxWarp(int, int) const {}
 };
 
 // Reducer CTAs are split into independent groups of kGroupThreads threads; a group owns one row at a
@@ -516,15 +546,17 @@ struct ResidualSumsqStore {
   float* sumsq;          // [M]
   int M, N;
   int blocksPerWarp;  // 64-column blocks per warp and tile
+  int probe;          // diagnostics, 0 in production: bit 4 no residual loads, bit 5 no sum-of-squares atomics, bit 6 no h
+                      // stores, bit 7 no normalisation (results are then wrong; timing only)
   uint4 pre[8];       // residual words of the block that comes next
   MSCCLPP_DEVICE_INLINE static float convert(float x) { return x; }
   MSCCLPP_DEVICE_INLINE void prefetch(int row0, int col0, int lane) {
-    if (residual == nullptr) return;
+    if (residual == nullptr || (probe & 16)) return;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
       const int row = row0 + gemm::stagedRow(i, lane);
       pre[i] = make_uint4(0, 0, 0, 0);
-      if (row < M) pre[i] = ptx::ld_nc_na_v4(residual + static_cast<size_t>(row) * N + col0 + gemm::stagedCol(lane));
+      if (row < M) pre[i] = ptx::ld_input_v4(residual + static_cast<size_t>(row) * N + col0 + gemm::stagedCol(lane));
     }
   }
   MSCCLPP_DEVICE_INLINE void tileBegin(int row0, int col0, int lane) { prefetch(row0, col0, lane); }
@@ -536,26 +568,16 @@ struct ResidualSumsqStore {
 #pragma unroll
     for (int i = 0; i < 8; i++) {
       const int row = row0 + gemm::stagedRow(i, lane);
-      float f[8];
-      Vec16<bf16>::toFloat(gemm::stagedRead(stage, i, lane), f);
-      if (residual != nullptr) {
-        float r[8];
-        Vec16<bf16>::toFloat(res[i], r);
-#pragma unroll
-        for (int j = 0; j < 8; j++) f[j] += r[j];
-      }
-      const uint4 packed = Vec16<bf16>::fromFloat(f);
-      Vec16<bf16>::toFloat(packed, f);
-      float ss = 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; j++) ss += f[j] * f[j];
+      uint4 packed = gemm::stagedRead(stage, i, lane);
+      if (residual != nullptr) packed = addBf16x8(packed, res[i]);
+      float ss = sumSquaresBf16x8(packed);
       // the eight lanes that share a row
       ss += __shfl_xor_sync(0xffffffffu, ss, 1);
       ss += __shfl_xor_sync(0xffffffffu, ss, 2);
       ss += __shfl_xor_sync(0xffffffffu, ss, 4);
       if (row < M) {
-        *reinterpret_cast<uint4*>(h + static_cast<size_t>(row) * N + col0 + gemm::stagedCol(lane)) = packed;
-        if ((lane & 7) == 0) atomicAdd(sumsq + row, ss);
+        if (!(probe & 64)) *reinterpret_cast<uint4*>(h + static_cast<size_t>(row) * N + col0 + gemm::stagedCol(lane)) = packed;
+        if ((lane & 7) == 0 && !(probe & 32)) atomicAdd(sumsq + row, ss);
       }
     }
     __syncwarp();
@@ -563,6 +585,7 @@ struct ResidualSumsqStore {
   MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
   MSCCLPP_DEVICE_INLINE void warpTileDone(int, int) const {}
   MSCCLPP_DEVICE_INLINE void warpDrain(int) const {}
+  MSCCLPP_DEVICE_INLINE void auxWarp(int, int) const {}
 };
 
 // The whole single-GPU layer in ONE kernel: the epilogue of ResidualSumsqStore, plus the normalisation. Every epilogue
@@ -570,11 +593,14 @@ struct ResidualSumsqStore {
 // final (h stored, sums of squares added) and become units of follow-up work, two rows each, handed out in ascending
 // order from one counter. A warp takes at most one unit after each tile part (without ever waiting: a unit is only
 // taken when its block is already complete), so the normalisation of block i runs in the shadow of the MMAs of the
-// blocks after it and h is re-read from L2; after its last tile a warp drains what is left, now with bounded waits.
+// blocks after it and h is re-read from L2. The units are taken by kAuxWarps extra warps per CTA that have no other job
+// (an epilogue warp that stopped for a row would hold up the accumulator hand-over of its tile); the epilogue warps join
+// them after their last tile. All waits are bounded.
 struct ResidualNormStore {
   static constexpr bool kNeedsTileBarrier = false;
   static constexpr bool kBulkStore = false;
   static constexpr int kRowsPerUnit = 2;
+  static constexpr int kAuxWarps = 4;
   ResidualSumsqStore base;
   bf16* out;            // [M, N]
   const bf16* gamma;    // [N] or null
@@ -585,47 +611,50 @@ struct ResidualNormStore {
   DeviceStatus* status;
   uint64_t budgetNs;
   uint32_t pendingUnit;  // per thread (lane 0 of each epilogue warp): a claimed unit whose block was not complete yet
+  int pendingArrive;     // per thread: row block whose arrival this warp still owes (-1 = none)
+  unsigned long long* stamps;  // optional time line (gemm::Shape::stamps): words 9-12 of a CTA are its first extra warp's
+                               // units done, ns waited for blocks, ns spent normalising, finish time
   MSCCLPP_DEVICE_INLINE static float convert(float x) { return x; }
   MSCCLPP_DEVICE_INLINE void tileBegin(int row0, int col0, int lane) { base.tileBegin(row0, col0, lane); }
-  MSCCLPP_DEVICE_INLINE void block(const uint8_t* stage, int row0, int col0, int lane, int b) { base.block(stage, row0, col0, lane, b); }
+  MSCCLPP_DEVICE_INLINE void block(const uint8_t* stage, int row0, int col0, int lane, int b) {
+    if (b == 0) flushArrival(lane);  // the previous tile's arrival (see warpTileDone)
+    base.block(stage, row0, col0, lane, b);
+  }
   MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
 
   MSCCLPP_DEVICE_INLINE void normaliseRow(int row, int lane) const {
     const int N = base.N;
     const float rinv = rsqrtf(__ldcg(base.sumsq + row) / static_cast<float>(N) + eps);
+    const __nv_bfloat16 hi1 = __float2bfloat16_rn(rinv);
+    const __nv_bfloat162 hi = __bfloat162bfloat162(hi1);
+    const __nv_bfloat162 lo = __float2bfloat162_rn(rinv - __bfloat162float(hi1));
     const int words = N / 8;
     const uint4* src = reinterpret_cast<const uint4*>(base.h + static_cast<size_t>(row) * N);
     uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * N);
     const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
-    for (int w0 = lane; w0 < words; w0 += 32 * 8) {
-      uint4 v[8];
+    const bool hasGamma = gamma != nullptr;
+    constexpr int kDepth = 16;  // 16-byte loads in flight per lane
+    for (int w0 = lane; w0 < words; w0 += 32 * kDepth) {
+      uint4 v[kDepth];
 #pragma unroll
-      for (int k = 0; k < 8; k++) {
+      for (int k = 0; k < kDepth; k++) {
         const int w = w0 + 32 * k;
-        if (w < words) v[k] = ptx::ld_nc_na_v4(src + w);  // written by other SMs during this launch: never through L1
+        if (w < words) v[k] = ptx::ld_cg_v4(src + w);  // written by other SMs during this launch: through L2, never L1
       }
 #pragma unroll
-      for (int k = 0; k < 8; k++) {
+      for (int k = 0; k < kDepth; k++) {
         const int w = w0 + 32 * k;
         if (w < words) {
-          float f[8];
-          Vec16<bf16>::toFloat(v[k], f);
-          if (gamma != nullptr) {
-            float g[8];
-            Vec16<bf16>::toFloat(__ldg(g4 + w), g);
-#pragma unroll
-            for (int i = 0; i < 8; i++) f[i] = f[i] * rinv * g[i];
-          } else {
-#pragma unroll
-            for (int i = 0; i < 8; i++) f[i] = f[i] * rinv;
-          }
-          dst[w] = Vec16<bf16>::fromFloat(f);
+          const uint4 g = hasGamma ? __ldg(g4 + w) : make_uint4(0, 0, 0, 0);
+          dst[w] = make_uint4(scaleBf16x2(v[k].x, g.x, hi, lo, hasGamma), scaleBf16x2(v[k].y, g.y, hi, lo, hasGamma),
+                              scaleBf16x2(v[k].z, g.z, hi, lo, hasGamma), scaleBf16x2(v[k].w, g.w, hi, lo, hasGamma));
         }
       }
     }
   }
 
   MSCCLPP_DEVICE_INLINE void normaliseUnit(uint32_t u, int lane) const {
+    if (base.probe & 128) return;
     const int r0 = static_cast<int>(u) * kRowsPerUnit;
 #pragma unroll 1
     for (int r = r0; r < r0 + kRowsPerUnit && r < base.M; r++) normaliseRow(r, lane);
@@ -634,41 +663,37 @@ struct ResidualNormStore {
     return ptx::ld_acquire_gpu(blockCount + unit * kRowsPerUnit / gemm::kBlockM) >= fullCount;
   }
 
-  // Between tiles (never waits). A warp holds at most one claimed unit. It claims the next one - an atomic add, which
-  // cannot fail, so hundreds of warps do not pile up on one word - when the unit at the head of the queue belongs to a
-  // complete block; the unit it gets may lie a little further on, in a block that is not complete yet, and then stays
-  // with the warp until a later call (or the drain) finds its block complete.
-  MSCCLPP_DEVICE_INLINE void warpTileDone(int mBlk, int lane) {
-    constexpr uint32_t kNone = 0xffffffffu;
-    const uint32_t totalUnits = static_cast<uint32_t>((base.M + kRowsPerUnit - 1) / kRowsPerUnit);
+  // An epilogue warp only counts its finished part of a tile (normalising rows between tiles would sit on the critical
+  // path of the accumulator hand-over: the MMA waits for the slowest of the eight warps). The count needs a fence after
+  // the warp's h stores and sum-of-squares updates, and a fence right behind the stores waits out their whole latency;
+  // so the arrival for a tile is only NOTED here and made one tile later (flushArrival, called when the next tile's
+  // accumulator has been read), when those stores have long been performed and the fence returns at once.
+  MSCCLPP_DEVICE_INLINE void warpTileDone(int mBlk, int /*lane*/) { pendingArrive = mBlk; }
+  MSCCLPP_DEVICE_INLINE void flushArrival(int lane) {
+    if (pendingArrive < 0) return;
     __syncwarp();
-    uint32_t go = kNone;
     if (lane == 0) {
-      __threadfence();  // this warp's h stores and sum-of-squares updates, before the arrival that may complete the block
-      atomicAdd(blockCount + mBlk, 1u);
-      if (pendingUnit == kNone) {
-        const uint32_t head = ptx::ld_volatile(nextUnit);
-        if (head < totalUnits && blockComplete(head)) {
-          const uint32_t mine = atomicAdd(nextUnit, 1u);
-          if (mine < totalUnits) pendingUnit = mine;
-        }
-      }
-      if (pendingUnit != kNone && blockComplete(pendingUnit)) {
-        go = pendingUnit;
-        pendingUnit = kNone;
-      }
+      __threadfence();
+      atomicAdd(blockCount + pendingArrive, 1u);
     }
-    go = __shfl_sync(0xffffffffu, go, 0);
-    if (go != kNone) normaliseUnit(go, lane);
+    pendingArrive = -1;
+  }
+  // The extra warps of the launch do nothing but normalise: claim the next unit, wait (bounded) for its block, scale.
+  MSCCLPP_DEVICE_INLINE void auxWarp(int idx, int lane) {
+    drain(lane, (stamps != nullptr && idx == 0 && lane == 0) ? stamps + static_cast<size_t>(blockIdx.x) * gemm::kStampWords : nullptr);
   }
 
   // The warp has no tile left: finish the unit it holds, then claim and finish units until none is left. Waiting is
   // safe here (bounded all the same): what a block still lacks is produced by warps that do not depend on this one.
-  MSCCLPP_DEVICE_INLINE void warpDrain(int lane) {
+  MSCCLPP_DEVICE_INLINE void warpDrain(int lane) { drain(lane, nullptr); }
+  MSCCLPP_DEVICE_INLINE void drain(int lane, unsigned long long* tl) {
     constexpr uint32_t kNone = 0xffffffffu;
     const uint32_t totalUnits = static_cast<uint32_t>((base.M + kRowsPerUnit - 1) / kRowsPerUnit);
+    flushArrival(lane);  // the last tile's arrival
     for (;;) {
       uint32_t go = kNone;
+      unsigned long long t0 = 0;
+      if (tl != nullptr) t0 = ptx::globaltimer();
       if (lane == 0) {
         uint32_t mine = pendingUnit;
         pendingUnit = kNone;
@@ -691,14 +716,26 @@ struct ResidualNormStore {
         }
       }
       go = __shfl_sync(0xffffffffu, go, 0);
-      if (go == kNone) return;
+      unsigned long long t1 = 0;
+      if (tl != nullptr) {
+        t1 = ptx::globaltimer();
+        tl[10] += t1 - t0;
+      }
+      if (go == kNone) {
+        if (tl != nullptr) tl[12] = t1;
+        return;
+      }
       normaliseUnit(go, lane);
+      if (tl != nullptr) {
+        tl[11] += ptx::globaltimer() - t1;
+        tl[9] += 1;
+      }
     }
   }
 };
 
 template <int kBlockN>
-__global__ void __launch_bounds__(gemm::kNumThreads, 1)
+__global__ void __launch_bounds__(gemm::kNumThreads + 32 * ResidualNormStore::kAuxWarps, 1)
     tpLocalFusedKernel(const __grid_constant__ CUtensorMap tmapA, const __grid_constant__ CUtensorMap tmapB, gemm::Shape shape,
                        ResidualNormStore epi) {
   extern __shared__ uint8_t smemRaw[];
@@ -821,7 +858,6 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   if (N * 2 / 16 > kWordsPerThread * kGroupThreads) return cudaErrorInvalidValue;
   const int numMBlk = (M + gemm::kBlockM - 1) / gemm::kBlockM;
   if (numMBlk > kMaxMBlk) return cudaErrorInvalidValue;
-  static_assert(static_cast<uint64_t>(kMaxMBlk) * (kMaxRanks + 1) * 4 <= kAuxFlagBytes, "aux flag region too small");
   if (args.mode == 1 && args.rinv == nullptr) return cudaErrorInvalidValue;
   if (args.nvls && args.comm.mcBase == 0) return cudaErrorInvalidValue;
   const int emu = args.emuRanks > 1 ? args.emuRanks : 1;
@@ -967,6 +1003,8 @@ cudaError_t launchGemmResidualSumsq(const void* A, const void* B, const void* re
   }
 }
 
+constexpr int kLocalFusedThreads = gemm::kNumThreads + 32 * ResidualNormStore::kAuxWarps;
+
 template <int kBlockN>
 cudaError_t launchLocalFusedTyped(const CUtensorMap& ta, const CUtensorMap& tb, gemm::Shape shape, ResidualNormStore epi, cudaStream_t stream) {
   using Cfg = SmemOf<kBlockN>;
@@ -978,13 +1016,13 @@ cudaError_t launchLocalFusedTyped(const CUtensorMap& ta, const CUtensorMap& tb, 
     int grid = gemm::smCount() & ~1;
     if (grid > 2 * tiles) grid = 2 * tiles;
     void* params[] = {const_cast<CUtensorMap*>(&ta), const_cast<CUtensorMap*>(&tb), &shape, &epi};
-    return gemm::launchClusterPair(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(gemm::kNumThreads), Cfg::kSmemBytes, params, false,
-                                   stream);
+    return gemm::launchClusterPair(reinterpret_cast<const void*>(kernel), dim3(grid), dim3(kLocalFusedThreads), Cfg::kSmemBytes, params,
+                                   false, stream);
   } else {
     const int tiles = ((shape.M + gemm::kBlockM - 1) / gemm::kBlockM) * (shape.N / kBlockN);
     int grid = gemm::smCount();
     if (grid > tiles) grid = tiles;
-    kernel<<<grid, gemm::kNumThreads, Cfg::kSmemBytes, stream>>>(ta, tb, shape, epi);
+    kernel<<<grid, kLocalFusedThreads, Cfg::kSmemBytes, stream>>>(ta, tb, shape, epi);
     return cudaGetLastError();
   }
 }
@@ -996,7 +1034,8 @@ size_t tpLocalFusedWorkspaceBytes(int M) {
 }
 
 cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residual, void* h, void* out, const void* gamma, void* workspace,
-                               int M, int N, int K, float eps, int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream) {
+                               int M, int N, int K, float eps, int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream, int probe,
+                               unsigned long long* stamps) {
   if (M <= 0 || N <= 0 || K <= 0 || K % gemm::kBlockK != 0 || N % 8 != 0) return cudaErrorInvalidValue;
   if (twoSm && (M < gemm::Config2::kPairM || N % gemm::Config2::kBlockN != 0)) return cudaErrorInvalidValue;
   if (!twoSm && (blockN != 64 && blockN != 128 && blockN != 256)) return cudaErrorInvalidValue;
@@ -1007,7 +1046,7 @@ cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residua
   cudaError_t e = cudaMemsetAsync(workspace, 0, tpLocalFusedWorkspaceBytes(M), stream);
   if (e != cudaSuccess) return e;
   // row blocks are walked one after the other (all their N tiles first), so that they complete in order and early
-  gemm::Shape shape{M, N, K, M < gemm::kBlockM ? M : gemm::kBlockM, 1, 0, 0, 0};
+  gemm::Shape shape{M, N, K, M < gemm::kBlockM ? M : gemm::kBlockM, 1, 0, 0, probe & 15, stamps};
   if (twoSm) shape.aBoxRows = gemm::kBlockM;
   CUtensorMap ta, tb;
   e = gemm::makeTensorMapBf16(&ta, A, M, K, static_cast<uint64_t>(K) * 2, shape.aBoxRows);
@@ -1023,6 +1062,7 @@ cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residua
   epi.base.M = M;
   epi.base.N = N;
   epi.base.blocksPerWarp = tileN / (epiWarps / 4) / 64;
+  epi.base.probe = probe;
   epi.out = static_cast<bf16*>(out);
   epi.gamma = static_cast<const bf16*>(gamma);
   epi.blockCount = reinterpret_cast<uint32_t*>(static_cast<float*>(workspace) + M);
@@ -1032,6 +1072,8 @@ cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residua
   epi.status = status;
   epi.budgetNs = 2000000000ull;
   epi.pendingUnit = 0xffffffffu;
+  epi.pendingArrive = -1;
+  epi.stamps = stamps;
   if (twoSm) return launchLocalFusedTyped<0>(ta, tb, shape, epi, stream);
   switch (blockN) {
     case 64:

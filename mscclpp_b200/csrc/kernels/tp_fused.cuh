@@ -42,6 +42,15 @@ struct TpFusedArgs {
 
 constexpr int kTimelineWords = 16;
 
+// Layout of the fused kernel's part of a heap's aux flag region (DeviceComm::auxFlagsOff), shared with every host file
+// that has to clear or place it: [kTpMaxMBlk][kMaxRanks] epoch-stamped "row block of rank src is complete" words, then
+// kTpMaxMBlk tile counters (zero between launches).
+constexpr int kTpMaxMBlk = 4096;
+constexpr size_t kTpReadyFlagBytes = static_cast<size_t>(kTpMaxMBlk) * kMaxRanks * 4;
+constexpr size_t kTpTileCounterOffset = kTpReadyFlagBytes;  // bytes from the start of the aux region
+constexpr size_t kTpTileCounterBytes = static_cast<size_t>(kTpMaxMBlk) * 4;
+static_assert(kTpTileCounterOffset + kTpTileCounterBytes <= kAuxFlagBytes, "aux flag region too small");
+
 // A[e], B[e]: operands of (emulated) rank e; real multi-GPU use passes one entry each.
 // A: [M, K] bf16 row-major activations, B: [N, K] bf16 row-major weights (nn.Linear layout).
 cudaError_t launchTpFused(const TpFusedArgs& args, const void* const* A, const void* const* B, int numReducers,
@@ -62,10 +71,12 @@ cudaError_t launchTpScaleRowsFromSumsq(const void* h, const float* sumsq, const 
 
 // The same single-GPU layer in ONE launch: h = bf16(A * B^T) + residual and out = h * rsqrt(mean(h^2) + eps) * gamma.
 // Rows are normalised by the epilogue warps as soon as their 128-row block is complete, while the MMAs of later blocks
-// run. `workspace`: tpLocalFusedWorkspaceBytes(M) bytes of device memory, 16-byte aligned (cleared here on `stream`).
+// run. `stamps`: optional zeroed device buffer of gemm::kStampWords words per CTA that receives a time line (one-SM tiles).
+// `workspace`: tpLocalFusedWorkspaceBytes(M) bytes of device memory, 16-byte aligned (cleared here on `stream`).
 size_t tpLocalFusedWorkspaceBytes(int M);
 cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residual, void* h, void* out, const void* gamma, void* workspace,
-                               int M, int N, int K, float eps, int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream);
+                               int M, int N, int K, float eps, int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream,
+                               int probe = 0, unsigned long long* stamps = nullptr);
 
 // Local pass of mode 1: out = h * rinv[row] * gamma.
 cudaError_t launchTpScaleRows(const void* h, const float* rinv, const void* gamma, void* out, int M, int N,

@@ -19,9 +19,9 @@ constexpr size_t kAuxOff = kStatusOff + 4096;
 constexpr size_t kPartialOff = kAuxOff + kAuxFlagBytes;
 constexpr size_t kPartialBytes = static_cast<size_t>(MSCCLPP_B200_NOALLOC_MAX_ELEMS) * 2;
 constexpr size_t kScratchBytes = kPartialOff + kPartialBytes;
-// tile counters follow the ready flags inside the aux region (layout of tp_fused.cu)
-constexpr size_t kTileCounterOff = kAuxOff + static_cast<size_t>(4096) * kMaxRanks * 4;
-constexpr size_t kTileCounterBytes = 4096 * 4;
+// tile counters inside the aux region: the layout constants are the fused kernel's own (tp_fused.cuh)
+constexpr size_t kTileCounterOff = kAuxOff + kTpTileCounterOffset;
+constexpr size_t kTileCounterBytes = kTpTileCounterBytes;
 
 // The scratch. In host code this name is only a handle for cudaGetSymbolAddress, never an address a
 // kernel could use.
@@ -97,7 +97,9 @@ extern "C" int mscclpp_b200_tp_layer_noalloc(const void* x, const void* w, const
   args.shape.N = n;
   args.shape.K = k;
   args.partial = reinterpret_cast<__nv_bfloat16*>(scratch + kPartialOff);
-  // user buffers are addressed relative to the scratch base; the kernel adds the base back
+  // The kernel was written for buffers inside a heap and turns every pointer into "heap base + offset". The caller's
+  // buffers are outside the scratch, so their "offsets" (pointer minus scratch base, in unsigned 64-bit arithmetic) wrap
+  // around; adding the base again gives back the original pointer exactly. Only this rank's base is ever used (world 1).
   args.residualIn = static_cast<const __nv_bfloat16*>(residual);
   args.residualOut = static_cast<__nv_bfloat16*>(residual_out);
   args.out = static_cast<__nv_bfloat16*>(out);
@@ -121,5 +123,28 @@ extern "C" int mscclpp_b200_tp_layer_noalloc(const void* x, const void* w, const
   const void* B[1] = {w};
   e = launchTpFused(args, A, B, /*numReducers=*/64, stream);
   if (e != cudaSuccess) return fail(e, err, err_len, "kernel launch failed");
+  return 0;
+}
+
+extern "C" int mscclpp_b200_tp_layer_noalloc_status(void* cuda_stream, unsigned int* status_words, char* err, size_t err_len) {
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (status_words == nullptr) return fail(cudaErrorInvalidValue, err, err_len, "status_words must not be NULL");
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(e, err, err_len, "cudaGetDevice failed");
+  if (dev < 0 || dev >= kMaxDevices) return fail(cudaErrorInvalidDevice, err, err_len, "device index out of range");
+  unsigned char* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    scratch = g_scratchPtr[dev];
+  }
+  static_assert(sizeof(DeviceStatus) == 64, "the status block is 16 words");
+  if (scratch == nullptr) {  // the entry point never ran on this device: nothing can have gone wrong yet
+    std::memset(status_words, 0, sizeof(DeviceStatus));
+    return 0;
+  }
+  e = cudaMemcpyAsync(status_words, scratch + kStatusOff, sizeof(DeviceStatus), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  if (e != cudaSuccess) return fail(e, err, err_len, "reading the status block failed");
   return 0;
 }

@@ -3,6 +3,7 @@
 Algorithm names follow the reference's default collection
 (src/ext/collectives/algorithm_collection_builder.cc:64-104):
   "packet" / "nvls_packet"          one-shot LL16 over peer stores / one multimem.st per packet
+  "allpair_packet"                  one-shot with 8-byte LL8 packets over peer stores
   "rsag_zero_copy"                  two-shot over peer loads+stores, zero copy
   "nvls_zero_copy"                  two-shot through NVSwitch multimem.ld_reduce + multimem.st
   "nvls_block_pipeline" / "rsag_pipeline"   tensors OUTSIDE the heap: one kernel copies in, reduces through heap scratch
@@ -88,7 +89,7 @@ def _ll_capacity(symm: SymmetricMemory) -> int:
 
 
 def _grid_for(nbytes: int, algo: str, world: int) -> tuple[int, int]:
-    if algo in ("packet", "nvls_packet"):
+    if algo in ("packet", "nvls_packet", "allpair_packet"):
         units = max(1, (nbytes + 15) // 16)
         threads = 512
         blocks = max(1, min(56, (units + threads - 1) // threads))
@@ -130,11 +131,11 @@ def all_reduce(symm: SymmetricMemory, inp: torch.Tensor, out: Optional[torch.Ten
     blocks = n_blocks or blocks
     threads = n_threads or threads
     dt = torch_dtype_to_native(inp.dtype)
-    if algo in ("packet", "nvls_packet"):
+    if algo in ("packet", "nvls_packet", "allpair_packet"):
         if symm.emulated_mode and not symmetric:
             raise ValueError("emulated ranks need heap tensors")
         n.allreduce_ll(symm.heap, inp.data_ptr(), out.data_ptr(), nbytes, dt, _op(op), blocks, threads, _stream(stream),
-                       algo == "nvls_packet")
+                       algo == "nvls_packet", algo == "allpair_packet")
     elif algo in ("rsag_zero_copy", "nvls_zero_copy"):
         if not symmetric:
             raise ValueError(f"{algo} needs tensors from symm.tensor()")

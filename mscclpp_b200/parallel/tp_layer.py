@@ -62,7 +62,7 @@ class RowParallelLinearNorm:
     def forward_fused(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, mode: Optional[int] = None,
                       nvls: Optional[bool] = None, block_n: int = 0, num_reducers: int = 0, num_gemm_ctas: int = 0,
                       rows_per_unit: int = 0, stream: Optional[torch.cuda.Stream] = None,
-                      emulated_inputs=None, timeline: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                      emulated_inputs=None, timeline: Optional[torch.Tensor] = None, row_offset: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
         """Same result as forward(), in ONE kernel: GEMM tiles, cross-rank reduction, residual add and norm
         overlap tile by tile. mode 1 halves NVLink traffic by broadcasting h and 1/rms only and finishing
         `out` with a local pass (second, local-only launch); mode 0 is one launch. Default: mode 1 from 1024 tokens on
@@ -72,16 +72,18 @@ class RowParallelLinearNorm:
         emulated_inputs: for emulated heaps, [(x_r, weight_r)] for every emulated rank.
         timeline: optional int64 CUDA tensor [grid CTAs, 16] that receives per-CTA time stamps (ns): start, GEMM part
         done, reducer part done, rows reduced / ns waited / ns worked by the CTA's first reducer group, first row done,
-        and (words 8-10) the ns of the work spent in the gather, the residual math and the broadcast stores."""
+        and (words 8-10) the ns of the work spent in the gather, the residual math and the broadcast stores.
+        row_offset: the rows of x are rows [row_offset, row_offset + T) of the layer's buffers (the same on every rank);
+        used to run a long sequence as a few launches, e.g. while later rows are still arriving from the host."""
         from .._core import native
 
         n = native.load()
         t = x.shape[0]
-        assert t <= self.max_tokens and x.shape[1] == self.k_shard and x.is_contiguous()
+        assert row_offset + t <= self.max_tokens and x.shape[1] == self.k_shard and x.is_contiguous()
         if mode is None:
             mode = 1 if t >= 1024 else 0
         if residual is not None:
-            self.residual_in[:t].copy_(residual)
+            self.residual_in[row_offset:row_offset + t].copy_(residual)
         nvls = self.symm.nvls if nvls is None else nvls
         if block_n < 0 or (block_n == 0 and t >= 1024 and self.out_features % 256 == 0):
             bn = 0  # 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2)
@@ -93,47 +95,87 @@ class RowParallelLinearNorm:
             b_ptrs = [wi.data_ptr() for _, wi in emulated_inputs]
         else:
             a_ptrs, b_ptrs = [x.data_ptr()], [self.weight.data_ptr()]
-        n.tp_fused(self.symm.heap, a_ptrs, b_ptrs, self.partial.data_ptr(), self.residual_in.data_ptr(),
-                   self.residual_out.data_ptr(), self.out.data_ptr(), self.gamma.data_ptr(), self.rinv.data_ptr(), t,
+        rows = slice(row_offset, row_offset + t)
+        n.tp_fused(self.symm.heap, a_ptrs, b_ptrs, self.partial[rows].data_ptr(), self.residual_in[rows].data_ptr(),
+                   self.residual_out[rows].data_ptr(), self.out[rows].data_ptr(), self.gamma.data_ptr(), self.rinv[rows].data_ptr(), t,
                    self.out_features, self.k_shard, self.eps, bn, num_gemm_ctas, num_reducers, rows_per_unit, mode, nvls, s,
                    0 if timeline is None else timeline.data_ptr())
         if mode == 1:
             ranks = range(self.symm.world) if self.symm.emulated_mode else [self.symm.rank]
             for r in ranks:  # one local pass per (emulated) rank
                 view = (lambda t_: self.symm.rank_view(t_, r)) if self.symm.emulated_mode else (lambda t_: t_)
-                n.tp_scale_rows(view(self.residual_out).data_ptr(), view(self.rinv).data_ptr(), self.gamma.data_ptr(),
-                                view(self.out).data_ptr(), t, self.out_features, s)
-        return self.out[:t], self.residual_out[:t]
+                n.tp_scale_rows(view(self.residual_out)[rows].data_ptr(), view(self.rinv)[rows].data_ptr(), self.gamma.data_ptr(),
+                                view(self.out)[rows].data_ptr(), t, self.out_features, s)
+        return self.out[rows], self.residual_out[rows]
 
     def forward_local(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, two_sm: Optional[bool] = None,
-                      stream: Optional[torch.cuda.Stream] = None, one_kernel: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
-        """World size 1 (no collective). one_kernel (default): ONE launch - the GEMM's epilogue adds the residual, stores h
-        and accumulates every row's sum of squares, and the epilogue warps normalise each 128-row block as soon as it is
-        complete, in the shadow of the MMAs of the later blocks. one_kernel=False: the same epilogue, then a second,
-        memory-bound launch that applies 1/rms and gamma."""
+                      stream: Optional[torch.cuda.Stream] = None, one_kernel: Optional[bool] = None, row_offset: int = 0,
+                      probe: int = 0, timeline: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """World size 1 (no collective). one_kernel: ONE launch - the GEMM's epilogue adds the residual, stores h and
+        accumulates every row's sum of squares, and extra warps normalise each 128-row block as soon as it is complete,
+        while the MMAs of the later blocks run. one_kernel=False: the same epilogue, then a second, memory-bound launch
+        that applies 1/rms and gamma. None picks by size: one launch up to 512 tokens (launch cost dominates there), two
+        from there on (measured on B200: with the tensor pipe's operand traffic loading L2, the in-kernel normalisation
+        of long sequences is slower than a separate pass at full memory bandwidth).
+        timeline (one-kernel path, one-SM tiles): zeroed int64 CUDA tensor [148, 16] that receives per-CTA time stamps in ns
+        (start, last MMA issued, MMA waits, epilogue waits and work, drain, first extra warp's rows / waits / work)."""
         from .._core import native
 
         assert self.symm.world == 1, "forward_local is the single-GPU path"
         n = native.load()
         t = x.shape[0]
-        assert t <= self.max_tokens and x.shape[1] == self.k_shard and x.is_contiguous()
+        assert row_offset + t <= self.max_tokens and x.shape[1] == self.k_shard and x.is_contiguous()
+        rows = slice(row_offset, row_offset + t)
         if residual is not None:
-            self.residual_in[:t].copy_(residual)
+            self.residual_in[rows].copy_(residual)
         if two_sm is None:
             two_sm = t >= 1024 and self.out_features % 256 == 0
+        if one_kernel is None:
+            one_kernel = t <= 512
         s = (stream or torch.cuda.current_stream()).cuda_stream
         if one_kernel:
-            if self._local_ws is None:
-                self._local_ws = torch.empty((n.tp_local_fused_workspace_bytes(self.max_tokens) + 15) // 16 * 4, dtype=torch.float32,
-                                             device=self.symm.device)
-            n.tp_local_fused(x.data_ptr(), self.weight.data_ptr(), self.residual_in.data_ptr(), self.residual_out.data_ptr(),
-                             self.out.data_ptr(), self.gamma.data_ptr(), self._local_ws.data_ptr(), t, self.out_features, self.k_shard,
-                             self.eps, pick_block_n(t, self.out_features), two_sm, 0, s)
-            return self.out[:t], self.residual_out[:t]
-        n.gemm_residual_sumsq(x.data_ptr(), self.weight.data_ptr(), self.residual_in.data_ptr(), self.residual_out.data_ptr(),
-                              self.rinv.data_ptr(), t, self.out_features, self.k_shard, pick_block_n(t, self.out_features), two_sm, s)
-        n.tp_scale_rows_from_sumsq(self.residual_out.data_ptr(), self.rinv.data_ptr(), self.gamma.data_ptr(), self.out.data_ptr(), t,
-                                   self.out_features, self.eps, s)
+            ws_bytes = (n.tp_local_fused_workspace_bytes(self.max_tokens) + 255) // 256 * 256
+            if self._local_ws is None:  # one workspace per 256-row-aligned launch that may be in flight: indexed by row offset
+                self._local_ws = torch.empty((8, ws_bytes // 4), dtype=torch.float32, device=self.symm.device)
+            ws = self._local_ws[(row_offset // 256) % 8]
+            n.tp_local_fused(x.data_ptr(), self.weight.data_ptr(), self.residual_in[rows].data_ptr(), self.residual_out[rows].data_ptr(),
+                             self.out[rows].data_ptr(), self.gamma.data_ptr(), ws.data_ptr(), t, self.out_features, self.k_shard,
+                             self.eps, pick_block_n(t, self.out_features), two_sm, 0, s, probe, 0 if timeline is None else timeline.data_ptr())
+            return self.out[rows], self.residual_out[rows]
+        n.gemm_residual_sumsq(x.data_ptr(), self.weight.data_ptr(), self.residual_in[rows].data_ptr(), self.residual_out[rows].data_ptr(),
+                              self.rinv[rows].data_ptr(), t, self.out_features, self.k_shard, pick_block_n(t, self.out_features), two_sm, s)
+        n.tp_scale_rows_from_sumsq(self.residual_out[rows].data_ptr(), self.rinv[rows].data_ptr(), self.gamma.data_ptr(),
+                                   self.out[rows].data_ptr(), t, self.out_features, self.eps, s)
+        return self.out[rows], self.residual_out[rows]
+
+    def forward_from_host(self, x_host: torch.Tensor, chunks: int = 4, **fused_kwargs) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The layer on activations that are still in (pinned) host memory. The rows are cut into `chunks` pieces of whole
+        256-row blocks; piece i+1 crosses PCIe on a copy stream while piece i is computed (one launch per piece, on the
+        current stream, with the kernels writing straight into rows [r0, r1) of the layer's buffers). The residual
+        stream is what self.residual_in already holds. Every rank must call it with the same shape and `chunks`.
+        fused_kwargs go to forward_fused (world > 1). Returns (normalised output, new residual) for all rows."""
+        t = x_host.shape[0]
+        assert t <= self.max_tokens and x_host.shape[1] == self.k_shard and x_host.is_contiguous()
+        dev = self.symm.device
+        if getattr(self, "_x_stage", None) is None:
+            self._x_stage = torch.empty((self.max_tokens, self.k_shard), dtype=torch.bfloat16, device=dev)
+            self._h2d_stream = torch.cuda.Stream(device=dev)
+            self._h2d_events = [torch.cuda.Event() for _ in range(64)]
+        per = max(256, ((t + chunks - 1) // chunks + 255) // 256 * 256)
+        bounds = [(r0, min(t, r0 + per)) for r0 in range(0, t, per)]
+        cur = torch.cuda.current_stream()
+        self._h2d_stream.wait_stream(cur)  # the staging rows are free once everything queued so far has read them
+        with torch.cuda.stream(self._h2d_stream):
+            for i, (r0, r1) in enumerate(bounds):
+                self._x_stage[r0:r1].copy_(x_host[r0:r1], non_blocking=True)
+                self._h2d_events[i].record(self._h2d_stream)
+        for i, (r0, r1) in enumerate(bounds):
+            cur.wait_event(self._h2d_events[i])
+            x = self._x_stage[r0:r1]
+            if self.symm.world == 1:
+                self.forward_local(x, row_offset=r0)
+            else:
+                self.forward_fused(x, row_offset=r0, **fused_kwargs)
         return self.out[:t], self.residual_out[:t]
 
     @torch.no_grad()

@@ -35,10 +35,11 @@ def _tol(dtype):
     return {torch.bfloat16: 2e-2, torch.float16: 4e-3, torch.float32: 1e-5}.get(dtype, 0)
 
 
+@pytest.mark.parametrize("algo", ["packet", "allpair_packet"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("numel", [8, 40, 1024, 33000, 262144])
-def test_allreduce_ll(world, dtype, numel):
+def test_allreduce_ll(world, dtype, numel, algo):
     from mscclpp_b200.ops import all_reduce
 
     symm = _symm(world)
@@ -47,7 +48,7 @@ def test_allreduce_ll(world, dtype, numel):
     for launch in range(3):  # consecutive launches alternate the LL scratch buffer
         ref = _fill(symm, inp, seed=launch + 1)
         expect = torch.stack(ref).sum(0)
-        all_reduce(symm, inp, out, algo="packet", n_blocks=4)
+        all_reduce(symm, inp, out, algo=algo, n_blocks=4)
         torch.cuda.synchronize()
         symm.check()
         for r in range(world):

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 NP2TORCH = {np.float32: torch.float32, np.float16: torch.float16, np.int32: torch.int32}
 
 
-def _run_both(plan_json, world, in_elems, out_elems, np_dtype, inplace, launches=2):
+def _run_both(plan_json, world, in_elems, out_elems, np_dtype, inplace, launches=2, packet_type="LL16"):
     from mscclpp_b200 import SymmetricMemory, native
     from mscclpp_b200.language.interpreter import PlanInterpreter
 
@@ -38,7 +38,7 @@ def _run_both(plan_json, world, in_elems, out_elems, np_dtype, inplace, launches
                 symm.rank_view(t_out, r).zero_()
         expect = interp.run([a.copy() for a in ins], None if inplace else outs)
         executor.execute(0, t_in.data_ptr(), t_out.data_ptr(), in_elems * ins[0].itemsize, out_elems * ins[0].itemsize, dt,
-                         plans[0], torch.cuda.current_stream().cuda_stream)
+                         plans[0], torch.cuda.current_stream().cuda_stream, getattr(n.PacketType, packet_type))
         torch.cuda.synchronize()
         symm.check()
         for r in range(world):
@@ -46,7 +46,8 @@ def _run_both(plan_json, world, in_elems, out_elems, np_dtype, inplace, launches
             if np_dtype == np.int32:
                 np.testing.assert_array_equal(got, expect[r])
             else:
-                np.testing.assert_allclose(got.astype(np.float32), expect[r].astype(np.float32), rtol=2e-3, atol=2e-3)
+                np.testing.assert_allclose(got.astype(np.float32), expect[r].astype(np.float32), rtol=2e-3, atol=2e-3,
+                                           err_msg=f"rank {r} of {world}, launch {launch}, {in_elems} elements, packets {packet_type}")
     executor.reset()
     symm.destroy()
 
@@ -61,6 +62,65 @@ def test_allreduce_plans(world, algo, instances):
     elems = 4 * world * instances * 64
     _run_both(plan, world, elems, elems, np.float32, inplace=True)
     _run_both(plan, world, elems, elems, np.float16, inplace=True)
+
+
+@pytest.mark.parametrize("world", [2, 8])
+@pytest.mark.parametrize("packet_type", ["LL8", "LL16"])
+def test_packet_plans_with_both_packet_formats(world, packet_type):
+    """The same LL plan through 8-byte and 16-byte packets, a small and a larger message. (Sizes divide evenly into the
+    plan's chunks: with a remainder the plan format maps unequal input chunks onto scratch chunks of other sizes, in
+    the reference as well, and neighbouring ranges then overlap.)"""
+    from mscclpp_b200.default_algos import single_node
+
+    plan = single_node.build("allreduce_allpairs_packet", world).to_json()
+    for elems in (4 * world * 16, 4 * world * 1024):
+        _run_both(plan, world, elems, elems, np.float32, inplace=True, packet_type=packet_type)
+
+
+@pytest.mark.parametrize("nodes,gpus", [(2, 2), (2, 4)])
+def test_port_channel_plans_go_through_the_host_proxy(nodes, gpus):
+    """The hierarchical multi-node plans talk to the GPUs of other nodes through port channels: the interpreter kernel
+    queues requests in the executor's FIFO and the executor's proxy thread moves the packets with the copy engines.
+    Here the 'nodes' are groups of emulated ranks on one GPU, which exercises exactly that path."""
+    from mscclpp_b200.default_algos import allreduce_multi_nodes, reducescatter_multi_nodes
+    from mscclpp_b200.language.collectives import AllReduce, ReduceScatter
+    from mscclpp_b200.language.utils import AlgoSpec
+
+    w = nodes * gpus
+
+    def spec(name, coll):
+        return AlgoSpec(name=name, collective=coll, nranks_per_node=gpus, world_size=w, in_place=True, instances=1, protocol="LL",
+                        auto_sync=False, num_threads_per_block=1024, reuse_resources=True, use_double_scratch_buffer=True)
+
+    plan = allreduce_multi_nodes(spec("ar_mn_gpu", AllReduce(w, 1, True))).to_json()
+    assert '"port"' in plan
+    elems = w * nodes * 64
+    _run_both(plan, w, elems, elems, np.float32, inplace=True, launches=3)
+    plan = reducescatter_multi_nodes(spec("rs_mn_gpu", ReduceScatter(w, 1, True))).to_json()
+    assert '"port"' in plan
+
+
+def test_plan_with_more_blocks_than_the_gpu_can_hold_is_refused():
+    """Thread blocks of a plan wait on one another, so all of them (times the emulated ranks) must be resident at once;
+    a launch that cannot be is refused with a message that names the plan and the numbers, before anything runs."""
+    from mscclpp_b200 import SymmetricMemory, native
+    from mscclpp_b200.default_algos import single_node
+
+    n = native()
+    world = 8
+    plan_json = single_node.build("allreduce_allpairs", world, instances=32).to_json()  # 32 blocks of 1024 threads per rank
+    blocks = max(len(g["threadblocks"]) for g in json.loads(plan_json)["gpus"])
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    if blocks * world <= sms:
+        pytest.skip("this plan fits the GPU even with all ranks emulated")
+    symm = SymmetricMemory.emulated(world, nbytes=128 << 20, timeout_ms=1000)
+    elems = 4 * world * 32 * 64
+    t = symm.tensor((elems,), torch.float32, zero=True)
+    ex = n.Executor(symm.heap)
+    with pytest.raises(Exception, match="resident at the same time"):
+        ex.execute(0, t.data_ptr(), t.data_ptr(), elems * 4, elems * 4, n.DataType.float32, n.ExecutionPlan.from_string(plan_json, 0), 0)
+    ex.reset()
+    symm.destroy()
 
 
 @pytest.mark.parametrize("world", [2, 8])
