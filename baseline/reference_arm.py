@@ -215,7 +215,7 @@ def main() -> int:
     def e2e_step():
         x_dev.copy_(x_host, non_blocking=True)
         out, _ = layer(x_dev, residual)
-        result_host.copy_(out[:, :8].float().abs().mean().reshape(1), non_blocking=True)
+        result_host.copy_(out[-1].sum(dtype=torch.float32).reshape(1), non_blocking=True)  # one small kernel on the last row
         torch.cuda.current_stream().synchronize()
 
     e2e_ms = time_steps(e2e_step, args.steps, warmup)

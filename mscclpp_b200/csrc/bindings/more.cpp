@@ -145,6 +145,38 @@ void registerMoreBindings(py::module_& m) {
       },
       py::arg("a"), py::arg("b"), py::arg("residual"), py::arg("h"), py::arg("sumsq"), py::arg("m"), py::arg("n"), py::arg("k"),
       py::arg("block_n") = 256, py::arg("two_sm") = false, py::arg("stream") = 0);
+  m.def(
+      "tp_decode",
+      [](SymmetricHeap& heap, std::vector<uintptr_t> x, std::vector<uintptr_t> w, uintptr_t residualIn, uintptr_t residualOut, uintptr_t out,
+         uintptr_t gamma, int T, int N, int K, float eps, bool nvls, int numCtas, uintptr_t stream) {
+        const size_t need = heap.emulated() ? static_cast<size_t>(heap.world()) : 1;
+        if (x.size() != need || w.size() != need) throw Error("tp_decode: one x and one w pointer per (emulated) rank", ErrorCode::InvalidUsage);
+        for (uintptr_t p : {residualOut, out}) {
+          if (p != 0 && !heap.contains(reinterpret_cast<const void*>(p))) throw Error("tp_decode: out and residual_out must be symmetric-heap memory", ErrorCode::InvalidUsage);
+        }
+        if (residualIn != 0 && !heap.contains(reinterpret_cast<const void*>(residualIn))) throw Error("tp_decode: residual_in must be symmetric-heap memory", ErrorCode::InvalidUsage);
+        if (nvls && !heap.nvls()) throw Error("NVLS requested but the heap has no multicast mapping", ErrorCode::InvalidUsage);
+        TpDecodeArgs a{};
+        a.comm = heap.deviceComm();
+        for (size_t e = 0; e < need; e++) {
+          a.x[e] = reinterpret_cast<const __nv_bfloat16*>(x[e]);
+          a.w[e] = reinterpret_cast<const __nv_bfloat16*>(w[e]);
+        }
+        a.residualIn = reinterpret_cast<const __nv_bfloat16*>(residualIn);
+        a.residualOut = reinterpret_cast<__nv_bfloat16*>(residualOut);
+        a.out = reinterpret_cast<__nv_bfloat16*>(out);
+        a.gamma = reinterpret_cast<const __nv_bfloat16*>(gamma);
+        a.T = T;
+        a.N = N;
+        a.K = K;
+        a.eps = eps;
+        a.nvls = nvls ? 1 : 0;
+        a.emuRanks = heap.emulated() ? heap.world() : 1;
+        a.numCtas = numCtas;
+        checkCudaMore(launchTpDecode(a, reinterpret_cast<cudaStream_t>(stream)), "tp_decode");
+      },
+      py::arg("heap"), py::arg("x"), py::arg("w"), py::arg("residual_in"), py::arg("residual_out"), py::arg("out"), py::arg("gamma"),
+      py::arg("t"), py::arg("n"), py::arg("k"), py::arg("eps") = 1e-5f, py::arg("nvls") = false, py::arg("num_ctas") = 0, py::arg("stream") = 0);
   m.def("tp_local_fused_workspace_bytes", [](int M) { return tpLocalFusedWorkspaceBytes(M); }, py::arg("m"));
   m.def(
       "tp_local_fused",

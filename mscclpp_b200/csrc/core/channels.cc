@@ -140,7 +140,10 @@ ProxyHandlerResult ProxyService::handleTrigger(ProxyTrigger trigger) {
       pending = 0;
     }
   } catch (const std::exception& e) {
+    // A write or signal that did not happen must not look like one that did: the request stays unconsumed, so the
+    // device-side flush() / putWithSignalAndFlush() that waits for it gives up with an error after its time limit.
     LOG_ERROR(LogSubsys::CONN, "proxy: request failed: ", e.what());
+    return ProxyHandlerResult::Abort;
   }
   return ProxyHandlerResult::Continue;
 }

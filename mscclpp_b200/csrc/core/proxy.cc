@@ -18,6 +18,7 @@ struct Proxy::Impl {
   std::thread thread;
   std::atomic<bool> running{false};
   std::atomic<bool> stopRequested{false};
+  std::atomic<bool> failed{false};
 };
 
 Proxy::Proxy(ProxyHandler handler, std::function<void()> threadInit, int fifoSize) : pimpl_(std::make_unique<Impl>()) {
@@ -30,6 +31,7 @@ Proxy::~Proxy() { stop(); }
 
 std::shared_ptr<Fifo> Proxy::fifo() { return pimpl_->fifo; }
 bool Proxy::running() const { return pimpl_->running.load(); }
+bool Proxy::failed() const { return pimpl_->failed.load(); }
 void Proxy::setProgressHook(std::function<void()> hook) { pimpl_->progress = std::move(hook); }
 
 void Proxy::start(bool blocking) {
@@ -56,6 +58,11 @@ void Proxy::start(bool blocking) {
       }
       idle = 0;
       ProxyHandlerResult r = pimpl_->handler(t);
+      if (r == ProxyHandlerResult::Abort) {
+        pimpl_->failed.store(true);
+        LOG_ERROR(LogSubsys::CONN, "proxy: a request failed; the proxy thread stops and leaves the request unconsumed");
+        break;
+      }
       fifo.pop();
       if (pimpl_->progress) pimpl_->progress();
       if (r == ProxyHandlerResult::Stop) break;

@@ -2,12 +2,14 @@
 
 #include <algorithm>
 #include <cstring>
+#include <mutex>
 #include <unistd.h>
 
 #include <mscclpp/gpu_utils.hpp>
 
 #include "cuda_driver.hpp"
 #include "logger.hpp"
+#include "range_allocator.hpp"
 #include "unix_socket.hpp"
 
 namespace mscclpp {
@@ -21,12 +23,13 @@ struct NvlsConnection::Impl {
   CUmemGenericAllocationHandle mcHandle = 0;
   CUdeviceptr mcVa = 0;     // multicast mapping of the whole object
   size_t mapped = 0;
-  size_t nextOffset = 0;    // bump allocator over the object (ranges are never returned individually)
+  RangeAllocator ranges;    // offsets of the object: a range goes back when the last copy of its SwitchChannel is gone
+  std::mutex mutex;
   struct Binding {
     size_t offset;
     size_t size;
   };
-  std::vector<Binding> bindings;
+  std::vector<Binding> bindings;  // what is bound right now (the barrier granule included)
   // group barrier: one granule of this rank's own memory bound at the end of the object
   void* barrierMem = nullptr;
   std::shared_ptr<uint64_t> barrierExpected;
@@ -65,14 +68,51 @@ SwitchChannel NvlsConnection::bindAllocatedMemory(void* devicePtr, size_t size) 
     throw Error("bindAllocatedMemory: pointer and size must be multiples of the multicast granularity (" + std::to_string(g) + ")",
                 ErrorCode::InvalidUsage);
   }
-  if (s.nextOffset + size > s.capacity) throw Error("multicast object is full", ErrorCode::InvalidUsage);
-  const size_t offset = s.nextOffset;
-  MSCCLPP_CUTHROW(drv.cuMulticastBindAddr(s.mcHandle, offset, reinterpret_cast<CUdeviceptr>(devicePtr), size, 0));
-  s.nextOffset += size;
-  s.bindings.push_back({offset, size});
+  size_t offset;
+  {
+    std::lock_guard<std::mutex> lock(s.mutex);
+    offset = s.ranges.allocate(size);
+    if (offset == RangeAllocator::npos) {
+      throw Error("multicast object has no free range of " + std::to_string(size) + " bytes (" + std::to_string(s.ranges.bytesFree()) +
+                      " bytes free, largest piece " + std::to_string(s.ranges.largestFree()) + ")",
+                  ErrorCode::InvalidUsage);
+    }
+  }
+  CUresult res = drv.cuMulticastBindAddr(s.mcHandle, offset, reinterpret_cast<CUdeviceptr>(devicePtr), size, 0);
+  if (res != CUDA_SUCCESS) {
+    std::lock_guard<std::mutex> lock(s.mutex);
+    s.ranges.release(offset);
+    MSCCLPP_CUTHROW(res);
+  }
+  {
+    std::lock_guard<std::mutex> lock(s.mutex);
+    s.bindings.push_back({offset, size});
+  }
   // nobody may touch the multicast alias before every member has bound its part
   s.comm->bootstrap()->groupBarrier(s.ranks);
-  return SwitchChannel(devicePtr, reinterpret_cast<void*>(s.mcVa + offset), size, shared_from_this());
+  // The range is unbound and handed back when the last copy of the channel is destroyed. Members have to drop their
+  // channels in the same order as well, or their next bindings land at different offsets.
+  std::weak_ptr<NvlsConnection> weak = weak_from_this();
+  const int deviceId = s.deviceId;
+  std::shared_ptr<void> token(nullptr, [weak, offset, size, deviceId](void*) {
+    auto conn = weak.lock();
+    if (!conn) return;  // the connection went first and has released everything
+    const CudaDriver* d = CudaDriver::tryGet();
+    if (d == nullptr) return;
+    NvlsConnection::Impl& impl = *conn->impl();
+    (void)cudaDeviceSynchronize();  // nothing in flight may still use the alias
+    CUdevice dev;
+    if (d->cuDeviceGet(&dev, deviceId) == CUDA_SUCCESS) (void)d->cuMulticastUnbind(impl.mcHandle, dev, offset, size);
+    std::lock_guard<std::mutex> lock(impl.mutex);
+    for (auto it = impl.bindings.begin(); it != impl.bindings.end(); ++it) {
+      if (it->offset == offset) {
+        impl.bindings.erase(it);
+        break;
+      }
+    }
+    impl.ranges.release(offset);
+  });
+  return SwitchChannel(devicePtr, reinterpret_cast<void*>(s.mcVa + offset), size, shared_from_this(), std::move(token));
 }
 
 SwitchChannel::DeviceHandle SwitchChannel::deviceHandle() const {
@@ -118,6 +158,7 @@ std::shared_ptr<NvlsConnection> connectNvlsCollective(std::shared_ptr<Communicat
   const size_t g = detail::physicalGranularity(true);
   impl->granularity = g;
   impl->capacity = (bufferSize + g - 1) / g * g;
+  impl->ranges.reset(impl->capacity, g);
   const size_t total = impl->capacity + g;  // + one granule for the group barrier word
   const int root = allRanks[0];
 

@@ -181,6 +181,7 @@ struct Layout {
   uint64_t S = 0, C = 0, A = 16;
   uint64_t chunkUpper = 0;
   uint64_t inOff = 0, outOff = 0, scratchOff = 0;  // heap offsets
+  uint64_t inBytes = 0, outBytes = 0, scratchBytes = 0;  // extent of each buffer (scratch: one half, payload space)
 };
 
 class Resolver {
@@ -290,6 +291,16 @@ class Resolver {
     }
     d.isScratch = type == "s" ? 1 : 0;
     d.offset = baseOf(type) + start;
+    // Every range a plan names is checked against the buffer it names before anything is launched: a plan whose chunk
+    // arithmetic runs past a buffer is reported here, with its name, instead of scribbling over the neighbours on the GPU
+    // (the role a memory checker plays where one can be run). Packet ranges are checked in payload space; the packet
+    // form spends exactly twice that inside the scratch half, which is sized for it.
+    const uint64_t extent = type == "i" ? l_.inBytes : (type == "o" ? l_.outBytes : l_.scratchBytes);
+    if (extent != 0 && start + d.size > extent) {
+      throw Error("plan '" + p_.name + "': rank " + std::to_string(rank_) + " names bytes [" + std::to_string(start) + ", " +
+                      std::to_string(start + d.size) + ") of a '" + type + "' buffer of " + std::to_string(extent) + " bytes",
+                  ErrorCode::ExecutorError);
+    }
     return d;
   }
 
@@ -442,7 +453,7 @@ struct Executor::Impl {
     if (ctx == nullptr || localRank >= static_cast<int>(ctx->portChannels.size()) ||
         r.channel >= ctx->portChannels[localRank].size()) {
       failProxy("request names an unknown context or channel");
-      return ProxyHandlerResult::Continue;
+      return ProxyHandlerResult::Abort;
     }
     const DevChannel ch = ctx->portChannels[localRank][r.channel];
     const int srcRank = heap->emulated() ? static_cast<int>(r.rank) : heap->rank();
@@ -452,7 +463,7 @@ struct Executor::Impl {
     if ((r.kind & kPortData) && r.size != 0) {
       if (r.srcOff + r.size > heap->bytes() || r.dstOff + r.size > heap->bytes()) {
         failProxy("request reaches beyond the heap");
-        return ProxyHandlerResult::Continue;
+        return ProxyHandlerResult::Abort;
       }
       e = cudaMemcpyAsync(dstBase + r.dstOff, srcBase + r.srcOff, r.size, cudaMemcpyDeviceToDevice, proxyStream);
     }
@@ -468,7 +479,10 @@ struct Executor::Impl {
       }
     }
     if (e == cudaSuccess && (r.kind & kPortSync)) e = cudaStreamSynchronize(proxyStream);
-    if (e != cudaSuccess) failProxy(std::string("CUDA call failed: ") + cudaGetErrorString(e));
+    if (e != cudaSuccess) {
+      failProxy(std::string("CUDA call failed: ") + cudaGetErrorString(e));
+      return ProxyHandlerResult::Abort;
+    }
     return ProxyHandlerResult::Continue;
   }
 
@@ -652,6 +666,9 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
     if (out == nullptr) layout.outOff = layout.inOff;
   }
   layout.scratchOff = ctx.scratch ? reinterpret_cast<uint64_t>(ctx.scratch) - base : 0;
+  layout.inBytes = in ? sendBuffSize : recvBuffSize;
+  layout.outBytes = out ? recvBuffSize : sendBuffSize;
+  layout.scratchBytes = maxScratchChunks * layout.chunkUpper;
   if (ctx.inOff != layout.inOff || ctx.outOff != layout.outOff) rebuild = true;
 
   // ---- device plans (cached per message size and buffer placement)

@@ -12,6 +12,8 @@ namespace mscclpp {
 enum class ProxyHandlerResult {
   Continue,  // keep polling
   Stop,      // leave the loop after this trigger
+  Abort,     // the request could not be carried out: leave the loop WITHOUT marking it consumed, so that a device-side
+             // sync on it (or on anything queued behind it) runs into its time limit instead of reporting success
 };
 
 class Proxy;
@@ -25,6 +27,8 @@ class Proxy {
   void start(bool blocking = false);
   void stop();
   bool running() const;
+  // True once a handler answered Abort: the thread has stopped and the FIFO is no longer drained.
+  bool failed() const;
   std::shared_ptr<Fifo> fifo();
   // Called on the proxy thread between polls (progress of asynchronous work such as flushes).
   void setProgressHook(std::function<void()> hook);

@@ -15,8 +15,9 @@ class NvlsConnection;
 class SwitchChannel {
  public:
   SwitchChannel() = default;
-  SwitchChannel(void* devicePtr, void* mcPtr, size_t bufferSize, std::shared_ptr<NvlsConnection> connection)
-      : devicePtr_(devicePtr), mcPtr_(mcPtr), bufferSize_(bufferSize), connection_(std::move(connection)) {}
+  SwitchChannel(void* devicePtr, void* mcPtr, size_t bufferSize, std::shared_ptr<NvlsConnection> connection,
+                std::shared_ptr<void> binding = nullptr)
+      : devicePtr_(devicePtr), mcPtr_(mcPtr), bufferSize_(bufferSize), connection_(std::move(connection)), binding_(std::move(binding)) {}
   using DeviceHandle = SwitchChannelDeviceHandle;
   DeviceHandle deviceHandle() const;
   void* getDevicePtr() const { return devicePtr_; }
@@ -28,6 +29,7 @@ class SwitchChannel {
   void* mcPtr_ = nullptr;
   size_t bufferSize_ = 0;
   std::shared_ptr<NvlsConnection> connection_;
+  std::shared_ptr<void> binding_;  // shared by the copies of the channel; the last one to go returns the range of the object
 };
 
 class NvlsConnection : public std::enable_shared_from_this<NvlsConnection> {
@@ -36,8 +38,9 @@ class NvlsConnection : public std::enable_shared_from_this<NvlsConnection> {
   // Minimum size and alignment of what bindAllocatedMemory accepts.
   static size_t getMultiCastMinGranularity();
   // Bind [devicePtr, +size) - memory from the VMM path (GpuBuffer, gpuCallocPhysical, SymmetricHeap) -
-  // into the next free range of the multicast object. Collective: every member must bind ranges of
-  // the same size in the same order.
+  // into the lowest free range of the multicast object that fits. Collective: every member must bind ranges of
+  // the same size in the same order (and drop the returned channels in the same order: a range is unbound and
+  // reused once the last copy of its channel is destroyed).
   SwitchChannel bindAllocatedMemory(void* devicePtr, size_t size);
   size_t capacity() const;
   int groupSize() const;

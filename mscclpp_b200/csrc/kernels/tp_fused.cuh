@@ -78,6 +78,31 @@ cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residua
                                int M, int N, int K, float eps, int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream,
                                int probe = 0, unsigned long long* stamps = nullptr);
 
+// The layer for a handful of tokens (decode): one launch, no tensor-core tiles - every SM streams the weight rows of its
+// slab of output columns, the slabs meet the other ranks in a one-shot LL packet allreduce done by the same thread
+// blocks, residual add and RMSNorm follow in registers (see tp_decode.cu). Every rank ends up with the whole result.
+constexpr int kTpDecodeMaxTokens = 8;
+// this kernel's words in a heap's aux flag region: [kBarrierSlots][kTpDecodeMaxTokens] fp32 row sums, behind the flags of
+// the fused layer, of the all-gather GEMM and of the pipelined allreduce
+constexpr uint64_t kTpDecodeAuxOffset = (4096ull * (kMaxRanks + 1) + 4096ull) * 4ull + 2ull * kBarrierSlots * kMaxRanks * 8ull;
+static_assert(kTpDecodeAuxOffset + static_cast<uint64_t>(kBarrierSlots) * kTpDecodeMaxTokens * 4 <= kAuxFlagBytes, "aux flag region too small");
+struct TpDecodeArgs {
+  DeviceComm comm;
+  const __nv_bfloat16* x[8];      // [T, K] activations of (emulated) rank e; real multi-GPU use fills entry 0
+  const __nv_bfloat16* w[8];      // [N, K] weight shard of (emulated) rank e
+  const __nv_bfloat16* residualIn;  // symmetric-heap [T, N], replicated content (may be null)
+  __nv_bfloat16* residualOut;     // symmetric-heap [T, N] (may be null)
+  __nv_bfloat16* out;             // symmetric-heap [T, N]
+  const __nv_bfloat16* gamma;     // [N] local (may be null)
+  int T, N, K;                    // T <= kTpDecodeMaxTokens, N % 8 == 0, K % 256 == 0, T * K * 4 bytes of shared memory
+  float eps;
+  int nvls;                       // packets leave through one multimem.st instead of world - 1 peer stores
+  int emuRanks;
+  int numCtas;                    // 0 = one thread block per SM
+  int colsPerCta;                 // set by the launcher
+};
+cudaError_t launchTpDecode(const TpDecodeArgs& args, cudaStream_t stream);
+
 // Local pass of mode 1: out = h * rinv[row] * gamma.
 cudaError_t launchTpScaleRows(const void* h, const float* rinv, const void* gamma, void* out, int M, int N,
                               cudaStream_t stream);

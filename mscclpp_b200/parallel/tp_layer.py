@@ -108,6 +108,34 @@ class RowParallelLinearNorm:
                                 view(self.out)[rows].data_ptr(), t, self.out_features, s)
         return self.out[rows], self.residual_out[rows]
 
+    DECODE_MAX_TOKENS = 8
+
+    def forward_decode(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, nvls: Optional[bool] = None, num_ctas: int = 0,
+                       stream: Optional[torch.cuda.Stream] = None, emulated_inputs=None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """The layer for up to 8 tokens in ONE launch without tensor-core tiles: every SM streams the weight rows of its slab
+        of output columns, the slabs are all-reduced with LL packets by the same thread blocks (no barrier between the
+        ranks), residual add and RMSNorm follow in registers. Any world size, 1 included. k_shard must be a multiple of 256.
+        nvls: packets leave through one multimem.st instead of one store per peer (default: where the heap has it and
+        there are more than two ranks)."""
+        from .._core import native
+
+        n = native.load()
+        t = x.shape[0]
+        assert t <= self.DECODE_MAX_TOKENS and x.shape[1] == self.k_shard and x.is_contiguous() and self.k_shard % 256 == 0
+        if residual is not None:
+            self.residual_in[:t].copy_(residual)
+        if nvls is None:
+            nvls = bool(self.symm.nvls) and self.symm.world > 2
+        s = (stream or torch.cuda.current_stream()).cuda_stream
+        if emulated_inputs is not None:
+            xp = [xi.data_ptr() for xi, _ in emulated_inputs]
+            wp = [wi.data_ptr() for _, wi in emulated_inputs]
+        else:
+            xp, wp = [x.data_ptr()], [self.weight.data_ptr()]
+        n.tp_decode(self.symm.heap, xp, wp, self.residual_in.data_ptr(), self.residual_out.data_ptr(), self.out.data_ptr(),
+                    self.gamma.data_ptr(), t, self.out_features, self.k_shard, self.eps, nvls, num_ctas, s)
+        return self.out[:t], self.residual_out[:t]
+
     def forward_local(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, two_sm: Optional[bool] = None,
                       stream: Optional[torch.cuda.Stream] = None, one_kernel: Optional[bool] = None, row_offset: int = 0,
                       probe: int = 0, timeline: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:

@@ -19,11 +19,13 @@
 #include <mscclpp/executor.hpp>
 #include <mscclpp/gpu_utils.hpp>
 #include <mscclpp/numa.hpp>
+#include <mscclpp/proxy.hpp>
 #include <mscclpp/utils.hpp>
 #include <mscclpp/version.hpp>
 #include <mscclpp/device.hpp>
 
 #include "core/json.hpp"
+#include "core/range_allocator.hpp"
 #include "core/socket.hpp"
 #include "core/unix_socket.hpp"
 #include "framework.hpp"
@@ -287,6 +289,56 @@ TEST(GpuUtils, AllocationFamilyInstantiates) {
   void (*e)(void*, int, size_t) = &gpuMemset;
   EXPECT_TRUE(a != nullptr && b != nullptr && c != nullptr && d != nullptr && e != nullptr);
   EXPECT_TRUE(static_cast<int>(GpuBufferGranularity::MultiCastMinimum) != static_cast<int>(GpuBufferGranularity::MultiCastRecommended));
+}
+
+TEST(Proxy, AFailedRequestStaysUnconsumed) {
+  // a handler that cannot carry out a request answers Abort: the proxy stops and the request is NOT marked consumed, so a
+  // device-side sync on it times out instead of reporting a transfer that never happened
+  std::atomic<int> handled{0};
+  Proxy proxy([&](ProxyTrigger t) {
+    handled++;
+    return t.fst == 13 ? ProxyHandlerResult::Abort : ProxyHandlerResult::Continue;
+  });
+  proxy.start();
+  auto fifo = proxy.fifo();
+  ProxyTrigger good{1, 1}, bad{13, 1};
+  fifo->pushFromHost(good);
+  fifo->pushFromHost(bad);
+  fifo->pushFromHost(good);
+  for (int i = 0; i < 2000 && !proxy.failed(); i++) usleep(1000);
+  EXPECT_TRUE(proxy.failed());
+  EXPECT_EQ(handled.load(), 2);             // the request behind the failed one is never looked at
+  EXPECT_EQ(fifo->consumed(), uint64_t(1));  // only the first one counts as done
+  proxy.stop();
+}
+
+TEST(RangeAllocator, FirstFitReleaseAndCoalescing) {
+  // offsets of a multicast object: ranges come back when channels go away and are reused, lowest address first
+  RangeAllocator r(10 * 4096 + 100, 4096);
+  EXPECT_EQ(r.capacity(), size_t(10 * 4096));
+  const size_t a = r.allocate(4096), b = r.allocate(5000), c = r.allocate(3 * 4096);
+  EXPECT_EQ(a, size_t(0));
+  EXPECT_EQ(b, size_t(4096));       // 5000 bytes take two granules
+  EXPECT_EQ(c, size_t(3 * 4096));
+  EXPECT_EQ(r.bytesFree(), size_t(4 * 4096));
+  EXPECT_EQ(r.allocate(5 * 4096), RangeAllocator::npos);
+  r.release(b);
+  EXPECT_EQ(r.largestFree(), size_t(4 * 4096));  // the tail, not the two-granule hole
+  EXPECT_EQ(r.allocate(2 * 4096), size_t(4096));  // the hole is taken first
+  r.release(a);
+  r.release(4096);
+  r.release(c);
+  EXPECT_EQ(r.largestFree(), r.capacity());  // everything merged back into one range
+  EXPECT_EQ(r.rangesInUse(), size_t(0));
+  // many rounds of bind / unbind never exhaust the object (a pointer that only advances would after ten)
+  for (int round = 0; round < 1000; round++) {
+    const size_t x = r.allocate(6 * 4096), y = r.allocate(4 * 4096);
+    EXPECT_TRUE(x != RangeAllocator::npos && y != RangeAllocator::npos);
+    r.release(round % 2 ? x : y);
+    r.release(round % 2 ? y : x);
+  }
+  EXPECT_THROW(r.release(12345), std::invalid_argument);
+  EXPECT_EQ(r.allocate(0), RangeAllocator::npos);
 }
 
 TEST(Numa, CpuListsAndBinding) {

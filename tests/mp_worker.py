@@ -165,6 +165,27 @@ def main():
                 e2 = (res.float() - h).abs().max().item()
                 report(f"tp_fused/T={tokens}/nvls={use_nvls}/mode={mode}", e1 < 0.12 and e2 <= 0.02 * h.abs().max().item() + 0.05, err=e1, res_err=e2)
 
+    # decode kernel: weight-streaming GEMV slabs + one-shot packet allreduce + residual + RMSNorm in one launch
+    for tokens in (1, 3, 8):
+        gen = torch.Generator(device=dev).manual_seed(2000 + tokens)
+        residual = torch.randn((tokens, 4096), generator=gen, device=dev).to(torch.bfloat16)
+        x = torch.randn((tokens, 512), device=dev).to(torch.bfloat16)
+        part = (x.float() @ layer.weight.float().t()).to(torch.bfloat16)
+        h = (gathered_reference(part).to(torch.bfloat16).float() + residual.float()).to(torch.bfloat16).float()
+        ref = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + layer.eps) * layer.gamma.float()).to(torch.bfloat16).float()
+        for use_nvls in ([False, True] if symm.nvls else [False]):
+            layer.out.zero_()
+            layer.residual_out.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            for rep in range(3):
+                out, res = layer.forward_decode(x, residual, nvls=use_nvls)
+            torch.cuda.synchronize()
+            symm.check()
+            e1 = (out.float() - ref).abs().max().item()
+            e2 = (res.float() - h).abs().max().item()
+            report(f"tp_decode/T={tokens}/nvls={use_nvls}", e1 < 0.12 and e2 <= 0.02 * h.abs().max().item() + 0.05, err=e1, res_err=e2)
+
     # sequence-parallel halves: all-gather -> GEMM and GEMM -> reduce-scatter, one kernel each
     from mscclpp_b200.parallel.sp_layer import all_gather_gemm, gemm_reduce_scatter
 

@@ -230,6 +230,43 @@ def symm_ctrl_epoch(symm):
     return tensor_from_pointer(symm.heap.local_base, (1,), torch.int32, symm.device, owner=symm)
 
 
+@pytest.mark.parametrize("world", [1, 2, 8])
+@pytest.mark.parametrize("tokens,hidden,k", [(1, 1024, 256), (5, 2048, 512), (8, 8192, 1024)])
+def test_decode_layer_one_kernel(world, tokens, hidden, k):
+    """Up to 8 tokens: weight-streaming slabs + one-shot packet allreduce + residual + RMSNorm in one launch, all ranks
+    emulated on one GPU; three launches in a row alternate the packet scratch."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.tp_layer import RowParallelLinearNorm
+
+    symm = SymmetricMemory.emulated(world, nbytes=256 << 20, timeout_ms=3000)
+    layer = RowParallelLinearNorm(symm, out_features=hidden, k_shard=k, max_tokens=8)
+    g = torch.Generator(device="cuda").manual_seed(tokens + hidden)
+    ws = [(torch.randn((hidden, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(world)]
+    gam = (1 + 0.1 * torch.randn((hidden,), generator=g, device="cuda")).to(torch.bfloat16)
+    for r in range(world):
+        symm.rank_view(layer.gamma, r).copy_(gam)
+    ctas = max(1, 128 // world)
+    for rep in range(3):
+        xs = [torch.randn((tokens, k), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+        residual = torch.randn((tokens, hidden), generator=g, device="cuda").to(torch.bfloat16)
+        for r in range(world):
+            symm.rank_view(layer.residual_in, r)[:tokens].copy_(residual)
+            symm.rank_view(layer.out, r).fill_(float("nan"))
+            symm.rank_view(layer.residual_out, r).fill_(float("nan"))
+        layer.forward_decode(xs[0], nvls=False, num_ctas=ctas, emulated_inputs=list(zip(xs, ws)))
+        torch.cuda.synchronize()
+        symm.check()
+        acc = sum((x.float() @ w.float().t()).to(torch.bfloat16).float() for x, w in zip(xs, ws))
+        h = (acc.to(torch.bfloat16).float() + residual.float()).to(torch.bfloat16).float()
+        y = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + layer.eps) * gam.float()).to(torch.bfloat16).float()
+        for r in range(world):
+            got_h = symm.rank_view(layer.residual_out, r)[:tokens].float()
+            got_y = symm.rank_view(layer.out, r)[:tokens].float()
+            assert (got_h - h).abs().max().item() <= 0.02 * h.abs().max().item() + 0.05, f"rank {r} rep {rep}"
+            assert (got_y - y).abs().max().item() <= 0.1, f"rank {r} rep {rep}"
+    symm.destroy()
+
+
 @pytest.mark.parametrize("world", [1, 2, 4])
 @pytest.mark.parametrize("mode", [0, 1])
 @pytest.mark.parametrize("tokens,hidden,k", [(1, 1024, 128), (8, 2048, 256), (128, 8192, 256), (300, 1024, 512), (1024, 2048, 128)])
