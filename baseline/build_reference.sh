@@ -34,4 +34,7 @@ cmake -S "$WORK/src" -B "$WORK/build" -G Ninja -DCMAKE_BUILD_TYPE=Release \
   -DCMAKE_CUDA_COMPILER="${CUDA_HOME:-/usr/local/cuda}/bin/nvcc"
 cmake --build "$WORK/build" -j "$(nproc)"
 cmake --install "$WORK/build" --prefix "$HERE/_ref"
+# the reference's own execution plans (test inputs of its executor), for the plan-compatibility tests
+mkdir -p "$HERE/_ref/share/execution-files"
+cp "$REF_SRC"/test/execution-files/*.json "$HERE/_ref/share/execution-files/"
 echo "installed: $HERE/_ref/lib"

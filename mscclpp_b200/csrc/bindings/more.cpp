@@ -50,8 +50,10 @@ void registerMoreBindings(py::module_& m) {
       "tp_fused",
       [](SymmetricHeap& heap, std::vector<uintptr_t> a, std::vector<uintptr_t> b, uintptr_t partial, uintptr_t residualIn,
          uintptr_t residualOut, uintptr_t out, uintptr_t gamma, uintptr_t rinv, int M, int N, int K, float eps, int blockN,
-         int numGemmCtas, int numReducers, int rowsPerUnit, int mode, bool nvls, uintptr_t stream, uintptr_t timeline) {
+         int numGemmCtas, int numReducers, int rowsPerUnit, int mode, bool nvls, uintptr_t stream, uintptr_t timeline,
+         int sysFence) {
         TpFusedArgs args{};
+        args.sysFence = sysFence;
         args.comm = heap.deviceComm();
         args.shape.M = M;
         args.shape.N = N;
@@ -80,7 +82,7 @@ void registerMoreBindings(py::module_& m) {
       py::arg("heap"), py::arg("a"), py::arg("b"), py::arg("partial"), py::arg("residual_in"), py::arg("residual_out"),
       py::arg("out"), py::arg("gamma"), py::arg("rinv"), py::arg("m"), py::arg("n"), py::arg("k"), py::arg("eps"),
       py::arg("block_n") = 256, py::arg("num_gemm_ctas") = 0, py::arg("num_reducers") = 0, py::arg("rows_per_unit") = 0,
-      py::arg("mode") = 0, py::arg("nvls") = false, py::arg("stream") = 0, py::arg("timeline") = 0);
+      py::arg("mode") = 0, py::arg("nvls") = false, py::arg("stream") = 0, py::arg("timeline") = 0, py::arg("sys_fence") = -1);
   m.def(
       "all_gather_gemm",
       [](SymmetricHeap& heap, uintptr_t aLocal, uintptr_t aFull, std::vector<uintptr_t> b, uintptr_t d, int M, int N, int K, int blockN,
@@ -142,6 +144,7 @@ void registerMoreBindings(py::module_& m) {
                                               reinterpret_cast<float*>(sumsq), M, N, K, blockN, twoSm, nullptr,
                                               reinterpret_cast<cudaStream_t>(stream)),
                       "gemm_residual_sumsq");
+        return tpSumsqParts(N, blockN, twoSm);  // parts per row written to sumsq[part][row]
       },
       py::arg("a"), py::arg("b"), py::arg("residual"), py::arg("h"), py::arg("sumsq"), py::arg("m"), py::arg("n"), py::arg("k"),
       py::arg("block_n") = 256, py::arg("two_sm") = false, py::arg("stream") = 0);
@@ -177,7 +180,7 @@ void registerMoreBindings(py::module_& m) {
       },
       py::arg("heap"), py::arg("x"), py::arg("w"), py::arg("residual_in"), py::arg("residual_out"), py::arg("out"), py::arg("gamma"),
       py::arg("t"), py::arg("n"), py::arg("k"), py::arg("eps") = 1e-5f, py::arg("nvls") = false, py::arg("num_ctas") = 0, py::arg("stream") = 0);
-  m.def("tp_local_fused_workspace_bytes", [](int M) { return tpLocalFusedWorkspaceBytes(M); }, py::arg("m"));
+  m.def("tp_local_fused_workspace_bytes", [](int M, int N) { return tpLocalFusedWorkspaceBytes(M, N); }, py::arg("m"), py::arg("n"));
   m.def(
       "tp_local_fused",
       [](uintptr_t a, uintptr_t b, uintptr_t residual, uintptr_t h, uintptr_t out, uintptr_t gamma, uintptr_t workspace, int M, int N, int K,
@@ -194,13 +197,14 @@ void registerMoreBindings(py::module_& m) {
       py::arg("stream") = 0, py::arg("probe") = 0, py::arg("stamps") = 0);
   m.def(
       "tp_scale_rows_from_sumsq",
-      [](uintptr_t h, uintptr_t sumsq, uintptr_t gamma, uintptr_t out, int M, int N, float eps, uintptr_t stream) {
-        checkCudaMore(launchTpScaleRowsFromSumsq(reinterpret_cast<const void*>(h), reinterpret_cast<const float*>(sumsq),
+      [](uintptr_t h, uintptr_t sumsq, int numParts, uintptr_t gamma, uintptr_t out, int M, int N, float eps, uintptr_t stream) {
+        checkCudaMore(launchTpScaleRowsFromSumsq(reinterpret_cast<const void*>(h), reinterpret_cast<const float*>(sumsq), numParts,
                                                  reinterpret_cast<const void*>(gamma), reinterpret_cast<void*>(out), M, N, eps,
                                                  reinterpret_cast<cudaStream_t>(stream)),
                       "tp_scale_rows_from_sumsq");
       },
-      py::arg("h"), py::arg("sumsq"), py::arg("gamma"), py::arg("out"), py::arg("m"), py::arg("n"), py::arg("eps"), py::arg("stream") = 0);
+      py::arg("h"), py::arg("sumsq"), py::arg("num_parts"), py::arg("gamma"), py::arg("out"), py::arg("m"), py::arg("n"), py::arg("eps"),
+      py::arg("stream") = 0);
   m.def("moe_workspace_bytes", [] { return moeWorkspaceBytes(); });
   m.def(
       "moe_dispatch",
@@ -235,8 +239,11 @@ void registerMoreBindings(py::module_& m) {
   m.def(
       "moe_combine",
       [](SymmetricHeap& heap, uintptr_t topkIdx, uintptr_t topkWeights, uintptr_t slotMap, uintptr_t expertOut, uintptr_t y, int tokens,
-         int hidden, int topk, int numExperts, int nBlocks, uintptr_t stream) {
+         int hidden, int topk, int numExperts, int nBlocks, uintptr_t stream, uintptr_t outScales) {
         MoeCombineArgs a{};
+        a.fp8 = outScales != 0 ? 1 : 0;
+        a.outScales = reinterpret_cast<const float*>(outScales);
+        if (outScales != 0 && !heap.contains(reinterpret_cast<const void*>(outScales))) throw Error("moe_combine: out_scales must be symmetric-heap memory", ErrorCode::InvalidUsage);
         a.comm = heap.deviceComm();
         a.tokens = tokens;
         a.hidden = hidden;
@@ -245,14 +252,22 @@ void registerMoreBindings(py::module_& m) {
         a.topkIdx = reinterpret_cast<const int32_t*>(topkIdx);
         a.topkWeights = reinterpret_cast<const float*>(topkWeights);
         a.slotMap = reinterpret_cast<const int32_t*>(slotMap);
-        a.expertOut = reinterpret_cast<const __nv_bfloat16*>(expertOut);
+        a.expertOut = reinterpret_cast<const void*>(expertOut);
         a.y = reinterpret_cast<__nv_bfloat16*>(y);
         a.emuRanks = heap.emulated() ? heap.world() : 1;
         if (!heap.contains(reinterpret_cast<const void*>(expertOut))) throw Error("moe_combine: expert_out must be symmetric-heap memory", ErrorCode::InvalidUsage);
         checkCudaMore(launchMoeCombine(a, nBlocks, reinterpret_cast<cudaStream_t>(stream)), "moe_combine");
       },
       py::arg("heap"), py::arg("topk_idx"), py::arg("topk_weights"), py::arg("slot_map"), py::arg("expert_out"), py::arg("y"), py::arg("tokens"),
-      py::arg("hidden"), py::arg("topk"), py::arg("num_experts"), py::arg("n_blocks") = 0, py::arg("stream") = 0);
+      py::arg("hidden"), py::arg("topk"), py::arg("num_experts"), py::arg("n_blocks") = 0, py::arg("stream") = 0, py::arg("out_scales") = 0);
+  m.def(
+      "moe_quantize_rows",
+      [](uintptr_t x, uintptr_t q, uintptr_t scales, int rows, int hidden, uintptr_t stream) {
+        checkCudaMore(launchMoeQuantizeRows(reinterpret_cast<const __nv_bfloat16*>(x), reinterpret_cast<void*>(q), reinterpret_cast<float*>(scales),
+                                            rows, hidden, reinterpret_cast<cudaStream_t>(stream)),
+                      "moe_quantize_rows");
+      },
+      py::arg("x"), py::arg("q"), py::arg("scales"), py::arg("rows"), py::arg("hidden"), py::arg("stream") = 0);
   m.def(
       "tp_scale_rows",
       [](uintptr_t h, uintptr_t rinv, uintptr_t gamma, uintptr_t out, int M, int N, uintptr_t stream) {

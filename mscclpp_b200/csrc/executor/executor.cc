@@ -238,7 +238,8 @@ class Resolver {
         plan.groups[g] = grp;
         found = g++;
       }
-      switchChannels_.push_back({ch.at("buffer_type").asString(), found});
+      // older plan files name the buffer "buff"
+      switchChannels_.push_back({ch.at(ch.contains("buffer_type") ? "buffer_type" : "buff").asString(), found});
     }
   }
 

@@ -13,7 +13,8 @@
 //        bytes on NVLink.
 // combine: the reverse direction is a PULL - the source rank reads the expert outputs of its tokens out of the
 //   hosting ranks' buffers (16-byte peer loads), applies the routing weights in fp32 and writes the bf16 result.
-//   No staging buffer and no second pass.
+//   No staging buffer and no second pass. With fp8 = 1 the expert outputs are e4m3 with 1 x 128 scales (quantised by
+//   the expert GEMM's epilogue or by launchMoeQuantizeRows), half the bytes over NVLink.
 // Both end with a cross-rank barrier: after dispatch returns every row sent to this rank has landed; after combine
 // returns the peers are done reading this rank's expert outputs.
 //
@@ -42,6 +43,43 @@ MSCCLPP_DEVICE_INLINE Workspace workspaceOf(const DeviceComm& c, int rank, uint6
   w.cnt = reinterpret_cast<uint32_t*>(c.peerBase[rank] + wsOff);
   w.matrix = reinterpret_cast<uint2*>(c.peerBase[rank] + wsOff + kMoeMaxExperts * sizeof(uint32_t));
   return w;
+}
+
+
+// Quantises the 8 values of one lane to e4m3 with the scale of its 128-element group (the 16 consecutive lanes that
+// hold the group): returns the packed bytes, sets `scale` (the same on all 16 lanes).
+MSCCLPP_DEVICE_INLINE uint2 quantizeWordE4m3(const float (&f)[8], float& scale) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(f[i]));
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  scale = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
+  const float inv = 1.f / scale;
+  uint32_t q2[2];
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * i] * inv, f[4 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * i + 2] * inv, f[4 * i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
+    q2[i] = lo | (hi << 16);
+  }
+  return make_uint2(q2[0], q2[1]);
+}
+
+// 16 e4m3 bytes -> 16 floats (not yet scaled).
+MSCCLPP_DEVICE_INLINE void e4m3x16ToFloat(const uint4& v, float (&f)[16]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    const __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] & 0xffffu), __NV_E4M3);
+    const __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>(w[i] >> 16), __NV_E4M3);
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&lo));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&hi));
+    f[4 * i] = a.x;
+    f[4 * i + 1] = a.y;
+    f[4 * i + 2] = b.x;
+    f[4 * i + 3] = b.y;
+  }
 }
 
 __global__ void __launch_bounds__(kThreads, 1) moeDispatchKernel(MoeDispatchArgs a) {
@@ -181,34 +219,31 @@ __global__ void __launch_bounds__(kThreads, 1) moeDispatchKernel(MoeDispatchArgs
           }
         }
       } else {
-        // 32 lanes x 8 elements = 256 elements per step = two scale groups (lanes 0-15, 16-31)
+        // 32 lanes x 8 elements = 256 elements per step = two scale groups (lanes 0-15, 16-31). Eight steps are loaded
+        // before the first is quantised, so a lane keeps 128 bytes of the row in flight instead of 16.
 #pragma unroll 1
-        for (int w0 = 0; w0 < words; w0 += 32) {
-          const int w = w0 + lane;
-          float f[8];
-          Vec16<bf16>::toFloat(w < words ? ptx::ld_nc_na_v4(src + w) : make_uint4(0, 0, 0, 0), f);
-          float amax = 0.f;
+        for (int w0 = 0; w0 < words; w0 += 32 * 8) {
+          uint4 v[8];
 #pragma unroll
-          for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(f[i]));
-#pragma unroll
-          for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-          const float scale = amax > 0.f ? amax * (1.f / 448.f) : 1.f;
-          const float inv = 1.f / scale;
-          uint32_t q2[2];
-#pragma unroll
-          for (int i = 0; i < 2; i++) {
-            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * i] * inv, f[4 * i + 1] * inv), __NV_SATFINITE, __NV_E4M3);
-            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(f[4 * i + 2] * inv, f[4 * i + 3] * inv), __NV_SATFINITE, __NV_E4M3);
-            q2[i] = lo | (hi << 16);
+          for (int j = 0; j < 8; j++) {
+            const int w = w0 + j * 32 + lane;
+            v[j] = w < words ? ptx::ld_nc_na_v4(src + w) : make_uint4(0, 0, 0, 0);
           }
-          if (w < words) {
-            for (int q = 0; q < nd; q++) {
-              const uint64_t peer = c.peerBase[dstRank[q]];
-              ptx::st_volatile_v2(reinterpret_cast<void*>(peer + recvXOff + static_cast<uint64_t>(dstRow[q]) * a.hidden + static_cast<uint64_t>(w) * 8),
-                                  make_uint2(q2[0], q2[1]));
-              if ((lane & 15) == 0) {
-                float* sc = reinterpret_cast<float*>(peer + recvScalesOff) + static_cast<uint64_t>(dstRow[q]) * scalesPerRow + w / 16;
-                ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(sc), __float_as_uint(scale));
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            const int w = w0 + j * 32 + lane;
+            float f[8];
+            Vec16<bf16>::toFloat(v[j], f);
+            float scale;
+            const uint2 packed = quantizeWordE4m3(f, scale);
+            if (w < words) {
+              for (int q = 0; q < nd; q++) {
+                const uint64_t peer = c.peerBase[dstRank[q]];
+                ptx::st_volatile_v2(reinterpret_cast<void*>(peer + recvXOff + static_cast<uint64_t>(dstRow[q]) * a.hidden + static_cast<uint64_t>(w) * 8), packed);
+                if ((lane & 15) == 0) {
+                  float* sc = reinterpret_cast<float*>(peer + recvScalesOff) + static_cast<uint64_t>(dstRow[q]) * scalesPerRow + w / 16;
+                  ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(sc), __float_as_uint(scale));
+                }
               }
             }
           }
@@ -241,6 +276,8 @@ __global__ void __launch_bounds__(kThreads, 1) moeCombineKernel(MoeCombineArgs a
   const int32_t* slotMap = reinterpret_cast<const int32_t*>(local + (reinterpret_cast<uint64_t>(a.slotMap) - base));
   bf16* y = reinterpret_cast<bf16*>(local + (reinterpret_cast<uint64_t>(a.y) - base));
   const uint64_t outOff = reinterpret_cast<uint64_t>(a.expertOut) - base;
+  const uint64_t scalesOff = a.fp8 ? reinterpret_cast<uint64_t>(a.outScales) - base : 0;
+  const int scalesPerRow = a.hidden / kMoeScaleGroup;
   const int El = a.numExperts / world;
   const int words = a.hidden / 8;
 
@@ -252,17 +289,69 @@ __global__ void __launch_bounds__(kThreads, 1) moeCombineKernel(MoeCombineArgs a
   if (healthy) {
     for (int t = blockIdx.x * warpsPerBlock + (threadIdx.x >> 5); t < a.tokens; t += numWarps) {
       uint64_t rowBase[kMoeMaxTopk];
+      uint64_t scaleBase[kMoeMaxTopk];
       float wgt[kMoeMaxTopk];
       int nd = 0;
       for (int k = 0; k < a.topk; k++) {
         const int e = topkIdx[t * a.topk + k];
         const int row = slotMap[t * a.topk + k];
         if (e < 0 || e >= a.numExperts || row < 0) continue;
-        rowBase[nd] = c.peerBase[e / El] + outOff + static_cast<uint64_t>(row) * a.hidden * 2;
+        rowBase[nd] = c.peerBase[e / El] + outOff + static_cast<uint64_t>(row) * a.hidden * (a.fp8 ? 1 : 2);
+        scaleBase[nd] = c.peerBase[e / El] + scalesOff + static_cast<uint64_t>(row) * scalesPerRow * 4;
         wgt[nd] = weights[t * a.topk + k];
         nd++;
       }
       uint4* dst = reinterpret_cast<uint4*>(y + static_cast<size_t>(t) * a.hidden);
+      if (a.fp8) {
+        // a lane's 16-byte word holds 16 values; the 8 lanes of a 128-element group share one scale
+        const int words16 = a.hidden / 16;
+#pragma unroll 1
+        for (int w0 = 0; w0 < words16; w0 += 32 * 4) {
+          float acc[4][16];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[j][i] = 0.f;
+          }
+          for (int q = 0; q < nd; q++) {
+            uint4 v[4];
+            float sc[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              const int w = w0 + j * 32 + lane;
+              v[j] = make_uint4(0, 0, 0, 0);
+              sc[j] = 0.f;
+              if (w < words16) {
+                v[j] = ptx::ld_nc_na_v4(reinterpret_cast<const void*>(rowBase[q] + static_cast<uint64_t>(w) * 16));
+                sc[j] = __uint_as_float(ptx::ld_relaxed_sys(reinterpret_cast<const uint32_t*>(scaleBase[q]) + w / 8));
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              float f[16];
+              e4m3x16ToFloat(v[j], f);
+              const float m = wgt[q] * sc[j];
+#pragma unroll
+              for (int i = 0; i < 16; i++) acc[j][i] += m * f[i];
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const int w = w0 + j * 32 + lane;
+            if (w < words16) {
+              float lo[8], hi[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) {
+                lo[i] = acc[j][i];
+                hi[i] = acc[j][8 + i];
+              }
+              dst[2 * w] = Vec16<bf16>::fromFloat(lo);
+              dst[2 * w + 1] = Vec16<bf16>::fromFloat(hi);
+            }
+          }
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int w0 = 0; w0 < words; w0 += 32 * 4) {
         float acc[4][8];
@@ -297,6 +386,38 @@ __global__ void __launch_bounds__(kThreads, 1) moeCombineKernel(MoeCombineArgs a
   // my reads are done: the peers may overwrite their expert outputs after this
   if (healthy) rankBarrier(c, rank, 1, blockIdx.x, epoch);
   finishLaunch(c, rank, epoch);
+}
+
+// One warp per row: the dispatch's quantiser as a stand-alone pass (for expert outputs that are to be combined as fp8).
+__global__ void __launch_bounds__(kThreads) moeQuantizeRowsKernel(const bf16* x, uint8_t* q, float* scales, int rows, int hidden) {
+  const int lane = threadIdx.x & 31;
+  const int warpsPerBlock = blockDim.x >> 5;
+  const int words = hidden / 8;
+  const int scalesPerRow = hidden / kMoeScaleGroup;
+  for (int r = blockIdx.x * warpsPerBlock + (threadIdx.x >> 5); r < rows; r += gridDim.x * warpsPerBlock) {
+    const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(r) * hidden);
+#pragma unroll 1
+    for (int w0 = 0; w0 < words; w0 += 32 * 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int w = w0 + j * 32 + lane;
+        v[j] = w < words ? src[w] : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; j++) {
+        const int w = w0 + j * 32 + lane;
+        float f[8];
+        Vec16<bf16>::toFloat(v[j], f);
+        float scale;
+        const uint2 packed = quantizeWordE4m3(f, scale);
+        if (w < words) {
+          *reinterpret_cast<uint2*>(q + static_cast<size_t>(r) * hidden + static_cast<size_t>(w) * 8) = packed;
+          if ((lane & 15) == 0) scales[static_cast<size_t>(r) * scalesPerRow + w / 16] = scale;
+        }
+      }
+    }
+  }
 }
 
 template <typename Kernel, typename Args>
@@ -334,9 +455,20 @@ cudaError_t launchMoeDispatch(const MoeDispatchArgs& args, int nBlocks, cudaStre
   return launchCoop(moeDispatchKernel, args, nBlocks, emu, stream);
 }
 
+cudaError_t launchMoeQuantizeRows(const __nv_bfloat16* x, void* q, float* scales, int rows, int hidden, cudaStream_t stream) {
+  if (rows < 0 || hidden <= 0 || hidden % 256 != 0) return cudaErrorInvalidValue;
+  if (rows == 0) return cudaSuccess;
+  const int warpsPerBlock = kThreads / 32;
+  int blocks = (rows + warpsPerBlock - 1) / warpsPerBlock;
+  if (blocks > 148 * 4) blocks = 148 * 4;
+  moeQuantizeRowsKernel<<<blocks, kThreads, 0, stream>>>(x, static_cast<uint8_t*>(q), scales, rows, hidden);
+  return cudaGetLastError();
+}
+
 cudaError_t launchMoeCombine(const MoeCombineArgs& args, int nBlocks, cudaStream_t stream) {
   const int emu = args.emuRanks > 1 ? args.emuRanks : 1;
   if (!validCommon(args.comm, args.tokens, args.hidden, args.topk, args.numExperts, emu)) return cudaErrorInvalidValue;
+  if (args.fp8 && args.outScales == nullptr) return cudaErrorInvalidValue;
   if (nBlocks <= 0) nBlocks = defaultBlocks(emu);
   if (nBlocks > kBarrierSlots) return cudaErrorInvalidValue;
   return launchCoop(moeCombineKernel, args, nBlocks, emu, stream);

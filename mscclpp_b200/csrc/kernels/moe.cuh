@@ -38,10 +38,18 @@ struct MoeCombineArgs {
   const int32_t* topkIdx;       // [tokens, topk]
   const float* topkWeights;     // [tokens, topk]
   const int32_t* slotMap;       // [tokens, topk] from dispatch
-  const __nv_bfloat16* expertOut;  // symmetric [capacity, hidden]: expert outputs in the rows dispatch assigned
+  const void* expertOut;        // symmetric [capacity, hidden]: expert outputs in the rows dispatch assigned (bf16, or
+                                // e4m3 bytes when fp8 is set)
   __nv_bfloat16* y;             // [tokens, hidden] out: sum_k w[t,k] * expertOut_{rank(e_k)}[slot(t,k)]
   int emuRanks;
+  int fp8;                      // 1: expertOut holds e4m3 with one fp32 scale per 128 elements in outScales (half the
+                                // bytes pulled over NVLink); the weighted sum is still taken in fp32
+  const float* outScales;       // symmetric [capacity, hidden / 128] (fp8 only)
 };
+
+// Quantiser for the fp8 form of the combine (and for tests): q[r] = e4m3(x[r] / scale), scale = amax of each 128-element
+// group / 448. x [rows, hidden] bf16, q [rows, hidden] bytes, scales [rows, hidden / 128]; hidden % 256 == 0.
+cudaError_t launchMoeQuantizeRows(const __nv_bfloat16* x, void* q, float* scales, int rows, int hidden, cudaStream_t stream);
 
 // nBlocks <= 0 picks a default. Both launches are cooperative (grid barriers, and emulated ranks wait on each other).
 cudaError_t launchMoeDispatch(const MoeDispatchArgs& args, int nBlocks, cudaStream_t stream);

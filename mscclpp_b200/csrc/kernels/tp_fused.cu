@@ -24,6 +24,8 @@
 // The reference library has no counterpart: it provides the allreduce only.
 #include "tp_fused.cuh"
 
+#include <cstdlib>
+
 #include <mscclpp/gpu_data_types.hpp>
 
 #include "gemm2_sm100.cuh"
@@ -91,6 +93,7 @@ struct PartialStoreSignal {
   int numNBlk;
   uint32_t epoch;
   unsigned long long* tl;  // this CTA's time-line words or null
+  int sysFence;            // publish with a system-scope fence and release stores
 
   static constexpr bool kBulkStore = false;
   MSCCLPP_DEVICE_INLINE static float convert(float x) { return x; }
@@ -132,7 +135,7 @@ struct PartialStoreSignal {
     }
     if (done != static_cast<uint32_t>(numNBlk)) return;
     *counter = 0;  // every tile of this row block has been counted: ready for the next launch
-    __threadfence();
+    if (sysFence) __threadfence_system(); else __threadfence();
     const int world = comm->world;
     const int u0 = (mBlk * gemm::kBlockM) / rowsPerUnit;
     int u1 = ((mBlk + 1) * gemm::kBlockM + rowsPerUnit - 1) / rowsPerUnit;
@@ -141,10 +144,15 @@ struct PartialStoreSignal {
     // or multimem) goes through, so "performed at this GPU's L2" is all a reader needs; the flag goes out after it.
     // A system-scope fence here also waits for this SM's share of the NVLink queues to drain: once the reducers
     // saturate the links that took tens of microseconds per row block and stalled the GEMM CTA that published it.
+    // sysFence restores the conservative form (system-scope fence, release stores) for comparison and for fabrics
+    // where a peer's load might not go through this GPU's L2.
     for (int o = 0; o < world; o++) {
       // does rank o own one of the units [u0, u1)?
       const int first = (o - (u0 % world) + world) % world;
-      if (first < u1 - u0) ptx::st_relaxed_sys(readyFlag(*comm, o, mBlk, rank), epoch);
+      if (first < u1 - u0) {
+        if (sysFence) ptx::st_release_sys(readyFlag(*comm, o, mBlk, rank), epoch);
+        else ptx::st_relaxed_sys(readyFlag(*comm, o, mBlk, rank), epoch);
+      }
     }
     if (tl) tl[13] += ptx::globaltimer() - tIn;
   }
@@ -509,7 +517,8 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
     constexpr int kTileN = kBlockN == 0 ? gemm::Config2::kBlockN : kBlockN;
     PartialStoreSignal epi{&c, reinterpret_cast<bf16*>(c.peerBase[rank] + partialOff), a.shape.M, a.shape.N, rank,
                            a.rowsPerUnit, numUnits, a.shape.N / kTileN, epoch,
-                           (a.timeline != nullptr && blockIdx.y == 0) ? a.timeline + static_cast<size_t>(blockIdx.x) * kTimelineWords : nullptr};
+                           (a.timeline != nullptr && blockIdx.y == 0) ? a.timeline + static_cast<size_t>(blockIdx.x) * kTimelineWords : nullptr,
+                           a.sysFence};
     if constexpr (kBlockN == 0) {
       gemm::gemmCtaPair(&maps.a[blockIdx.y], &maps.b[blockIdx.y], a.shape, blockIdx.x / 2, a.numGemmCtas / 2, gate, epi, c.status,
                         c.timeoutNs, smemRaw);
@@ -535,7 +544,10 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1) tpReduceNormKernel(const
 }
 
 // Epilogue of the single-GPU layer: h = bf16(acc) + residual (rounded to bf16 like the unfused composition), stored;
-// the row's sum of squares of the rounded values is added to sumsq[row] (one fp32 reduction per row and 64-column block).
+// the sum of squares of the rounded values over the columns that ONE epilogue warp handles in a tile goes to
+// sumsq[part][row] (part = those columns' index, N / (64 * blocksPerWarp) parts per row): every word of the table is
+// written exactly once per launch, so nothing has to be cleared before it and no atomics are involved. Whoever needs a
+// row's sum adds up its parts.
 // The residual of a block is requested one block ahead (the first at tileBegin, before the accumulator is ready), with the
 // row-contiguous lane mapping of the staging buffer: every load and store covers complete 128-byte lines.
 struct ResidualSumsqStore {
@@ -543,12 +555,14 @@ struct ResidualSumsqStore {
   static constexpr bool kBulkStore = false;
   const bf16* residual;  // [M, N] or null
   bf16* h;               // [M, N]
-  float* sumsq;          // [M]
+  float* sumsq;          // [N / (64 * blocksPerWarp)][M]
   int M, N;
   int blocksPerWarp;  // 64-column blocks per warp and tile
-  int probe;          // diagnostics, 0 in production: bit 4 no residual loads, bit 5 no sum-of-squares atomics, bit 6 no h
+  int probe;          // diagnostics, 0 in production: bit 4 no residual loads, bit 5 no sum-of-squares stores, bit 6 no h
                       // stores, bit 7 no normalisation (results are then wrong; timing only)
   uint4 pre[8];       // residual words of the block that comes next
+  float ssAcc[8];     // this lane's rows: sum of squares over the blocks of the current tile so far
+  MSCCLPP_DEVICE_INLINE int numParts() const { return N / (64 * blocksPerWarp); }
   MSCCLPP_DEVICE_INLINE static float convert(float x) { return x; }
   MSCCLPP_DEVICE_INLINE void prefetch(int row0, int col0, int lane) {
     if (residual == nullptr || (probe & 16)) return;
@@ -575,9 +589,12 @@ struct ResidualSumsqStore {
       ss += __shfl_xor_sync(0xffffffffu, ss, 1);
       ss += __shfl_xor_sync(0xffffffffu, ss, 2);
       ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+      ssAcc[i] = b == 0 ? ss : ssAcc[i] + ss;
       if (row < M) {
         if (!(probe & 64)) *reinterpret_cast<uint4*>(h + static_cast<size_t>(row) * N + col0 + gemm::stagedCol(lane)) = packed;
-        if ((lane & 7) == 0 && !(probe & 32)) atomicAdd(sumsq + row, ss);
+        if (b == blocksPerWarp - 1 && (lane & 7) == 0 && !(probe & 32)) {
+          sumsq[static_cast<size_t>((col0 - b * 64) / (64 * blocksPerWarp)) * M + row] = ssAcc[i];
+        }
       }
     }
     __syncwarp();
@@ -624,7 +641,11 @@ struct ResidualNormStore {
 
   MSCCLPP_DEVICE_INLINE void normaliseRow(int row, int lane) const {
     const int N = base.N;
-    const float rinv = rsqrtf(__ldcg(base.sumsq + row) / static_cast<float>(N) + eps);
+    float total = 0.f;
+    for (int p = lane; p < base.numParts(); p += 32) total += __ldcg(base.sumsq + static_cast<size_t>(p) * base.M + row);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    const float rinv = rsqrtf(total / static_cast<float>(N) + eps);
     const __nv_bfloat16 hi1 = __float2bfloat16_rn(rinv);
     const __nv_bfloat162 hi = __bfloat162bfloat162(hi1);
     const __nv_bfloat162 lo = __float2bfloat162_rn(rinv - __bfloat162float(hi1));
@@ -760,26 +781,49 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
   }
 }
 
-__global__ void __launch_bounds__(512) tpScaleRowsSumsqKernel(const bf16* h, const float* sumsq, const bf16* gamma, bf16* out, int M, int N,
-                                                              float eps) {
-  const int unitsPerRow = N / 8;
-  const size_t total = static_cast<size_t>(M) * unitsPerRow;
-  const float invN = 1.f / static_cast<float>(N);
-  for (size_t u = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < total; u += static_cast<size_t>(gridDim.x) * blockDim.x) {
-    const int row = static_cast<int>(u / unitsPerRow), ru = static_cast<int>(u % unitsPerRow);
-    float f[8];
-    Vec16<bf16>::toFloat(*reinterpret_cast<const uint4*>(h + u * 8), f);
-    const float s = rsqrtf(sumsq[row] * invN + eps);
-    if (gamma) {
-      float g[8];
-      Vec16<bf16>::toFloat(*reinterpret_cast<const uint4*>(gamma + static_cast<size_t>(ru) * 8), g);
+// out[row] = h[row] * rsqrt(sum of the row's parts / N + eps) * gamma. `tpr` threads (a multiple of 32) share a row; every
+// warp adds up the parts for itself. Eight 16-byte loads are in flight per thread.
+__global__ void __launch_bounds__(512) tpScaleRowsPartsKernel(const bf16* h, const float* parts, int numParts, const bf16* gamma, bf16* out,
+                                                              int M, int N, float eps, int tpr) {
+  const int lane = threadIdx.x & 31;
+  const int groupsPerBlock = blockDim.x / tpr;
+  const int inGroup = threadIdx.x % tpr;
+  const int words = N / 8;
+  const uint4* g4 = reinterpret_cast<const uint4*>(gamma);
+  for (int row = blockIdx.x * groupsPerBlock + threadIdx.x / tpr; row < M; row += gridDim.x * groupsPerBlock) {
+    float total = 0.f;
+    for (int p = lane; p < numParts; p += 32) total += parts[static_cast<size_t>(p) * M + row];
 #pragma unroll
-      for (int i = 0; i < 8; i++) f[i] = f[i] * s * g[i];
-    } else {
+    for (int o = 16; o > 0; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    const float sc = rsqrtf(total / static_cast<float>(N) + eps);
+    const uint4* src = reinterpret_cast<const uint4*>(h + static_cast<size_t>(row) * N);
+    uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * N);
+    for (int w0 = inGroup; w0 < words; w0 += tpr * 8) {
+      uint4 v[8];
 #pragma unroll
-      for (int i = 0; i < 8; i++) f[i] = f[i] * s;
+      for (int k = 0; k < 8; k++) {
+        const int w = w0 + k * tpr;
+        if (w < words) v[k] = ptx::ld_input_v4(src + w);
+      }
+#pragma unroll
+      for (int k = 0; k < 8; k++) {
+        const int w = w0 + k * tpr;
+        if (w < words) {
+          float f[8];
+          Vec16<bf16>::toFloat(v[k], f);
+          if (gamma != nullptr) {
+            float g[8];
+            Vec16<bf16>::toFloat(__ldg(g4 + w), g);
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = f[i] * sc * g[i];
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = f[i] * sc;
+          }
+          dst[w] = Vec16<bf16>::fromFloat(f);
+        }
+      }
     }
-    *reinterpret_cast<uint4*>(out + u * 8) = Vec16<bf16>::fromFloat(f);
   }
 }
 
@@ -862,6 +906,10 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   if (args.nvls && args.comm.mcBase == 0) return cudaErrorInvalidValue;
   const int emu = args.emuRanks > 1 ? args.emuRanks : 1;
   if (emu > 8) return cudaErrorInvalidValue;
+  if (args.sysFence < 0) {
+    const char* env = std::getenv("MSCCLPP_TP_SYS_FENCE");
+    args.sysFence = (env != nullptr && env[0] != '\0' && env[0] != '0') ? 1 : 0;
+  }
   args.shape.aBoxRows = M < gemm::kBlockM ? M : gemm::kBlockM;
   args.shape.rowMajorTiles = 1;
   if (args.mode == 2) {
@@ -970,14 +1018,18 @@ cudaError_t launchLocalTyped(const CUtensorMap& ta, const CUtensorMap& tb, gemm:
   }
 }
 
+int tpSumsqParts(int N, int blockN, bool twoSm) {
+  const int blocksPerWarp = twoSm ? gemm::Config2::kColsPerWarp / 64 : (blockN >= 128 ? blockN / 128 : 1);
+  return N / (64 * blocksPerWarp);
+}
+
 cudaError_t launchGemmResidualSumsq(const void* A, const void* B, const void* residual, void* h, float* sumsq, int M, int N, int K,
                                     int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || K % gemm::kBlockK != 0 || N % 8 != 0) return cudaErrorInvalidValue;
   if (twoSm && (M < gemm::Config2::kPairM || N % gemm::Config2::kBlockN != 0)) return cudaErrorInvalidValue;
   if (!twoSm && (blockN != 64 && blockN != 128 && blockN != 256)) return cudaErrorInvalidValue;
   if (!twoSm && N % blockN != 0) return cudaErrorInvalidValue;
-  cudaError_t e = cudaMemsetAsync(sumsq, 0, static_cast<size_t>(M) * sizeof(float), stream);
-  if (e != cudaSuccess) return e;
+  cudaError_t e = cudaSuccess;
   gemm::Shape shape{M, N, K, M < gemm::kBlockM ? M : gemm::kBlockM, 0, 0, 0};
   if (twoSm) shape.aBoxRows = gemm::kBlockM;
   CUtensorMap ta, tb;
@@ -1027,10 +1079,18 @@ cudaError_t launchLocalFusedTyped(const CUtensorMap& ta, const CUtensorMap& tb, 
   }
 }
 
-size_t tpLocalFusedWorkspaceBytes(int M) {
-  // [M] sums of squares, [row blocks, rounded up to the pair core's 256-row tiles] arrival counters, one unit counter
+namespace {
+// words of counters at the start of the one-kernel path's workspace: [row blocks, rounded up to the pair core's 256-row
+// tiles] arrival counters and one unit counter, rounded up to a multiple of four words
+size_t localFusedCounterWords(int M) {
   const size_t blocks = 2 * static_cast<size_t>((M + gemm::Config2::kPairM - 1) / gemm::Config2::kPairM);
-  return (static_cast<size_t>(M) + blocks + 1) * 4;
+  return (blocks + 1 + 3) / 4 * 4;
+}
+}  // namespace
+
+size_t tpLocalFusedWorkspaceBytes(int M, int N) {
+  // the counters (cleared before every launch), then the [N / 64][M] parts of the rows' sums of squares (never cleared)
+  return (localFusedCounterWords(M) + static_cast<size_t>(M) * (N / 64)) * 4;
 }
 
 cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residual, void* h, void* out, const void* gamma, void* workspace,
@@ -1043,7 +1103,7 @@ cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residua
   if ((reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(residual) |
        reinterpret_cast<uintptr_t>(gamma) | reinterpret_cast<uintptr_t>(workspace)) & 15)
     return cudaErrorInvalidValue;
-  cudaError_t e = cudaMemsetAsync(workspace, 0, tpLocalFusedWorkspaceBytes(M), stream);
+  cudaError_t e = cudaMemsetAsync(workspace, 0, localFusedCounterWords(M) * 4, stream);
   if (e != cudaSuccess) return e;
   // row blocks are walked one after the other (all their N tiles first), so that they complete in order and early
   gemm::Shape shape{M, N, K, M < gemm::kBlockM ? M : gemm::kBlockM, 1, 0, 0, probe & 15, stamps};
@@ -1058,14 +1118,14 @@ cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residua
   ResidualNormStore epi{};
   epi.base.residual = static_cast<const bf16*>(residual);
   epi.base.h = static_cast<bf16*>(h);
-  epi.base.sumsq = static_cast<float*>(workspace);
+  epi.base.sumsq = static_cast<float*>(workspace) + localFusedCounterWords(M);
   epi.base.M = M;
   epi.base.N = N;
   epi.base.blocksPerWarp = tileN / (epiWarps / 4) / 64;
   epi.base.probe = probe;
   epi.out = static_cast<bf16*>(out);
   epi.gamma = static_cast<const bf16*>(gamma);
-  epi.blockCount = reinterpret_cast<uint32_t*>(static_cast<float*>(workspace) + M);
+  epi.blockCount = static_cast<uint32_t*>(workspace);
   epi.nextUnit = epi.blockCount + 2 * ((M + gemm::Config2::kPairM - 1) / gemm::Config2::kPairM);
   epi.fullCount = static_cast<uint32_t>((N / tileN) * epiWarps);
   epi.eps = eps;
@@ -1085,16 +1145,17 @@ cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residua
   }
 }
 
-cudaError_t launchTpScaleRowsFromSumsq(const void* h, const float* sumsq, const void* gamma, void* out, int M, int N, float eps,
-                                       cudaStream_t stream) {
-  if (N % 8 != 0) return cudaErrorInvalidValue;
-  const size_t total = static_cast<size_t>(M) * (N / 8);
-  int blocks = static_cast<int>((total + 511) / 512);
-  const int cap = gemm::smCount() * 4;
-  if (blocks > cap) blocks = cap;
-  if (blocks < 1) blocks = 1;
-  tpScaleRowsSumsqKernel<<<blocks, 512, 0, stream>>>(static_cast<const bf16*>(h), sumsq, static_cast<const bf16*>(gamma), static_cast<bf16*>(out),
-                                                      M, N, eps);
+cudaError_t launchTpScaleRowsFromSumsq(const void* h, const float* sumsqParts, int numParts, const void* gamma, void* out, int M, int N,
+                                       float eps, cudaStream_t stream) {
+  if (N % 8 != 0 || numParts < 1 || M < 1) return cudaErrorInvalidValue;
+  // few rows: a whole thread block per row (one batch of loads); many rows: a warp per row
+  const int sms = gemm::smCount();
+  const int tpr = M <= 2 * sms ? 512 : (M <= 16 * sms ? 128 : 32);
+  const int groupsPerBlock = 512 / tpr;
+  int blocks = (M + groupsPerBlock - 1) / groupsPerBlock;
+  if (blocks > sms * 4) blocks = sms * 4;
+  tpScaleRowsPartsKernel<<<blocks, 512, 0, stream>>>(static_cast<const bf16*>(h), sumsqParts, numParts, static_cast<const bf16*>(gamma),
+                                                      static_cast<bf16*>(out), M, N, eps, tpr);
   return cudaGetLastError();
 }
 

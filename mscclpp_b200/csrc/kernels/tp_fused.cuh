@@ -29,6 +29,9 @@ struct TpFusedArgs {
   int nvls;                     // multimem through comm.mcBase instead of peer loads/stores
   int emuRanks;                 // > 1: that many emulated ranks in one cooperative launch (tests)
   int noFlags;                  // set by launchTpReduceNorm: rows are complete at kernel start, no per-block flags
+  int sysFence;                 // 1: row-block flags go out as fence.acq_rel.sys + st.release.sys (the conservative form);
+                                // 0 (default): GPU-scope fence + relaxed system-scope store. -1 on entry = read the
+                                // environment variable MSCCLPP_TP_SYS_FENCE (unset = 0).
   unsigned long long* timeline; // optional device buffer, kTimelineWords words per CTA (of emulated rank 0's grid layout):
                                 // [0] CTA start, [1] GEMM part done, [2] reducer part done (all globaltimer ns),
                                 // [3] rows reduced by group 0, [4] ns group 0 waited for readiness, [5] ns it spent on rows,
@@ -60,20 +63,22 @@ cudaError_t launchTpFused(const TpFusedArgs& args, const void* const* A, const v
 // Starts with a cross-rank barrier (every rank's partial is final), then every CTA is a reducer.
 cudaError_t launchTpReduceNorm(const TpFusedArgs& args, int numCtas, cudaStream_t stream);
 
-// One GPU, no collective: h = bf16(A * B^T) + residual written by the GEMM epilogue, which also adds every row's
-// sum of squares into sumsq[M] (fp32, zeroed here first); launchTpScaleRowsFromSumsq then produces the RMSNorm.
+// One GPU, no collective: h = bf16(A * B^T) + residual written by the GEMM epilogue, which also writes every row's
+// sum of squares in parts: sumsq[part][row], tpSumsqParts(N, blockN, twoSm) parts of M floats each, every word written
+// exactly once (no clearing, no atomics); launchTpScaleRowsFromSumsq adds the parts up and produces the RMSNorm.
 // twoSm selects the 256 x 256 pair tiles (M >= 256, N % 256 == 0), else one-SM tiles of blockN columns.
+int tpSumsqParts(int N, int blockN, bool twoSm);
 cudaError_t launchGemmResidualSumsq(const void* A, const void* B, const void* residual, void* h, float* sumsq, int M, int N, int K,
                                     int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream);
-// out = h * rsqrt(sumsq[row] / N + eps) * gamma
-cudaError_t launchTpScaleRowsFromSumsq(const void* h, const float* sumsq, const void* gamma, void* out, int M, int N, float eps,
-                                       cudaStream_t stream);
+// out = h * rsqrt(sum_p sumsqParts[p][row] / N + eps) * gamma
+cudaError_t launchTpScaleRowsFromSumsq(const void* h, const float* sumsqParts, int numParts, const void* gamma, void* out, int M, int N,
+                                       float eps, cudaStream_t stream);
 
 // The same single-GPU layer in ONE launch: h = bf16(A * B^T) + residual and out = h * rsqrt(mean(h^2) + eps) * gamma.
 // Rows are normalised by the epilogue warps as soon as their 128-row block is complete, while the MMAs of later blocks
 // run. `stamps`: optional zeroed device buffer of gemm::kStampWords words per CTA that receives a time line (one-SM tiles).
-// `workspace`: tpLocalFusedWorkspaceBytes(M) bytes of device memory, 16-byte aligned (cleared here on `stream`).
-size_t tpLocalFusedWorkspaceBytes(int M);
+// `workspace`: tpLocalFusedWorkspaceBytes(M, N) bytes of device memory, 16-byte aligned (its counters are cleared here on `stream`).
+size_t tpLocalFusedWorkspaceBytes(int M, int N);
 cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residual, void* h, void* out, const void* gamma, void* workspace,
                                int M, int N, int K, float eps, int blockN, bool twoSm, DeviceStatus* status, cudaStream_t stream,
                                int probe = 0, unsigned long long* stamps = nullptr);
@@ -82,10 +87,10 @@ cudaError_t launchTpLocalFused(const void* A, const void* B, const void* residua
 // slab of output columns, the slabs meet the other ranks in a one-shot LL packet allreduce done by the same thread
 // blocks, residual add and RMSNorm follow in registers (see tp_decode.cu). Every rank ends up with the whole result.
 constexpr int kTpDecodeMaxTokens = 8;
-// this kernel's words in a heap's aux flag region: [kBarrierSlots][kTpDecodeMaxTokens] fp32 row sums, behind the flags of
+// this kernel's words in a heap's aux flag region: [kBarrierSlots][kTpDecodeMaxTokens] {fp32 row sum, epoch} pairs, behind the flags of
 // the fused layer, of the all-gather GEMM and of the pipelined allreduce
 constexpr uint64_t kTpDecodeAuxOffset = (4096ull * (kMaxRanks + 1) + 4096ull) * 4ull + 2ull * kBarrierSlots * kMaxRanks * 8ull;
-static_assert(kTpDecodeAuxOffset + static_cast<uint64_t>(kBarrierSlots) * kTpDecodeMaxTokens * 4 <= kAuxFlagBytes, "aux flag region too small");
+static_assert(kTpDecodeAuxOffset % 8 == 0 && kTpDecodeAuxOffset + static_cast<uint64_t>(kBarrierSlots) * kTpDecodeMaxTokens * 8 <= kAuxFlagBytes, "aux flag region too small");
 struct TpDecodeArgs {
   DeviceComm comm;
   const __nv_bfloat16* x[8];      // [T, K] activations of (emulated) rank e; real multi-GPU use fills entry 0
@@ -94,7 +99,7 @@ struct TpDecodeArgs {
   __nv_bfloat16* residualOut;     // symmetric-heap [T, N] (may be null)
   __nv_bfloat16* out;             // symmetric-heap [T, N]
   const __nv_bfloat16* gamma;     // [N] local (may be null)
-  int T, N, K;                    // T <= kTpDecodeMaxTokens, N % 8 == 0, K % 256 == 0, T * K * 4 bytes of shared memory
+  int T, N, K;                    // T <= kTpDecodeMaxTokens, N % 8 == 0, K % 256 == 0, 128 KB + T * K * 4 bytes of shared memory
   float eps;
   int nvls;                       // packets leave through one multimem.st instead of world - 1 peer stores
   int emuRanks;

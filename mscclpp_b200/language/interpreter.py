@@ -234,6 +234,7 @@ class PlanInterpreter:
             for i in range(iters):
                 for inner in op["ops"]:
                     yield from self._exec(g, tb, inner, (unit, i))
+                    yield "progress"  # an inner op that completed may have unblocked another thread block
             return
         if name == "barrier":
             key = (rank, op["barrier_id"])
@@ -366,7 +367,7 @@ class PlanInterpreter:
                 cid = self._tb_channel(tb, "switch", o["switch_channel_id"])
                 chans = [c for c in g["channels"] if c["channel_type"] == "switch"]
                 ch = chans[cid]
-                return ch["buffer_type"], ch["rank_groups"][0]["ranks"]
+                return ch.get("buffer_type", ch.get("buff")), ch["rank_groups"][0]["ranks"]  # "buff": older plan files
             if name == "glres":
                 btype, ranks = switch(src[0])
                 so, n = span(src[0])
@@ -423,7 +424,7 @@ def validate_plan(plan: Union[str, dict]) -> None:
                         raise PlanError(f"rank {g['id']}: channel to invalid rank {peer}")
         for tb in g["threadblocks"]:
             chan_counts = {c["channel_type"]: len(c["channel_ids"]) for c in tb["channels"]}
-            ref_counts = {r["access_channel_type"]: len(r["remote_buffer_ids"]) for r in tb["remote_buffer_refs"]}
+            ref_counts = {r["access_channel_type"]: len(r["remote_buffer_ids"]) for r in tb.get("remote_buffer_refs", [])}
 
             def check_ops(ops):
                 for op in ops:

@@ -7,8 +7,10 @@ combine (pull the expert outputs back and apply the routing weights), one kernel
     y = disp.combine(topk_idx, topk_weights, handle)
 
 With ``fp8=True`` rows travel as e4m3 with one fp32 scale per 128 elements (``recv_x`` is uint8, scales in
-``disp.recv_scales``), which halves the NVLink bytes of the dispatch. The reference library has no MoE layer; it
-ships the bulk-copy primitives for writing one.
+``disp.recv_scales``), which halves the NVLink bytes of the dispatch. With ``fp8_combine=True`` the way back is halved
+too: the expert outputs are combined from ``disp.expert_out_q`` (e4m3) and ``disp.expert_out_scales``, which the
+experts' GEMM epilogue fills directly or ``disp.quantize_expert_out(rows)`` derives from ``disp.expert_out``. The
+reference library has no MoE layer; it ships the bulk-copy primitives for writing one.
 """
 from __future__ import annotations
 
@@ -22,7 +24,7 @@ from .._core.symm import SymmetricMemory
 
 class ExpertParallelDispatcher:
     def __init__(self, symm: SymmetricMemory, num_experts: int = 64, hidden: int = 4096, max_tokens: int = 4096, topk: int = 2,
-                 capacity: Optional[int] = None, fp8: bool = False):
+                 capacity: Optional[int] = None, fp8: bool = False, fp8_combine: bool = False):
         assert num_experts % symm.world == 0 and hidden % 256 == 0
         self.symm, self.num_experts, self.hidden, self.max_tokens, self.topk, self.fp8 = symm, num_experts, hidden, max_tokens, topk, fp8
         self.experts_per_rank = num_experts // symm.world
@@ -33,6 +35,9 @@ class ExpertParallelDispatcher:
         self.recv_scales = symm.tensor((self.capacity, hidden // 128), torch.float32) if fp8 else None
         self.recv_src = symm.tensor((self.capacity,), torch.int32)
         self.expert_out = symm.tensor((self.capacity, hidden), torch.bfloat16)
+        self.fp8_combine = fp8_combine
+        self.expert_out_q = symm.tensor((self.capacity, hidden), torch.uint8) if fp8_combine else None
+        self.expert_out_scales = symm.tensor((self.capacity, hidden // 128), torch.float32) if fp8_combine else None
         self.workspace = symm.tensor((n.moe_workspace_bytes() // 4,), torch.int32)
         self.slot_map = symm.tensor((max_tokens, topk), torch.int32)
         self.recv_counts = symm.tensor((self.experts_per_rank + 1,), torch.int32)
@@ -60,17 +65,33 @@ class ExpertParallelDispatcher:
                        self.workspace.data_ptr(), t, self.hidden, self.topk, self.num_experts, self.capacity, self.fp8, n_blocks, st)
         return self.recv_x, self.recv_counts, self.slot_map[:t]
 
+    def quantize_expert_out(self, rows: int, rank: Optional[int] = None, stream: Optional[torch.cuda.Stream] = None) -> None:
+        """Quantise rows [0, rows) of expert_out into expert_out_q / expert_out_scales (e4m3, one scale per 128 elements).
+        rank: which emulated rank's buffers (emulated heaps only)."""
+        assert self.fp8_combine, "construct the dispatcher with fp8_combine=True"
+        view = (lambda ten: self.symm.rank_view(ten, rank)) if (self.symm.emulated_mode and rank is not None) else (lambda ten: ten)
+        st = (stream or torch.cuda.current_stream()).cuda_stream
+        native.load().moe_quantize_rows(view(self.expert_out).data_ptr(), view(self.expert_out_q).data_ptr(), view(self.expert_out_scales).data_ptr(),
+                                        rows, self.hidden, st)
+
     def combine(self, topk_idx: torch.Tensor, topk_weights: torch.Tensor, slot_map: torch.Tensor, expert_out: Optional[torch.Tensor] = None,
-                out: Optional[torch.Tensor] = None, n_blocks: int = 0, stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
-        """y[t] = sum_k topk_weights[t, k] * expert_out(rank of expert k)[slot_map[t, k]]; returns y [T, hidden] bf16."""
+                out: Optional[torch.Tensor] = None, n_blocks: int = 0, stream: Optional[torch.cuda.Stream] = None,
+                fp8: Optional[bool] = None) -> torch.Tensor:
+        """y[t] = sum_k topk_weights[t, k] * expert_out(rank of expert k)[slot_map[t, k]]; returns y [T, hidden] bf16.
+        fp8 (default: the dispatcher's fp8_combine): pull the rows from expert_out_q / expert_out_scales instead."""
         n = native.load()
         t = topk_idx.shape[0]
-        expert_out = self.expert_out if expert_out is None else expert_out
+        fp8 = self.fp8_combine if fp8 is None else fp8
+        if fp8:
+            assert self.fp8_combine and expert_out is None
+            expert_out = self.expert_out_q
+        else:
+            expert_out = self.expert_out if expert_out is None else expert_out
         out = self.y[:t] if out is None else out
         assert topk_weights.dtype == torch.float32 and topk_weights.shape == (t, self.topk) and slot_map.shape == (t, self.topk)
         st = (stream or torch.cuda.current_stream()).cuda_stream
         n.moe_combine(self.symm.heap, topk_idx.data_ptr(), topk_weights.data_ptr(), slot_map.data_ptr(), expert_out.data_ptr(), out.data_ptr(),
-                      t, self.hidden, self.topk, self.num_experts, n_blocks, st)
+                      t, self.hidden, self.topk, self.num_experts, n_blocks, st, self.expert_out_scales.data_ptr() if fp8 else 0)
         return out
 
     # ------------------------------------------------------------------ helpers for tests and emulated heaps

@@ -42,6 +42,7 @@ class RowParallelLinearNorm:
         self.gamma.fill_(1.0)
         self.rinv = symm.tensor((max_tokens,), torch.float32)
         self._local_ws = None  # workspace of the one-kernel single-GPU path, made on first use
+        self._sumsq_parts = None  # parts of the rows' sums of squares between the two launches of the two-kernel path
         self.launches_per_forward = 1  # forward_fused, mode 0
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, algo: Optional[str] = None,
@@ -62,7 +63,8 @@ class RowParallelLinearNorm:
     def forward_fused(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, mode: Optional[int] = None,
                       nvls: Optional[bool] = None, block_n: int = 0, num_reducers: int = 0, num_gemm_ctas: int = 0,
                       rows_per_unit: int = 0, stream: Optional[torch.cuda.Stream] = None,
-                      emulated_inputs=None, timeline: Optional[torch.Tensor] = None, row_offset: int = 0) -> Tuple[torch.Tensor, torch.Tensor]:
+                      emulated_inputs=None, timeline: Optional[torch.Tensor] = None, row_offset: int = 0,
+                      sys_fence: Optional[bool] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """Same result as forward(), in ONE kernel: GEMM tiles, cross-rank reduction, residual add and norm
         overlap tile by tile. mode 1 halves NVLink traffic by broadcasting h and 1/rms only and finishing
         `out` with a local pass (second, local-only launch); mode 0 is one launch. Default: mode 1 from 1024 tokens on
@@ -74,7 +76,10 @@ class RowParallelLinearNorm:
         done, reducer part done, rows reduced / ns waited / ns worked by the CTA's first reducer group, first row done,
         and (words 8-10) the ns of the work spent in the gather, the residual math and the broadcast stores.
         row_offset: the rows of x are rows [row_offset, row_offset + T) of the layer's buffers (the same on every rank);
-        used to run a long sequence as a few launches, e.g. while later rows are still arriving from the host."""
+        used to run a long sequence as a few launches, e.g. while later rows are still arriving from the host.
+        sys_fence: how a finished row block is announced to the peers. False: GPU-scope fence, then relaxed system-scope
+        flag stores (the default: the partial product lives in this GPU's memory and every peer load passes through
+        this GPU's L2). True: system-scope fence and release stores. None: environment variable MSCCLPP_TP_SYS_FENCE."""
         from .._core import native
 
         n = native.load()
@@ -99,7 +104,7 @@ class RowParallelLinearNorm:
         n.tp_fused(self.symm.heap, a_ptrs, b_ptrs, self.partial[rows].data_ptr(), self.residual_in[rows].data_ptr(),
                    self.residual_out[rows].data_ptr(), self.out[rows].data_ptr(), self.gamma.data_ptr(), self.rinv[rows].data_ptr(), t,
                    self.out_features, self.k_shard, self.eps, bn, num_gemm_ctas, num_reducers, rows_per_unit, mode, nvls, s,
-                   0 if timeline is None else timeline.data_ptr())
+                   0 if timeline is None else timeline.data_ptr(), -1 if sys_fence is None else int(bool(sys_fence)))
         if mode == 1:
             ranks = range(self.symm.world) if self.symm.emulated_mode else [self.symm.rank]
             for r in ranks:  # one local pass per (emulated) rank
@@ -162,7 +167,7 @@ class RowParallelLinearNorm:
             one_kernel = t <= 512
         s = (stream or torch.cuda.current_stream()).cuda_stream
         if one_kernel:
-            ws_bytes = (n.tp_local_fused_workspace_bytes(self.max_tokens) + 255) // 256 * 256
+            ws_bytes = (n.tp_local_fused_workspace_bytes(self.max_tokens, self.out_features) + 255) // 256 * 256
             if self._local_ws is None:  # one workspace per 256-row-aligned launch that may be in flight: indexed by row offset
                 self._local_ws = torch.empty((8, ws_bytes // 4), dtype=torch.float32, device=self.symm.device)
             ws = self._local_ws[(row_offset // 256) % 8]
@@ -170,9 +175,15 @@ class RowParallelLinearNorm:
                              self.out[rows].data_ptr(), self.gamma.data_ptr(), ws.data_ptr(), t, self.out_features, self.k_shard,
                              self.eps, pick_block_n(t, self.out_features), two_sm, 0, s, probe, 0 if timeline is None else timeline.data_ptr())
             return self.out[rows], self.residual_out[rows]
-        n.gemm_residual_sumsq(x.data_ptr(), self.weight.data_ptr(), self.residual_in[rows].data_ptr(), self.residual_out[rows].data_ptr(),
-                              self.rinv[rows].data_ptr(), t, self.out_features, self.k_shard, pick_block_n(t, self.out_features), two_sm, s)
-        n.tp_scale_rows_from_sumsq(self.residual_out[rows].data_ptr(), self.rinv[rows].data_ptr(), self.gamma.data_ptr(),
+        # the rows' sums of squares travel between the two launches in parts ([parts][t] floats, nothing to clear); launches
+        # on disjoint row ranges use disjoint pieces of the buffer
+        per_row = self.out_features // 64
+        if self._sumsq_parts is None:
+            self._sumsq_parts = torch.empty((self.max_tokens * per_row,), dtype=torch.float32, device=self.symm.device)
+        parts_buf = self._sumsq_parts[row_offset * per_row:]
+        parts = n.gemm_residual_sumsq(x.data_ptr(), self.weight.data_ptr(), self.residual_in[rows].data_ptr(), self.residual_out[rows].data_ptr(),
+                                      parts_buf.data_ptr(), t, self.out_features, self.k_shard, pick_block_n(t, self.out_features), two_sm, s)
+        n.tp_scale_rows_from_sumsq(self.residual_out[rows].data_ptr(), parts_buf.data_ptr(), parts, self.gamma.data_ptr(),
                                    self.out[rows].data_ptr(), t, self.out_features, self.eps, s)
         return self.out[rows], self.residual_out[rows]
 

@@ -471,6 +471,54 @@ def test_moe_dispatch_combine(world, experts, tokens, hidden, topk, fp8):
     symm.destroy()
 
 
+@pytest.mark.parametrize("world,experts,tokens,hidden,topk", [(2, 8, 120, 512, 2), (8, 64, 48, 4096, 2), (4, 16, 64, 1024, 4)])
+def test_moe_combine_fp8_payload(world, experts, tokens, hidden, topk):
+    """Combine with e4m3 expert outputs (1 x 128 scales): the stand-alone quantiser against a PyTorch model of it, then the
+    combined rows against the fp32 weighted sum of the bf16 expert outputs (tolerance of the e4m3 rounding)."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.moe import ExpertParallelDispatcher, dequantize_rows
+
+    symm = SymmetricMemory.emulated(world, nbytes=256 << 20, timeout_ms=3000)
+    disp = ExpertParallelDispatcher(symm, num_experts=experts, hidden=hidden, max_tokens=tokens, topk=topk, fp8_combine=True)
+    el = experts // world
+    g = torch.Generator(device="cuda").manual_seed(world * 77 + tokens)
+    for rep in range(2):
+        xs = [torch.randn((tokens, hidden), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+        idxs = [torch.stack([torch.randperm(experts, generator=g, device="cuda")[:topk] for _ in range(tokens)]).to(torch.int32) for _ in range(world)]
+        wts = [torch.rand((tokens, topk), generator=g, device="cuda") for _ in range(world)]
+        for r in range(world):
+            x_s, idx_s, w_s = disp.stage(r, xs[r], idxs[r], wts[r])
+        recv_x, counts, slot_map = disp.dispatch(x_s, idx_s, n_blocks=4)
+        torch.cuda.synchronize()
+        symm.check()
+        for d in range(world):
+            cnt = symm.rank_view(counts, d).cpu().tolist()
+            rows = symm.rank_view(recv_x, d)
+            out = symm.rank_view(disp.expert_out, d)
+            start = 0
+            for j in range(el):
+                out[start:start + cnt[j]] = (rows[start:start + cnt[j]].float() * (0.5 * (d * el + j + 1))).to(torch.bfloat16)
+                start += cnt[j]
+            disp.quantize_expert_out(cnt[el], rank=d)
+            torch.cuda.synchronize()
+            # the quantiser: scale = amax / 448 per 128 elements, values within one e4m3 step of the input
+            val = out[:cnt[el]].float()
+            scales = symm.rank_view(disp.expert_out_scales, d)[:cnt[el]]
+            want_scale = val.view(cnt[el], -1, 128).abs().amax(-1) / 448.0
+            want_scale = torch.where(want_scale > 0, want_scale, torch.ones_like(want_scale))
+            assert torch.allclose(scales, want_scale, rtol=1e-5, atol=0)
+            back = dequantize_rows(symm.rank_view(disp.expert_out_q, d)[:cnt[el]], scales)
+            assert (back - val).abs().max().item() <= 0.07 * val.abs().max().item()
+        y = disp.combine(idx_s, w_s, slot_map, n_blocks=4)
+        torch.cuda.synchronize()
+        symm.check()
+        ref = _moe_reference(xs, idxs, wts, world, experts, lambda e, rows: (rows * (0.5 * (e + 1))).to(torch.bfloat16).float())
+        for r in range(world):
+            got = symm.rank_view(y, r).float()
+            assert (got - ref[r]).abs().max().item() <= 0.08 * ref[r].abs().max().item() + 0.02, (r, rep)
+    symm.destroy()
+
+
 def test_moe_dispatch_reports_small_receive_buffer():
     """A receive buffer that cannot hold the routed rows is reported as an error; nothing is written out of bounds."""
     from mscclpp_b200 import SymmetricMemory, native

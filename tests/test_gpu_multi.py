@@ -64,3 +64,14 @@ def test_algorithm_collection_on_real_peers(tmp_path):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, (r.stdout[-4000:], r.stderr[-3000:])
     assert '"ok": false' not in r.stdout
+
+
+@pytest.mark.skipif(_ngpus() < 2, reason="needs at least two GPUs")
+def test_fused_layer_flag_protocol_stress():
+    """1000 back-to-back launches per mode / transport / fence flavour with per-row checksums against fp32."""
+    n = min(_ngpus(), 8)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
+           "--master-port", "29751", os.path.join(HERE, "mp_stress_worker.py")]
+    r = subprocess.run(cmd, env=dict(os.environ), capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, (r.stdout[-4000:], r.stderr[-3000:])
+    assert '"ok": false' not in r.stdout and "tp_fused_stress" in r.stdout
