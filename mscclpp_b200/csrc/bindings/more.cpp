@@ -151,7 +151,7 @@ void registerMoreBindings(py::module_& m) {
   m.def(
       "tp_decode",
       [](SymmetricHeap& heap, std::vector<uintptr_t> x, std::vector<uintptr_t> w, uintptr_t residualIn, uintptr_t residualOut, uintptr_t out,
-         uintptr_t gamma, int T, int N, int K, float eps, bool nvls, int numCtas, uintptr_t stream) {
+         uintptr_t gamma, int T, int N, int K, float eps, bool nvls, int numCtas, uintptr_t stream, uintptr_t stamps) {
         const size_t need = heap.emulated() ? static_cast<size_t>(heap.world()) : 1;
         if (x.size() != need || w.size() != need) throw Error("tp_decode: one x and one w pointer per (emulated) rank", ErrorCode::InvalidUsage);
         for (uintptr_t p : {residualOut, out}) {
@@ -176,10 +176,12 @@ void registerMoreBindings(py::module_& m) {
         a.nvls = nvls ? 1 : 0;
         a.emuRanks = heap.emulated() ? heap.world() : 1;
         a.numCtas = numCtas;
+        a.stamps = reinterpret_cast<unsigned long long*>(stamps);
         checkCudaMore(launchTpDecode(a, reinterpret_cast<cudaStream_t>(stream)), "tp_decode");
       },
       py::arg("heap"), py::arg("x"), py::arg("w"), py::arg("residual_in"), py::arg("residual_out"), py::arg("out"), py::arg("gamma"),
-      py::arg("t"), py::arg("n"), py::arg("k"), py::arg("eps") = 1e-5f, py::arg("nvls") = false, py::arg("num_ctas") = 0, py::arg("stream") = 0);
+      py::arg("t"), py::arg("n"), py::arg("k"), py::arg("eps") = 1e-5f, py::arg("nvls") = false, py::arg("num_ctas") = 0, py::arg("stream") = 0,
+      py::arg("stamps") = 0);
   m.def("tp_local_fused_workspace_bytes", [](int M, int N) { return tpLocalFusedWorkspaceBytes(M, N); }, py::arg("m"), py::arg("n"));
   m.def(
       "tp_local_fused",

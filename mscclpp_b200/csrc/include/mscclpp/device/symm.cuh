@@ -95,6 +95,25 @@ MSCCLPP_DEVICE_INLINE void finishLaunch(const DeviceComm& c, int rank, uint32_t 
   }
 }
 
+// The same bookkeeping, done EARLY: for kernels that use none of the grid-barrier counters. All the count decides is when
+// the rank's epoch moves on, which only the NEXT launch reads, and that one starts after this one has ended; so a block
+// may count itself out as soon as every one of its threads holds its copy of the epoch (the barrier below takes a
+// predicate computed from it, which forces the loads to have completed). The last block to get here moves the epoch - by
+// then every block has read the old one. At the end of a kernel the round trip of this atomic is exposed; placed before
+// a wait (for packets, for copies) it costs nothing. All threads of the block must call it, exactly once.
+MSCCLPP_DEVICE_INLINE void retireLaunchEarly(const DeviceComm& c, int rank, uint32_t epoch) {
+  (void)__syncthreads_or(epoch == 0u ? 1 : 0);
+  if (threadIdx.x == 0) {
+    SymmControl* ctl = control(c, rank);
+    const uint32_t prev = atomicAdd(&ctl->done, 1u);
+    if (prev == gridDim.x - 1) {
+      ctl->done = 0;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(&ctl->epoch) = epoch;
+    }
+  }
+}
+
 // Cross-rank barrier for block `slot` (same slot index on every rank). All threads of the block
 // call it. Writes made by this block before the call are visible to peers after their barrier
 // returns. Returns false if a peer did not show up within the budget.

@@ -20,6 +20,8 @@
 //  residual-add and norm are one kernel.
 #include "collectives.cuh"
 
+#include <type_traits>
+
 #include <mscclpp/packet_device.hpp>
 
 namespace mscclpp {
@@ -180,6 +182,9 @@ __global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
       for (uint64_t u = start; u < nunits; u += step) sendUnit(u);
     }
   }
+  // the packets are on their way: count this block out of the launch while they travel (instead of at the very end,
+  // where the round trip of that atomic would be exposed)
+  retireLaunchEarly(c, rank, flag);
 
   // ---- receive + reduce
   bool healthy = true;
@@ -242,7 +247,6 @@ __global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
       }
     }
   }
-  finishLaunch(c, rank, flag);
 }
 
 // ============================================================================================
@@ -416,30 +420,43 @@ __global__ void __launch_bounds__(512, 1) twoShotKernel(CollArgs a) {
       }
     } else {
       const uint64_t nunits = a.bytes / 16;
-      const uint64_t begin = splitStart(nunits, world, rank), end = splitStart(nunits, world, rank + 1);
+      // One-shot form (allreduce, peer loads): every rank reduces the WHOLE buffer out of all peers' inputs and writes only
+      // its own output - (world - 1) x the bytes come in over NVLink, nothing goes out, and no store has to land anywhere
+      // before the closing barrier. With two ranks that is the same number of bytes per link direction as the two-shot
+      // form, in one phase of loads.
+      const bool oneShot = a.oneShot == 1 && a.mode == kAllReduce && !kNvls;
+      const uint64_t begin = oneShot ? 0 : splitStart(nunits, world, rank);
+      const uint64_t end = oneShot ? nunits : splitStart(nunits, world, rank + 1);
       const uint64_t local = c.peerBase[rank];
-      // 4 independent 16-byte requests per thread keep enough bytes in flight over NVLink
-      constexpr int kUnroll = 4;
       const uint64_t tid = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
       const uint64_t nthreads = static_cast<uint64_t>(gridDim.x) * blockDim.x;
-      for (uint64_t u0 = begin + tid; u0 < end; u0 += nthreads * kUnroll) {
-        uint4 r[kUnroll];
+      // several independent 16-byte requests per thread and peer keep enough bytes in flight over NVLink: four words
+      // (x world loads each), eight when there are only two ranks to load from
+      auto sweep = [&](auto unrollTag) {
+        constexpr int kUnroll = decltype(unrollTag)::value;
+        for (uint64_t u0 = begin + tid; u0 < end; u0 += nthreads * kUnroll) {
+          uint4 r[kUnroll];
 #pragma unroll
-        for (int k = 0; k < kUnroll; k++) {
-          const uint64_t u = u0 + k * nthreads;
-          if (u < end) r[k] = gatherReduce<T, Op, kNvls>(c, rank, inOff, u * 16);
-        }
+          for (int k = 0; k < kUnroll; k++) {
+            const uint64_t u = u0 + k * nthreads;
+            if (u < end) r[k] = gatherReduce<T, Op, kNvls>(c, rank, inOff, u * 16);
+          }
 #pragma unroll
-        for (int k = 0; k < kUnroll; k++) {
-          const uint64_t u = u0 + k * nthreads;
-          if (u < end) {
-            if (a.mode == kReduceScatter)
-              *reinterpret_cast<uint4*>(local + outOff + (u - begin) * 16) = r[k];
-            else
-              scatterStore<kNvls>(c, rank, outOff, u * 16, r[k]);
+          for (int k = 0; k < kUnroll; k++) {
+            const uint64_t u = u0 + k * nthreads;
+            if (u < end) {
+              if (a.mode == kReduceScatter)
+                *reinterpret_cast<uint4*>(local + outOff + (u - begin) * 16) = r[k];
+              else if (oneShot)
+                *reinterpret_cast<uint4*>(local + outOff + u * 16) = r[k];
+              else
+                scatterStore<kNvls>(c, rank, outOff, u * 16, r[k]);
+            }
           }
         }
-      }
+      };
+      if (!kNvls && world <= 2) sweep(std::integral_constant<int, 8>{});
+      else sweep(std::integral_constant<int, 4>{});
     }
   }
   // all my stores are issued; tell the peers, and learn that theirs into my buffers are done
@@ -539,8 +556,13 @@ cudaError_t launchAllreduceLL(const CollArgs& args, DataType dtype, ReduceOp op,
   MSCCLPP_DISPATCH_TYPE_OP(launchLLTyped, dtype, op, args, nBlocks, nThreads, stream);
 }
 
-cudaError_t launchTwoShot(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads,
+cudaError_t launchTwoShot(const CollArgs& argsIn, DataType dtype, ReduceOp op, int nBlocks, int nThreads,
                           cudaStream_t stream) {
+  CollArgs args = argsIn;
+  if (args.oneShot == 0) {
+    const bool fits = args.comm.world == 2 && args.mode == kAllReduce && !args.norm && !args.nvls && args.bytes <= (64ull << 20);
+    args.oneShot = fits ? 1 : 2;
+  }
   if (args.bytes % 16 != 0) return cudaErrorInvalidValue;
   if (nBlocks < 1 || nBlocks > kBarrierSlots || nThreads < 32 || nThreads > 512) return cudaErrorInvalidValue;
   if (nThreads < args.comm.world) return cudaErrorInvalidValue;

@@ -105,6 +105,9 @@ struct TpDecodeArgs {
   int emuRanks;
   int numCtas;                    // 0 = one thread block per SM
   int colsPerCta;                 // set by the launcher
+  unsigned long long* stamps;     // optional time line: 8 words per thread block (globaltimer ns, thread 0): [0] entry,
+                                  // [1] activations staged, [2] its warp's weight pieces consumed, [3] all warps done,
+                                  // [4] allreduce + residual done, [5] row-sum shares of all blocks read, [6] last store
 };
 cudaError_t launchTpDecode(const TpDecodeArgs& args, cudaStream_t stream);
 

@@ -116,12 +116,15 @@ class RowParallelLinearNorm:
     DECODE_MAX_TOKENS = 8
 
     def forward_decode(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, nvls: Optional[bool] = None, num_ctas: int = 0,
-                       stream: Optional[torch.cuda.Stream] = None, emulated_inputs=None) -> Tuple[torch.Tensor, torch.Tensor]:
+                       stream: Optional[torch.cuda.Stream] = None, emulated_inputs=None,
+                       timeline: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """The layer for up to 8 tokens in ONE launch without tensor-core tiles: every SM streams the weight rows of its slab
         of output columns, the slabs are all-reduced with LL packets by the same thread blocks (no barrier between the
         ranks), residual add and RMSNorm follow in registers. Any world size, 1 included. k_shard must be a multiple of 256.
         nvls: packets leave through one multimem.st instead of one store per peer (default: where the heap has it and
-        there are more than two ranks)."""
+        there are more than two ranks). timeline: optional zeroed int64 CUDA tensor [thread blocks, 8] that receives each
+        block's time stamps in ns (entry, activations staged, weight pieces consumed, all warps done, allreduce + residual
+        done, row-sum shares read, last store)."""
         from .._core import native
 
         n = native.load()
@@ -138,7 +141,8 @@ class RowParallelLinearNorm:
         else:
             xp, wp = [x.data_ptr()], [self.weight.data_ptr()]
         n.tp_decode(self.symm.heap, xp, wp, self.residual_in.data_ptr(), self.residual_out.data_ptr(), self.out.data_ptr(),
-                    self.gamma.data_ptr(), t, self.out_features, self.k_shard, self.eps, nvls, num_ctas, s)
+                    self.gamma.data_ptr(), t, self.out_features, self.k_shard, self.eps, nvls, num_ctas, s,
+                    0 if timeline is None else timeline.data_ptr())
         return self.out[:t], self.residual_out[:t]
 
     def forward_local(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None, two_sm: Optional[bool] = None,
