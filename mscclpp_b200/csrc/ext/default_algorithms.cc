@@ -69,7 +69,8 @@ CollArgs baseArgs(SymmetricHeap& heap, const void* in, void* out, size_t bytes, 
 void gridFor(size_t bytes, bool nvls, int& blocks, int& threads) {
   threads = 512;
   if (nvls) blocks = bytes < (8u << 20) ? 16 : (bytes < (64u << 20) ? 32 : 64);
-  else blocks = bytes < (8u << 20) ? 32 : (bytes < (64u << 20) ? 64 : 128);
+  // peer loads are bound by what one SM keeps in flight over NVLink: from 1 MB on one block per SM, 128 of them
+  else blocks = bytes < (1u << 20) ? 32 : 128;
 }
 
 std::shared_ptr<Algorithm> makeLL(const std::string& name, std::shared_ptr<SymmetricHeap> heap, bool nvls, bool ll8 = false) {
@@ -342,8 +343,9 @@ std::shared_ptr<Algorithm> selectDefaultAlgorithm(
     if (!request.symmetricMemory) pktMax *= 2;
     if (n <= pktMax && n <= llCap && pkt) return pkt;
     if (request.symmetricMemory && n % 16 == 0) {
-      // with two ranks the switch has nothing to combine: plain peer loads win from 16 MB on
-      const bool preferSwitch = world > 2 || n < (16u << 20);
+      // with two ranks the switch has nothing to combine: plain peer loads and stores on 128 SMs win from 4 MB on
+      // (measured on two B200s: 2 MB 24.6 vs 23.6 us through the switch, 4 MB 26.8 vs 28.5, 16 MB 52.0 vs 59.7)
+      const bool preferSwitch = world > 2 || n < (4u << 20);
       if (preferSwitch) {
         if (auto a = get("default_allreduce_nvls_zero_copy")) return a;
       }

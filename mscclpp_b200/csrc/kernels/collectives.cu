@@ -560,8 +560,10 @@ cudaError_t launchTwoShot(const CollArgs& argsIn, DataType dtype, ReduceOp op, i
                           cudaStream_t stream) {
   CollArgs args = argsIn;
   if (args.oneShot == 0) {
-    const bool fits = args.comm.world == 2 && args.mode == kAllReduce && !args.norm && !args.nvls && args.bytes <= (64ull << 20);
-    args.oneShot = fits ? 1 : 2;
+    // measured on two B200s: the one-shot form is slower than the two-shot form at every size from 1 MB to 128 MB (56 vs
+    // 52 us at 16 MB with 128 blocks): loads over NVLink are the scarcer direction, and the two-shot form turns half of
+    // them into stores. It stays available on request.
+    args.oneShot = 2;
   }
   if (args.bytes % 16 != 0) return cudaErrorInvalidValue;
   if (nBlocks < 1 || nBlocks > kBarrierSlots || nThreads < 32 || nThreads > 512) return cudaErrorInvalidValue;

@@ -33,7 +33,7 @@ struct CollArgs {
   int root;                 // kBroadcast: the rank whose `in` is copied into everybody's `out`
   int ll8;                  // one-shot allreduce only: 8-byte {data, flag} packets instead of 16-byte ones (peer stores, no norm)
   int oneShot;              // launchTwoShot, allreduce over peer loads: every rank reduces the whole buffer for itself (no stores
-                            // to peers). 0 = the launcher decides (two ranks, up to 64 MB), 1 = always, 2 = never.
+                            // to peers). 0 = the launcher decides (currently: never), 1 = always, 2 = never.
 };
 
 // One-shot LL16 allreduce (every rank sends its whole buffer to every peer as packets).

@@ -50,10 +50,10 @@ def select_allreduce(symm: SymmetricMemory, nbytes: int, symmetric: bool) -> str
     ll_max = ll_max_bytes(symm.world) * (1 if symmetric else 2)
     if nbytes <= min(ll_max, ll_cap):
         return "nvls_packet" if symm.nvls and nbytes <= (64 << 10) else "packet"
-    # with two ranks the switch has nothing to combine: plain peer loads win from 16 MB on
-    use_switch = symm.nvls and (symm.world > 2 or nbytes < (16 << 20))
-    if not symmetric:
-        return "nvls_block_pipeline" if use_switch else "rsag_pipeline"
+    # with two ranks the switch has nothing to combine: plain peer loads and stores on 128 SMs win from 4 MB on
+    use_switch = symm.nvls and (symm.world > 2 or nbytes < (4 << 20))
+    if not symmetric:  # (the pipelined kernels were tuned separately: through the switch up to 16 MB)
+        return "nvls_block_pipeline" if symm.nvls and (symm.world > 2 or nbytes < (16 << 20)) else "rsag_pipeline"
     if nbytes % 16 != 0:
         raise ValueError("zero-copy allreduce needs a multiple of 16 bytes")
     return "nvls_zero_copy" if use_switch else "rsag_zero_copy"
@@ -97,7 +97,10 @@ def _grid_for(nbytes: int, algo: str, world: int) -> tuple[int, int]:
     if algo == "nvls_zero_copy":
         blocks = 16 if nbytes < (8 << 20) else (32 if nbytes < (64 << 20) else 64)
         return blocks, 512
-    blocks = 32 if nbytes < (8 << 20) else (64 if nbytes < (64 << 20) else 128)
+    # peer loads are bound by what ONE SM can keep in flight over NVLink (measured on two B200s: 16 MB takes 100 / 61 /
+    # 52 us with 32 / 64 / 128 thread blocks, and more than one block per SM is slower again): from 1 MB on, one block per
+    # SM, 128 of them
+    blocks = 32 if nbytes < (1 << 20) else 128
     return blocks, 512
 
 
