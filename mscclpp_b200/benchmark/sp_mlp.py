@@ -119,6 +119,41 @@ def run(args) -> dict:
     base_us = time_eager(d, base_mlp, args.iters, args.warmup) * 1e3
     out["mlp"] = {"us": round(mlp_us, 2), "nccl_cublas_us": round(base_us, 2), "speedup": round(base_us / mlp_us, 3),
                   "tflops_per_gpu": round((flops_up + flops_down) / mlp_us / 1e6, 1)}
+    # ---- gated form (SwiGLU): all-gather -> GEMM over interleaved gate / up weights, silu(gate) * up in the epilogue
+    if args.gated:
+        del mlp
+        symm.destroy()
+        f_g = args.gated_ffn // tp
+        heap = 2 * (seq // tp) * hidden * 2 + 2 * seq * hidden * 2 + seq * f_g * 2 + (512 << 20)
+        symm = mp.SymmetricMemory.from_env(nbytes=heap)
+        gm = SequenceParallelMLP(symm, hidden=hidden, ffn=args.gated_ffn, seq=seq, activation="swiglu")
+        gm.x_local.copy_(torch.randn(gm.x_local.shape, generator=g, device=d.device).to(torch.bfloat16))
+        flops_g = 2.0 * seq * hidden * (2 * f_g)
+        best = None
+        for copiers in args.copiers:
+            us = time_eager(d, lambda: all_gather_gemm(symm, gm.x_local, gm.x_full, gm.w1, gm.h, activation="swiglu", num_copiers=copiers),
+                            args.iters, args.warmup, check=symm.check) * 1e3
+            if best is None or us < best[0]:
+                best = (us, copiers)
+        wg_t, wu_t = gm.w_gate.t(), gm.w_up.t()
+
+        def base_gated():
+            if tp > 1:
+                dist.all_gather_into_tensor(x_full, gm.x_local)
+            else:
+                x_full.copy_(gm.x_local)
+            return torch.nn.functional.silu(torch.matmul(x_full, wg_t)) * torch.matmul(x_full, wu_t)
+
+        base_us = time_eager(d, base_gated, args.iters, args.warmup) * 1e3
+        ref = base_gated().float()
+        all_gather_gemm(symm, gm.x_local, gm.x_full, gm.w1, gm.h, activation="swiglu", num_copiers=best[1])
+        torch.cuda.synchronize()
+        err_g = (gm.h.float() - ref).abs().max().item() / max(ref.abs().max().item(), 1e-9)
+        roof = roofline_us(flops_g, ag_bytes)
+        out["all_gather_gemm_swiglu"] = {"ffn": args.gated_ffn, "n_per_rank": 2 * f_g, "us": round(best[0], 2), "copier_ctas": best[1],
+                                         "tflops_per_gpu": round(flops_g / best[0] / 1e6, 1), "roofline_us": round(roof, 2),
+                                         "frac_of_roofline": round(roof / best[0], 3), "nccl_cublas_us": round(base_us, 2),
+                                         "speedup": round(base_us / best[0], 3), "rel_err": err_g}
     d.barrier()
     symm.destroy()
     if args.standalone:
@@ -131,6 +166,8 @@ def main(argv=None) -> int:
     p.add_argument("--seq", type=int, default=8192)
     p.add_argument("--hidden", type=int, default=8192)
     p.add_argument("--ffn", type=int, default=28672)
+    p.add_argument("--gated", action="store_true", help="also time the gated (SwiGLU) all-gather -> GEMM, N = 2 x gated-ffn / tp per rank")
+    p.add_argument("--gated-ffn", type=int, default=28672)
     p.add_argument("--iters", type=int, default=10)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--copiers", type=int, nargs="*", default=[8, 12, 16, 24])

@@ -23,6 +23,7 @@
 // frees its TMEM and returns.
 #pragma once
 
+#include <type_traits>
 #include <cstdint>
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -154,6 +155,15 @@ MSCCLPP_DEVICE_INLINE uint4 packChunk(const uint32_t (&v)[32], int k) {
   return make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// Epilogues that combine the two 32-column halves of every 64-column block into 32 output columns (gated activations: the
+// weight rows are interleaved so that columns [0, 32) of a block are "gate" features and [32, 64) the matching "up"
+// features) say so with `static constexpr bool kGatedPairs = true` and a `static float gatePair(float gate, float up)`.
+// Only chunks 0-3 of a staged row then carry data.
+template <typename E, typename = void>
+struct IsGatedEpilogue : std::false_type {};
+template <typename E>
+struct IsGatedEpilogue<E, std::void_t<decltype(E::kGatedPairs)>> : std::bool_constant<E::kGatedPairs> {};
+
 // One epilogue warp, one tile: `taddr` is the TMEM address of the warp's lane quarter at its first column,
 // (row0, col0) the global coordinates of that corner. Calls arriveEmpty() as soon as the warp's last accumulator
 // read has completed, i.e. before the last block is written out.
@@ -185,10 +195,17 @@ MSCCLPP_DEVICE_INLINE void stagedEpilogueTile(Epilogue& epi, uint32_t taddr, uin
       if (lane == 0) ptx::bulk_wait_read<0>();
     }
     __syncwarp();
+    if constexpr (IsGatedEpilogue<Epilogue>::value) {
 #pragma unroll
-    for (int c = 0; c < 4; c++) {
-      *reinterpret_cast<uint4*>(stage + stagedOffset(lane, c)) = packChunk<Epilogue>(v0, c);
-      *reinterpret_cast<uint4*>(stage + stagedOffset(lane, c + 4)) = packChunk<Epilogue>(v1, c);
+      for (int i = 0; i < 32; i++) v0[i] = __float_as_uint(Epilogue::gatePair(__uint_as_float(v0[i]), __uint_as_float(v1[i])));
+#pragma unroll
+      for (int c = 0; c < 4; c++) *reinterpret_cast<uint4*>(stage + stagedOffset(lane, c)) = packChunk<Epilogue>(v0, c);
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        *reinterpret_cast<uint4*>(stage + stagedOffset(lane, c)) = packChunk<Epilogue>(v0, c);
+        *reinterpret_cast<uint4*>(stage + stagedOffset(lane, c + 4)) = packChunk<Epilogue>(v1, c);
+      }
     }
     if constexpr (Epilogue::kBulkStore) ptx::fence_proxy_async_smem();
     __syncwarp();

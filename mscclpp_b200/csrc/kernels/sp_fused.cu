@@ -97,6 +97,37 @@ struct StoreAct {
   MSCCLPP_DEVICE_INLINE void auxWarp(int, int) const {}
 };
 
+// Gated activation (SwiGLU): the GEMM's N columns are gate/up features interleaved in groups of 32 (columns [64 b, 64 b +
+// 32) gate features 32 b .., columns [64 b + 32, 64 b + 64) the matching up features); the output has N / 2 columns,
+// out[:, 32 b + j] = silu(gate) * up, taken in fp32 on the accumulators. Rows leave with plain 64-byte-contiguous stores.
+struct StoreGated {
+  static constexpr bool kNeedsTileBarrier = false;
+  static constexpr bool kBulkStore = false;
+  static constexpr bool kGatedPairs = true;
+  __nv_bfloat16* out;  // [M, N / 2]
+  int M, halfN;
+  MSCCLPP_DEVICE_INLINE static float convert(float x) { return x; }
+  MSCCLPP_DEVICE_INLINE static float gatePair(float g, float u) { return g / (1.f + __expf(-g)) * u; }
+  MSCCLPP_DEVICE_INLINE void tileBegin(int, int, int) const {}
+  MSCCLPP_DEVICE_INLINE void block(const uint8_t* stage, int row0, int col0, int lane, int /*b*/) const {
+    // four lanes per row (chunks 0-3), eight rows per step
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+      const int r = 8 * i + (lane >> 2), ch = lane & 3;
+      const int row = row0 + r;
+      if (row < M) {
+        *reinterpret_cast<uint4*>(out + static_cast<size_t>(row) * halfN + col0 / 2 + ch * 8) =
+            *reinterpret_cast<const uint4*>(stage + gemm::stagedOffset(r, ch));
+      }
+    }
+    __syncwarp();  // the staging buffer may be overwritten from here on
+  }
+  MSCCLPP_DEVICE_INLINE void tileDone(int, int, int) const {}
+  MSCCLPP_DEVICE_INLINE void warpTileDone(int, int) const {}
+  MSCCLPP_DEVICE_INLINE void warpDrain(int) const {}
+  MSCCLPP_DEVICE_INLINE void auxWarp(int, int) const {}
+};
+
 constexpr uint32_t kPieceBytes = 32768;
 constexpr int kRingStages = 6;  // 192 KiB of the CTA's dynamic shared memory
 
@@ -193,7 +224,16 @@ __global__ void __launch_bounds__(gemm::kNumThreads, 1)
   if (static_cast<int>(blockIdx.x) < a.numGemmCtas) {
     const int per = a.shape.M / gemm::kBlockM / c.world;
     GatherGate gate{&c, &maps.aLocal[blockIdx.y], rank, rank * per, per, epoch};
-    StoreAct<kAct> epi{&maps.d[blockIdx.y], a.shape.M};
+    auto makeEpilogue = [&] {
+      if constexpr (kAct == 3) {
+        // D of (emulated) rank blockIdx.y: same heap offset as a.D
+        const uint64_t dOff = reinterpret_cast<uint64_t>(a.D) - c.peerBase[c.rank];
+        return StoreGated{reinterpret_cast<__nv_bfloat16*>(c.peerBase[rank] + dOff), a.shape.M, a.shape.N / 2};
+      } else {
+        return StoreAct<kAct>{&maps.d[blockIdx.y], a.shape.M};
+      }
+    };
+    auto epi = makeEpilogue();
     gemm::Shape shape = a.shape;
     shape.mOrder = 2;
     if constexpr (kBlockN == 0) {
@@ -249,6 +289,8 @@ cudaError_t launchAct(const AgTmaps& maps, const AgGemmArgs& args, int grid, cud
       return launchTyped<kBlockN, 1>(maps, args, grid, stream);
     case 2:
       return launchTyped<kBlockN, 2>(maps, args, grid, stream);
+    case 3:
+      return launchTyped<kBlockN, 3>(maps, args, grid, stream);
     default:
       return cudaErrorInvalidValue;
   }
@@ -289,7 +331,8 @@ cudaError_t launchAllGatherGemm(const AgGemmArgs& argsIn, const void* const* B, 
     if (err != cudaSuccess) return err;
     err = gemm::makeTensorMapBf16(&maps.b[e], B[e], N, K, static_cast<uint64_t>(K) * 2, twoSm ? tileN / 2 : tileN);
     if (err != cudaSuccess) return err;
-    err = gemm::makeTensorMapBf16(&maps.d[e], reinterpret_cast<const void*>(heap + dOff), M, N, static_cast<uint64_t>(N) * 2, 32);
+    const int dCols = args.activation == 3 ? N / 2 : N;  // (the gated epilogue stores without this map)
+    err = gemm::makeTensorMapBf16(&maps.d[e], reinterpret_cast<const void*>(heap + dOff), M, dCols, static_cast<uint64_t>(dCols) * 2, 32);
     if (err != cudaSuccess) return err;
   }
   const int tiles = numMBlk * (N / tileN);

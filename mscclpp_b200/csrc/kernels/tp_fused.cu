@@ -832,8 +832,11 @@ __global__ void __launch_bounds__(512) tpScaleRowsKernel(const bf16* h, const fl
                                                          int M, int N) {
   const int unitsPerRow = N / 8;
   const size_t total = static_cast<size_t>(M) * unitsPerRow;
-  for (size_t u = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; u < total;
-       u += static_cast<size_t>(gridDim.x) * blockDim.x) {
+  // The rows arrived in ascending order during the launch before this one, so the LAST rows are the ones still in L2:
+  // the pass walks the rows from the end.
+  for (size_t v = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; v < total;
+       v += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t u = total - 1 - v;
     const int row = static_cast<int>(u / unitsPerRow), ru = static_cast<int>(u % unitsPerRow);
     float f[8];
     Vec16<bf16>::toFloat(*reinterpret_cast<const uint4*>(h + u * 8), f);

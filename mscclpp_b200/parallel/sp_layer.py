@@ -17,19 +17,29 @@ import torch
 from .._core import native
 from .._core.symm import SymmetricMemory
 
-ACTIVATIONS = {"none": 0, "gelu": 1, "silu": 2}
+ACTIVATIONS = {"none": 0, "gelu": 1, "silu": 2, "swiglu": 3}
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """[F, K] gate and up projection weights -> the [2 F, K] matrix the "swiglu" epilogue expects: rows in groups of 64,
+    the first 32 of a group gate features 32 b .. 32 b + 31, the other 32 the matching up features (F % 32 == 0). With
+    it one all-gather -> GEMM launch produces silu(x W_gate^T) * (x W_up^T) directly, [S, F]."""
+    f, k = w_gate.shape
+    assert w_up.shape == (f, k) and f % 32 == 0
+    return torch.stack([w_gate.view(f // 32, 32, k), w_up.view(f // 32, 32, k)], dim=1).reshape(2 * f, k).contiguous()
 
 
 def all_gather_gemm(symm: SymmetricMemory, a_local: torch.Tensor, a_full: torch.Tensor, weight, out: torch.Tensor,
                     activation: str = "none", block_n: int = -1, num_copiers: int = 0, num_gemm_ctas: int = 0,
                     stream: Optional[torch.cuda.Stream] = None) -> torch.Tensor:
     """out[S, N] = act(concat_r(a_local_r) @ weight^T). `a_local` [S/tp, K], `a_full` [S, K] workspace and `out` are
-    symmetric-heap tensors; `weight` [N, K] is local (a list with one weight per rank for emulated heaps)."""
+    symmetric-heap tensors; `weight` [N, K] is local (a list with one weight per rank for emulated heaps).
+    activation "swiglu": `weight` is interleave_gate_up(w_gate, w_up) and `out` is [S, N / 2] = silu(gate) * up."""
     n = native.load()
     s_rows, k = a_full.shape
     weights = weight if isinstance(weight, (list, tuple)) else [weight]
     n_cols = weights[0].shape[0]
-    assert a_local.shape == (s_rows // symm.world, k) and out.shape == (s_rows, n_cols)
+    assert a_local.shape == (s_rows // symm.world, k) and out.shape == (s_rows, n_cols // 2 if activation == "swiglu" else n_cols)
     if block_n < 0:  # 0 = two-SM tiles (256 x 256 on SM pairs) when the shape allows, else one-SM 256- or 128-wide tiles
         block_n = 0 if (s_rows % (symm.world * 256) == 0 and n_cols % 256 == 0) else (256 if n_cols % 256 == 0 else 128)
     assert all(w.shape == (n_cols, k) and w.is_contiguous() and w.dtype == torch.bfloat16 for w in weights)
@@ -60,7 +70,9 @@ def gemm_reduce_scatter(symm: SymmetricMemory, a, weight, partial: torch.Tensor,
 
 
 class SequenceParallelMLP:
-    """Two-matrix MLP of one tensor-parallel rank on sequence-sharded activations (random-initialised weights)."""
+    """MLP of one tensor-parallel rank on sequence-sharded activations (random-initialised weights): two matrices, or
+    three with activation="swiglu" (gate and up projections interleaved into one [2 F/tp, hidden] matrix, so that the
+    all-gather -> GEMM launch produces silu(gate) * up directly)."""
 
     def __init__(self, symm: SymmetricMemory, hidden: int = 8192, ffn: int = 28672, seq: int = 8192, activation: str = "gelu",
                  seed: int = 0, init_std: float = 0.02):
@@ -69,7 +81,12 @@ class SequenceParallelMLP:
         self.symm, self.hidden, self.ffn_shard, self.seq, self.activation = symm, hidden, ffn // tp, seq, activation
         dev = symm.device
         g = torch.Generator(device=dev).manual_seed(seed * 1000 + symm.rank)
-        self.w1 = (torch.randn((self.ffn_shard, hidden), generator=g, device=dev) * init_std).to(torch.bfloat16)
+        if activation == "swiglu":
+            self.w_gate = (torch.randn((self.ffn_shard, hidden), generator=g, device=dev) * init_std).to(torch.bfloat16)
+            self.w_up = (torch.randn((self.ffn_shard, hidden), generator=g, device=dev) * init_std).to(torch.bfloat16)
+            self.w1 = interleave_gate_up(self.w_gate, self.w_up)
+        else:
+            self.w1 = (torch.randn((self.ffn_shard, hidden), generator=g, device=dev) * init_std).to(torch.bfloat16)
         self.w2 = (torch.randn((hidden, self.ffn_shard), generator=g, device=dev) * init_std).to(torch.bfloat16)
         self.x_local = symm.tensor((seq // tp, hidden), torch.bfloat16)
         self.x_full = symm.tensor((seq, hidden), torch.bfloat16)

@@ -363,6 +363,39 @@ def test_all_gather_gemm_one_kernel(world, rows_per_rank, k, n_cols, act):
     symm.destroy()
 
 
+@pytest.mark.parametrize("world,rows_per_rank,k,ffn,block_n", [(2, 256, 256, 256, 256), (4, 128, 512, 128, 128), (2, 256, 128, 384, -1)])
+def test_all_gather_gemm_swiglu(world, rows_per_rank, k, ffn, block_n):
+    """All-gather -> GEMM over interleaved gate / up weights with the gated epilogue: out = silu(x Wg^T) * (x Wu^T), one
+    launch, all ranks emulated on one GPU; against the fp32 composition."""
+    from mscclpp_b200 import SymmetricMemory
+    from mscclpp_b200.parallel.sp_layer import all_gather_gemm, interleave_gate_up
+
+    symm = SymmetricMemory.emulated(world, nbytes=128 << 20, timeout_ms=3000)
+    s_rows = world * rows_per_rank
+    a_local = symm.tensor((rows_per_rank, k), torch.bfloat16)
+    a_full = symm.tensor((s_rows, k), torch.bfloat16)
+    out = symm.tensor((s_rows, ffn), torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(world * 31 + ffn)
+    wg = [(torch.randn((ffn, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(world)]
+    wu = [(torch.randn((ffn, k), generator=g, device="cuda") * 0.05).to(torch.bfloat16) for _ in range(world)]
+    ws = [interleave_gate_up(a, b) for a, b in zip(wg, wu)]
+    for rep in range(2):
+        shards = [torch.randn((rows_per_rank, k), generator=g, device="cuda").to(torch.bfloat16) for _ in range(world)]
+        for r in range(world):
+            symm.rank_view(a_local, r).copy_(shards[r])
+            symm.rank_view(a_full, r).fill_(float("nan"))
+            symm.rank_view(out, r).fill_(float("nan"))
+        all_gather_gemm(symm, a_local, a_full, ws, out, activation="swiglu", block_n=block_n, num_copiers=2, num_gemm_ctas=max(2, 16 // world))
+        torch.cuda.synchronize()
+        symm.check()
+        full = torch.cat(shards).float()
+        for r in range(world):
+            ref = torch.nn.functional.silu(full @ wg[r].float().t()) * (full @ wu[r].float().t())
+            got = symm.rank_view(out, r).float()
+            assert (got - ref).abs().max().item() <= 0.02 * ref.abs().max().item() + 0.02, (r, rep)
+    symm.destroy()
+
+
 @pytest.mark.parametrize("world,rows_per_rank,k,n_cols", [(2, 256, 128, 512), (4, 128, 256, 1024), (8, 128, 64, 256)])
 def test_gemm_reduce_scatter_one_kernel(world, rows_per_rank, k, n_cols):
     """GEMM -> reduce-scatter in one launch: rank r ends with its row block of the summed product."""
