@@ -318,6 +318,19 @@ PYBIND11_MODULE(_native, m) {
       py::arg("heap"), py::arg("input"), py::arg("output"), py::arg("bytes"), py::arg("dtype"), py::arg("op") = SUM,
       py::arg("n_blocks") = 8, py::arg("n_threads") = 512, py::arg("stream") = 0, py::arg("nvls") = false, py::arg("ll8") = false);
   m.def(
+      "allreduce_ll128",
+      [](SymmetricHeap& heap, uintptr_t in, uintptr_t out, uint64_t bytes, DataType dtype, ReduceOp op, uintptr_t scratch, uint64_t slotBytes,
+         int nBlocks, int nThreads, uintptr_t stream) {
+        CollArgs a = makeCollArgs(heap, in, out, bytes, kAllReduce, false);
+        if (!heap.contains(reinterpret_cast<const void*>(scratch), ll128ScratchBytes(heap.world(), slotBytes)))
+          throw Error("allreduce_ll128: the scratch must be symmetric-heap memory of 2 x world x slot_bytes", ErrorCode::InvalidUsage);
+        a.ll128Scratch = reinterpret_cast<void*>(scratch);
+        a.ll128SlotBytes = slotBytes;
+        checkCuda(launchAllreduceLL128(a, dtype, op, nBlocks, nThreads, reinterpret_cast<cudaStream_t>(stream)), "allreduce_ll128");
+      },
+      py::arg("heap"), py::arg("input"), py::arg("output"), py::arg("bytes"), py::arg("dtype"), py::arg("op") = SUM, py::arg("scratch"),
+      py::arg("slot_bytes"), py::arg("n_blocks") = 32, py::arg("n_threads") = 512, py::arg("stream") = 0);
+  m.def(
       "allreduce_ll_rmsnorm",
       [](SymmetricHeap& heap, uintptr_t in, uintptr_t out, int rows, int hidden, DataType dtype, float eps,
          uintptr_t residualIn, uintptr_t residualOut, uintptr_t gamma, int nBlocks, int nThreads, uintptr_t stream,

@@ -250,6 +250,105 @@ __global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
 }
 
 // ============================================================================================
+// One-shot LL128 allreduce
+// ============================================================================================
+// The same exchange as allreduceLLKernel with 128-byte lines instead of 16-byte packets: a line carries 120 bytes of
+// payload and one 8-byte flag (15/16 of the scratch traffic is payload, against 1/2 with LL16), and is written by eight
+// consecutive lanes of a warp in ONE instruction, so that it leaves the SM as one 128-byte transaction; the receiver
+// takes a line once the flag lane sees this launch's epoch (packet_device.hpp: ll128Write / ll128Read, every wait
+// bounded). Line L covers bytes [120 L, 120 L + 120) of the buffer: lane s < 7 of the line's group holds bytes
+// [16 s, 16 s + 16) of them, lane 7 the last 8. Pieces start on 8-byte boundaries, so they move as two 8-byte words.
+// Role of the reference's packet allreduce for mid-size messages (its LL protocol has the 8- and 16-byte packets only,
+// include/mscclpp/packet_device.hpp); the line format follows the description in this library's own header.
+MSCCLPP_DEVICE_INLINE uint4 loadPiece(const char* base, uint64_t off, uint64_t bytes, int pieceBytes) {
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (off + pieceBytes <= bytes) {
+    const uint2 lo = *reinterpret_cast<const uint2*>(base + off);
+    v.x = lo.x;
+    v.y = lo.y;
+    if (pieceBytes == 16) {
+      const uint2 hi = *reinterpret_cast<const uint2*>(base + off + 8);
+      v.z = hi.x;
+      v.w = hi.y;
+    }
+  } else if (off < bytes) {
+    uint32_t w[4] = {0, 0, 0, 0};
+    for (uint64_t i = off; i < bytes && i < off + pieceBytes; i++) {
+      w[(i - off) >> 2] |= static_cast<uint32_t>(static_cast<uint8_t>(base[i])) << (8 * ((i - off) & 3));
+    }
+    v = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+  return v;
+}
+MSCCLPP_DEVICE_INLINE void storePiece(char* base, uint64_t off, uint64_t bytes, int pieceBytes, uint4 v) {
+  if (off + pieceBytes <= bytes) {
+    *reinterpret_cast<uint2*>(base + off) = make_uint2(v.x, v.y);
+    if (pieceBytes == 16) *reinterpret_cast<uint2*>(base + off + 8) = make_uint2(v.z, v.w);
+  } else if (off < bytes) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    for (uint64_t i = off; i < bytes && i < off + pieceBytes; i++) base[i] = static_cast<char>(w[(i - off) >> 2] >> (8 * ((i - off) & 3)));
+  }
+}
+
+template <typename T, ReduceOp Op>
+__global__ void __launch_bounds__(512, 1) allreduceLL128Kernel(CollArgs a) {
+  const DeviceComm& c = a.comm;
+  const int rank = deviceRank(c);
+  const int world = c.world;
+  const uint64_t emu = static_cast<uint64_t>(blockIdx.y) * a.emuStride;
+  const char* in = reinterpret_cast<const char*>(a.in) + emu;
+  char* out = reinterpret_cast<char*>(a.out) + emu;
+  const uint32_t epoch = launchEpoch(c, rank);
+  const uint64_t flag = (static_cast<uint64_t>(0x4c4c3132u) << 32) | epoch;  // never equal to payload left by the 16-byte formats
+  // the lines have a scratch of their own ([2 buffers][world][slot]): in the scratch of the 8- and 16-byte packets every odd
+  // 32-bit word is a flag, and payload of this format left there could pass for one
+  const uint64_t slotBytes = a.ll128SlotBytes;
+  const uint64_t bufOff = (reinterpret_cast<uint64_t>(a.ll128Scratch) - c.peerBase[c.rank]) +
+                          static_cast<uint64_t>(epoch & 1u) * (static_cast<uint64_t>(world) * slotBytes);
+  const uint64_t bytes = a.bytes;
+  const uint64_t numLines = (bytes + kLL128PayloadBytes - 1) / kLL128PayloadBytes;
+  const uint32_t sub = threadIdx.x & 7;
+  const uint32_t groupMask = 0xffu << ((threadIdx.x & 31) & ~7u);
+  const int pieceBytes = sub == 7 ? 8 : 16;
+  const uint64_t firstLine = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
+  const uint64_t lineStep = (static_cast<uint64_t>(gridDim.x) * blockDim.x) >> 3;
+
+  // ---- send: my whole input to every peer
+  for (uint64_t line = firstLine; line < numLines; line += lineStep) {
+    const uint4 d = loadPiece(in, line * kLL128PayloadBytes + sub * 16, bytes, pieceBytes);
+    for (int i = 1; i < world; i++) {
+      const int p = (rank + i) % world;
+      LL128Line* dst = reinterpret_cast<LL128Line*>(c.peerBase[p] + bufOff + static_cast<uint64_t>(rank) * slotBytes) + line;
+      ll128Write(dst, sub, d, flag);
+    }
+  }
+  // the lines are on their way: count this block out of the launch while they travel
+  retireLaunchEarly(c, rank, epoch);
+
+  // ---- receive + reduce (contributions in rank order: every rank computes the same bits)
+  bool healthy = true;
+  for (uint64_t line = firstLine; line < numLines && healthy; line += lineStep) {
+    const uint64_t off = line * kLL128PayloadBytes + sub * 16;
+    const uint4 own = loadPiece(in, off, bytes, pieceBytes);
+    Accum<T, Op> acc;
+    for (int p = 0; p < world; p++) {
+      uint4 v = own;
+      if (p != rank) {
+        const LL128Line* src = reinterpret_cast<const LL128Line*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * slotBytes) + line;
+        if (!ll128Read(src, sub, groupMask, flag, v, c.status, c.timeoutNs, rank, p)) {
+          healthy = false;
+          break;
+        }
+        if (sub == 7) v.z = v.w = 0;  // the flag is not data
+      }
+      if (p == 0) acc.init(v); else acc.add(v);
+    }
+    // (a group leaves the loop together: ll128Read returns the same answer to its eight lanes)
+    if (healthy) storePiece(out, off, bytes, pieceBytes, acc.result());
+  }
+}
+
+// ============================================================================================
 // Two-shot zero-copy (peer loads/stores or NVLS multimem)
 // ============================================================================================
 template <typename T, ReduceOp Op>
@@ -554,6 +653,21 @@ cudaError_t launchAllreduceLL(const CollArgs& args, DataType dtype, ReduceOp op,
   if (nBlocks < 1 || nThreads < 32 || nThreads > 1024) return cudaErrorInvalidValue;
   if (args.norm && ((static_cast<uint64_t>(args.hidden) * dataTypeSize(dtype)) % 16 != 0)) return cudaErrorInvalidValue;
   MSCCLPP_DISPATCH_TYPE_OP(launchLLTyped, dtype, op, args, nBlocks, nThreads, stream);
+}
+
+template <typename T, ReduceOp Op>
+cudaError_t launchLL128Typed(const CollArgs& a, int nBlocks, int nThreads, cudaStream_t s) {
+  return launchMaybeCooperative(allreduceLL128Kernel<T, Op>, a, nBlocks, nThreads, s);
+}
+
+cudaError_t launchAllreduceLL128(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads, cudaStream_t stream) {
+  const uint64_t lines = (args.bytes + kLL128PayloadBytes - 1) / kLL128PayloadBytes;
+  if (args.ll128Scratch == nullptr || args.ll128SlotBytes % 128 != 0 || lines * sizeof(LL128Line) > args.ll128SlotBytes) return cudaErrorInvalidValue;
+  if (reinterpret_cast<uintptr_t>(args.ll128Scratch) % 128 != 0) return cudaErrorInvalidValue;
+  if (nBlocks < 1 || nThreads < 32 || nThreads > 512 || nThreads % 32 != 0) return cudaErrorInvalidValue;
+  if (args.norm || args.nvls || args.bytes % 8 != 0) return cudaErrorInvalidValue;  // pieces move as 8-byte words
+  if ((reinterpret_cast<uintptr_t>(args.in) | reinterpret_cast<uintptr_t>(args.out)) % 8 != 0) return cudaErrorInvalidValue;
+  MSCCLPP_DISPATCH_TYPE_OP(launchLL128Typed, dtype, op, args, nBlocks, nThreads, stream);
 }
 
 cudaError_t launchTwoShot(const CollArgs& argsIn, DataType dtype, ReduceOp op, int nBlocks, int nThreads,

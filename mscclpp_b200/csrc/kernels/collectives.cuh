@@ -32,6 +32,8 @@ struct CollArgs {
   int broadcastResidual;    // two-shot only: write residualOut on every rank, not just the owner's rows
   int root;                 // kBroadcast: the rank whose `in` is copied into everybody's `out`
   int ll8;                  // one-shot allreduce only: 8-byte {data, flag} packets instead of 16-byte ones (peer stores, no norm)
+  void* ll128Scratch;       // launchAllreduceLL128: symmetric-heap scratch of ll128ScratchBytes(world, slot) bytes at the same offset
+  uint64_t ll128SlotBytes;  // on every rank, zeroed once before its first use; a slot takes ceil(bytes / 120) lines of 128 bytes
   int oneShot;              // launchTwoShot, allreduce over peer loads: every rank reduces the whole buffer for itself (no stores
                             // to peers). 0 = the launcher decides (currently: never), 1 = always, 2 = never.
 };
@@ -40,6 +42,12 @@ struct CollArgs {
 // Buffers may live anywhere in local memory. bytes <= comm.llSlotBytes / 2.
 cudaError_t launchAllreduceLL(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads,
                               cudaStream_t stream);
+
+// One-shot LL128 allreduce: as launchAllreduceLL with 128-byte lines (120 bytes of payload + flag) instead of 16-byte packets,
+// for messages too long for 50 % scratch efficiency and too short for the two-shot algorithms. bytes % 8 == 0, buffers 8-byte
+// aligned; ceil(bytes / 120) * 128 <= args.ll128SlotBytes; peer stores only (no multimem form, no fused norm).
+constexpr size_t ll128ScratchBytes(int world, size_t slotBytes) { return 2 * static_cast<size_t>(world) * slotBytes; }
+cudaError_t launchAllreduceLL128(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads, cudaStream_t stream);
 
 // Two-shot zero-copy allreduce / reduce-scatter / allgather over peer pointers or NVLS multimem.
 // `in` and `out` must be symmetric-heap buffers at the same offset on every rank; bytes % 16 == 0.

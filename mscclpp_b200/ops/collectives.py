@@ -4,6 +4,7 @@ Algorithm names follow the reference's default collection
 (src/ext/collectives/algorithm_collection_builder.cc:64-104):
   "packet" / "nvls_packet"          one-shot LL16 over peer stores / one multimem.st per packet
   "allpair_packet"                  one-shot with 8-byte LL8 packets over peer stores
+  "packet128"                       one-shot with 128-byte LL128 lines (120 bytes of payload + flag) over peer stores
   "rsag_zero_copy"                  two-shot over peer loads+stores, zero copy
   "nvls_zero_copy"                  two-shot through NVSwitch multimem.ld_reduce + multimem.st
   "nvls_block_pipeline" / "rsag_pipeline"   tensors OUTSIDE the heap: one kernel copies in, reduces through heap scratch
@@ -79,6 +80,25 @@ def _pipeline_slice(symm: SymmetricMemory) -> int:
     return (PIPELINE_SLICE_BYTES + unit - 1) // unit * unit
 
 
+LL128_MAX_BYTES = 2 << 20  # largest message the LL128 scratch is sized for (2 x world x 2.1 MB of heap)
+
+
+def _ll128_scratch(symm: SymmetricMemory):
+    """Heap scratch of the LL128 allreduce, made and zeroed on first use (every rank gets here on the same call)."""
+    cache = symm.__dict__.get("_ll128_scratch")
+    if cache is None:
+        slot = (LL128_MAX_BYTES + 119) // 120 * 128
+        buf = symm.tensor((2 * symm.world * slot,), torch.uint8)
+        ranks = range(symm.world) if symm.emulated_mode else [symm.rank]
+        for r in ranks:
+            (symm.rank_view(buf, r) if symm.emulated_mode else buf).zero_()
+        torch.cuda.synchronize()
+        symm.barrier()  # peers write lines into this scratch: nobody may start before everybody has zeroed it
+        cache = (buf, slot)
+        symm.__dict__["_ll128_scratch"] = cache
+    return cache
+
+
 def _ll_capacity(symm: SymmetricMemory) -> int:
     import struct
 
@@ -139,6 +159,16 @@ def all_reduce(symm: SymmetricMemory, inp: torch.Tensor, out: Optional[torch.Ten
             raise ValueError("emulated ranks need heap tensors")
         n.allreduce_ll(symm.heap, inp.data_ptr(), out.data_ptr(), nbytes, dt, _op(op), blocks, threads, _stream(stream),
                        algo == "nvls_packet", algo == "allpair_packet")
+    elif algo == "packet128":
+        if nbytes % 8 != 0 or nbytes > LL128_MAX_BYTES:
+            raise ValueError("packet128 takes multiples of 8 bytes up to LL128_MAX_BYTES")
+        if symm.emulated_mode and not symmetric:
+            raise ValueError("emulated ranks need heap tensors")
+        scratch, slot = _ll128_scratch(symm)
+        lines = (nbytes + 119) // 120
+        blocks = n_blocks or max(1, min(64, (lines * 8 + 511) // 512))
+        n.allreduce_ll128(symm.heap, inp.data_ptr(), out.data_ptr(), nbytes, dt, _op(op), scratch.data_ptr(), slot, blocks, n_threads or 512,
+                          _stream(stream))
     elif algo in ("rsag_zero_copy", "nvls_zero_copy"):
         if not symmetric:
             raise ValueError(f"{algo} needs tensors from symm.tensor()")

@@ -36,13 +36,15 @@ def main():
         dist.all_gather(parts, t)
         return torch.stack([p.float() for p in parts]).sum(0)
 
-    algos = ["packet", "allpair_packet", "rsag_zero_copy"] + (["nvls_packet", "nvls_zero_copy"] if symm.nvls else [])
+    algos = ["packet", "allpair_packet", "packet128", "rsag_zero_copy"] + (["nvls_packet", "nvls_zero_copy"] if symm.nvls else [])
     for dtype in (torch.bfloat16, torch.float16, torch.float32):
         for numel in (256, 4096, 65536, 1 << 20):
             inp = symm.tensor((numel,), dtype)
             out = symm.tensor((numel,), dtype)
             for algo in algos:
                 if algo in ("packet", "nvls_packet", "allpair_packet") and numel * inp.element_size() > (1 << 20):
+                    continue
+                if algo == "packet128" and numel * inp.element_size() > (2 << 20):
                     continue
                 for rep in range(2):
                     g = torch.Generator(device=dev).manual_seed(rank * 7 + numel + rep)
