@@ -408,8 +408,11 @@ def main():
                 row["auto_graph_us"] = graph_us(lambda st: all_reduce(symm, buf_in[:n], buf_out[:n], stream=st))
             # the mid-size range, where the packet formats hand over to the two-shot algorithms: each candidate replayed from a
             # graph (eager launches all cost the same ~15 us there)
-            if (32 << 10) <= size <= (2 << 20) and world > 1:
-                mids = ["packet128"] + (["packet"] if size <= (1 << 20) else []) + ["rsag_zero_copy"] + (["nvls_zero_copy"] if symm.nvls else [])
+            if (32 << 10) <= size <= (4 << 20) and world > 1:
+                from mscclpp_b200.ops.collectives import ll128_max_bytes
+
+                mids = (["packet128"] if size <= ll128_max_bytes(world) else []) + (["packet"] if size <= (1 << 20) else [])
+                mids += ["rsag_zero_copy"] + (["nvls_zero_copy"] if symm.nvls else [])
                 for algo in mids:
                     try:
                         row[algo + "_graph_us"] = graph_us(lambda st, algo=algo: all_reduce(symm, buf_in[:n], buf_out[:n], algo=algo, stream=st))

@@ -140,6 +140,28 @@ struct PipeScratch {
   }
 };
 
+// Largest message of the LL128 allreduce: every rank receives the whole message from every peer, so the useful range (and
+// the scratch, 2 x world x 1.07 x this) shrinks as the world grows.
+size_t ll128MaxBytes(int world) { return world <= 2 ? (4u << 20) : (world <= 4 ? (2u << 20) : (1u << 20)); }
+
+// One-shot allreduce with 128-byte lines (120 bytes of payload + flag), in a zeroed heap scratch of its own.
+std::shared_ptr<Algorithm> makeLL128(const std::string& name, std::shared_ptr<SymmetricHeap> heap, std::shared_ptr<PipeScratch> scratch,
+                                     size_t slotBytes) {
+  return std::make_shared<NativeAlgorithm>(
+      name, "allreduce", nullptr,
+      [heap, scratch, slotBytes](const void* in, void* out, size_t inBytes, size_t, DataType dtype, ReduceOp op, cudaStream_t stream, int nBlocks,
+                                 int nThreads, bool, const std::unordered_map<std::string, uintptr_t>&) {
+        CollArgs a = baseArgs(*heap, in, out, inBytes, kAllReduce, false);
+        a.ll128Scratch = scratch->base;
+        a.ll128SlotBytes = slotBytes;
+        const size_t lines = (inBytes + 119) / 120;
+        if (nThreads <= 0) nThreads = 512;
+        if (nBlocks <= 0) nBlocks = static_cast<int>(std::max<size_t>(1, std::min<size_t>(64, (lines * 8 + nThreads - 1) / nThreads)));
+        return toResult(launchAllreduceLL128(a, dtype, op, nBlocks, nThreads, stream));
+      },
+      0, ll128MaxBytes(heap->world()), CollectiveBufferMode::Any);
+}
+
 // Allreduce of buffers outside the heap in one kernel. sliceBytes == 0: one round covers the whole message.
 std::shared_ptr<Algorithm> makePipeline(const std::string& name, std::shared_ptr<SymmetricHeap> heap, bool nvls, size_t sliceBytes,
                                         std::shared_ptr<PipeScratch> scratch) {
@@ -256,6 +278,43 @@ AlgorithmCollection AlgorithmCollectionBuilder::buildDefaultAlgorithms(std::shar
   if (nvls) add(makeLL("default_allreduce_nvls_packet", heap, true));
   if (nvls) add(makeTwoShot("default_allreduce_nvls_zero_copy", "allreduce", heap, kAllReduce, true, false, staging));
   add(makeTwoShot("default_allreduce_rsag_zero_copy", "allreduce", heap, kAllReduce, false, false, staging));
+  // LL128 lines for the mid-size range: a scratch of their own (see collectives.cu), zeroed before anybody may write into it
+  {
+    auto llScratch = std::make_shared<PipeScratch>();
+    llScratch->heap = heap;
+    const size_t slot = (ll128MaxBytes(heap->world()) + 119) / 120 * 128;
+    const size_t want = ll128ScratchBytes(heap->world(), slot);
+    if (heap->bytesFree() >= want + (64u << 20)) {
+      try {
+        llScratch->base = heap->alloc(want, 256);
+        llScratch->bytes = want;
+      } catch (const BaseError&) {
+        llScratch->base = nullptr;
+      }
+    }
+    if (llScratch->base != nullptr) {
+      if (cudaMemset(llScratch->base, 0, want) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        (void)cudaGetLastError();
+        heap->free(llScratch->base);
+        llScratch->base = nullptr;
+      }
+    }
+    // every rank must agree on whether the algorithm exists, and nobody may send lines before everybody has zeroed
+    int mine = llScratch->base != nullptr ? 1 : 0;
+    std::vector<int> all(heap->world(), 0);
+    all[heap->rank()] = mine;
+    if (heap->bootstrap()) {
+      heap->bootstrap()->allGather(all.data(), sizeof(int));
+    }
+    bool everybody = true;
+    for (int v : all) everybody = everybody && v != 0;
+    if (everybody) {
+      add(makeLL128("default_allreduce_packet_ll128", heap, llScratch, slot));
+    } else if (llScratch->base != nullptr) {
+      heap->free(llScratch->base);
+      llScratch->base = nullptr;
+    }
+  }
   // Buffers outside the heap: one pipelined kernel through heap scratch. The scratch is carved out here, where every
   // rank is (building the collection is collective), never on a code path that only some ranks may take.
   auto pipeScratch = std::make_shared<PipeScratch>();
@@ -341,6 +400,11 @@ std::shared_ptr<Algorithm> selectDefaultAlgorithm(
     size_t pktMax = world <= 2 ? (1u << 20) : (world <= 4 ? (256u << 10) : (128u << 10));
     // buffers outside the heap pay the scratch detour on the large-message path, so packets stay ahead a little longer
     if (!request.symmetricMemory) pktMax *= 2;
+    // 128-byte lines carry 15/16 payload instead of 1/2: ahead of the 16-byte packets from 64 KB on and of the two-shot
+    // kernels (two cross-rank barriers, ~20 us before the first byte) up to a few MB (measured on two B200s in graph
+    // replay: 1 MB 7.1 vs 10.4 us with LL16, 2 MB 11.0 vs 23.7 us two-shot, 4 MB 18.6 vs 27.2 us)
+    auto pkt128 = get("default_allreduce_packet_ll128");
+    if (pkt128 && n > (64u << 10) && n <= pkt128->messageRange().second) return pkt128;
     if (n <= pktMax && n <= llCap && pkt) return pkt;
     if (request.symmetricMemory && n % 16 == 0) {
       // with two ranks the switch has nothing to combine: plain peer loads and stores on 128 SMs win from 4 MB on

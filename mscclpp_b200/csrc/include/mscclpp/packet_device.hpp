@@ -148,6 +148,37 @@ MSCCLPP_DEVICE_INLINE bool ll128Read(const LL128Line* line, uint32_t sub, uint32
   }
 }
 
+// The fast form, as NCCL's LL128 uses the format: ONE 16-byte load per lane, taken by the eight lanes in one warp
+// instruction, and the line is accepted as loaded when lane 7's copy carries the flag. It rests on the property that makes
+// the format worth having at all - the eight 16-byte stores of ll128Write leave as one 128-byte transaction and arrive as
+// one, and the eight loads here are one transaction too, so flag and payload of a line are never from different writes.
+// (That holds for GPUs connected by NVLink, where 128 bytes is the transfer unit end to end; ll128Read above makes no
+// such assumption and pays a system-scope fence and a second read per line for it.) Returns false on budget expiry.
+MSCCLPP_DEVICE_INLINE bool ll128ReadFast(const LL128Line* line, uint32_t sub, uint32_t groupMask, uint64_t flag, uint4& payload,
+                                         DeviceStatus* st, uint64_t budgetNs, uint32_t rank = 0, uint32_t peer = 0) {
+  uint4 v = ptx::ld_volatile_v4(&line->w[sub]);
+  bool mine = sub != 7 || ((v.z == static_cast<uint32_t>(flag)) && (v.w == static_cast<uint32_t>(flag >> 32)));
+  if ((__ballot_sync(groupMask, mine) & groupMask) == groupMask) {
+    payload = v;
+    return true;
+  }
+  SpinGuard g(st, budgetNs);
+  bool alive = true;
+  while (true) {
+    v = ptx::ld_volatile_v4(&line->w[sub]);
+    mine = sub != 7 || ((v.z == static_cast<uint32_t>(flag)) && (v.w == static_cast<uint32_t>(flag >> 32)));
+    if ((__ballot_sync(groupMask, mine) & groupMask) == groupMask) {
+      payload = v;
+      return true;
+    }
+    if (alive && !g.keepSpinning()) {
+      g.report(kDevTimeoutPacket, rank, 129, peer, flag, v.z);
+      alive = false;
+    }
+    if ((__ballot_sync(groupMask, alive) & groupMask) != groupMask) return false;
+  }
+}
+
 #endif  // __CUDACC__
 
 }  // namespace mscclpp

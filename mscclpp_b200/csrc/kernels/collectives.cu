@@ -255,14 +255,14 @@ __global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
 // The same exchange as allreduceLLKernel with 128-byte lines instead of 16-byte packets: a line carries 120 bytes of
 // payload and one 8-byte flag (15/16 of the scratch traffic is payload, against 1/2 with LL16), and is written by eight
 // consecutive lanes of a warp in ONE instruction, so that it leaves the SM as one 128-byte transaction; the receiver
-// takes a line once the flag lane sees this launch's epoch (packet_device.hpp: ll128Write / ll128Read, every wait
+// takes a line once the flag lane sees this launch's epoch (packet_device.hpp: ll128Write / ll128ReadFast, every wait
 // bounded). Line L covers bytes [120 L, 120 L + 120) of the buffer: lane s < 7 of the line's group holds bytes
 // [16 s, 16 s + 16) of them, lane 7 the last 8. Pieces start on 8-byte boundaries, so they move as two 8-byte words.
 // Role of the reference's packet allreduce for mid-size messages (its LL protocol has the 8- and 16-byte packets only,
 // include/mscclpp/packet_device.hpp); the line format follows the description in this library's own header.
-MSCCLPP_DEVICE_INLINE uint4 loadPiece(const char* base, uint64_t off, uint64_t bytes, int pieceBytes) {
+MSCCLPP_DEVICE_INLINE uint4 loadPiece(const char* base, uint64_t off, uint64_t bytes, int pieceBytes, bool aligned8) {
   uint4 v = make_uint4(0, 0, 0, 0);
-  if (off + pieceBytes <= bytes) {
+  if (aligned8 && off + pieceBytes <= bytes) {
     const uint2 lo = *reinterpret_cast<const uint2*>(base + off);
     v.x = lo.x;
     v.y = lo.y;
@@ -280,8 +280,8 @@ MSCCLPP_DEVICE_INLINE uint4 loadPiece(const char* base, uint64_t off, uint64_t b
   }
   return v;
 }
-MSCCLPP_DEVICE_INLINE void storePiece(char* base, uint64_t off, uint64_t bytes, int pieceBytes, uint4 v) {
-  if (off + pieceBytes <= bytes) {
+MSCCLPP_DEVICE_INLINE void storePiece(char* base, uint64_t off, uint64_t bytes, int pieceBytes, uint4 v, bool aligned8) {
+  if (aligned8 && off + pieceBytes <= bytes) {
     *reinterpret_cast<uint2*>(base + off) = make_uint2(v.x, v.y);
     if (pieceBytes == 16) *reinterpret_cast<uint2*>(base + off + 8) = make_uint2(v.z, v.w);
   } else if (off < bytes) {
@@ -310,12 +310,15 @@ __global__ void __launch_bounds__(512, 1) allreduceLL128Kernel(CollArgs a) {
   const uint32_t sub = threadIdx.x & 7;
   const uint32_t groupMask = 0xffu << ((threadIdx.x & 31) & ~7u);
   const int pieceBytes = sub == 7 ? 8 : 16;
+  // pieces move as 8-byte words when both buffers allow it, byte by byte otherwise (slow, but every rank may take the
+  // decision for itself: it changes nothing on the wire)
+  const bool aligned8 = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 7) == 0;
   const uint64_t firstLine = (static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 3;
   const uint64_t lineStep = (static_cast<uint64_t>(gridDim.x) * blockDim.x) >> 3;
 
   // ---- send: my whole input to every peer
   for (uint64_t line = firstLine; line < numLines; line += lineStep) {
-    const uint4 d = loadPiece(in, line * kLL128PayloadBytes + sub * 16, bytes, pieceBytes);
+    const uint4 d = loadPiece(in, line * kLL128PayloadBytes + sub * 16, bytes, pieceBytes, aligned8);
     for (int i = 1; i < world; i++) {
       const int p = (rank + i) % world;
       LL128Line* dst = reinterpret_cast<LL128Line*>(c.peerBase[p] + bufOff + static_cast<uint64_t>(rank) * slotBytes) + line;
@@ -329,13 +332,13 @@ __global__ void __launch_bounds__(512, 1) allreduceLL128Kernel(CollArgs a) {
   bool healthy = true;
   for (uint64_t line = firstLine; line < numLines && healthy; line += lineStep) {
     const uint64_t off = line * kLL128PayloadBytes + sub * 16;
-    const uint4 own = loadPiece(in, off, bytes, pieceBytes);
+    const uint4 own = loadPiece(in, off, bytes, pieceBytes, aligned8);
     Accum<T, Op> acc;
     for (int p = 0; p < world; p++) {
       uint4 v = own;
       if (p != rank) {
         const LL128Line* src = reinterpret_cast<const LL128Line*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * slotBytes) + line;
-        if (!ll128Read(src, sub, groupMask, flag, v, c.status, c.timeoutNs, rank, p)) {
+        if (!ll128ReadFast(src, sub, groupMask, flag, v, c.status, c.timeoutNs, rank, p)) {
           healthy = false;
           break;
         }
@@ -344,7 +347,7 @@ __global__ void __launch_bounds__(512, 1) allreduceLL128Kernel(CollArgs a) {
       if (p == 0) acc.init(v); else acc.add(v);
     }
     // (a group leaves the loop together: ll128Read returns the same answer to its eight lanes)
-    if (healthy) storePiece(out, off, bytes, pieceBytes, acc.result());
+    if (healthy) storePiece(out, off, bytes, pieceBytes, acc.result(), aligned8);
   }
 }
 
@@ -665,8 +668,7 @@ cudaError_t launchAllreduceLL128(const CollArgs& args, DataType dtype, ReduceOp 
   if (args.ll128Scratch == nullptr || args.ll128SlotBytes % 128 != 0 || lines * sizeof(LL128Line) > args.ll128SlotBytes) return cudaErrorInvalidValue;
   if (reinterpret_cast<uintptr_t>(args.ll128Scratch) % 128 != 0) return cudaErrorInvalidValue;
   if (nBlocks < 1 || nThreads < 32 || nThreads > 512 || nThreads % 32 != 0) return cudaErrorInvalidValue;
-  if (args.norm || args.nvls || args.bytes % 8 != 0) return cudaErrorInvalidValue;  // pieces move as 8-byte words
-  if ((reinterpret_cast<uintptr_t>(args.in) | reinterpret_cast<uintptr_t>(args.out)) % 8 != 0) return cudaErrorInvalidValue;
+  if (args.norm || args.nvls) return cudaErrorInvalidValue;
   MSCCLPP_DISPATCH_TYPE_OP(launchLL128Typed, dtype, op, args, nBlocks, nThreads, stream);
 }
 

@@ -44,8 +44,9 @@ cudaError_t launchAllreduceLL(const CollArgs& args, DataType dtype, ReduceOp op,
                               cudaStream_t stream);
 
 // One-shot LL128 allreduce: as launchAllreduceLL with 128-byte lines (120 bytes of payload + flag) instead of 16-byte packets,
-// for messages too long for 50 % scratch efficiency and too short for the two-shot algorithms. bytes % 8 == 0, buffers 8-byte
-// aligned; ceil(bytes / 120) * 128 <= args.ll128SlotBytes; peer stores only (no multimem form, no fused norm).
+// for messages too long for 50 % scratch efficiency and too short for the two-shot algorithms. Any size and alignment (8-byte
+// aligned buffers take the fast path); ceil(bytes / 120) * 128 <= args.ll128SlotBytes; peer stores only (no multimem form, no
+// fused norm).
 constexpr size_t ll128ScratchBytes(int world, size_t slotBytes) { return 2 * static_cast<size_t>(world) * slotBytes; }
 cudaError_t launchAllreduceLL128(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads, cudaStream_t stream);
 

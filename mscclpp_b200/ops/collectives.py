@@ -49,8 +49,15 @@ def ll_max_bytes(world: int) -> int:
 def select_allreduce(symm: SymmetricMemory, nbytes: int, symmetric: bool) -> str:
     ll_cap = _ll_capacity(symm)
     ll_max = ll_max_bytes(symm.world) * (1 if symmetric else 2)
+    if nbytes <= (64 << 10) and nbytes <= ll_cap:
+        return "nvls_packet" if symm.nvls else "packet"
+    # 128-byte lines (15/16 payload) are ahead of the 16-byte packets from 64 KB on and of the two-shot kernels (two cross-rank
+    # barriers, ~20 us before the first byte) up to a few MB: measured on two B200s in graph replay, 1 MB 7.1 vs 10.4 us
+    # with LL16, 2 MB 11.0 vs 23.7 us two-shot, 4 MB 18.6 vs 27.2 us
+    if nbytes <= ll128_max_bytes(symm.world) and (symmetric or not symm.emulated_mode):
+        return "packet128"
     if nbytes <= min(ll_max, ll_cap):
-        return "nvls_packet" if symm.nvls and nbytes <= (64 << 10) else "packet"
+        return "packet"
     # with two ranks the switch has nothing to combine: plain peer loads and stores on 128 SMs win from 4 MB on
     use_switch = symm.nvls and (symm.world > 2 or nbytes < (4 << 20))
     if not symmetric:  # (the pipelined kernels were tuned separately: through the switch up to 16 MB)
@@ -80,14 +87,18 @@ def _pipeline_slice(symm: SymmetricMemory) -> int:
     return (PIPELINE_SLICE_BYTES + unit - 1) // unit * unit
 
 
-LL128_MAX_BYTES = 2 << 20  # largest message the LL128 scratch is sized for (2 x world x 2.1 MB of heap)
+def ll128_max_bytes(world: int) -> int:
+    """Largest message the LL128 scratch is sized for: every rank receives the whole message from every peer, so the
+    useful range (and the scratch, 2 x world x 1.07 x this) shrinks as the world grows."""
+    return (4 << 20) if world <= 2 else ((2 << 20) if world <= 4 else (1 << 20))
+
 
 
 def _ll128_scratch(symm: SymmetricMemory):
     """Heap scratch of the LL128 allreduce, made and zeroed on first use (every rank gets here on the same call)."""
     cache = symm.__dict__.get("_ll128_scratch")
     if cache is None:
-        slot = (LL128_MAX_BYTES + 119) // 120 * 128
+        slot = (ll128_max_bytes(symm.world) + 119) // 120 * 128
         buf = symm.tensor((2 * symm.world * slot,), torch.uint8)
         ranks = range(symm.world) if symm.emulated_mode else [symm.rank]
         for r in ranks:
@@ -160,8 +171,8 @@ def all_reduce(symm: SymmetricMemory, inp: torch.Tensor, out: Optional[torch.Ten
         n.allreduce_ll(symm.heap, inp.data_ptr(), out.data_ptr(), nbytes, dt, _op(op), blocks, threads, _stream(stream),
                        algo == "nvls_packet", algo == "allpair_packet")
     elif algo == "packet128":
-        if nbytes % 8 != 0 or nbytes > LL128_MAX_BYTES:
-            raise ValueError("packet128 takes multiples of 8 bytes up to LL128_MAX_BYTES")
+        if nbytes > ll128_max_bytes(symm.world):
+            raise ValueError("packet128 takes messages up to ll128_max_bytes(world)")
         if symm.emulated_mode and not symmetric:
             raise ValueError("emulated ranks need heap tensors")
         scratch, slot = _ll128_scratch(symm)

@@ -44,7 +44,7 @@ def main():
             for algo in algos:
                 if algo in ("packet", "nvls_packet", "allpair_packet") and numel * inp.element_size() > (1 << 20):
                     continue
-                if algo == "packet128" and numel * inp.element_size() > (2 << 20):
+                if algo == "packet128" and numel * inp.element_size() > (1 << 20):
                     continue
                 for rep in range(2):
                     g = torch.Generator(device=dev).manual_seed(rank * 7 + numel + rep)
