@@ -41,7 +41,7 @@ def run(args) -> dict:
     out = {"config": {"experts": E, "topk": K, "hidden": H, "tokens_per_rank": T, "ep": ep, "routing": "uniform random top-k",
                       "l2": "64 MB of rows per direction per step plus receive buffers exceed the L2"}}
     for fp8 in (False, True):
-        disp = ExpertParallelDispatcher(symm, num_experts=E, hidden=H, max_tokens=T, topk=K, capacity=cap, fp8=fp8)
+        disp = ExpertParallelDispatcher(symm, num_experts=E, hidden=H, max_tokens=T, topk=K, capacity=cap, fp8=fp8, fp8_combine=not fp8)
         best = None
         for nb in args.blocks:
             us = time_eager(d, lambda: disp.dispatch(x, idx, n_blocks=nb), args.iters, args.warmup, check=symm.check) * 1e3
@@ -58,16 +58,33 @@ def run(args) -> dict:
             d.barrier()
             bestc = None
             for nb in args.blocks:
-                us = time_eager(d, lambda: disp.combine(idx, wts, slot_map, n_blocks=nb), args.iters, args.warmup, check=symm.check) * 1e3
+                us = time_eager(d, lambda: disp.combine(idx, wts, slot_map, n_blocks=nb, fp8=False), args.iters, args.warmup, check=symm.check) * 1e3
                 if bestc is None or us < bestc[0]:
                     bestc = (us, nb)
-            y = disp.combine(idx, wts, slot_map, n_blocks=bestc[1])
+            y = disp.combine(idx, wts, slot_map, n_blocks=bestc[1], fp8=False)
             torch.cuda.synchronize()
             ref = x.float() * wts.sum(1, keepdim=True)  # identity experts: y = sum_k w_k x
             err = (y.float() - ref).abs().max().item() / ref.abs().max().item()
             out["combine_bf16"] = {"us": round(bestc[0], 2), "blocks": bestc[1], "rel_err": err,
                                    "nvlink_gbs_per_gpu": round(remote_pairs * H * 2 / bestc[0] / 1e3, 1),
                                    "frac_of_link": round(remote_pairs * H * 2 / bestc[0] / 1e3 / LINK_GBS, 3)}
+            # the same combine with e4m3 expert outputs (1 x 128 scales): half the bytes pulled over NVLink
+            rows = int(disp.recv_counts[-1].item())
+            disp.quantize_expert_out(rows)
+            torch.cuda.synchronize()
+            d.barrier()
+            bestq = None
+            for nb in args.blocks:
+                us = time_eager(d, lambda: disp.combine(idx, wts, slot_map, n_blocks=nb, fp8=True), args.iters, args.warmup, check=symm.check) * 1e3
+                if bestq is None or us < bestq[0]:
+                    bestq = (us, nb)
+            yq = disp.combine(idx, wts, slot_map, n_blocks=bestq[1], fp8=True)
+            torch.cuda.synchronize()
+            errq = (yq.float() - ref).abs().max().item() / ref.abs().max().item()
+            q_bytes = H + H // 128 * 4
+            out["combine_fp8"] = {"us": round(bestq[0], 2), "blocks": bestq[1], "rel_err": errq,
+                                  "nvlink_gbs_per_gpu": round(remote_pairs * q_bytes / bestq[0] / 1e3, 1),
+                                  "frac_of_link": round(remote_pairs * q_bytes / bestq[0] / 1e3 / LINK_GBS, 3)}
         del disp
 
     # ---- NCCL baseline: sort pairs by destination rank, exchange sizes, all_to_all_single both ways
