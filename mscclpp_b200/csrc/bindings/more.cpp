@@ -44,7 +44,8 @@ void registerMoreBindings(py::module_& m) {
           },
           py::arg("rank"), py::arg("sendbuff"), py::arg("recvbuff"), py::arg("send_bytes"), py::arg("recv_bytes"),
           py::arg("dtype"), py::arg("plan"), py::arg("stream") = 0, py::arg("packet_type") = PacketType::LL16)
-      .def("reset", &Executor::reset);
+      .def("reset", &Executor::reset)
+      .def("zero_copy_launches", &Executor::zeroCopyLaunches);
 
   m.def(
       "tp_fused",

@@ -182,6 +182,12 @@ struct Layout {
   uint64_t chunkUpper = 0;
   uint64_t inOff = 0, outOff = 0, scratchOff = 0;  // heap offsets
   uint64_t inBytes = 0, outBytes = 0, scratchBytes = 0;  // extent of each buffer (scratch: one half, payload space)
+  // Buffers OUTSIDE the heap that every rank has mapped (zero copy): delta[r] = address of rank r's buffer in this process
+  // minus the base of rank r's heap, so that the interpreter's "heap base of the owner + offset" lands in the buffer
+  // (unsigned arithmetic, the sum wraps to the right address). Heap-resident buffers have the same delta on every rank:
+  // their heap offset.
+  bool inMapped = false, outMapped = false;
+  uint64_t inDelta[kMaxRanks] = {}, outDelta[kMaxRanks] = {};
 };
 
 class Resolver {
@@ -243,11 +249,13 @@ class Resolver {
     }
   }
 
-  uint64_t baseOf(const std::string& type) const {
-    if (type == "i") return l_.inOff;
-    if (type == "o") return l_.outOff;
+  uint64_t baseOf(const std::string& type, int owner, bool viaSwitch) const {
     if (type == "s") return l_.scratchOff;
-    throw Error("plan '" + p_.name + "': unknown buffer type '" + type + "'", ErrorCode::ExecutorError);
+    if (type != "i" && type != "o") throw Error("plan '" + p_.name + "': unknown buffer type '" + type + "'", ErrorCode::ExecutorError);
+    const bool mapped = type == "i" ? l_.inMapped : l_.outMapped;
+    if (!mapped) return type == "i" ? l_.inOff : l_.outOff;
+    if (viaSwitch) throw Error("plan '" + p_.name + "': switch channels need their buffers in the symmetric heap", ErrorCode::ExecutorError);
+    return type == "i" ? l_.inDelta[owner] : l_.outDelta[owner];
   }
 
   DevOperand operand(const json::Value& o, const json::Value& op) const {
@@ -291,7 +299,7 @@ class Resolver {
       type = o.at("type").asString();
     }
     d.isScratch = type == "s" ? 1 : 0;
-    d.offset = baseOf(type) + start;
+    d.offset = baseOf(type, d.rank, d.isSwitch != 0) + start;
     // Every range a plan names is checked against the buffer it names before anything is launched: a plan whose chunk
     // arithmetic runs past a buffer is reported here, with its name, instead of scribbling over the neighbours on the GPU
     // (the role a memory checker plays where one can be run). Packet ranges are checked in payload space; the packet
@@ -402,7 +410,8 @@ struct Executor::Impl {
     uint64_t scratchBytesTotal = 0;
     // device plans for the last message size
     uint64_t S = 0;
-    uint64_t inOff = 0, outOff = 0;
+    uint64_t placement = 0;   // hash of where the buffers were when the device plans were resolved
+    int zeroCopyPlan = -1;    // 1: the plan may run on mapped user buffers (memory channels only), 0: not, -1: not looked at yet
     std::vector<DevOp*> devOps;
     std::vector<DevPlan*> devPlans;
     int maxThreadBlocks = 0;
@@ -413,6 +422,92 @@ struct Executor::Impl {
     std::vector<std::vector<uint64_t>> portSignalsSent;    // [local rank][channel]: value last written to the peer's word
   };
   std::map<std::string, Context> contexts;
+
+  // ---- zero copy on buffers outside the heap (the reference's executor registers whatever buffer it is given and
+  // exchanges the handles, src/core/executor/executor.cc: setupRegisteredMemories): the buffer of every rank is mapped into
+  // every other rank's address space once and found again by (address, size).
+  struct MappedBuffer {
+    RegisteredMemory local;
+    std::vector<char> wire;                    // the local registration, serialised
+    std::vector<RegisteredMemory> remote;      // [rank], imported
+    std::vector<std::vector<char>> remoteWire; // what each rank sent last time (re-imported only when it changes)
+    uint64_t address[kMaxRanks] = {};          // rank r's buffer as mapped here
+    bool usable = false;
+  };
+  std::shared_ptr<mscclpp::Context> regContext;
+  std::map<std::pair<uintptr_t, size_t>, MappedBuffer> mapped;
+  uint64_t zeroCopyLaunches = 0;
+
+  // The first execute() that names a buffer (address, size) exchanges its registration with every rank; later calls find
+  // it in the cache. Like the reference's executor (its contexts are keyed by the buffers' addresses,
+  // src/core/executor/executor.cc), this assumes that the ranks see new buffers on the same calls - true of programs that
+  // allocate alike on every rank, and the only case in which an exchange could be entered by some ranks only.
+  // MSCCLPP_EXECUTOR_ZERO_COPY=0 switches zero copy off for programs that cannot promise it. Returns null when some rank
+  // could not export or import (then every rank stages, by the same answer, and remembers it).
+  MappedBuffer* mapEverywhere(void* ptr, size_t bytes) {
+    constexpr int kSlot = 1024;
+    auto bs = heap->bootstrap();
+    if (!bs) return nullptr;
+    if (!regContext) regContext = mscclpp::Context::create();
+    const int world = heap->world(), me = heap->rank();
+    auto found = mapped.find({reinterpret_cast<uintptr_t>(ptr), bytes});
+    if (found != mapped.end()) return found->second.usable ? &found->second : nullptr;
+    MappedBuffer& mb = mapped[{reinterpret_cast<uintptr_t>(ptr), bytes}];
+    if (mb.wire.empty()) {
+      try {
+        mb.local = regContext->registerMemory(ptr, bytes, TransportFlags(Transport::CudaIpc));
+        mb.wire = mb.local.serialize();
+        if (mb.wire.size() + 8 > kSlot) mb.wire.clear();
+      } catch (const BaseError& e) {
+        LOG_WARN(LogSubsys::EXEC, "buffer outside the heap cannot be exported (", e.what(), "): staged copies instead");
+        mb.wire.clear();
+      }
+      mb.remote.assign(world, RegisteredMemory());
+      mb.remoteWire.assign(world, {});
+    }
+    std::vector<char> all(static_cast<size_t>(world) * kSlot, 0);
+    {
+      char* mine = all.data() + static_cast<size_t>(me) * kSlot;
+      const uint32_t len = static_cast<uint32_t>(mb.wire.size());
+      std::memcpy(mine, &len, 4);
+      if (len) std::memcpy(mine + 8, mb.wire.data(), len);
+    }
+    bs->allGather(all.data(), kSlot);
+    int ok = 1;
+    for (int r = 0; r < world && ok; r++) {
+      const char* slot = all.data() + static_cast<size_t>(r) * kSlot;
+      uint32_t len = 0;
+      std::memcpy(&len, slot, 4);
+      if (len == 0 || len + 8 > kSlot) {
+        ok = 0;
+        break;
+      }
+      if (r == me) {
+        mb.address[r] = reinterpret_cast<uint64_t>(ptr);
+        continue;
+      }
+      std::vector<char> wire(slot + 8, slot + 8 + len);
+      if (wire != mb.remoteWire[r]) {
+        try {
+          mb.remote[r] = RegisteredMemory::deserialize(wire);
+          mb.remoteWire[r] = wire;
+        } catch (const BaseError& e) {
+          LOG_WARN(LogSubsys::EXEC, "cannot import rank ", r, "'s buffer (", e.what(), "): staged copies instead");
+          ok = 0;
+          break;
+        }
+      }
+      mb.address[r] = reinterpret_cast<uint64_t>(mb.remote[r].data());
+      if (mb.address[r] == 0) ok = 0;
+    }
+    // a rank that failed to import says so; everybody takes the common answer
+    std::vector<int> votes(world, 0);
+    votes[me] = ok;
+    bs->allGather(votes.data(), sizeof(int));
+    for (int v : votes) ok = ok && v;
+    mb.usable = ok != 0;
+    return mb.usable ? &mb : nullptr;
+  }
 
   // ---- host proxy for port-channel operations (the reference's executor owns a ProxyService the same way,
   // src/core/executor/executor.cc:145-155): one thread drains the FIFO the interpreter kernel pushes requests into.
@@ -570,11 +665,13 @@ Executor::~Executor() {
 }
 
 std::shared_ptr<SymmetricHeap> Executor::heap() const { return impl_->heap; }
+uint64_t Executor::zeroCopyLaunches() const { return impl_->zeroCopyLaunches; }
 
 void Executor::reset() {
   (void)cudaDeviceSynchronize();
   for (auto& kv : impl_->contexts) impl_->freeContext(kv.second);
   impl_->contexts.clear();
+  impl_->mapped.clear();  // imported mappings are released with their RegisteredMemory objects
 }
 
 void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuffSize, size_t recvBuffSize, DataType dataType,
@@ -639,12 +736,54 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
   ctx.scratchHalf = half;
   ctx.doubleScratch = p.doubleScratch;
 
-  // ---- buffers: in the heap -> in place; elsewhere -> staged
-  auto stage = [&](void* user, size_t bytes, void*& slot, size_t& slotBytes) -> void* {
-    if (user == nullptr || bytes == 0) return user;
-    // in place only when every rank's buffer sits in the heap at the same offset (the plan addresses peers by offset)
-    if (heap.symmetricOnAllRanks(user, bytes)) return user;
-    if (heap.emulated()) throw Error("emulated ranks need buffers from the heap", ErrorCode::InvalidUsage);
+  // ---- buffers: in the heap -> in place; elsewhere -> mapped on every rank (zero copy) when the plan and the size allow
+  // it, else staged through the heap
+  const bool sameBuffer = p.inplace && recvbuff == sendbuff;
+  auto symmetric = [&](void* user, size_t bytes) { return user == nullptr || bytes == 0 || heap.symmetricOnAllRanks(user, bytes); };
+  const bool inSym = symmetric(sendbuff, sendBuffSize);
+  const bool outSym = sameBuffer ? inSym : symmetric(recvbuff, recvBuffSize);
+  if ((!inSym || !outSym) && heap.emulated()) throw Error("emulated ranks need buffers from the heap", ErrorCode::InvalidUsage);
+  // Zero copy is decided from what every rank knows alike: the plan (memory channels only - the switch addresses heap
+  // offsets, and the host proxy of the port channels copies inside the heap), the message size (small messages are staged: two
+  // copies of less than a megabyte are not worth a mapping), the environment switch.
+  Impl::MappedBuffer* inMap = nullptr;
+  Impl::MappedBuffer* outMap = nullptr;
+  if (!inSym || !outSym) {
+    if (ctx.zeroCopyPlan < 0) {
+      bool eligible = true;
+      for (int r = 0; r < p.nRanks && eligible; r++) {
+        const json::Value& chans = p.root.at("gpus").at(r).at("channels");
+        for (size_t i = 0; i < chans.size() && eligible; i++) {
+          const std::string type = chans.at(i).at("channel_type").asString();
+          if (type == "port") eligible = false;
+          if (type == "switch") {
+            const std::string buf = chans.at(i).at(chans.at(i).contains("buffer_type") ? "buffer_type" : "buff").asString();
+            if (buf != "s") eligible = false;
+          }
+        }
+      }
+      ctx.zeroCopyPlan = eligible ? 1 : 0;
+    }
+    const char* knob = std::getenv("MSCCLPP_EXECUTOR_ZERO_COPY");
+    size_t minBytes = 1u << 20;
+    if (const char* e = std::getenv("MSCCLPP_EXECUTOR_ZERO_COPY_MIN_BYTES")) minBytes = static_cast<size_t>(std::strtoull(e, nullptr, 10));
+    const bool want = ctx.zeroCopyPlan == 1 && !(knob != nullptr && knob[0] == '0') && std::max(sendBuffSize, recvBuffSize) >= minBytes;
+    if (want) {
+      bool ok = true;
+      if (!inSym) {
+        inMap = impl_->mapEverywhere(sendbuff, sendBuffSize);
+        ok = inMap != nullptr;
+      }
+      if (ok && !outSym && !sameBuffer) {
+        outMap = impl_->mapEverywhere(recvbuff, recvBuffSize);
+        ok = outMap != nullptr;
+      }
+      if (!ok) inMap = outMap = nullptr;  // (the same answer on every rank) -> staged
+      if (sameBuffer) outMap = inMap;
+    }
+  }
+  auto stage = [&](void* user, size_t bytes, bool isSym, void*& slot, size_t& slotBytes) -> void* {
+    if (user == nullptr || bytes == 0 || isSym) return user;
     if (slotBytes < bytes) {
       if (slot) {
         MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
@@ -656,8 +795,8 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
     }
     return slot;
   };
-  void* in = stage(sendbuff, sendBuffSize, ctx.stageIn, ctx.stageInBytes);
-  void* out = p.inplace && recvbuff == sendbuff ? in : stage(recvbuff, recvBuffSize, ctx.stageOut, ctx.stageOutBytes);
+  void* in = inMap ? sendbuff : stage(sendbuff, sendBuffSize, inSym, ctx.stageIn, ctx.stageInBytes);
+  void* out = sameBuffer ? in : (outMap ? recvbuff : stage(recvbuff, recvBuffSize, outSym, ctx.stageOut, ctx.stageOutBytes));
   if (in != sendbuff) MSCCLPP_CUDATHROW(cudaMemcpyAsync(in, sendbuff, sendBuffSize, cudaMemcpyDeviceToDevice, stream));
   const uint64_t base = reinterpret_cast<uint64_t>(heap.localBase());
   layout.inOff = in ? reinterpret_cast<uint64_t>(in) - base : 0;
@@ -666,11 +805,33 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
     if (in == nullptr) layout.inOff = layout.outOff;
     if (out == nullptr) layout.outOff = layout.inOff;
   }
+  const DeviceComm dc = heap.deviceComm();
+  uint64_t placement = 1469598103934665603ull;  // what the device plans were resolved against (offsets, or every rank's mapping)
+  auto mix = [&](uint64_t v) { placement = (placement ^ v) * 1099511628211ull; };
+  if (inMap) {
+    layout.inMapped = true;
+    for (int r = 0; r < p.nRanks; r++) {
+      layout.inDelta[r] = inMap->address[r] - dc.peerBase[r];
+      mix(layout.inDelta[r]);
+    }
+  } else {
+    mix(layout.inOff);
+  }
+  if (outMap) {
+    layout.outMapped = true;
+    for (int r = 0; r < p.nRanks; r++) {
+      layout.outDelta[r] = outMap->address[r] - dc.peerBase[r];
+      mix(layout.outDelta[r] + 1);
+    }
+  } else {
+    mix(layout.outOff + 1);
+  }
+  if (inMap || outMap) impl_->zeroCopyLaunches++;
   layout.scratchOff = ctx.scratch ? reinterpret_cast<uint64_t>(ctx.scratch) - base : 0;
   layout.inBytes = in ? sendBuffSize : recvBuffSize;
   layout.outBytes = out ? recvBuffSize : sendBuffSize;
   layout.scratchBytes = maxScratchChunks * layout.chunkUpper;
-  if (ctx.inOff != layout.inOff || ctx.outOff != layout.outOff) rebuild = true;
+  if (ctx.placement != placement) rebuild = true;
 
   // ---- device plans (cached per message size and buffer placement)
   if (rebuild) {
@@ -696,8 +857,7 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
       ctx.maxThreadBlocks = std::max<int>(ctx.maxThreadBlocks, static_cast<int>(res.plan.nThreadBlocks));
     }
     ctx.S = layout.S;
-    ctx.inOff = layout.inOff;
-    ctx.outOff = layout.outOff;
+    ctx.placement = placement;
   }
 
   ExecArgs args{};

@@ -58,6 +58,8 @@ class Executor {
   // Drops cached plan contexts (their heap allocations are returned).
   void reset();
   std::shared_ptr<SymmetricHeap> heap() const;
+  // How many execute() calls so far ran directly on buffers outside the heap (mapped on every rank) instead of staging them.
+  uint64_t zeroCopyLaunches() const;
 
  private:
   struct Impl;

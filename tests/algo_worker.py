@@ -138,6 +138,30 @@ def main():
     err = (heap_in.float() - expect).abs().max().item()
     report("dsl_algorithm", rc == 0 and err <= 6e-2 * max(1.0, expect.abs().max().item()), err=err)
 
+    # the same plan on ORDINARY tensors (outside the heap), large enough for zero copy: every rank maps every rank's buffer
+    # once, the plan runs on the tensors themselves, and a second call on the same tensors finds the mappings again
+    big = 1 << 20  # 2 MiB of bf16
+    user = torch.empty(big, dtype=torch.bfloat16, device=dev)
+    before = executor.zero_copy_launches()
+    for rep in range(2):
+        g = torch.Generator(device=dev).manual_seed(rank * 3 + rep)
+        user.copy_(torch.randn(big, generator=g, device=dev).to(torch.bfloat16))
+        expect = reference(user).to(torch.bfloat16).float()
+        torch.cuda.synchronize()
+        dist.barrier()
+        rc = dsl.execute(None, user.data_ptr(), user.data_ptr(), big * 2, big * 2, n.DataType.bfloat16, n.ReduceOp.SUM, stream, executor)
+        torch.cuda.synchronize()
+        symm.check()
+        err = (user.float() - expect).abs().max().item()
+        report(f"dsl_algorithm/user_buffer_zero_copy/{rep}", rc == 0 and err <= 6e-2 * max(1.0, expect.abs().max().item()), err=err)
+    report("dsl_algorithm/zero_copy_taken", executor.zero_copy_launches() == before + 2, launches=executor.zero_copy_launches() - before)
+    # a small message on an ordinary tensor is staged (two short copies cost less than a mapping)
+    small_t = torch.ones(4096, dtype=torch.bfloat16, device=dev)
+    before = executor.zero_copy_launches()
+    rc = dsl.execute(None, small_t.data_ptr(), small_t.data_ptr(), 8192, 8192, n.DataType.bfloat16, n.ReduceOp.SUM, stream, executor)
+    torch.cuda.synchronize()
+    report("dsl_algorithm/small_user_buffer_staged", rc == 0 and executor.zero_copy_launches() == before and bool((small_t == world).all().item()))
+
     torch.cuda.synchronize()
     dist.barrier()
     executor.reset()
