@@ -261,9 +261,9 @@ def main():
 
     # the switch reduction wins from 8 ranks on; with 2 or 4 peers plain peer loads/stores are as fast or faster
     nvls_opts = ([True, False] if world <= 4 else [True]) if symm.nvls else [False]
-    variants = [(m, nv, r, c) for m in (0, 1) for nv in nvls_opts for r in (8, 16, 32, 48, 64) for c in (1, 2)] + [(-1, symm.nvls, 0, 1)]
+    variants = [(m, nv, r, c) for m in (0, 1, 3) for nv in nvls_opts for r in (8, 16, 32, 48, 64) for c in (1, 2)] + [(-1, symm.nvls, 0, 1)]
     if world > 4 and symm.nvls:  # plain peer loads/stores for comparison
-        variants += [(1, False, r, 2) for r in (32, 64)]
+        variants += [(m, False, r, 2) for m in (1, 3) for r in (32, 64)]
     if world == 1:
         variants = [(1, False, 64, 1), (-1, False, 0, 1), (-2, False, 0, 1), (-2, False, 0, 2), (-3, False, 0, 1), (-3, False, 0, 2)]
     best = {}
@@ -307,9 +307,9 @@ def main():
     head_mode, head_nvls, head_reducers, head_core = best[HEADLINE_T]
     head_fn = fused(HEADLINE_T, head_mode, head_nvls, head_reducers, head_core)
     ms_per_step = time_steps(head_fn, args.steps, max(args.warmup, 3))
-    # kernels of this library per step: the one-kernel paths (fused mode 0, the single-GPU layer) launch 1, fused mode 1 adds
-    # its local scale pass, the unfused path is GEMM + allreduce/norm kernel
-    launches = args.steps * (1 if head_mode in (0, -3) else 2)
+    # kernels of this library per step: the one-kernel paths (fused modes 0 and 3, the single-GPU layer) launch 1, fused mode 1
+    # adds its local scale pass, the unfused path is GEMM + allreduce/norm kernel
+    launches = args.steps * (1 if head_mode in (0, 3, -3) else 2)
 
     # ------------------------------------------------------------------ per-T table: eager launches and CUDA-graph replay
     tp_us, tp_graph_us, tp_unfused_us, tp_baseline_us = {}, {}, {}, {}
@@ -458,7 +458,7 @@ def main():
                                    "tpLocalFusedKernel (tcgen05 GEMM + residual + RMSNorm in one launch)" if head_mode == -3 else
                                    "gemmBf16Kernel (tcgen05) then twoShot/LL allreduce+residual+RMSNorm kernel" if head_mode < 0 else
                                    "tpFusedKernel (tcgen05 GEMM + multimem/peer reduce + residual + RMSNorm in one launch)" +
-                                   ("" if head_mode == 0 else " + local scale pass")),
+                                   ("" if head_mode == 0 else (" with the scale pass inside the launch" if head_mode == 3 else " + local scale pass"))),
                         "per_T": {str(t): list(best[t]) for t in TOKEN_SIZES},
                         "autotune_us (mode/nvls/reducer_ctas/gemm_core)": tune_scores[str(HEADLINE_T)]},
             "tp_layer_us": tp_us,

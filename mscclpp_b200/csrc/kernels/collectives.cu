@@ -130,7 +130,7 @@ MSCCLPP_DEVICE_INLINE uint4 scaleRow(uint4 x, float rinv, const char* gamma, uin
 // One-shot LL16 allreduce
 // ============================================================================================
 template <typename T, ReduceOp Op, bool kNvls, bool kNorm, bool kLL8 = false>
-__global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
+__global__ void __launch_bounds__(kNorm ? 1024 : 512, 1) allreduceLLKernel(CollArgs a) {
   static_assert(!(kLL8 && (kNvls || kNorm)), "the 8-byte packet form is the plain peer-store exchange only");
   const DeviceComm& c = a.comm;
   const int rank = deviceRank(c);
@@ -186,30 +186,76 @@ __global__ void __launch_bounds__(1024, 1) allreduceLLKernel(CollArgs a) {
   // where the round trip of that atomic would be exposed)
   retireLaunchEarly(c, rank, flag);
 
-  // ---- receive + reduce
+  // ---- receive + reduce. The packets of ALL peers are requested before the first one is looked at: polled one after the
+  // other they cost a dependent L2 round trip each (14 in a row with eight ranks); a packet that has not arrived yet is
+  // then waited for on its own, with the usual budget.
   bool healthy = true;
   auto recvUnit = [&](uint64_t u, uint4& result) -> bool {
     const uint4 own = loadUnit(in, u, bytes);
+    const uint64_t slotBase = c.peerBase[rank] + bufOff + u * 32;
     Accum<T, Op> acc;
-    for (int p = 0; p < world; p++) {
-      uint4 v = own;
-      if (p != rank) {
-        if constexpr (kLL8) {
-          const LL8Packet* pk = reinterpret_cast<const LL8Packet*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * c.llSlotBytes + u * 32);
-          if (!pk[0].read(flag, v.x, c.status, c.timeoutNs, rank, p)) return false;
-          if (!pk[1].read(flag, v.y, c.status, c.timeoutNs, rank, p)) return false;
-          if (!pk[2].read(flag, v.z, c.status, c.timeoutNs, rank, p)) return false;
-          if (!pk[3].read(flag, v.w, c.status, c.timeoutNs, rank, p)) return false;
-        } else {
-          const LL16Packet* pk = reinterpret_cast<const LL16Packet*>(c.peerBase[rank] + bufOff +
-                                                                     static_cast<uint64_t>(p) * c.llSlotBytes + u * 32);
-          uint2 lo, hi;
-          if (!pk[0].read(flag, lo, c.status, c.timeoutNs, rank, p)) return false;
-          if (!pk[1].read(flag, hi, c.status, c.timeoutNs, rank, p)) return false;
-          v = make_uint4(lo.x, lo.y, hi.x, hi.y);
+    // one peer's word out of its slot, waiting (bounded) for packets that are not there yet
+    auto slowRead = [&](int p, uint4& v) -> bool {
+      if constexpr (kLL8) {
+        const LL8Packet* pk = reinterpret_cast<const LL8Packet*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
+        return pk[0].read(flag, v.x, c.status, c.timeoutNs, rank, p) && pk[1].read(flag, v.y, c.status, c.timeoutNs, rank, p) &&
+               pk[2].read(flag, v.z, c.status, c.timeoutNs, rank, p) && pk[3].read(flag, v.w, c.status, c.timeoutNs, rank, p);
+      } else {
+        const LL16Packet* pk = reinterpret_cast<const LL16Packet*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
+        uint2 lo, hi;
+        if (!pk[0].read(flag, lo, c.status, c.timeoutNs, rank, p) || !pk[1].read(flag, hi, c.status, c.timeoutNs, rank, p)) return false;
+        v = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        return true;
+      }
+    };
+    // Peers are taken in batches whose packets are all requested before any flag is looked at (eight at a time where the
+    // registers allow it, four in the variants with 64 registers per thread or four packets per word). When every packet
+    // of the batch is there - the usual case - the words are added straight from the registers; else the batch is read
+    // again peer by peer with the bounded waits. Either way the contributions are added in rank order.
+    constexpr int kBatch = (kNorm || kLL8) ? 4 : 8;
+    for (int p0 = 0; p0 < world; p0 += kBatch) {
+      uint4 word[kBatch];
+      bool allHere = true;
+      if constexpr (kLL8) {
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+          const int p = p0 + i;
+          if (p < world && p != rank) {
+            const char* pk = reinterpret_cast<const char*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
+            const uint4 a0 = ptx::ld_volatile_v4(pk), a1 = ptx::ld_volatile_v4(pk + 16);  // two packets per 16 bytes
+            word[i] = make_uint4(a0.x, a0.z, a1.x, a1.z);
+            allHere = allHere && a0.y == flag && a0.w == flag && a1.y == flag && a1.w == flag;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+          const int p = p0 + i;
+          if (p < world && p != rank) {
+            const char* pk = reinterpret_cast<const char*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
+            const uint4 a0 = ptx::ld_volatile_v4(pk), a1 = ptx::ld_volatile_v4(pk + 16);
+            word[i] = make_uint4(a0.x, a0.z, a1.x, a1.z);
+            allHere = allHere && a0.y == flag && a0.w == flag && a1.y == flag && a1.w == flag;
+          }
         }
       }
-      if (p == 0) acc.init(v); else acc.add(v);
+      if (allHere) {
+#pragma unroll
+        for (int i = 0; i < kBatch; i++) {
+          const int p = p0 + i;
+          if (p < world) {
+            const uint4 v = p == rank ? own : word[i];
+            if (p == 0) acc.init(v); else acc.add(v);
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int p = p0; p < p0 + kBatch && p < world; p++) {
+          uint4 v = own;
+          if (p != rank && !slowRead(p, v)) return false;
+          if (p == 0) acc.init(v); else acc.add(v);
+        }
+      }
     }
     result = acc.result();
     return true;
@@ -333,18 +379,40 @@ __global__ void __launch_bounds__(512, 1) allreduceLL128Kernel(CollArgs a) {
   for (uint64_t line = firstLine; line < numLines && healthy; line += lineStep) {
     const uint64_t off = line * kLL128PayloadBytes + sub * 16;
     const uint4 own = loadPiece(in, off, bytes, pieceBytes, aligned8);
+    // every peer's line is requested before the first flag is looked at (one L2 round trip instead of one per peer)
+    uint4 got[8];
+#pragma unroll
+    for (int p = 0; p < 8; p++) {
+      if (p < world && p != rank) {
+        const LL128Line* src = reinterpret_cast<const LL128Line*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * slotBytes) + line;
+        got[p] = ptx::ld_volatile_v4(&src->w[sub]);
+      }
+    }
     Accum<T, Op> acc;
-    for (int p = 0; p < world; p++) {
+#pragma unroll
+    for (int p = 0; p < 8; p++) {
+      if (p < world && healthy) {
+        uint4 v = own;
+        if (p != rank) {
+          v = got[p];
+          const bool mine = sub != 7 || (v.z == static_cast<uint32_t>(flag) && v.w == static_cast<uint32_t>(flag >> 32));
+          if ((__ballot_sync(groupMask, mine) & groupMask) != groupMask) {
+            const LL128Line* src = reinterpret_cast<const LL128Line*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * slotBytes) + line;
+            if (!ll128ReadFast(src, sub, groupMask, flag, v, c.status, c.timeoutNs, rank, p)) healthy = false;
+          }
+          if (sub == 7) v.z = v.w = 0;  // the flag is not data
+        }
+        if (p == 0) acc.init(v); else acc.add(v);
+      }
+    }
+    for (int p = 8; p < world && healthy; p++) {
       uint4 v = own;
       if (p != rank) {
         const LL128Line* src = reinterpret_cast<const LL128Line*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * slotBytes) + line;
-        if (!ll128ReadFast(src, sub, groupMask, flag, v, c.status, c.timeoutNs, rank, p)) {
-          healthy = false;
-          break;
-        }
-        if (sub == 7) v.z = v.w = 0;  // the flag is not data
+        if (!ll128ReadFast(src, sub, groupMask, flag, v, c.status, c.timeoutNs, rank, p)) healthy = false;
+        if (sub == 7) v.z = v.w = 0;
       }
-      if (p == 0) acc.init(v); else acc.add(v);
+      acc.add(v);
     }
     // (a group leaves the loop together: ll128Read returns the same answer to its eight lanes)
     if (healthy) storePiece(out, off, bytes, pieceBytes, acc.result(), aligned8);
@@ -653,7 +721,7 @@ cudaError_t launchTwoShotTyped(const CollArgs& a, int nBlocks, int nThreads, cud
 cudaError_t launchAllreduceLL(const CollArgs& args, DataType dtype, ReduceOp op, int nBlocks, int nThreads,
                               cudaStream_t stream) {
   if (args.bytes * 2 > args.comm.llSlotBytes) return cudaErrorInvalidValue;
-  if (nBlocks < 1 || nThreads < 32 || nThreads > 1024) return cudaErrorInvalidValue;
+  if (nBlocks < 1 || nThreads < 32 || nThreads > (args.norm ? 1024 : 512)) return cudaErrorInvalidValue;
   if (args.norm && ((static_cast<uint64_t>(args.hidden) * dataTypeSize(dtype)) % 16 != 0)) return cudaErrorInvalidValue;
   MSCCLPP_DISPATCH_TYPE_OP(launchLLTyped, dtype, op, args, nBlocks, nThreads, stream);
 }

@@ -237,18 +237,44 @@ __global__ void __launch_bounds__(kThreads, 1) tpDecodeKernel(TpDecodeArgs a) {
             pk[1].write(mine.z, mine.w, epoch);
           }
         }
-        // contributions are added in rank order, so that every rank computes bit-identical sums
+        // contributions are added in rank order, so that every rank computes bit-identical sums. All peers' packets are
+        // requested before any flag is looked at (one L2 round trip instead of two per peer); if some are not there yet,
+        // the peers are read again one by one with the bounded waits.
         float sum[8];
-        for (int p = 0; p < world && healthy; p++) {
-          uint4 v = mine;
-          if (p != rank) {
-            const LL16Packet* pk = reinterpret_cast<const LL16Packet*>(local + bufOff + static_cast<uint64_t>(p) * c.llSlotBytes + u * 32);
-            uint2 lo, hi;
-            healthy = pk[0].read(epoch, lo, c.status, c.timeoutNs, rank, p) && pk[1].read(epoch, hi, c.status, c.timeoutNs, rank, p);
-            v = make_uint4(lo.x, lo.y, hi.x, hi.y);
+        const uint64_t slotBase = local + bufOff + u * 32;
+        uint4 word[8];
+        bool allHere = true;
+#pragma unroll
+        for (int p = 0; p < 8; p++) {
+          if (p < world && p != rank) {
+            const char* pk = reinterpret_cast<const char*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
+            const uint4 a0 = ptx::ld_volatile_v4(pk), a1 = ptx::ld_volatile_v4(pk + 16);
+            word[p] = make_uint4(a0.x, a0.z, a1.x, a1.z);
+            allHere = allHere && a0.y == epoch && a0.w == epoch && a1.y == epoch && a1.w == epoch;
           }
-          if (p == 0) Vec16<bf16>::toFloat(v, sum);
-          else accumulate16<bf16, SUM>(sum, v);
+        }
+        if (allHere) {
+#pragma unroll
+          for (int p = 0; p < 8; p++) {
+            if (p < world) {
+              const uint4 v = p == rank ? mine : word[p];
+              if (p == 0) Vec16<bf16>::toFloat(v, sum);
+              else accumulate16<bf16, SUM>(sum, v);
+            }
+          }
+        } else {
+#pragma unroll 1
+          for (int p = 0; p < world && healthy; p++) {
+            uint4 v = mine;
+            if (p != rank) {
+              const LL16Packet* pk = reinterpret_cast<const LL16Packet*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
+              uint2 lo, hi;
+              healthy = pk[0].read(epoch, lo, c.status, c.timeoutNs, rank, p) && pk[1].read(epoch, hi, c.status, c.timeoutNs, rank, p);
+              v = make_uint4(lo.x, lo.y, hi.x, hi.y);
+            }
+            if (p == 0) Vec16<bf16>::toFloat(v, sum);
+            else accumulate16<bf16, SUM>(sum, v);
+          }
         }
         mine = Vec16<bf16>::fromFloat(sum);
       }

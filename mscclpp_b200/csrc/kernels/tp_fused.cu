@@ -82,6 +82,13 @@ MSCCLPP_DEVICE_INLINE uint32_t* tileCounter(const DeviceComm& c, int rank, int m
   return reinterpret_cast<uint32_t*>(c.peerBase[rank] + c.auxFlagsOff + kTpTileCounterOffset) + mBlk;
 }
 
+MSCCLPP_DEVICE_INLINE uint32_t* landedFlag(const DeviceComm& c, int onRank, int unit) {
+  return reinterpret_cast<uint32_t*>(c.peerBase[onRank] + c.auxFlagsOff + kTpLandedOffset) + unit;
+}
+MSCCLPP_DEVICE_INLINE uint32_t* unitDoneCounter(const DeviceComm& c, int rank, int unit) {
+  return reinterpret_cast<uint32_t*>(c.peerBase[rank] + c.auxFlagsOff + kTpUnitDoneOffset) + unit;
+}
+
 struct PartialStoreSignal {
   static constexpr bool kNeedsTileBarrier = true;
   const DeviceComm* comm;
@@ -195,6 +202,115 @@ MSCCLPP_DEVICE_INLINE void scatterWord(const DeviceComm& c, int rank, uint64_t h
   }
 }
 
+// ---- mode 3: the local scale pass inside the launch -------------------------------------------------------------
+// One warp turns landed rows into out = h * rinv * gamma, local memory only. Rows are handed out in ascending order
+// from a per-rank counter; a row's ownership unit must have been announced by its owner (landedFlag, written behind a
+// system-scope fence that covers every store of the unit's rows - see publisherWarp). h and rinv were written by other
+// GPUs: they are read through L2 (ld.global.cg), behind an acquire on the flag.
+constexpr int kPubQueue = 64;  // finished rows a reducer group may have waiting for the publisher
+
+MSCCLPP_DEVICE_INLINE bool scaleRowsWarp(const TpFusedArgs& a, int rank, uint32_t epoch, int lane) {
+  const DeviceComm& c = a.comm;
+  const int M = a.shape.M, N = a.shape.N, rpu = a.rowsPerUnit;
+  const uint64_t local = c.peerBase[rank];
+  const uint64_t base = c.peerBase[c.rank];
+  const uint4* hBase = reinterpret_cast<const uint4*>(local + (reinterpret_cast<uint64_t>(a.residualOut) - base));
+  uint4* outBase = reinterpret_cast<uint4*>(local + (reinterpret_cast<uint64_t>(a.out) - base));
+  const float* rinv = reinterpret_cast<const float*>(local + (reinterpret_cast<uint64_t>(a.rinv) - base));
+  const uint4* g4 = reinterpret_cast<const uint4*>(a.gamma);
+  const bool hasGamma = a.gamma != nullptr;
+  const int words = N / 8;
+  uint32_t* scaleCounter = &control(c, rank)->gridSync[6];  // zero at launch start (finishLaunch re-arms it)
+  int knownUnit = -1;
+  for (;;) {
+    int s = 0;
+    if (lane == 0) s = static_cast<int>(atomicAdd(scaleCounter, 1u));
+    s = __shfl_sync(0xffffffffu, s, 0);
+    if (s >= M) return true;
+    const int unit = s / rpu;
+    if (unit != knownUnit) {
+      int ok = 1;
+      if (lane == 0) {
+        ok = waitGreaterEqualBackoff(landedFlag(c, rank, unit), epoch, c.status, c.timeoutNs, kDevTimeoutFlag, rank, 7600 + (unit & 255),
+                                     unit % c.world)
+                 ? 1
+                 : 0;
+      }
+      ok = __shfl_sync(0xffffffffu, ok, 0);  // (the shuffle also orders the other lanes' loads behind lane 0's acquire)
+      if (!ok) return false;
+      knownUnit = unit;
+    }
+    const float sc = __ldcg(rinv + s);
+    const __nv_bfloat16 hi1 = __float2bfloat16_rn(sc);
+    const __nv_bfloat162 hi = __bfloat162bfloat162(hi1);
+    const __nv_bfloat162 lo = __float2bfloat162_rn(sc - __bfloat162float(hi1));
+    const uint4* src = hBase + static_cast<size_t>(s) * words;
+    uint4* dst = outBase + static_cast<size_t>(s) * words;
+    constexpr int kDepth = 16;
+    for (int w0 = lane; w0 < words; w0 += 32 * kDepth) {
+      uint4 v[kDepth];
+#pragma unroll
+      for (int k = 0; k < kDepth; k++) {
+        const int w = w0 + 32 * k;
+        if (w < words) v[k] = ptx::ld_cg_v4(src + w);
+      }
+#pragma unroll
+      for (int k = 0; k < kDepth; k++) {
+        const int w = w0 + 32 * k;
+        if (w < words) {
+          const uint4 g = hasGamma ? __ldg(g4 + w) : make_uint4(0, 0, 0, 0);
+          dst[w] = make_uint4(scaleBf16x2(v[k].x, g.x, hi, lo, hasGamma), scaleBf16x2(v[k].y, g.y, hi, lo, hasGamma),
+                              scaleBf16x2(v[k].z, g.z, hi, lo, hasGamma), scaleBf16x2(v[k].w, g.w, hi, lo, hasGamma));
+        }
+      }
+    }
+  }
+}
+
+// The publisher warp of a CTA (mode 3). Reducer groups push the unit of every row they have finished into their ring;
+// this warp, and only this warp, pays for making those rows' stores system-visible: it takes what has been pushed, issues
+// ONE system-scope fence (cumulative: it covers the stores of the threads whose pushes it has observed), and then counts
+// the rows on their unit's counter in this rank's memory. Whoever completes a unit resets the counter, fences again (the
+// acquire side of the counter chain: the other CTAs' publishers fenced before they counted) and writes the launch epoch
+// into the unit's "landed" word on every rank. The reducer groups never wait for a fence.
+MSCCLPP_DEVICE_INLINE void publisherWarp(const TpFusedArgs& a, int rank, uint32_t epoch, int lane, int numProducers, const int (*queue)[kPubQueue],
+                                         volatile int* tails, volatile int* heads, volatile int* producersLeft) {
+  const DeviceComm& c = a.comm;
+  const int M = a.shape.M, rpu = a.rowsPerUnit;
+  int head = 0;
+  SpinGuard guard(c.status, c.timeoutNs);
+  for (;;) {
+    const int left = *producersLeft;  // read BEFORE the tails: a group pushes its last row before it signs off
+    __syncwarp();
+    int tail = head;
+    if (lane < numProducers) tail = tails[lane];
+    if (!__any_sync(0xffffffffu, tail != head)) {
+      if (left == 0) return;
+      __nanosleep(200);
+      if (!guard.keepSpinning()) {
+        if (lane == 0) guard.report(kDevTimeoutFlag, rank, 7700, 0, left, 0);
+        return;
+      }
+      continue;
+    }
+    __threadfence_system();
+    if (lane < numProducers) {
+      for (int i = head; i != tail; i++) {
+        const int unit = queue[lane][i % kPubQueue];
+        const uint32_t prev = atomicAdd(unitDoneCounter(c, rank, unit), 1u);
+        const int rowsInUnit = M - unit * rpu < rpu ? M - unit * rpu : rpu;
+        if (static_cast<int>(prev) + 1 == rowsInUnit) {
+          *unitDoneCounter(c, rank, unit) = 0;  // nobody else counts on this unit in this launch: ready for the next one
+          __threadfence_system();
+          for (int p = 0; p < c.world; p++) ptx::st_relaxed_sys(landedFlag(c, (rank + p) % c.world, unit), epoch);
+        }
+      }
+      head = tail;
+      heads[lane] = head;
+    }
+  }
+}
+
 template <bool kNvls>
 // `slot` names this CTA in the closing cross-rank barrier (the same grid runs on every rank). Rows are handed out
 // dynamically, in ascending order, from a per-rank counter: CTAs that were GEMM CTAs join in when their tiles are done,
@@ -230,6 +346,29 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
   const int lane = threadIdx.x % kGroupThreads;
   if (lane == 0) okSmem[group] = 1;
   groupBarrier(group);
+
+  // mode 3: the last group of the CTA does not reduce - its first warp publishes finished rows, its second warp scales
+  // landed rows from the start; the other groups scale when they run out of rows to reduce
+  const bool fold = a.mode == 3;
+  constexpr int kProducers = kGroupsPerCta - 1;
+  __shared__ int pubQueue[kProducers][kPubQueue];
+  __shared__ volatile int pubTail[kProducers], pubHead[kProducers];
+  __shared__ volatile int producersLeft;
+  if (threadIdx.x < kProducers) pubTail[threadIdx.x] = pubHead[threadIdx.x] = 0;
+  if (threadIdx.x == 0) producersLeft = fold ? kProducers : 0;
+  __syncthreads();
+  if (fold && group == kGroupsPerCta - 1) {
+    const int lane32 = threadIdx.x & 31;
+    if (((threadIdx.x >> 5) & 1) == 0) {
+      publisherWarp(a, rank, epoch, lane32, kProducers, pubQueue, pubTail, pubHead, &producersLeft);
+    }
+    if (!scaleRowsWarp(a, rank, epoch, lane32) && lane32 == 0) okSmem[group] = 0;
+    __syncthreads();
+    bool everyOk = true;
+    for (int g = 0; g < kGroupsPerCta; g++) everyOk = everyOk && okSmem[g] != 0;
+    if (everyOk) rankBarrier(c, rank, 2, slot, epoch);
+    return;
+  }
 
   __shared__ int nextRow[kGroupsPerCta];
   uint32_t* rowCounter = &control(c, rank)->gridSync[7];  // zero at launch start (finishLaunch re-arms it)
@@ -446,14 +585,35 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
     const float total = groupSum(ss, sumSmem[group], group);
     const float rinv = rsqrtf(total / static_cast<float>(N) + a.eps);
 
-    // ---- normalise and publish (mode 0), or publish 1/rms only (mode 1)
-    if (a.mode == 1) {
+    // ---- normalise and publish (mode 0), or publish 1/rms only (modes 1 and 3)
+    if (a.mode == 1 || fold) {
       if (lane == 0) {
         const uint64_t off = rinvOff + static_cast<uint64_t>(row) * 4;
         if constexpr (kNvls) {
           ptx::multimem_st_u32(reinterpret_cast<void*>(c.mcBase + off), __float_as_uint(rinv));
         } else {
           for (int p = 0; p < world; p++) ptx::st_relaxed_sys(reinterpret_cast<uint32_t*>(c.peerBase[p] + off), __float_as_uint(rinv));
+        }
+        if (fold) {
+          // hand the row to the publisher (every thread of the group issued its stores before the barriers of groupSum)
+          const int t = pubTail[group];
+          SpinGuard g(c.status, c.timeoutNs);
+          bool room = true;
+          while (t - pubHead[group] >= kPubQueue) {
+            __nanosleep(100);
+            if (!g.keepSpinning()) {
+              g.report(kDevTimeoutFlag, rank, 7800 + group, 0, t, pubHead[group]);
+              room = false;
+              break;
+            }
+          }
+          if (room) {
+            pubQueue[group][t % kPubQueue] = row / rpu;
+            __threadfence_block();
+            pubTail[group] = t + 1;
+          } else {
+            okSmem[group] = 0;
+          }
         }
       }
     } else {
@@ -490,6 +650,15 @@ MSCCLPP_DEVICE_INLINE void reducerCta(const TpFusedArgs& a, int rank, uint32_t e
     tl[8] = tlGather;
     tl[9] = tlMath;
     tl[10] = tlScatter;
+  }
+  if (fold) {
+    // this group has pushed its last row: tell the publisher, then join the scale pass (every warp for itself)
+    groupBarrier(group);
+    if (lane == 0) {
+      __threadfence_block();
+      atomicSub(const_cast<int*>(&producersLeft), 1);
+    }
+    if (okSmem[group] != 0 && !scaleRowsWarp(a, rank, epoch, threadIdx.x & 31) && (threadIdx.x & 31) == 0) okSmem[group] = 0;
   }
   // every store of mine is issued: meet the peers' reducers with the same index. After it, everything
   // their reducers wrote into my buffers has landed.
@@ -905,7 +1074,7 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
   if (N * 2 / 16 > kWordsPerThread * kGroupThreads) return cudaErrorInvalidValue;
   const int numMBlk = (M + gemm::kBlockM - 1) / gemm::kBlockM;
   if (numMBlk > kMaxMBlk) return cudaErrorInvalidValue;
-  if (args.mode == 1 && args.rinv == nullptr) return cudaErrorInvalidValue;
+  if ((args.mode == 1 || args.mode == 3) && args.rinv == nullptr) return cudaErrorInvalidValue;
   if (args.nvls && args.comm.mcBase == 0) return cudaErrorInvalidValue;
   const int emu = args.emuRanks > 1 ? args.emuRanks : 1;
   if (emu > 8) return cudaErrorInvalidValue;
@@ -928,6 +1097,7 @@ cudaError_t launchTpFused(const TpFusedArgs& argsIn, const void* const* A, const
     while (rpu > 1 && M < rpu * world) rpu >>= 1;
     args.rowsPerUnit = rpu;
   }
+  if (args.mode == 3 && (args.residualOut == nullptr || (M + args.rowsPerUnit - 1) / args.rowsPerUnit > kTpMaxUnits)) return cudaErrorInvalidValue;
   TmapSet maps;
   for (int e = 0; e < emu; e++) {
     cudaError_t err = gemm::makeTensorMapBf16(&maps.a[e], A[e], M, K, static_cast<uint64_t>(K) * 2, args.shape.aBoxRows);
@@ -973,7 +1143,7 @@ cudaError_t launchTpReduceNorm(const TpFusedArgs& argsIn, int numCtas, cudaStrea
   const int world = args.comm.world;
   if (M <= 0 || N % 8 != 0 || N * 2 / 16 > kWordsPerThread * kGroupThreads || world > 8) return cudaErrorInvalidValue;
   if (args.mode != 0 && args.mode != 1) return cudaErrorInvalidValue;
-  if (args.mode == 1 && args.rinv == nullptr) return cudaErrorInvalidValue;
+  if ((args.mode == 1 || args.mode == 3) && args.rinv == nullptr) return cudaErrorInvalidValue;
   if (args.nvls && args.comm.mcBase == 0) return cudaErrorInvalidValue;
   const int emu = args.emuRanks > 1 ? args.emuRanks : 1;
   if (emu > 8) return cudaErrorInvalidValue;

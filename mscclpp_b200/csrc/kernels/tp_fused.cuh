@@ -25,7 +25,10 @@ struct TpFusedArgs {
   int numGemmCtas;              // 0 = all SMs but the reducers
   int rowsPerUnit;              // ownership granule, power of two <= 128; 0 = pick from M and world
   int mode;                     // 0: owners broadcast out + residualOut; 1: owners broadcast residualOut + rinv;
-                                // 2: reduce-scatter, out is this rank's [M / world, N] block (M % (world * 128) == 0)
+                                // 2: reduce-scatter, out is this rank's [M / world, N] block (M % (world * 128) == 0);
+                                // 3: as 1, and `out` is produced inside the same launch: owners announce every ownership
+                                // unit whose rows have landed everywhere, and warps that have no row to reduce turn
+                                // landed rows into out = h * rinv * gamma locally (no second launch)
   int nvls;                     // multimem through comm.mcBase instead of peer loads/stores
   int emuRanks;                 // > 1: that many emulated ranks in one cooperative launch (tests)
   int noFlags;                  // set by launchTpReduceNorm: rows are complete at kernel start, no per-block flags
@@ -53,6 +56,13 @@ constexpr size_t kTpReadyFlagBytes = static_cast<size_t>(kTpMaxMBlk) * kMaxRanks
 constexpr size_t kTpTileCounterOffset = kTpReadyFlagBytes;  // bytes from the start of the aux region
 constexpr size_t kTpTileCounterBytes = static_cast<size_t>(kTpMaxMBlk) * 4;
 static_assert(kTpTileCounterOffset + kTpTileCounterBytes <= kAuxFlagBytes, "aux flag region too small");
+// mode 3: [kTpMaxUnits] "unit has landed on this rank" words written by the unit's owner (epoch-stamped), then [kTpMaxUnits]
+// counters of finished rows per unit in the owner's own memory (zero between launches)
+constexpr int kTpMaxUnits = 4096;
+constexpr size_t kTpLandedOffset = 512u << 10;
+constexpr size_t kTpUnitDoneOffset = kTpLandedOffset + static_cast<size_t>(kTpMaxUnits) * 4;
+static_assert(kTpLandedOffset >= kTpTileCounterOffset + kTpTileCounterBytes && kTpUnitDoneOffset + static_cast<size_t>(kTpMaxUnits) * 4 <= kAuxFlagBytes,
+              "aux flag region too small");
 
 // A[e], B[e]: operands of (emulated) rank e; real multi-GPU use passes one entry each.
 // A: [M, K] bf16 row-major activations, B: [N, K] bf16 row-major weights (nn.Linear layout).

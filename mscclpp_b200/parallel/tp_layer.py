@@ -67,7 +67,9 @@ class RowParallelLinearNorm:
                       sys_fence: Optional[bool] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """Same result as forward(), in ONE kernel: GEMM tiles, cross-rank reduction, residual add and norm
         overlap tile by tile. mode 1 halves NVLink traffic by broadcasting h and 1/rms only and finishing
-        `out` with a local pass (second, local-only launch); mode 0 is one launch. Default: mode 1 from 1024 tokens on
+        `out` with a local pass (second, local-only launch); mode 0 is one launch; mode 3 is mode 1 with the local pass
+        inside the same launch (owners announce the row units that have landed everywhere, and warps without a row to
+        reduce turn landed rows into `out`). Default: mode 1 from 1024 tokens on
         (measured on 2 and 8 GPUs: the saved bytes outweigh the second launch there), else mode 0. block_n: N tile of the one-SM GEMM core (64/128/256), -1
         forces the two-SM core (256 x 256 tiles on SM pairs), 0 picks (two-SM from 1024 tokens on).
 
@@ -105,7 +107,7 @@ class RowParallelLinearNorm:
                    self.residual_out[rows].data_ptr(), self.out[rows].data_ptr(), self.gamma.data_ptr(), self.rinv[rows].data_ptr(), t,
                    self.out_features, self.k_shard, self.eps, bn, num_gemm_ctas, num_reducers, rows_per_unit, mode, nvls, s,
                    0 if timeline is None else timeline.data_ptr(), -1 if sys_fence is None else int(bool(sys_fence)))
-        if mode == 1:
+        if mode == 1:  # (mode 3 has produced `out` already)
             ranks = range(self.symm.world) if self.symm.emulated_mode else [self.symm.rank]
             for r in ranks:  # one local pass per (emulated) rank
                 view = (lambda t_: self.symm.rank_view(t_, r)) if self.symm.emulated_mode else (lambda t_: t_)

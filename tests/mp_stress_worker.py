@@ -60,7 +60,7 @@ def main():
 
     sums_h = torch.zeros((launches, max_t), device=dev)
     sums_y = torch.zeros((launches, max_t), device=dev)
-    configs = [(mode, nv, False) for mode in (0, 1) for nv in ([False, True] if symm.nvls else [False])]
+    configs = [(mode, nv, False) for mode in (0, 1, 3) for nv in ([False, True] if symm.nvls else [False])]
     configs.append((0, False, True))  # the conservative publication (system-scope fence + release stores) as well
     configs.append((1, symm.nvls, True))
     for mode, nv, sys_fence in configs:

@@ -154,7 +154,7 @@ def main():
         h = (gathered_reference(part).to(torch.bfloat16).float() + residual.float()).to(torch.bfloat16).float()
         ref = (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + layer.eps) * layer.gamma.float()).to(torch.bfloat16).float()
         for use_nvls in ([False, True] if symm.nvls else [False]):
-            for mode in (0, 1):
+            for mode in (0, 1, 3):
                 layer.out.zero_()
                 layer.residual_out.zero_()
                 torch.cuda.synchronize()

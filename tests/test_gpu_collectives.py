@@ -268,7 +268,7 @@ def test_decode_layer_one_kernel(world, tokens, hidden, k):
 
 
 @pytest.mark.parametrize("world", [1, 2, 4])
-@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("mode", [0, 1, 3])
 @pytest.mark.parametrize("tokens,hidden,k", [(1, 1024, 128), (8, 2048, 256), (128, 8192, 256), (300, 1024, 512), (1024, 2048, 128)])
 def test_fused_tp_layer_one_kernel(world, mode, tokens, hidden, k):
     """GEMM + allreduce + residual + RMSNorm in one launch, all ranks emulated on one GPU."""
