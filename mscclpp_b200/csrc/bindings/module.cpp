@@ -347,15 +347,16 @@ PYBIND11_MODULE(_native, m) {
   m.def(
       "two_shot",
       [](SymmetricHeap& heap, uintptr_t in, uintptr_t out, uint64_t bytes, DataType dtype, ReduceOp op, int mode,
-         int nBlocks, int nThreads, uintptr_t stream, bool nvls, int root, int oneShot) {
+         int nBlocks, int nThreads, uintptr_t stream, bool nvls, int root, int oneShot, uintptr_t stamps) {
         CollArgs a = makeCollArgs(heap, in, out, bytes, mode, nvls);
         a.root = root;
         a.oneShot = oneShot;
+        a.stamps = reinterpret_cast<unsigned long long*>(stamps);
         checkCuda(launchTwoShot(a, dtype, op, nBlocks, nThreads, reinterpret_cast<cudaStream_t>(stream)), "two_shot");
       },
       py::arg("heap"), py::arg("input"), py::arg("output"), py::arg("bytes"), py::arg("dtype"), py::arg("op") = SUM,
       py::arg("mode") = 0, py::arg("n_blocks") = 32, py::arg("n_threads") = 512, py::arg("stream") = 0,
-      py::arg("nvls") = false, py::arg("root") = 0, py::arg("one_shot") = 0);
+      py::arg("nvls") = false, py::arg("root") = 0, py::arg("one_shot") = 0, py::arg("stamps") = 0);
   m.def(
       "pipeline_allreduce",
       [](SymmetricHeap& heap, uintptr_t in, uintptr_t out, uint64_t bytes, DataType dtype, ReduceOp op, uintptr_t scratch, uint64_t sliceBytes,

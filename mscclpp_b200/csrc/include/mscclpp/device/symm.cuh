@@ -115,20 +115,33 @@ MSCCLPP_DEVICE_INLINE void retireLaunchEarly(const DeviceComm& c, int rank, uint
 }
 
 // Cross-rank barrier for block `slot` (same slot index on every rank). All threads of the block
-// call it. Writes made by this block before the call are visible to peers after their barrier
-// returns. Returns false if a peer did not show up within the budget.
-MSCCLPP_DEVICE_INLINE bool rankBarrier(const DeviceComm& c, int rank, int phase, int slot, uint32_t epoch) {
+// call it. With `publish` (the default) writes made by this block before the call are visible to peers after their
+// barrier returns: one system-scope fence (behind the block's own barrier, so it covers every thread's writes), then a
+// relaxed flag store - a release store on top of the fence would pay for a second fence. Without `publish` the flag
+// only says "this rank has got here" (an opening barrier, when everything the peers will read was written by earlier
+// launches): no fence at all. The wait polls with relaxed loads and takes one acquire when the flag has arrived.
+// Returns false if a peer did not show up within the budget.
+MSCCLPP_DEVICE_INLINE bool rankBarrier(const DeviceComm& c, int rank, int phase, int slot, uint32_t epoch, bool publish = true) {
   __shared__ int ok_s;
   if (threadIdx.x == 0) ok_s = 1;
   __syncthreads();
   const int t = threadIdx.x;
   if (t < c.world && t != rank) {
-    ptx::fence_acq_rel_sys();
-    ptx::st_release_sys(&control(c, t)->barrier[phase][slot][rank], epoch);
-    if (!waitGreaterEqual(&control(c, rank)->barrier[phase][slot][t], epoch, c.status, c.timeoutNs, kDevTimeoutBarrier,
-                          rank, phase * 1000 + slot, t)) {
-      ok_s = 0;
+    if (publish) ptx::fence_acq_rel_sys();
+    ptx::st_relaxed_sys(&control(c, t)->barrier[phase][slot][rank], epoch);
+    const uint32_t* mine = &control(c, rank)->barrier[phase][slot][t];
+    SpinGuard g(c.status, c.timeoutNs);
+    uint32_t v;
+    bool here = true;
+    while (static_cast<int32_t>((v = ptx::ld_relaxed_sys(mine)) - epoch) < 0) {
+      if (!g.keepSpinning()) {
+        g.report(kDevTimeoutBarrier, rank, phase * 1000 + slot, t, epoch, v);
+        here = false;
+        break;
+      }
     }
+    if (here) (void)ptx::ld_acquire_sys(mine);
+    else ok_s = 0;
   }
   __syncthreads();
   return ok_s != 0;

@@ -517,8 +517,15 @@ __global__ void __launch_bounds__(512, 1) twoShotKernel(CollArgs a) {
   const uint64_t outOff = reinterpret_cast<uint64_t>(a.out) - c.peerBase[c.rank];
   const uint32_t epoch = launchEpoch(c, rank);
   const int slot = blockIdx.x;
+  unsigned long long* tl = (a.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) ? a.stamps : nullptr;
+  if (tl) tl[0] = ptx::globaltimer();
 
-  bool healthy = rankBarrier(c, rank, 0, slot, epoch);
+  // opening barrier: the peers only have to be IN this launch (what they will read of mine was written by earlier
+  // launches, and what I will read of theirs likewise): a flag, no fence
+  bool healthy = rankBarrier(c, rank, 0, slot, epoch, false);
+  // no grid barrier in this kernel: the block counts itself out of the launch now, under the work, not at the end
+  retireLaunchEarly(c, rank, epoch);
+  if (tl) tl[1] = ptx::globaltimer();
 
   if (healthy) {
     if constexpr (kNorm) {
@@ -629,9 +636,10 @@ __global__ void __launch_bounds__(512, 1) twoShotKernel(CollArgs a) {
       else sweep(std::integral_constant<int, 4>{});
     }
   }
+  if (tl) tl[2] = ptx::globaltimer();
   // all my stores are issued; tell the peers, and learn that theirs into my buffers are done
   if (healthy) rankBarrier(c, rank, 1, slot, epoch);
-  finishLaunch(c, rank, epoch);
+  if (tl) tl[3] = tl[4] = ptx::globaltimer();
 }
 
 // --------------------------------------------------------------------------------------------

@@ -34,6 +34,8 @@ struct CollArgs {
   int ll8;                  // one-shot allreduce only: 8-byte {data, flag} packets instead of 16-byte ones (peer stores, no norm)
   void* ll128Scratch;       // launchAllreduceLL128: symmetric-heap scratch of ll128ScratchBytes(world, slot) bytes at the same offset
   uint64_t ll128SlotBytes;  // on every rank, zeroed once before its first use; a slot takes ceil(bytes / 120) lines of 128 bytes
+  unsigned long long* stamps;  // launchTwoShot, optional: five globaltimer reads of block 0 (entry, after the opening barrier,
+                               // after its share of the work, after the closing barrier, at the end); null = none
   int oneShot;              // launchTwoShot, allreduce over peer loads: every rank reduces the whole buffer for itself (no stores
                             // to peers). 0 = the launcher decides (currently: never), 1 = always, 2 = never.
 };
