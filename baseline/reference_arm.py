@@ -218,7 +218,6 @@ def main() -> int:
         result_host.copy_(out[-1].sum(dtype=torch.float32).reshape(1), non_blocking=True)  # one small kernel on the last row
         torch.cuda.current_stream().synchronize()
 
-    e2e_ms = time_steps(e2e_step, args.steps, warmup)
     t_end = time.time() + 1.5
     while time.time() < t_end:
         for _ in range(20):
@@ -226,6 +225,8 @@ def main() -> int:
         torch.cuda.synchronize()
     barrier()
     clocks = sampler.stop() if rank == 0 else {}
+    # timed with the clock sampler stopped (a driver query by nvidia-smi inside a host-synchronised step stalls it)
+    e2e_ms = time_steps(e2e_step, args.steps, warmup)
 
     # ---- allreduce sweep through the same path (ordinary torch tensors, in place), eager and CUDA-graph replay
     sweep = []

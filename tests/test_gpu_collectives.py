@@ -41,7 +41,10 @@ def _tol(dtype):
 @pytest.mark.parametrize("numel", [8, 40, 1024, 33000, 262144])
 def test_allreduce_ll(world, dtype, numel, algo):
     from mscclpp_b200.ops import all_reduce
+    from mscclpp_b200.ops.collectives import ll128_max_bytes
 
+    if algo == "packet128" and numel * torch.empty((), dtype=dtype).element_size() > ll128_max_bytes(world):
+        pytest.skip("beyond the range the LL128 scratch is sized for at this world size")
     symm = _symm(world)
     inp = symm.tensor((numel,), dtype)
     out = symm.tensor((numel,), dtype)
