@@ -142,7 +142,7 @@ struct PipeScratch {
 
 // Largest message of the LL128 allreduce: every rank receives the whole message from every peer, so the useful range (and
 // the scratch, 2 x world x 1.07 x this) shrinks as the world grows.
-size_t ll128MaxBytes(int world) { return world <= 2 ? (4u << 20) : (world <= 4 ? (2u << 20) : (256u << 10)); }
+size_t ll128MaxBytes(int world) { return world <= 2 ? (4u << 20) : (world <= 4 ? (512u << 10) : (256u << 10)); }
 
 // One-shot allreduce with 128-byte lines (120 bytes of payload + flag), in a zeroed heap scratch of its own.
 std::shared_ptr<Algorithm> makeLL128(const std::string& name, std::shared_ptr<SymmetricHeap> heap, std::shared_ptr<PipeScratch> scratch,

@@ -187,47 +187,23 @@ __global__ void __launch_bounds__(kNorm ? 1024 : 512, 1) allreduceLLKernel(CollA
   retireLaunchEarly(c, rank, flag);
 
   // ---- receive + reduce. The packets of ALL peers are requested before the first one is looked at: polled one after the
-  // other they cost a dependent L2 round trip each (14 in a row with eight ranks); a packet that has not arrived yet is
-  // then waited for on its own, with the usual budget.
+  // other they cost a dependent L2 round trip each (14 in a row with eight ranks).
   bool healthy = true;
   auto recvUnit = [&](uint64_t u, uint4& result) -> bool {
     const uint4 own = loadUnit(in, u, bytes);
     const uint64_t slotBase = c.peerBase[rank] + bufOff + u * 32;
     Accum<T, Op> acc;
-    // one peer's word out of its slot, waiting (bounded) for packets that are not there yet
-    auto slowRead = [&](int p, uint4& v) -> bool {
-      if constexpr (kLL8) {
-        const LL8Packet* pk = reinterpret_cast<const LL8Packet*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
-        return pk[0].read(flag, v.x, c.status, c.timeoutNs, rank, p) && pk[1].read(flag, v.y, c.status, c.timeoutNs, rank, p) &&
-               pk[2].read(flag, v.z, c.status, c.timeoutNs, rank, p) && pk[3].read(flag, v.w, c.status, c.timeoutNs, rank, p);
-      } else {
-        const LL16Packet* pk = reinterpret_cast<const LL16Packet*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
-        uint2 lo, hi;
-        if (!pk[0].read(flag, lo, c.status, c.timeoutNs, rank, p) || !pk[1].read(flag, hi, c.status, c.timeoutNs, rank, p)) return false;
-        v = make_uint4(lo.x, lo.y, hi.x, hi.y);
-        return true;
-      }
-    };
-    // Peers are taken in batches whose packets are all requested before any flag is looked at (eight at a time where the
-    // registers allow it, four in the variants with 64 registers per thread or four packets per word). When every packet
-    // of the batch is there - the usual case - the words are added straight from the registers; else the batch is read
-    // again peer by peer with the bounded waits. Either way the contributions are added in rank order.
+    // Peers are taken in batches (eight at a time where the registers allow it, four in the variants with 64 registers per
+    // thread). The packets of a batch are all requested before any flag is looked at, and polled TOGETHER until every one
+    // carries this launch's flag: the wait for the slowest peer is paid once, and one round trip after it everything is
+    // in registers. The contributions are added in rank order. (LL8 and LL16 share the layout: data words at even, flags
+    // at odd 32-bit positions.)
     constexpr int kBatch = (kNorm || kLL8) ? 4 : 8;
     for (int p0 = 0; p0 < world; p0 += kBatch) {
       uint4 word[kBatch];
-      bool allHere = true;
-      if constexpr (kLL8) {
-#pragma unroll
-        for (int i = 0; i < kBatch; i++) {
-          const int p = p0 + i;
-          if (p < world && p != rank) {
-            const char* pk = reinterpret_cast<const char*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
-            const uint4 a0 = ptx::ld_volatile_v4(pk), a1 = ptx::ld_volatile_v4(pk + 16);  // two packets per 16 bytes
-            word[i] = make_uint4(a0.x, a0.z, a1.x, a1.z);
-            allHere = allHere && a0.y == flag && a0.w == flag && a1.y == flag && a1.w == flag;
-          }
-        }
-      } else {
+      SpinGuard guard(c.status, c.timeoutNs);
+      for (;;) {
+        bool allHere = true;
 #pragma unroll
         for (int i = 0; i < kBatch; i++) {
           const int p = p0 + i;
@@ -238,21 +214,17 @@ __global__ void __launch_bounds__(kNorm ? 1024 : 512, 1) allreduceLLKernel(CollA
             allHere = allHere && a0.y == flag && a0.w == flag && a1.y == flag && a1.w == flag;
           }
         }
-      }
-      if (allHere) {
-#pragma unroll
-        for (int i = 0; i < kBatch; i++) {
-          const int p = p0 + i;
-          if (p < world) {
-            const uint4 v = p == rank ? own : word[i];
-            if (p == 0) acc.init(v); else acc.add(v);
-          }
+        if (allHere) break;
+        if (!guard.keepSpinning()) {
+          guard.report(kDevTimeoutPacket, rank, kLL8 ? 8 : 16, p0, flag, 0);
+          return false;
         }
-      } else {
-#pragma unroll 1
-        for (int p = p0; p < p0 + kBatch && p < world; p++) {
-          uint4 v = own;
-          if (p != rank && !slowRead(p, v)) return false;
+      }
+#pragma unroll
+      for (int i = 0; i < kBatch; i++) {
+        const int p = p0 + i;
+        if (p < world) {
+          const uint4 v = p == rank ? own : word[i];
           if (p == 0) acc.init(v); else acc.add(v);
         }
       }
@@ -379,30 +351,45 @@ __global__ void __launch_bounds__(512, 1) allreduceLL128Kernel(CollArgs a) {
   for (uint64_t line = firstLine; line < numLines && healthy; line += lineStep) {
     const uint64_t off = line * kLL128PayloadBytes + sub * 16;
     const uint4 own = loadPiece(in, off, bytes, pieceBytes, aligned8);
-    // every peer's line is requested before the first flag is looked at (one L2 round trip instead of one per peer)
+    // every peer's line is requested before the first flag is looked at, and the lines are polled together until the flag
+    // lane has seen this launch's flag on all of them (one wait for the slowest peer, one round trip after it)
     uint4 got[8];
+    {
+      SpinGuard guard(c.status, c.timeoutNs);
+      bool alive = true;
+      for (;;) {
+        bool mine = true;
 #pragma unroll
-    for (int p = 0; p < 8; p++) {
-      if (p < world && p != rank) {
-        const LL128Line* src = reinterpret_cast<const LL128Line*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * slotBytes) + line;
-        got[p] = ptx::ld_volatile_v4(&src->w[sub]);
+        for (int p = 0; p < 8; p++) {
+          if (p < world && p != rank) {
+            const LL128Line* src = reinterpret_cast<const LL128Line*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * slotBytes) + line;
+            got[p] = ptx::ld_volatile_v4(&src->w[sub]);
+            if (sub == 7) mine = mine && got[p].z == static_cast<uint32_t>(flag) && got[p].w == static_cast<uint32_t>(flag >> 32);
+          }
+        }
+        if ((__ballot_sync(groupMask, mine) & groupMask) == groupMask) break;
+        if (alive && !guard.keepSpinning()) {
+          guard.report(kDevTimeoutPacket, rank, 129, 0, flag, 0);
+          alive = false;
+        }
+        if ((__ballot_sync(groupMask, alive) & groupMask) != groupMask) {
+          healthy = false;
+          break;
+        }
       }
     }
     Accum<T, Op> acc;
+    if (healthy) {
 #pragma unroll
-    for (int p = 0; p < 8; p++) {
-      if (p < world && healthy) {
-        uint4 v = own;
-        if (p != rank) {
-          v = got[p];
-          const bool mine = sub != 7 || (v.z == static_cast<uint32_t>(flag) && v.w == static_cast<uint32_t>(flag >> 32));
-          if ((__ballot_sync(groupMask, mine) & groupMask) != groupMask) {
-            const LL128Line* src = reinterpret_cast<const LL128Line*>(c.peerBase[rank] + bufOff + static_cast<uint64_t>(p) * slotBytes) + line;
-            if (!ll128ReadFast(src, sub, groupMask, flag, v, c.status, c.timeoutNs, rank, p)) healthy = false;
+      for (int p = 0; p < 8; p++) {
+        if (p < world) {
+          uint4 v = own;
+          if (p != rank) {
+            v = got[p];
+            if (sub == 7) v.z = v.w = 0;  // the flag is not data
           }
-          if (sub == 7) v.z = v.w = 0;  // the flag is not data
+          if (p == 0) acc.init(v); else acc.add(v);
         }
-        if (p == 0) acc.init(v); else acc.add(v);
       }
     }
     for (int p = 8; p < world && healthy; p++) {

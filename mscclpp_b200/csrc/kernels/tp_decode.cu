@@ -238,22 +238,31 @@ __global__ void __launch_bounds__(kThreads, 1) tpDecodeKernel(TpDecodeArgs a) {
           }
         }
         // contributions are added in rank order, so that every rank computes bit-identical sums. All peers' packets are
-        // requested before any flag is looked at (one L2 round trip instead of two per peer); if some are not there yet,
-        // the peers are read again one by one with the bounded waits.
+        // requested before any flag is looked at, and polled together until all carry this launch's flag (the wait for the
+        // slowest peer is paid once, one round trip after it everything is in registers).
         float sum[8];
         const uint64_t slotBase = local + bufOff + u * 32;
         uint4 word[8];
-        bool allHere = true;
+        SpinGuard guard(c.status, c.timeoutNs);
+        for (;;) {
+          bool allHere = true;
 #pragma unroll
-        for (int p = 0; p < 8; p++) {
-          if (p < world && p != rank) {
-            const char* pk = reinterpret_cast<const char*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
-            const uint4 a0 = ptx::ld_volatile_v4(pk), a1 = ptx::ld_volatile_v4(pk + 16);
-            word[p] = make_uint4(a0.x, a0.z, a1.x, a1.z);
-            allHere = allHere && a0.y == epoch && a0.w == epoch && a1.y == epoch && a1.w == epoch;
+          for (int p = 0; p < 8; p++) {
+            if (p < world && p != rank) {
+              const char* pk = reinterpret_cast<const char*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
+              const uint4 a0 = ptx::ld_volatile_v4(pk), a1 = ptx::ld_volatile_v4(pk + 16);
+              word[p] = make_uint4(a0.x, a0.z, a1.x, a1.z);
+              allHere = allHere && a0.y == epoch && a0.w == epoch && a1.y == epoch && a1.w == epoch;
+            }
+          }
+          if (allHere) break;
+          if (!guard.keepSpinning()) {
+            guard.report(kDevTimeoutPacket, rank, 16, 0, epoch, 0);
+            healthy = false;
+            break;
           }
         }
-        if (allHere) {
+        if (healthy) {
 #pragma unroll
           for (int p = 0; p < 8; p++) {
             if (p < world) {
@@ -261,19 +270,6 @@ __global__ void __launch_bounds__(kThreads, 1) tpDecodeKernel(TpDecodeArgs a) {
               if (p == 0) Vec16<bf16>::toFloat(v, sum);
               else accumulate16<bf16, SUM>(sum, v);
             }
-          }
-        } else {
-#pragma unroll 1
-          for (int p = 0; p < world && healthy; p++) {
-            uint4 v = mine;
-            if (p != rank) {
-              const LL16Packet* pk = reinterpret_cast<const LL16Packet*>(slotBase + static_cast<uint64_t>(p) * c.llSlotBytes);
-              uint2 lo, hi;
-              healthy = pk[0].read(epoch, lo, c.status, c.timeoutNs, rank, p) && pk[1].read(epoch, hi, c.status, c.timeoutNs, rank, p);
-              v = make_uint4(lo.x, lo.y, hi.x, hi.y);
-            }
-            if (p == 0) Vec16<bf16>::toFloat(v, sum);
-            else accumulate16<bf16, SUM>(sum, v);
           }
         }
         mine = Vec16<bf16>::fromFloat(sum);

@@ -91,7 +91,7 @@ def ll128_max_bytes(world: int) -> int:
     """Largest message the LL128 scratch is sized for: every rank receives the whole message from every peer, so the
     useful range (and the scratch, 2 x world x 1.07 x this) shrinks as the world grows (measured on eight B200s in graph
     replay: 256 KB 10.8 us against 22.6 us two-shot through the switch, 512 KB 17.8 against 23.2, 1 MB 33.0 against 24.1)."""
-    return (4 << 20) if world <= 2 else ((2 << 20) if world <= 4 else (256 << 10))
+    return (4 << 20) if world <= 2 else ((512 << 10) if world <= 4 else (256 << 10))
 
 
 
