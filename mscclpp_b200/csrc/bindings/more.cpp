@@ -45,7 +45,13 @@ void registerMoreBindings(py::module_& m) {
           py::arg("rank"), py::arg("sendbuff"), py::arg("recvbuff"), py::arg("send_bytes"), py::arg("recv_bytes"),
           py::arg("dtype"), py::arg("plan"), py::arg("stream") = 0, py::arg("packet_type") = PacketType::LL16)
       .def("reset", &Executor::reset)
-      .def("zero_copy_launches", &Executor::zeroCopyLaunches);
+      .def("zero_copy_launches", &Executor::zeroCopyLaunches)
+      .def("check_canaries", &Executor::checkCanaries)
+      .def("canary_regions", [](const Executor& self) {
+        std::vector<std::tuple<std::string, uint64_t, size_t>> out;
+        for (const auto& r : self.canaryRegions()) out.emplace_back(r.label, r.address, r.bytes);
+        return out;
+      });
 
   m.def(
       "tp_fused",

@@ -6,7 +6,9 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
+#include <exception>
 #include <map>
 #include <mutex>
 #include <unordered_map>
@@ -438,6 +440,78 @@ struct Executor::Impl {
   std::map<std::pair<uintptr_t, size_t>, MappedBuffer> mapped;
   uint64_t zeroCopyLaunches = 0;
 
+  // ---- guard bands around the executor's own heap buffers (MSCCLPP_EXECUTOR_CANARY=1). The reference has no such
+  // check; its plans are trusted. Here a plan's operands are range-checked when they are resolved, and the bands catch
+  // what the checks cannot see: a kernel (this rank's or a peer's) that writes past the extent it was given.
+  static constexpr size_t kGuardBytes = 256;
+  static constexpr int kGuardByte = 0xA5;
+  bool canaries = false;
+  struct Guarded {
+    std::string label;
+    size_t bytes;
+  };
+  std::map<void*, Guarded> guarded;  // payload pointer -> what it is
+
+  int localRanks() const { return heap->emulated() ? heap->world() : 1; }
+  void* onRank(void* p, int r) const { return heap->emulated() ? heap->emulatedPtr(p, r) : p; }
+
+  void* allocGuarded(size_t bytes, const std::string& label) {
+    if (!canaries) return heap->alloc(bytes, 256);
+    char* raw = static_cast<char*>(heap->alloc(bytes + 2 * kGuardBytes, 256));
+    for (int r = 0; r < localRanks(); r++) {
+      MSCCLPP_CUDATHROW(cudaMemset(onRank(raw, r), kGuardByte, kGuardBytes));
+      MSCCLPP_CUDATHROW(cudaMemset(onRank(raw + kGuardBytes + bytes, r), kGuardByte, kGuardBytes));
+    }
+    MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
+    guarded[raw + kGuardBytes] = Guarded{label, bytes};
+    return raw + kGuardBytes;
+  }
+
+  void freeGuarded(void* p) {
+    if (!canaries) {
+      heap->free(p);
+      return;
+    }
+    guarded.erase(p);
+    heap->free(static_cast<char*>(p) - kGuardBytes);
+  }
+
+  std::vector<Executor::CanaryRegion> canaryRegions() const {
+    std::vector<Executor::CanaryRegion> out;
+    for (const auto& kv : guarded) {
+      char* payload = static_cast<char*>(kv.first);
+      for (int r = 0; r < localRanks(); r++) {
+        const std::string who = heap->emulated() ? "/rank " + std::to_string(r) : std::string();
+        out.push_back({kv.second.label + "/front" + who, reinterpret_cast<uint64_t>(onRank(payload - kGuardBytes, r)), kGuardBytes});
+        out.push_back({kv.second.label + "/back" + who, reinterpret_cast<uint64_t>(onRank(payload + kv.second.bytes, r)), kGuardBytes});
+      }
+    }
+    return out;
+  }
+
+  size_t checkCanaries() const {
+    if (!canaries) return 0;
+    MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
+    const auto regions = canaryRegions();
+    std::vector<unsigned char> host(kGuardBytes);
+    for (const auto& reg : regions) {
+      MSCCLPP_CUDATHROW(cudaMemcpy(host.data(), reinterpret_cast<const void*>(reg.address), reg.bytes, cudaMemcpyDeviceToHost));
+      size_t first = reg.bytes, count = 0;
+      for (size_t i = 0; i < reg.bytes; i++) {
+        if (host[i] != kGuardByte) {
+          if (first == reg.bytes) first = i;
+          count++;
+        }
+      }
+      if (count != 0)
+        throw Error("executor guard band " + reg.label + ": " + std::to_string(count) + " of " + std::to_string(reg.bytes) +
+                        " bytes were overwritten, the first at byte " + std::to_string(first) +
+                        " of the band (a kernel wrote outside the buffer it was given)",
+                    ErrorCode::ExecutorError);
+    }
+    return regions.size();
+  }
+
   // The first execute() that names a buffer (address, size) exchanges its registration with every rank; later calls find
   // it in the cache. Like the reference's executor (its contexts are keyed by the buffers' addresses,
   // src/core/executor/executor.cc), this assumes that the ranks see new buffers on the same calls - true of programs that
@@ -625,9 +699,9 @@ struct Executor::Impl {
     }
     freeDevPlans(c);
     if (c.state) heap->free(c.state);
-    if (c.scratch) heap->free(c.scratch);
-    if (c.stageIn) heap->free(c.stageIn);
-    if (c.stageOut) heap->free(c.stageOut);
+    if (c.scratch) freeGuarded(c.scratch);
+    if (c.stageIn) freeGuarded(c.stageIn);
+    if (c.stageOut) freeGuarded(c.stageOut);
     c = Context();
   }
 };
@@ -638,10 +712,15 @@ namespace {
 void startTracing(SymmetricHeap& heap) {
   if (!env()->npkitDumpDir.empty() && !NpKit::Enabled()) NpKit::Init(heap.rank());
 }
+bool canariesWanted() {
+  const char* e = std::getenv("MSCCLPP_EXECUTOR_CANARY");
+  return e != nullptr && e[0] != '\0' && e[0] != '0';
+}
 }  // namespace
 
 Executor::Executor(std::shared_ptr<SymmetricHeap> heap) : impl_(std::make_unique<Impl>()) {
   impl_->heap = std::move(heap);
+  impl_->canaries = canariesWanted();
   startTracing(*impl_->heap);
 }
 
@@ -649,6 +728,7 @@ Executor::Executor(std::shared_ptr<Communicator> comm, std::shared_ptr<char>) : 
   impl_->comm = comm;
   SymmetricHeap::Options opt;
   impl_->heap = SymmetricHeap::create(comm->bootstrap(), opt);
+  impl_->canaries = canariesWanted();
   startTracing(*impl_->heap);
 }
 
@@ -666,12 +746,21 @@ Executor::~Executor() {
 
 std::shared_ptr<SymmetricHeap> Executor::heap() const { return impl_->heap; }
 uint64_t Executor::zeroCopyLaunches() const { return impl_->zeroCopyLaunches; }
+std::vector<Executor::CanaryRegion> Executor::canaryRegions() const { return impl_->canaryRegions(); }
+size_t Executor::checkCanaries() { return impl_->checkCanaries(); }
 
 void Executor::reset() {
   (void)cudaDeviceSynchronize();
+  std::exception_ptr overwritten;  // the buffers are returned either way; the finding is reported afterwards
+  try {
+    impl_->checkCanaries();
+  } catch (...) {
+    overwritten = std::current_exception();
+  }
   for (auto& kv : impl_->contexts) impl_->freeContext(kv.second);
   impl_->contexts.clear();
   impl_->mapped.clear();  // imported mappings are released with their RegisteredMemory objects
+  if (overwritten) std::rethrow_exception(overwritten);
 }
 
 void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuffSize, size_t recvBuffSize, DataType dataType,
@@ -720,9 +809,9 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
   if (total > ctx.scratchBytesTotal) {
     if (ctx.scratch) {
       MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
-      heap.free(ctx.scratch);
+      impl_->freeGuarded(ctx.scratch);
     }
-    ctx.scratch = total ? heap.alloc(total, 256) : nullptr;
+    ctx.scratch = total ? impl_->allocGuarded(total, p.name + "/scratch") : nullptr;
     if (ctx.scratch) {
       for (int r = 0; r < (heap.emulated() ? heap.world() : 1); r++)
         MSCCLPP_CUDATHROW(cudaMemset(heap.emulated() ? heap.emulatedPtr(ctx.scratch, r) : ctx.scratch, 0, total));
@@ -782,21 +871,21 @@ void Executor::execute(int rank, void* sendbuff, void* recvbuff, size_t sendBuff
       if (sameBuffer) outMap = inMap;
     }
   }
-  auto stage = [&](void* user, size_t bytes, bool isSym, void*& slot, size_t& slotBytes) -> void* {
+  auto stage = [&](void* user, size_t bytes, bool isSym, void*& slot, size_t& slotBytes, const char* what) -> void* {
     if (user == nullptr || bytes == 0 || isSym) return user;
     if (slotBytes < bytes) {
       if (slot) {
         MSCCLPP_CUDATHROW(cudaDeviceSynchronize());
-        heap.free(slot);
+        impl_->freeGuarded(slot);
       }
-      slot = heap.alloc(bytes, 256);
+      slot = impl_->allocGuarded(bytes, p.name + what);
       slotBytes = bytes;
       rebuild = true;
     }
     return slot;
   };
-  void* in = inMap ? sendbuff : stage(sendbuff, sendBuffSize, inSym, ctx.stageIn, ctx.stageInBytes);
-  void* out = sameBuffer ? in : (outMap ? recvbuff : stage(recvbuff, recvBuffSize, outSym, ctx.stageOut, ctx.stageOutBytes));
+  void* in = inMap ? sendbuff : stage(sendbuff, sendBuffSize, inSym, ctx.stageIn, ctx.stageInBytes, "/staged input");
+  void* out = sameBuffer ? in : (outMap ? recvbuff : stage(recvbuff, recvBuffSize, outSym, ctx.stageOut, ctx.stageOutBytes, "/staged output"));
   if (in != sendbuff) MSCCLPP_CUDATHROW(cudaMemcpyAsync(in, sendbuff, sendBuffSize, cudaMemcpyDeviceToDevice, stream));
   const uint64_t base = reinterpret_cast<uint64_t>(heap.localBase());
   layout.inOff = in ? reinterpret_cast<uint64_t>(in) - base : 0;

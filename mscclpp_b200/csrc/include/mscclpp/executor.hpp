@@ -10,6 +10,7 @@
 
 #include <memory>
 #include <string>
+#include <vector>
 
 #include "core.hpp"
 #include "gpu_data_types.hpp"
@@ -60,6 +61,19 @@ class Executor {
   std::shared_ptr<SymmetricHeap> heap() const;
   // How many execute() calls so far ran directly on buffers outside the heap (mapped on every rank) instead of staging them.
   uint64_t zeroCopyLaunches() const;
+
+  // Debugging aid, switched on with MSCCLPP_EXECUTOR_CANARY=1 when the executor is created: every buffer the executor
+  // allocates for a plan (scratch, staging) gets a guard band of 256 bytes of 0xA5 on both sides. checkCanaries()
+  // waits for the device, reads all bands back and throws an Error that names plan, buffer, side and the first
+  // overwritten byte; it returns the number of bands it looked at (0 when the switch is off). Every rank's bands also
+  // catch what a PEER wrote past the end of this rank's scratch. reset() runs the check before it frees the buffers.
+  struct CanaryRegion {
+    std::string label;  // "<plan>/<buffer>/<front|back>[/rank r]"
+    uint64_t address;   // device address of the band
+    size_t bytes;
+  };
+  std::vector<CanaryRegion> canaryRegions() const;
+  size_t checkCanaries();
 
  private:
   struct Impl;

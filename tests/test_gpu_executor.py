@@ -186,3 +186,47 @@ def test_tracer_records_executor_operations(tmp_path):
     assert {"EXECUTOR_OP_SIGNAL", "EXECUTOR_OP_WAIT"} & {e["name"] for e in slices} or any("EXECUTOR_OP" in e["name"] for e in slices)
     executor.reset()
     symm.destroy()
+
+
+def test_guard_bands_around_executor_buffers(monkeypatch):
+    """With MSCCLPP_EXECUTOR_CANARY=1 the executor's scratch sits between two bands of 0xA5 on every rank. A correct plan
+    leaves them alone (a packet plan writes its scratch from every peer, up to the last byte); a byte written just past
+    the scratch is found by check_canaries() and again reported by reset(), which still returns the buffers."""
+    from mscclpp_b200 import SymmetricMemory, native
+    from mscclpp_b200._core.symm import tensor_from_pointer
+    from mscclpp_b200.default_algos import single_node
+
+    monkeypatch.setenv("MSCCLPP_EXECUTOR_CANARY", "1")
+    n = native()
+    world = 4
+    symm = SymmetricMemory.emulated(world, nbytes=64 << 20, timeout_ms=3000)
+    elems = 4 * world * 256
+    t = symm.tensor((elems,), torch.float32)
+    for r in range(world):
+        symm.rank_view(t, r).fill_(r + 1.0)
+    executor = n.Executor(symm.heap)
+    assert executor.check_canaries() == 0  # nothing allocated yet
+    plan = n.ExecutionPlan.from_string(single_node.build("allreduce_allpairs_packet", world).to_json(), 0)
+    for _ in range(3):
+        executor.execute(0, t.data_ptr(), t.data_ptr(), elems * 4, elems * 4, n.DataType.float32, plan,
+                         torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    symm.check()
+    regions = executor.canary_regions()
+    assert len(regions) == 2 * world and all(nbytes == 256 for _, _, nbytes in regions)
+    assert executor.check_canaries() == len(regions)
+
+    label, address, nbytes = next(r for r in regions if "/scratch/back" in r[0] and r[0].endswith("rank 2"))
+    band = tensor_from_pointer(address, (nbytes,), torch.uint8, t.device)
+    assert bool((band == 0xA5).all().item())
+    band[3] = 0
+    torch.cuda.synchronize()
+    with pytest.raises(Exception, match="guard band .*scratch/back/rank 2.*first at byte 3"):
+        executor.check_canaries()
+    free_before = symm.heap.bytes_free() if hasattr(symm.heap, "bytes_free") else None
+    with pytest.raises(Exception, match="guard band"):
+        executor.reset()
+    if free_before is not None:
+        assert symm.heap.bytes_free() > free_before  # the buffers went back to the heap all the same
+    assert executor.canary_regions() == []
+    symm.destroy()
