@@ -2,19 +2,26 @@
 // src/core/context.cc:16-105, src/core/connection.cc:85-715).
 //   CudaIpc   peer-mapped memory, copy engine via cudaMemcpyAsync on a private non-blocking stream
 //   Ethernet  TCP: data staged through host memory; a receive thread applies writes at the destination
-//   IBx       declared for API compatibility; this build has no verbs support and refuses to connect
+//   IBx       RDMA writes over a reliable-connection queue pair of a run-time loaded verbs library; tokens by RDMA
+//             fetch-and-add, or (mode HostNoAtomic) as the immediate value of an empty write that the receiver's CPU
+//             thread forwards into the semaphore's token
 #include <mscclpp/core.hpp>
 
 #include <atomic>
 #include <condition_variable>
 #include <cstring>
 #include <deque>
+#include <thread>
+
+#include <arpa/inet.h>
 
 #include <mscclpp/env.hpp>
 #include <mscclpp/gpu_utils.hpp>
 #include <mscclpp/npkit/npkit.hpp>
+#include <mscclpp/utils.hpp>
 
 #include "context.hpp"
+#include "gdr.hpp"
 #include "logger.hpp"
 #include "registered_memory.hpp"
 #include "serialize.hpp"
@@ -47,6 +54,8 @@ std::vector<char> Endpoint::Impl::serialize() const {
   w.put<uint64_t>(hostHash);
   w.put<uint64_t>(pidHash);
   w.putRaw(&ethAddress, sizeof(ethAddress));
+  w.putRaw(&ibQpInfo, sizeof(ibQpInfo));
+  w.put<uint8_t>(ibNoAtomic ? 1 : 0);
   return w.bytes;
 }
 
@@ -61,6 +70,8 @@ std::shared_ptr<Endpoint::Impl> Endpoint::Impl::deserialize(const std::vector<ch
   impl->hostHash = r.get<uint64_t>();
   impl->pidHash = r.get<uint64_t>();
   r.getRaw(&impl->ethAddress, sizeof(impl->ethAddress));
+  r.getRaw(&impl->ibQpInfo, sizeof(impl->ibQpInfo));
+  impl->ibNoAtomic = r.get<uint8_t>() != 0;
   return impl;
 }
 
@@ -246,6 +257,213 @@ class EthernetConnection : public BaseConnection {
   std::string recvError_;
 };
 
+// ------------------------------------------------------------------------------------------ InfiniBand
+bool isIb(Transport t) { return AllIBTransports.has(t); }
+
+class IBConnection : public BaseConnection {
+ public:
+  IBConnection(std::shared_ptr<Context> ctx, const Endpoint& local, const Endpoint& remote)
+      : BaseConnection(ctx, local, remote),
+        transport_(local.transport()),
+        remoteTransport_(remote.transport()),
+        qp_(local.pimpl_->ibQp),
+        noAtomic_(local.pimpl_->ibNoAtomic),
+        maxSendWr_(local.config().ib.maxSendWr) {
+    if (!qp_) throw Error("the local endpoint of an InfiniBand connection must have been created by this context", ErrorCode::InvalidUsage);
+    if (noAtomic_ != remote.pimpl_->ibNoAtomic) {
+      throw Error("both endpoints of an InfiniBand connection must use the same mode (RDMA atomics, or immediate data)",
+                  ErrorCode::InvalidUsage);
+    }
+    qp_->rtr(remote.pimpl_->ibQpInfo);
+    qp_->rts();
+    // where the old value of a fetch-and-add lands; nobody reads it
+    landingMr_ = ctx->impl()->ibContext(transport_).registerMr(&landing_, sizeof(landing_));
+    if (noAtomic_) {
+      // every token of the peer consumes one receive; the receive thread re-posts them
+      const int n = std::max(local.config().ib.maxRecvWr, 1);
+      for (int i = 0; i < n; i++) qp_->stageRecv(0);
+      qp_->postRecv();
+    }
+    LOG_INFO(LogSubsys::CONN, "InfiniBand connection via ", ctx->impl()->ibContext(transport_).deviceName(),
+             noAtomic_ ? " (tokens as immediate data)" : " (tokens by RDMA atomics)");
+  }
+
+  ~IBConnection() override {
+    stop_.store(true);
+    if (recvThread_.joinable()) recvThread_.join();
+    if (sinkStream_ != nullptr) (void)cudaStreamDestroy(sinkStream_);
+    if (sinkStaging_ != nullptr) (void)cudaFreeHost(sinkStaging_);
+  }
+
+  Transport transport() const override { return transport_; }
+  Transport remoteTransport() const override { return remoteTransport_; }
+
+  void write(RegisteredMemory dst, uint64_t dstOffset, RegisteredMemory src, uint64_t srcOffset, uint64_t size) override {
+    validateTransport(dst, remoteTransport_, dstOffset, size);
+    validateTransport(src, transport_, srcOffset, size);
+    const auto& local = src.pimpl_->ibEntry(transport_);
+    if (!local.mr) throw Error("the source of an InfiniBand write must be memory registered by this process", ErrorCode::InvalidUsage);
+    const IbMrInfo remote = dst.pimpl_->ibEntry(remoteTransport_).info;
+    constexpr uint64_t kMaxMessage = 1ull << 30;  // the verbs limit is 2 GiB per work request
+    for (uint64_t done = 0; done < size;) {
+      const uint32_t piece = static_cast<uint32_t>(std::min<uint64_t>(size - done, kMaxMessage));
+      makeRoom();
+      qp_->stageWrite(*local.mr, remote, piece, nextWrId_++, srcOffset + done, dstOffset + done, true);
+      qp_->postSend();
+      done += piece;
+    }
+  }
+
+  void updateAndSync(RegisteredMemory dst, uint64_t dstOffset, uint64_t* src, uint64_t newValue) override {
+    validateTransport(dst, remoteTransport_, dstOffset, sizeof(uint64_t));
+    const IbMrInfo remote = dst.pimpl_->ibEntry(remoteTransport_).info;
+    const uint64_t oldValue = *src;
+    *src = newValue;
+    makeRoom();
+    if (noAtomic_) {
+      // an empty write with the token's low half as immediate data: it completes at the peer after every earlier write of
+      // this queue pair, and the peer's receive thread rebuilds the 64-bit value from the increasing sequence
+      qp_->stageWriteWithImm(nullptr, remote, 0, nextWrId_++, 0, dstOffset, true, htonl(static_cast<uint32_t>(newValue)));
+    } else {
+      qp_->stageAtomicAdd(*landingMr_, remote, nextWrId_++, dstOffset, newValue - oldValue, true);
+    }
+    qp_->postSend();
+  }
+
+  void flush(int64_t timeoutUsec) override {
+    const auto t0 = std::chrono::steady_clock::now();
+    while (qp_->outstandingSignaled() > 0) {
+      pollOnce();
+      if (timeoutUsec >= 0 && qp_->outstandingSignaled() > 0 &&
+          std::chrono::duration_cast<std::chrono::microseconds>(std::chrono::steady_clock::now() - t0).count() > timeoutUsec) {
+        throw Error("InfiniBand flush timed out with " + std::to_string(qp_->outstandingSignaled()) + " work requests outstanding",
+                    ErrorCode::Timeout);
+      }
+    }
+    checkReceiver();
+  }
+
+  void startSignalForwarding(void* token, bool isHostMemory, int deviceId) override {
+    if (!noAtomic_) return;
+    std::lock_guard<std::mutex> lock(sinkMutex_);
+    if (sinkAddr_ != nullptr) {
+      if (sinkAddr_ == token) return;
+      throw Error("an InfiniBand connection that carries tokens as immediate data serves one semaphore", ErrorCode::InvalidUsage);
+    }
+    sinkAddr_ = token;
+    sinkIsHost_ = isHostMemory;
+    sinkDevice_ = deviceId;
+    if (!isHostMemory) {
+      gdrMap_ = std::make_unique<GdrMap>(token, deviceId);
+      if (!gdrMap_->valid()) {
+        LOG_WARN(LogSubsys::CONN, "tokens of this InfiniBand connection reach GPU memory through cudaMemcpy: ", gdrStatusMessage());
+        gdrMap_.reset();
+      }
+    }
+    recvThread_ = std::thread([this] { recvLoop(); });
+  }
+
+ private:
+  // keeps the number of unpolled signalled work requests below the send queue's depth
+  void makeRoom() {
+    while (qp_->outstandingSignaled() >= maxSendWr_ - 1) pollOnce();
+  }
+
+  void pollOnce() {
+    const int n = qp_->pollSendCq();
+    if (n < 0) throw IbError("polling the send completion queue failed", errno);
+    for (int i = 0; i < n; i++) {
+      const ibv_wc& wc = qp_->sendWc(i);
+      if (wc.status != IBV_WC_SUCCESS) {
+        throw Error("InfiniBand work request " + std::to_string(wc.wr_id) + " failed: " + qp_->wcStatusString(wc.status),
+                    ErrorCode::RemoteError);
+      }
+    }
+  }
+
+  void checkReceiver() {
+    if (recvFailed_.load(std::memory_order_acquire)) {
+      std::lock_guard<std::mutex> lock(sinkMutex_);
+      throw Error("the receive thread of this InfiniBand connection stopped: " + recvError_, ErrorCode::RemoteError);
+    }
+  }
+
+  void failReceiver(const std::string& why) {
+    {
+      std::lock_guard<std::mutex> lock(sinkMutex_);
+      recvError_ = why;
+    }
+    recvFailed_.store(true, std::memory_order_release);
+    LOG_WARN(LogSubsys::CONN, "InfiniBand receive thread: ", why);
+  }
+
+  void deliver(uint64_t value) {
+    if (sinkIsHost_) {
+      reinterpret_cast<std::atomic<uint64_t>*>(sinkAddr_)->store(value, std::memory_order_release);
+    } else if (gdrMap_) {
+      gdrMap_->store(value);
+    } else {
+      if (sinkStream_ == nullptr) {
+        MSCCLPP_CUDATHROW(cudaStreamCreateWithFlags(&sinkStream_, cudaStreamNonBlocking));
+        MSCCLPP_CUDATHROW(cudaHostAlloc(reinterpret_cast<void**>(&sinkStaging_), sizeof(uint64_t), cudaHostAllocDefault));
+      }
+      *sinkStaging_ = value;
+      MSCCLPP_CUDATHROW(cudaMemcpyAsync(sinkAddr_, sinkStaging_, sizeof(uint64_t), cudaMemcpyHostToDevice, sinkStream_));
+      MSCCLPP_CUDATHROW(cudaStreamSynchronize(sinkStream_));
+    }
+  }
+
+  void recvLoop() {
+    try {
+      if (!sinkIsHost_ && sinkDevice_ >= 0) MSCCLPP_CUDATHROW(cudaSetDevice(sinkDevice_));
+      uint32_t lastLow = 0;
+      uint64_t high = 0;
+      while (!stop_.load(std::memory_order_relaxed)) {
+        const int n = qp_->pollRecvCq();
+        if (n < 0) return failReceiver("polling the receive completion queue failed");
+        if (n == 0) {
+          std::this_thread::yield();
+          continue;
+        }
+        for (int i = 0; i < n; i++) {
+          const ibv_wc& wc = qp_->recvWc(i);
+          if (wc.status != IBV_WC_SUCCESS) return failReceiver("a receive failed: " + qp_->wcStatusString(wc.status));
+          // tokens only grow: a low half below the previous one means the high half moved on
+          const uint32_t low = ntohl(wc.imm_data);
+          if (low < lastLow) high += 1ull << 32;
+          lastLow = low;
+          deliver(high | low);
+          qp_->stageRecv(0);
+        }
+        qp_->postRecv();
+      }
+    } catch (const std::exception& e) {
+      failReceiver(e.what());
+    }
+  }
+
+  Transport transport_;
+  Transport remoteTransport_;
+  std::shared_ptr<IbQp> qp_;
+  bool noAtomic_;
+  int maxSendWr_;
+  uint64_t landing_ = 0;
+  std::shared_ptr<const IbMr> landingMr_;
+  uint64_t nextWrId_ = 1;
+  // token forwarding (immediate-data mode)
+  std::mutex sinkMutex_;
+  void* sinkAddr_ = nullptr;
+  bool sinkIsHost_ = true;
+  int sinkDevice_ = -1;
+  std::unique_ptr<GdrMap> gdrMap_;
+  cudaStream_t sinkStream_ = nullptr;
+  uint64_t* sinkStaging_ = nullptr;
+  std::thread recvThread_;
+  std::atomic<bool> stop_{false};
+  std::atomic<bool> recvFailed_{false};
+  std::string recvError_;
+};
+
 }  // namespace
 
 // ------------------------------------------------------------------------------------------ Context
@@ -280,6 +498,20 @@ std::shared_ptr<IpcStream> Context::Impl::ipcStream() {
   return s;
 }
 
+IbCtx& Context::Impl::ibContext(Transport ibTransport) {
+  std::lock_guard<std::mutex> lock(mutex);
+  auto& slot = ibContexts[ibTransport];
+  if (!slot) slot = std::make_shared<IbCtx>(getIBDeviceName(ibTransport));
+  return *slot;
+}
+
+const RegisteredMemory::Impl::IbEntry& RegisteredMemory::Impl::ibEntry(Transport t) const {
+  for (const auto& e : ib) {
+    if (e.transport == t) return e;
+  }
+  throw Error("RegisteredMemory carries no InfiniBand registration for " + transportToString(t), ErrorCode::InvalidUsage);
+}
+
 Context::Context() : pimpl_(std::make_unique<Impl>()) {}
 Context::~Context() = default;
 
@@ -292,8 +524,14 @@ RegisteredMemory Context::registerMemory(void* ptr, size_t size, TransportFlags 
   impl->pidHash = getPidHash();
   impl->transports = transports;
   impl->isLocal = true;
-  if ((transports & AllIBTransports).any()) {
-    throw Error("this build has no InfiniBand support: register with CudaIpc and/or Ethernet", ErrorCode::InvalidUsage);
+  for (int t = static_cast<int>(Transport::IB0); t <= static_cast<int>(Transport::IB7); t++) {
+    const Transport ibT = static_cast<Transport>(t);
+    if (!transports.has(ibT)) continue;
+    RegisteredMemory::Impl::IbEntry e;
+    e.transport = ibT;
+    e.mr = pimpl_->ibContext(ibT).registerMr(ptr, size);
+    e.info = e.mr->info();
+    impl->ib.push_back(std::move(e));
   }
   if (transports.has(Transport::CudaIpc)) {
     impl->ipc = GpuIpcMemHandle::create(ptr, size);
@@ -333,18 +571,30 @@ Endpoint Context::createEndpoint(EndpointConfig config) {
     a.setPort(0);
     impl->ethListener = std::make_shared<Socket>();
     impl->ethAddress = impl->ethListener->listen(a);
-  } else if (config.transport != Transport::CudaIpc) {
-    if (config.transport == Transport::Unknown || config.transport == Transport::NumTransports) {
-      throw Error("endpoint needs a transport", ErrorCode::InvalidUsage);
+  } else if (isIb(config.transport)) {
+    IbCtx& ib = pimpl_->ibContext(config.transport);
+    EndpointConfig::Ib::Mode mode = config.ib.mode;
+    if (mode == EndpointConfig::Ib::Mode::Default) {
+      mode = env()->ibvMode == "host-no-atomic" ? EndpointConfig::Ib::Mode::HostNoAtomic : EndpointConfig::Ib::Mode::Host;
     }
-    throw Error("transport " + transportToString(config.transport) + " is not available: this build has no InfiniBand support",
-                ErrorCode::InvalidUsage);
+    if (mode == EndpointConfig::Ib::Mode::Host && !ib.supportsRdmaAtomics()) {
+      LOG_WARN(LogSubsys::CONN, ib.deviceName(), " has no RDMA atomics: tokens travel as immediate data");
+      mode = EndpointConfig::Ib::Mode::HostNoAtomic;
+    }
+    impl->ibNoAtomic = mode == EndpointConfig::Ib::Mode::HostNoAtomic;
+    const IbQp::Limits limits{config.ib.maxCqSize, config.ib.maxCqPollNum, config.ib.maxSendWr, config.ib.maxRecvWr,
+                              config.ib.maxWrPerSend};
+    impl->ibQp = ib.createQp(config.ib.port, config.ib.gidIndex, limits);
+    impl->ibQpInfo = impl->ibQp->info();
+  } else if (config.transport != Transport::CudaIpc) {
+    throw Error("endpoint needs a transport", ErrorCode::InvalidUsage);
   }
   return Endpoint(impl);
 }
 
 Connection Context::connect(const Endpoint& localEndpoint, const Endpoint& remoteEndpoint) {
-  if (localEndpoint.transport() != remoteEndpoint.transport()) {
+  const bool bothIb = isIb(localEndpoint.transport()) && isIb(remoteEndpoint.transport());  // IB0 may face the peer's IB3
+  if (localEndpoint.transport() != remoteEndpoint.transport() && !bothIb) {
     throw Error("endpoints of one connection must use the same transport", ErrorCode::InvalidUsage);
   }
   std::shared_ptr<BaseConnection> conn;
@@ -356,8 +606,8 @@ Connection Context::connect(const Endpoint& localEndpoint, const Endpoint& remot
       conn = std::make_shared<EthernetConnection>(shared_from_this(), localEndpoint, remoteEndpoint);
       break;
     default:
-      throw Error("transport " + transportToString(localEndpoint.transport()) + " is not available in this build",
-                  ErrorCode::InvalidUsage);
+      if (!bothIb) throw Error("transport " + transportToString(localEndpoint.transport()) + " cannot connect", ErrorCode::InvalidUsage);
+      conn = std::make_shared<IBConnection>(shared_from_this(), localEndpoint, remoteEndpoint);
   }
   return Connection(conn);
 }

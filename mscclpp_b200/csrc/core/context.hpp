@@ -10,6 +10,8 @@
 
 #include <mscclpp/core.hpp>
 
+#include "ib.hpp"
+
 namespace mscclpp {
 
 class IpcStream {
@@ -48,8 +50,10 @@ struct Context::Impl {
   std::mutex mutex;
   std::vector<std::shared_ptr<IpcStream>> streams;
   std::map<int, std::shared_ptr<TokenPool>> tokenPools;  // one pool per GPU of this process
+  std::map<Transport, std::shared_ptr<IbCtx>> ibContexts;  // opened on first use, one per IB device
   std::shared_ptr<IpcStream> ipcStream();
   std::shared_ptr<TokenPool> tokens();  // the pool of the current device
+  IbCtx& ibContext(Transport ibTransport);
 };
 
 }  // namespace mscclpp

@@ -43,6 +43,8 @@ struct CudaDriver {
   CUresult (*cuFuncSetAttribute)(CUfunction, CUfunction_attribute, int);
   CUresult (*cuLaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**);
   CUresult (*cuLaunchCooperativeKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**);
+  // optional (null on drivers without it): DMA-BUF export of a device address range, for InfiniBand registration
+  CUresult (*cuMemGetHandleForAddressRange)(void*, CUdeviceptr, size_t, CUmemRangeHandleType, unsigned long long);
 };
 
 }  // namespace mscclpp

@@ -60,6 +60,7 @@ CudaDriver* loadDriver() {
   MSCCLPP_RESOLVE(cuLaunchKernel);
   MSCCLPP_RESOLVE(cuLaunchCooperativeKernel);
 #undef MSCCLPP_RESOLVE
+  if (!resolve(table.cuMemGetHandleForAddressRange, "cuMemGetHandleForAddressRange")) table.cuMemGetHandleForAddressRange = nullptr;
   return ok ? &table : nullptr;
 }
 

@@ -141,6 +141,12 @@ std::vector<char> RegisteredMemory::Impl::serialize() const {
   w.put<uint8_t>(isHostMemory ? 1 : 0);
   w.put<int32_t>(deviceId);
   w.putRaw(&ipc, sizeof(ipc));
+  w.put<uint32_t>(static_cast<uint32_t>(ib.size()));
+  for (const auto& e : ib) {
+    w.put<int32_t>(static_cast<int32_t>(e.transport));
+    w.put<uint64_t>(e.info.addr);
+    w.put<uint32_t>(e.info.rkey);
+  }
   return w.bytes;
 }
 
@@ -155,6 +161,14 @@ std::shared_ptr<RegisteredMemory::Impl> RegisteredMemory::Impl::deserialize(cons
   impl->isHostMemory = r.get<uint8_t>() != 0;
   impl->deviceId = r.get<int32_t>();
   r.getRaw(&impl->ipc, sizeof(impl->ipc));
+  const uint32_t nIb = r.get<uint32_t>();
+  for (uint32_t i = 0; i < nIb; i++) {
+    IbEntry e;
+    e.transport = static_cast<Transport>(r.get<int32_t>());
+    e.info.addr = r.get<uint64_t>();
+    e.info.rkey = r.get<uint32_t>();
+    impl->ib.push_back(std::move(e));
+  }
   impl->isLocal = false;
   const bool sameProcess = impl->hostHash == getHostHash() && impl->pidHash == getPidHash();
   if (sameProcess) {

@@ -10,6 +10,7 @@
 
 #include <mscclpp/core.hpp>
 
+#include "ib.hpp"
 #include "socket.hpp"
 
 namespace mscclpp {
@@ -62,6 +63,15 @@ struct RegisteredMemory::Impl {
   GpuIpcMemHandle ipc;
   std::shared_ptr<GpuIpcMapping> mapping;   // imported memory only
   uint32_t registeredFdId = 0;              // local VMM memory only (fd parked in the fd server)
+  // InfiniBand: one memory region per IB transport the memory was registered for. The owner holds the region, everybody
+  // else the address and remote key that came with the serialised form.
+  struct IbEntry {
+    Transport transport = Transport::Unknown;
+    std::shared_ptr<const IbMr> mr;
+    IbMrInfo info;
+  };
+  std::vector<IbEntry> ib;
+  const IbEntry& ibEntry(Transport t) const;
 
   ~Impl();
   std::vector<char> serialize() const;
@@ -74,6 +84,9 @@ struct Endpoint::Impl {
   uint64_t pidHash = 0;
   SocketAddress ethAddress;                  // Ethernet: where this endpoint accepts its peer
   std::shared_ptr<Socket> ethListener;       // local side only
+  std::shared_ptr<IbQp> ibQp;                // InfiniBand, local side only
+  IbQpInfo ibQpInfo;                         // InfiniBand: what the peer needs to reach the queue pair
+  bool ibNoAtomic = false;                   // tokens travel as immediate data instead of RDMA atomics
   std::vector<char> serialize() const;
   static std::shared_ptr<Impl> deserialize(const std::vector<char>& data);
 };
@@ -88,6 +101,9 @@ class BaseConnection {
   virtual void flush(int64_t timeoutUsec) = 0;
   virtual Transport transport() const = 0;
   virtual Transport remoteTransport() const = 0;
+  // Transports whose tokens arrive at the CPU (InfiniBand without RDMA atomics) forward them to the semaphore's inbound
+  // token: the semaphore names the token when it is built. One semaphore per such connection.
+  virtual void startSignalForwarding(void* /*token*/, bool /*isHostMemory*/, int /*deviceId*/) {}
   std::shared_ptr<Context> context() const { return context_; }
   const Device& localDevice() const { return local_.device(); }
   int maxWriteQueueSize() const { return local_.maxWriteQueueSize(); }

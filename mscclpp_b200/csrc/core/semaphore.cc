@@ -92,6 +92,10 @@ Semaphore::Semaphore(const SemaphoreStub& localStub, const SemaphoreStub& remote
   // peer access does not cover; other memory goes through cudaDeviceEnablePeerAccess.
   const auto& l = *localStub.pimpl_;
   const auto& r = *remoteStub.pimpl_;
+  // transports that deliver tokens to the CPU learn here where this semaphore's inbound token lives
+  if (l.connection.valid() && l.token) {
+    l.connection.impl_->startSignalForwarding(l.token.get(), l.device.type != DeviceType::GPU, l.device.id);
+  }
   if (r.token && l.device.type == DeviceType::GPU && r.device.type == DeviceType::GPU && l.device.id != r.device.id && l.device.id >= 0) {
     CudaDeviceGuard guard(l.device.id);
     if (!detail::gpuGrantAccessPhysical(r.token.get(), l.device.id)) {

@@ -13,6 +13,8 @@
 
 #include <cuda_runtime.h>
 
+#include "ib.hpp"
+
 namespace mscclpp {
 
 std::string getHostName(int maxlen, const char delim) {
@@ -38,6 +40,9 @@ std::vector<std::string> ibDeviceNames() {
     }
     return names;
   }
+  // what the loaded verbs library lists (a software provider has no sysfs entries), else what the kernel lists
+  names = ibDeviceNamesFromLibrary();
+  if (!names.empty()) return names;
   if (DIR* d = ::opendir("/sys/class/infiniband")) {
     while (dirent* e = ::readdir(d)) {
       const std::string n = e->d_name;

@@ -18,7 +18,7 @@ def test_cmake_configures_and_declares_targets(tmp_path):
     assert "arch 100a" in r.stdout
     r = subprocess.run(["cmake", "--build", str(build), "--target", "help"], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stderr[-2000:]
-    for target in ("mscclpp_b200", "mscclpp_b200_nccl", "mscclpp_b200_audit_nccl", "_native", "core_tests", "host_tests",
+    for target in ("mscclpp_b200", "mscclpp_b200_nccl", "mscclpp_b200_audit_nccl", "_native", "core_tests", "host_tests", "ib_tests", "fake_ibverbs",
                    "tutorial_01_basic_concepts", "customized_allgather", "peer_access_test"):
         assert target in r.stdout, target
     # the optional-dependency modules answer without the libraries being present
