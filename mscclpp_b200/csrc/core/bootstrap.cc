@@ -7,6 +7,10 @@
 // publishes the full address table once, so any pair can open a socket lazily without a third party.
 #include <mscclpp/core.hpp>
 
+#include <cstdlib>
+#include <functional>
+#include <sstream>
+
 #include <atomic>
 #include <cstring>
 #include <map>
@@ -156,6 +160,7 @@ class TcpBootstrap::Impl {
   Socket peerListen;
   std::vector<RankInfo> table;
   int nRanksPerNode = 1;
+  int nRanksPerIpcDomain = 0;  // 0 = not determined yet
 
   std::mutex mutex;
   std::map<std::pair<int, int>, Socket> sendSocks;
@@ -378,7 +383,42 @@ void TcpBootstrap::abort() { pimpl_->abortFlag.store(1, std::memory_order_releas
 int TcpBootstrap::getRank() const { return pimpl_->rank; }
 int TcpBootstrap::getNranks() const { return pimpl_->nRanks; }
 int TcpBootstrap::getNranksPerNode() const { return pimpl_->nRanksPerNode; }
-int TcpBootstrap::getNranksPerIpcDomain() const { return pimpl_->nRanksPerNode; }
+// Ranks that can map one another's GPU memory: the ranks of this host, or of this NVLink fabric clique when there is
+// one (reference: src/core/bootstrap/bootstrap.cc:459-493). Collective on first use (an allGather of domain hashes);
+// domains must have equal sizes and hold consecutive ranks, which the channel and plan code relies on.
+int TcpBootstrap::getNranksPerIpcDomain() const {
+  Impl& impl = *pimpl_;
+  impl.checkInit();
+  if (impl.nRanksPerIpcDomain > 0) return impl.nRanksPerIpcDomain;
+  std::vector<uint64_t> hashes(impl.nRanks, 0);
+  hashes[impl.rank] = getIpcDomainHash();
+  // MSCCLPP_IPC_DOMAIN="a,a,b,b": one domain name per rank, for launchers that know the topology (and for tests)
+  if (const char* forced = std::getenv("MSCCLPP_IPC_DOMAIN")) {
+    std::vector<std::string> names;
+    std::stringstream ss(forced);
+    for (std::string item; std::getline(ss, item, ',');) names.push_back(item);
+    if (names.size() > 1) hashes[impl.rank] = std::hash<std::string>{}("domain:" + names[impl.rank % names.size()]);
+  }
+  const_cast<TcpBootstrap*>(this)->allGather(hashes.data(), sizeof(uint64_t));
+  int mine = 0;
+  for (uint64_t h : hashes) mine += h == hashes[impl.rank] ? 1 : 0;
+  const std::string rule = "IPC domains must have equal sizes and hold consecutive ranks: ";
+  if (impl.nRanks % mine != 0) {
+    throw Error(rule + std::to_string(impl.nRanks) + " ranks do not divide into domains of " + std::to_string(mine), ErrorCode::InvalidUsage);
+  }
+  for (int r = 0; r < impl.nRanks; r++) {
+    const int first = r - r % mine;
+    if (hashes[r] != hashes[first]) {
+      throw Error(rule + "rank " + std::to_string(r) + " is not in the domain of rank " + std::to_string(first), ErrorCode::InvalidUsage);
+    }
+    if (r % mine == 0 && r > 0 && hashes[r] == hashes[r - mine]) {
+      throw Error(rule + "the domain of rank " + std::to_string(r) + " is larger than that of rank " + std::to_string(impl.rank), ErrorCode::InvalidUsage);
+    }
+  }
+  LOG_INFO(LogSubsys::NET, "rank ", impl.rank, ": ", mine, " ranks per IPC domain");
+  impl.nRanksPerIpcDomain = mine;
+  return mine;
+}
 
 void TcpBootstrap::send(void* data, int size, int peer, int tag) { pimpl_->sendTo(data, size, peer, tag); }
 void TcpBootstrap::recv(void* data, int size, int peer, int tag) { pimpl_->recvFrom(data, size, peer, tag); }

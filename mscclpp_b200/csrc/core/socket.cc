@@ -4,7 +4,9 @@
 #include <arpa/inet.h>
 #include <cerrno>
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
+#include <dlfcn.h>
 #include <fstream>
 #include <ifaddrs.h>
 #include <net/if.h>
@@ -13,6 +15,9 @@
 #include <netinet/tcp.h>
 #include <poll.h>
 #include <unistd.h>
+
+#include <cuda_runtime.h>
+#include <nvml.h>
 
 #include <mscclpp/env.hpp>
 #include <mscclpp/errors.hpp>
@@ -370,6 +375,57 @@ uint64_t getHostHash() {
     if (boot && std::getline(boot, bootId)) id += bootId;
   }
   return fnv1a(id);
+}
+
+namespace {
+// NVML is loaded on demand (it is part of the driver, absent on machines without one). True when the current CUDA device
+// reports a completed, healthy fabric registration; then `hash` covers cluster id + clique.
+bool fabricDomainHash(uint64_t& hash) {
+  int dev = 0;
+  char busId[32] = {0};
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetPCIBusId(busId, sizeof(busId), dev) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return false;
+  }
+  void* lib = ::dlopen("libnvidia-ml.so.1", RTLD_NOW | RTLD_LOCAL);
+  if (lib == nullptr) return false;
+  using InitFn = nvmlReturn_t (*)();
+  using HandleFn = nvmlReturn_t (*)(const char*, nvmlDevice_t*);
+  using FabricFn = nvmlReturn_t (*)(nvmlDevice_t, nvmlGpuFabricInfoV_t*);
+  auto init = reinterpret_cast<InitFn>(::dlsym(lib, "nvmlInit_v2"));
+  auto shutdown = reinterpret_cast<InitFn>(::dlsym(lib, "nvmlShutdown"));
+  auto byBusId = reinterpret_cast<HandleFn>(::dlsym(lib, "nvmlDeviceGetHandleByPciBusId_v2"));
+  auto fabric = reinterpret_cast<FabricFn>(::dlsym(lib, "nvmlDeviceGetGpuFabricInfoV"));
+  bool ok = false;
+  if (init != nullptr && shutdown != nullptr && byBusId != nullptr && fabric != nullptr && init() == NVML_SUCCESS) {
+    nvmlDevice_t handle;
+    nvmlGpuFabricInfoV_t info{};
+    info.version = nvmlGpuFabricInfo_v2;
+    if (byBusId(busId, &handle) == NVML_SUCCESS && fabric(handle, &info) == NVML_SUCCESS &&
+        info.state == NVML_GPU_FABRIC_STATE_COMPLETED && info.status == NVML_SUCCESS) {
+      std::string id(reinterpret_cast<const char*>(info.clusterUuid), sizeof(info.clusterUuid));
+      bool allZero = true;
+      for (char c : id) allZero = allZero && c == 0;
+      if (!allZero) {
+        id += ":" + std::to_string(info.cliqueId);
+        hash = fnv1a(id);
+        ok = true;
+      }
+    }
+    (void)shutdown();
+  }
+  ::dlclose(lib);
+  return ok;
+}
+}  // namespace
+
+uint64_t getIpcDomainHash() {
+  if (const char* forced = std::getenv("MSCCLPP_IPC_DOMAIN")) {
+    if (forced[0] != '\0') return fnv1a(std::string("domain:") + forced);
+  }
+  uint64_t h = 0;
+  if (fabricDomainHash(h)) return h;
+  return getHostHash();
 }
 
 uint64_t getPidHash() {

@@ -77,6 +77,9 @@ class Socket {
 };
 
 uint64_t getHostHash();          // hash of MSCCLPP_HOSTID or hostname + boot id
+// Hash of the domain inside which GPU memory can be shared between processes: the NVLink fabric's cluster id and clique
+// (multi-node NVLink, from NVML) when the current GPU is part of one, else the host. MSCCLPP_IPC_DOMAIN overrides it.
+uint64_t getIpcDomainHash();
 uint64_t getPidHash();           // hash of pid + mount namespace
 
 }  // namespace mscclpp

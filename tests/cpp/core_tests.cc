@@ -64,6 +64,35 @@ TEST(Bootstrap, AllGatherBarrierSendRecv) {
   testing::reportPerf("bootstrap_4_ranks_setup_and_exchange", timer.elapsedUs(), "us");
 }
 
+TEST(Bootstrap, IpcDomains) {
+  const int n = 4;
+  std::vector<int> perDomain(n, 0), perNode(n, 0);
+  // one host, no NVLink fabric: the domain is the node
+  runRanks(n, [&](int r, std::shared_ptr<TcpBootstrap> b) {
+    perDomain[r] = b->getNranksPerIpcDomain();
+    perNode[r] = b->getNranksPerNode();
+  });
+  for (int r = 0; r < n; r++) EXPECT_EQ(perDomain[r], perNode[r]);
+  // two domains of two consecutive ranks
+  ::setenv("MSCCLPP_IPC_DOMAIN", "a,a,b,b", 1);
+  runRanks(n, [&](int r, std::shared_ptr<TcpBootstrap> b) { perDomain[r] = b->getNranksPerIpcDomain(); });
+  for (int r = 0; r < n; r++) EXPECT_EQ(perDomain[r], 2);
+  // interleaved domains and domains of different sizes are refused on every rank
+  for (const char* layout : {"a,b,a,b", "a,a,a,b"}) {
+    ::setenv("MSCCLPP_IPC_DOMAIN", layout, 1);
+    std::vector<int> refused(n, 0);
+    runRanks(n, [&](int r, std::shared_ptr<TcpBootstrap> b) {
+      try {
+        (void)b->getNranksPerIpcDomain();
+      } catch (const Error& e) {
+        refused[r] = e.getErrorCode() == ErrorCode::InvalidUsage;
+      }
+    });
+    for (int r = 0; r < n; r++) EXPECT_EQ(refused[r], 1);
+  }
+  ::unsetenv("MSCCLPP_IPC_DOMAIN");
+}
+
 TEST(Ethernet, WriteAndHostSemaphore) {
   std::vector<uint64_t> received(2, 0);
   runRanks(2, [&](int r, std::shared_ptr<TcpBootstrap> b) {
