@@ -127,7 +127,8 @@ PYBIND11_MODULE(_native, m) {
       .def("get_rank", &Bootstrap::getRank)
       .def("get_n_ranks", &Bootstrap::getNranks)
       .def("get_n_ranks_per_node", &Bootstrap::getNranksPerNode)
-      .def("get_n_ranks_per_ipc_domain", &Bootstrap::getNranksPerIpcDomain)
+      // collective on first use (the ranks exchange their domains): other Python threads must be able to run
+      .def("get_n_ranks_per_ipc_domain", &Bootstrap::getNranksPerIpcDomain, py::call_guard<py::gil_scoped_release>())
       .def(
           "send",
           [](Bootstrap& b, py::bytes data, int peer, int tag) {
