@@ -270,6 +270,55 @@ TEST(IbSemaphore, RoceNeedsGlobalRouting) {
   ::unsetenv("FAKE_IBV_ROCE");
 }
 
+TEST(IbCommunicator, TwoRanksOverTheBootstrap) {
+  // the whole path a program takes: bootstrap, Communicator::connect with an InfiniBand endpoint per rank (IB0 faces IB1),
+  // memory exchange, semaphore construction, write + signal in both directions
+  UniqueId id = TcpBootstrap::createUniqueId();
+  std::vector<uint64_t> seen(2, 0);
+  std::vector<std::string> errors(2);
+  std::vector<std::thread> ranks;
+  for (int r = 0; r < 2; r++) {
+    ranks.emplace_back([&, r] {
+      try {
+        auto bootstrap = std::make_shared<TcpBootstrap>(r, 2);
+        bootstrap->initialize(id, 30);
+        Communicator comm(bootstrap);
+        const int peer = 1 - r;
+        const Transport mine = r == 0 ? Transport::IB0 : Transport::IB1;
+        std::vector<uint64_t> buf(256, r == 0 ? 0xabcd0000ull : 0);
+        Connection conn = comm.connect(EndpointConfig(mine, Device(DeviceType::CPU)), peer).get();
+        RegisteredMemory local = comm.registerMemory(buf.data(), buf.size() * 8, mine);
+        comm.sendMemory(local, peer);
+        RegisteredMemory remote = comm.recvMemory(peer).get();
+        Host2HostSemaphore sem(comm, conn);
+        if (r == 0) {
+          for (size_t i = 0; i < buf.size(); i++) buf[i] += i;
+          conn.write(remote, 0, local, 0, buf.size() * 8);
+          sem.signal();
+          conn.flush(5000000);
+          sem.wait(200000000);  // the peer's answer
+          seen[0] = buf[0];
+        } else {
+          sem.wait(200000000);
+          seen[1] = buf[255];
+          buf[0] = 0x600d;
+          conn.write(remote, 0, local, 0, 8);
+          sem.signal();
+          conn.flush(5000000);
+        }
+        bootstrap->barrier();
+      } catch (const std::exception& e) {
+        errors[r] = e.what();
+      }
+    });
+  }
+  for (auto& t : ranks) t.join();
+  EXPECT_EQ(errors[0], std::string());
+  EXPECT_EQ(errors[1], std::string());
+  EXPECT_EQ(seen[1], uint64_t(0xabcd0000ull + 255));
+  EXPECT_EQ(seen[0], uint64_t(0x600d));
+}
+
 TEST(Gdr, MapsThePageAroundAnAddress) {
   ASSERT_TRUE(gdrEnabled());
   EXPECT_EQ(gdrStatusMessage(), std::string("GDRCopy is available"));

@@ -56,7 +56,7 @@ def test_cpp_infiniband_transport_against_software_provider(tmp_path):
         env = dict(os.environ, MSCCLPP_IBV_SO=ibv, MSCCLPP_GDRCOPY_SO=gdr)
         r = subprocess.run([exe], capture_output=True, text=True, timeout=300, env=env)
         assert r.returncode == 0, (r.stdout[-3000:], r.stderr[-3000:])
-        assert "12 tests, 0 failures" in r.stdout
+        assert "13 tests, 0 failures" in r.stdout
 
 
 def test_infiniband_is_reported_absent_without_a_verbs_library(tmp_path):
