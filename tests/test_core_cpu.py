@@ -164,11 +164,17 @@ def test_host_semaphore_wait_runs_out(native):
     assert all(_run_ranks(2, body))
 
 
-def test_ib_transport_is_refused_cleanly(native):
+def test_ib_transport_is_refused_cleanly_without_a_device(native):
+    """No verbs library or no HCA: the endpoint is refused with an error that says so (the transport itself is covered
+    against a software provider in test_cpp_unit.py)."""
     ctx = native.Context.create()
-    with pytest.raises(native.Error) as ei:
+    try:
         ctx.create_endpoint(native.EndpointConfig(native.Transport.IB0))
-    assert ei.value.error_code == native.ErrorCode.InvalidUsage
+    except native.Error as e:
+        assert e.error_code in (native.ErrorCode.InvalidUsage, native.ErrorCode.SystemError)
+        assert "InfiniBand" in str(e)
+    else:
+        pytest.skip("this machine has an InfiniBand device")
 
 
 def test_fifo_protocol_with_lap_wrap(native):
