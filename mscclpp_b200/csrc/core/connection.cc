@@ -92,7 +92,8 @@ class CudaIpcConnection : public BaseConnection {
  public:
   CudaIpcConnection(std::shared_ptr<Context> ctx, const Endpoint& local, const Endpoint& remote)
       : BaseConnection(ctx, local, remote) {
-    if (local.hostHash() != remote.hostHash()) {
+    // one host, or (with fabric handles switched on) the hosts of one multi-node NVLink domain
+    if (local.hostHash() != remote.hostHash() && !detail::fabricHandlesWanted()) {
       throw Error("CudaIpc connections need both endpoints on one host", ErrorCode::InvalidUsage);
     }
     stream_ = ctx->impl()->ipcStream();

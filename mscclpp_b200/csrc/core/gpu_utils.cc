@@ -1,4 +1,7 @@
 #include <mscclpp/gpu_utils.hpp>
+#include <mscclpp/utils.hpp>
+
+#include <cstdlib>
 
 #include <cstring>
 #include <map>
@@ -151,18 +154,29 @@ cudaStream_t setupStream() {
   return s;
 }
 
-CUmemAllocationProp physicalProp(int deviceId) {
+CUmemAllocationProp physicalProp(int deviceId, bool withFabric = false) {
   CUmemAllocationProp prop{};
   prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
   prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
   prop.location.id = deviceId;
   prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  if (withFabric) {
+    prop.requestedHandleTypes = static_cast<CUmemAllocationHandleType>(CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR | CU_MEM_HANDLE_TYPE_FABRIC);
+  }
   return prop;
 }
 
 }  // namespace
 
 namespace detail {
+
+bool fabricHandlesWanted() {
+  static const bool wanted = [] {
+    const char* e = std::getenv("MSCCLPP_FABRIC_HANDLES");
+    return e != nullptr && e[0] == '1' && isFabricMemHandleAvailable();
+  }();
+  return wanted;
+}
 
 void* gpuCalloc(size_t bytes) {
   AvoidCudaGraphCaptureGuard guard;
@@ -229,7 +243,14 @@ void* gpuCallocPhysical(size_t bytes, size_t granularity) {
   const size_t rounded = (bytes + granularity - 1) / granularity * granularity;
   CUmemAllocationProp prop = physicalProp(dev);
   CUmemGenericAllocationHandle handle;
-  MSCCLPP_CUTHROW(drv.cuMemCreate(&handle, rounded, &prop, 0));
+  // Multi-node NVLink: memory that other nodes of the fabric may import has to be created exportable as a fabric handle
+  // (it needs the IMEX service; without it the creation fails and the allocation stays node-local).
+  bool created = false;
+  if (fabricHandlesWanted()) {
+    CUmemAllocationProp fabricProp = physicalProp(dev, true);
+    created = drv.cuMemCreate(&handle, rounded, &fabricProp, 0) == CUDA_SUCCESS;
+  }
+  if (!created) MSCCLPP_CUTHROW(drv.cuMemCreate(&handle, rounded, &prop, 0));
   CUdeviceptr va = 0;
   MSCCLPP_CUTHROW(drv.cuMemAddressReserve(&va, rounded, granularity, 0, 0));
   MSCCLPP_CUTHROW(drv.cuMemMap(va, rounded, 0, handle, 0));

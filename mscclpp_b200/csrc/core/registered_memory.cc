@@ -38,6 +38,11 @@ GpuIpcMemHandle GpuIpcMemHandle::create(void* ptr, size_t size) {
   h.offset = reinterpret_cast<uint64_t>(ptr) - base;
   CUmemGenericAllocationHandle vmm;
   if (drv.cuMemRetainAllocationHandle(&vmm, reinterpret_cast<void*>(base)) == CUDA_SUCCESS) {
+    if (detail::fabricHandlesWanted()) {
+      static_assert(sizeof(CUmemFabricHandle) == sizeof(h.fabric), "fabric handle size");
+      // succeeds only for allocations that were created exportable as fabric handles (gpuCallocPhysical does that)
+      if (drv.cuMemExportToShareableHandle(h.fabric, vmm, CU_MEM_HANDLE_TYPE_FABRIC, 0) == CUDA_SUCCESS) h.kinds |= kFabric;
+    }
     int fd = -1;
     CUresult r = drv.cuMemExportToShareableHandle(&fd, vmm, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
     (void)drv.cuMemRelease(vmm);
@@ -62,14 +67,21 @@ GpuIpcMemHandle GpuIpcMemHandle::create(void* ptr, size_t size) {
 
 GpuIpcMapping::GpuIpcMapping(const GpuIpcMemHandle& h) {
   AvoidCudaGraphCaptureGuard guard;
-  if (h.kinds & GpuIpcMemHandle::kPosixFd) {
+  if (h.kinds & (GpuIpcMemHandle::kPosixFd | GpuIpcMemHandle::kFabric)) {
     const CudaDriver& drv = CudaDriver::get();
-    int fd = requestFdFromPeer(h.fdServer, h.fdId);
     CUmemGenericAllocationHandle handle;
-    CUresult r = drv.cuMemImportFromShareableHandle(&handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
-                                                    CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
-    ::close(fd);
-    MSCCLPP_CUTHROW(r);
+    bool imported = false;
+    if (h.kinds & GpuIpcMemHandle::kFabric) {  // works across the hosts of one NVLink fabric, and inside a host as well
+      imported = drv.cuMemImportFromShareableHandle(&handle, const_cast<unsigned char*>(h.fabric), CU_MEM_HANDLE_TYPE_FABRIC) == CUDA_SUCCESS;
+    }
+    if (!imported) {
+      if ((h.kinds & GpuIpcMemHandle::kPosixFd) == 0) throw Error("the fabric handle of this memory could not be imported", ErrorCode::SystemError);
+      int fd = requestFdFromPeer(h.fdServer, h.fdId);
+      CUresult r = drv.cuMemImportFromShareableHandle(&handle, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)),
+                                                      CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR);
+      ::close(fd);
+      MSCCLPP_CUTHROW(r);
+    }
     int dev = 0;
     MSCCLPP_CUDATHROW(cudaGetDevice(&dev));
     size_t gran = detail::physicalGranularity(false);
@@ -97,7 +109,7 @@ std::shared_ptr<GpuIpcMapping> GpuIpcMapping::acquire(const GpuIpcMemHandle& h) 
   static std::mutex mutex;
   static std::map<std::string, std::weak_ptr<GpuIpcMapping>> cache;
   std::string key;
-  if (h.kinds & GpuIpcMemHandle::kPosixFd) {
+  if (h.kinds & (GpuIpcMemHandle::kPosixFd | GpuIpcMemHandle::kFabric)) {
     key = std::string("fd:") + h.fdServer + ":" + std::to_string(h.baseAddr) + ":" + std::to_string(h.allocSize);
   } else {
     key = "ipc:" + std::string(reinterpret_cast<const char*>(&h.runtimeIpc), sizeof(h.runtimeIpc));
@@ -188,7 +200,9 @@ std::shared_ptr<RegisteredMemory::Impl> RegisteredMemory::Impl::deserialize(cons
         }
       }
     }
-  } else if (impl->transports.has(Transport::CudaIpc) && impl->hostHash == getHostHash() && !impl->isHostMemory) {
+  } else if (impl->transports.has(Transport::CudaIpc) && !impl->isHostMemory &&
+             (impl->hostHash == getHostHash() || (impl->ipc.kinds & GpuIpcMemHandle::kFabric) != 0)) {
+    // this host, or another host of the same NVLink fabric (the handle then carries a fabric export)
     impl->mapping = GpuIpcMapping::acquire(impl->ipc);
     impl->data = static_cast<char*>(impl->mapping->base()) + impl->ipc.offset;
   } else {

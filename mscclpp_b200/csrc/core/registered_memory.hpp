@@ -16,15 +16,17 @@
 namespace mscclpp {
 
 // Everything needed to reach one GPU (or host) allocation from another process of the same host.
-// Import order: same process -> raw pointer; VMM allocation -> POSIX fd through the fd server;
-// cudaMalloc allocation -> legacy CUDA IPC handle. (Fabric handles for multi-node NVLink are not
-// produced: this library targets one NVSwitch box.)
+// Import order: same process -> raw pointer; VMM allocation on another host of the same NVLink fabric -> fabric
+// handle; VMM allocation on this host -> POSIX fd through the fd server; cudaMalloc allocation -> legacy CUDA IPC
+// handle. Fabric handles are produced only with MSCCLPP_FABRIC_HANDLES=1 (they need the IMEX service of a multi-node
+// NVLink system); the reference tries Fabric -> PosixFd -> RuntimeIpc in the same spirit (src/core/gpu_ipc_mem.cc:386-432).
 struct GpuIpcMemHandle {
-  enum Kind : uint32_t { kNone = 0, kRuntimeIpc = 1, kPosixFd = 2, kHost = 4 };
+  enum Kind : uint32_t { kNone = 0, kRuntimeIpc = 1, kPosixFd = 2, kHost = 4, kFabric = 8 };
   uint32_t kinds = kNone;
   cudaIpcMemHandle_t runtimeIpc{};
   char fdServer[96] = {0};
   uint32_t fdId = 0;
+  unsigned char fabric[64] = {0};  // CUmemFabricHandle
   uint64_t baseAddr = 0;   // base of the allocation in the owner
   uint64_t allocSize = 0;  // size of the whole allocation
   uint64_t offset = 0;     // offset of the registered range inside the allocation

@@ -69,6 +69,8 @@ void gpuFreePhysical(void* ptr);
 // to it (VMM allocations are not covered by cudaDeviceEnablePeerAccess). Returns false for other memory.
 bool gpuGrantAccessPhysical(const void* ptr, int dev);
 size_t physicalGranularity(bool forMulticast);
+// MSCCLPP_FABRIC_HANDLES=1 on a GPU that can export fabric handles (multi-node NVLink); off by default.
+bool fabricHandlesWanted();
 // Allocation granularity that is also valid for binding to a multicast object: the larger of the device's allocation
 // granularity and the multicast granularity, both taken as the driver's minimum or recommended value.
 size_t multicastGranularity(bool recommended);

@@ -42,6 +42,15 @@ struct Pair {
 
 RegisteredMemory asSeenByPeer(const RegisteredMemory& m) { return RegisteredMemory::deserialize(m.serialize()); }
 
+// Waits by the clock, not by a spin count: on a loaded machine with few cores the peer thread may not run for a while.
+void waitFor(Host2HostSemaphore& sem, double seconds = 30.0) {
+  testing::Timer t;
+  while (!sem.poll()) {
+    if (t.elapsedUs() > seconds * 1e6) throw Error("the peer's signal did not arrive", ErrorCode::Timeout);
+    std::this_thread::yield();
+  }
+}
+
 }  // namespace
 
 TEST(IbvTable, LoadsTheProviderAndListsItsDevices) {
@@ -237,7 +246,7 @@ static void pingPong(Mode mode, int rounds) {
   std::atomic<int> bad{0};
   std::thread peer([&] {
     for (int r = 1; r <= rounds; r++) {
-      b.wait(200000000);
+      waitFor(b);
       // the token is ordered after the write that preceded it
       for (uint64_t v : landed) bad += (v != uint64_t(r));
       b.signal();
@@ -248,7 +257,7 @@ static void pingPong(Mode mode, int rounds) {
     for (auto& v : payload) v = r;
     p.ab.write(remoteLanded, 0, memPayload, 0, payload.size() * 8);
     a.signal();
-    a.wait(200000000);
+    waitFor(a);
   }
   p.ab.flush(5000000);
   peer.join();
@@ -296,10 +305,10 @@ TEST(IbCommunicator, TwoRanksOverTheBootstrap) {
           conn.write(remote, 0, local, 0, buf.size() * 8);
           sem.signal();
           conn.flush(5000000);
-          sem.wait(200000000);  // the peer's answer
+          waitFor(sem);  // the peer's answer
           seen[0] = buf[0];
         } else {
-          sem.wait(200000000);
+          waitFor(sem);
           seen[1] = buf[255];
           buf[0] = 0x600d;
           conn.write(remote, 0, local, 0, 8);
