@@ -302,6 +302,7 @@ class IBConnection : public BaseConnection {
   void write(RegisteredMemory dst, uint64_t dstOffset, RegisteredMemory src, uint64_t srcOffset, uint64_t size) override {
     validateTransport(dst, remoteTransport_, dstOffset, size);
     validateTransport(src, transport_, srcOffset, size);
+    checkBroken();
     const auto& local = src.pimpl_->ibEntry(transport_);
     if (!local.mr) throw Error("the source of an InfiniBand write must be memory registered by this process", ErrorCode::InvalidUsage);
     const IbMrInfo remote = dst.pimpl_->ibEntry(remoteTransport_).info;
@@ -317,6 +318,7 @@ class IBConnection : public BaseConnection {
 
   void updateAndSync(RegisteredMemory dst, uint64_t dstOffset, uint64_t* src, uint64_t newValue) override {
     validateTransport(dst, remoteTransport_, dstOffset, sizeof(uint64_t));
+    checkBroken();
     const IbMrInfo remote = dst.pimpl_->ibEntry(remoteTransport_).info;
     const uint64_t oldValue = *src;
     *src = newValue;
@@ -332,6 +334,7 @@ class IBConnection : public BaseConnection {
   }
 
   void flush(int64_t timeoutUsec) override {
+    checkBroken();
     const auto t0 = std::chrono::steady_clock::now();
     while (qp_->outstandingSignaled() > 0) {
       pollOnce();
@@ -371,15 +374,22 @@ class IBConnection : public BaseConnection {
   }
 
   void pollOnce() {
+    checkBroken();
     const int n = qp_->pollSendCq();
     if (n < 0) throw IbError("polling the send completion queue failed", errno);
     for (int i = 0; i < n; i++) {
       const ibv_wc& wc = qp_->sendWc(i);
       if (wc.status != IBV_WC_SUCCESS) {
-        throw Error("InfiniBand work request " + std::to_string(wc.wr_id) + " failed: " + qp_->wcStatusString(wc.status),
-                    ErrorCode::RemoteError);
+        // The queue pair is in its error state now: whatever else was posted is flushed by the device and nothing
+        // further can be sent. Remember it, so that later calls fail at once instead of waiting for completions.
+        broken_ = "work request " + std::to_string(wc.wr_id) + " failed: " + qp_->wcStatusString(wc.status);
+        checkBroken();
       }
     }
+  }
+
+  void checkBroken() const {
+    if (!broken_.empty()) throw Error("InfiniBand connection is broken: " + broken_, ErrorCode::RemoteError);
   }
 
   void checkReceiver() {
@@ -451,6 +461,7 @@ class IBConnection : public BaseConnection {
   uint64_t landing_ = 0;
   std::shared_ptr<const IbMr> landingMr_;
   uint64_t nextWrId_ = 1;
+  std::string broken_;  // why the queue pair stopped working (empty: it works)
   // token forwarding (immediate-data mode)
   std::mutex sinkMutex_;
   void* sinkAddr_ = nullptr;

@@ -381,7 +381,7 @@ void IbQp::postRecv() {
 
 int IbQp::pollSendCq() {
   const int n = api_->pollCq(sendCq_, static_cast<int>(sendWcs_.size()), sendWcs_.data());
-  if (n > 0) outstandingSignaled_ -= n;
+  if (n > 0) outstandingSignaled_ = std::max(0, outstandingSignaled_ - n);  // error completions also come for unsignalled requests
   return n;
 }
 

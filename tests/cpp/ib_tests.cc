@@ -186,6 +186,9 @@ TEST(IbConnection, RemoteFaultSurfacesInFlush) {
   }
   EXPECT_TRUE(remoteError);
   EXPECT_EQ(int((*dst)[0]), 0);
+  // the queue pair is gone for good: later calls say so at once instead of waiting for completions that cannot come
+  EXPECT_THROW(p.ab.write(remoteDst, 0, memSrc, 0, 64), Error);
+  EXPECT_THROW(p.ab.flush(), Error);
 }
 
 TEST(IbConnection, FlushGivesUpAfterItsTimeLimit) {
