@@ -97,11 +97,6 @@ bool IbvApi::available() {
   }
 }
 
-void IbvApi::unload() {
-  std::lock_guard<std::mutex> lock(g_apiMutex);
-  g_api.reset();  // the library stays mapped while objects made from it are alive (they hold the table)
-}
-
 int IbvApi::postSend(ibv_qp* qp, ibv_send_wr* wr, ibv_send_wr** bad) const {
   return postSendSym_ != nullptr ? postSendSym_(qp, wr, bad) : qp->context->ops.post_send(qp, wr, bad);
 }
@@ -215,8 +210,17 @@ IbQp::IbQp(std::shared_ptr<const IbvApi> api, ibv_context* ctx, ibv_pd* pd, int 
     throw IbError("ibv_create_qp failed", e);
   }
 
+  // from here on a failure has to give back what exists already: the destructor does not run for a constructor that throws
+  auto fail = [this](const std::string& what, int err) {
+    (void)api_->destroyQp(qp_);
+    (void)api_->destroyCq(recvCq_);
+    (void)api_->destroyCq(sendCq_);
+    qp_ = nullptr;
+    sendCq_ = recvCq_ = nullptr;
+    throw IbError(what, err);
+  };
   ibv_port_attr pa{};
-  if (api_->queryPort(ctx, static_cast<uint8_t>(port), &pa) != 0) throw IbError("ibv_query_port failed", errno);
+  if (api_->queryPort(ctx, static_cast<uint8_t>(port), &pa) != 0) fail("ibv_query_port failed", errno);
   info_.lid = pa.lid;
   info_.port = static_cast<uint8_t>(port);
   info_.linkLayer = pa.link_layer;
@@ -225,7 +229,7 @@ IbQp::IbQp(std::shared_ptr<const IbvApi> api, ibv_context* ctx, ibv_pd* pd, int 
   info_.useGrh = (pa.link_layer == IBV_LINK_LAYER_ETHERNET || gidIndex >= 0) ? 1 : 0;
   if (info_.useGrh) {
     ibv_gid gid{};
-    if (api_->queryGid(ctx, static_cast<uint8_t>(port), std::max(gidIndex, 0), &gid) != 0) throw IbError("ibv_query_gid failed", errno);
+    if (api_->queryGid(ctx, static_cast<uint8_t>(port), std::max(gidIndex, 0), &gid) != 0) fail("ibv_query_gid failed", errno);
     info_.subnetPrefix = gid.global.subnet_prefix;
     info_.interfaceId = gid.global.interface_id;
   }
@@ -236,7 +240,7 @@ IbQp::IbQp(std::shared_ptr<const IbvApi> api, ibv_context* ctx, ibv_pd* pd, int 
   attr.port_num = static_cast<uint8_t>(port);
   attr.qp_access_flags = kMrAccess;
   if (api_->modifyQp(qp_, &attr, IBV_QP_STATE | IBV_QP_PKEY_INDEX | IBV_QP_PORT | IBV_QP_ACCESS_FLAGS) != 0) {
-    throw IbError("ibv_modify_qp to INIT failed", errno);
+    fail("ibv_modify_qp to INIT failed", errno);
   }
 
   sendWrs_.resize(limits.maxWrPerSend);

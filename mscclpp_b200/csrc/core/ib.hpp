@@ -20,8 +20,6 @@ struct IbvApi {
   static std::shared_ptr<const IbvApi> get();
   // True when get() would succeed.
   static bool available();
-  // Forget the cached table (tests that switch MSCCLPP_IBV_SO between providers).
-  static void unload();
 
   ibv_device** (*getDeviceList)(int*) = nullptr;
   void (*freeDeviceList)(ibv_device**) = nullptr;
