@@ -383,36 +383,67 @@ void TcpBootstrap::abort() { pimpl_->abortFlag.store(1, std::memory_order_releas
 int TcpBootstrap::getRank() const { return pimpl_->rank; }
 int TcpBootstrap::getNranks() const { return pimpl_->nRanks; }
 int TcpBootstrap::getNranksPerNode() const { return pimpl_->nRanksPerNode; }
-// Ranks that can map one another's GPU memory: the ranks of this host, or of this NVLink fabric clique when there is
-// one (reference: src/core/bootstrap/bootstrap.cc:459-493). Collective on first use (an allGather of domain hashes);
-// domains must have equal sizes and hold consecutive ranks, which the channel and plan code relies on.
+// Ranks that can map one another's GPU memory: the ranks of this host, widened to this NVLink fabric clique when the
+// GPUs are part of one (reference: src/core/bootstrap/bootstrap.cc:459-493). Collective on first use (an allGather of
+// host and fabric hashes). Domains must have equal sizes and hold consecutive ranks, which the channel and plan code
+// relies on: an explicit layout (MSCCLPP_IPC_DOMAIN="a,a,b,b", one name per rank) that breaks the rule is refused; a
+// detected fabric layout that breaks it is ignored with a warning and the hosts are the domains.
 int TcpBootstrap::getNranksPerIpcDomain() const {
   Impl& impl = *pimpl_;
   impl.checkInit();
   if (impl.nRanksPerIpcDomain > 0) return impl.nRanksPerIpcDomain;
-  std::vector<uint64_t> hashes(impl.nRanks, 0);
-  hashes[impl.rank] = getIpcDomainHash();
-  // MSCCLPP_IPC_DOMAIN="a,a,b,b": one domain name per rank, for launchers that know the topology (and for tests)
+  struct Entry {
+    uint64_t host, domain;
+    uint32_t forced;
+  };
+  std::vector<Entry> all(impl.nRanks, Entry{0, 0, 0});
+  Entry& me = all[impl.rank];
+  me.host = getHostHash();
+  me.domain = getIpcDomainHash();
   if (const char* forced = std::getenv("MSCCLPP_IPC_DOMAIN")) {
     std::vector<std::string> names;
     std::stringstream ss(forced);
     for (std::string item; std::getline(ss, item, ',');) names.push_back(item);
-    if (names.size() > 1) hashes[impl.rank] = std::hash<std::string>{}("domain:" + names[impl.rank % names.size()]);
+    if (!names.empty() && forced[0] != '\0') me.forced = 1;
+    if (names.size() > 1) me.domain = std::hash<std::string>{}("domain:" + names[impl.rank % names.size()]);
   }
-  const_cast<TcpBootstrap*>(this)->allGather(hashes.data(), sizeof(uint64_t));
-  int mine = 0;
-  for (uint64_t h : hashes) mine += h == hashes[impl.rank] ? 1 : 0;
-  const std::string rule = "IPC domains must have equal sizes and hold consecutive ranks: ";
-  if (impl.nRanks % mine != 0) {
-    throw Error(rule + std::to_string(impl.nRanks) + " ranks do not divide into domains of " + std::to_string(mine), ErrorCode::InvalidUsage);
-  }
-  for (int r = 0; r < impl.nRanks; r++) {
-    const int first = r - r % mine;
-    if (hashes[r] != hashes[first]) {
-      throw Error(rule + "rank " + std::to_string(r) + " is not in the domain of rank " + std::to_string(first), ErrorCode::InvalidUsage);
+  const_cast<TcpBootstrap*>(this)->allGather(all.data(), sizeof(Entry));
+  bool forced = false;
+  for (const Entry& e : all) forced = forced || e.forced != 0;
+
+  // size of this rank's domain under `key`, or a description of why the layout cannot be used
+  auto layout = [&](auto key, std::string& problem) {
+    int mine = 0;
+    for (const Entry& e : all) mine += key(e) == key(all[impl.rank]) ? 1 : 0;
+    if (impl.nRanks % mine != 0) {
+      problem = std::to_string(impl.nRanks) + " ranks do not divide into domains of " + std::to_string(mine);
+      return 0;
     }
-    if (r % mine == 0 && r > 0 && hashes[r] == hashes[r - mine]) {
-      throw Error(rule + "the domain of rank " + std::to_string(r) + " is larger than that of rank " + std::to_string(impl.rank), ErrorCode::InvalidUsage);
+    for (int r = 0; r < impl.nRanks; r++) {
+      const int first = r - r % mine;
+      if (key(all[r]) != key(all[first])) {
+        problem = "rank " + std::to_string(r) + " is not in the domain of rank " + std::to_string(first);
+        return 0;
+      }
+      if (r % mine == 0 && r > 0 && key(all[r]) == key(all[r - mine])) {
+        problem = "the domain of rank " + std::to_string(r) + " is larger than that of rank " + std::to_string(impl.rank);
+        return 0;
+      }
+    }
+    return mine;
+  };
+  const std::string rule = "IPC domains must have equal sizes and hold consecutive ranks: ";
+  std::string problem;
+  int mine = layout([](const Entry& e) { return e.domain; }, problem);
+  if (forced) {
+    if (mine == 0) throw Error(rule + problem, ErrorCode::InvalidUsage);
+  } else {
+    std::string hostProblem;
+    const int perHost = layout([](const Entry& e) { return e.host; }, hostProblem);
+    if (mine == 0 || (perHost > 0 && mine < perHost)) {
+      // a fabric layout that cannot be used, or one that would split a host: processes of one host can always share memory
+      if (mine == 0) LOG_WARN(LogSubsys::NET, "ignoring the detected NVLink fabric layout (", problem, "): hosts are the IPC domains");
+      mine = perHost > 0 ? perHost : impl.nRanksPerNode;
     }
   }
   LOG_INFO(LogSubsys::NET, "rank ", impl.rank, ": ", mine, " ranks per IPC domain");
