@@ -83,8 +83,13 @@ def main():
         again.initialize(f"127.0.0.1:{port_box[0]}", 2)
         report("failure/bootstrap_times_out", False)
     except N.Error as e:
-        report("failure/bootstrap_times_out", e.error_code == N.ErrorCode.Timeout and time.time() - t0 < 30,
-               seconds=round(time.time() - t0, 2))
+        # rank 0 runs into its time limit; another survivor may instead see rank 0 give up and close the connection first.
+        # Either way the call ends with an error within its bound instead of hanging.
+        bounded = time.time() - t0 < 30
+        ok = bounded and (e.error_code == N.ErrorCode.Timeout or rank != 0)
+        if not ok:
+            print(json.dumps({"rank": rank, "bootstrap_error": str(e), "code": str(e.error_code)}), flush=True)
+        report("failure/bootstrap_times_out", ok, seconds=round(time.time() - t0, 2))
     # (c) the survivors carry on among themselves
     smaller = N.TcpBootstrap.create(rank, world - 1)
     if rank == 0:
