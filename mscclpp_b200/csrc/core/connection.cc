@@ -358,10 +358,9 @@ class IBConnection : public BaseConnection {
     sinkIsHost_ = isHostMemory;
     sinkDevice_ = deviceId;
     if (!isHostMemory) {
-      gdrMap_ = std::make_unique<GdrMap>(token, deviceId);
-      if (!gdrMap_->valid()) {
-        LOG_WARN(LogSubsys::CONN, "tokens of this InfiniBand connection reach GPU memory through cudaMemcpy: ", gdrStatusMessage());
-        gdrMap_.reset();
+      gdrWindow_ = GdrWindow::open(token, deviceId);
+      if (!gdrWindow_) {
+        LOG_WARN(LogSubsys::CONN, "tokens of this InfiniBand connection reach GPU memory through cudaMemcpy: ", gdrAvailability().reason);
       }
     }
     recvThread_ = std::thread([this] { recvLoop(); });
@@ -411,8 +410,8 @@ class IBConnection : public BaseConnection {
   void deliver(uint64_t value) {
     if (sinkIsHost_) {
       reinterpret_cast<std::atomic<uint64_t>*>(sinkAddr_)->store(value, std::memory_order_release);
-    } else if (gdrMap_) {
-      gdrMap_->store(value);
+    } else if (gdrWindow_) {
+      gdrWindow_->store(value);
     } else {
       if (sinkStream_ == nullptr) {
         MSCCLPP_CUDATHROW(cudaStreamCreateWithFlags(&sinkStream_, cudaStreamNonBlocking));
@@ -467,7 +466,7 @@ class IBConnection : public BaseConnection {
   void* sinkAddr_ = nullptr;
   bool sinkIsHost_ = true;
   int sinkDevice_ = -1;
-  std::unique_ptr<GdrMap> gdrMap_;
+  std::unique_ptr<GdrWindow> gdrWindow_;
   cudaStream_t sinkStream_ = nullptr;
   uint64_t* sinkStaging_ = nullptr;
   std::thread recvThread_;

@@ -36,7 +36,8 @@ constexpr size_t kGpuPage = 64 * 1024;
 struct GdrApi {
   void* lib = nullptr;
   void* ctx = nullptr;  // gdr_t
-  GdrStatus status = GdrStatus::LibraryMissing;
+  enum class State { Open, SwitchedOff, NoLibrary, NoDriver, OpenFailed };
+  State state = State::NoLibrary;
   std::string detail;
   void* (*open)() = nullptr;
   int (*close)(void*) = nullptr;
@@ -48,7 +49,7 @@ struct GdrApi {
 
   GdrApi() {
     if (env()->forceDisableGdr) {
-      status = GdrStatus::Disabled;
+      state = State::SwitchedOff;
       return;
     }
     const char* forced = std::getenv("MSCCLPP_GDRCOPY_SO");
@@ -73,11 +74,11 @@ struct GdrApi {
     }
     // the stock library talks to /dev/gdrdrv; a library named explicitly may be a software stand-in without a driver
     if (forced == nullptr && ::access("/dev/gdrdrv", F_OK) != 0) {
-      status = GdrStatus::DriverMissing;
+      state = State::NoDriver;
       return;
     }
     ctx = open();
-    status = ctx != nullptr ? GdrStatus::Ok : GdrStatus::OpenFailed;
+    state = ctx != nullptr ? State::Open : State::OpenFailed;
   }
   ~GdrApi() {
     if (ctx != nullptr) (void)close(ctx);
@@ -91,64 +92,75 @@ GdrApi& gdr() {
 
 }  // namespace
 
-GdrStatus gdrStatus() { return gdr().status; }
-
-std::string gdrStatusMessage() {
-  switch (gdr().status) {
-    case GdrStatus::Ok:
-      return "GDRCopy is available";
-    case GdrStatus::Disabled:
-      return "GDRCopy is switched off by MSCCLPP_FORCE_DISABLE_GDR";
-    case GdrStatus::LibraryMissing:
-      return "libgdrapi could not be loaded (" + gdr().detail + ")";
-    case GdrStatus::DriverMissing:
-      return "the gdrdrv kernel module is not loaded (/dev/gdrdrv is absent)";
-    case GdrStatus::OpenFailed:
-      return "gdr_open() failed";
-  }
-  return "unknown";
+const GdrAvailability& gdrAvailability() {
+  static const GdrAvailability answer = [] {
+    GdrAvailability a;
+    const GdrApi& g = gdr();
+    a.usable = g.state == GdrApi::State::Open;
+    switch (g.state) {
+      case GdrApi::State::Open:
+        a.reason = "GDRCopy is available";
+        break;
+      case GdrApi::State::SwitchedOff:
+        a.reason = "GDRCopy is switched off by MSCCLPP_FORCE_DISABLE_GDR";
+        break;
+      case GdrApi::State::NoLibrary:
+        a.reason = "libgdrapi could not be loaded (" + g.detail + ")";
+        break;
+      case GdrApi::State::NoDriver:
+        a.reason = "the gdrdrv kernel module is not loaded (/dev/gdrdrv is absent)";
+        break;
+      case GdrApi::State::OpenFailed:
+        a.reason = "gdr_open() failed";
+        break;
+    }
+    return a;
+  }();
+  return answer;
 }
 
-GdrMap::GdrMap(void* deviceAddr, int deviceId) {
+std::unique_ptr<GdrWindow> GdrWindow::open(void* deviceAddr, int deviceId) {
   GdrApi& g = gdr();
-  if (g.status != GdrStatus::Ok || deviceAddr == nullptr) return;
+  if (g.state != GdrApi::State::Open || deviceAddr == nullptr) return nullptr;
   std::unique_ptr<CudaDeviceGuard> guard;
   if (deviceId >= 0) guard = std::make_unique<CudaDeviceGuard>(deviceId);
   const unsigned long addr = reinterpret_cast<unsigned long>(deviceAddr);
   const unsigned long page = addr & ~(kGpuPage - 1);
+  std::unique_ptr<GdrWindow> w(new GdrWindow());  // its destructor undoes whatever was done when a later step fails
   GdrMh mh{};
   if (g.pin(g.ctx, page, kGpuPage, 0, 0, &mh) != 0) {
     LOG_WARN(LogSubsys::CONN, "gdr_pin_buffer failed for the GPU page at ", reinterpret_cast<void*>(page));
-    return;
+    return nullptr;
   }
-  handle_ = mh.h;
-  pinned_ = true;
+  w->pinHandle_ = mh.h;
+  w->pinned_ = true;
   void* va = nullptr;
   if (g.map(g.ctx, mh, &va, kGpuPage) != 0 || va == nullptr) {
     LOG_WARN(LogSubsys::CONN, "gdr_map failed");
-    return;
+    return nullptr;
   }
-  mapBase_ = va;
-  mapBytes_ = kGpuPage;
+  w->mapBase_ = va;
+  w->mapBytes_ = kGpuPage;
   GdrInfo info{};
   uint64_t start = page;
   if (g.getInfo(g.ctx, mh, &info) == 0 && info.va != 0) start = info.va;  // the pinned range may begin below the page asked for
-  hostPtr_ = reinterpret_cast<uint64_t*>(static_cast<char*>(va) + (addr - start));
+  w->word_ = reinterpret_cast<uint64_t*>(static_cast<char*>(va) + (addr - start));
+  return w;
 }
 
-GdrMap::~GdrMap() {
+GdrWindow::~GdrWindow() {
   GdrApi& g = gdr();
-  GdrMh mh{handle_};
+  GdrMh mh{pinHandle_};
   if (mapBase_ != nullptr) (void)g.unmap(g.ctx, mh, mapBase_, mapBytes_);
   if (pinned_) (void)g.unpin(g.ctx, mh);
 }
 
-void GdrMap::store(uint64_t value) const {
+void GdrWindow::store(uint64_t value) const {
   // BAR1 is mapped write-combining: the fence pushes the store out instead of leaving it in a combining buffer
-  reinterpret_cast<std::atomic<uint64_t>*>(hostPtr_)->store(value, std::memory_order_release);
+  reinterpret_cast<std::atomic<uint64_t>*>(word_)->store(value, std::memory_order_release);
   std::atomic_thread_fence(std::memory_order_seq_cst);
 }
 
-uint64_t GdrMap::load() const { return reinterpret_cast<std::atomic<uint64_t>*>(hostPtr_)->load(std::memory_order_acquire); }
+uint64_t GdrWindow::load() const { return reinterpret_cast<std::atomic<uint64_t>*>(word_)->load(std::memory_order_acquire); }
 
 }  // namespace mscclpp

@@ -1,5 +1,5 @@
 // A stand-in for libgdrapi for tests without the gdrdrv kernel module: "pinning" accepts any address and the "BAR1
-// window" is the memory itself, so a test can hand GdrMap a host buffer and check the pointer arithmetic (the pinned range
+// window" is the memory itself, so a test can hand GdrWindow a host buffer and check the pointer arithmetic (the pinned range
 // starts at a 64 KB boundary below the address) and the ordered store.
 // Build: g++ -shared -fPIC fake_gdrapi.cc -o libfake_gdrapi.so
 #include <cstddef>

@@ -332,21 +332,20 @@ TEST(IbCommunicator, TwoRanksOverTheBootstrap) {
 }
 
 TEST(Gdr, MapsThePageAroundAnAddress) {
-  ASSERT_TRUE(gdrEnabled());
-  EXPECT_EQ(gdrStatusMessage(), std::string("GDRCopy is available"));
+  ASSERT_TRUE(gdrAvailability().usable);
+  EXPECT_EQ(gdrAvailability().reason, std::string("GDRCopy is available"));
   char* block = static_cast<char*>(std::aligned_alloc(65536, 3 * 65536));
   std::memset(block, 0, 3 * 65536);
   uint64_t* word = reinterpret_cast<uint64_t*>(block + 65536 + 4096 + 24);
   {
-    GdrMap map(word, -1);
-    ASSERT_TRUE(map.valid());
-    EXPECT_TRUE(map.hostPtr() == word);
-    map.store(0x1122334455667788ull);
+    auto window = GdrWindow::open(word, -1);
+    ASSERT_TRUE(window != nullptr);
+    EXPECT_TRUE(window->word() == word);
+    window->store(0x1122334455667788ull);
     EXPECT_EQ(*word, 0x1122334455667788ull);
-    EXPECT_EQ(map.load(), 0x1122334455667788ull);
+    EXPECT_EQ(window->load(), 0x1122334455667788ull);
   }
-  GdrMap none(nullptr, -1);
-  EXPECT_TRUE(!none.valid());
+  EXPECT_TRUE(GdrWindow::open(nullptr, -1) == nullptr);
   std::free(block);
 }
 
