@@ -2,6 +2,7 @@
 native algorithms are compiled against them at run time) and the perf-gate baselines."""
 import glob
 import os
+import shutil
 import subprocess
 import sys
 import zipfile
@@ -10,8 +11,13 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_wheel_builds_and_is_complete(tmp_path):
-    r = subprocess.run([sys.executable, "-m", "pip", "wheel", "--no-deps", "--no-build-isolation", "--no-index", "-w", str(tmp_path), ROOT],
-                       capture_output=True, text=True, timeout=1800)
+    leftovers = [os.path.join(ROOT, d) for d in ("build", "mscclpp_b200.egg-info") if not os.path.exists(os.path.join(ROOT, d))]
+    try:
+        r = subprocess.run([sys.executable, "-m", "pip", "wheel", "--no-deps", "--no-build-isolation", "--no-index", "-w", str(tmp_path), ROOT],
+                           capture_output=True, text=True, timeout=1800)
+    finally:
+        for d in leftovers:  # setuptools builds inside the source tree; leave it as it was
+            shutil.rmtree(d, ignore_errors=True)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     wheels = glob.glob(str(tmp_path / "mscclpp_b200-*.whl"))
     assert len(wheels) == 1
