@@ -28,6 +28,8 @@
 #include "core/range_allocator.hpp"
 #include "core/socket.hpp"
 #include "core/unix_socket.hpp"
+#include <mscclpp/ext/collectives/algorithm_collection_builder.hpp>
+
 #include "framework.hpp"
 
 using namespace mscclpp;
@@ -170,6 +172,72 @@ static std::shared_ptr<Algorithm> dummyAlgo(const std::string& name, const std::
         return CommResult::Success;
       },
       lo, hi);
+}
+
+TEST(DefaultSelector, SizesWorldsAndBufferPlacement) {
+  // the registered names with stand-in kernels; ranges as buildDefaultAlgorithms gives them on eight and on two ranks
+  using Map = std::unordered_map<std::string, std::unordered_map<std::string, std::shared_ptr<Algorithm>>>;
+  int calls = 0;
+  auto build = [&](int world) {
+    Map m;
+    auto add = [&](const char* coll, const char* name, uint64_t lo, uint64_t hi) { m[coll][name] = dummyAlgo(name, coll, lo, hi, &calls); };
+    add("allreduce", "default_allreduce_packet", 0, 8u << 20);
+    add("allreduce", "default_allreduce_nvls_packet", 0, 8u << 20);
+    add("allreduce", "default_allreduce_packet_ll128", 0, world <= 2 ? (4u << 20) : (world <= 4 ? (512u << 10) : (256u << 10)));
+    add("allreduce", "default_allreduce_nvls_zero_copy", 0, UINT64_MAX);
+    add("allreduce", "default_allreduce_rsag_zero_copy", 0, UINT64_MAX);
+    add("allreduce", "default_allreduce_nvls_warp_pipeline", 0, UINT64_MAX);
+    add("allreduce", "default_allreduce_nvls_block_pipeline", 0, UINT64_MAX);
+    add("allreduce", "default_allreduce_rsag", 0, 64u << 20);
+    add("allreduce", "default_allreduce_rsag_pipeline", 0, UINT64_MAX);
+    add("allgather", "default_allgather_fullmesh2", 0, UINT64_MAX);
+    add("reducescatter", "default_reducescatter_zero_copy", 0, UINT64_MAX);
+    add("alltoall", "default_alltoall", 0, UINT64_MAX);
+    add("broadcast", "default_broadcast", 0, UINT64_MAX);
+    return m;
+  };
+  auto pick = [&](const Map& m, const char* coll, int world, size_t bytes, bool symmetric) -> std::string {
+    CollectiveRequest req;
+    req.collective = coll;
+    req.worldSize = world;
+    req.messageSize = bytes;
+    req.symmetricMemory = symmetric;
+    auto a = collective::selectDefaultAlgorithm(m, req);
+    return a ? a->name() : std::string("(none)");
+  };
+  const Map m8 = build(8), m2 = build(2);
+  EXPECT_EQ(pick(m8, "allreduce", 8, 1u << 10, true), std::string("default_allreduce_nvls_packet"));
+  EXPECT_EQ(pick(m8, "allreduce", 8, 64u << 10, true), std::string("default_allreduce_nvls_packet"));
+  EXPECT_EQ(pick(m8, "allreduce", 8, 128u << 10, true), std::string("default_allreduce_packet_ll128"));
+  EXPECT_EQ(pick(m8, "allreduce", 8, 256u << 10, true), std::string("default_allreduce_packet_ll128"));
+  EXPECT_EQ(pick(m8, "allreduce", 8, 512u << 10, true), std::string("default_allreduce_nvls_zero_copy"));
+  EXPECT_EQ(pick(m8, "allreduce", 8, 256u << 20, true), std::string("default_allreduce_nvls_zero_copy"));
+  // two ranks: lines up to 4 MB, then plain peer loads and stores (the switch has nothing to combine)
+  EXPECT_EQ(pick(m2, "allreduce", 2, 2u << 20, true), std::string("default_allreduce_packet_ll128"));
+  EXPECT_EQ(pick(m2, "allreduce", 2, 8u << 20, true), std::string("default_allreduce_rsag_zero_copy"));
+  // buffers outside the heap: the pipelined kernels
+  EXPECT_EQ(pick(m8, "allreduce", 8, 2u << 20, false), std::string("default_allreduce_nvls_warp_pipeline"));
+  EXPECT_EQ(pick(m8, "allreduce", 8, 64u << 20, false), std::string("default_allreduce_nvls_block_pipeline"));
+  EXPECT_EQ(pick(m2, "allreduce", 2, 64u << 20, false), std::string("default_allreduce_rsag_pipeline"));
+  // a size that is not a whole number of 16-byte words cannot take the zero-copy kernels
+  EXPECT_EQ(pick(m8, "allreduce", 8, (64u << 20) + 2, true), std::string("default_allreduce_nvls_block_pipeline"));
+  // the other collectives: divisibility by 16 bytes per rank, else nothing (the caller falls back)
+  EXPECT_EQ(pick(m8, "allgather", 8, 1u << 20, true), std::string("default_allgather_fullmesh2"));
+  EXPECT_EQ(pick(m8, "reducescatter", 8, 1u << 20, true), std::string("default_reducescatter_zero_copy"));
+  EXPECT_EQ(pick(m8, "reducescatter", 8, (1u << 20) + 16, true), std::string("(none)"));
+  EXPECT_EQ(pick(m8, "alltoall", 8, 1u << 20, true), std::string("default_alltoall"));
+  EXPECT_EQ(pick(m8, "broadcast", 8, 12345, true), std::string("default_broadcast"));
+  EXPECT_EQ(pick(m8, "scan", 8, 1024, true), std::string("(none)"));
+  // without a multicast mapping the switch algorithms are not registered: packets and peer loads take over
+  Map plain = build(8);
+  plain["allreduce"].erase("default_allreduce_nvls_packet");
+  plain["allreduce"].erase("default_allreduce_nvls_zero_copy");
+  plain["allreduce"].erase("default_allreduce_nvls_warp_pipeline");
+  plain["allreduce"].erase("default_allreduce_nvls_block_pipeline");
+  EXPECT_EQ(pick(plain, "allreduce", 8, 1u << 10, true), std::string("default_allreduce_packet"));
+  EXPECT_EQ(pick(plain, "allreduce", 8, 64u << 20, true), std::string("default_allreduce_rsag_zero_copy"));
+  EXPECT_EQ(pick(plain, "allreduce", 8, 2u << 20, false), std::string("default_allreduce_rsag"));
+  EXPECT_EQ(pick(plain, "allreduce", 8, 64u << 20, false), std::string("default_allreduce_rsag_pipeline"));
 }
 
 TEST(AlgorithmCollection, RegistrySelectorsAndExtend) {
