@@ -88,7 +88,11 @@ def main(argv=None) -> int:
     if not rows:
         print("no timed sizes in the result", file=sys.stderr)
         return 2
-    path = args.baseline or default_baseline(rows[0]["collective"], int(rows[0]["world"]))
+    # the shipped baseline of the result's element type when there is one (bf16 for every world size, fp16 for some)
+    short = {"bfloat16": "bf16", "float16": "fp16", "float32": "fp32"}.get(result.get("dtype", "bfloat16") if isinstance(result, dict) else "bfloat16", "bf16")
+    path = args.baseline or default_baseline(rows[0]["collective"], int(rows[0]["world"]), short)
+    if not args.baseline and not os.path.exists(path):
+        path = default_baseline(rows[0]["collective"], int(rows[0]["world"]))
     if not os.path.exists(path):
         print(f"no baseline file {path}", file=sys.stderr)
         return 2

@@ -57,3 +57,22 @@ def test_shipped_baseline_is_well_formed():
             for (_, _, b), v in table.items()]
     report, compared = check_perf.compare(rows, table)
     assert compared == len(rows) and all(r["status"] == "ok" for r in report)
+
+
+def test_shipped_baselines_cover_2_4_8_gpus_and_the_gate_picks_by_dtype(tmp_path, capsys):
+    import os
+
+    for world in (2, 4, 8):
+        table = check_perf.load_baseline(check_perf.default_baseline("allreduce", world))
+        sizes = sorted(k[2] for k in table)
+        assert len(sizes) == 21 and sizes[0] == 1024 and sizes[-1] == 1 << 30  # powers of two, 1 KB - 1 GB
+    assert os.path.exists(check_perf.default_baseline("allreduce", 2, "fp16"))
+    # a float16 result of two ranks is compared with the fp16 file; an element type without a file falls back to bf16
+    base = check_perf.load_baseline(check_perf.default_baseline("allreduce", 2, "fp16"))
+    rows = [{"bytes": b, "best_us": v["time_us"], "busbw_gbs": v["busbw_gbs"], "algorithms": {}} for (_, _, b), v in base.items()]
+    for dtype in ("float16", "float32"):
+        res = tmp_path / f"{dtype}.json"
+        res.write_text(json.dumps({"collective": "allreduce", "world": 2, "dtype": dtype, "rows": rows}))
+        rc = check_perf.main([str(res), "--latency-tol", "0.5", "--bandwidth-tol", "0.5"])
+        assert rc == 0
+    capsys.readouterr()
