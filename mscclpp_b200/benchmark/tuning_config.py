@@ -35,6 +35,23 @@ class TuningConfig:
                 return r
         return rows[-1] if rows else None
 
+    def record_bench_result(self, profile: str, result: dict) -> int:
+        """Takes the best algorithm of every size from a `bench_collective --json` result (default launch shapes). Returns
+        the number of sizes recorded. The stores shipped in `benchmark/baselines/tuned_b200.json` were made this way from
+        the measured ladders."""
+        n = 0
+        for row in result.get("rows", []):
+            if "best" not in row:
+                continue
+            self.record(profile, result["collective"], result["dtype"], row["bytes"], row["best"], 0, 0, row["best_us"])
+            n += 1
+        return n
+
+    @staticmethod
+    def shipped() -> "TuningConfig":
+        """The store measured on B200 machines of 2, 4 and 8 GPUs that comes with the package."""
+        return TuningConfig(os.path.join(os.path.dirname(os.path.abspath(__file__)), "baselines", "tuned_b200.json"))
+
     def save(self, path: Optional[str] = None) -> str:
         path = path or self.path
         if not path:

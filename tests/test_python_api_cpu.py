@@ -181,6 +181,29 @@ def test_npkit_trace_generator(tmp_path):
     assert abs(wr["dur"] - 1.0) < 1e-6 and wr["tid"] == "channel0"
 
 
+def test_shipped_tuning_store_and_its_selector():
+    """The store measured on 2, 4 and 8 B200s: every size has an entry, and the selector made from it hands out the
+    recorded algorithm."""
+    from types import SimpleNamespace
+
+    from mscclpp_b200.benchmark.tuning_config import TuningConfig
+
+    store = TuningConfig.shipped()
+    for world in (2, 4, 8):
+        profile = f"NVIDIA_B200-x{world}-nvls"
+        rows = store.data[profile]["allreduce/bfloat16"]
+        assert len(rows) == 21 and rows[0]["max_bytes"] == 1024 and rows[-1]["max_bytes"] == 1 << 30
+        assert store.lookup(profile, "allreduce", "bfloat16", 1 << 30)["algorithm"].endswith("zero_copy")
+        assert "packet" in store.lookup(profile, "allreduce", "bfloat16", 2048)["algorithm"]
+    selector = store.make_selector("NVIDIA_B200-x8-nvls")
+    request = SimpleNamespace(collective="allreduce", dtype=SimpleNamespace(name="bfloat16"), message_size=128 << 10)
+    algo_map = {"allreduce": {"default_allreduce_packet_ll128": "LL128", "default_allreduce_nvls_zero_copy": "NVLS"}}
+    assert selector(algo_map, request) == "LL128"
+    request.message_size = 64 << 20
+    assert selector(algo_map, request) == "NVLS"
+    assert store.make_selector("some-other-gpu")(algo_map, request) is None
+
+
 def test_tuning_config_store(tmp_path):
     from mscclpp_b200.benchmark.tuning_config import TuningConfig
 
