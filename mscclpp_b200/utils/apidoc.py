@@ -173,7 +173,7 @@ def generate() -> str:
     out: List[str] = []
     out.append("# API reference\n")
     out.append("Generated by `python -m mscclpp_b200.utils.apidoc` from the package itself; do not edit by hand. Guides: "
-               "`quickstart.md`, `tutorials.md`, `fused-layers.md`, `dsl.md`, `nccl-shim.md`, `tracing.md`, `api-parity.md`.\n")
+               "`quickstart.md`, `tutorials.md`, `torch-integration.md`, `fused-layers.md`, `dsl.md`, `nccl-shim.md`, `tracing.md`, `api-parity.md`.\n")
     out.append("## Python\n")
     for modname, title in PYTHON_MODULES:
         describe_module(modname, title, out)
